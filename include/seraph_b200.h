@@ -1,0 +1,219 @@
+/*
+ * seraph_b200.h - C ABI of libseraph_b200.so.
+ *
+ * Part 1 and 2 are the entry points Seraph's own programs bind for the
+ * training path (its headers include/train_cuda.h and
+ * include/cuda_train_context.h, implementation src/train_cuda.c and
+ * src/cuda_train_context.cu); names, argument meaning and return conventions
+ * are theirs, so `seraph-train-cuda` links against this library in place of
+ * cuda_train_context.o / train_cuda.o / cuda_profiler.o.  Part 3 is the
+ * profiler ABI (include/cuda_profiler.h).  Part 4 are additions that have no
+ * counterpart in the reference.
+ *
+ * Everything runs on an NVIDIA B200 (sm_100a).  There is no CPU path: without
+ * a device cuda_train_init() returns NULL and nothing else may be called.
+ * All tensors are FP32, row-major, token-major: activations [T, dim] with
+ * heads contiguous inside a row, weights [out_dim, in_dim]; packed batches
+ * are concatenated sequences with seq_starts[B+1] prefix sums (uint32 on the
+ * device, int on the host side of the step functions).
+ */
+#ifndef SERAPH_B200_H
+#define SERAPH_B200_H
+
+#include "seraph_b200_abi.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ===== 1. step-level API (reference: include/train_cuda.h:12-64) ========== */
+
+/* src/cuda_train_context.cu:2246.  NULL when no sm_100 device can be used. */
+cuda_train_context_t* cuda_train_init(int device_id);
+/* src/cuda_train_context.cu:2404 */
+void cuda_train_free(cuda_train_context_t* ctx);
+/* src/cuda_train_context.cu:2559 */
+void cuda_train_sync(cuda_train_context_t* ctx);
+/* src/cuda_train_context.cu:2387 */
+void cuda_train_get_gpu_info(cuda_train_context_t* ctx, char* name, int name_len, float* memory_gb);
+
+/* One full-weight step on one sequence: forward, loss, backward, AdamW when the
+ * accumulation count is reached.  Returns the mean loss, -1.0f on bad
+ * arguments or allocation failure, 0.0f when nothing is predicted.
+ * src/train_cuda.c:597 */
+float cuda_train_step_gpu_full(train_state_t* state, int* tokens, int num_tokens, cuda_train_context_t* ctx);
+/* Packed batch of `batch_size` sequences.  src/train_cuda.c:1966 */
+float cuda_train_step_gpu_full_batch(train_state_t* state, int* tokens_packed, int total_tokens,
+                                     int* seq_starts, int batch_size, cuda_train_context_t* ctx);
+/* LoRA steps: frozen base, adapter gradients by the complete chain rule of the
+ * reference's Vulkan LoRA step (src/train.c:5847, backward :6287-6615).  The
+ * frozen base is taken from state->full_weights.  src/train_cuda.c:1599, :2332 */
+float cuda_train_step_gpu_lora(train_state_t* state, int* tokens, int num_tokens, cuda_train_context_t* ctx);
+float cuda_train_step_gpu_lora_batch(train_state_t* state, int* tokens_packed, int total_tokens,
+                                     int* seq_starts, int batch_size, cuda_train_context_t* ctx);
+/* src/train_cuda.c:1244 (weights and Adam moments) and :1317 (gradients) back into state->full_weights */
+void cuda_download_full_weights(cuda_train_context_t* ctx, train_state_t* state);
+void cuda_download_gpu_gradients(cuda_train_context_t* ctx, train_state_t* state);
+/* src/train_cuda.c:2677 and :2812 */
+float cuda_eval_forward(train_state_t* state, int* tokens, int num_tokens, cuda_train_context_t* ctx);
+float cuda_evaluate(train_state_t* state, int* val_tokens, int num_val_tokens, int* offsets, int num_samples,
+                    int max_seq_len, int max_eval_samples, cuda_train_context_t* ctx, float* out_perplexity);
+
+/* ===== 2. op-level API (reference: include/cuda_train_context.h:239-325) === */
+
+/* buffers: src/cuda_train_context.cu:2568-2640 */
+cuda_buffer_t* cuda_train_buffer_create(cuda_train_context_t* ctx, size_t size);
+void cuda_train_buffer_free(cuda_train_context_t* ctx, cuda_buffer_t* buf);
+void cuda_train_buffer_upload(cuda_train_context_t* ctx, cuda_buffer_t* buf, const float* data, size_t count);
+void cuda_train_buffer_upload_u32(cuda_train_context_t* ctx, cuda_buffer_t* buf, const uint32_t* data, size_t count);
+void cuda_train_buffer_download(cuda_train_context_t* ctx, cuda_buffer_t* buf, float* data, size_t count);
+void cuda_train_buffer_download_bytes(cuda_train_context_t* ctx, cuda_buffer_t* buf, void* data, size_t bytes);
+void cuda_train_fill_buffer(cuda_train_context_t* ctx, cuda_buffer_t* buf, uint32_t value, size_t bytes);
+void cuda_train_fill_buffer_range(cuda_train_context_t* ctx, cuda_buffer_t* buf, size_t offset, uint32_t value, size_t bytes);
+void cuda_train_copy_buffer(cuda_train_context_t* ctx, cuda_buffer_t* src, cuda_buffer_t* dst, size_t bytes);
+
+/* forward ops */
+void cuda_train_matmul(cuda_train_context_t* ctx, cuda_buffer_t* A, cuda_buffer_t* B, cuda_buffer_t* C, int M, int N, int K);                 /* :2697 */
+void cuda_train_matmul_transpose(cuda_train_context_t* ctx, cuda_buffer_t* A, cuda_buffer_t* B, cuda_buffer_t* C, int M, int N, int K,
+                                 int transpose_A, int transpose_B, int accumulate);                                                             /* :2702 */
+void cuda_train_silu(cuda_train_context_t* ctx, cuda_buffer_t* input, cuda_buffer_t* output, size_t count);                                     /* :2711 */
+void cuda_train_rmsnorm(cuda_train_context_t* ctx, cuda_buffer_t* input, cuda_buffer_t* scale, cuda_buffer_t* output, int rows, int cols, float eps);
+void cuda_train_softmax(cuda_train_context_t* ctx, cuda_buffer_t* input, cuda_buffer_t* output, int rows, int cols);
+void cuda_train_rope(cuda_train_context_t* ctx, cuda_buffer_t* x_in, cuda_buffer_t* x_out, int seq_len, int num_heads, int head_dim, float rope_theta);
+void cuda_train_add(cuda_train_context_t* ctx, cuda_buffer_t* A, cuda_buffer_t* B, cuda_buffer_t* C, size_t count);
+void cuda_train_mul(cuda_train_context_t* ctx, cuda_buffer_t* A, cuda_buffer_t* B, cuda_buffer_t* C, size_t count);
+void cuda_train_scale(cuda_train_context_t* ctx, cuda_buffer_t* A, size_t count, float alpha);
+void cuda_train_batch_attention(cuda_train_context_t* ctx, cuda_buffer_t* Q, cuda_buffer_t* K, cuda_buffer_t* V, cuda_buffer_t* out,
+                                cuda_buffer_t* lse_out, int seq_len, int num_heads, int kv_heads, int head_dim);
+void cuda_train_batch_attention_packed(cuda_train_context_t* ctx, cuda_buffer_t* Q, cuda_buffer_t* K, cuda_buffer_t* V, cuda_buffer_t* out,
+                                       cuda_buffer_t* lse_out, cuda_buffer_t* seq_starts, int total_tokens, int batch_size,
+                                       int num_heads, int kv_heads, int head_dim, int max_seq_in_batch);
+void cuda_train_embed_lookup(cuda_train_context_t* ctx, cuda_buffer_t* tokens_u32, cuda_buffer_t* embed_weight, cuda_buffer_t* out_hidden,
+                             int seq_len, int hidden_size, int vocab_size);
+void cuda_train_rope_packed(cuda_train_context_t* ctx, cuda_buffer_t* x_in, cuda_buffer_t* x_out, cuda_buffer_t* seq_starts,
+                            int total_tokens, int batch_size, int num_heads, int head_dim, float rope_theta);
+
+/* loss + backward ops */
+void cuda_train_cross_entropy_grad(cuda_train_context_t* ctx, cuda_buffer_t* logits, cuda_buffer_t* targets_u32, cuda_buffer_t* grad_logits,
+                                   cuda_buffer_t* loss_rows, int rows, int cols);                                                               /* :2941, kernel :1566 */
+void cuda_train_cross_entropy_grad_packed(cuda_train_context_t* ctx, cuda_buffer_t* logits, cuda_buffer_t* targets_u32,
+                                          cuda_buffer_t* grad_logits, cuda_buffer_t* loss_rows, cuda_buffer_t* seq_starts,
+                                          int total_tokens, int batch_size, int vocab_size, int num_valid_predictions);                        /* :3171, kernel :1657 */
+void cuda_train_reduce_sum(cuda_train_context_t* ctx, cuda_buffer_t* in_buf, cuda_buffer_t* out_buf, size_t count);                             /* :2966 */
+void cuda_train_silu_backward(cuda_train_context_t* ctx, cuda_buffer_t* input, cuda_buffer_t* grad_output, cuda_buffer_t* grad_input, size_t count);   /* :2978 */
+void cuda_train_elementwise_mul_backward(cuda_train_context_t* ctx, cuda_buffer_t* A, cuda_buffer_t* B, cuda_buffer_t* grad_C,
+                                         cuda_buffer_t* grad_A, cuda_buffer_t* grad_B, size_t count);                                           /* :2989 */
+void cuda_train_rmsnorm_backward_batch(cuda_train_context_t* ctx, cuda_buffer_t* input, cuda_buffer_t* scale, cuda_buffer_t* grad_output,
+                                       cuda_buffer_t* grad_input, cuda_buffer_t* grad_scale, int rows, int cols, float eps);                    /* :3001, kernel :1767 */
+void cuda_train_rope_backward(cuda_train_context_t* ctx, cuda_buffer_t* x_in, cuda_buffer_t* x_out, int seq_len, int num_heads, int head_dim, float rope_theta);
+void cuda_train_rope_backward_packed(cuda_train_context_t* ctx, cuda_buffer_t* x_in, cuda_buffer_t* x_out, cuda_buffer_t* seq_starts,
+                                     int total_tokens, int batch_size, int num_heads, int head_dim, float rope_theta);                          /* kernel :679 */
+void cuda_train_batch_attention_backward(cuda_train_context_t* ctx, cuda_buffer_t* Q, cuda_buffer_t* K, cuda_buffer_t* V,
+                                         cuda_buffer_t* attn_out, cuda_buffer_t* lse, cuda_buffer_t* grad_out,
+                                         cuda_buffer_t* grad_Q, cuda_buffer_t* grad_K, cuda_buffer_t* grad_V,
+                                         int seq_len, int num_heads, int kv_heads, int head_dim);                                               /* :3041 */
+void cuda_train_batch_attention_backward_packed(cuda_train_context_t* ctx, cuda_buffer_t* Q, cuda_buffer_t* K, cuda_buffer_t* V,
+                                                cuda_buffer_t* attn_out, cuda_buffer_t* lse, cuda_buffer_t* grad_out,
+                                                cuda_buffer_t* grad_Q, cuda_buffer_t* grad_K, cuda_buffer_t* grad_V,
+                                                cuda_buffer_t* seq_starts, int total_tokens, int batch_size,
+                                                int num_heads, int kv_heads, int head_dim, int max_seq_in_batch);                               /* :3107, kernels :1013/:2012 */
+void cuda_train_embedding_backward(cuda_train_context_t* ctx, cuda_buffer_t* tokens_u32, cuda_buffer_t* grad_hidden, cuda_buffer_t* grad_embed,
+                                   int seq_len, int hidden_size, int vocab_size);                                                               /* :3192, kernel :2175 */
+void cuda_train_adamw_update(cuda_train_context_t* ctx, cuda_buffer_t* weight, cuda_buffer_t* grad, cuda_buffer_t* m, cuda_buffer_t* v,
+                             float lr, float beta1, float beta2, float weight_decay, float eps, int step, size_t size,
+                             const char* tensor_name, int rows, int cols);                                                                      /* :3203, kernel :2187 */
+void cuda_train_nan_check(cuda_train_context_t* ctx, cuda_buffer_t* input, size_t count_floats, cuda_buffer_t* flags_u32, uint32_t flag_index);
+void cuda_train_set_profiler(cuda_train_context_t* ctx, cuda_profiler_t* prof);
+
+/* LoRA: src/cuda_train_context.cu:3240-3394 */
+void cuda_train_lora_backward(cuda_train_context_t* ctx, cuda_buffer_t* grad_output, cuda_buffer_t* input, cuda_buffer_t* A, cuda_buffer_t* B,
+                              cuda_buffer_t* gA, cuda_buffer_t* gB, cuda_buffer_t* hidden_tmp,
+                              int seq_len, int in_dim, int out_dim, int rank, float scale);
+void cuda_train_zero_lora_grads(cuda_train_context_t* ctx);
+void cuda_download_lora_weights(cuda_train_context_t* ctx, void* lora /* lora_model_t* */);
+
+/* ===== 3. profiler (reference: include/cuda_profiler.h:53-82) ============== */
+cuda_profiler_t* cuda_profiler_create(void);
+void cuda_profiler_destroy(cuda_profiler_t* prof);
+void cuda_profiler_enable(cuda_profiler_t* prof);
+void cuda_profiler_disable(cuda_profiler_t* prof);
+void cuda_profiler_reset(cuda_profiler_t* prof);
+int  cuda_profiler_begin_op(cuda_profiler_t* prof, const char* name, void* stream);
+void cuda_profiler_end_op(cuda_profiler_t* prof, int op_idx, void* stream);
+void cuda_profiler_set_launch(cuda_profiler_t* prof, int op_idx, int gx, int gy, int gz, int bx, int by, int bz, size_t shared_mem);
+void cuda_profiler_set_flops(cuda_profiler_t* prof, int op_idx, size_t flops);
+void cuda_profiler_set_bytes(cuda_profiler_t* prof, int op_idx, size_t bytes);
+void cuda_profiler_sync_and_analyze(cuda_profiler_t* prof, void* stream);
+void cuda_profiler_print(cuda_profiler_t* prof);
+void cuda_profiler_print_top(cuda_profiler_t* prof, int top_n);
+void cuda_profiler_set_log(cuda_profiler_t* prof, void* file_ptr);
+
+/* ===== 4. additions (no counterpart in the reference) ====================== */
+
+/* Status of the calls since the last query: 0 ok, 1 bad argument, 2 CUDA error,
+ * 3 out of memory, 4 token id outside the vocabulary reached a kernel, 5 a
+ * bounded wait ran out, 6 NCCL error, 7 size beyond a fixed capacity.
+ * Synchronises the stream, reads the device status word, clears both. */
+int seraph_b200_last_status(cuda_train_context_t* ctx);
+/* GEMM arithmetic: 0 = FP32-accurate on tensor cores (three TF32 passes on a
+ * hi/lo split, default), 1 = single-pass TF32, 2 = BF16 (also selected by
+ * ctx->use_bf16), 3 = FP32 FMA on CUDA cores. */
+int seraph_b200_set_gemm_mode(cuda_train_context_t* ctx, int mode);
+/* 0 (default): LoRA steps leave the adapters' own term out of dX, as the
+ * reference does; 1: full chain rule, dX += s (dY B) A. */
+int seraph_b200_set_lora_exact(cuda_train_context_t* ctx, int exact);
+/* Global-norm gradient clipping before AdamW; 0 switches it off (default: the
+ * reference clips nothing). */
+int seraph_b200_set_grad_clip(cuda_train_context_t* ctx, float max_norm);
+/* Kernels launched by this library on ctx since the last reset. */
+unsigned long long seraph_b200_launch_count(cuda_train_context_t* ctx, int reset);
+/* Integer tables of the last cuda_train_embedding_backward(seq_len=T, vocab=V):
+ * occurring rows in ascending order, their token counts, and the token
+ * positions sorted by (row, position).  Returns the number of rows or -1. */
+int seraph_b200_embedding_segments(cuda_train_context_t* ctx, int T, int V, int* rows_out, int* counts_out, int* sorted_pos_out);
+/* Fused SwiGLU: out = silu(gate)*up; backward gives dgate and dup from gate, up, dout. */
+void seraph_b200_swiglu(cuda_train_context_t* ctx, cuda_buffer_t* gate, cuda_buffer_t* up, cuda_buffer_t* out, size_t count);
+void seraph_b200_swiglu_backward(cuda_train_context_t* ctx, cuda_buffer_t* gate, cuda_buffer_t* up, cuda_buffer_t* grad_out,
+                                 cuda_buffer_t* grad_gate, cuda_buffer_t* grad_up, size_t count);
+/* CUDA-event timer on the context's stream: start, then stop returns milliseconds. */
+void seraph_b200_timer_start(cuda_train_context_t* ctx);
+float seraph_b200_timer_stop(cuda_train_context_t* ctx);
+/* Forget the resident weights, adapters and optimizer state: the next step uploads them again from
+ * the host state (like the reference, a context otherwise uploads once and then only downloads). */
+int seraph_b200_reset_model(cuda_train_context_t* ctx);
+/* Logits [T, vocab] of the last step or evaluation, copied to host memory. */
+int seraph_b200_download_logits(cuda_train_context_t* ctx, float* out, int T);
+
+/* Data parallel over NCCL: rank 0 makes the 128-byte id, every rank calls init
+ * with it before its first step; steps then all-reduce gradient buckets while
+ * backward still runs and AdamW applies the mean.  wait() is a host-side wait
+ * with a time limit that aborts the communicator instead of hanging. */
+int seraph_dp_get_unique_id(void* id_out_128);
+int seraph_dp_init(cuda_train_context_t* ctx, int rank, int world, const void* nccl_unique_id);
+void seraph_dp_finalize(cuda_train_context_t* ctx);
+int seraph_dp_wait(cuda_train_context_t* ctx, int timeout_ms);
+int seraph_dp_world(cuda_train_context_t* ctx);
+
+/* A train_state_t built in memory from flat float arrays, for callers that hold
+ * the weights already (the reference only builds one from a model directory,
+ * src/train.c:7854).  Flat parameter order: embed [V,d], final_norm [d], then
+ * per layer q, k, v, o, gate, up, down, in_norm, post_norm.  `which`: 0
+ * weights, 1 gradients, 2 Adam m, 3 Adam v.  LoRA mask bits: 0 q, 1 k, 2 v,
+ * 3 o, 4 gate, 5 up, 6 down; flat LoRA order: per layer, per selected adapter,
+ * A [r,in] then B [out,r]. */
+train_state_t* seraph_b200_state_create(int V, int d, int L, int Hq, int Hkv, int hd, int F, float theta, float lr, int accum);
+void seraph_b200_state_free(train_state_t* st);
+size_t seraph_b200_state_param_count(train_state_t* st);
+void seraph_b200_state_set(train_state_t* st, int which, const float* flat);
+void seraph_b200_state_get(train_state_t* st, int which, float* flat);
+void seraph_b200_state_set_counters(train_state_t* st, int optimizer_step, int accumulation_counter);
+void seraph_b200_state_get_counters(train_state_t* st, int* optimizer_step, int* accumulation_counter);
+void seraph_b200_state_set_lr(train_state_t* st, float lr, int accum);
+size_t seraph_b200_state_lora_count(train_state_t* st, int rank, int mask);
+int seraph_b200_state_attach_lora(train_state_t* st, int rank, float alpha, int mask, const float* flat);
+void seraph_b200_state_lora_get(train_state_t* st, int which, float* flat);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

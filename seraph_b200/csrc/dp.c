@@ -1,0 +1,156 @@
+/*
+ * dp.c - data parallelism for the training step: one process per GPU, every
+ * rank holds the full model and runs the step on its own micro-batch; the
+ * gradients are summed with NCCL all-reduce over NVLink.  The reference has no
+ * multi-GPU code at all, so these entry points have no counterpart there.
+ *
+ * Gradients live in one arena, so a bucket is a plain range.  During backward
+ * the step hands over each finished range (a layer, last the embedding and the
+ * final norm); the all-reduce of a bucket runs on a second stream while the
+ * next layer's backward computes.  AdamW waits for the last bucket and folds
+ * 1/world into its gradient read.
+ *
+ * NCCL is loaded at run time (dlopen of libnccl.so.2), so single-GPU users do
+ * not need it, and a process that already holds NCCL (for example through
+ * torch) shares that copy.  Errors are reported through the status code; a
+ * failed or timed-out communicator is aborted on the host, never waited on
+ * forever.
+ */
+#include <cuda_runtime_api.h>
+#include <dlfcn.h>
+#include <nccl.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <time.h>
+#include "sb_internal.h"
+
+static struct {
+    void* lib;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*);
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int);
+    ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t);
+    ncclResult_t (*CommDestroy)(ncclComm_t);
+    ncclResult_t (*CommAbort)(ncclComm_t);
+    ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*);
+    const char* (*GetErrorString)(ncclResult_t);
+} N;
+
+static int load_nccl(void) {
+    if (N.lib) return 0;
+    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) { fprintf(stderr, "seraph_b200: cannot load NCCL: %s\n", dlerror()); return 1; }
+#define SYM(f) do { *(void**)(&N.f) = dlsym(h, "nccl" #f); if (!N.f) { fprintf(stderr, "seraph_b200: NCCL lacks nccl" #f "\n"); dlclose(h); return 1; } } while (0)
+    SYM(GetUniqueId); SYM(CommInitRank); SYM(AllReduce); SYM(CommDestroy); SYM(CommAbort); SYM(CommGetAsyncError); SYM(GetErrorString);
+#undef SYM
+    N.lib = h;
+    return 0;
+}
+
+static int nccl_fail(sb_ctx_t* c, ncclResult_t r, const char* what) {
+    if (r == ncclSuccess) return 0;
+    fprintf(stderr, "seraph_b200: NCCL error in %s: %s\n", what, N.GetErrorString ? N.GetErrorString(r) : "?");
+    c->status = SB_ERR_NCCL;
+    return 1;
+}
+
+/* 128-byte id made on rank 0 and carried to the other ranks by the caller */
+int seraph_dp_get_unique_id(void* id_out_128) {
+    if (!id_out_128 || load_nccl()) return SB_ERR_NCCL;
+    ncclUniqueId id;
+    if (N.GetUniqueId(&id) != ncclSuccess) return SB_ERR_NCCL;
+    memcpy(id_out_128, &id, sizeof id);
+    return SB_OK;
+}
+
+int seraph_dp_init(cuda_train_context_t* ctx, int rank, int world, const void* nccl_unique_id) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c || world < 1 || rank < 0 || rank >= world) return SB_ERR_ARG;
+    if (world == 1) { c->dp_world = 1; c->dp_rank = 0; return SB_OK; }
+    if (!nccl_unique_id || load_nccl()) return SB_ERR_NCCL;
+    if (cudaSetDevice(ctx->device_id) != cudaSuccess) return SB_ERR_CUDA;
+    ncclUniqueId id; memcpy(&id, nccl_unique_id, sizeof id);
+    ncclComm_t comm;
+    if (nccl_fail(c, N.CommInitRank(&comm, world, id, rank), "ncclCommInitRank")) return SB_ERR_NCCL;
+    cudaStream_t cs;
+    if (cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking) != cudaSuccess) { N.CommAbort(comm); return SB_ERR_CUDA; }
+    c->nccl_comm = comm; c->comm_stream = cs; c->dp_rank = rank; c->dp_world = world;
+    for (int i = 0; i < 64; i++) { cudaEvent_t e; cudaEventCreateWithFlags(&e, cudaEventDisableTiming); c->ev_bucket[i] = e; }
+    return SB_OK;
+}
+
+void sb_dp_finalize(sb_ctx_t* c) {
+    if (!c || !c->nccl_comm) return;
+    cudaStreamSynchronize((cudaStream_t)c->comm_stream);
+    N.CommDestroy((ncclComm_t)c->nccl_comm);
+    for (int i = 0; i < 64; i++) if (c->ev_bucket[i]) cudaEventDestroy((cudaEvent_t)c->ev_bucket[i]);
+    cudaStreamDestroy((cudaStream_t)c->comm_stream);
+    c->nccl_comm = NULL; c->comm_stream = NULL; c->dp_world = 1; c->dp_rank = 0;
+}
+void seraph_dp_finalize(cuda_train_context_t* ctx) { sb_dp_finalize(sb_priv(ctx)); }
+
+/* Hand a finished gradient range to the communication stream.  Ordering: the
+ * compute stream records an event, the communication stream waits for it. */
+int sb_dp_bucket_ready(sb_ctx_t* c, float* p, size_t n) {
+    if (c->dp_world <= 1 || !n) return 0;
+    cudaEvent_t e = (cudaEvent_t)c->ev_bucket[c->n_buckets & 63];
+    c->n_buckets++;
+    if (sb_check(c, cudaEventRecord(e, (cudaStream_t)c->pub.stream), "bucket event")) return 1;
+    if (sb_check(c, cudaStreamWaitEvent((cudaStream_t)c->comm_stream, e, 0), "bucket wait")) return 1;
+    return nccl_fail(c, N.AllReduce(p, p, n, ncclFloat32, ncclSum, (ncclComm_t)c->nccl_comm, (cudaStream_t)c->comm_stream), "ncclAllReduce");
+}
+
+/* compute stream waits until every bucket handed over so far is reduced */
+int sb_dp_join(sb_ctx_t* c) {
+    if (c->dp_world <= 1) return 0;
+    cudaEvent_t e = (cudaEvent_t)c->ev_bucket[63];
+    if (sb_check(c, cudaEventRecord(e, (cudaStream_t)c->comm_stream), "join event")) return 1;
+    if (sb_check(c, cudaStreamWaitEvent((cudaStream_t)c->pub.stream, e, 0), "join wait")) return 1;
+    c->n_buckets = 0;
+    ncclResult_t async = ncclSuccess;
+    if (N.CommGetAsyncError((ncclComm_t)c->nccl_comm, &async) != ncclSuccess || async != ncclSuccess) {
+        fprintf(stderr, "seraph_b200: NCCL reported an asynchronous error; aborting the communicator\n");
+        N.CommAbort((ncclComm_t)c->nccl_comm);
+        c->nccl_comm = NULL; c->dp_world = 1; c->status = SB_ERR_NCCL;
+        return 1;
+    }
+    return 0;
+}
+
+/* whole range at once, on the compute stream's order (used when no bucket was handed over during backward) */
+int sb_dp_allreduce_range(sb_ctx_t* c, float* p, size_t n) {
+    if (c->dp_world <= 1) return 0;
+    if (sb_dp_bucket_ready(c, p, n)) return 1;
+    return sb_dp_join(c);
+}
+
+int sb_dp_allreduce_scalar(sb_ctx_t* c, float* p) { return sb_dp_allreduce_range(c, p, 1); }
+
+/* Host-side bounded wait for the communication stream: polls the stream and the
+ * communicator's asynchronous error until done or `timeout_ms` passed; on
+ * time-out or error the communicator is aborted and an error is returned. */
+int seraph_dp_wait(cuda_train_context_t* ctx, int timeout_ms) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c) return SB_ERR_ARG;
+    if (c->dp_world <= 1 || !c->nccl_comm) return SB_OK;
+    struct timespec t0, t; clock_gettime(CLOCK_MONOTONIC, &t0);
+    for (;;) {
+        cudaError_t q = cudaStreamQuery((cudaStream_t)c->comm_stream);
+        if (q == cudaSuccess) return SB_OK;
+        ncclResult_t async = ncclSuccess;
+        N.CommGetAsyncError((ncclComm_t)c->nccl_comm, &async);
+        clock_gettime(CLOCK_MONOTONIC, &t);
+        long ms = (t.tv_sec - t0.tv_sec) * 1000L + (t.tv_nsec - t0.tv_nsec) / 1000000L;
+        if (q != cudaErrorNotReady || async != ncclSuccess || ms > timeout_ms) {
+            fprintf(stderr, "seraph_b200: data-parallel wait failed (%s); aborting the communicator\n",
+                    ms > timeout_ms ? "time-out" : "error");
+            N.CommAbort((ncclComm_t)c->nccl_comm);
+            c->nccl_comm = NULL; c->dp_world = 1; c->status = ms > timeout_ms ? SB_ERR_TIMEOUT : SB_ERR_NCCL;
+            return c->status;
+        }
+        struct timespec nap = {0, 200000}; nanosleep(&nap, NULL);
+    }
+}
+
+int seraph_dp_world(cuda_train_context_t* ctx) { sb_ctx_t* c = sb_priv(ctx); return c ? c->dp_world : 0; }

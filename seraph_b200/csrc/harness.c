@@ -1,0 +1,183 @@
+/*
+ * harness.c - build a train_state_t in memory, without model files or a
+ * tokenizer, from flat float arrays.  The reference only builds one through
+ * train_init() (src/train.c:7854), which needs a model directory; tests,
+ * benchmarks and embedders that already hold the weights use this instead.
+ *
+ * Flat parameter order: embed [V,d], final_norm [d], then per layer
+ * q [qd,d], k [kvd,d], v [kvd,d], o [d,qd], gate [F,d], up [F,d], down [d,F],
+ * in_norm [d], post_norm [d].  Flat LoRA order: per layer, for each adapter
+ * selected by the mask (bit 0 q, 1 k, 2 v, 3 o, 4 gate, 5 up, 6 down): A [r,in]
+ * then B [out,r].
+ */
+#include <stdlib.h>
+#include <string.h>
+#include "sb_internal.h"
+
+typedef struct {
+    train_state_t st;          /* must stay first: the handle is a train_state_t* */
+    model_config_t cfg;
+    trainable_weights_t w;
+    lora_model_t lora;
+    int lora_mask;
+} harness_t;
+
+static int wt_alloc(weight_tensor_t* t, size_t n) {
+    t->weight = (float*)calloc(n, 4); t->grad = (float*)calloc(n, 4); t->m = (float*)calloc(n, 4); t->v = (float*)calloc(n, 4);
+    t->size = n;
+    return !(t->weight && t->grad && t->m && t->v);
+}
+static void wt_free(weight_tensor_t* t) { free(t->weight); free(t->grad); free(t->m); free(t->v); }
+
+typedef void (*visit_fn)(weight_tensor_t*, void*);
+static void visit(harness_t* h, visit_fn f, void* arg) {
+    f(&h->w.embed_tokens, arg); f(&h->w.final_norm, arg);
+    for (int l = 0; l < h->w.num_layers; l++) {
+        layer_weights_t* y = &h->w.layers[l];
+        f(&y->q_proj, arg); f(&y->k_proj, arg); f(&y->v_proj, arg); f(&y->o_proj, arg);
+        f(&y->gate_proj, arg); f(&y->up_proj, arg); f(&y->down_proj, arg); f(&y->input_norm, arg); f(&y->post_norm, arg);
+    }
+}
+
+train_state_t* seraph_b200_state_create(int V, int d, int L, int Hq, int Hkv, int hd, int F, float theta, float lr, int accum) {
+    if (V <= 0 || d <= 0 || L <= 0 || Hq <= 0 || Hkv <= 0 || hd <= 0 || F <= 0) return NULL;
+    harness_t* h = (harness_t*)calloc(1, sizeof(harness_t));
+    if (!h) return NULL;
+    model_config_t* c = &h->cfg;
+    c->vocab_size = V; c->hidden_size = d; c->num_hidden_layers = L; c->intermediate_size = F;
+    c->num_attention_heads = Hq; c->num_key_value_heads = Hkv; c->head_dim = hd; c->kv_dim = Hkv * hd;
+    c->rms_norm_eps = 1e-5f; c->rope_theta = theta; c->tie_word_embeddings = 1;
+    size_t qd = (size_t)Hq * hd, kvd = (size_t)Hkv * hd;
+    h->w.num_layers = L; h->w.hidden_size = d; h->w.intermediate_size = F; h->w.vocab_size = V;
+    h->w.layers = (layer_weights_t*)calloc((size_t)L, sizeof(layer_weights_t));
+    int bad = !h->w.layers;
+    bad |= wt_alloc(&h->w.embed_tokens, (size_t)V * d); bad |= wt_alloc(&h->w.final_norm, (size_t)d);
+    for (int l = 0; l < L && !bad; l++) {
+        layer_weights_t* y = &h->w.layers[l];
+        bad |= wt_alloc(&y->q_proj, qd * d); bad |= wt_alloc(&y->k_proj, kvd * d); bad |= wt_alloc(&y->v_proj, kvd * d);
+        bad |= wt_alloc(&y->o_proj, (size_t)d * qd); bad |= wt_alloc(&y->gate_proj, (size_t)F * d);
+        bad |= wt_alloc(&y->up_proj, (size_t)F * d); bad |= wt_alloc(&y->down_proj, (size_t)d * F);
+        bad |= wt_alloc(&y->input_norm, (size_t)d); bad |= wt_alloc(&y->post_norm, (size_t)d);
+    }
+    h->st.config = c; h->st.use_full_training = 1; h->st.full_weights = &h->w;
+    h->st.learning_rate = lr; h->st.gradient_accumulation_steps = accum;
+    if (bad) return NULL;
+    h->w.total_params = (size_t)V * d + (size_t)d + (size_t)L * (2 * qd * d + 2 * kvd * d + 3 * (size_t)F * d + 2 * (size_t)d);
+    return &h->st;
+}
+
+static void f_free(weight_tensor_t* t, void* a) { (void)a; wt_free(t); }
+static void lora_free_all(harness_t* h);
+void seraph_b200_state_free(train_state_t* st) {
+    harness_t* h = (harness_t*)st;
+    if (!h) return;
+    lora_free_all(h);
+    visit(h, f_free, NULL);
+    free(h->w.layers);
+    free(h);
+}
+
+static void f_count(weight_tensor_t* t, void* a) { *(size_t*)a += t->size; }
+size_t seraph_b200_state_param_count(train_state_t* st) { size_t n = 0; visit((harness_t*)st, f_count, &n); return n; }
+
+typedef struct { float* flat; int which; int set; } io_t;
+static void f_io(weight_tensor_t* t, void* a) {
+    io_t* io = (io_t*)a;
+    float* p = io->which == 0 ? t->weight : io->which == 1 ? t->grad : io->which == 2 ? t->m : t->v;
+    if (io->set) memcpy(p, io->flat, t->size * 4); else memcpy(io->flat, p, t->size * 4);
+    io->flat += t->size;
+}
+/* which: 0 weights, 1 gradients, 2 Adam m, 3 Adam v */
+void seraph_b200_state_set(train_state_t* st, int which, const float* flat) { io_t io = {(float*)flat, which, 1}; visit((harness_t*)st, f_io, &io); }
+void seraph_b200_state_get(train_state_t* st, int which, float* flat) { io_t io = {flat, which, 0}; visit((harness_t*)st, f_io, &io); }
+
+void seraph_b200_state_set_counters(train_state_t* st, int optimizer_step, int accumulation_counter) {
+    st->optimizer_step = optimizer_step; st->accumulation_counter = accumulation_counter;
+}
+void seraph_b200_state_get_counters(train_state_t* st, int* optimizer_step, int* accumulation_counter) {
+    if (optimizer_step) *optimizer_step = st->optimizer_step;
+    if (accumulation_counter) *accumulation_counter = st->accumulation_counter;
+}
+void seraph_b200_state_set_lr(train_state_t* st, float lr, int accum) { st->learning_rate = lr; st->gradient_accumulation_steps = accum; }
+
+/* ---- LoRA ---- */
+static void dims(const model_config_t* c, int a, int* in, int* out) {
+    int qd = c->num_attention_heads * c->head_dim, kvd = c->num_key_value_heads * c->head_dim;
+    switch (a) {
+        case 0: *in = c->hidden_size; *out = qd; break;
+        case 1: case 2: *in = c->hidden_size; *out = kvd; break;
+        case 3: *in = qd; *out = c->hidden_size; break;
+        case 4: case 5: *in = c->hidden_size; *out = c->intermediate_size; break;
+        default: *in = c->intermediate_size; *out = c->hidden_size; break;
+    }
+}
+static lora_adapter_t*** slot(lora_model_t* m, int a) {
+    switch (a) { case 0: return &m->q_adapters; case 1: return &m->k_adapters; case 2: return &m->v_adapters; case 3: return &m->o_adapters;
+                 case 4: return &m->gate_adapters; case 5: return &m->up_adapters; default: return &m->down_adapters; }
+}
+static void lora_free_all(harness_t* h) {
+    for (int a = 0; a < 7; a++) {
+        lora_adapter_t** ls = *slot(&h->lora, a);
+        if (!ls) continue;
+        for (int l = 0; l < h->lora.num_layers; l++) {
+            lora_adapter_t* ad = ls[l];
+            if (!ad) continue;
+            free(ad->A); free(ad->B); free(ad->grad_A); free(ad->grad_B); free(ad->m_A); free(ad->v_A); free(ad->m_B); free(ad->v_B);
+            free(ad);
+        }
+        free(ls);
+        *slot(&h->lora, a) = NULL;
+    }
+    h->st.lora = NULL; h->lora_mask = 0;
+}
+
+size_t seraph_b200_state_lora_count(train_state_t* st, int rank, int mask) {
+    harness_t* h = (harness_t*)st; size_t n = 0;
+    for (int a = 0; a < 7; a++) if (mask & (1 << a)) { int in, out; dims(&h->cfg, a, &in, &out); n += (size_t)rank * in + (size_t)out * rank; }
+    return n * (size_t)h->cfg.num_hidden_layers;
+}
+
+/* switch the state to LoRA training with adapters taken from `flat` (NULL: zeros) */
+int seraph_b200_state_attach_lora(train_state_t* st, int rank, float alpha, int mask, const float* flat) {
+    harness_t* h = (harness_t*)st;
+    if (!h || rank <= 0 || !(mask & 0x7f)) return 1;
+    lora_free_all(h);
+    int L = h->cfg.num_hidden_layers;
+    lora_model_t* m = &h->lora;
+    m->num_layers = L; m->rank = rank; m->alpha = alpha; m->dropout = 0.f;
+    m->apply_to_q = mask & 1; m->apply_to_k = (mask >> 1) & 1; m->apply_to_v = (mask >> 2) & 1; m->apply_to_o = (mask >> 3) & 1;
+    m->apply_to_ffn = (mask >> 4) & 7 ? 1 : 0;
+    for (int a = 0; a < 7; a++) if (mask & (1 << a)) *slot(m, a) = (lora_adapter_t**)calloc((size_t)L, sizeof(lora_adapter_t*));
+    const float* p = flat;
+    for (int l = 0; l < L; l++)
+        for (int a = 0; a < 7; a++) {
+            if (!(mask & (1 << a))) continue;
+            int in, out; dims(&h->cfg, a, &in, &out);
+            size_t nA = (size_t)rank * in, nB = (size_t)out * rank;
+            lora_adapter_t* ad = (lora_adapter_t*)calloc(1, sizeof(lora_adapter_t));
+            ad->in_dim = in; ad->out_dim = out; ad->rank = rank; ad->alpha = alpha;
+            ad->A = (float*)calloc(nA, 4); ad->grad_A = (float*)calloc(nA, 4); ad->m_A = (float*)calloc(nA, 4); ad->v_A = (float*)calloc(nA, 4);
+            ad->B = (float*)calloc(nB, 4); ad->grad_B = (float*)calloc(nB, 4); ad->m_B = (float*)calloc(nB, 4); ad->v_B = (float*)calloc(nB, 4);
+            if (p) { memcpy(ad->A, p, nA * 4); p += nA; memcpy(ad->B, p, nB * 4); p += nB; }
+            (*slot(m, a))[l] = ad;
+        }
+    h->lora_mask = mask;
+    h->st.lora = m; h->st.use_full_training = 0;
+    return 0;
+}
+
+/* which: 0 weights, 1 gradients, 2 Adam m, 3 Adam v (host copies; call cuda_download_lora_weights first) */
+void seraph_b200_state_lora_get(train_state_t* st, int which, float* flat) {
+    harness_t* h = (harness_t*)st;
+    if (!h || !h->st.lora) return;
+    float* p = flat;
+    for (int l = 0; l < h->lora.num_layers; l++)
+        for (int a = 0; a < 7; a++) {
+            if (!(h->lora_mask & (1 << a))) continue;
+            lora_adapter_t* ad = (*slot(&h->lora, a))[l];
+            size_t nA = (size_t)ad->rank * ad->in_dim, nB = (size_t)ad->out_dim * ad->rank;
+            const float* sa = which == 0 ? ad->A : which == 1 ? ad->grad_A : which == 2 ? ad->m_A : ad->v_A;
+            const float* sb = which == 0 ? ad->B : which == 1 ? ad->grad_B : which == 2 ? ad->m_B : ad->v_B;
+            memcpy(p, sa, nA * 4); p += nA; memcpy(p, sb, nB * 4); p += nB;
+        }
+}

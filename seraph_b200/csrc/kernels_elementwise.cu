@@ -1,0 +1,264 @@
+// kernels_elementwise.cu - bandwidth-bound elementwise kernels (sm_100a).
+// All of them stream float4 with a grid-stride loop over a grid that is a
+// multiple of the SM count, so every SM keeps several 16-byte loads in flight.
+//
+// Reference kernels replaced (src/cuda_train_context.cu): add :1442, silu :1451,
+// mul :1462, scale :1471, silu_backward :1744, elementwise_mul_backward :1756,
+// rope[_packed] :616/:652, rope_backward[_packed] :1831/:679, embed_lookup :119,
+// nan_check :2227.
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include "sb_internal.h"
+
+#define EW_THREADS 256
+
+static inline int ew_grid(sb_ctx_t* c, size_t work_items) {
+    int sms = c->pub.gpu_sm_count > 0 ? c->pub.gpu_sm_count : 148;
+    size_t blocks = (work_items + EW_THREADS - 1) / EW_THREADS;
+    size_t cap = (size_t)sms * 8;            // 8 resident CTAs of 256 threads per SM
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// op codes for the generic binary/unary streamers
+enum { OP_ADD, OP_MUL, OP_SILU, OP_SILU_BWD, OP_SWIGLU };
+
+template <int OP>
+__device__ __forceinline__ float ew_apply(float a, float b) {
+    if (OP == OP_ADD) return a + b;
+    if (OP == OP_MUL) return a * b;
+    if (OP == OP_SILU) return a / (1.0f + expf(-a));
+    if (OP == OP_SILU_BWD) { float s = sigmoidf_(a); return b * (s + a * s * (1.0f - s)); }  // a = x, b = dy
+    if (OP == OP_SWIGLU) return (a / (1.0f + expf(-a))) * b;                                  // a = gate, b = up
+    return 0.f;
+}
+
+template <int OP, bool BINARY>
+__global__ void __launch_bounds__(EW_THREADS) ew_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                                        float* __restrict__ c, size_t n, int vec_ok) {
+    size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    if (vec_ok) {
+        size_t n4 = n >> 2;
+        const float4* a4 = (const float4*)a; const float4* b4 = (const float4*)b; float4* c4 = (float4*)c;
+        for (size_t i = tid; i < n4; i += nth) {
+            float4 x = a4[i], y = BINARY ? b4[i] : x, r;
+            r.x = ew_apply<OP>(x.x, y.x); r.y = ew_apply<OP>(x.y, y.y);
+            r.z = ew_apply<OP>(x.z, y.z); r.w = ew_apply<OP>(x.w, y.w);
+            c4[i] = r;
+        }
+        for (size_t i = (n4 << 2) + tid; i < n; i += nth) c[i] = ew_apply<OP>(a[i], BINARY ? b[i] : a[i]);
+    } else {
+        for (size_t i = tid; i < n; i += nth) c[i] = ew_apply<OP>(a[i], BINARY ? b[i] : a[i]);
+    }
+}
+
+static inline int aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
+
+template <int OP, bool BINARY>
+static void ew_launch(sb_ctx_t* c, const float* a, const float* b, float* o, size_t n) {
+    if (!n) return;
+    int vec = aligned16(a) && aligned16(o) && (!BINARY || aligned16(b));
+    ew_kernel<OP, BINARY><<<ew_grid(c, (n + 3) / 4), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(a, b, o, n, vec);
+    c->launches++;
+}
+
+__global__ void __launch_bounds__(EW_THREADS) scale_kernel(float* x, size_t n, float alpha) {
+    size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = tid; i < n; i += nth) x[i] *= alpha;
+}
+
+// dA = dC*B, dB = dC*A  (three reads, two writes)
+__global__ void __launch_bounds__(EW_THREADS) mul_bwd_kernel(const float* __restrict__ A, const float* __restrict__ B,
+                                                             const float* __restrict__ dC, float* __restrict__ dA,
+                                                             float* __restrict__ dB, size_t n) {
+    size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = tid; i < n; i += nth) { float g = dC[i], a = A[i], b = B[i]; dA[i] = g * b; dB[i] = g * a; }
+}
+
+// Fused SwiGLU backward: reads gate, up, dout; writes dgate, dup (20 bytes per element).
+//   s = silu(gate); dup = dout*s; dgate = dout*up * silu'(gate)
+// which is elementwise_mul_backward followed by silu_backward in the reference
+// (src/train_cuda.c:2197-2203) without the intermediate tensors.
+__global__ void __launch_bounds__(EW_THREADS) swiglu_bwd_kernel(const float* __restrict__ gate, const float* __restrict__ up,
+                                                                const float* __restrict__ dout, float* __restrict__ dgate,
+                                                                float* __restrict__ dup, size_t n, int vec_ok) {
+    size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+#define SWIGLU_BWD_ONE(g, u, d, dg, du) { float sg = sigmoidf_(g); float si = (g) * sg; \
+        float dsl = (d) * (u); du = (d) * si; dg = dsl * (sg + (g) * sg * (1.0f - sg)); }
+    if (vec_ok) {
+        size_t n4 = n >> 2;
+        for (size_t i = tid; i < n4; i += nth) {
+            float4 g = ((const float4*)gate)[i], u = ((const float4*)up)[i], d = ((const float4*)dout)[i], dg, du;
+            SWIGLU_BWD_ONE(g.x, u.x, d.x, dg.x, du.x) SWIGLU_BWD_ONE(g.y, u.y, d.y, dg.y, du.y)
+            SWIGLU_BWD_ONE(g.z, u.z, d.z, dg.z, du.z) SWIGLU_BWD_ONE(g.w, u.w, d.w, dg.w, du.w)
+            ((float4*)dgate)[i] = dg; ((float4*)dup)[i] = du;
+        }
+        for (size_t i = (n4 << 2) + tid; i < n; i += nth) SWIGLU_BWD_ONE(gate[i], up[i], dout[i], dgate[i], dup[i])
+    } else {
+        for (size_t i = tid; i < n; i += nth) SWIGLU_BWD_ONE(gate[i], up[i], dout[i], dgate[i], dup[i])
+    }
+}
+
+// out[t,:] = E[tok[t],:]; one CTA per few rows, float4 when d%4==0.  Token ids
+// beyond the table set the status word and read row 0 instead of faulting.
+__global__ void __launch_bounds__(EW_THREADS) embed_lookup_kernel(const uint32_t* __restrict__ tok, const float* __restrict__ E,
+                                                                  float* __restrict__ out, int T, int d, int V, int vec, int* status) {
+    for (int t = blockIdx.x; t < T; t += gridDim.x) {
+        uint32_t id = tok[t];
+        if (id >= (uint32_t)V) { if (threadIdx.x == 0) atomicExch(status, SB_ERR_TOKEN_RANGE); id = 0; }
+        const float* src = E + (size_t)id * d; float* dst = out + (size_t)t * d;
+        if (vec) {
+            for (int i = threadIdx.x; i < d / 4; i += blockDim.x) ((float4*)dst)[i] = ((const float4*)src)[i];
+        } else {
+            for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = src[i];
+        }
+    }
+}
+
+// position of each packed row inside its sequence, and the sequence index
+__global__ void seq_index_kernel(const uint32_t* __restrict__ ss, int B, int T, uint32_t* pos_ids, uint32_t* seq_ids) {
+    int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    int lo = 0, hi = B;
+    while (lo < hi) { int mid = (lo + hi) >> 1; if ((int)ss[mid + 1] <= t) lo = mid + 1; else hi = mid; }
+    if (lo >= B) lo = B - 1;
+    pos_ids[t] = (uint32_t)(t - (int)ss[lo]);
+    seq_ids[t] = (uint32_t)lo;
+}
+
+// cos/sin table [max_pos, hd/2] built with the same FP32 expression the
+// reference evaluates per element: angle = pos * (1/powf(theta, 2p/hd)).
+__global__ void rope_table_kernel(float2* tab, int max_pos, int half, int hd, float theta) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= max_pos * half) return;
+    int pos = i / half, p = i % half;
+    float freq = 1.0f / powf(theta, (float)(p * 2) / hd);
+    float ang = pos * freq;
+    tab[i] = make_float2(cosf(ang), sinf(ang));
+}
+
+// Interleaved-pair rotation, forward or transposed.  One float4 = two pairs.
+__global__ void __launch_bounds__(EW_THREADS) rope_kernel(const float* __restrict__ in, float* __restrict__ out,
+                                                          const uint32_t* __restrict__ pos_ids, const float2* __restrict__ tab,
+                                                          int T, int H, int hd, int backward) {
+    int half = hd >> 1, quads = hd >> 2;
+    size_t total = (size_t)T * H * quads;
+    size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = tid; i < total; i += nth) {
+        int qd = (int)(i % quads); size_t th = i / quads; int t = (int)(th / H);
+        int pos = (int)pos_ids[t];
+        float4 x = ((const float4*)in)[i];
+        float2 cs0 = tab[(size_t)pos * half + 2 * qd], cs1 = tab[(size_t)pos * half + 2 * qd + 1];
+        float4 r;
+        if (!backward) {
+            r.x = x.x * cs0.x - x.y * cs0.y; r.y = x.x * cs0.y + x.y * cs0.x;
+            r.z = x.z * cs1.x - x.w * cs1.y; r.w = x.z * cs1.y + x.w * cs1.x;
+        } else {
+            r.x = x.x * cs0.x + x.y * cs0.y; r.y = -x.x * cs0.y + x.y * cs0.x;
+            r.z = x.z * cs1.x + x.w * cs1.y; r.w = -x.z * cs1.y + x.w * cs1.x;
+        }
+        ((float4*)out)[i] = r;
+    }
+}
+
+// pair-at-a-time variant for head_dim not divisible by 4 or unaligned buffers
+__global__ void rope_pair_kernel(const float* __restrict__ in, float* __restrict__ out, const uint32_t* __restrict__ pos_ids,
+                                 const float2* __restrict__ tab, int T, int H, int hd, int backward) {
+    int half = hd >> 1;
+    size_t total = (size_t)T * H * half;
+    size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = tid; i < total; i += nth) {
+        int p = (int)(i % half); size_t th = i / half; int t = (int)(th / H);
+        float2 cs = tab[(size_t)pos_ids[t] * half + p];
+        size_t o = th * hd + 2 * p;
+        float x0 = in[o], x1 = in[o + 1];
+        if (!backward) { out[o] = x0 * cs.x - x1 * cs.y; out[o + 1] = x0 * cs.y + x1 * cs.x; }
+        else           { out[o] = x0 * cs.x + x1 * cs.y; out[o + 1] = -x0 * cs.y + x1 * cs.x; }
+    }
+}
+
+__global__ void __launch_bounds__(EW_THREADS) nan_check_kernel(const float* __restrict__ x, size_t n, uint32_t* flags, uint32_t idx) {
+    size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    bool bad = false;
+    for (size_t i = tid; i < n; i += nth) { float v = x[i]; bad |= (isnan(v) || isinf(v)); }
+    if (bad) flags[idx] = 1;
+}
+
+extern "C" {
+
+void sb_add(sb_ctx_t* c, const float* a, const float* b, float* o, size_t n) { ew_launch<OP_ADD, true>(c, a, b, o, n); }
+void sb_mul(sb_ctx_t* c, const float* a, const float* b, float* o, size_t n) { ew_launch<OP_MUL, true>(c, a, b, o, n); }
+void sb_silu(sb_ctx_t* c, const float* x, float* y, size_t n) { ew_launch<OP_SILU, false>(c, x, x, y, n); }
+void sb_silu_backward(sb_ctx_t* c, const float* x, const float* dy, float* dx, size_t n) { ew_launch<OP_SILU_BWD, true>(c, x, dy, dx, n); }
+void sb_swiglu(sb_ctx_t* c, const float* g, const float* u, float* o, size_t n) { ew_launch<OP_SWIGLU, true>(c, g, u, o, n); }
+
+void sb_scale(sb_ctx_t* c, float* a, size_t n, float alpha) {
+    if (!n) return;
+    scale_kernel<<<ew_grid(c, n), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(a, n, alpha);
+    c->launches++;
+}
+
+void sb_mul_backward(sb_ctx_t* c, const float* A, const float* B, const float* dC, float* dA, float* dB, size_t n) {
+    if (!n) return;
+    mul_bwd_kernel<<<ew_grid(c, n), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(A, B, dC, dA, dB, n);
+    c->launches++;
+}
+
+void sb_swiglu_backward(sb_ctx_t* c, const float* gate, const float* up, const float* dout, float* dgate, float* dup, size_t n) {
+    if (!n) return;
+    int vec = aligned16(gate) && aligned16(up) && aligned16(dout) && aligned16(dgate) && aligned16(dup);
+    swiglu_bwd_kernel<<<ew_grid(c, (n + 3) / 4), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(gate, up, dout, dgate, dup, n, vec);
+    c->launches++;
+}
+
+void sb_embed_lookup(sb_ctx_t* c, const uint32_t* tok, const float* E, float* out, int T, int d, int V) {
+    if (T <= 0) return;
+    int sms = c->pub.gpu_sm_count > 0 ? c->pub.gpu_sm_count : 148;
+    int grid = T < sms * 8 ? T : sms * 8;
+    int vec = ((d & 3) == 0) && aligned16(E) && aligned16(out);
+    embed_lookup_kernel<<<grid, EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(tok, E, out, T, d, V, vec, c->d_status);
+    c->launches++;
+}
+
+void sb_seq_index(sb_ctx_t* c, const uint32_t* seq_starts, int B, int T, uint32_t* pos_ids, uint32_t* seq_ids) {
+    if (T <= 0) return;
+    seq_index_kernel<<<(T + 255) / 256, 256, 0, (cudaStream_t)c->pub.stream>>>(seq_starts, B, T, pos_ids, seq_ids);
+    c->launches++;
+}
+
+void sb_rope(sb_ctx_t* c, const float* in, float* out, const uint32_t* pos_ids, int T, int H, int hd, float theta,
+             int max_pos, int backward) {
+    if (T <= 0 || H <= 0 || hd < 2) return;
+    int half = hd / 2;
+    if (!c->rope_tab || c->rope_tab_pos < max_pos || c->rope_tab_hd != hd || c->rope_tab_theta != theta) {
+        cudaStreamSynchronize((cudaStream_t)c->pub.stream);
+        if (c->rope_tab) cudaFree(c->rope_tab);
+        c->rope_tab = NULL;
+        int cap = max_pos < 1024 ? 1024 : max_pos;
+        if (sb_check(c, cudaMalloc(&c->rope_tab, (size_t)cap * half * sizeof(float2)), "rope table")) return;
+        c->rope_tab_pos = cap; c->rope_tab_hd = hd; c->rope_tab_theta = theta;
+        int n = cap * half;
+        rope_table_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)c->pub.stream>>>((float2*)c->rope_tab, cap, half, hd, theta);
+        c->launches++;
+    }
+    if ((hd & 3) == 0 && aligned16(in) && aligned16(out)) {
+        size_t work = (size_t)T * H * (hd / 4);
+        rope_kernel<<<ew_grid(c, work), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(in, out, pos_ids, (const float2*)c->rope_tab, T, H, hd, backward);
+    } else {
+        size_t work = (size_t)T * H * half;
+        rope_pair_kernel<<<ew_grid(c, work), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(in, out, pos_ids, (const float2*)c->rope_tab, T, H, hd, backward);
+    }
+    c->launches++;
+}
+
+void sb_nan_check(sb_ctx_t* c, const float* x, size_t n, uint32_t* flags, uint32_t idx) {
+    if (!n) return;
+    nan_check_kernel<<<ew_grid(c, n), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(x, n, flags, idx);
+    c->launches++;
+}
+
+}  // extern "C"

@@ -1,0 +1,488 @@
+// kernels_reduce.cu - row-reduction and optimizer kernels (sm_100a), all deterministic:
+// no floating-point atomics anywhere, so two runs give the same bits.
+//
+// Reference kernels replaced (src/cuda_train_context.cu): rmsnorm :148,
+// rmsnorm_backward :1767 (atomicAdd on grad_scale), softmax :1486,
+// cross_entropy_grad[_packed] :1566/:1657, reduce_sum :2209 (atomicAdd),
+// embedding_backward :2175 (atomicAdd, blockDim = hidden_size), adamw :2187.
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include "sb_internal.h"
+
+#define RB_THREADS 256
+
+static inline int aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
+static inline int sm_count(sb_ctx_t* c) { return c->pub.gpu_sm_count > 0 ? c->pub.gpu_sm_count : 148; }
+
+__device__ __forceinline__ float warp_sum(float v) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// block-wide sum of up to two values; every thread gets the result.  red: >= 2*32 floats of smem
+__device__ __forceinline__ void block_sum2(float& a, float& b, float* red) {
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    a = warp_sum(a); b = warp_sum(b);
+    __syncthreads();
+    if (lane == 0) { red[w] = a; red[32 + w] = b; }
+    __syncthreads();
+    float x = 0.f, y = 0.f;
+    for (int i = 0; i < nw; i++) { x += red[i]; y += red[32 + i]; }   // fixed order
+    a = x; b = y;
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm forward: y = x * (1/sqrt(mean(x^2)+eps)) * w.   8 bytes per element + w.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(RB_THREADS) rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                             float* __restrict__ y, int rows, int cols, float eps, int vec) {
+    __shared__ float red[64];
+    for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+        const float* xr = x + (size_t)r * cols; float* yr = y + (size_t)r * cols;
+        float ss = 0.f, dummy = 0.f;
+        if (vec) for (int i = threadIdx.x; i < cols / 4; i += blockDim.x) { float4 v = ((const float4*)xr)[i]; ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
+        else     for (int i = threadIdx.x; i < cols; i += blockDim.x) { float v = xr[i]; ss += v * v; }
+        block_sum2(ss, dummy, red);
+        float inv = 1.0f / sqrtf(ss / cols + eps);
+        if (vec) for (int i = threadIdx.x; i < cols / 4; i += blockDim.x) {
+            float4 v = ((const float4*)xr)[i], s = ((const float4*)w)[i];
+            ((float4*)yr)[i] = make_float4(v.x * inv * s.x, v.y * inv * s.y, v.z * inv * s.z, v.w * inv * s.w);
+        } else for (int i = threadIdx.x; i < cols; i += blockDim.x) yr[i] = xr[i] * inv * w[i];
+    }
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm backward.  Each CTA owns rows r = blockIdx.x, +gridDim.x, ...; it
+// writes dx for them (optionally fused with the residual-gradient add) and
+// keeps a per-column partial of dscale in registers, stored once to
+// partial[blockIdx.x][cols].  A second kernel adds the partials in block
+// order into dscale.  Algorithmic traffic: 12 bytes per element (+4 when the
+// residual is fused) + cols*4.
+// ---------------------------------------------------------------------------
+#define RN_MAX_SWEEP 16     // cols <= RB_THREADS*4*RN_MAX_SWEEP = 16384
+__global__ void __launch_bounds__(RB_THREADS) rmsnorm_bwd_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                                 const float* __restrict__ dy, const float* __restrict__ resid,
+                                                                 float* __restrict__ dx, float* __restrict__ partial,
+                                                                 int rows, int cols, float eps, int vec) {
+    __shared__ float red[64];
+    float acc[RN_MAX_SWEEP * 4];
+#pragma unroll
+    for (int i = 0; i < RN_MAX_SWEEP * 4; i++) acc[i] = 0.f;
+    const int c4 = cols / 4;
+    for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+        const float* xr = x + (size_t)r * cols; const float* gr = dy + (size_t)r * cols;
+        float ss = 0.f, cp = 0.f;
+        if (vec) for (int i = threadIdx.x; i < c4; i += blockDim.x) {
+            float4 v = ((const float4*)xr)[i], g = ((const float4*)gr)[i], s = ((const float4*)w)[i];
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            cp += g.x * s.x * v.x + g.y * s.y * v.y + g.z * s.z * v.z + g.w * s.w * v.w;
+        } else for (int i = threadIdx.x; i < cols; i += blockDim.x) { float v = xr[i]; ss += v * v; cp += gr[i] * w[i] * v; }
+        block_sum2(ss, cp, red);
+        float inv = 1.0f / sqrtf(ss / cols + eps);
+        float k = inv * inv * inv / cols * cp;
+        float* dr = dx + (size_t)r * cols; const float* rr = resid ? resid + (size_t)r * cols : nullptr;
+        if (vec) {
+#pragma unroll
+            for (int sw = 0; sw < RN_MAX_SWEEP; sw++) {
+                int i = threadIdx.x + sw * RB_THREADS;
+                if (i < c4) {
+                    float4 v = ((const float4*)xr)[i], g = ((const float4*)gr)[i], s = ((const float4*)w)[i], o;
+                    acc[sw * 4 + 0] += g.x * v.x * inv; acc[sw * 4 + 1] += g.y * v.y * inv;
+                    acc[sw * 4 + 2] += g.z * v.z * inv; acc[sw * 4 + 3] += g.w * v.w * inv;
+                    o.x = g.x * s.x * inv - v.x * k; o.y = g.y * s.y * inv - v.y * k;
+                    o.z = g.z * s.z * inv - v.z * k; o.w = g.w * s.w * inv - v.w * k;
+                    if (rr) { float4 q = ((const float4*)rr)[i]; o.x += q.x; o.y += q.y; o.z += q.z; o.w += q.w; }
+                    ((float4*)dr)[i] = o;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int sw = 0; sw < RN_MAX_SWEEP * 4; sw++) {
+                int i = threadIdx.x + sw * RB_THREADS;
+                if (i < cols) {
+                    float v = xr[i], g = gr[i];
+                    acc[sw] += g * v * inv;
+                    float o = g * w[i] * inv - v * k;
+                    if (rr) o += rr[i];
+                    dr[i] = o;
+                }
+            }
+        }
+    }
+    float* pr = partial + (size_t)blockIdx.x * cols;
+    if (vec) {
+#pragma unroll
+        for (int sw = 0; sw < RN_MAX_SWEEP; sw++) {
+            int i = threadIdx.x + sw * RB_THREADS;
+            if (i < c4) ((float4*)pr)[i] = make_float4(acc[sw * 4], acc[sw * 4 + 1], acc[sw * 4 + 2], acc[sw * 4 + 3]);
+        }
+    } else {
+#pragma unroll
+        for (int sw = 0; sw < RN_MAX_SWEEP * 4; sw++) { int i = threadIdx.x + sw * RB_THREADS; if (i < cols) pr[i] = acc[sw]; }
+    }
+}
+
+// dscale[c] += sum over blocks (fixed order) of partial[b][c]
+__global__ void colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ dscale, int nblocks, int cols) {
+    int cidx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (cidx >= cols) return;
+    float s = 0.f;
+    for (int b = 0; b < nblocks; b++) s += partial[(size_t)b * cols + cidx];
+    dscale[cidx] += s;
+}
+
+// ---------------------------------------------------------------------------
+// Row softmax (kept for API completeness; no training step uses it)
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(RB_THREADS) softmax_kernel(const float* __restrict__ x, float* __restrict__ y, int rows, int cols) {
+    __shared__ float red[64];
+    for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+        const float* xr = x + (size_t)r * cols; float* yr = y + (size_t)r * cols;
+        float m = -INFINITY;
+        for (int i = threadIdx.x; i < cols; i += blockDim.x) m = fmaxf(m, xr[i]);
+        m = warp_max(m);
+        __syncthreads();
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+        __syncthreads();
+        m = -INFINITY;
+        for (int i = 0; i < (blockDim.x + 31) / 32; i++) m = fmaxf(m, red[i]);
+        float s = 0.f, d0 = 0.f;
+        for (int i = threadIdx.x; i < cols; i += blockDim.x) s += expf(xr[i] - m);
+        block_sum2(s, d0, red);
+        float inv = 1.0f / s;
+        for (int i = threadIdx.x; i < cols; i += blockDim.x) yr[i] = expf(xr[i] - m) * inv;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Cross-entropy loss and gradient, packed.  One CTA per row: an online
+// (max,sum) pass over the logits, then one pass that writes the gradient:
+// 12 bytes per logit where the reference's three passes move 20.
+//   last token of a sequence -> zero row and zero loss
+//   loss = -(logit[target] - max - log(sum));  grad = (softmax - onehot)/num_valid
+// ---------------------------------------------------------------------------
+#define CE_THREADS 512
+__global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(const float* __restrict__ logits, const uint32_t* __restrict__ targets,
+                                                                   float* __restrict__ grad, float* __restrict__ loss_rows,
+                                                                   const uint32_t* __restrict__ pos_ids, const uint32_t* __restrict__ seq_ids,
+                                                                   const uint32_t* __restrict__ seq_starts,
+                                                                   int T, int V, float inv_valid, int vec, int* status) {
+    __shared__ float redm[32], reds[32];
+    int r = blockIdx.x;
+    if (r >= T) return;
+    const float* lr = logits + (size_t)r * V; float* gr = grad + (size_t)r * V;
+    uint32_t s = seq_ids[r];
+    int seq_len = (int)(seq_starts[s + 1] - seq_starts[s]);
+    if ((int)pos_ids[r] >= seq_len - 1) {
+        if (vec) for (int i = threadIdx.x; i < V / 4; i += blockDim.x) ((float4*)gr)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        else     for (int i = threadIdx.x; i < V; i += blockDim.x) gr[i] = 0.f;
+        if (threadIdx.x == 0) loss_rows[r] = 0.f;
+        return;
+    }
+    uint32_t tg = targets[r];
+    if (tg >= (uint32_t)V) { if (threadIdx.x == 0) atomicExch(status, SB_ERR_TOKEN_RANGE); tg = 0; }
+    float m = -INFINITY, sum = 0.f;
+#define CE_ONLINE(v) { float nv = (v); if (nv > m) { sum = sum * expf(m - nv) + 1.0f; m = nv; } else sum += expf(nv - m); }
+    if (vec) for (int i = threadIdx.x; i < V / 4; i += blockDim.x) { float4 v = ((const float4*)lr)[i]; CE_ONLINE(v.x) CE_ONLINE(v.y) CE_ONLINE(v.z) CE_ONLINE(v.w) }
+    else     for (int i = threadIdx.x; i < V; i += blockDim.x) CE_ONLINE(lr[i])
+    // combine (m,sum) pairs: warp, then block
+    for (int o = 16; o > 0; o >>= 1) {
+        float om = __shfl_xor_sync(0xffffffffu, m, o), os = __shfl_xor_sync(0xffffffffu, sum, o);
+        float nm = fmaxf(m, om);
+        sum = (m == -INFINITY ? 0.f : sum * expf(m - nm)) + (om == -INFINITY ? 0.f : os * expf(om - nm));
+        m = nm;
+    }
+    if ((threadIdx.x & 31) == 0) { redm[threadIdx.x >> 5] = m; reds[threadIdx.x >> 5] = sum; }
+    __syncthreads();
+    m = -INFINITY; sum = 0.f;
+    for (int i = 0; i < CE_THREADS / 32; i++) {
+        float om = redm[i], os = reds[i], nm = fmaxf(m, om);
+        sum = (m == -INFINITY ? 0.f : sum * expf(m - nm)) + (om == -INFINITY ? 0.f : os * expf(om - nm));
+        m = nm;
+    }
+    float inv = 1.0f / sum;
+    if (threadIdx.x == 0) loss_rows[r] = -((lr[tg] - m) - logf(sum));
+    if (vec) for (int i = threadIdx.x; i < V / 4; i += blockDim.x) {
+        float4 v = ((const float4*)lr)[i], g;
+        g.x = expf(v.x - m) * inv; g.y = expf(v.y - m) * inv; g.z = expf(v.z - m) * inv; g.w = expf(v.w - m) * inv;
+        uint32_t b = (uint32_t)i * 4;
+        if (tg - b < 4u) { if (tg == b) g.x -= 1.f; else if (tg == b + 1) g.y -= 1.f; else if (tg == b + 2) g.z -= 1.f; else g.w -= 1.f; }
+        g.x *= inv_valid; g.y *= inv_valid; g.z *= inv_valid; g.w *= inv_valid;
+        ((float4*)gr)[i] = g;
+    } else for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        float g = expf(lr[i] - m) * inv;
+        if ((uint32_t)i == tg) g -= 1.f;
+        gr[i] = g * inv_valid;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Deterministic sums: fixed grid, fixed per-thread assignment, fixed-order combine.
+// ---------------------------------------------------------------------------
+template <bool SQUARE>
+__global__ void __launch_bounds__(RB_THREADS) partial_sum_kernel(const float* __restrict__ x, size_t n, float* __restrict__ partial, int vec) {
+    __shared__ float red[64];
+    size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    float s = 0.f, d0 = 0.f;
+    if (vec) {
+        size_t n4 = n >> 2;
+        for (size_t i = tid; i < n4; i += nth) {
+            float4 v = ((const float4*)x)[i];
+            s += SQUARE ? (v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w) : (v.x + v.y + v.z + v.w);
+        }
+        for (size_t i = (n4 << 2) + tid; i < n; i += nth) s += SQUARE ? x[i] * x[i] : x[i];
+    } else for (size_t i = tid; i < n; i += nth) s += SQUARE ? x[i] * x[i] : x[i];
+    block_sum2(s, d0, red);
+    if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+__global__ void final_sum_kernel(const float* __restrict__ partial, int n, float* out) {
+    __shared__ float red[64];
+    float s = 0.f, d0 = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) s += partial[i];
+    block_sum2(s, d0, red);
+    if (threadIdx.x == 0) out[0] = s;
+}
+
+// ---------------------------------------------------------------------------
+// Embedding backward as a sorted-segment reduction.
+//   1. count_kernel     per-chunk token histograms (integer atomics: exact)
+//   2. scan_kernel      bucket starts over the vocabulary, list of rows that occur
+//   3. place_kernel     stable position of every token inside its bucket
+//   4. segsum_kernel    one CTA per occurring row adds its gradient rows in
+//                       ascending token position and does ONE += into dE
+// Integer work is exact, the float sums have a fixed order: bit-reproducible.
+// Algorithmic bytes: 4*T*d read + 8*U*d (read+write of U touched rows) + 4*T.
+// ---------------------------------------------------------------------------
+#define EB_CHUNK 1024
+__global__ void __launch_bounds__(EB_CHUNK) eb_count_kernel(const uint32_t* __restrict__ tok, int T, int V,
+                                                            int* __restrict__ chunk_cnt, int* __restrict__ cnt, int* status) {
+    int t = blockIdx.x * EB_CHUNK + threadIdx.x;
+    if (t >= T) return;
+    uint32_t id = tok[t];
+    if (id >= (uint32_t)V) { atomicExch(status, SB_ERR_TOKEN_RANGE); return; }
+    atomicAdd(&chunk_cnt[(size_t)blockIdx.x * V + id], 1);
+    atomicAdd(&cnt[id], 1);
+}
+
+// single CTA: exclusive scan of cnt[V] -> start[V]; compaction of rows with cnt>0 -> rows[], meta[0] = U
+__global__ void __launch_bounds__(1024) eb_scan_kernel(const int* __restrict__ cnt, int V, int* __restrict__ start,
+                                                       int* __restrict__ rows, int* __restrict__ meta) {
+    __shared__ int s_cnt[1024], s_u[1024];
+    int per = (V + 1023) / 1024, b = threadIdx.x * per, e = min(b + per, V);
+    int c = 0, u = 0;
+    for (int i = b; i < e; i++) { int k = cnt[i]; c += k; u += (k > 0); }
+    s_cnt[threadIdx.x] = c; s_u[threadIdx.x] = u;
+    __syncthreads();
+    for (int off = 1; off < 1024; off <<= 1) {            // Hillis-Steele inclusive scan
+        int vc = 0, vu = 0;
+        if ((int)threadIdx.x >= off) { vc = s_cnt[threadIdx.x - off]; vu = s_u[threadIdx.x - off]; }
+        __syncthreads();
+        s_cnt[threadIdx.x] += vc; s_u[threadIdx.x] += vu;
+        __syncthreads();
+    }
+    int base_c = s_cnt[threadIdx.x] - c, base_u = s_u[threadIdx.x] - u;
+    for (int i = b; i < e; i++) {
+        int k = cnt[i];
+        start[i] = base_c; base_c += k;
+        if (k > 0) rows[base_u++] = i;
+    }
+    if (threadIdx.x == 1023) { meta[0] = s_u[1023]; meta[1] = s_cnt[1023]; }
+}
+
+__global__ void __launch_bounds__(EB_CHUNK) eb_place_kernel(const uint32_t* __restrict__ tok, int T, int V,
+                                                            const int* __restrict__ chunk_cnt, const int* __restrict__ start,
+                                                            int* __restrict__ sorted_pos) {
+    __shared__ uint32_t s_tok[EB_CHUNK];
+    int t = blockIdx.x * EB_CHUNK + threadIdx.x;
+    uint32_t id = t < T ? tok[t] : 0xffffffffu;
+    s_tok[threadIdx.x] = id;
+    __syncthreads();
+    if (t >= T || id >= (uint32_t)V) return;
+    int rank = 0;
+    for (int cb = 0; cb < (int)blockIdx.x; cb++) rank += chunk_cnt[(size_t)cb * V + id];   // earlier chunks
+    for (int j = 0; j < (int)threadIdx.x; j++) rank += (s_tok[j] == id);                   // earlier in this chunk
+    sorted_pos[start[id] + rank] = t;
+}
+
+__global__ void __launch_bounds__(RB_THREADS) eb_segsum_kernel(const float* __restrict__ g, float* __restrict__ dE,
+                                                               const int* __restrict__ rows, const int* __restrict__ start,
+                                                               const int* __restrict__ cnt, const int* __restrict__ sorted_pos,
+                                                               const int* __restrict__ meta, int d, int vec) {
+    int U = meta[0];
+    for (int u = blockIdx.x; u < U; u += gridDim.x) {
+        int row = rows[u], s0 = start[row], n = cnt[row];
+        float* er = dE + (size_t)row * d;
+        if (vec) for (int i = threadIdx.x; i < d / 4; i += blockDim.x) {
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = 0; j < n; j++) { float4 v = ((const float4*)(g + (size_t)sorted_pos[s0 + j] * d))[i]; a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w; }
+            float4 e = ((float4*)er)[i]; e.x += a.x; e.y += a.y; e.z += a.z; e.w += a.w; ((float4*)er)[i] = e;
+        } else for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            float a = 0.f;
+            for (int j = 0; j < n; j++) a += g[(size_t)sorted_pos[s0 + j] * d + i];
+            er[i] += a;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// AdamW over a flat range: decoupled decay, bias correction (host-computed
+// 1-beta^t), optional global-norm clip and data-parallel 1/world folded into
+// the gradient read.  28 bytes per parameter.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(RB_THREADS) adamw_kernel(float* __restrict__ w, const float* __restrict__ g, float* __restrict__ m,
+                                                           float* __restrict__ v, size_t n, float lr, float b1, float b2, float wd,
+                                                           float eps, float c1, float c2, float grad_scale,
+                                                           const float* __restrict__ sumsq, float clip, int vec) {
+    float gs = grad_scale;
+    if (clip > 0.f && sumsq) {
+        float norm = sqrtf(sumsq[0]) * grad_scale;
+        if (norm > clip) gs *= clip / (norm + 1e-6f);
+    }
+    const float decay = 1.0f - lr * wd, ob1 = 1.0f - b1, ob2 = 1.0f - b2;
+    size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+#define ADAMW_ONE(W, G, M, V) { float gi = (G) * gs; float mi = b1 * (M) + ob1 * gi; float vi = b2 * (V) + ob2 * gi * gi; \
+        (M) = mi; (V) = vi; float mh = mi / c1, vh = vi / c2; (W) = (W) * decay - lr * mh / (sqrtf(vh) + eps); }
+    if (vec) {
+        size_t n4 = n >> 2;
+        for (size_t i = tid; i < n4; i += nth) {
+            float4 W = ((float4*)w)[i], G = ((const float4*)g)[i], M = ((float4*)m)[i], Vv = ((float4*)v)[i];
+            ADAMW_ONE(W.x, G.x, M.x, Vv.x) ADAMW_ONE(W.y, G.y, M.y, Vv.y) ADAMW_ONE(W.z, G.z, M.z, Vv.z) ADAMW_ONE(W.w, G.w, M.w, Vv.w)
+            ((float4*)w)[i] = W; ((float4*)m)[i] = M; ((float4*)v)[i] = Vv;
+        }
+        for (size_t i = (n4 << 2) + tid; i < n; i += nth) ADAMW_ONE(w[i], g[i], m[i], v[i])
+    } else for (size_t i = tid; i < n; i += nth) ADAMW_ONE(w[i], g[i], m[i], v[i])
+}
+
+extern "C" {
+
+void sb_rmsnorm(sb_ctx_t* c, const float* x, const float* w, float* y, int rows, int cols, float eps) {
+    if (rows <= 0 || cols <= 0) return;
+    int grid = rows < sm_count(c) * 8 ? rows : sm_count(c) * 8;
+    int vec = (cols % 4 == 0) && aligned16(x) && aligned16(w) && aligned16(y);
+    rmsnorm_kernel<<<grid, RB_THREADS, 0, (cudaStream_t)c->pub.stream>>>(x, w, y, rows, cols, eps, vec);
+    c->launches++;
+}
+
+// number of CTAs the rmsnorm backward uses for `rows` rows (also the row count of its partial buffer)
+static int rn_bwd_grid(sb_ctx_t* c, int rows) { int cap = sm_count(c) * 2; return rows < cap ? rows : cap; }
+
+void sb_rmsnorm_backward_with_partials(sb_ctx_t* c, const float* x, const float* w, const float* dy, const float* resid,
+                                       float* dx_out, float* dscale, int rows, int cols, float eps, float* partial, int grid) {
+    int vec = (cols % 4 == 0) && aligned16(x) && aligned16(w) && aligned16(dy) && aligned16(dx_out) && (!resid || aligned16(resid));
+    cudaStream_t s = (cudaStream_t)c->pub.stream;
+    rmsnorm_bwd_kernel<<<grid, RB_THREADS, 0, s>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps, vec);
+    colsum_partials_kernel<<<(cols + 255) / 256, 256, 0, s>>>(partial, dscale, grid, cols);
+    c->launches += 2;
+}
+
+void sb_rmsnorm_backward(sb_ctx_t* c, const float* x, const float* w, const float* dy, const float* resid,
+                         float* dx_out, float* dscale, int rows, int cols, float eps) {
+    if (rows <= 0 || cols <= 0) return;
+    if (cols > RB_THREADS * 4 * RN_MAX_SWEEP || (cols % 4 != 0 && cols > RB_THREADS * RN_MAX_SWEEP * 4)) { sb_set_status(c, SB_ERR_SIZE); return; }
+    int grid = rn_bwd_grid(c, rows);
+    float* partial = (float*)sb_scratch(c, (size_t)grid * cols * sizeof(float));
+    if (!partial) return;
+    sb_rmsnorm_backward_with_partials(c, x, w, dy, resid, dx_out, dscale, rows, cols, eps, partial, grid);
+}
+
+void sb_softmax(sb_ctx_t* c, const float* x, float* y, int rows, int cols) {
+    if (rows <= 0 || cols <= 0) return;
+    int grid = rows < sm_count(c) * 8 ? rows : sm_count(c) * 8;
+    softmax_kernel<<<grid, RB_THREADS, 0, (cudaStream_t)c->pub.stream>>>(x, y, rows, cols);
+    c->launches++;
+}
+
+void sb_cross_entropy(sb_ctx_t* c, const float* logits, const uint32_t* targets, float* grad, float* loss_rows,
+                      const uint32_t* pos_ids, const uint32_t* seq_ids, const uint32_t* seq_starts, int T, int V, int num_valid) {
+    if (T <= 0 || V <= 0) return;
+    int vec = (V % 4 == 0) && aligned16(logits) && aligned16(grad);
+    cross_entropy_kernel<<<T, CE_THREADS, 0, (cudaStream_t)c->pub.stream>>>(logits, targets, grad, loss_rows, pos_ids, seq_ids,
+                                                                          seq_starts, T, V, 1.0f / (float)num_valid, vec, c->d_status);
+    c->launches++;
+}
+
+static void sum_impl(sb_ctx_t* c, const float* in, float* out, size_t n, bool square) {
+    cudaStream_t s = (cudaStream_t)c->pub.stream;
+    if (n == 0) { cudaMemsetAsync(out, 0, sizeof(float), s); return; }
+    int grid = sm_count(c) * 4;
+    size_t need = (n + RB_THREADS * 4 - 1) / (RB_THREADS * 4);
+    if ((size_t)grid > need) grid = (int)need;
+    float* partial = (float*)sb_scratch(c, (size_t)grid * sizeof(float));
+    if (!partial) return;
+    int vec = aligned16(in);
+    if (square) partial_sum_kernel<true><<<grid, RB_THREADS, 0, s>>>(in, n, partial, vec);
+    else        partial_sum_kernel<false><<<grid, RB_THREADS, 0, s>>>(in, n, partial, vec);
+    final_sum_kernel<<<1, RB_THREADS, 0, s>>>(partial, grid, out);
+    c->launches += 2;
+}
+void sb_reduce_sum(sb_ctx_t* c, const float* in, float* out, size_t n) { sum_impl(c, in, out, n, false); }
+void sb_sumsq(sb_ctx_t* c, const float* g, size_t n, float* d_out) { sum_impl(c, g, d_out, n, true); }
+
+// Scratch layout of the embedding backward (ints): cnt[V] start[V] rows[V] meta[4] sorted_pos[T] chunk_cnt[nchunk*V]
+size_t sb_embedding_scratch_ints(int T, int V) {
+    size_t nchunk = ((size_t)T + EB_CHUNK - 1) / EB_CHUNK;
+    return 3 * (size_t)V + 4 + (size_t)T + nchunk * (size_t)V;
+}
+
+void sb_embedding_backward(sb_ctx_t* c, const uint32_t* tok, const float* g, float* dE, int T, int d, int V) {
+    if (T <= 0 || d <= 0 || V <= 0) return;
+    cudaStream_t s = (cudaStream_t)c->pub.stream;
+    int nchunk = (T + EB_CHUNK - 1) / EB_CHUNK;
+    size_t ints = sb_embedding_scratch_ints(T, V);
+    int* base = (int*)sb_scratch(c, ints * sizeof(int));
+    if (!base) return;
+    int *cnt = base, *start = cnt + V, *rows = start + V, *meta = rows + V, *sorted_pos = meta + 4, *chunk_cnt = sorted_pos + T;
+    cudaMemsetAsync(cnt, 0, (size_t)V * sizeof(int), s);
+    cudaMemsetAsync(chunk_cnt, 0, (size_t)nchunk * V * sizeof(int), s);
+    eb_count_kernel<<<nchunk, EB_CHUNK, 0, s>>>(tok, T, V, chunk_cnt, cnt, c->d_status);
+    eb_scan_kernel<<<1, 1024, 0, s>>>(cnt, V, start, rows, meta);
+    eb_place_kernel<<<nchunk, EB_CHUNK, 0, s>>>(tok, T, V, chunk_cnt, start, sorted_pos);
+    int grid = T < V ? T : V;
+    if (grid > sm_count(c) * 8) grid = sm_count(c) * 8;
+    int vec = (d % 4 == 0) && aligned16(g) && aligned16(dE);
+    eb_segsum_kernel<<<grid, RB_THREADS, 0, s>>>(g, dE, rows, start, cnt, sorted_pos, meta, d, vec);
+    c->launches += 4;
+}
+
+// copies the segment tables of the last sb_embedding_backward(T, V) to the host:
+// rows[U] (ascending), counts[U], sorted_pos[T]; returns U, or -1 on error
+int sb_embedding_segments(sb_ctx_t* c, int T, int V, int* rows_out, int* counts_out, int* sorted_pos_out) {
+    size_t ints = sb_embedding_scratch_ints(T, V);
+    if (!c->scratch || c->scratch_bytes < ints * sizeof(int)) return -1;
+    cudaStream_t s = (cudaStream_t)c->pub.stream;
+    cudaStreamSynchronize(s);
+    int* base = (int*)c->scratch;
+    int *cnt = base, *start = cnt + V, *rows = start + V, *meta = rows + V, *sorted_pos = meta + 4;
+    int h_meta[4];
+    if (cudaMemcpy(h_meta, meta, sizeof h_meta, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    int U = h_meta[0];
+    if (U < 0 || U > V) return -1;
+    int* h_cnt = (int*)malloc((size_t)V * sizeof(int));
+    if (!h_cnt) return -1;
+    cudaMemcpy(h_cnt, cnt, (size_t)V * sizeof(int), cudaMemcpyDeviceToHost);
+    cudaMemcpy(rows_out, rows, (size_t)U * sizeof(int), cudaMemcpyDeviceToHost);
+    cudaMemcpy(sorted_pos_out, sorted_pos, (size_t)T * sizeof(int), cudaMemcpyDeviceToHost);
+    for (int i = 0; i < U; i++) counts_out[i] = h_cnt[rows_out[i]];
+    free(h_cnt);
+    (void)start;
+    return U;
+}
+
+void sb_adamw(sb_ctx_t* c, float* w, const float* g, float* m, float* v, size_t n, float lr, float b1, float b2,
+              float wd, float eps, int step, float grad_scale, const float* d_sumsq, float clip) {
+    if (!n) return;
+    float c1 = 1.0f - powf(b1, (float)step), c2 = 1.0f - powf(b2, (float)step);
+    int vec = aligned16(w) && aligned16(g) && aligned16(m) && aligned16(v);
+    size_t need = (n + RB_THREADS * 4 - 1) / (RB_THREADS * 4);
+    size_t grid = (size_t)sm_count(c) * 8;
+    if (grid > need) grid = need;
+    adamw_kernel<<<(int)grid, RB_THREADS, 0, (cudaStream_t)c->pub.stream>>>(w, g, m, v, n, lr, b1, b2, wd, eps, c1, c2,
+                                                                         grad_scale, d_sumsq, clip, vec);
+    c->launches++;
+}
+
+}  // extern "C"

@@ -1,0 +1,155 @@
+/*
+ * sb_internal.h - private state and kernel-launch entry points of libseraph_b200.
+ *
+ * The public cuda_train_context_t keeps the reference's layout; everything this
+ * library adds lives in sb_ctx_t, which embeds the public struct as its first
+ * member so the pointer handed to callers is also the pointer to the private
+ * state.  All launchers take raw device pointers and run on ctx->stream.
+ */
+#ifndef SB_INTERNAL_H
+#define SB_INTERNAL_H
+
+#include "../../include/seraph_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SB_MAGIC 0x5342323030u   /* "SB200" */
+
+/* status codes (seraph_b200_last_status) */
+enum {
+    SB_OK = 0,
+    SB_ERR_ARG = 1,          /* NULL / shape argument rejected */
+    SB_ERR_CUDA = 2,         /* a CUDA runtime call failed */
+    SB_ERR_OOM = 3,
+    SB_ERR_TOKEN_RANGE = 4,  /* a token id >= vocab reached a kernel */
+    SB_ERR_TIMEOUT = 5,      /* a bounded device-side wait ran out */
+    SB_ERR_NCCL = 6,
+    SB_ERR_SIZE = 7          /* size beyond a fixed capacity */
+};
+
+/* GEMM arithmetic modes */
+enum {
+    SB_GEMM_FP32X3 = 0,  /* tcgen05 kind::tf32, hi/lo split, 3 MMAs per k-block: FP32-level accuracy (default) */
+    SB_GEMM_TF32   = 1,  /* tcgen05 kind::tf32, one MMA per k-block */
+    SB_GEMM_BF16   = 2,  /* tcgen05 kind::f16 on BF16 copies (use_bf16) */
+    SB_GEMM_SIMT   = 3   /* FP32 FMA on CUDA cores */
+};
+
+typedef struct { size_t q, k, v, o, gate, up, down, in_norm, post_norm; } sb_layer_off_t;
+
+typedef struct {
+    float *layer_in, *x_norm_attn, *q, *k, *v, *attn_out, *lse, *post_attn_in, *x_norm_ffn, *gate, *up, *ffn_hidden;
+} sb_layer_act_t;
+
+typedef struct sb_ctx {
+    cuda_train_context_t pub;        /* MUST stay first */
+    uint32_t magic;
+    int status;                      /* last host-side status */
+    int* d_status;                   /* device status word (bounds checks, bounded waits) */
+    int gemm_mode;                   /* SB_GEMM_* (use_bf16 in pub overrides to BF16) */
+    int lora_exact;                  /* 0: reference behaviour (adapter dX term left out), 1: full chain rule */
+    float grad_clip;                 /* 0 = off (the reference has none) */
+    cuda_profiler_t* profiler;
+    size_t launches;                 /* kernels launched since the last reset */
+
+    /* model geometry of the resident weights */
+    int V, d, L, Hq, Hkv, hd, F, qd, kvd;
+    size_t n_params;
+    sb_layer_off_t* off;             /* [L] offsets into the arenas */
+    float *W, *G, *M, *Vv;           /* parameter, gradient, Adam m, Adam v arenas (flat order) */
+    int frozen_base;                 /* 1: LoRA mode, G/M/Vv not allocated */
+
+    /* LoRA adapters: one arena per kind, same flat order as the oracle */
+    int lora_rank, lora_mask; float lora_alpha;
+    size_t n_lora;
+    float *LW, *LG, *LM, *LV;
+    float* lora_tmp; size_t lora_tmp_cap;
+
+    /* activations */
+    int T_cap;
+    sb_layer_act_t* act;             /* [L] */
+    float* act_arena; size_t act_arena_bytes;
+    float *hidden, *hidden_norm, *final_in, *logits, *dlogits, *loss_rows;
+    float *g_hidden, *g_tmp, *g_xnorm, *g_q, *g_k, *g_v, *g_attn, *g_ffn, *g_gate, *g_up, *attn_delta;
+    uint32_t *tokens, *targets, *seq_starts, *pos_ids, *seq_ids;
+    int seq_cap, seq_starts_cap;
+    float* d_loss;                   /* device scalar */
+    float* d_gnorm;                  /* device scalar: sum of squares of all gradients */
+    void* h_pinned; size_t h_pinned_bytes;   /* pinned staging for tokens/targets/seq_starts/loss */
+
+    /* scratch shared by kernels (partials of deterministic reductions, sort tables) */
+    void* scratch; size_t scratch_bytes;
+    /* operand staging of the tensor-core GEMM (hi/lo, transposed copies) */
+    void* gemm_stage[4]; size_t gemm_stage_bytes[4];
+    /* rope cos/sin table */
+    float* rope_tab; int rope_tab_pos, rope_tab_hd; float rope_tab_theta;
+
+    /* data parallel */
+    void* nccl_comm; int dp_rank, dp_world;
+    void* comm_stream; void* ev_bucket[64]; int n_buckets;
+    size_t bucket_begin[64], bucket_end[64];
+} sb_ctx_t;
+
+static inline sb_ctx_t* sb_priv(cuda_train_context_t* c) {
+    sb_ctx_t* p = (sb_ctx_t*)c;
+    return (p && p->magic == SB_MAGIC) ? p : (sb_ctx_t*)0;
+}
+
+/* ---- helpers (context.cu) ---- */
+void* sb_scratch(sb_ctx_t* c, size_t bytes);                 /* grow-only device scratch; NULL on failure */
+void* sb_gemm_stage(sb_ctx_t* c, int slot, size_t bytes);
+int   sb_check(sb_ctx_t* c, int cuda_err, const char* what); /* records + prints, returns nonzero on error */
+void  sb_set_status(sb_ctx_t* c, int st);
+
+/* ---- kernel launchers (raw pointers) ---- */
+void sb_embed_lookup(sb_ctx_t*, const uint32_t* tok, const float* E, float* out, int T, int d, int V);
+void sb_rmsnorm(sb_ctx_t*, const float* x, const float* w, float* y, int rows, int cols, float eps);
+/* dx = rmsnorm'(x; dy); if resid != NULL, dx_out = resid + dx (fused residual-gradient add) */
+void sb_rmsnorm_backward(sb_ctx_t*, const float* x, const float* w, const float* dy, const float* resid,
+                         float* dx_out, float* dscale, int rows, int cols, float eps);
+void sb_add(sb_ctx_t*, const float* a, const float* b, float* c, size_t n);
+void sb_mul(sb_ctx_t*, const float* a, const float* b, float* c, size_t n);
+void sb_scale(sb_ctx_t*, float* a, size_t n, float alpha);
+void sb_silu(sb_ctx_t*, const float* x, float* y, size_t n);
+void sb_softmax(sb_ctx_t*, const float* x, float* y, int rows, int cols);
+void sb_silu_backward(sb_ctx_t*, const float* x, const float* dy, float* dx, size_t n);
+void sb_mul_backward(sb_ctx_t*, const float* A, const float* B, const float* dC, float* dA, float* dB, size_t n);
+void sb_swiglu(sb_ctx_t*, const float* gate, const float* up, float* out, size_t n);
+void sb_swiglu_backward(sb_ctx_t*, const float* gate, const float* up, const float* dout, float* dgate, float* dup, size_t n);
+void sb_seq_index(sb_ctx_t*, const uint32_t* seq_starts, int B, int T, uint32_t* pos_ids, uint32_t* seq_ids);
+void sb_rope(sb_ctx_t*, const float* in, float* out, const uint32_t* pos_ids, int T, int H, int hd, float theta,
+             int max_pos, int backward);
+void sb_attention(sb_ctx_t*, const float* Q, const float* K, const float* V, float* out, float* lse,
+                  const uint32_t* seq_starts_dev, const uint32_t* seq_ids, int T, int Hq, int Hkv, int hd);
+void sb_attention_backward(sb_ctx_t*, const float* Q, const float* K, const float* V, const float* O, const float* lse,
+                           const float* dO, float* dQ, float* dK, float* dV, int accumulate_kv,
+                           const uint32_t* seq_starts_dev, const uint32_t* seq_ids, int B, int T, int Hq, int Hkv, int hd);
+void sb_cross_entropy(sb_ctx_t*, const float* logits, const uint32_t* targets, float* grad, float* loss_rows,
+                      const uint32_t* pos_ids, const uint32_t* seq_ids, const uint32_t* seq_starts,
+                      int T, int V, int num_valid);
+void sb_reduce_sum(sb_ctx_t*, const float* in, float* out, size_t n);          /* deterministic; out[0] = sum */
+void sb_embedding_backward(sb_ctx_t*, const uint32_t* tok, const float* g, float* dE, int T, int d, int V);
+void sb_adamw(sb_ctx_t*, float* w, const float* g, float* m, float* v, size_t n, float lr, float b1, float b2,
+              float wd, float eps, int step, float grad_scale, const float* d_sumsq, float clip);
+void sb_sumsq(sb_ctx_t*, const float* g, size_t n, float* d_out);               /* deterministic sum of squares */
+void sb_nan_check(sb_ctx_t*, const float* x, size_t n, uint32_t* flags, uint32_t idx);
+/* C[M,N] (+)= op(A) op(B); same semantics as the reference's matmul_dispatch */
+void sb_gemm(sb_ctx_t*, const float* A, const float* B, float* C, int M, int N, int K, int tA, int tB, int acc);
+void sb_gemm_simt(sb_ctx_t*, const float* A, const float* B, float* C, int M, int N, int K, int tA, int tB, int acc);
+/* returns 0 if the tensor-core path took the call, nonzero if the shape is not eligible */
+int  sb_gemm_tc(sb_ctx_t*, const float* A, const float* B, float* C, int M, int N, int K, int tA, int tB, int acc, int mode);
+void sb_lora_backward(sb_ctx_t*, const float* dY, const float* X, const float* A, const float* B, float* gA, float* gB,
+                      float* tmp, int T, int in, int out, int r, float s);
+void sb_memset(sb_ctx_t*, void* p, int byte, size_t bytes);
+void sb_copy(sb_ctx_t*, void* dst, const void* src, size_t bytes);
+
+/* profiler hooks used around launches */
+int  sb_prof_begin(sb_ctx_t*, const char* name);
+void sb_prof_end(sb_ctx_t*, int op, size_t flops, size_t bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,718 @@
+/*
+ * train_step.c - host orchestration of the training step, in C.
+ *
+ * Implements the step-level C ABI of the reference (include/train_cuda.h:12-64,
+ * src/train_cuda.c): cuda_train_step_gpu_full[_batch], cuda_train_step_gpu_lora[_batch],
+ * cuda_download_full_weights, cuda_download_gpu_gradients, cuda_download_lora_weights,
+ * cuda_eval_forward, cuda_evaluate, cuda_train_zero_lora_grads, cuda_train_free.
+ *
+ * What is different from the reference's op list (src/train_cuda.c:2081-2287),
+ * with identical results:
+ *   - weights, gradients and both Adam moments live in four contiguous arenas
+ *     (one memset zeroes all gradients, one kernel launch is the whole AdamW
+ *     step, gradient buckets for data parallel are plain ranges);
+ *   - activations are written straight into their per-layer cache slots (the
+ *     reference copies every one of them, 12 device copies per layer);
+ *   - residual adds ride on the GEMM's `C +=` epilogue; the residual-gradient
+ *     add is fused into the RMSNorm backward; SwiGLU forward/backward are one
+ *     kernel each; dK/dV need no zero fill (attention backward owns them).
+ * The LoRA steps follow the complete chain rule of the reference's Vulkan
+ * LoRA step (src/train.c:6095-6186 forward adds, :6287-6615 backward), not the
+ * reference CUDA LoRA step, which feeds the LM-head gradient to every adapter
+ * (src/train_cuda.c:1847-1906).
+ */
+#include <cuda_runtime_api.h>
+#include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include "sb_internal.h"
+
+int sb_ensure_tokens(sb_ctx_t* c, int T, int B);
+int sb_dp_bucket_ready(sb_ctx_t* c, float* p, size_t n);      /* dp.c: no-ops when not data parallel */
+int sb_dp_join(sb_ctx_t* c);
+
+#define RMS_EPS 1e-5f   /* hard-coded in every training path of the reference (src/train_cuda.c:1984) */
+
+/* ------------------------------------------------------------------------ */
+/* geometry                                                                  */
+/* ------------------------------------------------------------------------ */
+static size_t layout_offsets(int V, int d, int L, int qd, int kvd, int F, sb_layer_off_t* off) {
+    size_t n = (size_t)V * d + (size_t)d;      /* embed, final_norm */
+    for (int l = 0; l < L; l++) {
+        sb_layer_off_t o;
+        o.q = n; n += (size_t)qd * d;
+        o.k = n; n += (size_t)kvd * d;
+        o.v = n; n += (size_t)kvd * d;
+        o.o = n; n += (size_t)d * qd;
+        o.gate = n; n += (size_t)F * d;
+        o.up = n; n += (size_t)F * d;
+        o.down = n; n += (size_t)d * F;
+        o.in_norm = n; n += (size_t)d;
+        o.post_norm = n; n += (size_t)d;
+        if (off) off[l] = o;
+    }
+    return n;
+}
+
+static void lora_dims(const sb_ctx_t* c, int a, int* in, int* out) {
+    switch (a) {
+        case 0: *in = c->d; *out = c->qd; break;
+        case 1: case 2: *in = c->d; *out = c->kvd; break;
+        case 3: *in = c->qd; *out = c->d; break;
+        case 4: case 5: *in = c->d; *out = c->F; break;
+        default: *in = c->F; *out = c->d; break;
+    }
+}
+static size_t lora_layer_params(const sb_ctx_t* c) {
+    size_t n = 0;
+    for (int a = 0; a < 7; a++) if (c->lora_mask & (1 << a)) { int in, out; lora_dims(c, a, &in, &out); n += (size_t)c->lora_rank * in + (size_t)out * c->lora_rank; }
+    return n;
+}
+/* offset of A of adapter a in layer l; B follows at + rank*in */
+static size_t lora_off(const sb_ctx_t* c, int l, int a) {
+    size_t n = lora_layer_params(c) * (size_t)l;
+    for (int b = 0; b < a; b++) if (c->lora_mask & (1 << b)) { int in, out; lora_dims(c, b, &in, &out); n += (size_t)c->lora_rank * in + (size_t)out * c->lora_rank; }
+    return n;
+}
+
+static cudaStream_t S(sb_ctx_t* c) { return (cudaStream_t)c->pub.stream; }
+
+static cuda_buffer_t* view(float* p, size_t floats) {
+    cuda_buffer_t* b = (cuda_buffer_t*)malloc(sizeof(cuda_buffer_t));
+    if (b) { b->data = p; b->size = floats * sizeof(float); }
+    return b;
+}
+static cuda_buffer_t** view_array(int n) { return (cuda_buffer_t**)calloc((size_t)n, sizeof(cuda_buffer_t*)); }
+static void free_view_array(cuda_buffer_t** a, int n) { if (!a) return; for (int i = 0; i < n; i++) free(a[i]); free(a); }
+
+/* ------------------------------------------------------------------------ */
+/* resident model                                                            */
+/* ------------------------------------------------------------------------ */
+static void free_model(sb_ctx_t* c) {
+    cuda_train_context_t* p = &c->pub;
+    int L = c->L;
+    if (c->W) cudaFree(c->W);
+    if (c->G) cudaFree(c->G);
+    if (c->M) cudaFree(c->M);
+    if (c->Vv) cudaFree(c->Vv);
+    c->W = c->G = c->M = c->Vv = NULL;
+    free(c->off); c->off = NULL;
+#define FREE1(f) do { free(p->f); p->f = NULL; } while (0)
+#define FREEL(f) do { free_view_array(p->f, L); p->f = NULL; } while (0)
+    FREE1(gpu_w_embed); FREE1(gpu_g_embed); FREE1(gpu_m_embed); FREE1(gpu_v_embed);
+    FREE1(gpu_w_final_norm); FREE1(gpu_g_final_norm); FREE1(gpu_m_final_norm); FREE1(gpu_v_final_norm);
+    FREEL(gpu_w_q); FREEL(gpu_g_q); FREEL(gpu_m_q); FREEL(gpu_v_q);
+    FREEL(gpu_w_k); FREEL(gpu_g_k); FREEL(gpu_m_k); FREEL(gpu_v_k);
+    FREEL(gpu_w_v); FREEL(gpu_g_v); FREEL(gpu_m_v); FREEL(gpu_v_v);
+    FREEL(gpu_w_o); FREEL(gpu_g_o); FREEL(gpu_m_o); FREEL(gpu_v_o);
+    FREEL(gpu_w_gate); FREEL(gpu_g_gate); FREEL(gpu_m_gate); FREEL(gpu_v_gate);
+    FREEL(gpu_w_up); FREEL(gpu_g_up); FREEL(gpu_m_up); FREEL(gpu_v_up);
+    FREEL(gpu_w_down); FREEL(gpu_g_down); FREEL(gpu_m_down); FREEL(gpu_v_down);
+    FREEL(gpu_w_in_norm); FREEL(gpu_g_in_norm); FREEL(gpu_m_in_norm); FREEL(gpu_v_in_norm);
+    FREEL(gpu_w_post_norm); FREEL(gpu_g_post_norm); FREEL(gpu_m_post_norm); FREEL(gpu_v_post_norm);
+#undef FREE1
+#undef FREEL
+    c->n_params = 0; c->L = 0;
+}
+
+/* expose the arenas through the reference's per-tensor buffer fields (views, not owners) */
+static void publish_views(sb_ctx_t* c) {
+    cuda_train_context_t* p = &c->pub;
+    int L = c->L, d = c->d, qd = c->qd, kvd = c->kvd, F = c->F;
+    size_t nE = (size_t)c->V * d;
+    float* A[4] = {c->W, c->G, c->M, c->Vv};
+    cuda_buffer_t** e[4] = {&p->gpu_w_embed, &p->gpu_g_embed, &p->gpu_m_embed, &p->gpu_v_embed};
+    cuda_buffer_t** f[4] = {&p->gpu_w_final_norm, &p->gpu_g_final_norm, &p->gpu_m_final_norm, &p->gpu_v_final_norm};
+    cuda_buffer_t*** lq[4] = {&p->gpu_w_q, &p->gpu_g_q, &p->gpu_m_q, &p->gpu_v_q};
+    cuda_buffer_t*** lk[4] = {&p->gpu_w_k, &p->gpu_g_k, &p->gpu_m_k, &p->gpu_v_k};
+    cuda_buffer_t*** lv[4] = {&p->gpu_w_v, &p->gpu_g_v, &p->gpu_m_v, &p->gpu_v_v};
+    cuda_buffer_t*** lo[4] = {&p->gpu_w_o, &p->gpu_g_o, &p->gpu_m_o, &p->gpu_v_o};
+    cuda_buffer_t*** lg[4] = {&p->gpu_w_gate, &p->gpu_g_gate, &p->gpu_m_gate, &p->gpu_v_gate};
+    cuda_buffer_t*** lu[4] = {&p->gpu_w_up, &p->gpu_g_up, &p->gpu_m_up, &p->gpu_v_up};
+    cuda_buffer_t*** ld[4] = {&p->gpu_w_down, &p->gpu_g_down, &p->gpu_m_down, &p->gpu_v_down};
+    cuda_buffer_t*** li[4] = {&p->gpu_w_in_norm, &p->gpu_g_in_norm, &p->gpu_m_in_norm, &p->gpu_v_in_norm};
+    cuda_buffer_t*** lp[4] = {&p->gpu_w_post_norm, &p->gpu_g_post_norm, &p->gpu_m_post_norm, &p->gpu_v_post_norm};
+    for (int k = 0; k < 4; k++) {
+        if (!A[k]) continue;
+        *e[k] = view(A[k], nE);
+        *f[k] = view(A[k] + nE, (size_t)d);
+        *lq[k] = view_array(L); *lk[k] = view_array(L); *lv[k] = view_array(L); *lo[k] = view_array(L);
+        *lg[k] = view_array(L); *lu[k] = view_array(L); *ld[k] = view_array(L); *li[k] = view_array(L); *lp[k] = view_array(L);
+        for (int l = 0; l < L; l++) {
+            const sb_layer_off_t* o = &c->off[l];
+            (*lq[k])[l] = view(A[k] + o->q, (size_t)qd * d);
+            (*lk[k])[l] = view(A[k] + o->k, (size_t)kvd * d);
+            (*lv[k])[l] = view(A[k] + o->v, (size_t)kvd * d);
+            (*lo[k])[l] = view(A[k] + o->o, (size_t)d * qd);
+            (*lg[k])[l] = view(A[k] + o->gate, (size_t)F * d);
+            (*lu[k])[l] = view(A[k] + o->up, (size_t)F * d);
+            (*ld[k])[l] = view(A[k] + o->down, (size_t)d * F);
+            (*li[k])[l] = view(A[k] + o->in_norm, (size_t)d);
+            (*lp[k])[l] = view(A[k] + o->post_norm, (size_t)d);
+        }
+    }
+    p->gpu_weights_num_layers = L; p->gpu_weights_hidden_size = d; p->gpu_weights_intermediate_size = F;
+    p->gpu_weights_q_dim = qd; p->gpu_weights_kv_dim = kvd; p->gpu_weights_vocab_size = c->V;
+}
+
+typedef void (*tensor_fn)(sb_ctx_t* c, weight_tensor_t* t, size_t off, void* arg);
+static void for_each_tensor(sb_ctx_t* c, trainable_weights_t* w, tensor_fn fn, void* arg) {
+    fn(c, &w->embed_tokens, 0, arg);
+    fn(c, &w->final_norm, (size_t)c->V * c->d, arg);
+    for (int l = 0; l < c->L; l++) {
+        layer_weights_t* y = &w->layers[l]; const sb_layer_off_t* o = &c->off[l];
+        fn(c, &y->q_proj, o->q, arg); fn(c, &y->k_proj, o->k, arg); fn(c, &y->v_proj, o->v, arg); fn(c, &y->o_proj, o->o, arg);
+        fn(c, &y->gate_proj, o->gate, arg); fn(c, &y->up_proj, o->up, arg); fn(c, &y->down_proj, o->down, arg);
+        fn(c, &y->input_norm, o->in_norm, arg); fn(c, &y->post_norm, o->post_norm, arg);
+    }
+}
+static size_t tensor_len(sb_ctx_t* c, size_t off) {
+    /* length of the tensor that starts at `off`, from the layout */
+    size_t nE = (size_t)c->V * c->d;
+    if (off == 0) return nE;
+    if (off == nE) return (size_t)c->d;
+    for (int l = 0; l < c->L; l++) {
+        const sb_layer_off_t* o = &c->off[l];
+        if (off == o->q) return (size_t)c->qd * c->d;
+        if (off == o->k || off == o->v) return (size_t)c->kvd * c->d;
+        if (off == o->o) return (size_t)c->d * c->qd;
+        if (off == o->gate || off == o->up || off == o->down) return (size_t)c->F * c->d;
+        if (off == o->in_norm || off == o->post_norm) return (size_t)c->d;
+    }
+    return 0;
+}
+static void up_tensor(sb_ctx_t* c, weight_tensor_t* t, size_t off, void* arg) {
+    (void)arg;
+    size_t n = tensor_len(c, off);
+    if (t->weight) cudaMemcpyAsync(c->W + off, t->weight, n * 4, cudaMemcpyHostToDevice, S(c));
+    if (!c->frozen_base) {
+        if (t->m) cudaMemcpyAsync(c->M + off, t->m, n * 4, cudaMemcpyHostToDevice, S(c));
+        if (t->v) cudaMemcpyAsync(c->Vv + off, t->v, n * 4, cudaMemcpyHostToDevice, S(c));
+    }
+}
+static void down_tensor(sb_ctx_t* c, weight_tensor_t* t, size_t off, void* arg) {
+    int what = *(int*)arg;     /* 0: weights + moments, 1: gradients */
+    size_t n = tensor_len(c, off);
+    if (what == 0) {
+        if (t->weight) cudaMemcpyAsync(t->weight, c->W + off, n * 4, cudaMemcpyDeviceToHost, S(c));
+        if (t->m && c->M) cudaMemcpyAsync(t->m, c->M + off, n * 4, cudaMemcpyDeviceToHost, S(c));
+        if (t->v && c->Vv) cudaMemcpyAsync(t->v, c->Vv + off, n * 4, cudaMemcpyDeviceToHost, S(c));
+    } else if (t->grad && c->G) {
+        cudaMemcpyAsync(t->grad, c->G + off, n * 4, cudaMemcpyDeviceToHost, S(c));
+    }
+}
+
+/* Allocate the arenas for this geometry and upload the host master copy once
+ * (the reference uploads once and afterwards only downloads, src/train_cuda.c:286-291). */
+static int ensure_model(sb_ctx_t* c, const train_state_t* st, int frozen_base) {
+    const model_config_t* cfg = st->config;
+    int V = cfg->vocab_size, d = cfg->hidden_size, L = cfg->num_hidden_layers, F = cfg->intermediate_size;
+    int Hq = cfg->num_attention_heads, Hkv = cfg->num_key_value_heads, hd = cfg->head_dim;
+    if (V <= 0 || d <= 0 || L <= 0 || F <= 0 || Hq <= 0 || Hkv <= 0 || hd <= 0 || Hq % Hkv) { sb_set_status(c, SB_ERR_ARG); return 1; }
+    if (c->W && c->V == V && c->d == d && c->L == L && c->F == F && c->Hq == Hq && c->Hkv == Hkv && c->hd == hd &&
+        c->frozen_base == frozen_base) return 0;
+    if (!st->full_weights) { sb_set_status(c, SB_ERR_ARG); return 1; }
+    cudaStreamSynchronize(S(c));
+    free_model(c);
+    c->V = V; c->d = d; c->L = L; c->F = F; c->Hq = Hq; c->Hkv = Hkv; c->hd = hd; c->qd = Hq * hd; c->kvd = Hkv * hd;
+    c->frozen_base = frozen_base;
+    c->off = (sb_layer_off_t*)calloc((size_t)L, sizeof(sb_layer_off_t));
+    if (!c->off) return 1;
+    c->n_params = layout_offsets(V, d, L, c->qd, c->kvd, F, c->off);
+    size_t bytes = c->n_params * sizeof(float);
+    if (sb_check(c, cudaMalloc((void**)&c->W, bytes), "weight arena")) { c->status = SB_ERR_OOM; return 1; }
+    if (!frozen_base) {
+        if (sb_check(c, cudaMalloc((void**)&c->G, bytes), "gradient arena") ||
+            sb_check(c, cudaMalloc((void**)&c->M, bytes), "Adam m arena") ||
+            sb_check(c, cudaMalloc((void**)&c->Vv, bytes), "Adam v arena")) { c->status = SB_ERR_OOM; return 1; }
+        cudaMemsetAsync(c->G, 0, bytes, S(c));
+        cudaMemsetAsync(c->M, 0, bytes, S(c));
+        cudaMemsetAsync(c->Vv, 0, bytes, S(c));
+    }
+    for_each_tensor(c, st->full_weights, up_tensor, NULL);
+    publish_views(c);
+    return sb_check(c, cudaStreamSynchronize(S(c)), "weight upload");
+}
+
+/* ------------------------------------------------------------------------ */
+/* LoRA adapters                                                             */
+/* ------------------------------------------------------------------------ */
+static lora_adapter_t** lora_list(const lora_model_t* m, int a) {
+    switch (a) { case 0: return m->q_adapters; case 1: return m->k_adapters; case 2: return m->v_adapters; case 3: return m->o_adapters;
+                 case 4: return m->gate_adapters; case 5: return m->up_adapters; default: return m->down_adapters; }
+}
+static cuda_lora_gpu_adapter_t* lora_pub(cuda_lora_gpu_state_t* s, int a) {
+    switch (a) { case 0: return &s->q; case 1: return &s->k; case 2: return &s->v; case 3: return &s->o;
+                 case 4: return &s->gate; case 5: return &s->up; default: return &s->down; }
+}
+static void free_lora(sb_ctx_t* c) {
+    if (c->LW) cudaFree(c->LW);
+    if (c->LG) cudaFree(c->LG);
+    if (c->LM) cudaFree(c->LM);
+    if (c->LV) cudaFree(c->LV);
+    if (c->lora_tmp) cudaFree(c->lora_tmp);
+    c->LW = c->LG = c->LM = c->LV = c->lora_tmp = NULL; c->lora_tmp_cap = 0;
+    cuda_lora_gpu_state_t* s = (cuda_lora_gpu_state_t*)c->pub.lora_gpu;
+    if (s) {
+        for (int a = 0; a < 7; a++) {
+            cuda_lora_gpu_adapter_t* g = lora_pub(s, a);
+            free_view_array(g->A, s->num_layers); free_view_array(g->B, s->num_layers);
+            free_view_array(g->gA, s->num_layers); free_view_array(g->gB, s->num_layers);
+            free_view_array(g->mA, s->num_layers); free_view_array(g->vA, s->num_layers);
+            free_view_array(g->mB, s->num_layers); free_view_array(g->vB, s->num_layers);
+        }
+        free(s);
+        c->pub.lora_gpu = NULL;
+    }
+    c->n_lora = 0; c->lora_rank = 0; c->lora_mask = 0;
+}
+
+static int ensure_lora(sb_ctx_t* c, const lora_model_t* m) {
+    int mask = 0;
+    for (int a = 0; a < 7; a++) { lora_adapter_t** ls = lora_list(m, a); if (ls && ls[0]) mask |= 1 << a; }
+    if (c->LW && c->lora_rank == m->rank && c->lora_mask == mask) return 0;
+    if (m->rank <= 0 || mask == 0) { sb_set_status(c, SB_ERR_ARG); return 1; }
+    cudaStreamSynchronize(S(c));
+    free_lora(c);
+    c->lora_rank = m->rank; c->lora_mask = mask; c->lora_alpha = m->alpha;
+    c->n_lora = lora_layer_params(c) * (size_t)c->L;
+    size_t bytes = c->n_lora * sizeof(float);
+    if (sb_check(c, cudaMalloc((void**)&c->LW, bytes), "lora weights") || sb_check(c, cudaMalloc((void**)&c->LG, bytes), "lora grads") ||
+        sb_check(c, cudaMalloc((void**)&c->LM, bytes), "lora m") || sb_check(c, cudaMalloc((void**)&c->LV, bytes), "lora v")) {
+        c->status = SB_ERR_OOM; return 1;
+    }
+    cudaMemsetAsync(c->LG, 0, bytes, S(c)); cudaMemsetAsync(c->LM, 0, bytes, S(c)); cudaMemsetAsync(c->LV, 0, bytes, S(c));
+    cuda_lora_gpu_state_t* s = (cuda_lora_gpu_state_t*)calloc(1, sizeof(cuda_lora_gpu_state_t));
+    if (!s) return 1;
+    s->num_layers = c->L; s->rank = m->rank; s->alpha = m->alpha; s->scale = m->alpha / (float)m->rank;
+    for (int a = 0; a < 7; a++) {
+        if (!(mask & (1 << a))) continue;
+        int in, out; lora_dims(c, a, &in, &out);
+        size_t nA = (size_t)m->rank * in, nB = (size_t)out * m->rank;
+        cuda_lora_gpu_adapter_t* g = lora_pub(s, a);
+        g->active = 1;
+        g->A = view_array(c->L); g->B = view_array(c->L); g->gA = view_array(c->L); g->gB = view_array(c->L);
+        g->mA = view_array(c->L); g->vA = view_array(c->L); g->mB = view_array(c->L); g->vB = view_array(c->L);
+        lora_adapter_t** ls = lora_list(m, a);
+        for (int l = 0; l < c->L; l++) {
+            size_t o = lora_off(c, l, a);
+            g->A[l] = view(c->LW + o, nA); g->B[l] = view(c->LW + o + nA, nB);
+            g->gA[l] = view(c->LG + o, nA); g->gB[l] = view(c->LG + o + nA, nB);
+            g->mA[l] = view(c->LM + o, nA); g->mB[l] = view(c->LM + o + nA, nB);
+            g->vA[l] = view(c->LV + o, nA); g->vB[l] = view(c->LV + o + nA, nB);
+            const lora_adapter_t* ad = ls[l];
+            if (!ad || ad->in_dim != in || ad->out_dim != out || ad->rank != m->rank) { sb_set_status(c, SB_ERR_ARG); free(s); return 1; }
+            cudaMemcpyAsync(c->LW + o, ad->A, nA * 4, cudaMemcpyHostToDevice, S(c));
+            cudaMemcpyAsync(c->LW + o + nA, ad->B, nB * 4, cudaMemcpyHostToDevice, S(c));
+            if (ad->m_A) cudaMemcpyAsync(c->LM + o, ad->m_A, nA * 4, cudaMemcpyHostToDevice, S(c));
+            if (ad->m_B) cudaMemcpyAsync(c->LM + o + nA, ad->m_B, nB * 4, cudaMemcpyHostToDevice, S(c));
+            if (ad->v_A) cudaMemcpyAsync(c->LV + o, ad->v_A, nA * 4, cudaMemcpyHostToDevice, S(c));
+            if (ad->v_B) cudaMemcpyAsync(c->LV + o + nA, ad->v_B, nB * 4, cudaMemcpyHostToDevice, S(c));
+        }
+    }
+    c->pub.lora_gpu = s;
+    return sb_check(c, cudaStreamSynchronize(S(c)), "lora upload");
+}
+
+/* ------------------------------------------------------------------------ */
+/* activations                                                               */
+/* ------------------------------------------------------------------------ */
+static void free_activations(sb_ctx_t* c) {
+    if (c->act_arena) cudaFree(c->act_arena);
+    c->act_arena = NULL; c->act_arena_bytes = 0; c->T_cap = 0;
+    free(c->act); c->act = NULL;
+}
+
+static size_t r4(size_t n) { return (n + 63) & ~(size_t)63; }     /* keep every slot 256-byte aligned */
+
+static int ensure_activations(sb_ctx_t* c, int T, int need_logits_grad) {
+    if (c->act_arena && c->T_cap >= T) return 0;
+    cudaStreamSynchronize(S(c));
+    free_activations(c);
+    size_t Td = r4((size_t)T * c->d), TF = r4((size_t)T * c->F), Tq = r4((size_t)T * c->qd), Tkv = r4((size_t)T * c->kvd);
+    size_t TH = r4((size_t)T * c->Hq), TV = r4((size_t)T * c->V);
+    size_t per_layer = 4 * Td + 2 * Tq + 2 * Tkv + TH + 3 * TF;    /* layer_in x_norm_attn post_attn_in x_norm_ffn | q attn_out | k v | lse | gate up ffn_hidden */
+    size_t shared = 3 * Td /* hidden_norm final_in (+1 spare) */ + 2 * TV + r4((size_t)T)
+                  + 3 * Td /* g_hidden g_tmp g_xnorm */ + 2 * Tq + 2 * Tkv + 3 * TF;
+    (void)need_logits_grad;
+    size_t total = per_layer * (size_t)c->L + shared;
+    if (sb_check(c, cudaMalloc((void**)&c->act_arena, total * sizeof(float)), "activation arena")) { c->status = SB_ERR_OOM; return 1; }
+    c->act_arena_bytes = total * sizeof(float); c->T_cap = T;
+    c->act = (sb_layer_act_t*)calloc((size_t)c->L, sizeof(sb_layer_act_t));
+    if (!c->act) return 1;
+    float* p = c->act_arena;
+#define TAKE(dst, n) do { dst = p; p += (n); } while (0)
+    for (int l = 0; l < c->L; l++) {
+        sb_layer_act_t* a = &c->act[l];
+        TAKE(a->layer_in, Td); TAKE(a->x_norm_attn, Td); TAKE(a->post_attn_in, Td); TAKE(a->x_norm_ffn, Td);
+        TAKE(a->q, Tq); TAKE(a->attn_out, Tq); TAKE(a->k, Tkv); TAKE(a->v, Tkv); TAKE(a->lse, TH);
+        TAKE(a->gate, TF); TAKE(a->up, TF); TAKE(a->ffn_hidden, TF);
+    }
+    TAKE(c->hidden_norm, Td); TAKE(c->final_in, Td); TAKE(c->hidden, Td);
+    TAKE(c->logits, TV); TAKE(c->dlogits, TV); TAKE(c->loss_rows, r4((size_t)T));
+    TAKE(c->g_hidden, Td); TAKE(c->g_tmp, Td); TAKE(c->g_xnorm, Td);
+    TAKE(c->g_q, Tq); TAKE(c->g_attn, Tq); TAKE(c->g_k, Tkv); TAKE(c->g_v, Tkv);
+    TAKE(c->g_ffn, TF); TAKE(c->g_gate, TF); TAKE(c->g_up, TF);
+#undef TAKE
+    return 0;
+}
+
+static int ensure_pinned(sb_ctx_t* c, size_t bytes) {
+    if (c->h_pinned && c->h_pinned_bytes >= bytes) return 0;
+    cudaStreamSynchronize(S(c));
+    if (c->h_pinned) cudaFreeHost(c->h_pinned);
+    c->h_pinned = NULL; c->h_pinned_bytes = 0;
+    size_t want = bytes < 65536 ? 65536 : bytes;
+    if (sb_check(c, cudaMallocHost(&c->h_pinned, want), "pinned staging")) return 1;
+    c->h_pinned_bytes = want;
+    return 0;
+}
+
+/* ------------------------------------------------------------------------ */
+/* the step                                                                  */
+/* ------------------------------------------------------------------------ */
+typedef struct { const float *A, *B; float *gA, *gB; int in, out; } lora_ref_t;
+static int lora_get(sb_ctx_t* c, int l, int a, lora_ref_t* r) {
+    if (!c->LW || !(c->lora_mask & (1 << a))) return 0;
+    lora_dims(c, a, &r->in, &r->out);
+    size_t o = lora_off(c, l, a), nA = (size_t)c->lora_rank * r->in;
+    r->A = c->LW + o; r->B = c->LW + o + nA; r->gA = c->LG + o; r->gB = c->LG + o + nA;
+    return 1;
+}
+
+/* Y[T,out] (+)= X[T,in] W[out,in]^T, plus the adapter's (s X A^T) B^T when one is active */
+static void linear_fwd(sb_ctx_t* c, int use_lora, int l, int a, const float* X, const float* W, float* Y, int T, int in, int out, int acc) {
+    sb_gemm(c, X, W, Y, T, out, in, 0, 1, acc);
+    lora_ref_t r;
+    if (use_lora && lora_get(c, l, a, &r)) {
+        float s = c->lora_alpha / (float)c->lora_rank;
+        sb_gemm(c, X, r.A, c->lora_tmp, T, c->lora_rank, in, 0, 1, 0);
+        sb_scale(c, c->lora_tmp, (size_t)T * c->lora_rank, s);
+        sb_gemm(c, c->lora_tmp, r.B, Y, T, out, c->lora_rank, 0, 1, 1);
+    }
+}
+/* adapter gradients for one projection; in exact mode also dX += (s dY B) A */
+static void lora_bwd(sb_ctx_t* c, int l, int a, const float* dY, const float* X, float* dX, int T) {
+    lora_ref_t r;
+    if (!lora_get(c, l, a, &r)) return;
+    float s = c->lora_alpha / (float)c->lora_rank;
+    sb_lora_backward(c, dY, X, r.A, r.B, r.gA, r.gB, c->lora_tmp, T, r.in, r.out, c->lora_rank, s);
+    if (c->lora_exact && dX) sb_gemm(c, c->lora_tmp, r.A, dX, T, r.in, c->lora_rank, 0, 0, 1);
+}
+
+static void forward_pass(sb_ctx_t* c, int T, int max_seq, float theta, int use_lora) {
+    const int d = c->d, F = c->F, qd = c->qd, kvd = c->kvd, L = c->L;
+    const size_t Td = (size_t)T * d;
+    sb_embed_lookup(c, c->tokens, c->W, c->act[0].layer_in, T, d, c->V);
+    for (int l = 0; l < L; l++) {
+        const sb_layer_off_t* o = &c->off[l];
+        sb_layer_act_t* a = &c->act[l];
+        float* next_in = (l + 1 < L) ? c->act[l + 1].layer_in : c->final_in;
+        sb_rmsnorm(c, a->layer_in, c->W + o->in_norm, a->x_norm_attn, T, d, RMS_EPS);
+        linear_fwd(c, use_lora, l, 0, a->x_norm_attn, c->W + o->q, a->q, T, d, qd, 0);
+        linear_fwd(c, use_lora, l, 1, a->x_norm_attn, c->W + o->k, a->k, T, d, kvd, 0);
+        linear_fwd(c, use_lora, l, 2, a->x_norm_attn, c->W + o->v, a->v, T, d, kvd, 0);
+        sb_rope(c, a->q, a->q, c->pos_ids, T, c->Hq, c->hd, theta, max_seq, 0);
+        sb_rope(c, a->k, a->k, c->pos_ids, T, c->Hkv, c->hd, theta, max_seq, 0);
+        sb_attention(c, a->q, a->k, a->v, a->attn_out, a->lse, c->seq_starts, c->seq_ids, T, c->Hq, c->Hkv, c->hd);
+        sb_copy(c, a->post_attn_in, a->layer_in, Td * sizeof(float));
+        linear_fwd(c, use_lora, l, 3, a->attn_out, c->W + o->o, a->post_attn_in, T, qd, d, 1);
+        sb_rmsnorm(c, a->post_attn_in, c->W + o->post_norm, a->x_norm_ffn, T, d, RMS_EPS);
+        linear_fwd(c, use_lora, l, 4, a->x_norm_ffn, c->W + o->gate, a->gate, T, d, F, 0);
+        linear_fwd(c, use_lora, l, 5, a->x_norm_ffn, c->W + o->up, a->up, T, d, F, 0);
+        sb_swiglu(c, a->gate, a->up, a->ffn_hidden, (size_t)T * F);
+        sb_copy(c, next_in, a->post_attn_in, Td * sizeof(float));
+        linear_fwd(c, use_lora, l, 6, a->ffn_hidden, c->W + o->down, next_in, T, F, d, 1);
+    }
+    sb_rmsnorm(c, c->final_in, c->W + (size_t)c->V * d, c->hidden_norm, T, d, RMS_EPS);
+    sb_gemm(c, c->hidden_norm, c->W, c->logits, T, c->V, d, 0, 1, 0);       /* tied LM head */
+}
+
+/* `reduce`: hand every finished gradient range to the data-parallel all-reduce as soon as it is complete */
+static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, int full, int reduce) {
+    const int d = c->d, F = c->F, qd = c->qd, kvd = c->kvd, L = c->L, V = c->V;
+    float* gh = c->g_hidden; float* gx = c->g_xnorm;
+    float* Gd = full ? c->G : NULL;
+    float* norm_sink = c->g_tmp;                 /* LoRA mode: norm-scale gradients are discarded */
+    if (!full) sb_memset(c, norm_sink, 0, (size_t)d * sizeof(float));
+    sb_gemm(c, c->dlogits, c->W, gx, T, d, V, 0, 0, 0);
+    if (full) sb_gemm(c, c->dlogits, c->hidden_norm, Gd, V, d, T, 1, 0, 1);
+    sb_rmsnorm_backward(c, c->final_in, c->W + (size_t)V * d, gx, NULL, gh, full ? Gd + (size_t)V * d : norm_sink, T, d, RMS_EPS);
+    for (int l = L - 1; l >= 0; l--) {
+        const sb_layer_off_t* o = &c->off[l];
+        sb_layer_act_t* a = &c->act[l];
+        /* FFN */
+        if (full) sb_gemm(c, gh, a->ffn_hidden, Gd + o->down, d, F, T, 1, 0, 1);
+        sb_gemm(c, gh, c->W + o->down, c->g_ffn, T, F, d, 0, 0, 0);
+        if (!full) lora_bwd(c, l, 6, gh, a->ffn_hidden, c->g_ffn, T);
+        sb_swiglu_backward(c, a->gate, a->up, c->g_ffn, c->g_gate, c->g_up, (size_t)T * F);
+        if (full) {
+            sb_gemm(c, c->g_gate, a->x_norm_ffn, Gd + o->gate, F, d, T, 1, 0, 1);
+            sb_gemm(c, c->g_up, a->x_norm_ffn, Gd + o->up, F, d, T, 1, 0, 1);
+        }
+        sb_gemm(c, c->g_gate, c->W + o->gate, gx, T, d, F, 0, 0, 0);
+        sb_gemm(c, c->g_up, c->W + o->up, gx, T, d, F, 0, 0, 1);
+        if (!full) { lora_bwd(c, l, 4, c->g_gate, a->x_norm_ffn, gx, T); lora_bwd(c, l, 5, c->g_up, a->x_norm_ffn, gx, T); }
+        sb_rmsnorm_backward(c, a->post_attn_in, c->W + o->post_norm, gx, gh, gh, full ? Gd + o->post_norm : norm_sink, T, d, RMS_EPS);
+        /* attention */
+        if (full) sb_gemm(c, gh, a->attn_out, Gd + o->o, d, qd, T, 1, 0, 1);
+        sb_gemm(c, gh, c->W + o->o, c->g_attn, T, qd, d, 0, 0, 0);
+        if (!full) lora_bwd(c, l, 3, gh, a->attn_out, c->g_attn, T);
+        sb_attention_backward(c, a->q, a->k, a->v, a->attn_out, a->lse, c->g_attn, c->g_q, c->g_k, c->g_v, 0,
+                              c->seq_starts, c->seq_ids, B, T, c->Hq, c->Hkv, c->hd);
+        sb_rope(c, c->g_q, c->g_q, c->pos_ids, T, c->Hq, c->hd, theta, max_seq, 1);
+        sb_rope(c, c->g_k, c->g_k, c->pos_ids, T, c->Hkv, c->hd, theta, max_seq, 1);
+        if (full) {
+            sb_gemm(c, c->g_q, a->x_norm_attn, Gd + o->q, qd, d, T, 1, 0, 1);
+            sb_gemm(c, c->g_k, a->x_norm_attn, Gd + o->k, kvd, d, T, 1, 0, 1);
+            sb_gemm(c, c->g_v, a->x_norm_attn, Gd + o->v, kvd, d, T, 1, 0, 1);
+        }
+        sb_gemm(c, c->g_q, c->W + o->q, gx, T, d, qd, 0, 0, 0);
+        sb_gemm(c, c->g_k, c->W + o->k, gx, T, d, kvd, 0, 0, 1);
+        sb_gemm(c, c->g_v, c->W + o->v, gx, T, d, kvd, 0, 0, 1);
+        if (!full) { lora_bwd(c, l, 0, c->g_q, a->x_norm_attn, gx, T); lora_bwd(c, l, 1, c->g_k, a->x_norm_attn, gx, T); lora_bwd(c, l, 2, c->g_v, a->x_norm_attn, gx, T); }
+        sb_rmsnorm_backward(c, a->layer_in, c->W + o->in_norm, gx, gh, gh, full ? Gd + o->in_norm : norm_sink, T, d, RMS_EPS);
+        if (reduce) {
+            if (full) sb_dp_bucket_ready(c, Gd + o->q, o->post_norm + (size_t)d - o->q);
+            else { size_t per = lora_layer_params(c); sb_dp_bucket_ready(c, c->LG + per * (size_t)l, per); }
+        }
+    }
+    if (full) {
+        sb_embedding_backward(c, c->tokens, gh, Gd, T, d, V);
+        if (reduce) sb_dp_bucket_ready(c, Gd, c->off[0].q);      /* embedding (LM head + scatter) and final norm */
+    }
+}
+
+/* tokens, targets and sequence starts: clamp negative ids to 0, last token of a
+ * sequence has target 0 (src/train_cuda.c:2030-2043); staged in pinned memory */
+static int upload_batch(sb_ctx_t* c, const int* tokens, int T, const int* seq_starts, int B, int* max_seq_out) {
+    if (sb_ensure_tokens(c, T, B)) return 1;
+    size_t words = (size_t)2 * T + (size_t)B + 1 + 4;
+    if (ensure_pinned(c, words * sizeof(uint32_t) + 64)) return 1;
+    uint32_t* h_tok = (uint32_t*)c->h_pinned; uint32_t* h_tgt = h_tok + T; uint32_t* h_ss = h_tgt + T;
+    int max_seq = 0;
+    for (int b = 0; b < B; b++) {
+        int s = seq_starts[b], e = seq_starts[b + 1];
+        if (s < 0 || e < s || e > T) { sb_set_status(c, SB_ERR_ARG); return 1; }
+        if (e - s > max_seq) max_seq = e - s;
+        for (int t = s; t < e; t++) {
+            int tk = tokens[t];
+            h_tok[t] = tk < 0 ? 0u : (uint32_t)tk;
+            if (t < e - 1) { int nx = tokens[t + 1]; h_tgt[t] = nx < 0 ? 0u : (uint32_t)nx; } else h_tgt[t] = 0u;
+        }
+    }
+    if (seq_starts[0] != 0 || seq_starts[B] != T) { sb_set_status(c, SB_ERR_ARG); return 1; }
+    for (int b = 0; b <= B; b++) h_ss[b] = (uint32_t)seq_starts[b];
+    cudaMemcpyAsync(c->tokens, h_tok, (size_t)T * 4, cudaMemcpyHostToDevice, S(c));
+    cudaMemcpyAsync(c->targets, h_tgt, (size_t)T * 4, cudaMemcpyHostToDevice, S(c));
+    cudaMemcpyAsync(c->seq_starts, h_ss, (size_t)(B + 1) * 4, cudaMemcpyHostToDevice, S(c));
+    sb_seq_index(c, c->seq_starts, B, T, c->pos_ids, c->seq_ids);
+    *max_seq_out = max_seq;
+    return 0;
+}
+
+static float lr_for_step(const train_state_t* st, int accum) {
+    /* 100-step linear warm-up, then divided by the accumulation count (src/train_cuda.c:2298-2303) */
+    float lr = st->learning_rate;
+    if (st->optimizer_step < 100.0f) lr = st->learning_rate * (st->optimizer_step / 100.0f);
+    return lr / accum;
+}
+
+static float step_common(train_state_t* st, int* tokens, int T, int* seq_starts, int B, cuda_train_context_t* ctx, int full, int train) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!st || !st->config || !c || !tokens || !seq_starts || T <= 0 || B <= 0) return -1.0f;
+    if (full && !st->full_weights) return -1.0f;
+    if (!full && train && !st->lora) return -1.0f;
+    int num_valid = T - B;
+    if (num_valid <= 0) return 0.0f;
+    int use_lora = (!full && st->lora != NULL);
+    if (ensure_model(c, st, full ? 0 : (use_lora ? 1 : c->frozen_base))) return -1.0f;
+    if (use_lora && ensure_lora(c, st->lora)) return -1.0f;
+    if (ensure_activations(c, T, train)) return -1.0f;
+    if (use_lora && c->lora_tmp_cap < (size_t)T * c->lora_rank) {
+        cudaStreamSynchronize(S(c));
+        if (c->lora_tmp) cudaFree(c->lora_tmp);
+        c->lora_tmp = NULL;
+        if (sb_check(c, cudaMalloc((void**)&c->lora_tmp, (size_t)T * c->lora_rank * sizeof(float)), "lora tmp")) return -1.0f;
+        c->lora_tmp_cap = (size_t)T * c->lora_rank;
+    }
+    float theta = st->config->rope_theta > 0 ? st->config->rope_theta : 10000.0f;
+    int max_seq = 0;
+    if (upload_batch(c, tokens, T, seq_starts, B, &max_seq)) return -1.0f;
+    c->pub.batch_size = B;
+
+    if (train && st->accumulation_counter == 0) {
+        if (full) sb_memset(c, c->G, 0, c->n_params * sizeof(float));
+        else sb_memset(c, c->LG, 0, c->n_lora * sizeof(float));
+    }
+    forward_pass(c, T, max_seq, theta, use_lora);
+    sb_cross_entropy(c, c->logits, c->targets, c->dlogits, c->loss_rows, c->pos_ids, c->seq_ids, c->seq_starts, T, c->V, num_valid);
+    sb_reduce_sum(c, c->loss_rows, c->d_loss, (size_t)T);
+
+    if (train) {
+        int accum = st->gradient_accumulation_steps < 1 ? 1 : st->gradient_accumulation_steps;
+        int last_micro = (st->accumulation_counter + 1 >= accum);
+        backward_pass(c, T, B, max_seq, theta, full, last_micro && c->dp_world > 1);
+        st->accumulation_counter++;
+        if (st->accumulation_counter >= accum) {
+            st->optimizer_step++;
+            float lr = lr_for_step(st, accum);
+            float* w = full ? c->W : c->LW; float* g = full ? c->G : c->LG;
+            float* m = full ? c->M : c->LM; float* v = full ? c->Vv : c->LV;
+            size_t n = full ? c->n_params : c->n_lora;
+            float gscale = 1.0f;
+            if (c->dp_world > 1) {
+                if (sb_dp_join(c)) return -1.0f;
+                gscale = 1.0f / (float)c->dp_world;
+            }
+            const float* sumsq = NULL;
+            if (c->grad_clip > 0.f) { sb_sumsq(c, g, n, c->d_gnorm); sumsq = c->d_gnorm; }
+            sb_adamw(c, w, g, m, v, n, lr, 0.9f, 0.999f, 0.01f, 1e-8f, st->optimizer_step, gscale, sumsq, c->grad_clip);
+            st->accumulation_counter = 0;
+        }
+    }
+    float* h_loss = (float*)((char*)c->h_pinned + c->h_pinned_bytes - 64);
+    cudaMemcpyAsync(h_loss, c->d_loss, sizeof(float), cudaMemcpyDeviceToHost, S(c));
+    if (sb_check(c, cudaStreamSynchronize(S(c)), "training step")) return -1.0f;
+    float loss = *h_loss / (float)num_valid;
+    if (train && st->debug_nan_check && (isnan(loss) || isinf(loss))) { st->nan_detected = 1; return NAN; }
+    return loss;
+}
+
+float cuda_train_step_gpu_full_batch(train_state_t* state, int* tokens_packed, int total_tokens, int* seq_starts, int batch_size,
+                                     cuda_train_context_t* ctx) {
+    return step_common(state, tokens_packed, total_tokens, seq_starts, batch_size, ctx, 1, 1);
+}
+float cuda_train_step_gpu_full(train_state_t* state, int* tokens, int num_tokens, cuda_train_context_t* ctx) {
+    int ss[2] = {0, num_tokens};
+    return step_common(state, tokens, num_tokens, ss, 1, ctx, 1, 1);
+}
+float cuda_train_step_gpu_lora_batch(train_state_t* state, int* tokens_packed, int total_tokens, int* seq_starts, int batch_size,
+                                     cuda_train_context_t* ctx) {
+    return step_common(state, tokens_packed, total_tokens, seq_starts, batch_size, ctx, 0, 1);
+}
+float cuda_train_step_gpu_lora(train_state_t* state, int* tokens, int num_tokens, cuda_train_context_t* ctx) {
+    int ss[2] = {0, num_tokens};
+    return step_common(state, tokens, num_tokens, ss, 1, ctx, 0, 1);
+}
+
+/* forward + loss only (src/train_cuda.c:2677); uses the adapters when the state trains LoRA */
+float cuda_eval_forward(train_state_t* state, int* tokens, int num_tokens, cuda_train_context_t* ctx) {
+    if (!state || !state->config || !ctx || num_tokens < 2) return -1.0f;
+    int ss[2] = {0, num_tokens};
+    int full = state->lora == NULL;
+    return step_common(state, tokens, num_tokens, ss, 1, ctx, full, 0);
+}
+
+/* src/train_cuda.c:2812-2846: evenly spaced samples, mean loss, perplexity = exp(mean) */
+float cuda_evaluate(train_state_t* state, int* val_tokens, int num_val_tokens, int* offsets, int num_samples, int max_seq_len,
+                    int max_eval_samples, cuda_train_context_t* ctx, float* out_perplexity) {
+    if (!state || !val_tokens || num_samples <= 0 || !ctx) { if (out_perplexity) *out_perplexity = 0.0f; return -1.0f; }
+    int max_eval = max_eval_samples > 0 ? max_eval_samples : num_samples;
+    int stride = num_samples > max_eval ? num_samples / max_eval : 1;
+    double total = 0.0; int valid = 0;
+    for (int s = 0; s < num_samples; s += stride) {
+        int start = offsets[s], end = (s + 1 < num_samples) ? offsets[s + 1] : num_val_tokens;
+        int n = end - start;
+        if (n > max_seq_len) n = max_seq_len;
+        if (n < 2) continue;
+        float loss = cuda_eval_forward(state, &val_tokens[start], n, ctx);
+        if (loss >= 0.0f && !isnan(loss)) { total += loss; valid++; }
+    }
+    float avg = valid > 0 ? (float)(total / valid) : -1.0f;
+    if (out_perplexity) *out_perplexity = avg > 0.0f ? expf(avg) : 0.0f;
+    return avg;
+}
+
+/* src/train_cuda.c:1244 / :1317 */
+void cuda_download_full_weights(cuda_train_context_t* ctx, train_state_t* state) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c || !state || !state->full_weights || !c->W) return;
+    int what = 0;
+    for_each_tensor(c, state->full_weights, down_tensor, &what);
+    sb_check(c, cudaStreamSynchronize(S(c)), "weight download");
+}
+void cuda_download_gpu_gradients(cuda_train_context_t* ctx, train_state_t* state) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c || !state || !state->full_weights || !c->G) return;
+    int what = 1;
+    for_each_tensor(c, state->full_weights, down_tensor, &what);
+    sb_check(c, cudaStreamSynchronize(S(c)), "gradient download");
+}
+/* src/cuda_train_context.cu:3330: adapters A, B and their Adam moments back to the host model.
+ * Gradients are copied too when the host adapter has room for them. */
+void cuda_download_lora_weights(cuda_train_context_t* ctx, void* lora_ptr) {
+    sb_ctx_t* c = sb_priv(ctx);
+    lora_model_t* m = (lora_model_t*)lora_ptr;
+    if (!c || !m || !c->LW) return;
+    for (int a = 0; a < 7; a++) {
+        if (!(c->lora_mask & (1 << a))) continue;
+        lora_adapter_t** ls = lora_list(m, a);
+        if (!ls) continue;
+        int in, out; lora_dims(c, a, &in, &out);
+        size_t nA = (size_t)c->lora_rank * in, nB = (size_t)out * c->lora_rank;
+        for (int l = 0; l < c->L; l++) {
+            lora_adapter_t* ad = ls[l];
+            if (!ad) continue;
+            size_t o = lora_off(c, l, a);
+            cudaMemcpyAsync(ad->A, c->LW + o, nA * 4, cudaMemcpyDeviceToHost, S(c));
+            cudaMemcpyAsync(ad->B, c->LW + o + nA, nB * 4, cudaMemcpyDeviceToHost, S(c));
+            if (ad->m_A) cudaMemcpyAsync(ad->m_A, c->LM + o, nA * 4, cudaMemcpyDeviceToHost, S(c));
+            if (ad->m_B) cudaMemcpyAsync(ad->m_B, c->LM + o + nA, nB * 4, cudaMemcpyDeviceToHost, S(c));
+            if (ad->v_A) cudaMemcpyAsync(ad->v_A, c->LV + o, nA * 4, cudaMemcpyDeviceToHost, S(c));
+            if (ad->v_B) cudaMemcpyAsync(ad->v_B, c->LV + o + nA, nB * 4, cudaMemcpyDeviceToHost, S(c));
+            if (ad->grad_A) cudaMemcpyAsync(ad->grad_A, c->LG + o, nA * 4, cudaMemcpyDeviceToHost, S(c));
+            if (ad->grad_B) cudaMemcpyAsync(ad->grad_B, c->LG + o + nA, nB * 4, cudaMemcpyDeviceToHost, S(c));
+        }
+    }
+    sb_check(c, cudaStreamSynchronize(S(c)), "lora download");
+}
+void cuda_train_zero_lora_grads(cuda_train_context_t* ctx) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c || !c->LG) return;
+    sb_memset(c, c->LG, 0, c->n_lora * sizeof(float));
+}
+
+/* Extension: logits [T,V] of the last step/eval, copied to the host */
+int seraph_b200_download_logits(cuda_train_context_t* ctx, float* out, int T) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c || !out || !c->logits || T > c->T_cap) return SB_ERR_ARG;
+    cudaMemcpyAsync(out, c->logits, (size_t)T * c->V * 4, cudaMemcpyDeviceToHost, S(c));
+    return sb_check(c, cudaStreamSynchronize(S(c)), "logits download") ? SB_ERR_CUDA : SB_OK;
+}
+
+/* Extension: forget the resident weights, adapters and optimizer state, so that the next step uploads
+ * them again from the host state (the reference uploads once per context, src/train_cuda.c:286-291). */
+int seraph_b200_reset_model(cuda_train_context_t* ctx) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c) return SB_ERR_ARG;
+    cudaStreamSynchronize(S(c));
+    free_lora(c);
+    free_model(c);
+    return SB_OK;
+}
+
+/* src/cuda_train_context.cu:2404 */
+void sb_dp_finalize(sb_ctx_t* c);
+void cuda_train_free(cuda_train_context_t* ctx) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c) return;
+    cudaStreamSynchronize(S(c));
+    sb_dp_finalize(c);
+    free_lora(c);
+    free_activations(c);
+    free_model(c);
+    if (c->tokens) cudaFree(c->tokens);
+    if (c->seq_starts) cudaFree(c->seq_starts);
+    if (c->scratch) cudaFree(c->scratch);
+    for (int i = 0; i < 4; i++) if (c->gemm_stage[i]) cudaFree(c->gemm_stage[i]);
+    if (c->rope_tab) cudaFree(c->rope_tab);
+    if (c->d_status) cudaFree(c->d_status);
+    if (c->d_loss) cudaFree(c->d_loss);
+    if (c->h_pinned) cudaFreeHost(c->h_pinned);
+    if (c->pub.debug_nan_flags) cuda_train_buffer_free(ctx, c->pub.debug_nan_flags);
+    cudaStreamDestroy(S(c));
+    c->magic = 0;
+    free(c);
+}

@@ -138,6 +138,9 @@ int refshim_cuda_init(void* p, int device, int flash) {
     s->cuda = cuda_train_init(device);
     if (!s->cuda) return -1;
     ((cuda_train_context_t*)s->cuda)->use_flash_attn = flash;
+    /* the reference CLI sizes this before the first step (tools/seraph_train_cuda.c:215-216) */
+    ((cuda_train_context_t*)s->cuda)->max_fwd_buffer_size =
+        (size_t)s->cfg.max_position_embeddings * (size_t)s->cfg.intermediate_size * sizeof(float);
     s->st.cuda_ctx = s->cuda;
     return 0;
 }

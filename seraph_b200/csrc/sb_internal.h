@@ -15,7 +15,7 @@
 extern "C" {
 #endif
 
-#define SB_MAGIC 0x5342323030u   /* "SB200" */
+#define SB_MAGIC 0x53423230u   /* "SB20" */
 
 /* status codes (seraph_b200_last_status) */
 enum {

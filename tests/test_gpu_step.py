@@ -219,6 +219,7 @@ def test_full_size_properties_qwen_shaped(ctx):
     assert a["loss"] == b["loss"] and np.array_equal(a["grads"], b["grads"])
     assert abs(a["loss"][0] - np.log(cfg.V)) < 0.5
     st = api.TrainState(cfg, p, accum=2)
+    ctx.lib.seraph_b200_reset_model(ctx.h)
     api.step_full_batch(ctx, st, tok, ss)
     api.step_full_batch(ctx, st, tok, ss)
     ctx.lib.cuda_download_gpu_gradients(ctx.h, st.h)

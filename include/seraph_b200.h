@@ -181,6 +181,17 @@ float seraph_b200_timer_stop(cuda_train_context_t* ctx);
 /* Forget the resident weights, adapters and optimizer state: the next step uploads them again from
  * the host state (like the reference, a context otherwise uploads once and then only downloads). */
 int seraph_b200_reset_model(cuda_train_context_t* ctx);
+/* Repeat the full-weight step on the batch the previous step call left on the device: nothing is
+ * copied between host and device and the call does not wait for the GPU.  The mean loss of the
+ * last step can be read (with a synchronisation) through seraph_b200_last_loss. */
+int seraph_b200_step_full_resident(train_state_t* state, cuda_train_context_t* ctx);
+float seraph_b200_last_loss(cuda_train_context_t* ctx);
+/* Per-class kernel timing with CUDA events on the context's stream.  read() fills
+ * out[class*4 + {0 ms, 1 algorithmic FLOPs, 2 algorithmic bytes, 3 launches}] and resets. */
+int seraph_b200_timing_enable(cuda_train_context_t* ctx, int on);
+int seraph_b200_timing_classes(void);
+const char* seraph_b200_timing_class_name(int cls);
+int seraph_b200_timing_read(cuda_train_context_t* ctx, double* out);
 /* Logits [T, vocab] of the last step or evaluation, copied to host memory. */
 int seraph_b200_download_logits(cuda_train_context_t* ctx, float* out, int T);
 
@@ -202,6 +213,8 @@ int seraph_dp_world(cuda_train_context_t* ctx);
  * 3 o, 4 gate, 5 up, 6 down; flat LoRA order: per layer, per selected adapter,
  * A [r,in] then B [out,r]. */
 train_state_t* seraph_b200_state_create(int V, int d, int L, int Hq, int Hkv, int hd, int F, float theta, float lr, int accum);
+/* weights only on the host: gradients and Adam moments live on the device alone */
+train_state_t* seraph_b200_state_create_lean(int V, int d, int L, int Hq, int Hkv, int hd, int F, float theta, float lr, int accum);
 void seraph_b200_state_free(train_state_t* st);
 size_t seraph_b200_state_param_count(train_state_t* st);
 void seraph_b200_state_set(train_state_t* st, int which, const float* flat);

@@ -87,6 +87,10 @@ def load():
         "seraph_b200_swiglu": (None, [vp, B, B, B, sz]), "seraph_b200_swiglu_backward": (None, [vp, B, B, B, B, B, sz]),
         "seraph_b200_timer_start": (None, [vp]), "seraph_b200_timer_stop": (f, [vp]),
         "seraph_b200_download_logits": (i, [vp, vp, i]), "seraph_b200_reset_model": (i, [vp]),
+        "seraph_b200_step_full_resident": (i, [vp, vp]), "seraph_b200_last_loss": (f, [vp]),
+        "seraph_b200_timing_enable": (i, [vp, i]), "seraph_b200_timing_classes": (i, []),
+        "seraph_b200_timing_class_name": (C.c_char_p, [i]), "seraph_b200_timing_read": (i, [vp, vp]),
+        "seraph_b200_state_create_lean": (vp, [i] * 7 + [f, f, i]),
         "seraph_dp_get_unique_id": (i, [vp]), "seraph_dp_init": (i, [vp, i, i, vp]), "seraph_dp_finalize": (None, [vp]),
         "seraph_dp_wait": (i, [vp, i]), "seraph_dp_world": (i, [vp]),
         "seraph_b200_state_create": (vp, [i] * 7 + [f, f, i]), "seraph_b200_state_free": (None, [vp]),
@@ -217,10 +221,11 @@ class Context:
 class TrainState:
     """A train_state_t built in memory (seraph_b200_state_*), flat-array access."""
 
-    def __init__(self, cfg, params, lr=3.14e-4, accum=1):
+    def __init__(self, cfg, params, lr=3.14e-4, accum=1, lean=False):
         self.lib = load()
         self.cfg = cfg
-        self.h = self.lib.seraph_b200_state_create(cfg.V, cfg.d, cfg.L, cfg.Hq, cfg.Hkv, cfg.hd, cfg.F, cfg.theta, lr, accum)
+        create = self.lib.seraph_b200_state_create_lean if lean else self.lib.seraph_b200_state_create
+        self.h = create(cfg.V, cfg.d, cfg.L, cfg.Hq, cfg.Hkv, cfg.hd, cfg.F, cfg.theta, lr, accum)
         if not self.h:
             raise MemoryError("seraph_b200_state_create failed")
         self.n = int(self.lib.seraph_b200_state_param_count(self.h))

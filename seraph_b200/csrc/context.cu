@@ -41,10 +41,14 @@ void* sb_gemm_stage(sb_ctx_t* c, int slot, size_t bytes) {
 }
 
 void sb_memset(sb_ctx_t* c, void* p, int byte, size_t bytes) {
+    int t = sb_tick_begin(c, SB_CLS_COPY);
     sb_check(c, cudaMemsetAsync(p, byte, bytes, (cudaStream_t)c->pub.stream), "memset");
+    sb_tick_end(c, t, 0, (double)bytes);
 }
 void sb_copy(sb_ctx_t* c, void* dst, const void* src, size_t bytes) {
+    int t = sb_tick_begin(c, SB_CLS_COPY);
     sb_check(c, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)c->pub.stream), "copy");
+    sb_tick_end(c, t, 0, 2.0 * (double)bytes);
 }
 
 // ---------------------------------------------------------------------------
@@ -170,6 +174,69 @@ void cuda_train_copy_buffer(cuda_train_context_t* ctx, cuda_buffer_t* src, cuda_
     if (!ctx || !src || !dst) return;
     sb_check(sb_priv(ctx), cudaMemcpyAsync(dst->data, src->data, bytes, cudaMemcpyDeviceToDevice,
                                            (cudaStream_t)ctx->stream), "copy_buffer");
+}
+
+// ---------------------------------------------------------------------------
+// Per-class timer: one CUDA-event pair per launch, recorded on the context's
+// stream, summed per kernel class on read-out.
+// ---------------------------------------------------------------------------
+int sb_tick_begin(sb_ctx_t* c, int cls) {
+    if (!c->timing_on) return -1;
+    if (c->tick_n >= c->tick_cap) {
+        int ncap = c->tick_cap ? c->tick_cap * 2 : 4096;
+        void** ev = (void**)realloc(c->tick_ev, sizeof(void*) * 2 * ncap);
+        int* cl = (int*)realloc(c->tick_cls, sizeof(int) * ncap);
+        double* fl = (double*)realloc(c->tick_flops, sizeof(double) * ncap);
+        double* by = (double*)realloc(c->tick_bytes, sizeof(double) * ncap);
+        if (ev) c->tick_ev = ev;
+        if (cl) c->tick_cls = cl;
+        if (fl) c->tick_flops = fl;
+        if (by) c->tick_bytes = by;
+        if (!ev || !cl || !fl || !by) return -1;
+        for (int i = c->tick_cap; i < ncap; i++) {
+            cudaEvent_t a, b;
+            cudaEventCreate(&a); cudaEventCreate(&b);
+            c->tick_ev[2 * i] = a; c->tick_ev[2 * i + 1] = b;
+        }
+        c->tick_cap = ncap;
+    }
+    int i = c->tick_n++;
+    c->tick_cls[i] = cls; c->tick_flops[i] = 0; c->tick_bytes[i] = 0;
+    cudaEventRecord((cudaEvent_t)c->tick_ev[2 * i], (cudaStream_t)c->pub.stream);
+    return i;
+}
+void sb_tick_end(sb_ctx_t* c, int slot, double flops, double bytes) {
+    if (slot < 0) return;
+    cudaEventRecord((cudaEvent_t)c->tick_ev[2 * slot + 1], (cudaStream_t)c->pub.stream);
+    c->tick_flops[slot] = flops; c->tick_bytes[slot] = bytes;
+}
+int seraph_b200_timing_enable(cuda_train_context_t* ctx, int on) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c) return SB_ERR_ARG;
+    c->timing_on = on ? 1 : 0;
+    if (on) c->tick_n = 0;
+    return SB_OK;
+}
+int seraph_b200_timing_classes(void) { return SB_NCLS; }
+const char* seraph_b200_timing_class_name(int cls) {
+    static const char* names[SB_NCLS] = {"gemm", "gemm_operand_prep", "attention_fwd", "attention_bwd", "rmsnorm_fwd", "rmsnorm_bwd",
+                                         "swiglu", "rope", "cross_entropy", "embedding", "adamw", "copy_fill", "other"};
+    return (cls >= 0 && cls < SB_NCLS) ? names[cls] : "";
+}
+// out[cls*4 + {0: milliseconds, 1: algorithmic FLOPs, 2: algorithmic bytes, 3: launches}]; resets the record
+int seraph_b200_timing_read(cuda_train_context_t* ctx, double* out) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c || !out) return SB_ERR_ARG;
+    cudaStreamSynchronize((cudaStream_t)ctx->stream);
+    for (int i = 0; i < SB_NCLS * 4; i++) out[i] = 0.0;
+    for (int i = 0; i < c->tick_n; i++) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, (cudaEvent_t)c->tick_ev[2 * i], (cudaEvent_t)c->tick_ev[2 * i + 1]) != cudaSuccess) continue;
+        int k = c->tick_cls[i];
+        out[k * 4 + 0] += ms; out[k * 4 + 1] += c->tick_flops[i]; out[k * 4 + 2] += c->tick_bytes[i]; out[k * 4 + 3] += 1.0;
+    }
+    c->tick_n = 0;
+    return SB_OK;
 }
 
 // ---------------------------------------------------------------------------

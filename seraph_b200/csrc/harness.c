@@ -22,9 +22,12 @@ typedef struct {
     int lora_mask;
 } harness_t;
 
+static int g_lean = 0;     /* weights only: no host copies of gradients and Adam moments */
 static int wt_alloc(weight_tensor_t* t, size_t n) {
-    t->weight = (float*)calloc(n, 4); t->grad = (float*)calloc(n, 4); t->m = (float*)calloc(n, 4); t->v = (float*)calloc(n, 4);
+    t->weight = (float*)calloc(n, 4);
     t->size = n;
+    if (g_lean) { t->grad = t->m = t->v = NULL; return !t->weight; }
+    t->grad = (float*)calloc(n, 4); t->m = (float*)calloc(n, 4); t->v = (float*)calloc(n, 4);
     return !(t->weight && t->grad && t->m && t->v);
 }
 static void wt_free(weight_tensor_t* t) { free(t->weight); free(t->grad); free(t->m); free(t->v); }
@@ -66,6 +69,15 @@ train_state_t* seraph_b200_state_create(int V, int d, int L, int Hq, int Hkv, in
     return &h->st;
 }
 
+/* same, but the host state holds the weights only (a quarter of the host memory): gradients and
+ * Adam moments then live on the device alone and cannot be downloaded into this state */
+train_state_t* seraph_b200_state_create_lean(int V, int d, int L, int Hq, int Hkv, int hd, int F, float theta, float lr, int accum) {
+    g_lean = 1;
+    train_state_t* st = seraph_b200_state_create(V, d, L, Hq, Hkv, hd, F, theta, lr, accum);
+    g_lean = 0;
+    return st;
+}
+
 static void f_free(weight_tensor_t* t, void* a) { (void)a; wt_free(t); }
 static void lora_free_all(harness_t* h);
 void seraph_b200_state_free(train_state_t* st) {
@@ -84,7 +96,8 @@ typedef struct { float* flat; int which; int set; } io_t;
 static void f_io(weight_tensor_t* t, void* a) {
     io_t* io = (io_t*)a;
     float* p = io->which == 0 ? t->weight : io->which == 1 ? t->grad : io->which == 2 ? t->m : t->v;
-    if (io->set) memcpy(p, io->flat, t->size * 4); else memcpy(io->flat, p, t->size * 4);
+    if (!p) { if (!io->set) memset(io->flat, 0, t->size * 4); }
+    else if (io->set) memcpy(p, io->flat, t->size * 4); else memcpy(io->flat, p, t->size * 4);
     io->flat += t->size;
 }
 /* which: 0 weights, 1 gradients, 2 Adam m, 3 Adam v */

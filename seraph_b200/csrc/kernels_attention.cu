@@ -332,9 +332,12 @@ void sb_attention(sb_ctx_t* c, const float* Q, const float* K, const float* V, f
     dim3 grid((T + AT - 1) / AT, Hq);
     size_t smem = ((size_t)3 * hd * AT + (size_t)AT * PLD) * sizeof(float);
     cudaStream_t s = (cudaStream_t)c->pub.stream;
+    int tk = sb_tick_begin(c, SB_CLS_ATTN_FWD);
 #define CALL(N) if (set_smem(c, attn_fwd_kernel<N>, smem)) attn_fwd_kernel<N><<<grid, AT_THREADS, smem, s>>>(Q, K, V, out, lse, seq_starts, seq_ids, T, Hq, Hkv, hd, scale);
     DISPATCH_CPT(hd, CALL);
 #undef CALL
+    // causal: about half of the T x S score matrix per head is live; counted as 2*T*T/B... reported per call as 2 matmuls
+    sb_tick_end(c, tk, 0.0, 4.0 * ((double)T * Hq * hd * 2 + (double)T * Hkv * hd * 2));
     c->launches++;
 }
 
@@ -349,6 +352,7 @@ void sb_attention_backward(sb_ctx_t* c, const float* Q, const float* K, const fl
     float* delta = (float*)sb_scratch(c, (size_t)T * Hq * sizeof(float));
     if (!delta) return;
     int warps = T * Hq;
+    int tk = sb_tick_begin(c, SB_CLS_ATTN_BWD);
     attn_delta_kernel<<<(warps * 32 + 255) / 256, 256, 0, s>>>(dO, O, delta, T, Hq, hd);
     dim3 gq((T + AT - 1) / AT, Hq), gk((T + AT - 1) / AT, Hkv);
     size_t smem_q = ((size_t)5 * hd * AT + (size_t)AT * PLD) * sizeof(float);
@@ -359,6 +363,7 @@ void sb_attention_backward(sb_ctx_t* c, const float* Q, const float* K, const fl
 #define CALL(N) if (set_smem(c, attn_bwd_dkv_kernel<N>, smem_k)) attn_bwd_dkv_kernel<N><<<gk, AT_THREADS, smem_k, s>>>(Q, K, V, dO, lse, delta, dK, dV, accumulate_kv, seq_starts, seq_ids, T, Hq, Hkv, hd, scale);
     DISPATCH_CPT(hd, CALL);
 #undef CALL
+    sb_tick_end(c, tk, 0.0, 4.0 * ((double)T * Hq * hd * 4 + (double)T * Hkv * hd * 4));
     c->launches += 3;
 }
 

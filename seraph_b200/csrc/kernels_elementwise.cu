@@ -62,7 +62,9 @@ template <int OP, bool BINARY>
 static void ew_launch(sb_ctx_t* c, const float* a, const float* b, float* o, size_t n) {
     if (!n) return;
     int vec = aligned16(a) && aligned16(o) && (!BINARY || aligned16(b));
+    int tk = sb_tick_begin(c, OP == OP_SWIGLU ? SB_CLS_SWIGLU : SB_CLS_OTHER);
     ew_kernel<OP, BINARY><<<ew_grid(c, (n + 3) / 4), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(a, b, o, n, vec);
+    sb_tick_end(c, tk, 0.0, (BINARY ? 12.0 : 8.0) * (double)n);
     c->launches++;
 }
 
@@ -211,7 +213,9 @@ void sb_mul_backward(sb_ctx_t* c, const float* A, const float* B, const float* d
 void sb_swiglu_backward(sb_ctx_t* c, const float* gate, const float* up, const float* dout, float* dgate, float* dup, size_t n) {
     if (!n) return;
     int vec = aligned16(gate) && aligned16(up) && aligned16(dout) && aligned16(dgate) && aligned16(dup);
+    int tk = sb_tick_begin(c, SB_CLS_SWIGLU);
     swiglu_bwd_kernel<<<ew_grid(c, (n + 3) / 4), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(gate, up, dout, dgate, dup, n, vec);
+    sb_tick_end(c, tk, 0.0, 20.0 * (double)n);
     c->launches++;
 }
 
@@ -220,7 +224,9 @@ void sb_embed_lookup(sb_ctx_t* c, const uint32_t* tok, const float* E, float* ou
     int sms = c->pub.gpu_sm_count > 0 ? c->pub.gpu_sm_count : 148;
     int grid = T < sms * 8 ? T : sms * 8;
     int vec = ((d & 3) == 0) && aligned16(E) && aligned16(out);
+    int tk = sb_tick_begin(c, SB_CLS_EMBED);
     embed_lookup_kernel<<<grid, EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(tok, E, out, T, d, V, vec, c->d_status);
+    sb_tick_end(c, tk, 0.0, 8.0 * T * d);
     c->launches++;
 }
 
@@ -245,6 +251,7 @@ void sb_rope(sb_ctx_t* c, const float* in, float* out, const uint32_t* pos_ids, 
         rope_table_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)c->pub.stream>>>((float2*)c->rope_tab, cap, half, hd, theta);
         c->launches++;
     }
+    int tk = sb_tick_begin(c, SB_CLS_ROPE);
     if ((hd & 3) == 0 && aligned16(in) && aligned16(out)) {
         size_t work = (size_t)T * H * (hd / 4);
         rope_kernel<<<ew_grid(c, work), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(in, out, pos_ids, (const float2*)c->rope_tab, T, H, hd, backward);
@@ -252,6 +259,7 @@ void sb_rope(sb_ctx_t* c, const float* in, float* out, const uint32_t* pos_ids, 
         size_t work = (size_t)T * H * half;
         rope_pair_kernel<<<ew_grid(c, work), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(in, out, pos_ids, (const float2*)c->rope_tab, T, H, hd, backward);
     }
+    sb_tick_end(c, tk, 0.0, 8.0 * T * H * hd);
     c->launches++;
 }
 

@@ -363,7 +363,9 @@ void sb_rmsnorm(sb_ctx_t* c, const float* x, const float* w, float* y, int rows,
     if (rows <= 0 || cols <= 0) return;
     int grid = rows < sm_count(c) * 8 ? rows : sm_count(c) * 8;
     int vec = (cols % 4 == 0) && aligned16(x) && aligned16(w) && aligned16(y);
+    int tk = sb_tick_begin(c, SB_CLS_NORM_FWD);
     rmsnorm_kernel<<<grid, RB_THREADS, 0, (cudaStream_t)c->pub.stream>>>(x, w, y, rows, cols, eps, vec);
+    sb_tick_end(c, tk, 0.0, 8.0 * rows * cols);
     c->launches++;
 }
 
@@ -374,8 +376,10 @@ void sb_rmsnorm_backward_with_partials(sb_ctx_t* c, const float* x, const float*
                                        float* dx_out, float* dscale, int rows, int cols, float eps, float* partial, int grid) {
     int vec = (cols % 4 == 0) && aligned16(x) && aligned16(w) && aligned16(dy) && aligned16(dx_out) && (!resid || aligned16(resid));
     cudaStream_t s = (cudaStream_t)c->pub.stream;
+    int tk = sb_tick_begin(c, SB_CLS_NORM_BWD);
     rmsnorm_bwd_kernel<<<grid, RB_THREADS, 0, s>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps, vec);
     colsum_partials_kernel<<<(cols + 255) / 256, 256, 0, s>>>(partial, dscale, grid, cols);
+    sb_tick_end(c, tk, 0.0, (resid ? 16.0 : 12.0) * rows * cols);
     c->launches += 2;
 }
 
@@ -400,8 +404,10 @@ void sb_cross_entropy(sb_ctx_t* c, const float* logits, const uint32_t* targets,
                       const uint32_t* pos_ids, const uint32_t* seq_ids, const uint32_t* seq_starts, int T, int V, int num_valid) {
     if (T <= 0 || V <= 0) return;
     int vec = (V % 4 == 0) && aligned16(logits) && aligned16(grad);
+    int tk = sb_tick_begin(c, SB_CLS_CE);
     cross_entropy_kernel<<<T, CE_THREADS, 0, (cudaStream_t)c->pub.stream>>>(logits, targets, grad, loss_rows, pos_ids, seq_ids,
                                                                           seq_starts, T, V, 1.0f / (float)num_valid, vec, c->d_status);
+    sb_tick_end(c, tk, 0.0, 12.0 * T * V);
     c->launches++;
 }
 
@@ -414,9 +420,11 @@ static void sum_impl(sb_ctx_t* c, const float* in, float* out, size_t n, bool sq
     float* partial = (float*)sb_scratch(c, (size_t)grid * sizeof(float));
     if (!partial) return;
     int vec = aligned16(in);
+    int tk = sb_tick_begin(c, SB_CLS_OTHER);
     if (square) partial_sum_kernel<true><<<grid, RB_THREADS, 0, s>>>(in, n, partial, vec);
     else        partial_sum_kernel<false><<<grid, RB_THREADS, 0, s>>>(in, n, partial, vec);
     final_sum_kernel<<<1, RB_THREADS, 0, s>>>(partial, grid, out);
+    sb_tick_end(c, tk, 0.0, 4.0 * (double)n);
     c->launches += 2;
 }
 void sb_reduce_sum(sb_ctx_t* c, const float* in, float* out, size_t n) { sum_impl(c, in, out, n, false); }
@@ -436,6 +444,7 @@ void sb_embedding_backward(sb_ctx_t* c, const uint32_t* tok, const float* g, flo
     int* base = (int*)sb_scratch(c, ints * sizeof(int));
     if (!base) return;
     int *cnt = base, *start = cnt + V, *rows = start + V, *meta = rows + V, *sorted_pos = meta + 4, *chunk_cnt = sorted_pos + T;
+    int tk = sb_tick_begin(c, SB_CLS_EMBED);
     cudaMemsetAsync(cnt, 0, (size_t)V * sizeof(int), s);
     cudaMemsetAsync(chunk_cnt, 0, (size_t)nchunk * V * sizeof(int), s);
     eb_count_kernel<<<nchunk, EB_CHUNK, 0, s>>>(tok, T, V, chunk_cnt, cnt, c->d_status);
@@ -445,6 +454,7 @@ void sb_embedding_backward(sb_ctx_t* c, const uint32_t* tok, const float* g, flo
     if (grid > sm_count(c) * 8) grid = sm_count(c) * 8;
     int vec = (d % 4 == 0) && aligned16(g) && aligned16(dE);
     eb_segsum_kernel<<<grid, RB_THREADS, 0, s>>>(g, dE, rows, start, cnt, sorted_pos, meta, d, vec);
+    sb_tick_end(c, tk, 0.0, 12.0 * T * d);      // upper bound: every token a distinct row
     c->launches += 4;
 }
 
@@ -480,8 +490,10 @@ void sb_adamw(sb_ctx_t* c, float* w, const float* g, float* m, float* v, size_t 
     size_t need = (n + RB_THREADS * 4 - 1) / (RB_THREADS * 4);
     size_t grid = (size_t)sm_count(c) * 8;
     if (grid > need) grid = need;
+    int tk = sb_tick_begin(c, SB_CLS_ADAMW);
     adamw_kernel<<<(int)grid, RB_THREADS, 0, (cudaStream_t)c->pub.stream>>>(w, g, m, v, n, lr, b1, b2, wd, eps, c1, c2,
                                                                          grad_scale, d_sumsq, clip, vec);
+    sb_tick_end(c, tk, 0.0, 28.0 * (double)n);
     c->launches++;
 }
 

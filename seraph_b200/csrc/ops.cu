@@ -64,7 +64,9 @@ void sb_gemm(sb_ctx_t* c, const float* A, const float* B, float* C, int M, int N
     if (M <= 0 || N <= 0 || K < 0) return;
     int mode = c->pub.use_bf16 ? SB_GEMM_BF16 : c->gemm_mode;
     if (mode != SB_GEMM_SIMT && sb_gemm_tc(c, A, B, C, M, N, K, tA, tB, acc, mode) == 0) return;
+    int t = sb_tick_begin(c, SB_CLS_GEMM);
     sb_gemm_simt(c, A, B, C, M, N, K, tA, tB, acc);
+    sb_tick_end(c, t, 2.0 * M * N * K, 4.0 * ((double)M * K + (double)N * K + (double)M * N * (acc ? 2 : 1)));
 }
 
 // reference: cuda_train_matmul, src/cuda_train_context.cu:2697

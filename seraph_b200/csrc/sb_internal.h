@@ -29,6 +29,10 @@ enum {
     SB_ERR_SIZE = 7          /* size beyond a fixed capacity */
 };
 
+/* kernel classes of the built-in per-class timer (seraph_b200_timing_*) */
+enum { SB_CLS_GEMM = 0, SB_CLS_GEMM_PREP, SB_CLS_ATTN_FWD, SB_CLS_ATTN_BWD, SB_CLS_NORM_FWD, SB_CLS_NORM_BWD,
+       SB_CLS_SWIGLU, SB_CLS_ROPE, SB_CLS_CE, SB_CLS_EMBED, SB_CLS_ADAMW, SB_CLS_COPY, SB_CLS_OTHER, SB_NCLS };
+
 /* GEMM arithmetic modes */
 enum {
     SB_GEMM_FP32X3 = 0,  /* tcgen05 kind::tf32, hi/lo split, 3 MMAs per k-block: FP32-level accuracy (default) */
@@ -53,6 +57,9 @@ typedef struct sb_ctx {
     float grad_clip;                 /* 0 = off (the reference has none) */
     cuda_profiler_t* profiler;
     size_t launches;                 /* kernels launched since the last reset */
+    int timing_on;                   /* per-class CUDA-event timing of every launch */
+    void** tick_ev; int tick_cap, tick_n;   /* event pairs: tick_ev[2*i], tick_ev[2*i+1] */
+    int* tick_cls; double* tick_flops; double* tick_bytes;
 
     /* model geometry of the resident weights */
     int V, d, L, Hq, Hkv, hd, F, qd, kvd;
@@ -75,6 +82,7 @@ typedef struct sb_ctx {
     float *g_hidden, *g_tmp, *g_xnorm, *g_q, *g_k, *g_v, *g_attn, *g_ffn, *g_gate, *g_up, *attn_delta;
     uint32_t *tokens, *targets, *seq_starts, *pos_ids, *seq_ids;
     int seq_cap, seq_starts_cap;
+    int res_T, res_B, res_max_seq;   /* geometry of the batch currently resident on the device */
     float* d_loss;                   /* device scalar */
     float* d_gnorm;                  /* device scalar: sum of squares of all gradients */
     void* h_pinned; size_t h_pinned_bytes;   /* pinned staging for tokens/targets/seq_starts/loss */
@@ -102,6 +110,10 @@ void* sb_scratch(sb_ctx_t* c, size_t bytes);                 /* grow-only device
 void* sb_gemm_stage(sb_ctx_t* c, int slot, size_t bytes);
 int   sb_check(sb_ctx_t* c, int cuda_err, const char* what); /* records + prints, returns nonzero on error */
 void  sb_set_status(sb_ctx_t* c, int st);
+
+/* per-class timer: returns a slot (or -1 when timing is off) */
+int  sb_tick_begin(sb_ctx_t* c, int cls);
+void sb_tick_end(sb_ctx_t* c, int slot, double flops, double bytes);
 
 /* ---- kernel launchers (raw pointers) ---- */
 void sb_embed_lookup(sb_ctx_t*, const uint32_t* tok, const float* E, float* out, int T, int d, int V);

@@ -519,9 +519,10 @@ static float lr_for_step(const train_state_t* st, int accum) {
     return lr / accum;
 }
 
-static float step_common(train_state_t* st, int* tokens, int T, int* seq_starts, int B, cuda_train_context_t* ctx, int full, int train) {
+static float step_common(train_state_t* st, int* tokens, int T, int* seq_starts, int B, cuda_train_context_t* ctx, int full, int train, int resident) {
     sb_ctx_t* c = sb_priv(ctx);
-    if (!st || !st->config || !c || !tokens || !seq_starts || T <= 0 || B <= 0) return -1.0f;
+    if (!st || !st->config || !c || T <= 0 || B <= 0) return -1.0f;
+    if (!resident && (!tokens || !seq_starts)) return -1.0f;
     if (full && !st->full_weights) return -1.0f;
     if (!full && train && !st->lora) return -1.0f;
     int num_valid = T - B;
@@ -539,7 +540,14 @@ static float step_common(train_state_t* st, int* tokens, int T, int* seq_starts,
     }
     float theta = st->config->rope_theta > 0 ? st->config->rope_theta : 10000.0f;
     int max_seq = 0;
-    if (upload_batch(c, tokens, T, seq_starts, B, &max_seq)) return -1.0f;
+    if (resident) {
+        /* batch of the previous call is still on the device: no host-to-device copy, no loss read-back */
+        if (c->res_T != T || c->res_B != B) { sb_set_status(c, SB_ERR_ARG); return -1.0f; }
+        max_seq = c->res_max_seq;
+    } else {
+        if (upload_batch(c, tokens, T, seq_starts, B, &max_seq)) return -1.0f;
+        c->res_T = T; c->res_B = B; c->res_max_seq = max_seq;
+    }
     c->pub.batch_size = B;
 
     if (train && st->accumulation_counter == 0) {
@@ -572,6 +580,7 @@ static float step_common(train_state_t* st, int* tokens, int T, int* seq_starts,
             st->accumulation_counter = 0;
         }
     }
+    if (resident) return sb_check(c, cudaGetLastError(), "training step (resident batch)") ? -1.0f : 0.0f;
     float* h_loss = (float*)((char*)c->h_pinned + c->h_pinned_bytes - 64);
     cudaMemcpyAsync(h_loss, c->d_loss, sizeof(float), cudaMemcpyDeviceToHost, S(c));
     if (sb_check(c, cudaStreamSynchronize(S(c)), "training step")) return -1.0f;
@@ -582,19 +591,19 @@ static float step_common(train_state_t* st, int* tokens, int T, int* seq_starts,
 
 float cuda_train_step_gpu_full_batch(train_state_t* state, int* tokens_packed, int total_tokens, int* seq_starts, int batch_size,
                                      cuda_train_context_t* ctx) {
-    return step_common(state, tokens_packed, total_tokens, seq_starts, batch_size, ctx, 1, 1);
+    return step_common(state, tokens_packed, total_tokens, seq_starts, batch_size, ctx, 1, 1, 0);
 }
 float cuda_train_step_gpu_full(train_state_t* state, int* tokens, int num_tokens, cuda_train_context_t* ctx) {
     int ss[2] = {0, num_tokens};
-    return step_common(state, tokens, num_tokens, ss, 1, ctx, 1, 1);
+    return step_common(state, tokens, num_tokens, ss, 1, ctx, 1, 1, 0);
 }
 float cuda_train_step_gpu_lora_batch(train_state_t* state, int* tokens_packed, int total_tokens, int* seq_starts, int batch_size,
                                      cuda_train_context_t* ctx) {
-    return step_common(state, tokens_packed, total_tokens, seq_starts, batch_size, ctx, 0, 1);
+    return step_common(state, tokens_packed, total_tokens, seq_starts, batch_size, ctx, 0, 1, 0);
 }
 float cuda_train_step_gpu_lora(train_state_t* state, int* tokens, int num_tokens, cuda_train_context_t* ctx) {
     int ss[2] = {0, num_tokens};
-    return step_common(state, tokens, num_tokens, ss, 1, ctx, 0, 1);
+    return step_common(state, tokens, num_tokens, ss, 1, ctx, 0, 1, 0);
 }
 
 /* forward + loss only (src/train_cuda.c:2677); uses the adapters when the state trains LoRA */
@@ -602,7 +611,7 @@ float cuda_eval_forward(train_state_t* state, int* tokens, int num_tokens, cuda_
     if (!state || !state->config || !ctx || num_tokens < 2) return -1.0f;
     int ss[2] = {0, num_tokens};
     int full = state->lora == NULL;
-    return step_common(state, tokens, num_tokens, ss, 1, ctx, full, 0);
+    return step_common(state, tokens, num_tokens, ss, 1, ctx, full, 0, 0);
 }
 
 /* src/train_cuda.c:2812-2846: evenly spaced samples, mean loss, perplexity = exp(mean) */
@@ -672,6 +681,25 @@ void cuda_train_zero_lora_grads(cuda_train_context_t* ctx) {
     sb_ctx_t* c = sb_priv(ctx);
     if (!c || !c->LG) return;
     sb_memset(c, c->LG, 0, c->n_lora * sizeof(float));
+}
+
+/* Extension: repeat the full-weight step on the batch the previous step call left on the device.
+ * Nothing crosses the host-device boundary and the call does not wait for the GPU; the loss stays
+ * on the device (seraph_b200_last_loss).  Returns 0 or a status code. */
+int seraph_b200_step_full_resident(train_state_t* state, cuda_train_context_t* ctx) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c || !state || c->res_T <= 0) return SB_ERR_ARG;
+    float r = step_common(state, NULL, c->res_T, NULL, c->res_B, ctx, 1, 1, 1);
+    return r < 0.f ? (c->status ? c->status : SB_ERR_ARG) : SB_OK;
+}
+/* mean loss of the last step, read from the device (synchronises) */
+float seraph_b200_last_loss(cuda_train_context_t* ctx) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c || c->res_T <= c->res_B) return -1.0f;
+    float v = 0.f;
+    cudaStreamSynchronize(S(c));
+    if (cudaMemcpy(&v, c->d_loss, sizeof v, cudaMemcpyDeviceToHost) != cudaSuccess) return -1.0f;
+    return v / (float)(c->res_T - c->res_B);
 }
 
 /* Extension: logits [T,V] of the last step/eval, copied to the host */

@@ -253,7 +253,7 @@ def cpu_baseline(mc, quick=True, reps=1):
     L = O.ref_lib("cpu_fast") or O.ref_lib("cpu")
     if L is None:
         return {"value": None, "unit": "tokens/s", "cores": 1, "kind": "reference", "sample": "oracle/_ref not built"}
-    n = 16 if quick else 32
+    n = 4 if quick else 16
     times = {}
     for layers in (1, 2):
         cfg = O.ModelCfg(**{**mc, "L": layers})

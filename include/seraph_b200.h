@@ -195,6 +195,27 @@ int seraph_b200_timing_read(cuda_train_context_t* ctx, double* out);
 /* Logits [T, vocab] of the last step or evaluation, copied to host memory. */
 int seraph_b200_download_logits(cuda_train_context_t* ctx, float* out, int T);
 
+/* RMSNorm backward that never allocates.  No counterpart in the reference.
+ * For hosts that cannot call the CUDA allocator when they need this op (a stream
+ * capture open elsewhere in the process, a framework or real-time loop that bans
+ * cudaMalloc after start-up, an embedder that owns all device memory): the
+ * partial sums of the scale gradient go to a fixed array inside the library
+ * image (296 x 8192 floats, 9.7 MB, held by every GPU that loads the library
+ * until the process ends) instead of grow-on-demand scratch.
+ *   - all pointers are device pointers; grad_scale is accumulated into, grad_input
+ *     is written, exactly as cuda_train_rmsnorm_backward_batch does;
+ *   - cols must be <= 8192: larger rows return 7 (size beyond capacity) and print why;
+ *   - `stream` is a cudaStream_t (NULL = default stream); work is only enqueued;
+ *   - the first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress) and the SM count, so make that first call with the
+ *     device current and before any stream capture begins;
+ *   - all calls on a device share the one array: calls that may overlap on the GPU
+ *     (different streams without ordering) race on it and give wrong grad_scale;
+ *     nothing has to be cleared between calls, each call overwrites what it reads.
+ * Returns 0, or 1 bad argument / 2 CUDA error / 7 size. */
+int seraph_b200_rmsnorm_backward_static(const float* input, const float* scale, const float* grad_output,
+                                        float* grad_input, float* grad_scale, int rows, int cols, float eps, void* stream);
+
 /* Data parallel over NCCL: rank 0 makes the 128-byte id, every rank calls init
  * with it before its first step; steps then all-reduce gradient buckets while
  * backward still runs and AdamW applies the mean.  wait() is a host-side wait

@@ -91,6 +91,7 @@ def load():
         "seraph_b200_timing_enable": (i, [vp, i]), "seraph_b200_timing_classes": (i, []),
         "seraph_b200_timing_class_name": (C.c_char_p, [i]), "seraph_b200_timing_read": (i, [vp, vp]),
         "seraph_b200_state_create_lean": (vp, [i] * 7 + [f, f, i]),
+        "seraph_b200_rmsnorm_backward_static": (i, [vp, vp, vp, vp, vp, i, i, f, vp]),
         "seraph_dp_get_unique_id": (i, [vp]), "seraph_dp_init": (i, [vp, i, i, vp]), "seraph_dp_finalize": (None, [vp]),
         "seraph_dp_wait": (i, [vp, i]), "seraph_dp_world": (i, [vp]),
         "seraph_b200_state_create": (vp, [i] * 7 + [f, f, i]), "seraph_b200_state_free": (None, [vp]),

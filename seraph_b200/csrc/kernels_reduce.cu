@@ -7,6 +7,7 @@
 // embedding_backward :2175 (atomicAdd, blockDim = hidden_size), adamw :2187.
 #include <cuda_runtime.h>
 #include <math.h>
+#include <stdio.h>
 #include <stdint.h>
 #include "sb_internal.h"
 
@@ -498,3 +499,79 @@ void sb_adamw(sb_ctx_t* c, float* w, const float* g, float* m, float* v, size_t 
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// RMSNorm backward for callers that must not allocate.
+//
+// Some hosts of this library may not touch the CUDA allocator at the moment
+// they need a backward op: code running while a stream capture is open on
+// another thread, real-time loops and allocator-owning frameworks that forbid
+// cudaMalloc after start-up, and embedders that hand out every byte of device
+// memory themselves.  For them the two-stage reduction of dscale keeps its
+// per-CTA partial sums in a fixed array that lives in the library image
+// instead of in grow-on-demand scratch.
+//
+// The array belongs to the device that loaded the library and stays resident
+// until the process exits: SB_NOALLOC_MAX_CTAS * SB_NOALLOC_MAX_COLS floats
+// (296 * 8192 * 4 bytes = 9.7 MB) on every GPU that uses the library.
+// ---------------------------------------------------------------------------
+#define SB_NOALLOC_MAX_COLS 8192
+#define SB_NOALLOC_MAX_CTAS 296          // two CTAs per SM on a 148-SM part
+#define SB_NOALLOC_MAX_DEVICES 64
+
+static __device__ __align__(256) float g_rn_static_partials[(size_t)SB_NOALLOC_MAX_CTAS * SB_NOALLOC_MAX_COLS];
+
+// Device address of the array, looked up once per device.  In host code the
+// symbol's name is only a handle; the kernels need what cudaGetSymbolAddress
+// returns for the device that is current.
+static float* g_rn_static_ptr[SB_NOALLOC_MAX_DEVICES];
+static int g_rn_static_sms[SB_NOALLOC_MAX_DEVICES];
+
+extern "C" int seraph_b200_rmsnorm_backward_static(const float* input, const float* scale, const float* grad_output,
+                                                   float* grad_input, float* grad_scale, int rows, int cols, float eps,
+                                                   void* stream) {
+    if (!input || !scale || !grad_output || !grad_input || !grad_scale || rows < 0 || cols <= 0) {
+        fprintf(stderr, "seraph_b200_rmsnorm_backward_static: NULL pointer or bad shape (rows %d, cols %d)\n", rows, cols);
+        return SB_ERR_ARG;
+    }
+    if (cols > SB_NOALLOC_MAX_COLS) {
+        fprintf(stderr, "seraph_b200_rmsnorm_backward_static: cols %d exceeds the fixed scratch (at most %d columns); "
+                        "use cuda_train_rmsnorm_backward_batch, which may allocate\n", cols, SB_NOALLOC_MAX_COLS);
+        return SB_ERR_SIZE;
+    }
+    if (rows == 0) return SB_OK;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= SB_NOALLOC_MAX_DEVICES) {
+        fprintf(stderr, "seraph_b200_rmsnorm_backward_static: no usable current device\n");
+        return SB_ERR_CUDA;
+    }
+    if (!g_rn_static_ptr[dev]) {
+        // first call on this device: resolve the array's device address and the SM count
+        float* p = NULL;
+        cudaError_t e = cudaGetSymbolAddress((void**)&p, g_rn_static_partials);
+        if (e != cudaSuccess || !p) {
+            fprintf(stderr, "seraph_b200_rmsnorm_backward_static: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
+            return SB_ERR_CUDA;
+        }
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+        g_rn_static_sms[dev] = sms;
+        g_rn_static_ptr[dev] = p;
+    }
+    int grid = 2 * g_rn_static_sms[dev];
+    if (grid > SB_NOALLOC_MAX_CTAS) grid = SB_NOALLOC_MAX_CTAS;
+    if (grid > rows) grid = rows;
+    float* partial = g_rn_static_ptr[dev];
+    int vec = (cols % 4 == 0) && aligned16(input) && aligned16(scale) && aligned16(grad_output) && aligned16(grad_input);
+    cudaStream_t s = (cudaStream_t)stream;
+    // every CTA overwrites its whole row of partials before the column sum reads it,
+    // so nothing left over from an earlier call is ever read and no clearing is needed
+    rmsnorm_bwd_kernel<<<grid, RB_THREADS, 0, s>>>(input, scale, grad_output, nullptr, grad_input, partial, rows, cols, eps, vec);
+    colsum_partials_kernel<<<(cols + 255) / 256, 256, 0, s>>>(partial, grad_scale, grid, cols);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        fprintf(stderr, "seraph_b200_rmsnorm_backward_static: launch failed: %s\n", cudaGetErrorString(e));
+        return SB_ERR_CUDA;
+    }
+    return SB_OK;
+}

@@ -28,6 +28,7 @@
 #define TC_BM 128
 #define TC_EPI_WARPS 8                     // two per TMEM lane quarter, 128 columns each
 #define TC_THREADS (64 + 32 * TC_EPI_WARPS)  // TMA warp + MMA warp + epilogue warps
+#define TC_GROUP_M 16                      // row tiles per rasterisation group
 #define TC_CHUNK_K 128                     // floats of k accumulated in tensor memory before the FP32 round-to-nearest add
 #define TC_SPIN_CYCLES 4000000000ll      // ~2 s at 2 GHz: far beyond any legitimate wait
 
@@ -121,7 +122,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
+    // Tile order: groups of TC_GROUP_M row tiles; inside a group the row tile runs fastest.  CTAs that are
+    // resident together then share a few A row tiles and a few B row tiles, so both operands are re-read
+    // from L2 instead of HBM even when one of them (the embedding table) is far larger than L2.
+    const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + BN - 1) / BN;
+    int m_tile, n_tile;
+    {
+        const int per_group = TC_GROUP_M * tiles_n;
+        const int gid = blockIdx.x / per_group, in_g = blockIdx.x % per_group;
+        const int first_m = gid * TC_GROUP_M;
+        const int gsize = min(TC_GROUP_M, tiles_m - first_m);
+        m_tile = first_m + in_g % gsize;
+        n_tile = in_g / gsize;
+    }
+    const int m0 = m_tile * TC_BM, n0 = n_tile * BN;
     const int num_kb = (K + BK - 1) / BK;
     const int num_chunks = (num_kb + KB_PER_CHUNK - 1) / KB_PER_CHUNK;
 
@@ -225,25 +239,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
         }
-        if (!ok) { if (lane == 0) atomicExch(status, SB_ERR_TIMEOUT); }
-        else if (row < M) {
+        if (!ok && lane == 0) atomicExch(status, SB_ERR_TIMEOUT);
+        // The last chunk has arrived, so every MMA has finished reading the operand stages:
+        // their shared memory is free and now stages the 128 x BN tile, so that the global
+        // stores below are whole contiguous rows instead of one 128-byte piece per thread.
+        constexpr int SLD = BN + 4;                   // padded row pitch (floats): conflict-free 16-byte accesses
+        float* stage = (float*)smem;
+        {
+            float* srow = stage + (size_t)(q * 32 + lane) * SLD + col0;
 #pragma unroll
-            for (int g = 0; g < COLS_PER_WARP / 32; g++) {
-                const int c = n0 + col0 + g * 32;
-                if (c < N) {
-                    float* crow = C + (size_t)row * N + c;
-                    const int ncol = min(32, N - c);
-                    if (ncol == 32 && ((((uintptr_t)crow) & 15) == 0)) {
+            for (int j = 0; j < COLS_PER_WARP; j += 4)
+                *(float4*)(srow + j) = make_float4(accr[j], accr[j + 1], accr[j + 2], accr[j + 3]);
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * TC_EPI_WARPS) : "memory");      // epilogue warps only
+        (void)row;
+        if (ok) {
+            const bool vec = ((N & 3) == 0);
+            for (int r = ew; r < TC_BM; r += TC_EPI_WARPS) {
+                const int grow = m0 + r;
+                if (grow >= M) break;
+                const float* srow = stage + (size_t)r * SLD;
+                float* crow = C + (size_t)grow * N + n0;
+                if (vec) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 v = make_float4(accr[g * 32 + j], accr[g * 32 + j + 1], accr[g * 32 + j + 2], accr[g * 32 + j + 3]);
-                            if (acc) { float4 o = *(float4*)(crow + j); v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
-                            *(float4*)(crow + j) = v;
+                    for (int h = 0; h < BN / 128; h++) {
+                        const int col = (h * 32 + lane) * 4;
+                        if (n0 + col < N) {
+                            float4 v = *(const float4*)(srow + col);
+                            if (acc) { float4 o = *(const float4*)(crow + col); v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+                            *(float4*)(crow + col) = v;
                         }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++) if (j < ncol) crow[j] = acc ? crow[j] + accr[g * 32 + j] : accr[g * 32 + j];
                     }
+                } else {
+                    for (int col = lane; col < BN && n0 + col < N; col += 32)
+                        crow[col] = acc ? crow[col] + srow[col] : srow[col];
                 }
             }
         }
@@ -334,7 +363,7 @@ static bool launch_tc(sb_ctx_t* c, const float* Ah, const float* Al, size_t pitc
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
         attr_set = true;
     }
-    dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
+    dim3 grid((unsigned)(((N + BN - 1) / BN) * ((M + TC_BM - 1) / TC_BM)));
     kern<<<grid, TC_THREADS, smem, (cudaStream_t)c->pub.stream>>>(mAh, mAl, mBh, mBl, C, M, N, K, acc, c->d_status);
     c->launches++;
     return cudaGetLastError() == cudaSuccess;

@@ -1,394 +1,27 @@
-// gemm_tc.cu - tensor-core GEMM for sm_100a: TMA -> swizzled shared memory -> tcgen05.mma
-// (kind::tf32) with the FP32 accumulator in tensor memory, read back with tcgen05.ld.
-//
-//   C[M,N] (+)= A^[M,K] * B^[N,K]^T          both operands K-major (rows of K contiguous floats)
+// gemm_tc.cu - the reference's matmul entry points on the tcgen05 kernel of gemm_tc.cuh.
 //
 // The reference's three layouts (src/cuda_train_context.cu:2645-2709: NN, TN, NT, optional
-// accumulate) are brought to this one form by an operand-preparation pass that also writes
-// what the FP32-accurate mode needs:
-//   FP32X3 mode: x = hi + lo with hi = the 19 leading bits a TF32 tensor core reads from an
-//                FP32 word and lo = x - hi (exact in FP32).  The kernel issues
-//                hi*hi + lo*hi + hi*lo into one FP32 accumulator: three tensor-core passes
-//                give products good to ~2^-21, i.e. FP32-level results.
-//   TF32 mode:   one pass on the raw FP32 words.
-// An operand that already is K-major is used in place (only its lo copy is written); an
-// operand that is not gets a transposed hi copy and a transposed lo copy.
-//
-// Kernel shape: CTA tile 128 x 256, k-block BK floats (one swizzle span of BK*4 bytes), a ring
-// of STAGES shared-memory stages.  Warp 0 = TMA producer, warp 1 = MMA issuer (one elected
-// lane each; warp 1 also owns the TMEM allocation), warps 2-9 = epilogue: two warps per TMEM
-// lane quarter, 128 columns each, accumulators in registers.  All mbarrier waits are bounded: a wait that runs out sets the status word,
-// the CTA drains and frees its TMEM, and the host reports SB_ERR_TIMEOUT.
-#include <cuda.h>
-#include <cuda_runtime.h>
-#include <stdint.h>
+// accumulate) are brought to the kernel's one form, C (+)= A^[M,K] B^[N,K]^T with both
+// operands K-major, by an operand-preparation pass that also writes what the FP32-accurate
+// mode needs: an operand that already is K-major is used in place (only its lo part is
+// written, 8 bytes per element); an operand that is not gets a transposed hi copy and a
+// transposed lo copy (12 bytes per element).
 #include <stdio.h>
-#include "sb_internal.h"
+#include "gemm_tc.cuh"
 
-#define TC_BM 128
-#define TC_EPI_WARPS 8                     // two per TMEM lane quarter, 128 columns each
-#define TC_THREADS (64 + 32 * TC_EPI_WARPS)  // TMA warp + MMA warp + epilogue warps
-#define TC_GROUP_M 16                      // row tiles per rasterisation group
-#define TC_CHUNK_K 128                     // floats of k accumulated in tensor memory before the FP32 round-to-nearest add
-#define TC_SPIN_CYCLES 4000000000ll      // ~2 s at 2 GHz: far beyond any legitimate wait
-
-// --------------------------------------------------------------------------- PTX helpers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred = 0;
-    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
-    return pred != 0;
-}
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// bounded wait; returns false when the deadline passed
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t addr = smem_u32(bar), done = 0;
-    long long t0 = clock64();
-    for (;;) {
-        asm volatile("{\n\t.reg .pred P;\n\tmbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\tselp.u32 %0, 1, 0, P;\n\t}"
-                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-        if (clock64() - t0 > TC_SPIN_CYCLES) return false;
-    }
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// shared-memory matrix descriptor, K-major operand, rows of SWZ bytes (64 or 128), 8-row groups contiguous
-template <int SWZ>
-__device__ __forceinline__ uint64_t make_kmajor_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3fff);                 // start address
-    d |= (uint64_t)1 << 16;                                      // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(((8 * SWZ) >> 4) & 0x3fff) << 32;            // stride byte offset: one 8-row group
-    d |= (uint64_t)1 << 46;                                      // descriptor version for sm_100
-    d |= (uint64_t)(SWZ == 128 ? 2 : 4) << 61;                   // swizzle mode: 128B = 2, 64B = 4
-    return d;
-}
-
-// --------------------------------------------------------------------------- the GEMM kernel
-// The tensor core adds into its FP32 accumulator with truncation, so a long chain of
-// accumulating MMAs drifts by about one ulp per instruction (measured: 3e-5 relative after
-// K = 4096).  The k range is therefore cut into chunks of TC_CHUNK_KB k-blocks: each chunk is
-// accumulated in one of two TMEM buffers, and the epilogue warps add the finished chunk into
-// register accumulators with ordinary round-to-nearest FP32 adds while the next chunk is
-// already being multiplied into the other buffer.
-template <int BN, int BK, int NTERMS, int STAGES>
-__global__ void __launch_bounds__(TC_THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
-               const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
-               float* __restrict__ C, int M, int N, int K, int acc, int* status) {
-    constexpr int SWZ = BK * 4;
-    constexpr int A_BYTES = TC_BM * BK * 4, B_BYTES = BN * BK * 4;
-    constexpr int STAGE_BYTES = (NTERMS == 3 ? 2 : 1) * (A_BYTES + B_BYTES);
-    constexpr uint32_t TMEM_COLS = 2 * BN;                       // two accumulator buffers; 256 or 512 columns
-    constexpr int KB_PER_CHUNK = TC_CHUNK_K / BK;
-    constexpr int COLS_PER_WARP = BN / (TC_EPI_WARPS / 4);       // 128
-    static_assert(COLS_PER_WARP == 128, "each epilogue thread keeps 128 accumulators");
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
-    uint64_t* empty = full + STAGES;
-    uint64_t* acc_full = empty + STAGES;          // [2] MMA -> epilogue
-    uint64_t* acc_empty = acc_full + 2;           // [2] epilogue -> MMA
-    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Tile order: groups of TC_GROUP_M row tiles; inside a group the row tile runs fastest.  CTAs that are
-    // resident together then share a few A row tiles and a few B row tiles, so both operands are re-read
-    // from L2 instead of HBM even when one of them (the embedding table) is far larger than L2.
-    const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + BN - 1) / BN;
-    int m_tile, n_tile;
-    {
-        const int per_group = TC_GROUP_M * tiles_n;
-        const int gid = blockIdx.x / per_group, in_g = blockIdx.x % per_group;
-        const int first_m = gid * TC_GROUP_M;
-        const int gsize = min(TC_GROUP_M, tiles_m - first_m);
-        m_tile = first_m + in_g % gsize;
-        n_tile = in_g / gsize;
-    }
-    const int m0 = m_tile * TC_BM, n0 = n_tile * BN;
-    const int num_kb = (K + BK - 1) / BK;
-    const int num_chunks = (num_kb + KB_PER_CHUNK - 1) / KB_PER_CHUNK;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], TC_EPI_WARPS); }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-    bool ok = true;
-
-    if (warp == 0) {
-        // ---------------- TMA producer ----------------
-        if (elect_one()) {
-            for (int kb = 0; kb < num_kb && ok; kb++) {
-                int s = kb % STAGES;
-                uint32_t ph = (kb / STAGES) & 1;
-                ok = mbar_wait(&empty[s], ph ^ 1);
-                if (!ok) break;
-                uint8_t* st = smem + s * STAGE_BYTES;
-                mbar_expect_tx(&full[s], STAGE_BYTES);
-                tma_load_2d(st, &tmAh, &full[s], kb * BK, m0);
-                tma_load_2d(st + A_BYTES, &tmBh, &full[s], kb * BK, n0);
-                if (NTERMS == 3) {
-                    tma_load_2d(st + A_BYTES + B_BYTES, &tmAl, &full[s], kb * BK, m0);
-                    tma_load_2d(st + 2 * A_BYTES + B_BYTES, &tmBl, &full[s], kb * BK, n0);
-                }
-            }
-            if (!ok) atomicExch(status, SB_ERR_TIMEOUT);
-        }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (elect_one()) {
-            // instruction descriptor: D = F32, A = B = TF32, both K-major, N and M of the tile
-            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-            int kb = 0;
-            for (int ch = 0; ch < num_chunks && ok; ch++) {
-                const int buf = ch & 1;
-                ok = mbar_wait(&acc_empty[buf], ((ch >> 1) & 1) ^ 1);      // epilogue has drained this buffer
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
-                const int kb_end = min(kb + KB_PER_CHUNK, num_kb);
-                bool first = true;
-                for (; kb < kb_end && ok; kb++) {
-                    int s = kb % STAGES;
-                    uint32_t ph = (kb / STAGES) & 1;
-                    ok = mbar_wait(&full[s], ph);
-                    if (!ok) break;
-                    tc_fence_after();
-                    uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-                    uint64_t ah = make_kmajor_desc<SWZ>(sa), bh = make_kmajor_desc<SWZ>(sa + A_BYTES);
-                    uint64_t al = make_kmajor_desc<SWZ>(sa + A_BYTES + B_BYTES), bl = make_kmajor_desc<SWZ>(sa + 2 * A_BYTES + B_BYTES);
-#pragma unroll
-                    for (int k = 0; k < BK / 8; k++) {
-                        uint64_t adv = (uint64_t)(k * 2);             // 8 floats = 32 bytes, in 16-byte units
-                        tc_mma_tf32(tmem_d, ah + adv, bh + adv, idesc, first ? 0u : 1u);
-                        first = false;
-                        if (NTERMS == 3) {
-                            tc_mma_tf32(tmem_d, al + adv, bh + adv, idesc, 1);
-                            tc_mma_tf32(tmem_d, ah + adv, bl + adv, idesc, 1);
-                        }
-                    }
-                    tc_commit(&empty[s]);      // stage reusable once these MMAs have read it
-                }
-                tc_commit(&acc_full[buf]);     // chunk complete (also releases the epilogue on a time-out)
-            }
-            if (!ok) atomicExch(status, SB_ERR_TIMEOUT);
-        }
-    } else {
-        // ---------------- epilogue: TMEM chunks -> register accumulators -> global ----------------
-        const int ew = warp - 2;                      // 0..7
-        const int q = warp & 3;                       // TMEM lane quarter this warp may read
-        const int chalf = ew >> 2;                    // which 128 columns of the tile
-        const int row = m0 + q * 32 + lane;
-        const int col0 = chalf * COLS_PER_WARP;
-        float accr[COLS_PER_WARP];
-#pragma unroll
-        for (int j = 0; j < COLS_PER_WARP; j++) accr[j] = 0.f;
-        for (int ch = 0; ch < num_chunks && ok; ch++) {
-            const int buf = ch & 1;
-            ok = mbar_wait(&acc_full[buf], (ch >> 1) & 1);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + col0);
-#pragma unroll
-            for (int g = 0; g < COLS_PER_WARP / 32; g++) {
-                uint32_t r[32];
-                tc_ld32(taddr + (uint32_t)(g * 32), r);
-#pragma unroll
-                for (int j = 0; j < 32; j++) accr[g * 32 + j] += __uint_as_float(r[j]);
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
-        }
-        if (!ok && lane == 0) atomicExch(status, SB_ERR_TIMEOUT);
-        // The last chunk has arrived, so every MMA has finished reading the operand stages:
-        // their shared memory is free and now stages the 128 x BN tile, so that the global
-        // stores below are whole contiguous rows instead of one 128-byte piece per thread.
-        constexpr int SLD = BN + 4;                   // padded row pitch (floats): conflict-free 16-byte accesses
-        float* stage = (float*)smem;
-        {
-            float* srow = stage + (size_t)(q * 32 + lane) * SLD + col0;
-#pragma unroll
-            for (int j = 0; j < COLS_PER_WARP; j += 4)
-                *(float4*)(srow + j) = make_float4(accr[j], accr[j + 1], accr[j + 2], accr[j + 3]);
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * TC_EPI_WARPS) : "memory");      // epilogue warps only
-        (void)row;
-        if (ok) {
-            const bool vec = ((N & 3) == 0);
-            for (int r = ew; r < TC_BM; r += TC_EPI_WARPS) {
-                const int grow = m0 + r;
-                if (grow >= M) break;
-                const float* srow = stage + (size_t)r * SLD;
-                float* crow = C + (size_t)grow * N + n0;
-                if (vec) {
-#pragma unroll
-                    for (int h = 0; h < BN / 128; h++) {
-                        const int col = (h * 32 + lane) * 4;
-                        if (n0 + col < N) {
-                            float4 v = *(const float4*)(srow + col);
-                            if (acc) { float4 o = *(const float4*)(crow + col); v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
-                            *(float4*)(crow + col) = v;
-                        }
-                    }
-                } else {
-                    for (int col = lane; col < BN && n0 + col < N; col += 32)
-                        crow[col] = acc ? crow[col] + srow[col] : srow[col];
-                }
-            }
-        }
-        tc_fence_before();
-    }
-    __syncthreads();
-    if (warp == 1) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
-    }
-}
-
-// K == 0: the product is empty; C = 0 unless accumulating (handled on the host)
-
-// --------------------------------------------------------------------------- operand preparation
-__device__ __forceinline__ float tf32_lo(float x) {
-    float hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
-    return x - hi;
-}
-// lo[i] = x[i] - tf32_trunc(x[i]);  8 bytes per element
-__global__ void __launch_bounds__(256) split_lo_kernel(const float* __restrict__ x, float* __restrict__ lo, size_t n4) {
-    size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = tid; i < n4; i += nth) {
-        float4 v = ((const float4*)x)[i];
-        ((float4*)lo)[i] = make_float4(tf32_lo(v.x), tf32_lo(v.y), tf32_lo(v.z), tf32_lo(v.w));
-    }
-}
-// in [R, C] row-major -> hi [C, Rp] = in^T, lo [C, Rp] = lo(in^T); Rp = row pitch of the outputs (R rounded up to 4)
-__global__ void __launch_bounds__(256) transpose_split_kernel(const float* __restrict__ in, float* __restrict__ hi, float* __restrict__ lo,
-                                                              int R, int C, int Rp, int want_lo) {
-    __shared__ float tile[32][33];
-    int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
-    int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;      // 32 x 8
-    for (int i = ty; i < 32; i += 8) {
-        int r = r0 + i, c = c0 + tx;
-        tile[i][tx] = (r < R && c < C) ? in[(size_t)r * C + c] : 0.f;
-    }
-    __syncthreads();
-    for (int i = ty; i < 32; i += 8) {
-        int c = c0 + i, r = r0 + tx;
-        if (c < C && r < Rp) {
-            float v = tile[tx][i];
-            hi[(size_t)c * Rp + r] = v;
-            if (want_lo) lo[(size_t)c * Rp + r] = tf32_lo(v);
-        }
-    }
-}
-
-// --------------------------------------------------------------------------- host side
-typedef CUresult (*encode_fn_t)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static encode_fn_t g_encode = nullptr;
-
-static bool load_encode() {
-    if (g_encode) return true;
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) return false;
-    g_encode = (encode_fn_t)fn;
-    return true;
-}
-
-// 2D FP32 tensor [rows, K] with row pitch `pitch` floats; box = BK x box_rows; rows/cols beyond the extents read as zero
-static bool make_map(CUtensorMap* m, const float* base, int rows, int K, size_t pitch, int BK, int box_rows) {
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)pitch * sizeof(float)};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          BK * 4 == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
-}
-
-template <int BN, int BK, int NTERMS, int STAGES>
-static bool launch_tc(sb_ctx_t* c, const float* Ah, const float* Al, size_t pitchA, const float* Bh, const float* Bl, size_t pitchB,
-                      float* C, int M, int N, int K, int acc) {
-    CUtensorMap mAh, mAl, mBh, mBl;
-    if (!make_map(&mAh, Ah, M, K, pitchA, BK, TC_BM) || !make_map(&mBh, Bh, N, K, pitchB, BK, BN)) return false;
-    if (NTERMS == 3) { if (!make_map(&mAl, Al, M, K, pitchA, BK, TC_BM) || !make_map(&mBl, Bl, N, K, pitchB, BK, BN)) return false; }
-    else { mAl = mAh; mBl = mBh; }
-    constexpr int STAGE_BYTES = (NTERMS == 3 ? 2 : 1) * (TC_BM + BN) * BK * 4;
-    size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
-    auto kern = gemm_tc_kernel<BN, BK, NTERMS, STAGES>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
-        attr_set = true;
-    }
-    dim3 grid((unsigned)(((N + BN - 1) / BN) * ((M + TC_BM - 1) / TC_BM)));
-    kern<<<grid, TC_THREADS, smem, (cudaStream_t)c->pub.stream>>>(mAh, mAl, mBh, mBl, C, M, N, K, acc, c->d_status);
-    c->launches++;
-    return cudaGetLastError() == cudaSuccess;
-}
-
-static inline bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
-static inline int ew_blocks(sb_ctx_t* c, size_t items) {
-    size_t b = (items + 255) / 256, cap = (size_t)(c->pub.gpu_sm_count > 0 ? c->pub.gpu_sm_count : 148) * 8;
-    return (int)(b > cap ? cap : (b ? b : 1));
-}
-
-// Bring one operand to K-major [rows, K]: returns hi/lo pointers and the row pitch.
-// `kmajor` says the caller's array already is [rows, K] row-major.
-static bool prep_operand(sb_ctx_t* c, const float* src, int rows, int K, bool kmajor, bool want_lo, int slot,
-                         const float** hi, const float** lo, size_t* pitch) {
+// Bring one operand to K-major [rows, K].  `kmajor`: the caller's array already is [rows, K] row-major.
+static bool prep_operand(sb_ctx_t* c, const float* src, int rows, int K, bool kmajor, bool want_lo, int slot, TcOperand* op) {
     cudaStream_t s = (cudaStream_t)c->pub.stream;
+    op->rows = rows; op->c2_dim = 1; op->c2_stride = 0; op->c2_base = 0; op->c2_step = 0; op->lo = nullptr;
     if (kmajor) {
-        *hi = src; *pitch = (size_t)K; *lo = nullptr;
+        op->hi = src; op->pitch = K;
         if (want_lo) {
             size_t n = (size_t)rows * K;
             float* l = (float*)sb_gemm_stage(c, slot, n * sizeof(float));
             if (!l) return false;
-            split_lo_kernel<<<ew_blocks(c, n / 4), 256, 0, s>>>(src, l, n / 4);     // K % 4 == 0 and 16-byte aligned: checked by the caller
+            split_lo_kernel<<<tc_ew_blocks(c, n / 4), 256, 0, s>>>(src, l, n / 4);     // K % 4 == 0, 16-byte aligned: checked by the caller
             c->launches++;
-            *lo = l;
+            op->lo = l;
         }
         return true;
     }
@@ -401,32 +34,29 @@ static bool prep_operand(sb_ctx_t* c, const float* src, int rows, int K, bool km
     dim3 grid((rows + 31) / 32, (Kp + 31) / 32);
     transpose_split_kernel<<<grid, 256, 0, s>>>(src, h, l, K, rows, Kp, want_lo ? 1 : 0);
     c->launches++;
-    *hi = h; *lo = l; *pitch = (size_t)Kp;
+    op->hi = h; op->lo = l; op->pitch = Kp;
     return true;
 }
 
 extern "C" int sb_gemm_tc(sb_ctx_t* c, const float* A, const float* B, float* C, int M, int N, int K, int tA, int tB, int acc, int mode) {
     if (K <= 0 || M < 32 || N < 32) return 1;
     if ((double)M * N * K < (double)(1 << 21)) return 1;                 // too small to pay for the pipeline
-    if (!aligned16(A) || !aligned16(B) || !aligned16(C)) return 1;
-    if (!load_encode()) { sb_set_status(c, SB_ERR_CUDA); return 1; }
+    if (!tc_aligned16(A) || !tc_aligned16(B) || !tc_aligned16(C)) return 1;
+    if (!tc_load_encode()) { sb_set_status(c, SB_ERR_CUDA); return 1; }
     if (tA && tB) { tA = 0; tB = 0; }                                     // as the reference's dispatch does
-    // canonical operands: A^ = [M,K] rows, B^ = [N,K] rows
     bool a_kmajor = !tA;       // tA: A is [K,M]
     bool b_kmajor = tB != 0;   // !tB: B is [K,N]
     if ((a_kmajor || b_kmajor) && (K & 3)) return 1;                     // in-place K-major rows need a 16-byte pitch
-    bool x3 = (mode == SB_GEMM_FP32X3);
-    const float *Ah, *Al, *Bh, *Bl; size_t pA, pB;
+    const bool x3 = (mode == SB_GEMM_FP32X3);
+    TcProblem p;
     int tp = sb_tick_begin(c, SB_CLS_GEMM_PREP);
-    double prep_bytes = 0;
-    if (!prep_operand(c, A, M, K, a_kmajor, x3, 0, &Ah, &Al, &pA)) return 1;
-    if (!prep_operand(c, B, N, K, b_kmajor, x3, 1, &Bh, &Bl, &pB)) return 1;
-    prep_bytes += (double)M * K * (a_kmajor ? (x3 ? 8 : 0) : (x3 ? 12 : 8)) + (double)N * K * (b_kmajor ? (x3 ? 8 : 0) : (x3 ? 12 : 8));
+    if (!prep_operand(c, A, M, K, a_kmajor, x3, 0, &p.A)) return 1;
+    if (!prep_operand(c, B, N, K, b_kmajor, x3, 1, &p.B)) return 1;
+    double prep_bytes = (double)M * K * (a_kmajor ? (x3 ? 8 : 0) : (x3 ? 12 : 8)) + (double)N * K * (b_kmajor ? (x3 ? 8 : 0) : (x3 ? 12 : 8));
     sb_tick_end(c, tp, 0.0, prep_bytes);
+    p.C = C; p.ldc = N; p.c_batch_stride = 0; p.M = M; p.N = N; p.K = K; p.acc = acc; p.nbatch = 1; p.causal = TC_CAUSAL_NONE;
     int tg = sb_tick_begin(c, SB_CLS_GEMM);
-    bool ok;
-    if (x3) ok = launch_tc<256, 16, 3, 4>(c, Ah, Al, pA, Bh, Bl, pB, C, M, N, K, acc);
-    else    ok = launch_tc<256, 32, 1, 4>(c, Ah, Al, pA, Bh, Bl, pB, C, M, N, K, acc);
+    bool ok = tc_launch(c, p, x3 ? 3 : 1);
     sb_tick_end(c, tg, 2.0 * M * N * K, 4.0 * ((double)M * K + (double)N * K + (double)M * N * (acc ? 2 : 1)));
     if (!ok) { sb_set_status(c, SB_ERR_CUDA); return 1; }
     return 0;

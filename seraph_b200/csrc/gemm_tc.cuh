@@ -1,0 +1,421 @@
+// gemm_tc.cuh - the tcgen05 GEMM kernel and its launcher, shared by the plain GEMM
+// (gemm_tc.cu) and the attention path (attention_tc.cu).
+//
+//   C_b[M,N] (+)= A_b[M,K] * B_b[N,K]^T      for b in [0, nbatch)
+//
+// Both operands are K-major (rows of K contiguous floats, any 16-byte-multiple pitch) and are
+// fetched by TMA through 3-D tensor maps {K, rows, batch-slot}; the slot of batch b is
+// c2_base + b*c2_step, so one launch can walk over attention heads (and share one K/V head
+// between the query heads of a GQA group).
+//
+// Arithmetic: tcgen05.mma kind::tf32, accumulator in tensor memory.
+//   NTERMS = 3: FP32-accurate.  x = hi + lo, hi = the 19 leading bits the tensor core reads
+//               from an FP32 word, lo = x - hi; the kernel issues hi*hi + lo*hi + hi*lo.
+//   NTERMS = 1: single-pass TF32.
+// The tensor core adds into its FP32 accumulator with truncation, so a long chain of
+// accumulating MMAs drifts by about one ulp per instruction (measured: 3e-5 relative after
+// K = 4096).  The k range is therefore cut into chunks of TC_CHUNK_K: each chunk is accumulated
+// in one of two TMEM buffers and the epilogue warps add the finished chunk into register
+// accumulators with round-to-nearest FP32 adds while the next chunk is already being
+// multiplied into the other buffer.
+//
+// CTA: tile 128 x BN, ring of STAGES shared-memory stages of BK floats of k (one swizzle span).
+// Warp 0 = TMA producer, warp 1 = MMA issuer (one elected lane each; warp 1 owns the TMEM
+// allocation), warps 2-9 = epilogue: two warps per TMEM lane quarter, BN/2 columns each.
+// The finished tile is staged in the (by then idle) operand stages so that global stores are
+// whole rows.  Every mbarrier wait is bounded: a wait that runs out sets the status word, the
+// CTA drains, frees its TMEM and returns, and the host reports SB_ERR_TIMEOUT.
+//
+// Causal modes (attention; rows/columns are positions inside one sequence):
+//   TC_CAUSAL_NONE
+//   TC_CAUSAL_SKIP_UPPER   M = queries, N = keys   : tiles with every key after every query are not computed
+//   TC_CAUSAL_SKIP_LOWER   M = keys,    N = queries: tiles with every query before every key are not computed
+//   TC_CAUSAL_K_UPTO_M     M = queries, K = keys   : k runs over [0, m_tile_end)
+//   TC_CAUSAL_K_FROM_M     M = keys,    K = queries: k runs over [m_tile_start, K)
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "sb_internal.h"
+
+#define TC_BM 128
+#define TC_EPI_WARPS 8
+#define TC_THREADS (64 + 32 * TC_EPI_WARPS)
+#define TC_GROUP_M 16
+#define TC_CHUNK_K 128
+#define TC_SPIN_CYCLES 4000000000ll      // ~2 s at 2 GHz: far beyond any legitimate wait
+
+enum { TC_CAUSAL_NONE = 0, TC_CAUSAL_SKIP_UPPER, TC_CAUSAL_SKIP_LOWER, TC_CAUSAL_K_UPTO_M, TC_CAUSAL_K_FROM_M };
+
+struct TcOperand {
+    const float* hi; const float* lo;   // lo may be NULL when nterms == 1
+    int rows;                            // M or N
+    long pitch;                          // floats between rows
+    int c2_dim; long c2_stride;          // third tensor-map dimension (floats); c2_dim = 1 for a plain matrix
+    int c2_base, c2_step;                // slot of batch b = c2_base + b*c2_step
+};
+struct TcProblem {
+    TcOperand A, B;
+    float* C; long ldc; long c_batch_stride;
+    int M, N, K, acc, nbatch, causal;
+};
+
+// --------------------------------------------------------------------------- PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred = 0;
+    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// bounded wait; returns false when the deadline passed
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t addr = smem_u32(bar), done = 0;
+    long long t0 = clock64();
+    for (;;) {
+        asm volatile("{\n\t.reg .pred P;\n\tmbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\tselp.u32 %0, 1, 0, P;\n\t}"
+                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if (clock64() - t0 > TC_SPIN_CYCLES) return false;
+    }
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// shared-memory matrix descriptor, K-major operand, rows of SWZ bytes (64 or 128), 8-row groups contiguous
+template <int SWZ>
+__device__ __forceinline__ uint64_t make_kmajor_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3fff);                 // start address
+    d |= (uint64_t)1 << 16;                                      // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(((8 * SWZ) >> 4) & 0x3fff) << 32;            // stride byte offset: one 8-row group
+    d |= (uint64_t)1 << 46;                                      // descriptor version for sm_100
+    d |= (uint64_t)(SWZ == 128 ? 2 : 4) << 61;                   // swizzle mode: 128B = 2, 64B = 4
+    return d;
+}
+
+// --------------------------------------------------------------------------- the kernel
+template <int BN, int BK, int NTERMS, int STAGES>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
+               const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
+               float* __restrict__ Cbase, long ldc, long c_batch_stride, int M, int N, int K, int acc, int causal,
+               int a_c2_base, int a_c2_step, int b_c2_base, int b_c2_step, int swap_mask, int* status) {
+    constexpr int SWZ = BK * 4;
+    constexpr int A_BYTES = TC_BM * BK * 4, B_BYTES = BN * BK * 4;
+    constexpr int STAGE_BYTES = (NTERMS == 3 ? 2 : 1) * (A_BYTES + B_BYTES);
+    constexpr uint32_t TMEM_COLS = 2 * BN;                       // two accumulator buffers
+    constexpr int KB_PER_CHUNK = TC_CHUNK_K / BK;
+    constexpr int COLS_PER_WARP = BN / (TC_EPI_WARPS / 4);       // 128 or 64 register accumulators per epilogue thread
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;          // [2] MMA -> epilogue
+    uint64_t* acc_empty = acc_full + 2;           // [2] epilogue -> MMA
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int batch = blockIdx.y;
+    // Tile order: groups of TC_GROUP_M row tiles; inside a group the row tile runs fastest, so CTAs
+    // resident together share a few A row tiles and a few B row tiles and both operands are re-read
+    // from L2 even when one of them (the embedding table) is far larger than L2.
+    const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + BN - 1) / BN;
+    int m_tile, n_tile;
+    {
+        const int per_group = TC_GROUP_M * tiles_n;
+        const int gid = blockIdx.x / per_group, in_g = blockIdx.x % per_group;
+        const int first_m = gid * TC_GROUP_M;
+        const int gsize = min(TC_GROUP_M, tiles_m - first_m);
+        m_tile = first_m + in_g % gsize;
+        n_tile = in_g / gsize;
+    }
+    const int m0 = m_tile * TC_BM, n0 = n_tile * BN;
+    // causal structure: whole-tile skips and the k range (CTA-uniform)
+    if (causal == TC_CAUSAL_SKIP_UPPER && n0 > m0 + TC_BM - 1) return;
+    if (causal == TC_CAUSAL_SKIP_LOWER && n0 + BN - 1 < m0) return;
+    int kb_begin = 0, kb_end = (K + BK - 1) / BK;
+    if (causal == TC_CAUSAL_K_UPTO_M) kb_end = min(kb_end, (m0 + TC_BM + BK - 1) / BK);
+    if (causal == TC_CAUSAL_K_FROM_M) kb_begin = min(kb_end, m0 / BK);
+    const int num_kb = kb_end - kb_begin;
+    const int num_chunks = (num_kb + KB_PER_CHUNK - 1) / KB_PER_CHUNK;
+    float* C = Cbase + (size_t)batch * c_batch_stride;
+    const int a_c2 = a_c2_base + batch * a_c2_step, b_c2 = b_c2_base + batch * b_c2_step;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], TC_EPI_WARPS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (elect_one()) {
+            for (int it = 0; it < num_kb && ok; it++) {
+                const int s = it % STAGES, kb = kb_begin + it;
+                ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1);
+                if (!ok) break;
+                uint8_t* st = smem + s * STAGE_BYTES;
+                mbar_expect_tx(&full[s], STAGE_BYTES);
+                // a map whose slot stride is smaller than its row pitch is encoded as {k, slot, row}
+                const int a1 = (swap_mask & 1) ? a_c2 : m0, a2 = (swap_mask & 1) ? m0 : a_c2;
+                const int b1 = (swap_mask & 2) ? b_c2 : n0, b2 = (swap_mask & 2) ? n0 : b_c2;
+                tma_load_3d(st, &tmAh, &full[s], kb * BK, a1, a2);
+                tma_load_3d(st + A_BYTES, &tmBh, &full[s], kb * BK, b1, b2);
+                if (NTERMS == 3) {
+                    tma_load_3d(st + A_BYTES + B_BYTES, &tmAl, &full[s], kb * BK, a1, a2);
+                    tma_load_3d(st + 2 * A_BYTES + B_BYTES, &tmBl, &full[s], kb * BK, b1, b2);
+                }
+            }
+            if (!ok) atomicExch(status, SB_ERR_TIMEOUT);
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (elect_one()) {
+            // instruction descriptor: D = F32, A = B = TF32, both K-major, N and M of the tile
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            int it = 0;
+            for (int ch = 0; ch < num_chunks && ok; ch++) {
+                const int buf = ch & 1;
+                ok = mbar_wait(&acc_empty[buf], ((ch >> 1) & 1) ^ 1);      // epilogue has drained this buffer
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                const int it_end = min(it + KB_PER_CHUNK, num_kb);
+                bool first = true;
+                for (; it < it_end && ok; it++) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(&full[s], (it / STAGES) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+                    uint64_t ah = make_kmajor_desc<SWZ>(sa), bh = make_kmajor_desc<SWZ>(sa + A_BYTES);
+                    uint64_t al = make_kmajor_desc<SWZ>(sa + A_BYTES + B_BYTES), bl = make_kmajor_desc<SWZ>(sa + 2 * A_BYTES + B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 8; k++) {
+                        uint64_t adv = (uint64_t)(k * 2);             // 8 floats = 32 bytes, in 16-byte units
+                        tc_mma_tf32(tmem_d, ah + adv, bh + adv, idesc, first ? 0u : 1u);
+                        first = false;
+                        if (NTERMS == 3) {
+                            tc_mma_tf32(tmem_d, al + adv, bh + adv, idesc, 1);
+                            tc_mma_tf32(tmem_d, ah + adv, bl + adv, idesc, 1);
+                        }
+                    }
+                    tc_commit(&empty[s]);      // stage reusable once these MMAs have read it
+                }
+                tc_commit(&acc_full[buf]);     // chunk complete (also releases the epilogue on a time-out)
+            }
+            if (!ok) atomicExch(status, SB_ERR_TIMEOUT);
+        }
+    } else {
+        // ---------------- epilogue: TMEM chunks -> register accumulators -> shared -> global ----------------
+        const int ew = warp - 2;                      // 0..7
+        const int q = warp & 3;                       // TMEM lane quarter this warp may read
+        const int col0 = (ew >> 2) * COLS_PER_WARP;   // which half of the tile's columns
+        float accr[COLS_PER_WARP];
+#pragma unroll
+        for (int j = 0; j < COLS_PER_WARP; j++) accr[j] = 0.f;
+        for (int ch = 0; ch < num_chunks && ok; ch++) {
+            const int buf = ch & 1;
+            ok = mbar_wait(&acc_full[buf], (ch >> 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + col0);
+#pragma unroll
+            for (int g = 0; g < COLS_PER_WARP / 32; g++) {
+                uint32_t r[32];
+                tc_ld32(taddr + (uint32_t)(g * 32), r);
+#pragma unroll
+                for (int j = 0; j < 32; j++) accr[g * 32 + j] += __uint_as_float(r[j]);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
+        }
+        if (!ok && lane == 0) atomicExch(status, SB_ERR_TIMEOUT);
+        // The last chunk has arrived, so every MMA has finished reading the operand stages: their
+        // shared memory now stages the 128 x BN tile and the global stores are whole contiguous rows.
+        constexpr int SLD = BN + 4;                   // padded row pitch (floats): conflict-free 16-byte accesses
+        float* stage = (float*)smem;
+        {
+            float* srow = stage + (size_t)(q * 32 + lane) * SLD + col0;
+#pragma unroll
+            for (int j = 0; j < COLS_PER_WARP; j += 4)
+                *(float4*)(srow + j) = make_float4(accr[j], accr[j + 1], accr[j + 2], accr[j + 3]);
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * TC_EPI_WARPS) : "memory");      // epilogue warps only
+        if (ok) {
+            const bool vec = ((ldc & 3) == 0) && ((((uintptr_t)C) & 15) == 0);
+            for (int r = ew; r < TC_BM; r += TC_EPI_WARPS) {
+                const int grow = m0 + r;
+                if (grow >= M) break;
+                const float* srow = stage + (size_t)r * SLD;
+                float* crow = C + (size_t)grow * ldc + n0;
+                if (vec) {
+#pragma unroll
+                    for (int h = 0; h < (BN + 127) / 128; h++) {
+                        const int col = (h * 32 + lane) * 4;
+                        if (col < BN && n0 + col + 3 < N) {
+                            float4 v = *(const float4*)(srow + col);
+                            if (acc) { float4 o = *(const float4*)(crow + col); v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+                            *(float4*)(crow + col) = v;
+                        } else if (col < BN) {
+                            for (int j = 0; j < 4; j++) if (n0 + col + j < N) crow[col + j] = acc ? crow[col + j] + srow[col + j] : srow[col + j];
+                        }
+                    }
+                } else {
+                    for (int col = lane; col < BN && n0 + col < N; col += 32)
+                        crow[col] = acc ? crow[col] + srow[col] : srow[col];
+                }
+            }
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
+    }
+}
+
+// --------------------------------------------------------------------------- operand preparation kernels
+__device__ __forceinline__ float tf32_lo(float x) {
+    float hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
+    return x - hi;
+}
+// lo[i] = x[i] - tf32_trunc(x[i]);  8 bytes per element
+static __global__ void __launch_bounds__(256) split_lo_kernel(const float* __restrict__ x, float* __restrict__ lo, size_t n4) {
+    size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = tid; i < n4; i += nth) {
+        float4 v = ((const float4*)x)[i];
+        ((float4*)lo)[i] = make_float4(tf32_lo(v.x), tf32_lo(v.y), tf32_lo(v.z), tf32_lo(v.w));
+    }
+}
+// in [R, C] row-major -> hi [C, Rp] = in^T, lo [C, Rp] = lo(in^T); Rp = row pitch of the outputs (>= R, multiple of 4)
+static __global__ void __launch_bounds__(256) transpose_split_kernel(const float* __restrict__ in, float* __restrict__ hi, float* __restrict__ lo,
+                                                                     int R, int C, int Rp, int want_lo) {
+    __shared__ float tile[32][33];
+    int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;      // 32 x 8
+    for (int i = ty; i < 32; i += 8) {
+        int r = r0 + i, c = c0 + tx;
+        tile[i][tx] = (r < R && c < C) ? in[(size_t)r * C + c] : 0.f;
+    }
+    __syncthreads();
+    for (int i = ty; i < 32; i += 8) {
+        int c = c0 + i, r = r0 + tx;
+        if (c < C && r < Rp) {
+            float v = tile[tx][i];
+            hi[(size_t)c * Rp + r] = v;
+            if (want_lo) lo[(size_t)c * Rp + r] = tf32_lo(v);
+        }
+    }
+}
+
+// --------------------------------------------------------------------------- host side
+typedef CUresult (*tc_encode_fn_t)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static tc_encode_fn_t g_tc_encode = nullptr;
+
+static bool tc_load_encode() {
+    if (g_tc_encode) return true;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) return false;
+    g_tc_encode = (tc_encode_fn_t)fn;
+    return true;
+}
+
+// slot stride below the row pitch (heads interleaved inside a token row): dimensions are ordered {k, slot, row}
+static inline bool tc_swapped(const TcOperand& op) { return op.c2_dim > 1 && op.c2_stride < op.pitch; }
+
+// 3-D FP32 tensor {K, rows, slots} (or {K, slots, rows}); box = BK x box_rows x 1; reads beyond the extents give zero
+static bool tc_make_map(CUtensorMap* m, const float* base, const TcOperand& op, int K, int BK, int box_rows) {
+    const bool sw = tc_swapped(op);
+    const cuuint64_t nslot = (cuuint64_t)(op.c2_dim > 0 ? op.c2_dim : 1);
+    const cuuint64_t slot_stride = (cuuint64_t)(op.c2_dim > 1 ? op.c2_stride : (long)op.pitch * op.rows) * sizeof(float);
+    cuuint64_t dims[3] = {(cuuint64_t)K, sw ? nslot : (cuuint64_t)op.rows, sw ? (cuuint64_t)op.rows : nslot};
+    cuuint64_t strides[2] = {sw ? slot_stride : (cuuint64_t)op.pitch * sizeof(float), sw ? (cuuint64_t)op.pitch * sizeof(float) : slot_stride};
+    cuuint32_t box[3] = {(cuuint32_t)BK, sw ? 1u : (cuuint32_t)box_rows, sw ? (cuuint32_t)box_rows : 1u};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_tc_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             BK * 4 == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+template <int BN, int BK, int NTERMS, int STAGES>
+static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
+    CUtensorMap mAh, mAl, mBh, mBl;
+    if (!tc_make_map(&mAh, p.A.hi, p.A, p.K, BK, TC_BM) || !tc_make_map(&mBh, p.B.hi, p.B, p.K, BK, BN)) return false;
+    if (NTERMS == 3) { if (!tc_make_map(&mAl, p.A.lo, p.A, p.K, BK, TC_BM) || !tc_make_map(&mBl, p.B.lo, p.B, p.K, BK, BN)) return false; }
+    else { mAl = mAh; mBl = mBh; }
+    constexpr int STAGE_BYTES = (NTERMS == 3 ? 2 : 1) * (TC_BM + BN) * BK * 4;
+    constexpr size_t tile_bytes = (size_t)TC_BM * (BN + 4) * 4;
+    constexpr size_t ring_bytes = (size_t)STAGES * STAGE_BYTES;
+    static_assert(tile_bytes <= ring_bytes, "the output tile is staged in the operand ring");
+    size_t smem = ring_bytes + 1024 + 256;
+    auto kern = gemm_tc_kernel<BN, BK, NTERMS, STAGES>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
+        attr_set = true;
+    }
+    dim3 grid((unsigned)(((p.N + BN - 1) / BN) * ((p.M + TC_BM - 1) / TC_BM)), (unsigned)(p.nbatch > 0 ? p.nbatch : 1));
+    kern<<<grid, TC_THREADS, smem, (cudaStream_t)c->pub.stream>>>(mAh, mAl, mBh, mBl, p.C, p.ldc, p.c_batch_stride, p.M, p.N, p.K, p.acc,
+                                                                 p.causal, p.A.c2_base, p.A.c2_step, p.B.c2_base, p.B.c2_step,
+                                                                 (tc_swapped(p.A) ? 1 : 0) | (tc_swapped(p.B) ? 2 : 0), c->d_status);
+    c->launches++;
+    return cudaGetLastError() == cudaSuccess;
+}
+
+// picks the tile width from N; nterms: 3 = FP32-accurate, 1 = TF32
+static bool tc_launch(sb_ctx_t* c, const TcProblem& p, int nterms) {
+    if (!tc_load_encode()) return false;
+    if (p.N > 128) return nterms == 3 ? tc_launch_t<256, 16, 3, 4>(c, p) : tc_launch_t<256, 32, 1, 4>(c, p);
+    return nterms == 3 ? tc_launch_t<128, 16, 3, 6>(c, p) : tc_launch_t<128, 32, 1, 6>(c, p);
+}
+
+static inline bool tc_aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
+static inline int tc_ew_blocks(sb_ctx_t* c, size_t items) {
+    size_t b = (items + 255) / 256, cap = (size_t)(c->pub.gpu_sm_count > 0 ? c->pub.gpu_sm_count : 148) * 8;
+    return (int)(b > cap ? cap : (b ? b : 1));
+}

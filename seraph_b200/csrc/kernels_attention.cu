@@ -327,7 +327,8 @@ extern "C" {
 void sb_attention(sb_ctx_t* c, const float* Q, const float* K, const float* V, float* out, float* lse,
                   const uint32_t* seq_starts, const uint32_t* seq_ids, int T, int Hq, int Hkv, int hd) {
     if (T <= 0 || Hq <= 0 || Hkv <= 0 || hd <= 0) return;
-    if (hd > 256 || Hq % Hkv != 0 && (Hq < Hkv)) { sb_set_status(c, SB_ERR_SIZE); return; }
+    if (hd > 256 || Hq < Hkv) { sb_set_status(c, SB_ERR_SIZE); return; }
+    if (sb_attention_tc_forward(c, Q, K, V, out, lse, T, Hq, Hkv, hd) == 0) return;      // tensor-core path took it
     float scale = 1.0f / sqrtf((float)hd);
     dim3 grid((T + AT - 1) / AT, Hq);
     size_t smem = ((size_t)3 * hd * AT + (size_t)AT * PLD) * sizeof(float);
@@ -347,6 +348,7 @@ void sb_attention_backward(sb_ctx_t* c, const float* Q, const float* K, const fl
     (void)B;
     if (T <= 0 || Hq <= 0 || Hkv <= 0 || hd <= 0) return;
     if (hd > 256) { sb_set_status(c, SB_ERR_SIZE); return; }
+    if (sb_attention_tc_backward(c, Q, K, V, O, lse, dO, dQ, dK, dV, accumulate_kv, T, Hq, Hkv, hd) == 0) return;
     float scale = 1.0f / sqrtf((float)hd);
     cudaStream_t s = (cudaStream_t)c->pub.stream;
     float* delta = (float*)sb_scratch(c, (size_t)T * Hq * sizeof(float));

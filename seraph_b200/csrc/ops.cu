@@ -38,10 +38,34 @@ int sb_ensure_tokens(sb_ctx_t* c, int T, int B) {
     return 0;
 }
 
-// index tables for one packed batch described by a device seq_starts array
+int sb_set_host_seq(sb_ctx_t* c, const int* starts, int B) {
+    if (B + 1 > c->h_seq_cap) {
+        int cap = B + 1 < 64 ? 64 : B + 1;
+        int* p = (int*)realloc(c->h_seq, sizeof(int) * cap);
+        if (!p) { c->h_seq_n = 0; return 1; }
+        c->h_seq = p; c->h_seq_cap = cap;
+    }
+    for (int b = 0; b <= B; b++) c->h_seq[b] = starts[b];
+    for (int b = 0; b < B; b++) if (starts[b + 1] < starts[b]) { c->h_seq_n = 0; return 1; }
+    c->h_seq_n = B;
+    return 0;
+}
+
+// index tables for one packed batch described by a device seq_starts array; the boundaries are also read back
+// to the host (small synchronous copy) because the tensor-core attention builds its tile maps per sequence
 static int index_from_device_starts(sb_ctx_t* c, const uint32_t* d_starts, int B, int T) {
     if (sb_ensure_tokens(c, T, B)) return 1;
     sb_seq_index(c, d_starts, B, T, c->pos_ids, c->seq_ids);
+    c->h_seq_n = 0;
+    if (B > 0 && B < (1 << 20)) {
+        int* tmp = (int*)malloc(sizeof(int) * (size_t)(B + 1));
+        if (tmp) {
+            cudaStreamSynchronize((cudaStream_t)c->pub.stream);
+            if (cudaMemcpy(tmp, d_starts, sizeof(int) * (size_t)(B + 1), cudaMemcpyDeviceToHost) == cudaSuccess && tmp[0] == 0 && tmp[B] == T)
+                sb_set_host_seq(c, tmp, B);
+            free(tmp);
+        }
+    }
     return 0;
 }
 // single sequence of `len` rows (len may exceed T so that no row counts as "last")
@@ -50,6 +74,7 @@ static int index_single(sb_ctx_t* c, int T, int len) {
     uint32_t h[2] = {0u, (uint32_t)len};
     if (sb_check(c, cudaMemcpyAsync(c->seq_starts, h, sizeof h, cudaMemcpyHostToDevice, (cudaStream_t)c->pub.stream), "seq_starts upload")) return 1;
     sb_seq_index(c, c->seq_starts, 1, T, c->pos_ids, c->seq_ids);
+    if (len == T) { int hs[2] = {0, T}; sb_set_host_seq(c, hs, 1); } else c->h_seq_n = 0;
     return 0;
 }
 

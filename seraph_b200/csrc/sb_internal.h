@@ -82,6 +82,7 @@ typedef struct sb_ctx {
     float *g_hidden, *g_tmp, *g_xnorm, *g_q, *g_k, *g_v, *g_attn, *g_ffn, *g_gate, *g_up, *attn_delta;
     uint32_t *tokens, *targets, *seq_starts, *pos_ids, *seq_ids;
     int seq_cap, seq_starts_cap;
+    int* h_seq; int h_seq_n, h_seq_cap;   /* host copy of the current batch's sequence starts (h_seq_n + 1 entries); 0 = unknown */
     int res_T, res_B, res_max_seq;   /* geometry of the batch currently resident on the device */
     float* d_loss;                   /* device scalar */
     float* d_gnorm;                  /* device scalar: sum of squares of all gradients */
@@ -156,6 +157,13 @@ void sb_lora_backward(sb_ctx_t*, const float* dY, const float* X, const float* A
                       float* tmp, int T, int in, int out, int r, float s);
 void sb_memset(sb_ctx_t*, void* p, int byte, size_t bytes);
 void sb_copy(sb_ctx_t*, void* dst, const void* src, size_t bytes);
+
+/* host copy of the sequence boundaries of the batch the index tables describe */
+int  sb_set_host_seq(sb_ctx_t* c, const int* starts, int B);
+/* tensor-core attention (attention_tc.cu); nonzero = not eligible, caller uses the CUDA-core kernels */
+int  sb_attention_tc_forward(sb_ctx_t*, const float* Q, const float* K, const float* V, float* O, float* lse, int T, int Hq, int Hkv, int hd);
+int  sb_attention_tc_backward(sb_ctx_t*, const float* Q, const float* K, const float* V, const float* O, const float* lse, const float* dO,
+                              float* dQ, float* dK, float* dV, int accumulate_kv, int T, int Hq, int Hkv, int hd);
 
 /* profiler hooks used around launches */
 int  sb_prof_begin(sb_ctx_t*, const char* name);

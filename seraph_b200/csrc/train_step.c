@@ -508,6 +508,7 @@ static int upload_batch(sb_ctx_t* c, const int* tokens, int T, const int* seq_st
     cudaMemcpyAsync(c->targets, h_tgt, (size_t)T * 4, cudaMemcpyHostToDevice, S(c));
     cudaMemcpyAsync(c->seq_starts, h_ss, (size_t)(B + 1) * 4, cudaMemcpyHostToDevice, S(c));
     sb_seq_index(c, c->seq_starts, B, T, c->pos_ids, c->seq_ids);
+    sb_set_host_seq(c, seq_starts, B);
     *max_seq_out = max_seq;
     return 0;
 }
@@ -739,6 +740,7 @@ void cuda_train_free(cuda_train_context_t* ctx) {
     if (c->d_status) cudaFree(c->d_status);
     if (c->d_loss) cudaFree(c->d_loss);
     if (c->h_pinned) cudaFreeHost(c->h_pinned);
+    free(c->h_seq);
     if (c->pub.debug_nan_flags) cuda_train_buffer_free(ctx, c->pub.debug_nan_flags);
     cudaStreamDestroy(S(c));
     c->magic = 0;

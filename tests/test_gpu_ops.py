@@ -148,6 +148,9 @@ ATT_CASES = [
     ([0, 64, 129, 200, 333], 8, 2, 32),
     ([0, 257], 4, 1, 128),
     ([0, 100, 190], 2, 1, 90),
+    ([0, 300, 700], 4, 2, 64),
+    ([0, 1024], 4, 1, 128),
+    ([0, 513, 640, 1100], 6, 3, 32),
 ]
 
 

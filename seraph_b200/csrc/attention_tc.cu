@@ -19,10 +19,11 @@
 // flash_attention_bwd[_packed] :1859/:2012.
 #include <math.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include "gemm_tc.cuh"
 
 #define AT_ROWTILE 128
-#define AT_L2_BUDGET (80.0 * 1024 * 1024)
+#define AT_SCRATCH_BUDGET (512.0 * 1024 * 1024)   // causal part of the score scratch per launch; measured: fewer, larger launches beat L2 residency
 
 static inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
@@ -159,9 +160,16 @@ static void at_transpose(sb_ctx_t* c, const float* x, int tok0, int S, int cols,
     c->launches++;
 }
 
+// heads per launch: as many as keep the causal part of their score scratch inside the budget
+// (SERAPH_B200_ATTN_SCRATCH_MB overrides the default, which is sized to stay in L2)
 static int at_group(int S_pad, int nbuf, int Hkv) {
+    static double budget = 0;
+    if (budget == 0) {
+        const char* e = getenv("SERAPH_B200_ATTN_SCRATCH_MB");
+        budget = (e && atof(e) > 0) ? atof(e) * 1024 * 1024 : AT_SCRATCH_BUDGET;
+    }
     double per_head = (double)nbuf * S_pad * (double)S_pad * 4.0 * 0.55;
-    int G = (int)(AT_L2_BUDGET / per_head);
+    int G = (int)(budget / per_head);
     if (G < 1) G = 1;
     if (G > Hkv) G = Hkv;
     return G;

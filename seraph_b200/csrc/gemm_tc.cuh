@@ -36,6 +36,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
 #include "sb_internal.h"
 
 #define TC_BM 128
@@ -367,8 +369,29 @@ static bool tc_load_encode() {
 // slot stride below the row pitch (heads interleaved inside a token row): dimensions are ordered {k, slot, row}
 static inline bool tc_swapped(const TcOperand& op) { return op.c2_dim > 1 && op.c2_stride < op.pitch; }
 
+// Encoding a tensor map costs a few microseconds on the host and a training step re-issues the same
+// (pointer, shape) combinations every layer and every step, so encoded maps are kept in a small
+// direct-mapped cache keyed by everything that goes into the encoding.
+struct TcMapKey { const float* base; long pitch, c2_stride; int K, rows, c2_dim, BK, box_rows; };
+struct TcMapEntry { TcMapKey key; CUtensorMap map; bool valid; };
+#define TC_MAP_CACHE 8192
+static TcMapEntry* g_tc_map_cache = nullptr;
+
 // 3-D FP32 tensor {K, rows, slots} (or {K, slots, rows}); box = BK x box_rows x 1; reads beyond the extents give zero
 static bool tc_make_map(CUtensorMap* m, const float* base, const TcOperand& op, int K, int BK, int box_rows) {
+    TcMapKey key;
+    memset(&key, 0, sizeof key);
+    key.base = base; key.pitch = op.pitch; key.c2_stride = op.c2_dim > 1 ? op.c2_stride : 0; key.K = K; key.rows = op.rows;
+    key.c2_dim = op.c2_dim > 1 ? op.c2_dim : 1; key.BK = BK; key.box_rows = box_rows;
+    if (!g_tc_map_cache) g_tc_map_cache = (TcMapEntry*)calloc(TC_MAP_CACHE, sizeof(TcMapEntry));
+    TcMapEntry* e = nullptr;
+    if (g_tc_map_cache) {
+        uint64_t h = 1469598103934665603ull;
+        const unsigned char* kb = (const unsigned char*)&key;
+        for (size_t i = 0; i < sizeof key; i++) { h ^= kb[i]; h *= 1099511628211ull; }
+        e = &g_tc_map_cache[h % TC_MAP_CACHE];
+        if (e->valid && memcmp(&e->key, &key, sizeof key) == 0) { *m = e->map; return true; }
+    }
     const bool sw = tc_swapped(op);
     const cuuint64_t nslot = (cuuint64_t)(op.c2_dim > 0 ? op.c2_dim : 1);
     const cuuint64_t slot_stride = (cuuint64_t)(op.c2_dim > 1 ? op.c2_stride : (long)op.pitch * op.rows) * sizeof(float);
@@ -379,7 +402,9 @@ static bool tc_make_map(CUtensorMap* m, const float* base, const TcOperand& op, 
     CUresult r = g_tc_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                              BK * 4 == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
+    if (r != CUDA_SUCCESS) return false;
+    if (e) { e->key = key; e->map = *m; e->valid = true; }
+    return true;
 }
 
 template <int BN, int BK, int NTERMS, int STAGES>

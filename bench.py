@@ -30,8 +30,10 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 QWEN = dict(V=151936, d=2048, L=28, Hq=16, Hkv=8, hd=128, F=6144, theta=1e6)
 SMALL = dict(V=8192, d=512, L=8, Hq=8, Hkv=8, hd=64, F=1408, theta=10000.0)
+SLICE = dict(V=16384, d=2048, L=2, Hq=16, Hkv=8, hd=128, F=6144, theta=1e6)     # two Qwen3-1.7B-shaped layers: small enough to profile
 WORKLOADS = {
     "qwen3-1.7b-shaped full-weight FP32, 4x2048 tokens per rank": (QWEN, 4, 2048),
+    "profiling slice: 2 qwen3-1.7b-shaped layers, vocab 16384, 2x2048 tokens": (SLICE, 2, 2048),
     "33M Llama-style full-weight FP32, 8x256 tokens per rank": (SMALL, 8, 256),
 }
 
@@ -93,6 +95,9 @@ def attention_flops(B, S, Hq, hd):
 
 
 def run_ours(args):
+    # libraries (NCCL among them) may print to stdout; keep fd 1 for the one JSON line
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     import torch
     import torch.distributed as dist
     from seraph_b200 import api, build
@@ -150,7 +155,8 @@ def run_ours(args):
 
     # ---- warm-up through the public call (also uploads the model) ----
     loss0 = None
-    for i in range(max(args.warmup, 3)):
+    n_warm = args.warmup if args.short_warmup else max(args.warmup, 3)
+    for i in range(max(n_warm, 1)):
         loss0 = public_step(i % n_batches)
     ctx.check()
 
@@ -214,7 +220,7 @@ def run_ours(args):
         achieved = (g_fl / g_n) / ((g_ms / g_n) * 1e-3) * 1e-12 if g_n else None
         line = {
             "metric": "train tokens/sec (fwd+bwd+AdamW)", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+            "n_gpus": world, "steps": args.steps, "warmup": n_warm, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32" if args.gemm_mode in (0, 3) else ("tf32" if args.gemm_mode == 1 else "bf16"),
             "data": "synthetic",
@@ -236,7 +242,7 @@ def run_ours(args):
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(mc, quick=True)
-        print(json.dumps(line))
+        os.write(real_stdout, (json.dumps(line) + "\n").encode())
     st.close()
     ctx.close()
     if world > 1:
@@ -317,10 +323,15 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=list(WORKLOADS)[0], choices=list(WORKLOADS))
+    ap.add_argument("--workload", default=list(WORKLOADS)[0],
+                    help="a key of WORKLOADS or its index (0 = the benchmark configuration, 1 = profiling slice, 2 = 33M model)")
     ap.add_argument("--gemm-mode", type=int, default=0, help="0 FP32-accurate tensor cores (default), 1 TF32, 2 BF16, 3 CUDA cores")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--short-warmup", action="store_true", help="honour --warmup below 3 (profiler captures only; not a valid bench number)")
     args = ap.parse_args()
+    if args.workload.isdigit():
+        args.workload = list(WORKLOADS)[int(args.workload)]
+    assert args.workload in WORKLOADS, list(WORKLOADS)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -26,7 +26,7 @@ def _newer(srcs, target):
 def build(force=False, verbose=False):
     cu = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
     cc = sorted(glob.glob(os.path.join(CSRC, "*.c")))
-    hdr = glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(HERE, "..", "include", "*.h"))
+    hdr = glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(HERE, "..", "include", "*.h"))
     if not force and not _newer(cu + cc + hdr, OUT):
         return OUT
     objdir = os.path.join(HERE, "build")

@@ -13,8 +13,10 @@
 //               from an FP32 word, lo = x - hi; the kernel issues hi*hi + lo*hi + hi*lo.
 //   NTERMS = 1: single-pass TF32.
 // The tensor core adds into its FP32 accumulator with truncation, so a long chain of
-// accumulating MMAs drifts by about one ulp per instruction (measured: 3e-5 relative after
-// K = 4096).  The k range is therefore cut into chunks of TC_CHUNK_K: each chunk is accumulated
+// accumulating MMAs drifts by about half an ulp per instruction, always towards zero (measured:
+// 3e-5 relative after K = 4096 in one chain; 1.4e-6 per product with 48-instruction chains, which
+// the layers of a model amplify to 1e-5 in the deepest gradients; 12-instruction chains bring the
+// whole model to 3e-6).  The k range is therefore cut into chunks of TC_CHUNK_K floats: each chunk is accumulated
 // in one of two TMEM buffers and the epilogue warps add the finished chunk into register
 // accumulators with round-to-nearest FP32 adds while the next chunk is already being
 // multiplied into the other buffer.
@@ -44,7 +46,7 @@
 #define TC_EPI_WARPS 8
 #define TC_THREADS (64 + 32 * TC_EPI_WARPS)
 #define TC_GROUP_M 16
-#define TC_CHUNK_K 128
+#define TC_CHUNK_K 32
 #define TC_SPIN_CYCLES 4000000000ll      // ~2 s at 2 GHz: far beyond any legitimate wait
 
 enum { TC_CAUSAL_NONE = 0, TC_CAUSAL_SKIP_UPPER, TC_CAUSAL_SKIP_LOWER, TC_CAUSAL_K_UPTO_M, TC_CAUSAL_K_FROM_M };
@@ -318,9 +320,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
 }
 
 // --------------------------------------------------------------------------- operand preparation kernels
+// lo part of the hi/lo split: x minus the 19 leading bits the tensor core reads.  The result is
+// rounded to nearest at TF32 precision here, so the tensor core's own truncation of it is exact
+// and the cross terms carry no one-sided error.
 __device__ __forceinline__ float tf32_lo(float x) {
     float hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
-    return x - hi;
+    float lo = x - hi;
+    uint32_t u = __float_as_uint(lo);
+    u += 0x00000fffu + ((u >> 13) & 1u);
+    return __uint_as_float(u & 0xffffe000u);
 }
 // lo[i] = x[i] - tf32_trunc(x[i]);  8 bytes per element
 static __global__ void __launch_bounds__(256) split_lo_kernel(const float* __restrict__ x, float* __restrict__ lo, size_t n4) {

@@ -127,6 +127,86 @@ __global__ void __launch_bounds__(RB_THREADS) rmsnorm_bwd_kernel(const float* __
     }
 }
 
+// ---------------------------------------------------------------------------
+// Warp-per-row variants for rows of up to 128*NV floats (cols % 4 == 0): the whole row lives in
+// registers, every lane has NV independent 16-byte loads in flight, reductions are warp shuffles
+// only, and the row is read from memory exactly once.
+// ---------------------------------------------------------------------------
+template <int NV>
+__global__ void __launch_bounds__(RB_THREADS) rmsnorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                                  float* __restrict__ y, int rows, int cols, float eps) {
+    const int lane = threadIdx.x & 31, warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+    const int c4 = cols >> 2;
+    for (int r = warp; r < rows; r += nwarps) {
+        const float4* xr = (const float4*)(x + (size_t)r * cols);
+        float4 v[NV];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            int j = lane + 32 * i;
+            v[i] = j < c4 ? xr[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+            ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+        }
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / cols + eps);
+        float4* yr = (float4*)(y + (size_t)r * cols);
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            int j = lane + 32 * i;
+            if (j < c4) { float4 s = ((const float4*)w)[j]; yr[j] = make_float4(v[i].x * inv * s.x, v[i].y * inv * s.y, v[i].z * inv * s.z, v[i].w * inv * s.w); }
+        }
+    }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(RB_THREADS) rmsnorm_bwd_warp_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                                      const float* __restrict__ dy, const float* resid, float* dx,
+                                                                      float* __restrict__ partial, int rows, int cols, float eps) {
+    const int lane = threadIdx.x & 31, warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+    const int c4 = cols >> 2;
+    float4 acc[NV];
+#pragma unroll
+    for (int i = 0; i < NV; i++) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = warp; r < rows; r += nwarps) {
+        const float4* xr = (const float4*)(x + (size_t)r * cols); const float4* gr = (const float4*)(dy + (size_t)r * cols);
+        float4 v[NV], g[NV];
+        float ss = 0.f, cp = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            int j = lane + 32 * i;
+            if (j < c4) { v[i] = xr[j]; g[i] = gr[j]; } else { v[i] = make_float4(0.f, 0.f, 0.f, 0.f); g[i] = v[i]; }
+        }
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            int j = lane + 32 * i;
+            if (j < c4) {
+                float4 s = ((const float4*)w)[j];
+                ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+                cp += g[i].x * s.x * v[i].x + g[i].y * s.y * v[i].y + g[i].z * s.z * v[i].z + g[i].w * s.w * v[i].w;
+            }
+        }
+        ss = warp_sum(ss); cp = warp_sum(cp);
+        const float inv = 1.0f / sqrtf(ss / cols + eps);
+        const float k = inv * inv * inv / cols * cp;
+        float4* dr = (float4*)(dx + (size_t)r * cols); const float4* rr = resid ? (const float4*)(resid + (size_t)r * cols) : nullptr;
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            int j = lane + 32 * i;
+            if (j < c4) {
+                float4 s = ((const float4*)w)[j], o;
+                acc[i].x += g[i].x * v[i].x * inv; acc[i].y += g[i].y * v[i].y * inv; acc[i].z += g[i].z * v[i].z * inv; acc[i].w += g[i].w * v[i].w * inv;
+                o.x = g[i].x * s.x * inv - v[i].x * k; o.y = g[i].y * s.y * inv - v[i].y * k;
+                o.z = g[i].z * s.z * inv - v[i].z * k; o.w = g[i].w * s.w * inv - v[i].w * k;
+                if (rr) { float4 q = rr[j]; o.x += q.x; o.y += q.y; o.z += q.z; o.w += q.w; }
+                dr[j] = o;
+            }
+        }
+    }
+    float4* pr = (float4*)(partial + (size_t)warp * cols);          // one partial row per warp of the grid
+#pragma unroll
+    for (int i = 0; i < NV; i++) { int j = lane + 32 * i; if (j < c4) pr[j] = acc[i]; }
+}
+
 // dscale[c] += sum over blocks (fixed order) of partial[b][c]
 __global__ void colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ dscale, int nblocks, int cols) {
     int cidx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -365,6 +445,15 @@ void sb_rmsnorm(sb_ctx_t* c, const float* x, const float* w, float* y, int rows,
     int grid = rows < sm_count(c) * 8 ? rows : sm_count(c) * 8;
     int vec = (cols % 4 == 0) && aligned16(x) && aligned16(w) && aligned16(y);
     int tk = sb_tick_begin(c, SB_CLS_NORM_FWD);
+    if (vec && cols <= 4096 && rows >= 64) {
+        // warp per row: 8 rows per CTA
+        int wgrid = (rows + 7) / 8; if (wgrid > sm_count(c) * 8) wgrid = sm_count(c) * 8;
+        cudaStream_t st = (cudaStream_t)c->pub.stream;
+        if (cols <= 512)       rmsnorm_warp_kernel<4><<<wgrid, RB_THREADS, 0, st>>>(x, w, y, rows, cols, eps);
+        else if (cols <= 1024) rmsnorm_warp_kernel<8><<<wgrid, RB_THREADS, 0, st>>>(x, w, y, rows, cols, eps);
+        else if (cols <= 2048) rmsnorm_warp_kernel<16><<<wgrid, RB_THREADS, 0, st>>>(x, w, y, rows, cols, eps);
+        else                   rmsnorm_warp_kernel<32><<<wgrid, RB_THREADS, 0, st>>>(x, w, y, rows, cols, eps);
+    } else
     rmsnorm_kernel<<<grid, RB_THREADS, 0, (cudaStream_t)c->pub.stream>>>(x, w, y, rows, cols, eps, vec);
     sb_tick_end(c, tk, 0.0, 8.0 * rows * cols);
     c->launches++;
@@ -388,6 +477,23 @@ void sb_rmsnorm_backward(sb_ctx_t* c, const float* x, const float* w, const floa
                          float* dx_out, float* dscale, int rows, int cols, float eps) {
     if (rows <= 0 || cols <= 0) return;
     if (cols > RB_THREADS * 4 * RN_MAX_SWEEP || (cols % 4 != 0 && cols > RB_THREADS * RN_MAX_SWEEP * 4)) { sb_set_status(c, SB_ERR_SIZE); return; }
+    int vec = (cols % 4 == 0) && aligned16(x) && aligned16(w) && aligned16(dy) && aligned16(dx_out) && (!resid || aligned16(resid));
+    if (vec && cols <= 2048 && rows >= 64) {
+        // warp per row, rows kept in registers; one dscale partial per warp of the grid, summed in warp order
+        int wgrid = (rows + 7) / 8; if (wgrid > sm_count(c)) wgrid = sm_count(c);
+        int nwarps = wgrid * (RB_THREADS / 32);
+        float* partial = (float*)sb_scratch(c, (size_t)nwarps * cols * sizeof(float));
+        if (!partial) return;
+        cudaStream_t st = (cudaStream_t)c->pub.stream;
+        int tk = sb_tick_begin(c, SB_CLS_NORM_BWD);
+        if (cols <= 512)       rmsnorm_bwd_warp_kernel<4><<<wgrid, RB_THREADS, 0, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
+        else if (cols <= 1024) rmsnorm_bwd_warp_kernel<8><<<wgrid, RB_THREADS, 0, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
+        else                   rmsnorm_bwd_warp_kernel<16><<<wgrid, RB_THREADS, 0, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
+        colsum_partials_kernel<<<(cols + 255) / 256, 256, 0, st>>>(partial, dscale, nwarps, cols);
+        sb_tick_end(c, tk, 0.0, (resid ? 16.0 : 12.0) * rows * cols);
+        c->launches += 2;
+        return;
+    }
     int grid = rn_bwd_grid(c, rows);
     float* partial = (float*)sb_scratch(c, (size_t)grid * cols * sizeof(float));
     if (!partial) return;

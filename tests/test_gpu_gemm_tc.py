@@ -1,6 +1,6 @@
 """Tensor-core GEMM (tcgen05, TMA, TMEM) against the FP64-accumulate oracle, through the C ABI.
 Stated bounds (relative L2 of the whole result, standard-normal operands):
-  mode 0, FP32-accurate (three TF32 passes on a hi/lo split):  <= 1e-5   (the parity bar of the FP32 path)
+  mode 0, FP32-accurate (three TF32 passes on a hi/lo split):  <= 2e-6   (the FP32 path; whole-model gradients must meet 1e-5)
   mode 1, single-pass TF32:                                    <= 2e-3
 Shapes include ragged M/N/K edges (TMA zero fill), all three layouts, accumulate, long K."""
 import numpy as np
@@ -10,7 +10,7 @@ import oracle_lib as O
 from oracle_lib import rel_l2
 
 pytestmark = pytest.mark.gpu
-BOUND = {0: 1e-5, 1: 2e-3}
+BOUND = {0: 2e-6, 1: 2e-3}
 
 SHAPES = [(128, 256, 64), (256, 128, 32), (130, 257, 96), (384, 512, 1024), (100, 200, 4096), (1000, 1000, 40),
           (129, 33, 512), (2048, 64, 256)]
@@ -60,5 +60,5 @@ def test_tc_gemm_long_k_and_reproducible(ctx):
     ctx.check()
     e = rel_l2(o1, ref)
     print("FP32-accurate tensor-core GEMM, K=16384: rel-L2 vs FP64 accumulate =", e)
-    assert e < 1e-5 and np.array_equal(o1, o2)
+    assert e < 2e-6 and np.array_equal(o1, o2)
     ctx.release(a, b, c, c2)

@@ -159,6 +159,13 @@ int seraph_b200_last_status(cuda_train_context_t* ctx);
  * hi/lo split, default), 1 = single-pass TF32, 2 = BF16 (also selected by
  * ctx->use_bf16), 3 = FP32 FMA on CUDA cores. */
 int seraph_b200_set_gemm_mode(cuda_train_context_t* ctx, int mode);
+/* 1 (default): tensor-core GEMMs of plain matrices run on pairs of CTAs that
+ * share one 256-row MMA (half of each B tile per CTA); 0: one CTA per tile. */
+int seraph_b200_set_gemm_pair(cuda_train_context_t* ctx, int on);
+/* 1 (default): the tiles of a GEMM's last, partly filled wave are cut into
+ * pieces of the k range that fill the machine and are added in a fixed order;
+ * 0: whole tiles only. */
+int seraph_b200_set_gemm_tail_split(cuda_train_context_t* ctx, int on);
 /* 0 (default): LoRA steps leave the adapters' own term out of dX, as the
  * reference does; 1: full chain rule, dX += s (dY B) A. */
 int seraph_b200_set_lora_exact(cuda_train_context_t* ctx, int exact);

@@ -78,6 +78,8 @@ cuda_train_context_t* cuda_train_init(int device_id) {
     if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) { free(c); return NULL; }
     c->magic = SB_MAGIC;
     c->gemm_mode = SB_GEMM_FP32X3;
+    { const char* e = getenv("SERAPH_B200_GEMM_PAIR"); c->gemm_pair = (e && e[0] == '0') ? 0 : 1; }
+    { const char* e = getenv("SERAPH_B200_GEMM_TAIL_SPLIT"); c->gemm_tail_split = (e && e[0] == '0') ? 0 : 1; }
     c->dp_world = 1;
     cuda_train_context_t* p = &c->pub;
     p->device_id = device_id; p->stream = s; p->initialized = 1;
@@ -260,6 +262,20 @@ int seraph_b200_set_gemm_mode(cuda_train_context_t* ctx, int mode) {
     sb_ctx_t* c = sb_priv(ctx);
     if (!c || mode < 0 || mode > 3) return SB_ERR_ARG;
     c->gemm_mode = mode;
+    return SB_OK;
+}
+
+int seraph_b200_set_gemm_pair(cuda_train_context_t* ctx, int on) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c) return SB_ERR_ARG;
+    c->gemm_pair = on ? 1 : 0;
+    return SB_OK;
+}
+
+int seraph_b200_set_gemm_tail_split(cuda_train_context_t* ctx, int on) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c) return SB_ERR_ARG;
+    c->gemm_tail_split = on ? 1 : 0;
     return SB_OK;
 }
 

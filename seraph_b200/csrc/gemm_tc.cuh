@@ -92,6 +92,32 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, u
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
                  ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
+// ---- CTA-pair (cta_group::2) forms: the two CTAs of a cluster issue one 256-row MMA; rank 0 leads
+__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+    uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank)); return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// load into this CTA's shared memory, byte count credited to the barrier at cluster address `bar_cluster` (the leader's)
+__device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+// arrives on the barrier at the same offset in both CTAs of the pair once the MMAs issued so far have completed
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
@@ -126,15 +152,41 @@ __device__ __forceinline__ uint64_t make_kmajor_desc(uint32_t smem_addr) {
     return d;
 }
 
+// Tile order: groups of `group` row tiles; inside a group the row tile runs fastest, so CTAs
+// resident together share a few A row tiles and a few B row tiles and both operands are re-read
+// from L2 even when one of them (the embedding table) is far larger than L2.
+__device__ __forceinline__ void tc_raster(int tile_id, int tiles_m, int tiles_n, int group, int* m_tile, int* n_tile) {
+    const int per_group = group * tiles_n;
+    const int gid = tile_id / per_group, in_g = tile_id % per_group;
+    const int first_m = gid * group;
+    const int gsize = min(group, tiles_m - first_m);
+    *m_tile = first_m + in_g % gsize;
+    *n_tile = in_g / gsize;
+}
+
 // --------------------------------------------------------------------------- the kernel
-template <int BN, int BK, int NTERMS, int STAGES>
+// CTAS = 2: the CTA pair of a cluster computes a 256 x BN tile with cta_group::2 MMAs issued by the
+// pair's rank-0 CTA.  Each CTA loads its own 128 rows of A and BN/2 rows of B, so per flop it takes a
+// third less from L2 and the tensor core reads a third less shared memory than two independent CTAs
+// would; each CTA's tensor memory holds its 128 rows of the tile and its own epilogue warps drain them.
+// Plain GEMMs only (no causal modes, one batch).
+//
+// Tail split: the tiles beyond the last full wave (tile ids >= split_full) are each cut into split_s
+// pieces of the k range, one CTA (pair) per piece, so the last wave fills the machine with short
+// pieces instead of leaving most SMs idle behind a few whole tiles.  A piece writes its 128 x BN
+// block to `partial`; tc_splitk_fixup_kernel adds the pieces in piece order, so the result does not
+// depend on timing.
+template <int BN, int BK, int NTERMS, int STAGES, int CTAS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
                float* __restrict__ Cbase, long ldc, long c_batch_stride, int M, int N, int K, int acc, int causal,
-               int a_c2_base, int a_c2_step, int b_c2_base, int b_c2_step, int swap_mask, int* status) {
+               int a_c2_base, int a_c2_step, int b_c2_base, int b_c2_step, int swap_mask,
+               int split_full, int split_s, float* __restrict__ partial, int* status) {
     constexpr int SWZ = BK * 4;
-    constexpr int A_BYTES = TC_BM * BK * 4, B_BYTES = BN * BK * 4;
+    constexpr int BROWS = BN / CTAS;                             // B rows this CTA loads
+    constexpr int TILE_M = TC_BM * CTAS;
+    constexpr int A_BYTES = TC_BM * BK * 4, B_BYTES = BROWS * BK * 4;
     constexpr int STAGE_BYTES = (NTERMS == 3 ? 2 : 1) * (A_BYTES + B_BYTES);
     constexpr uint32_t TMEM_COLS = 2 * BN;                       // two accumulator buffers
     constexpr int KB_PER_CHUNK = TC_CHUNK_K / BK;
@@ -149,26 +201,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int batch = blockIdx.y;
-    // Tile order: groups of TC_GROUP_M row tiles; inside a group the row tile runs fastest, so CTAs
-    // resident together share a few A row tiles and a few B row tiles and both operands are re-read
-    // from L2 even when one of them (the embedding table) is far larger than L2.
-    const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + BN - 1) / BN;
+    const uint32_t rank = CTAS == 2 ? cluster_ctarank() : 0u;
+    const bool leader = rank == 0;
+    const int tiles_m = (M + TILE_M - 1) / TILE_M, tiles_n = (N + BN - 1) / BN;
     int m_tile, n_tile;
-    {
-        const int per_group = TC_GROUP_M * tiles_n;
-        const int gid = blockIdx.x / per_group, in_g = blockIdx.x % per_group;
-        const int first_m = gid * TC_GROUP_M;
-        const int gsize = min(TC_GROUP_M, tiles_m - first_m);
-        m_tile = first_m + in_g % gsize;
-        n_tile = in_g / gsize;
-    }
-    const int m0 = m_tile * TC_BM, n0 = n_tile * BN;
-    // causal structure: whole-tile skips and the k range (CTA-uniform)
-    if (causal == TC_CAUSAL_SKIP_UPPER && n0 > m0 + TC_BM - 1) return;
-    if (causal == TC_CAUSAL_SKIP_LOWER && n0 + BN - 1 < m0) return;
+    int tile_id = blockIdx.x / CTAS, piece = 0;
+    const bool split = split_s > 1 && tile_id >= split_full;
+    if (split) { const int t = tile_id - split_full; piece = t % split_s; tile_id = split_full + t / split_s; }
+    tc_raster(tile_id, tiles_m, tiles_n, TC_GROUP_M / CTAS, &m_tile, &n_tile);
+    const int m0 = m_tile * TILE_M + (int)rank * TC_BM, n0 = n_tile * BN;      // this CTA's rows of A and C; the tile's columns
+    const int nb0 = n0 + (int)rank * BROWS;                                     // this CTA's rows of B
     int kb_begin = 0, kb_end = (K + BK - 1) / BK;
-    if (causal == TC_CAUSAL_K_UPTO_M) kb_end = min(kb_end, (m0 + TC_BM + BK - 1) / BK);
-    if (causal == TC_CAUSAL_K_FROM_M) kb_begin = min(kb_end, m0 / BK);
+    if (CTAS == 1) {
+        // causal structure: whole-tile skips and the k range (CTA-uniform)
+        if (causal == TC_CAUSAL_SKIP_UPPER && n0 > m0 + TC_BM - 1) return;
+        if (causal == TC_CAUSAL_SKIP_LOWER && n0 + BN - 1 < m0) return;
+        if (causal == TC_CAUSAL_K_UPTO_M) kb_end = min(kb_end, (m0 + TC_BM + BK - 1) / BK);
+        if (causal == TC_CAUSAL_K_FROM_M) kb_begin = min(kb_end, m0 / BK);
+    }
+    if (split) {
+        const int per = ((kb_end + split_s - 1) / split_s + KB_PER_CHUNK - 1) / KB_PER_CHUNK * KB_PER_CHUNK;
+        kb_begin = min(kb_end, piece * per);
+        kb_end = min(kb_end, kb_begin + per);
+    }
     const int num_kb = kb_end - kb_begin;
     const int num_chunks = (num_kb + KB_PER_CHUNK - 1) / KB_PER_CHUNK;
     float* C = Cbase + (size_t)batch * c_batch_stride;
@@ -176,15 +231,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], TC_EPI_WARPS); }
+        for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], TC_EPI_WARPS * CTAS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+        if (CTAS == 2) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (CTAS == 2) cluster_sync_all();          // the peer's barriers exist before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
@@ -197,24 +258,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
                 ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1);
                 if (!ok) break;
                 uint8_t* st = smem + s * STAGE_BYTES;
-                mbar_expect_tx(&full[s], STAGE_BYTES);
+                if (leader) mbar_expect_tx(&full[s], STAGE_BYTES * CTAS);      // the pair's bytes all land on the leader's barrier
                 // a map whose slot stride is smaller than its row pitch is encoded as {k, slot, row}
                 const int a1 = (swap_mask & 1) ? a_c2 : m0, a2 = (swap_mask & 1) ? m0 : a_c2;
-                const int b1 = (swap_mask & 2) ? b_c2 : n0, b2 = (swap_mask & 2) ? n0 : b_c2;
-                tma_load_3d(st, &tmAh, &full[s], kb * BK, a1, a2);
-                tma_load_3d(st + A_BYTES, &tmBh, &full[s], kb * BK, b1, b2);
-                if (NTERMS == 3) {
-                    tma_load_3d(st + A_BYTES + B_BYTES, &tmAl, &full[s], kb * BK, a1, a2);
-                    tma_load_3d(st + 2 * A_BYTES + B_BYTES, &tmBl, &full[s], kb * BK, b1, b2);
+                const int b1 = (swap_mask & 2) ? b_c2 : nb0, b2 = (swap_mask & 2) ? nb0 : b_c2;
+                if (CTAS == 2) {
+                    const uint32_t fb = mapa_u32(smem_u32(&full[s]), 0);
+                    tma_load_3d_pair(st, &tmAh, fb, kb * BK, a1, a2);
+                    tma_load_3d_pair(st + A_BYTES, &tmBh, fb, kb * BK, b1, b2);
+                    if (NTERMS == 3) {
+                        tma_load_3d_pair(st + A_BYTES + B_BYTES, &tmAl, fb, kb * BK, a1, a2);
+                        tma_load_3d_pair(st + 2 * A_BYTES + B_BYTES, &tmBl, fb, kb * BK, b1, b2);
+                    }
+                } else {
+                    tma_load_3d(st, &tmAh, &full[s], kb * BK, a1, a2);
+                    tma_load_3d(st + A_BYTES, &tmBh, &full[s], kb * BK, b1, b2);
+                    if (NTERMS == 3) {
+                        tma_load_3d(st + A_BYTES + B_BYTES, &tmAl, &full[s], kb * BK, a1, a2);
+                        tma_load_3d(st + 2 * A_BYTES + B_BYTES, &tmBl, &full[s], kb * BK, b1, b2);
+                    }
                 }
             }
             if (!ok) atomicExch(status, SB_ERR_TIMEOUT);
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (elect_one()) {
+        if (leader && elect_one()) {
             // instruction descriptor: D = F32, A = B = TF32, both K-major, N and M of the tile
-            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
             int it = 0;
             for (int ch = 0; ch < num_chunks && ok; ch++) {
                 const int buf = ch & 1;
@@ -235,16 +306,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
 #pragma unroll
                     for (int k = 0; k < BK / 8; k++) {
                         uint64_t adv = (uint64_t)(k * 2);             // 8 floats = 32 bytes, in 16-byte units
-                        tc_mma_tf32(tmem_d, ah + adv, bh + adv, idesc, first ? 0u : 1u);
-                        first = false;
-                        if (NTERMS == 3) {
-                            tc_mma_tf32(tmem_d, al + adv, bh + adv, idesc, 1);
-                            tc_mma_tf32(tmem_d, ah + adv, bl + adv, idesc, 1);
+                        if (CTAS == 2) {
+                            tc_mma_tf32_pair(tmem_d, ah + adv, bh + adv, idesc, first ? 0u : 1u);
+                            if (NTERMS == 3) {
+                                tc_mma_tf32_pair(tmem_d, al + adv, bh + adv, idesc, 1);
+                                tc_mma_tf32_pair(tmem_d, ah + adv, bl + adv, idesc, 1);
+                            }
+                        } else {
+                            tc_mma_tf32(tmem_d, ah + adv, bh + adv, idesc, first ? 0u : 1u);
+                            if (NTERMS == 3) {
+                                tc_mma_tf32(tmem_d, al + adv, bh + adv, idesc, 1);
+                                tc_mma_tf32(tmem_d, ah + adv, bl + adv, idesc, 1);
+                            }
                         }
+                        first = false;
                     }
-                    tc_commit(&empty[s]);      // stage reusable once these MMAs have read it
+                    if (CTAS == 2) tc_commit_pair(&empty[s]); else tc_commit(&empty[s]);      // stage reusable once these MMAs have read it
                 }
-                tc_commit(&acc_full[buf]);     // chunk complete (also releases the epilogue on a time-out)
+                if (CTAS == 2) tc_commit_pair(&acc_full[buf]); else tc_commit(&acc_full[buf]); // chunk complete (also releases the epilogue on a time-out)
             }
             if (!ok) atomicExch(status, SB_ERR_TIMEOUT);
         }
@@ -266,12 +345,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
             for (int g = 0; g < COLS_PER_WARP / 32; g++) {
                 uint32_t r[32];
                 tc_ld32(taddr + (uint32_t)(g * 32), r);
+                if (g == COLS_PER_WARP / 32 - 1) {
+                    // the buffer is in registers: hand it back to the MMA warp before the adds
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (CTAS == 2) mbar_arrive_cluster(mapa_u32(smem_u32(&acc_empty[buf]), 0));
+                        else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
+                    }
+                }
 #pragma unroll
                 for (int j = 0; j < 32; j++) accr[g * 32 + j] += __uint_as_float(r[j]);
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
         }
         if (!ok && lane == 0) atomicExch(status, SB_ERR_TIMEOUT);
         // The last chunk has arrived, so every MMA has finished reading the operand stages: their
@@ -286,36 +371,82 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
         }
         asm volatile("bar.sync 1, %0;" ::"n"(32 * TC_EPI_WARPS) : "memory");      // epilogue warps only
         if (ok) {
-            const bool vec = ((ldc & 3) == 0) && ((((uintptr_t)C) & 15) == 0);
+            // destination: the tile's place in C, or (a piece of a split tile) its own block of `partial`
+            float* dst = split ? partial + ((size_t)((tile_id - split_full) * split_s + piece) * CTAS + rank) * (size_t)(TC_BM * BN)
+                               : C + (size_t)m0 * ldc + n0;
+            const long ld = split ? (long)BN : ldc;
+            const int rows_valid = split ? TC_BM : M - m0, cols_valid = split ? BN : N - n0;
+            const int accf = split ? 0 : acc;
+            const bool vec = ((ld & 3) == 0) && ((((uintptr_t)dst) & 15) == 0);
             for (int r = ew; r < TC_BM; r += TC_EPI_WARPS) {
-                const int grow = m0 + r;
-                if (grow >= M) break;
+                if (r >= rows_valid) break;
                 const float* srow = stage + (size_t)r * SLD;
-                float* crow = C + (size_t)grow * ldc + n0;
+                float* crow = dst + (size_t)r * ld;
                 if (vec) {
 #pragma unroll
                     for (int h = 0; h < (BN + 127) / 128; h++) {
                         const int col = (h * 32 + lane) * 4;
-                        if (col < BN && n0 + col + 3 < N) {
+                        if (col < BN && col + 3 < cols_valid) {
                             float4 v = *(const float4*)(srow + col);
-                            if (acc) { float4 o = *(const float4*)(crow + col); v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+                            if (accf) { float4 o = *(const float4*)(crow + col); v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
                             *(float4*)(crow + col) = v;
                         } else if (col < BN) {
-                            for (int j = 0; j < 4; j++) if (n0 + col + j < N) crow[col + j] = acc ? crow[col + j] + srow[col + j] : srow[col + j];
+                            for (int j = 0; j < 4; j++) if (col + j < cols_valid) crow[col + j] = accf ? crow[col + j] + srow[col + j] : srow[col + j];
                         }
                     }
                 } else {
-                    for (int col = lane; col < BN && n0 + col < N; col += 32)
-                        crow[col] = acc ? crow[col] + srow[col] : srow[col];
+                    for (int col = lane; col < BN && col < cols_valid; col += 32)
+                        crow[col] = accf ? crow[col] + srow[col] : srow[col];
                 }
             }
         }
         tc_fence_before();
     }
     __syncthreads();
+    if (CTAS == 2) cluster_sync_all();          // neither CTA leaves while the other may still signal it or read its operands
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
+        if (CTAS == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
+        else           asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
+    }
+}
+
+// Adds the pieces of the split tiles into C in piece order.  One thread per four columns of one row
+// (the loads of a thread are independent, and a grid of many small CTAs keeps the latency hidden).
+static __global__ void __launch_bounds__(256) tc_splitk_fixup_kernel(const float* __restrict__ partial, float* __restrict__ C, long ldc,
+                                                                     int M, int N, int acc, int BN, int ctas, int split_full, int split_s,
+                                                                     int nblocks) {
+    const int bn4 = BN >> 2;
+    const long item = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int blk = (int)(item / (TC_BM * bn4)), i = (int)(item % (TC_BM * bn4));
+    if (blk >= nblocks) return;
+    const int t = blk / ctas, rank = blk % ctas;
+    const int tile_m = TC_BM * ctas;
+    const int tiles_m = (M + tile_m - 1) / tile_m, tiles_n = (N + BN - 1) / BN;
+    int m_tile, n_tile;
+    tc_raster(split_full + t, tiles_m, tiles_n, TC_GROUP_M / ctas, &m_tile, &n_tile);
+    const int m0 = m_tile * tile_m + rank * TC_BM, n0 = n_tile * BN;
+    const size_t block = (size_t)TC_BM * BN;
+    const float* p0 = partial + ((size_t)t * split_s * ctas + rank) * block;
+    const size_t piece_stride = (size_t)ctas * block;
+    const bool vec = ((ldc & 3) == 0) && ((((uintptr_t)C) & 15) == 0);
+    {
+        const int r = i / bn4, col = (i % bn4) * 4;
+        if (m0 + r >= M || n0 + col >= N) return;
+        float* crow = C + (size_t)(m0 + r) * ldc + n0 + col;
+        const bool whole = vec && n0 + col + 3 < N;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (acc) {
+            if (whole) v = *(const float4*)crow;
+            else { v.x = crow[0]; if (n0 + col + 1 < N) v.y = crow[1]; if (n0 + col + 2 < N) v.z = crow[2]; if (n0 + col + 3 < N) v.w = crow[3]; }
+        }
+        float4 o[8];
+#pragma unroll
+        for (int p = 0; p < 8; p++) if (p < split_s) o[p] = *(const float4*)(p0 + (size_t)p * piece_stride + (size_t)r * BN + col);
+#pragma unroll
+        for (int p = 0; p < 8; p++) if (p < split_s) { v.x += o[p].x; v.y += o[p].y; v.z += o[p].z; v.w += o[p].w; }
+        if (whole) *(float4*)crow = v;
+        else { crow[0] = v.x; if (n0 + col + 1 < N) crow[1] = v.y; if (n0 + col + 2 < N) crow[2] = v.z; if (n0 + col + 3 < N) crow[3] = v.w; }
     }
 }
 
@@ -415,34 +546,84 @@ static bool tc_make_map(CUtensorMap* m, const float* base, const TcOperand& op, 
     return true;
 }
 
-template <int BN, int BK, int NTERMS, int STAGES>
+template <int BN, int BK, int NTERMS, int STAGES, int CTAS = 1>
 static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
     CUtensorMap mAh, mAl, mBh, mBl;
-    if (!tc_make_map(&mAh, p.A.hi, p.A, p.K, BK, TC_BM) || !tc_make_map(&mBh, p.B.hi, p.B, p.K, BK, BN)) return false;
-    if (NTERMS == 3) { if (!tc_make_map(&mAl, p.A.lo, p.A, p.K, BK, TC_BM) || !tc_make_map(&mBl, p.B.lo, p.B, p.K, BK, BN)) return false; }
+    constexpr int BROWS = BN / CTAS;
+    if (!tc_make_map(&mAh, p.A.hi, p.A, p.K, BK, TC_BM) || !tc_make_map(&mBh, p.B.hi, p.B, p.K, BK, BROWS)) return false;
+    if (NTERMS == 3) { if (!tc_make_map(&mAl, p.A.lo, p.A, p.K, BK, TC_BM) || !tc_make_map(&mBl, p.B.lo, p.B, p.K, BK, BROWS)) return false; }
     else { mAl = mAh; mBl = mBh; }
-    constexpr int STAGE_BYTES = (NTERMS == 3 ? 2 : 1) * (TC_BM + BN) * BK * 4;
+    constexpr int STAGE_BYTES = (NTERMS == 3 ? 2 : 1) * (TC_BM + BROWS) * BK * 4;
     constexpr size_t tile_bytes = (size_t)TC_BM * (BN + 4) * 4;
     constexpr size_t ring_bytes = (size_t)STAGES * STAGE_BYTES;
     static_assert(tile_bytes <= ring_bytes, "the output tile is staged in the operand ring");
     size_t smem = ring_bytes + 1024 + 256;
-    auto kern = gemm_tc_kernel<BN, BK, NTERMS, STAGES>;
+    auto kern = gemm_tc_kernel<BN, BK, NTERMS, STAGES, CTAS>;
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
         attr_set = true;
     }
-    dim3 grid((unsigned)(((p.N + BN - 1) / BN) * ((p.M + TC_BM - 1) / TC_BM)), (unsigned)(p.nbatch > 0 ? p.nbatch : 1));
-    kern<<<grid, TC_THREADS, smem, (cudaStream_t)c->pub.stream>>>(mAh, mAl, mBh, mBl, p.C, p.ldc, p.c_batch_stride, p.M, p.N, p.K, p.acc,
-                                                                 p.causal, p.A.c2_base, p.A.c2_step, p.B.c2_base, p.B.c2_step,
-                                                                 (tc_swapped(p.A) ? 1 : 0) | (tc_swapped(p.B) ? 2 : 0), c->d_status);
+    const int tiles = ((p.N + BN - 1) / BN) * ((p.M + TC_BM * CTAS - 1) / (TC_BM * CTAS));
+    // tail split: cut the tiles of the last, partly filled wave into k pieces that fill it
+    int split_full = tiles, split_s = 1;
+    float* partial = nullptr;
+    if (c->gemm_tail_split && p.nbatch <= 1 && p.causal == TC_CAUSAL_NONE) {
+        const int slots = (c->pub.gpu_sm_count > 0 ? c->pub.gpu_sm_count : 148) / CTAS;
+        const int full = tiles / slots * slots, rem = tiles - full;
+        constexpr int KB_PER_CHUNK = TC_CHUNK_K / BK > 0 ? TC_CHUNK_K / BK : 1;
+        const int num_kb = (p.K + BK - 1) / BK;
+        // measured: a CTA's prologue and epilogue cost about as much as 160 floats of k, the fix-up pass as much again
+        const double ovh = 10.0 * 16 / BK / num_kb;
+        double best = rem > 0 ? 1.0 + ovh : 0.0;
+        for (int s = 2; s <= 8 && rem > 0; s++) {
+            const int per = ((num_kb + s - 1) / s + KB_PER_CHUNK - 1) / KB_PER_CHUNK * KB_PER_CHUNK;
+            if (per * (s - 1) >= num_kb || per * BK < 128) continue;      // an empty or very short piece
+            const int waves = (rem * s + slots - 1) / slots;
+            const double cost = waves * ((double)per / num_kb + ovh) + ovh;
+            if (cost < best - 0.05) { best = cost; split_s = s; }
+        }
+        if (split_s > 1) {
+            split_full = full;
+            partial = (float*)sb_gemm_stage(c, 4, (size_t)rem * split_s * CTAS * TC_BM * BN * sizeof(float));
+            if (!partial) return false;
+        }
+    }
+    const int grid_tiles = split_full + (tiles - split_full) * split_s;
+    dim3 grid((unsigned)(grid_tiles * CTAS), (unsigned)(p.nbatch > 0 ? p.nbatch : 1));
+    const int swap_mask = (tc_swapped(p.A) ? 1 : 0) | (tc_swapped(p.B) ? 2 : 0);
+    if (CTAS == 2) {
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof cfg);
+        cfg.gridDim = grid; cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = (cudaStream_t)c->pub.stream;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, kern, mAh, mAl, mBh, mBl, p.C, p.ldc, p.c_batch_stride, p.M, p.N, p.K, p.acc, p.causal,
+                               p.A.c2_base, p.A.c2_step, p.B.c2_base, p.B.c2_step, swap_mask, split_full, split_s, partial,
+                               c->d_status) != cudaSuccess) return false;
+    } else {
+        kern<<<grid, TC_THREADS, smem, (cudaStream_t)c->pub.stream>>>(mAh, mAl, mBh, mBl, p.C, p.ldc, p.c_batch_stride, p.M, p.N, p.K, p.acc,
+                                                                     p.causal, p.A.c2_base, p.A.c2_step, p.B.c2_base, p.B.c2_step,
+                                                                     swap_mask, split_full, split_s, partial, c->d_status);
+    }
     c->launches++;
+    if (split_s > 1) {
+        const int nblocks = (tiles - split_full) * CTAS;
+        const long items = (long)nblocks * TC_BM * (BN / 4);
+        tc_splitk_fixup_kernel<<<(unsigned)((items + 255) / 256), 256, 0, (cudaStream_t)c->pub.stream>>>(partial, p.C, p.ldc, p.M, p.N, p.acc, BN, CTAS,
+                                                                                                        split_full, split_s, nblocks);
+        c->launches++;
+    }
     return cudaGetLastError() == cudaSuccess;
 }
 
 // picks the tile width from N; nterms: 3 = FP32-accurate, 1 = TF32
 static bool tc_launch(sb_ctx_t* c, const TcProblem& p, int nterms) {
     if (!tc_load_encode()) return false;
+    if (c->gemm_pair && p.causal == TC_CAUSAL_NONE && p.nbatch <= 1 && p.N > 128 && p.M > 128)
+        return nterms == 3 ? tc_launch_t<256, 16, 3, 6, 2>(c, p) : tc_launch_t<256, 32, 1, 6, 2>(c, p);
     if (p.N > 128) return nterms == 3 ? tc_launch_t<256, 16, 3, 4>(c, p) : tc_launch_t<256, 32, 1, 4>(c, p);
     return nterms == 3 ? tc_launch_t<128, 16, 3, 6>(c, p) : tc_launch_t<128, 32, 1, 6>(c, p);
 }

@@ -202,9 +202,25 @@ __global__ void __launch_bounds__(RB_THREADS) rmsnorm_bwd_warp_kernel(const floa
             }
         }
     }
-    float4* pr = (float4*)(partial + (size_t)warp * cols);          // one partial row per warp of the grid
+    // the warps of the CTA add their partials in warp order in shared memory: one partial row per CTA
+    extern __shared__ float4 s_acc[];
+    const int wib = threadIdx.x >> 5;
+    for (int w = 0; w < RB_THREADS / 32; w++) {
+        if (wib == w) {
 #pragma unroll
-    for (int i = 0; i < NV; i++) { int j = lane + 32 * i; if (j < c4) pr[j] = acc[i]; }
+            for (int i = 0; i < NV; i++) {
+                int j = lane + 32 * i;
+                if (j < c4) {
+                    float4 a = acc[i];
+                    if (w > 0) { float4 o = s_acc[j]; a.x += o.x; a.y += o.y; a.z += o.z; a.w += o.w; }
+                    s_acc[j] = a;
+                }
+            }
+        }
+        __syncthreads();
+    }
+    float4* pr = (float4*)(partial + (size_t)blockIdx.x * cols);
+    for (int j = threadIdx.x; j < c4; j += blockDim.x) pr[j] = s_acc[j];
 }
 
 // dscale[c] += sum over blocks (fixed order) of partial[b][c]
@@ -479,17 +495,17 @@ void sb_rmsnorm_backward(sb_ctx_t* c, const float* x, const float* w, const floa
     if (cols > RB_THREADS * 4 * RN_MAX_SWEEP || (cols % 4 != 0 && cols > RB_THREADS * RN_MAX_SWEEP * 4)) { sb_set_status(c, SB_ERR_SIZE); return; }
     int vec = (cols % 4 == 0) && aligned16(x) && aligned16(w) && aligned16(dy) && aligned16(dx_out) && (!resid || aligned16(resid));
     if (vec && cols <= 2048 && rows >= 64) {
-        // warp per row, rows kept in registers; one dscale partial per warp of the grid, summed in warp order
+        // warp per row, rows kept in registers; one dscale partial per CTA, summed in CTA order
         int wgrid = (rows + 7) / 8; if (wgrid > sm_count(c)) wgrid = sm_count(c);
-        int nwarps = wgrid * (RB_THREADS / 32);
-        float* partial = (float*)sb_scratch(c, (size_t)nwarps * cols * sizeof(float));
+        float* partial = (float*)sb_scratch(c, (size_t)wgrid * cols * sizeof(float));
         if (!partial) return;
         cudaStream_t st = (cudaStream_t)c->pub.stream;
+        size_t sm = (size_t)cols * sizeof(float);
         int tk = sb_tick_begin(c, SB_CLS_NORM_BWD);
-        if (cols <= 512)       rmsnorm_bwd_warp_kernel<4><<<wgrid, RB_THREADS, 0, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
-        else if (cols <= 1024) rmsnorm_bwd_warp_kernel<8><<<wgrid, RB_THREADS, 0, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
-        else                   rmsnorm_bwd_warp_kernel<16><<<wgrid, RB_THREADS, 0, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
-        colsum_partials_kernel<<<(cols + 255) / 256, 256, 0, st>>>(partial, dscale, nwarps, cols);
+        if (cols <= 512)       rmsnorm_bwd_warp_kernel<4><<<wgrid, RB_THREADS, sm, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
+        else if (cols <= 1024) rmsnorm_bwd_warp_kernel<8><<<wgrid, RB_THREADS, sm, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
+        else                   rmsnorm_bwd_warp_kernel<16><<<wgrid, RB_THREADS, sm, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
+        colsum_partials_kernel<<<(cols + 255) / 256, 256, 0, st>>>(partial, dscale, wgrid, cols);
         sb_tick_end(c, tk, 0.0, (resid ? 16.0 : 12.0) * rows * cols);
         c->launches += 2;
         return;

@@ -53,6 +53,8 @@ typedef struct sb_ctx {
     int status;                      /* last host-side status */
     int* d_status;                   /* device status word (bounds checks, bounded waits) */
     int gemm_mode;                   /* SB_GEMM_* (use_bf16 in pub overrides to BF16) */
+    int gemm_tail_split;             /* 1: tiles of the last partial wave are cut into k pieces */
+    int gemm_pair;                   /* 1: plain GEMMs run on CTA pairs (cta_group::2), 0: one CTA per tile */
     int lora_exact;                  /* 0: reference behaviour (adapter dX term left out), 1: full chain rule */
     float grad_clip;                 /* 0 = off (the reference has none) */
     cuda_profiler_t* profiler;
@@ -91,7 +93,7 @@ typedef struct sb_ctx {
     /* scratch shared by kernels (partials of deterministic reductions, sort tables) */
     void* scratch; size_t scratch_bytes;
     /* operand staging of the tensor-core GEMM (hi/lo, transposed copies) */
-    void* gemm_stage[4]; size_t gemm_stage_bytes[4];
+    void* gemm_stage[5]; size_t gemm_stage_bytes[5];
     /* rope cos/sin table */
     float* rope_tab; int rope_tab_pos, rope_tab_hd; float rope_tab_theta;
 

@@ -735,7 +735,7 @@ void cuda_train_free(cuda_train_context_t* ctx) {
     if (c->tokens) cudaFree(c->tokens);
     if (c->seq_starts) cudaFree(c->seq_starts);
     if (c->scratch) cudaFree(c->scratch);
-    for (int i = 0; i < 4; i++) if (c->gemm_stage[i]) cudaFree(c->gemm_stage[i]);
+    for (int i = 0; i < 5; i++) if (c->gemm_stage[i]) cudaFree(c->gemm_stage[i]);
     if (c->rope_tab) cudaFree(c->rope_tab);
     if (c->d_status) cudaFree(c->d_status);
     if (c->d_loss) cudaFree(c->d_loss);

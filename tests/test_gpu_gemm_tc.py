@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 BOUND = {0: 2e-6, 1: 2e-3}
 
 SHAPES = [(128, 256, 64), (256, 128, 32), (130, 257, 96), (384, 512, 1024), (100, 200, 4096), (1000, 1000, 40),
-          (129, 33, 512), (2048, 64, 256)]
+          (129, 33, 512), (2048, 64, 256), (300, 300, 64), (257, 512, 160), (512, 384, 2048)]
 
 
 @pytest.fixture(scope="module")
@@ -24,10 +24,14 @@ def ctx():
     c.close()
 
 
+@pytest.mark.parametrize("pair", [1, 0])
 @pytest.mark.parametrize("mode", [0, 1])
 @pytest.mark.parametrize("tA,tB,acc", [(0, 1, 0), (0, 0, 0), (1, 0, 1), (0, 1, 1)])
 @pytest.mark.parametrize("M,N,K", SHAPES)
-def test_tc_gemm_matches_oracle(ctx, M, N, K, tA, tB, acc, mode):
+def test_tc_gemm_matches_oracle(ctx, M, N, K, tA, tB, acc, mode, pair):
+    """pair = 1: tiles of 256 rows on CTA pairs (cta_group::2) where the shape allows; 0: one CTA per tile."""
+    if pair and (M <= 128 or N <= 128):
+        pytest.skip("shape runs on single CTAs either way")
     r = np.random.default_rng(M + 3 * N + 7 * K + tA + 2 * tB)
     A = r.standard_normal((K, M) if tA else (M, K)).astype(np.float32)
     B = r.standard_normal((N, K) if tB else (K, N)).astype(np.float32)
@@ -36,10 +40,12 @@ def test_tc_gemm_matches_oracle(ctx, M, N, K, tA, tB, acc, mode):
     O.lib().ref_matmul(A, B, ref, M, N, K, tA, tB, acc)
     a, b, c = ctx.upload(A), ctx.upload(B), ctx.upload(C0)
     ctx.set_gemm_mode(mode)
+    ctx.set_gemm_pair(pair)
     n0 = ctx.launches()
     ctx.lib.cuda_train_matmul_transpose(ctx.h, a.b, b.b, c.b, M, N, K, tA, tB, acc)
     out = c.numpy(shape=(M, N))
     ctx.set_gemm_mode(0)
+    ctx.set_gemm_pair(1)
     ctx.check()
     assert ctx.launches() > n0
     assert rel_l2(out, ref) < BOUND[mode], rel_l2(out, ref)
@@ -61,4 +67,11 @@ def test_tc_gemm_long_k_and_reproducible(ctx):
     e = rel_l2(o1, ref)
     print("FP32-accurate tensor-core GEMM, K=16384: rel-L2 vs FP64 accumulate =", e)
     assert e < 2e-6 and np.array_equal(o1, o2)
+    # the same product with whole tiles only (no k pieces in the last wave) meets the same bound
+    ctx.set_gemm_tail_split(0)
+    ctx.lib.cuda_train_matmul_transpose(ctx.h, a.b, b.b, c2.b, M, N, K, 0, 1, 0)
+    o3 = c2.numpy(shape=(M, N))
+    ctx.set_gemm_tail_split(1)
+    ctx.check()
+    assert rel_l2(o3, ref) < 2e-6
     ctx.release(a, b, c, c2)

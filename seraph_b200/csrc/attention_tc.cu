@@ -128,18 +128,18 @@ static bool at_eligible(sb_ctx_t* c, int T, int Hq, int Hkv, int hd) {
 static TcOperand op_tokens(const float* hi, const float* lo, int tok0, int S, int row_pitch, int nheads, int hd, int slot_base, int slot_step) {
     TcOperand o;
     o.hi = hi + (size_t)tok0 * row_pitch; o.lo = lo ? lo + (size_t)tok0 * row_pitch : nullptr;
-    o.rows = S; o.pitch = row_pitch; o.c2_dim = nheads; o.c2_stride = hd; o.c2_base = slot_base; o.c2_step = slot_step;
+    o.mn = 0; o.rows = S; o.pitch = row_pitch; o.c2_dim = nheads; o.c2_stride = hd; o.c2_base = slot_base; o.c2_step = slot_step;
     return o;
 }
 static TcOperand op_scratch(const float* hi, const float* lo, int S, int Sp, int nb) {
     TcOperand o;
-    o.hi = hi; o.lo = lo; o.rows = S; o.pitch = Sp; o.c2_dim = nb; o.c2_stride = (long)Sp * Sp; o.c2_base = 0; o.c2_step = 1;
+    o.hi = hi; o.lo = lo; o.mn = 0; o.rows = S; o.pitch = Sp; o.c2_dim = nb; o.c2_stride = (long)Sp * Sp; o.c2_base = 0; o.c2_step = 1;
     return o;
 }
 // transposed per-sequence copy X^T [nheads*hd rows][Sp]: rows of one head are hd consecutive rows
 static TcOperand op_transposed(const float* hi, const float* lo, int S, int Sp, int nheads, int hd, int slot_base, int slot_step) {
     TcOperand o;
-    o.hi = hi; o.lo = lo; o.rows = hd; o.pitch = Sp; o.c2_dim = nheads; o.c2_stride = (long)hd * Sp; o.c2_base = slot_base; o.c2_step = slot_step;
+    o.hi = hi; o.lo = lo; o.mn = 0; o.rows = hd; o.pitch = Sp; o.c2_dim = nheads; o.c2_stride = (long)hd * Sp; o.c2_base = slot_base; o.c2_step = slot_step;
     return o;
 }
 

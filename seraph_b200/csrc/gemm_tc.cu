@@ -1,18 +1,21 @@
 // gemm_tc.cu - the reference's matmul entry points on the tcgen05 kernel of gemm_tc.cuh.
 //
 // The reference's three layouts (src/cuda_train_context.cu:2645-2709: NN, TN, NT, optional
-// accumulate) are brought to the kernel's one form, C (+)= A^[M,K] B^[N,K]^T with both
-// operands K-major, by an operand-preparation pass that also writes what the FP32-accurate
-// mode needs: an operand that already is K-major is used in place (only its lo part is
-// written, 8 bytes per element); an operand that is not gets a transposed hi copy and a
-// transposed lo copy (12 bytes per element).
+// accumulate) map onto C (+)= A^[M,K] B^[N,K]^T:
+//   * large, 16-byte-aligned products go to the CTA-pair kernel as they are: it reads either
+//     operand in either layout and makes the lo parts of the FP32-accurate mode itself, so
+//     nothing is prepared in HBM;
+//   * the rest are brought to the single-CTA kernel's one form (both operands K-major) by an
+//     operand-preparation pass: an operand that already is K-major is used in place (only its lo
+//     part is written, 8 bytes per element); an operand that is not gets a transposed hi copy and
+//     a transposed lo copy (12 bytes per element).
 #include <stdio.h>
 #include "gemm_tc.cuh"
 
 // Bring one operand to K-major [rows, K].  `kmajor`: the caller's array already is [rows, K] row-major.
 static bool prep_operand(sb_ctx_t* c, const float* src, int rows, int K, bool kmajor, bool want_lo, int slot, TcOperand* op) {
     cudaStream_t s = (cudaStream_t)c->pub.stream;
-    op->rows = rows; op->c2_dim = 1; op->c2_stride = 0; op->c2_base = 0; op->c2_step = 0; op->lo = nullptr;
+    op->mn = 0; op->rows = rows; op->c2_dim = 1; op->c2_stride = 0; op->c2_base = 0; op->c2_step = 0; op->lo = nullptr;
     if (kmajor) {
         op->hi = src; op->pitch = K;
         if (want_lo) {
@@ -49,12 +52,23 @@ extern "C" int sb_gemm_tc(sb_ctx_t* c, const float* A, const float* B, float* C,
     if ((a_kmajor || b_kmajor) && (K & 3)) return 1;                     // in-place K-major rows need a 16-byte pitch
     const bool x3 = (mode == SB_GEMM_FP32X3);
     TcProblem p;
+    p.C = C; p.ldc = N; p.c_batch_stride = 0; p.M = M; p.N = N; p.K = K; p.acc = acc; p.nbatch = 1; p.causal = TC_CAUSAL_NONE;
+    // direct path: the pair kernel on the caller's arrays (rows of either layout must be 16-byte multiples)
+    if (c->gemm_pair && M > 128 && N > 128 && (a_kmajor ? (K & 3) == 0 : (M & 3) == 0) && (b_kmajor ? (K & 3) == 0 : (N & 3) == 0)) {
+        p.A.hi = A; p.A.lo = nullptr; p.A.rows = M; p.A.mn = a_kmajor ? 0 : 1; p.A.pitch = a_kmajor ? K : M;
+        p.B.hi = B; p.B.lo = nullptr; p.B.rows = N; p.B.mn = b_kmajor ? 0 : 1; p.B.pitch = b_kmajor ? K : N;
+        p.A.c2_dim = p.B.c2_dim = 1; p.A.c2_stride = p.B.c2_stride = 0; p.A.c2_base = p.B.c2_base = 0; p.A.c2_step = p.B.c2_step = 0;
+        int tg = sb_tick_begin(c, SB_CLS_GEMM);
+        bool ok = tc_launch(c, p, x3 ? 3 : 1);
+        sb_tick_end(c, tg, 2.0 * M * N * K, 4.0 * ((double)M * K + (double)N * K + (double)M * N * (acc ? 2 : 1)));
+        if (!ok) { sb_set_status(c, SB_ERR_CUDA); return 1; }
+        return 0;
+    }
     int tp = sb_tick_begin(c, SB_CLS_GEMM_PREP);
     if (!prep_operand(c, A, M, K, a_kmajor, x3, 0, &p.A)) return 1;
     if (!prep_operand(c, B, N, K, b_kmajor, x3, 1, &p.B)) return 1;
     double prep_bytes = (double)M * K * (a_kmajor ? (x3 ? 8 : 0) : (x3 ? 12 : 8)) + (double)N * K * (b_kmajor ? (x3 ? 8 : 0) : (x3 ? 12 : 8));
     sb_tick_end(c, tp, 0.0, prep_bytes);
-    p.C = C; p.ldc = N; p.c_batch_stride = 0; p.M = M; p.N = N; p.K = K; p.acc = acc; p.nbatch = 1; p.causal = TC_CAUSAL_NONE;
     int tg = sb_tick_begin(c, SB_CLS_GEMM);
     bool ok = tc_launch(c, p, x3 ? 3 : 1);
     sb_tick_end(c, tg, 2.0 * M * N * K, 4.0 * ((double)M * K + (double)N * K + (double)M * N * (acc ? 2 : 1)));

@@ -45,6 +45,7 @@
 #define TC_BM 128
 #define TC_EPI_WARPS 8
 #define TC_THREADS (64 + 32 * TC_EPI_WARPS)
+#define TC_CONV_WARPS 2                   // converter warps of the CTA-pair kernel (after the epilogue warps)
 #define TC_GROUP_M 16
 #define TC_CHUNK_K 32
 #define TC_SPIN_CYCLES 4000000000ll      // ~2 s at 2 GHz: far beyond any legitimate wait
@@ -52,9 +53,10 @@
 enum { TC_CAUSAL_NONE = 0, TC_CAUSAL_SKIP_UPPER, TC_CAUSAL_SKIP_LOWER, TC_CAUSAL_K_UPTO_M, TC_CAUSAL_K_FROM_M };
 
 struct TcOperand {
-    const float* hi; const float* lo;   // lo may be NULL when nterms == 1
+    const float* hi; const float* lo;   // lo may be NULL when nterms == 1, or when the kernel makes it (CTA pairs)
     int rows;                            // M or N
-    long pitch;                          // floats between rows
+    long pitch;                          // floats between rows (mn: between k-rows)
+    int mn;                              // 1: the array is [K, rows], rows contiguous (CTA-pair kernel only)
     int c2_dim; long c2_stride;          // third tensor-map dimension (floats); c2_dim = 1 for a plain matrix
     int c2_base, c2_step;                // slot of batch b = c2_base + b*c2_step
 };
@@ -118,6 +120,22 @@ __device__ __forceinline__ void tc_mma_tf32_pair(uint32_t tmem_d, uint64_t adesc
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
 }
+template <bool PAIRBAR>
+__device__ __forceinline__ void tc_load_box(void* dst, const CUtensorMap* map, uint64_t* bar, uint32_t bar_cluster, int c0, int c1, int c2) {
+    if (PAIRBAR) tma_load_3d_pair(dst, map, bar_cluster, c0, c1, c2); else tma_load_3d(dst, map, bar, c0, c1, c2);
+}
+// one operand tile of a stage: K-major = one box {BK, rows}; MN-major = four boxes {32 rows, BK} of BK*128 bytes each
+template <bool PAIRBAR, bool MN, int BK>
+__device__ __forceinline__ void tc_load_operand(uint8_t* dst, const CUtensorMap* map, uint64_t* bar, uint32_t bar_cluster,
+                                                int kb, int row0, int c2, bool swapped) {
+    if (MN) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) tc_load_box<PAIRBAR>(dst + j * BK * 128, map, bar, bar_cluster, row0 + 32 * j, kb * BK, 0);
+    } else {
+        // a map whose slot stride is smaller than its row pitch is encoded as {k, slot, row}
+        tc_load_box<PAIRBAR>(dst, map, bar, bar_cluster, kb * BK, swapped ? c2 : row0, swapped ? row0 : c2);
+    }
+}
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
@@ -164,20 +182,50 @@ __device__ __forceinline__ void tc_raster(int tile_id, int tiles_m, int tiles_n,
     *n_tile = in_g / gsize;
 }
 
+// shared-memory matrix descriptor, MN-major 32-bit operand: atoms of 4 k-rows x 128 bytes (32 floats of M or N) in
+// the 128-byte swizzle with 32-byte granularity (the only MN-major form for TF32; TMA writes it as
+// SWIZZLE_128B_ATOM_32B); the next 4 k-rows follow 512 bytes later, the atoms of the next 32 rows BK*128 bytes later
+template <int BK>
+__device__ __forceinline__ uint64_t make_mnmajor_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
+    d |= (uint64_t)(((BK * 128) >> 4) & 0x3fff) << 16;           // leading byte offset: next 32 rows
+    d |= (uint64_t)((512 >> 4) & 0x3fff) << 32;                  // stride byte offset: next 4 k-rows
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)1 << 61;                                      // 128-byte swizzle, 32-byte base
+    return d;
+}
+// lo part of the hi/lo split: x minus the 19 leading bits the tensor core reads, plus half a TF32 ulp
+// of the result.  The tensor core truncates the word it is given, so the half ulp turns its truncation
+// into rounding to nearest and the cross terms carry no one-sided error.
+__device__ __forceinline__ float tf32_lo(float x) {
+    float hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
+    float lo = x - hi;
+    return __uint_as_float(__float_as_uint(lo) + 0x00001000u);
+}
+
 // --------------------------------------------------------------------------- the kernel
 // CTAS = 2: the CTA pair of a cluster computes a 256 x BN tile with cta_group::2 MMAs issued by the
 // pair's rank-0 CTA.  Each CTA loads its own 128 rows of A and BN/2 rows of B, so per flop it takes a
 // third less from L2 and the tensor core reads a third less shared memory than two independent CTAs
 // would; each CTA's tensor memory holds its 128 rows of the tile and its own epilogue warps drain them.
-// Plain GEMMs only (no causal modes, one batch).
+// Plain GEMMs only (no causal modes, one batch).  In this form the kernel takes the caller's FP32
+// matrices as they are:
+//   * an operand stored [K, rows] (rows contiguous, "MN-major") is fetched in boxes of 32 floats x BK
+//     k-rows (128-byte swizzle of 32-byte units) and read by the MMA through an MN-major descriptor, so no
+//     transposed copy is made;
+//   * the lo parts of the FP32-accurate mode are computed in the kernel: two converter warps per CTA
+//     read each landed hi stage, write x - trunc_tf32(x) (rounded to nearest at TF32 precision) beside
+//     it at the same offsets - the layout, whatever its swizzle, carries over - and release the stage to
+//     the MMA warp.  TMA moves 4 bytes per operand element instead of 8 and nothing is prepared in HBM.
 //
 // Tail split: the tiles beyond the last full wave (tile ids >= split_full) are each cut into split_s
 // pieces of the k range, one CTA (pair) per piece, so the last wave fills the machine with short
 // pieces instead of leaving most SMs idle behind a few whole tiles.  A piece writes its 128 x BN
 // block to `partial`; tc_splitk_fixup_kernel adds the pieces in piece order, so the result does not
 // depend on timing.
-template <int BN, int BK, int NTERMS, int STAGES, int CTAS>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+template <int BN, int BK, int NTERMS, int STAGES, int CTAS, bool AMN, bool BMN>
+__global__ void __launch_bounds__(TC_THREADS + 32 * TC_CONV_WARPS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
                float* __restrict__ Cbase, long ldc, long c_batch_stride, int M, int N, int K, int acc, int causal,
@@ -187,7 +235,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
     constexpr int BROWS = BN / CTAS;                             // B rows this CTA loads
     constexpr int TILE_M = TC_BM * CTAS;
     constexpr int A_BYTES = TC_BM * BK * 4, B_BYTES = BROWS * BK * 4;
-    constexpr int STAGE_BYTES = (NTERMS == 3 ? 2 : 1) * (A_BYTES + B_BYTES);
+    constexpr int HI_BYTES = A_BYTES + B_BYTES;
+    constexpr int STAGE_BYTES = (NTERMS == 3 ? 2 : 1) * HI_BYTES;
+    constexpr bool CONV = (CTAS == 2 && NTERMS == 3);            // lo parts made in the kernel
+    static_assert(CTAS == 2 || (!AMN && !BMN), "MN-major operands: CTA-pair kernel only");
+    static_assert(!(AMN || BMN) || BROWS == 128, "an MN-major tile is four boxes of 32 rows");
     constexpr uint32_t TMEM_COLS = 2 * BN;                       // two accumulator buffers
     constexpr int KB_PER_CHUNK = TC_CHUNK_K / BK;
     constexpr int COLS_PER_WARP = BN / (TC_EPI_WARPS / 4);       // 128 or 64 register accumulators per epilogue thread
@@ -197,7 +249,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;          // [2] MMA -> epilogue
     uint64_t* acc_empty = acc_full + 2;           // [2] epilogue -> MMA
-    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    uint64_t* conv = acc_empty + 2;               // [STAGES] converter warps -> MMA (leader's copy is the one used)
+    uint32_t* tmem_slot = (uint32_t*)(conv + STAGES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int batch = blockIdx.y;
@@ -232,6 +285,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], TC_EPI_WARPS * CTAS); }
+        if (CONV) for (int s = 0; s < STAGES; s++) mbar_init(&conv[s], TC_CONV_WARPS * CTAS);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -258,24 +312,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
                 ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1);
                 if (!ok) break;
                 uint8_t* st = smem + s * STAGE_BYTES;
-                if (leader) mbar_expect_tx(&full[s], STAGE_BYTES * CTAS);      // the pair's bytes all land on the leader's barrier
-                // a map whose slot stride is smaller than its row pitch is encoded as {k, slot, row}
-                const int a1 = (swap_mask & 1) ? a_c2 : m0, a2 = (swap_mask & 1) ? m0 : a_c2;
-                const int b1 = (swap_mask & 2) ? b_c2 : nb0, b2 = (swap_mask & 2) ? nb0 : b_c2;
-                if (CTAS == 2) {
+                const bool swa = (swap_mask & 1) != 0, swb = (swap_mask & 2) != 0;
+                if (CONV) {
+                    // each CTA's hi tiles land on its own barrier; its converter warps take it from there
+                    mbar_expect_tx(&full[s], HI_BYTES);
+                    tc_load_operand<false, AMN, BK>(st, &tmAh, &full[s], 0, kb, m0, a_c2, swa);
+                    tc_load_operand<false, BMN, BK>(st + A_BYTES, &tmBh, &full[s], 0, kb, nb0, b_c2, swb);
+                } else if (CTAS == 2) {
+                    if (leader) mbar_expect_tx(&full[s], STAGE_BYTES * CTAS);      // the pair's bytes all land on the leader's barrier
                     const uint32_t fb = mapa_u32(smem_u32(&full[s]), 0);
-                    tma_load_3d_pair(st, &tmAh, fb, kb * BK, a1, a2);
-                    tma_load_3d_pair(st + A_BYTES, &tmBh, fb, kb * BK, b1, b2);
-                    if (NTERMS == 3) {
-                        tma_load_3d_pair(st + A_BYTES + B_BYTES, &tmAl, fb, kb * BK, a1, a2);
-                        tma_load_3d_pair(st + 2 * A_BYTES + B_BYTES, &tmBl, fb, kb * BK, b1, b2);
-                    }
+                    tc_load_operand<true, AMN, BK>(st, &tmAh, nullptr, fb, kb, m0, a_c2, swa);
+                    tc_load_operand<true, BMN, BK>(st + A_BYTES, &tmBh, nullptr, fb, kb, nb0, b_c2, swb);
                 } else {
-                    tma_load_3d(st, &tmAh, &full[s], kb * BK, a1, a2);
-                    tma_load_3d(st + A_BYTES, &tmBh, &full[s], kb * BK, b1, b2);
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    tc_load_operand<false, false, BK>(st, &tmAh, &full[s], 0, kb, m0, a_c2, swa);
+                    tc_load_operand<false, false, BK>(st + A_BYTES, &tmBh, &full[s], 0, kb, nb0, b_c2, swb);
                     if (NTERMS == 3) {
-                        tma_load_3d(st + A_BYTES + B_BYTES, &tmAl, &full[s], kb * BK, a1, a2);
-                        tma_load_3d(st + 2 * A_BYTES + B_BYTES, &tmBl, &full[s], kb * BK, b1, b2);
+                        tc_load_operand<false, false, BK>(st + HI_BYTES, &tmAl, &full[s], 0, kb, m0, a_c2, swa);
+                        tc_load_operand<false, false, BK>(st + HI_BYTES + A_BYTES, &tmBl, &full[s], 0, kb, nb0, b_c2, swb);
                     }
                 }
             }
@@ -285,7 +339,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
         // ---------------- MMA issuer ----------------
         if (leader && elect_one()) {
             // instruction descriptor: D = F32, A = B = TF32, both K-major, N and M of the tile
-            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((AMN ? 1u : 0u) << 15) | ((BMN ? 1u : 0u) << 16) |
+                                   ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
             int it = 0;
             for (int ch = 0; ch < num_chunks && ok; ch++) {
                 const int buf = ch & 1;
@@ -297,26 +352,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
                 bool first = true;
                 for (; it < it_end && ok; it++) {
                     const int s = it % STAGES;
-                    ok = mbar_wait(&full[s], (it / STAGES) & 1);
+                    ok = mbar_wait(CONV ? &conv[s] : &full[s], (it / STAGES) & 1);
                     if (!ok) break;
                     tc_fence_after();
-                    uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-                    uint64_t ah = make_kmajor_desc<SWZ>(sa), bh = make_kmajor_desc<SWZ>(sa + A_BYTES);
-                    uint64_t al = make_kmajor_desc<SWZ>(sa + A_BYTES + B_BYTES), bl = make_kmajor_desc<SWZ>(sa + 2 * A_BYTES + B_BYTES);
+                    const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+                    const uint64_t ah = AMN ? make_mnmajor_desc<BK>(sa) : make_kmajor_desc<SWZ>(sa);
+                    const uint64_t bh = BMN ? make_mnmajor_desc<BK>(sa + A_BYTES) : make_kmajor_desc<SWZ>(sa + A_BYTES);
+                    const uint64_t al = AMN ? make_mnmajor_desc<BK>(sa + HI_BYTES) : make_kmajor_desc<SWZ>(sa + HI_BYTES);
+                    const uint64_t bl = BMN ? make_mnmajor_desc<BK>(sa + HI_BYTES + A_BYTES) : make_kmajor_desc<SWZ>(sa + HI_BYTES + A_BYTES);
 #pragma unroll
                     for (int k = 0; k < BK / 8; k++) {
-                        uint64_t adv = (uint64_t)(k * 2);             // 8 floats = 32 bytes, in 16-byte units
+                        // 8 floats of k, in 16-byte units: 32 bytes along a K-major row, 8 k-rows of 128 bytes in an MN-major tile
+                        const uint64_t adva = (uint64_t)(AMN ? k * 64 : k * 2), advb = (uint64_t)(BMN ? k * 64 : k * 2);
                         if (CTAS == 2) {
-                            tc_mma_tf32_pair(tmem_d, ah + adv, bh + adv, idesc, first ? 0u : 1u);
+                            tc_mma_tf32_pair(tmem_d, ah + adva, bh + advb, idesc, first ? 0u : 1u);
                             if (NTERMS == 3) {
-                                tc_mma_tf32_pair(tmem_d, al + adv, bh + adv, idesc, 1);
-                                tc_mma_tf32_pair(tmem_d, ah + adv, bl + adv, idesc, 1);
+                                tc_mma_tf32_pair(tmem_d, al + adva, bh + advb, idesc, 1);
+                                tc_mma_tf32_pair(tmem_d, ah + adva, bl + advb, idesc, 1);
                             }
                         } else {
-                            tc_mma_tf32(tmem_d, ah + adv, bh + adv, idesc, first ? 0u : 1u);
+                            tc_mma_tf32(tmem_d, ah + adva, bh + advb, idesc, first ? 0u : 1u);
                             if (NTERMS == 3) {
-                                tc_mma_tf32(tmem_d, al + adv, bh + adv, idesc, 1);
-                                tc_mma_tf32(tmem_d, ah + adv, bl + adv, idesc, 1);
+                                tc_mma_tf32(tmem_d, al + adva, bh + advb, idesc, 1);
+                                tc_mma_tf32(tmem_d, ah + adva, bl + advb, idesc, 1);
                             }
                         }
                         first = false;
@@ -326,6 +384,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
                 if (CTAS == 2) tc_commit_pair(&acc_full[buf]); else tc_commit(&acc_full[buf]); // chunk complete (also releases the epilogue on a time-out)
             }
             if (!ok) atomicExch(status, SB_ERR_TIMEOUT);
+        }
+    } else if (warp >= 2 + TC_EPI_WARPS) {
+        // ---------------- converter (CTA-pair FP32-accurate kernel): lo = x - trunc_tf32(x) beside each landed hi stage ----------------
+        if (CONV) {
+            const int cw = warp - (2 + TC_EPI_WARPS);
+            constexpr int N4 = HI_BYTES / 16;
+            constexpr int PER = N4 / (32 * TC_CONV_WARPS);
+            static_assert(N4 % (32 * TC_CONV_WARPS) == 0 && PER % 8 == 0, "stage size against the converter's unroll");
+            const uint32_t cb_base = mapa_u32(smem_u32(&conv[0]), 0);
+            for (int it = 0; it < num_kb && ok; it++) {
+                const int s = it % STAGES;
+                ok = mbar_wait(&full[s], (it / STAGES) & 1);
+                if (!ok) break;
+                const float4* src = (const float4*)(smem + s * STAGE_BYTES);
+                float4* dst = (float4*)(smem + s * STAGE_BYTES + HI_BYTES);
+#pragma unroll
+                for (int b = 0; b < PER; b += 8) {
+                    float4 v[8];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) v[j] = src[(cw * PER + b + j) * 32 + lane];
+#pragma unroll
+                    for (int j = 0; j < 8; j++)
+                        dst[(cw * PER + b + j) * 32 + lane] = make_float4(tf32_lo(v[j].x), tf32_lo(v[j].y), tf32_lo(v[j].z), tf32_lo(v[j].w));
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the MMA reads these writes through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(cb_base + (uint32_t)(s * 8));
+            }
+            if (!ok && lane == 0) atomicExch(status, SB_ERR_TIMEOUT);
         }
     } else {
         // ---------------- epilogue: TMEM chunks -> register accumulators -> shared -> global ----------------
@@ -451,16 +538,6 @@ static __global__ void __launch_bounds__(256) tc_splitk_fixup_kernel(const float
 }
 
 // --------------------------------------------------------------------------- operand preparation kernels
-// lo part of the hi/lo split: x minus the 19 leading bits the tensor core reads.  The result is
-// rounded to nearest at TF32 precision here, so the tensor core's own truncation of it is exact
-// and the cross terms carry no one-sided error.
-__device__ __forceinline__ float tf32_lo(float x) {
-    float hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
-    float lo = x - hi;
-    uint32_t u = __float_as_uint(lo);
-    u += 0x00000fffu + ((u >> 13) & 1u);
-    return __uint_as_float(u & 0xffffe000u);
-}
 // lo[i] = x[i] - tf32_trunc(x[i]);  8 bytes per element
 static __global__ void __launch_bounds__(256) split_lo_kernel(const float* __restrict__ x, float* __restrict__ lo, size_t n4) {
     size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
@@ -511,7 +588,7 @@ static inline bool tc_swapped(const TcOperand& op) { return op.c2_dim > 1 && op.
 // Encoding a tensor map costs a few microseconds on the host and a training step re-issues the same
 // (pointer, shape) combinations every layer and every step, so encoded maps are kept in a small
 // direct-mapped cache keyed by everything that goes into the encoding.
-struct TcMapKey { const float* base; long pitch, c2_stride; int K, rows, c2_dim, BK, box_rows; };
+struct TcMapKey { const float* base; long pitch, c2_stride; int K, rows, c2_dim, BK, box_rows, mn; };
 struct TcMapEntry { TcMapKey key; CUtensorMap map; bool valid; };
 #define TC_MAP_CACHE 8192
 static TcMapEntry* g_tc_map_cache = nullptr;
@@ -521,7 +598,7 @@ static bool tc_make_map(CUtensorMap* m, const float* base, const TcOperand& op, 
     TcMapKey key;
     memset(&key, 0, sizeof key);
     key.base = base; key.pitch = op.pitch; key.c2_stride = op.c2_dim > 1 ? op.c2_stride : 0; key.K = K; key.rows = op.rows;
-    key.c2_dim = op.c2_dim > 1 ? op.c2_dim : 1; key.BK = BK; key.box_rows = box_rows;
+    key.c2_dim = op.c2_dim > 1 ? op.c2_dim : 1; key.BK = BK; key.box_rows = box_rows; key.mn = op.mn;
     if (!g_tc_map_cache) g_tc_map_cache = (TcMapEntry*)calloc(TC_MAP_CACHE, sizeof(TcMapEntry));
     TcMapEntry* e = nullptr;
     if (g_tc_map_cache) {
@@ -530,6 +607,18 @@ static bool tc_make_map(CUtensorMap* m, const float* base, const TcOperand& op, 
         for (size_t i = 0; i < sizeof key; i++) { h ^= kb[i]; h *= 1099511628211ull; }
         e = &g_tc_map_cache[h % TC_MAP_CACHE];
         if (e->valid && memcmp(&e->key, &key, sizeof key) == 0) { *m = e->map; return true; }
+    }
+    if (op.mn) {
+        // the array is [K, rows] with rows contiguous: {rows, K, 1}, boxes of 32 floats x BK k-rows, 128-byte swizzle of 32-byte units
+        cuuint64_t dims[3] = {(cuuint64_t)op.rows, (cuuint64_t)K, 1};
+        cuuint64_t strides[2] = {(cuuint64_t)op.pitch * sizeof(float), (cuuint64_t)op.pitch * sizeof(float) * (cuuint64_t)K};
+        cuuint32_t box[3] = {32u, (cuuint32_t)BK, 1u};
+        cuuint32_t estr[3] = {1, 1, 1};
+        CUresult r = g_tc_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return false;
+        if (e) { e->key = key; e->map = *m; e->valid = true; }
+        return true;
     }
     const bool sw = tc_swapped(op);
     const cuuint64_t nslot = (cuuint64_t)(op.c2_dim > 0 ? op.c2_dim : 1);
@@ -546,19 +635,21 @@ static bool tc_make_map(CUtensorMap* m, const float* base, const TcOperand& op, 
     return true;
 }
 
-template <int BN, int BK, int NTERMS, int STAGES, int CTAS = 1>
+template <int BN, int BK, int NTERMS, int STAGES, int CTAS = 1, bool AMN = false, bool BMN = false>
 static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
     CUtensorMap mAh, mAl, mBh, mBl;
     constexpr int BROWS = BN / CTAS;
+    constexpr bool CONV = (CTAS == 2 && NTERMS == 3);
     if (!tc_make_map(&mAh, p.A.hi, p.A, p.K, BK, TC_BM) || !tc_make_map(&mBh, p.B.hi, p.B, p.K, BK, BROWS)) return false;
-    if (NTERMS == 3) { if (!tc_make_map(&mAl, p.A.lo, p.A, p.K, BK, TC_BM) || !tc_make_map(&mBl, p.B.lo, p.B, p.K, BK, BROWS)) return false; }
+    if (NTERMS == 3 && !CONV) { if (!tc_make_map(&mAl, p.A.lo, p.A, p.K, BK, TC_BM) || !tc_make_map(&mBl, p.B.lo, p.B, p.K, BK, BROWS)) return false; }
     else { mAl = mAh; mBl = mBh; }
     constexpr int STAGE_BYTES = (NTERMS == 3 ? 2 : 1) * (TC_BM + BROWS) * BK * 4;
     constexpr size_t tile_bytes = (size_t)TC_BM * (BN + 4) * 4;
     constexpr size_t ring_bytes = (size_t)STAGES * STAGE_BYTES;
     static_assert(tile_bytes <= ring_bytes, "the output tile is staged in the operand ring");
     size_t smem = ring_bytes + 1024 + 256;
-    auto kern = gemm_tc_kernel<BN, BK, NTERMS, STAGES, CTAS>;
+    auto kern = gemm_tc_kernel<BN, BK, NTERMS, STAGES, CTAS, AMN, BMN>;
+    constexpr int THREADS = TC_THREADS + (CONV ? 32 * TC_CONV_WARPS : 0);
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
@@ -595,7 +686,7 @@ static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
     if (CTAS == 2) {
         cudaLaunchConfig_t cfg;
         memset(&cfg, 0, sizeof cfg);
-        cfg.gridDim = grid; cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = (cudaStream_t)c->pub.stream;
+        cfg.gridDim = grid; cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = (cudaStream_t)c->pub.stream;
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeClusterDimension;
         at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
@@ -604,7 +695,7 @@ static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
                                p.A.c2_base, p.A.c2_step, p.B.c2_base, p.B.c2_step, swap_mask, split_full, split_s, partial,
                                c->d_status) != cudaSuccess) return false;
     } else {
-        kern<<<grid, TC_THREADS, smem, (cudaStream_t)c->pub.stream>>>(mAh, mAl, mBh, mBl, p.C, p.ldc, p.c_batch_stride, p.M, p.N, p.K, p.acc,
+        kern<<<grid, THREADS, smem, (cudaStream_t)c->pub.stream>>>(mAh, mAl, mBh, mBl, p.C, p.ldc, p.c_batch_stride, p.M, p.N, p.K, p.acc,
                                                                      p.causal, p.A.c2_base, p.A.c2_step, p.B.c2_base, p.B.c2_step,
                                                                      swap_mask, split_full, split_s, partial, c->d_status);
     }
@@ -622,8 +713,23 @@ static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
 // picks the tile width from N; nterms: 3 = FP32-accurate, 1 = TF32
 static bool tc_launch(sb_ctx_t* c, const TcProblem& p, int nterms) {
     if (!tc_load_encode()) return false;
-    if (c->gemm_pair && p.causal == TC_CAUSAL_NONE && p.nbatch <= 1 && p.N > 128 && p.M > 128)
-        return nterms == 3 ? tc_launch_t<256, 16, 3, 6, 2>(c, p) : tc_launch_t<256, 32, 1, 6, 2>(c, p);
+    const bool raw = nterms == 1 || (p.A.lo == nullptr && p.B.lo == nullptr);      // the pair kernel makes the lo parts itself
+    if (c->gemm_pair && raw && p.causal == TC_CAUSAL_NONE && p.nbatch <= 1 && p.N > 128 && p.M > 128) {
+        const int lay = (p.A.mn ? 1 : 0) | (p.B.mn ? 2 : 0);
+        if (nterms == 3) switch (lay) {
+            case 0: return tc_launch_t<256, 16, 3, 6, 2, false, false>(c, p);
+            case 1: return tc_launch_t<256, 16, 3, 6, 2, true, false>(c, p);
+            case 2: return tc_launch_t<256, 16, 3, 6, 2, false, true>(c, p);
+            default: return tc_launch_t<256, 16, 3, 6, 2, true, true>(c, p);
+        }
+        switch (lay) {
+            case 0: return tc_launch_t<256, 32, 1, 6, 2, false, false>(c, p);
+            case 1: return tc_launch_t<256, 32, 1, 6, 2, true, false>(c, p);
+            case 2: return tc_launch_t<256, 32, 1, 6, 2, false, true>(c, p);
+            default: return tc_launch_t<256, 32, 1, 6, 2, true, true>(c, p);
+        }
+    }
+    if (p.A.mn || p.B.mn || (nterms == 3 && (!p.A.lo || !p.B.lo))) return false;    // only the pair kernel takes these
     if (p.N > 128) return nterms == 3 ? tc_launch_t<256, 16, 3, 4>(c, p) : tc_launch_t<256, 32, 1, 4>(c, p);
     return nterms == 3 ? tc_launch_t<128, 16, 3, 6>(c, p) : tc_launch_t<128, 32, 1, 6>(c, p);
 }

@@ -223,13 +223,30 @@ __global__ void __launch_bounds__(RB_THREADS) rmsnorm_bwd_warp_kernel(const floa
     for (int j = threadIdx.x; j < c4; j += blockDim.x) pr[j] = s_acc[j];
 }
 
-// dscale[c] += sum over blocks (fixed order) of partial[b][c]
-__global__ void colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ dscale, int nblocks, int cols) {
-    int cidx = blockIdx.x * blockDim.x + threadIdx.x;
-    if (cidx >= cols) return;
+// dscale[c] += sum over partial rows of partial[b][c], in a fixed order: 32 columns per CTA, the rows
+// dealt to 8 row groups (group g takes rows g, g+8, ...), the 8 group sums then added in group order.
+__global__ void __launch_bounds__(256) colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ dscale, int nblocks, int cols) {
+    __shared__ float s_part[8][32];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int cidx = blockIdx.x * 32 + tx;
     float s = 0.f;
-    for (int b = 0; b < nblocks; b++) s += partial[(size_t)b * cols + cidx];
-    dscale[cidx] += s;
+    if (cidx < cols) {
+        int b = ty;
+        for (; b + 24 < nblocks; b += 32) {
+            float a0 = partial[(size_t)b * cols + cidx], a1 = partial[(size_t)(b + 8) * cols + cidx];
+            float a2 = partial[(size_t)(b + 16) * cols + cidx], a3 = partial[(size_t)(b + 24) * cols + cidx];
+            s += a0; s += a1; s += a2; s += a3;
+        }
+        for (; b < nblocks; b += 8) s += partial[(size_t)b * cols + cidx];
+    }
+    s_part[ty][tx] = s;
+    __syncthreads();
+    if (ty == 0 && cidx < cols) {
+        float t = s_part[0][tx];
+#pragma unroll
+        for (int g = 1; g < 8; g++) t += s_part[g][tx];
+        dscale[cidx] += t;
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -484,7 +501,7 @@ void sb_rmsnorm_backward_with_partials(sb_ctx_t* c, const float* x, const float*
     cudaStream_t s = (cudaStream_t)c->pub.stream;
     int tk = sb_tick_begin(c, SB_CLS_NORM_BWD);
     rmsnorm_bwd_kernel<<<grid, RB_THREADS, 0, s>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps, vec);
-    colsum_partials_kernel<<<(cols + 255) / 256, 256, 0, s>>>(partial, dscale, grid, cols);
+    colsum_partials_kernel<<<(cols + 31) / 32, 256, 0, s>>>(partial, dscale, grid, cols);
     sb_tick_end(c, tk, 0.0, (resid ? 16.0 : 12.0) * rows * cols);
     c->launches += 2;
 }
@@ -505,7 +522,7 @@ void sb_rmsnorm_backward(sb_ctx_t* c, const float* x, const float* w, const floa
         if (cols <= 512)       rmsnorm_bwd_warp_kernel<4><<<wgrid, RB_THREADS, sm, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
         else if (cols <= 1024) rmsnorm_bwd_warp_kernel<8><<<wgrid, RB_THREADS, sm, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
         else                   rmsnorm_bwd_warp_kernel<16><<<wgrid, RB_THREADS, sm, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
-        colsum_partials_kernel<<<(cols + 255) / 256, 256, 0, st>>>(partial, dscale, wgrid, cols);
+        colsum_partials_kernel<<<(cols + 31) / 32, 256, 0, st>>>(partial, dscale, wgrid, cols);
         sb_tick_end(c, tk, 0.0, (resid ? 16.0 : 12.0) * rows * cols);
         c->launches += 2;
         return;
@@ -689,7 +706,7 @@ extern "C" int seraph_b200_rmsnorm_backward_static(const float* input, const flo
     // every CTA overwrites its whole row of partials before the column sum reads it,
     // so nothing left over from an earlier call is ever read and no clearing is needed
     rmsnorm_bwd_kernel<<<grid, RB_THREADS, 0, s>>>(input, scale, grad_output, nullptr, grad_input, partial, rows, cols, eps, vec);
-    colsum_partials_kernel<<<(cols + 255) / 256, 256, 0, s>>>(partial, grad_scale, grid, cols);
+    colsum_partials_kernel<<<(cols + 31) / 32, 256, 0, s>>>(partial, grad_scale, grid, cols);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         fprintf(stderr, "seraph_b200_rmsnorm_backward_static: launch failed: %s\n", cudaGetErrorString(e));

@@ -124,13 +124,15 @@ template <bool PAIRBAR>
 __device__ __forceinline__ void tc_load_box(void* dst, const CUtensorMap* map, uint64_t* bar, uint32_t bar_cluster, int c0, int c1, int c2) {
     if (PAIRBAR) tma_load_3d_pair(dst, map, bar_cluster, c0, c1, c2); else tma_load_3d(dst, map, bar, c0, c1, c2);
 }
-// one operand tile of a stage: K-major = one box {BK, rows}; MN-major = four boxes {32 rows, BK} of BK*128 bytes each
-template <bool PAIRBAR, bool MN, int BK>
+// one operand tile of a stage: K-major = one box {BK, rows}; MN-major = ROWS/32 boxes {32 rows, BK} of BK*128 bytes each
+template <bool PAIRBAR, bool MN, int BK, int ROWS>
 __device__ __forceinline__ void tc_load_operand(uint8_t* dst, const CUtensorMap* map, uint64_t* bar, uint32_t bar_cluster,
                                                 int kb, int row0, int c2, bool swapped) {
     if (MN) {
+        // {row, k, slot}, or {row, slot, k} when the slot stride is smaller than the k-row pitch
 #pragma unroll
-        for (int j = 0; j < 4; j++) tc_load_box<PAIRBAR>(dst + j * BK * 128, map, bar, bar_cluster, row0 + 32 * j, kb * BK, 0);
+        for (int j = 0; j < ROWS / 32; j++)
+            tc_load_box<PAIRBAR>(dst + j * BK * 128, map, bar, bar_cluster, row0 + 32 * j, swapped ? c2 : kb * BK, swapped ? kb * BK : c2);
     } else {
         // a map whose slot stride is smaller than its row pitch is encoded as {k, slot, row}
         tc_load_box<PAIRBAR>(dst, map, bar, bar_cluster, kb * BK, swapped ? c2 : row0, swapped ? row0 : c2);
@@ -209,8 +211,7 @@ __device__ __forceinline__ float tf32_lo(float x) {
 // pair's rank-0 CTA.  Each CTA loads its own 128 rows of A and BN/2 rows of B, so per flop it takes a
 // third less from L2 and the tensor core reads a third less shared memory than two independent CTAs
 // would; each CTA's tensor memory holds its 128 rows of the tile and its own epilogue warps drain them.
-// Plain GEMMs only (no causal modes, one batch).  In this form the kernel takes the caller's FP32
-// matrices as they are:
+// In this form the kernel takes the caller's FP32 matrices as they are:
 //   * an operand stored [K, rows] (rows contiguous, "MN-major") is fetched in boxes of 32 floats x BK
 //     k-rows (128-byte swizzle of 32-byte units) and read by the MMA through an MN-major descriptor, so no
 //     transposed copy is made;
@@ -239,7 +240,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
     constexpr int STAGE_BYTES = (NTERMS == 3 ? 2 : 1) * HI_BYTES;
     constexpr bool CONV = (CTAS == 2 && NTERMS == 3);            // lo parts made in the kernel
     static_assert(CTAS == 2 || (!AMN && !BMN), "MN-major operands: CTA-pair kernel only");
-    static_assert(!(AMN || BMN) || BROWS == 128, "an MN-major tile is four boxes of 32 rows");
+    static_assert(BROWS % 32 == 0, "an MN-major tile is made of boxes of 32 rows");
     constexpr uint32_t TMEM_COLS = 2 * BN;                       // two accumulator buffers
     constexpr int KB_PER_CHUNK = TC_CHUNK_K / BK;
     constexpr int COLS_PER_WARP = BN / (TC_EPI_WARPS / 4);       // 128 or 64 register accumulators per epilogue thread
@@ -265,12 +266,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
     const int m0 = m_tile * TILE_M + (int)rank * TC_BM, n0 = n_tile * BN;      // this CTA's rows of A and C; the tile's columns
     const int nb0 = n0 + (int)rank * BROWS;                                     // this CTA's rows of B
     int kb_begin = 0, kb_end = (K + BK - 1) / BK;
-    if (CTAS == 1) {
-        // causal structure: whole-tile skips and the k range (CTA-uniform)
-        if (causal == TC_CAUSAL_SKIP_UPPER && n0 > m0 + TC_BM - 1) return;
-        if (causal == TC_CAUSAL_SKIP_LOWER && n0 + BN - 1 < m0) return;
-        if (causal == TC_CAUSAL_K_UPTO_M) kb_end = min(kb_end, (m0 + TC_BM + BK - 1) / BK);
-        if (causal == TC_CAUSAL_K_FROM_M) kb_begin = min(kb_end, m0 / BK);
+    {
+        // causal structure: whole-tile skips and the k range, the same for both CTAs of a pair
+        const int tm0 = m_tile * TILE_M;
+        if (causal == TC_CAUSAL_SKIP_UPPER && n0 > tm0 + TILE_M - 1) return;
+        if (causal == TC_CAUSAL_SKIP_LOWER && n0 + BN - 1 < tm0) return;
+        if (causal == TC_CAUSAL_K_UPTO_M) kb_end = min(kb_end, (tm0 + TILE_M + BK - 1) / BK);
+        if (causal == TC_CAUSAL_K_FROM_M) kb_begin = min(kb_end, tm0 / BK);
     }
     if (split) {
         const int per = ((kb_end + split_s - 1) / split_s + KB_PER_CHUNK - 1) / KB_PER_CHUNK * KB_PER_CHUNK;
@@ -316,20 +318,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
                 if (CONV) {
                     // each CTA's hi tiles land on its own barrier; its converter warps take it from there
                     mbar_expect_tx(&full[s], HI_BYTES);
-                    tc_load_operand<false, AMN, BK>(st, &tmAh, &full[s], 0, kb, m0, a_c2, swa);
-                    tc_load_operand<false, BMN, BK>(st + A_BYTES, &tmBh, &full[s], 0, kb, nb0, b_c2, swb);
+                    tc_load_operand<false, AMN, BK, TC_BM>(st, &tmAh, &full[s], 0, kb, m0, a_c2, swa);
+                    tc_load_operand<false, BMN, BK, BROWS>(st + A_BYTES, &tmBh, &full[s], 0, kb, nb0, b_c2, swb);
                 } else if (CTAS == 2) {
                     if (leader) mbar_expect_tx(&full[s], STAGE_BYTES * CTAS);      // the pair's bytes all land on the leader's barrier
                     const uint32_t fb = mapa_u32(smem_u32(&full[s]), 0);
-                    tc_load_operand<true, AMN, BK>(st, &tmAh, nullptr, fb, kb, m0, a_c2, swa);
-                    tc_load_operand<true, BMN, BK>(st + A_BYTES, &tmBh, nullptr, fb, kb, nb0, b_c2, swb);
+                    tc_load_operand<true, AMN, BK, TC_BM>(st, &tmAh, nullptr, fb, kb, m0, a_c2, swa);
+                    tc_load_operand<true, BMN, BK, BROWS>(st + A_BYTES, &tmBh, nullptr, fb, kb, nb0, b_c2, swb);
                 } else {
                     mbar_expect_tx(&full[s], STAGE_BYTES);
-                    tc_load_operand<false, false, BK>(st, &tmAh, &full[s], 0, kb, m0, a_c2, swa);
-                    tc_load_operand<false, false, BK>(st + A_BYTES, &tmBh, &full[s], 0, kb, nb0, b_c2, swb);
+                    tc_load_operand<false, false, BK, TC_BM>(st, &tmAh, &full[s], 0, kb, m0, a_c2, swa);
+                    tc_load_operand<false, false, BK, BROWS>(st + A_BYTES, &tmBh, &full[s], 0, kb, nb0, b_c2, swb);
                     if (NTERMS == 3) {
-                        tc_load_operand<false, false, BK>(st + HI_BYTES, &tmAl, &full[s], 0, kb, m0, a_c2, swa);
-                        tc_load_operand<false, false, BK>(st + HI_BYTES + A_BYTES, &tmBl, &full[s], 0, kb, nb0, b_c2, swb);
+                        tc_load_operand<false, false, BK, TC_BM>(st + HI_BYTES, &tmAl, &full[s], 0, kb, m0, a_c2, swa);
+                        tc_load_operand<false, false, BK, BROWS>(st + HI_BYTES + A_BYTES, &tmBl, &full[s], 0, kb, nb0, b_c2, swb);
                     }
                 }
             }
@@ -391,7 +393,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
             const int cw = warp - (2 + TC_EPI_WARPS);
             constexpr int N4 = HI_BYTES / 16;
             constexpr int PER = N4 / (32 * TC_CONV_WARPS);
-            static_assert(N4 % (32 * TC_CONV_WARPS) == 0 && PER % 8 == 0, "stage size against the converter's unroll");
+            constexpr int UNR = PER % 8 == 0 ? 8 : 4;
+            static_assert(N4 % (32 * TC_CONV_WARPS) == 0 && PER % UNR == 0, "stage size against the converter's unroll");
             const uint32_t cb_base = mapa_u32(smem_u32(&conv[0]), 0);
             for (int it = 0; it < num_kb && ok; it++) {
                 const int s = it % STAGES;
@@ -400,12 +403,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
                 const float4* src = (const float4*)(smem + s * STAGE_BYTES);
                 float4* dst = (float4*)(smem + s * STAGE_BYTES + HI_BYTES);
 #pragma unroll
-                for (int b = 0; b < PER; b += 8) {
-                    float4 v[8];
+                for (int b = 0; b < PER; b += UNR) {
+                    float4 v[UNR];
 #pragma unroll
-                    for (int j = 0; j < 8; j++) v[j] = src[(cw * PER + b + j) * 32 + lane];
+                    for (int j = 0; j < UNR; j++) v[j] = src[(cw * PER + b + j) * 32 + lane];
 #pragma unroll
-                    for (int j = 0; j < 8; j++)
+                    for (int j = 0; j < UNR; j++)
                         dst[(cw * PER + b + j) * 32 + lane] = make_float4(tf32_lo(v[j].x), tf32_lo(v[j].y), tf32_lo(v[j].z), tf32_lo(v[j].w));
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the MMA reads these writes through the async proxy
@@ -583,6 +586,7 @@ static bool tc_load_encode() {
 }
 
 // slot stride below the row pitch (heads interleaved inside a token row): dimensions are ordered {k, slot, row}
+// (MN-major: {row, slot, k})
 static inline bool tc_swapped(const TcOperand& op) { return op.c2_dim > 1 && op.c2_stride < op.pitch; }
 
 // Encoding a tensor map costs a few microseconds on the host and a training step re-issues the same
@@ -610,9 +614,13 @@ static bool tc_make_map(CUtensorMap* m, const float* base, const TcOperand& op, 
     }
     if (op.mn) {
         // the array is [K, rows] with rows contiguous: {rows, K, 1}, boxes of 32 floats x BK k-rows, 128-byte swizzle of 32-byte units
-        cuuint64_t dims[3] = {(cuuint64_t)op.rows, (cuuint64_t)K, 1};
-        cuuint64_t strides[2] = {(cuuint64_t)op.pitch * sizeof(float), (cuuint64_t)op.pitch * sizeof(float) * (cuuint64_t)K};
-        cuuint32_t box[3] = {32u, (cuuint32_t)BK, 1u};
+        const bool swm = tc_swapped(op);
+        const cuuint64_t nsl = (cuuint64_t)(op.c2_dim > 1 ? op.c2_dim : 1);
+        const cuuint64_t krow = (cuuint64_t)op.pitch * sizeof(float);
+        const cuuint64_t sl = op.c2_dim > 1 ? (cuuint64_t)op.c2_stride * sizeof(float) : krow * (cuuint64_t)K;
+        cuuint64_t dims[3] = {(cuuint64_t)op.rows, swm ? nsl : (cuuint64_t)K, swm ? (cuuint64_t)K : nsl};
+        cuuint64_t strides[2] = {swm ? sl : krow, swm ? krow : sl};
+        cuuint32_t box[3] = {32u, swm ? 1u : (cuuint32_t)BK, swm ? (cuuint32_t)BK : 1u};
         cuuint32_t estr[3] = {1, 1, 1};
         CUresult r = g_tc_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                  CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -714,19 +722,34 @@ static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
 static bool tc_launch(sb_ctx_t* c, const TcProblem& p, int nterms) {
     if (!tc_load_encode()) return false;
     const bool raw = nterms == 1 || (p.A.lo == nullptr && p.B.lo == nullptr);      // the pair kernel makes the lo parts itself
-    if (c->gemm_pair && raw && p.causal == TC_CAUSAL_NONE && p.nbatch <= 1 && p.N > 128 && p.M > 128) {
+    if (c->gemm_pair && raw) {
         const int lay = (p.A.mn ? 1 : 0) | (p.B.mn ? 2 : 0);
+        if (p.N > 128) {
+            if (nterms == 3) switch (lay) {
+                case 0: return tc_launch_t<256, 16, 3, 6, 2, false, false>(c, p);
+                case 1: return tc_launch_t<256, 16, 3, 6, 2, true, false>(c, p);
+                case 2: return tc_launch_t<256, 16, 3, 6, 2, false, true>(c, p);
+                default: return tc_launch_t<256, 16, 3, 6, 2, true, true>(c, p);
+            }
+            switch (lay) {
+                case 0: return tc_launch_t<256, 32, 1, 6, 2, false, false>(c, p);
+                case 1: return tc_launch_t<256, 32, 1, 6, 2, true, false>(c, p);
+                case 2: return tc_launch_t<256, 32, 1, 6, 2, false, true>(c, p);
+                default: return tc_launch_t<256, 32, 1, 6, 2, true, true>(c, p);
+            }
+        }
+        // narrow outputs (attention's products with V, K, Q, dO: N = head_dim): 256 x 128 tiles
         if (nterms == 3) switch (lay) {
-            case 0: return tc_launch_t<256, 16, 3, 6, 2, false, false>(c, p);
-            case 1: return tc_launch_t<256, 16, 3, 6, 2, true, false>(c, p);
-            case 2: return tc_launch_t<256, 16, 3, 6, 2, false, true>(c, p);
-            default: return tc_launch_t<256, 16, 3, 6, 2, true, true>(c, p);
+            case 0: return tc_launch_t<128, 16, 3, 8, 2, false, false>(c, p);
+            case 1: return tc_launch_t<128, 16, 3, 8, 2, true, false>(c, p);
+            case 2: return tc_launch_t<128, 16, 3, 8, 2, false, true>(c, p);
+            default: return tc_launch_t<128, 16, 3, 8, 2, true, true>(c, p);
         }
         switch (lay) {
-            case 0: return tc_launch_t<256, 32, 1, 6, 2, false, false>(c, p);
-            case 1: return tc_launch_t<256, 32, 1, 6, 2, true, false>(c, p);
-            case 2: return tc_launch_t<256, 32, 1, 6, 2, false, true>(c, p);
-            default: return tc_launch_t<256, 32, 1, 6, 2, true, true>(c, p);
+            case 0: return tc_launch_t<128, 32, 1, 8, 2, false, false>(c, p);
+            case 1: return tc_launch_t<128, 32, 1, 8, 2, true, false>(c, p);
+            case 2: return tc_launch_t<128, 32, 1, 8, 2, false, true>(c, p);
+            default: return tc_launch_t<128, 32, 1, 8, 2, true, true>(c, p);
         }
     }
     if (p.A.mn || p.B.mn || (nterms == 3 && (!p.A.lo || !p.B.lo))) return false;    // only the pair kernel takes these

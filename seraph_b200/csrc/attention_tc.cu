@@ -148,26 +148,56 @@ static int at_group(int S_pad, int nbuf, int Hkv) {
     return G;
 }
 
+// Sequences are independent, and each of their launches ends in a partly filled wave (causal tiles differ
+// in length): up to four sequences run side by side on side streams, each with its own scratch slice, so
+// the tails of one fill with the tiles of another.  Fork: the side streams wait for the work queued so far;
+// join: the main stream waits for all of them.
+#define AT_SIDE 4
+static int at_fork(sb_ctx_t* c, int want) {
+    if (want < 2) return 1;
+    if (!c->side_ready) {
+        for (int i = 0; i < AT_SIDE; i++) { cudaStream_t st; if (cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) != cudaSuccess) return 1; c->side_stream[i] = st; }
+        for (int i = 0; i < AT_SIDE + 1; i++) { cudaEvent_t e; if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return 1; c->side_ev[i] = e; }
+        c->side_ready = 1;
+    }
+    const int ns = want < AT_SIDE ? want : AT_SIDE;
+    cudaEventRecord((cudaEvent_t)c->side_ev[AT_SIDE], (cudaStream_t)c->pub.stream);
+    for (int i = 0; i < ns; i++) cudaStreamWaitEvent((cudaStream_t)c->side_stream[i], (cudaEvent_t)c->side_ev[AT_SIDE], 0);
+    return ns;
+}
+static void at_join(sb_ctx_t* c, int ns, void* main_stream) {
+    c->pub.stream = main_stream;
+    if (ns < 2) return;
+    for (int i = 0; i < ns; i++) {
+        cudaEventRecord((cudaEvent_t)c->side_ev[i], (cudaStream_t)c->side_stream[i]);
+        cudaStreamWaitEvent((cudaStream_t)main_stream, (cudaEvent_t)c->side_ev[i], 0);
+    }
+}
+
 extern "C" int sb_attention_tc_forward(sb_ctx_t* c, const float* Q, const float* K, const float* V, float* O, float* lse,
                                        int T, int Hq, int Hkv, int hd) {
     if (!at_eligible(c, T, Hq, Hkv, hd)) return 1;
     const int qd = Hq * hd, kvd = Hkv * hd, g = Hq / Hkv;
     const float scale = 1.0f / sqrtf((float)hd);
-    cudaStream_t s = (cudaStream_t)c->pub.stream;
     int Smax = 0;
     for (int b = 0; b < c->h_seq_n; b++) Smax = max(Smax, c->h_seq[b + 1] - c->h_seq[b]);
     const int Sp = round_up(Smax, AT_ROWTILE);                       // one pitch for all sequences of the call
     const int G = at_group(Sp, 1, Hkv);
     const size_t n_s = (size_t)G * Sp * Sp;
-    float* Sb = (float*)sb_gemm_stage(c, 3, n_s * sizeof(float));
-    if (!Sb) return 1;
+    float* Sb0 = (float*)sb_gemm_stage(c, 3, AT_SIDE * n_s * sizeof(float));
+    if (!Sb0) return 1;
     int tk = sb_tick_begin(c, SB_CLS_ATTN_FWD);
     bool ok = true;
     double flops = 0;
+    void* main_stream = c->pub.stream;
+    const int ns = at_fork(c, c->h_seq_n);
     for (int b = 0; b < c->h_seq_n && ok; b++) {
         const int t0 = c->h_seq[b], S = c->h_seq[b + 1] - t0;
         if (S <= 0) continue;
         flops += 2.0 * Hq * (double)S * S * hd;
+        if (ns > 1) c->pub.stream = c->side_stream[b % ns];
+        cudaStream_t s = (cudaStream_t)c->pub.stream;
+        float* Sb = Sb0 + (size_t)(b % ns) * n_s;
         for (int r = 0; r < g && ok; r++)
             for (int i0 = 0; i0 < Hkv && ok; i0 += G) {
                 const int nb = min(G, Hkv - i0), qh0 = r + i0 * g;
@@ -179,6 +209,7 @@ extern "C" int sb_attention_tc_forward(sb_ctx_t* c, const float* Q, const float*
                                    O + (size_t)t0 * qd + (size_t)qh0 * hd, qd, (long)g * hd, S, hd, S, 0, nb, TC_CAUSAL_K_UPTO_M);
             }
     }
+    at_join(c, ns, main_stream);
     sb_tick_end(c, tk, flops, 0.0);
     if (!ok) { sb_set_status(c, SB_ERR_CUDA); return 1; }
     return 0;
@@ -190,25 +221,28 @@ extern "C" int sb_attention_tc_backward(sb_ctx_t* c, const float* Q, const float
     if (!at_eligible(c, T, Hq, Hkv, hd)) return 1;
     const int qd = Hq * hd, kvd = Hkv * hd, g = Hq / Hkv;
     const float scale = 1.0f / sqrtf((float)hd);
-    cudaStream_t s = (cudaStream_t)c->pub.stream;
     int Smax = 0;
     for (int b = 0; b < c->h_seq_n; b++) Smax = max(Smax, c->h_seq[b + 1] - c->h_seq[b]);
     const int Sp = round_up(Smax, AT_ROWTILE);
     const int G = at_group(Sp, 2, Hkv);
     const size_t n_s = (size_t)G * Sp * Sp;
     float* D = (float*)sb_gemm_stage(c, 2, ((size_t)T * Hq + 64) * sizeof(float));
-    float* b0 = (float*)sb_gemm_stage(c, 3, 2 * n_s * sizeof(float));
-    if (!D || !b0) return 1;
-    float* b1 = b0 + n_s;
+    float* bb = (float*)sb_gemm_stage(c, 3, AT_SIDE * 2 * n_s * sizeof(float));
+    if (!D || !bb) return 1;
     int tk = sb_tick_begin(c, SB_CLS_ATTN_BWD);
-    at_delta_kernel<<<(T * Hq * 32 + 255) / 256, 256, 0, s>>>(dO, O, D, T * Hq, hd);
+    at_delta_kernel<<<(T * Hq * 32 + 255) / 256, 256, 0, (cudaStream_t)c->pub.stream>>>(dO, O, D, T * Hq, hd);
     c->launches++;
     bool ok = true;
     double flops = 0;
+    void* main_stream = c->pub.stream;
+    const int ns = at_fork(c, c->h_seq_n);
     for (int b = 0; b < c->h_seq_n && ok; b++) {
         const int t0 = c->h_seq[b], S = c->h_seq[b + 1] - t0;
         if (S <= 0) continue;
         flops += 5.0 * Hq * (double)S * S * hd;
+        if (ns > 1) c->pub.stream = c->side_stream[b % ns];
+        cudaStream_t s = (cudaStream_t)c->pub.stream;
+        float* b0 = bb + (size_t)(b % ns) * 2 * n_s; float* b1 = b0 + n_s;
         for (int r = 0; r < g && ok; r++)
             for (int i0 = 0; i0 < Hkv && ok; i0 += G) {
                 const int nb = min(G, Hkv - i0), qh0 = r + i0 * g;
@@ -228,6 +262,7 @@ extern "C" int sb_attention_tc_backward(sb_ctx_t* c, const float* Q, const float
                                    dK + (size_t)t0 * kvd + (size_t)i0 * hd, kvd, hd, S, hd, S, acc, nb, TC_CAUSAL_K_FROM_M);          // dK += dS^T Q
             }
     }
+    at_join(c, ns, main_stream);
     sb_tick_end(c, tk, flops, 0.0);
     if (!ok) { sb_set_status(c, SB_ERR_CUDA); return 1; }
     return 0;

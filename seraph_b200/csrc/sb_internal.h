@@ -100,6 +100,7 @@ typedef struct sb_ctx {
     /* data parallel */
     void* nccl_comm; int dp_rank, dp_world;
     void* comm_stream; void* ev_bucket[64]; int n_buckets;
+    void* side_stream[4]; void* side_ev[5]; int side_ready;   /* side streams of the attention path (sequences run side by side) */
     size_t bucket_begin[64], bucket_end[64];
 } sb_ctx_t;
 

@@ -736,6 +736,10 @@ void cuda_train_free(cuda_train_context_t* ctx) {
     if (c->seq_starts) cudaFree(c->seq_starts);
     if (c->scratch) cudaFree(c->scratch);
     for (int i = 0; i < 5; i++) if (c->gemm_stage[i]) cudaFree(c->gemm_stage[i]);
+    if (c->side_ready) {
+        for (int i = 0; i < 4; i++) cudaStreamDestroy((cudaStream_t)c->side_stream[i]);
+        for (int i = 0; i < 5; i++) cudaEventDestroy((cudaEvent_t)c->side_ev[i]);
+    }
     if (c->rope_tab) cudaFree(c->rope_tab);
     if (c->d_status) cudaFree(c->d_status);
     if (c->d_loss) cudaFree(c->d_loss);

@@ -45,7 +45,14 @@
 #define TC_BM 128
 #define TC_EPI_WARPS 8
 #define TC_THREADS (64 + 32 * TC_EPI_WARPS)
-#define TC_CONV_WARPS 2                   // converter warps of the CTA-pair kernel (after the epilogue warps)
+#define TC_CONV_WARPS 4                   // converter warps of the FP32-accurate CTA-pair kernel
+// Warp roles.  Without converters: warp 0 TMA producer, warp 1 MMA issuer, warps 2-9 epilogue (10 warps).
+// With converters the CTA has four warpgroups of four warps, so that registers can be moved between them
+// (setmaxnreg works on aligned groups of four warps): warps 0/1 producer and MMA issuer, 2-3 and 12-13
+// converters, 4-11 epilogue, 14-15 idle; the epilogue warpgroups take the registers the others give up.
+#define TC_CONV_THREADS 512
+#define TC_REGS_LIGHT 72
+#define TC_REGS_EPI 176
 #define TC_GROUP_M 16
 #define TC_CHUNK_K 32
 #define TC_SPIN_CYCLES 4000000000ll      // ~2 s at 2 GHz: far beyond any legitimate wait
@@ -215,7 +222,7 @@ __device__ __forceinline__ float tf32_lo(float x) {
 //   * an operand stored [K, rows] (rows contiguous, "MN-major") is fetched in boxes of 32 floats x BK
 //     k-rows (128-byte swizzle of 32-byte units) and read by the MMA through an MN-major descriptor, so no
 //     transposed copy is made;
-//   * the lo parts of the FP32-accurate mode are computed in the kernel: two converter warps per CTA
+//   * the lo parts of the FP32-accurate mode are computed in the kernel: four converter warps per CTA
 //     read each landed hi stage, write x - trunc_tf32(x) (rounded to nearest at TF32 precision) beside
 //     it at the same offsets - the layout, whatever its swizzle, carries over - and release the stage to
 //     the MMA warp.  TMA moves 4 bytes per operand element instead of 8 and nothing is prepared in HBM.
@@ -226,7 +233,7 @@ __device__ __forceinline__ float tf32_lo(float x) {
 // block to `partial`; tc_splitk_fixup_kernel adds the pieces in piece order, so the result does not
 // depend on timing.
 template <int BN, int BK, int NTERMS, int STAGES, int CTAS, bool AMN, bool BMN>
-__global__ void __launch_bounds__(TC_THREADS + 32 * TC_CONV_WARPS, 1)
+__global__ void __launch_bounds__((CTAS == 2 && NTERMS == 3) ? TC_CONV_THREADS : TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
                float* __restrict__ Cbase, long ldc, long c_batch_stride, int M, int N, int K, int acc, int causal,
@@ -305,7 +312,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
+    constexpr int EPI0 = CONV ? 4 : 2;            // first epilogue warp
+    const bool is_epi = warp >= EPI0 && warp < EPI0 + TC_EPI_WARPS;
+    // converter index of this warp (CONV only): warps 2, 3, 12, 13 -> 0..3; -1 otherwise
+    const int cw = !CONV ? -1 : (warp == 2 || warp == 3) ? warp - 2 : (warp == 12 || warp == 13) ? warp - 10 : -1;
 
+    if (!is_epi) {
+    if (CONV) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(TC_REGS_LIGHT));      // whole warpgroups 0 and 3
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (elect_one()) {
@@ -387,13 +400,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
             }
             if (!ok) atomicExch(status, SB_ERR_TIMEOUT);
         }
-    } else if (warp >= 2 + TC_EPI_WARPS) {
+    } else {
         // ---------------- converter (CTA-pair FP32-accurate kernel): lo = x - trunc_tf32(x) beside each landed hi stage ----------------
-        if (CONV) {
-            const int cw = warp - (2 + TC_EPI_WARPS);
+        if (CONV && cw >= 0) {
             constexpr int N4 = HI_BYTES / 16;
             constexpr int PER = N4 / (32 * TC_CONV_WARPS);
-            constexpr int UNR = PER % 8 == 0 ? 8 : 4;
+            constexpr int UNR = PER % 8 == 0 ? 8 : (PER % 6 == 0 ? 6 : 4);
             static_assert(N4 % (32 * TC_CONV_WARPS) == 0 && PER % UNR == 0, "stage size against the converter's unroll");
             const uint32_t cb_base = mapa_u32(smem_u32(&conv[0]), 0);
             for (int it = 0; it < num_kb && ok; it++) {
@@ -417,9 +429,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
             }
             if (!ok && lane == 0) atomicExch(status, SB_ERR_TIMEOUT);
         }
+    }
     } else {
         // ---------------- epilogue: TMEM chunks -> register accumulators -> shared -> global ----------------
-        const int ew = warp - 2;                      // 0..7
+        if (CONV) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(TC_REGS_EPI));          // whole warpgroups 1 and 2
+        const int ew = warp - EPI0;                   // 0..7
         const int q = warp & 3;                       // TMEM lane quarter this warp may read
         const int col0 = (ew >> 2) * COLS_PER_WARP;   // which half of the tile's columns
         float accr[COLS_PER_WARP];
@@ -657,7 +671,7 @@ static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
     static_assert(tile_bytes <= ring_bytes, "the output tile is staged in the operand ring");
     size_t smem = ring_bytes + 1024 + 256;
     auto kern = gemm_tc_kernel<BN, BK, NTERMS, STAGES, CTAS, AMN, BMN>;
-    constexpr int THREADS = TC_THREADS + (CONV ? 32 * TC_CONV_WARPS : 0);
+    constexpr int THREADS = CONV ? TC_CONV_THREADS : TC_THREADS;
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;

@@ -33,45 +33,65 @@ __device__ __forceinline__ float warp_sum_f(float v) { for (int o = 16; o > 0; o
 __device__ __forceinline__ float warp_max_f(float v) { for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o)); return v; }
 
 // Forward rows: S[i][q][0..q] (raw dot products) -> P (in place), normalised; lse written.
-// Columns (q, end of q's row tile) are zeroed: the P V product reads them.
+// Columns (q, end of q's row tile) are zeroed: the P V product reads them.  A row of up to
+// 256*AT_SM_REGS scores is read once and kept in registers; longer rows are read three times.
+#define AT_SM_REGS 16
+__device__ __forceinline__ float at_block_max(float v, float* red) {
+    v = warp_max_f(v);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float m = red[0];
+    for (int w = 1; w < 8; w++) m = fmaxf(m, red[w]);
+    __syncthreads();
+    return m;
+}
+__device__ __forceinline__ float at_block_sum(float v, float* red) {
+    v = warp_sum_f(v);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float s = 0.f;
+    for (int w = 0; w < 8; w++) s += red[w];
+    __syncthreads();
+    return s;
+}
 __global__ void __launch_bounds__(256) at_softmax_rows(float* __restrict__ Sb, float* __restrict__ lse,
                                                        int S, int Sp, int Hq, int head0, int head_step, int tok0, float scale) {
-    __shared__ float red[16];
+    __shared__ float red[8];
     const int q = blockIdx.x, i = blockIdx.y, h = head0 + i * head_step;
     float* row = Sb + ((size_t)i * Sp + q) * Sp;
     const int n = q + 1, zend = min(Sp, (q / AT_ROWTILE + 1) * AT_ROWTILE);
+    if (n <= 256 * AT_SM_REGS) {
+        float v[AT_SM_REGS];
+        float m = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < AT_SM_REGS; j++) {
+            const int k = threadIdx.x + 256 * j;
+            v[j] = k < n ? row[k] * scale : -INFINITY;
+            m = fmaxf(m, v[j]);
+        }
+        m = at_block_max(m, red);
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < AT_SM_REGS; j++) s += expf(v[j] - m);                          // exp(-inf) = 0 beyond the row
+        s = at_block_sum(s, red);
+        const float L = m + logf(s);
+        if (threadIdx.x == 0 && lse) lse[(size_t)(tok0 + q) * Hq + h] = L;
+#pragma unroll
+        for (int j = 0; j < AT_SM_REGS; j++) {
+            const int k = threadIdx.x + 256 * j;
+            if (k < zend) row[k] = expf(v[j] - L);                                          // 0 past the diagonal
+        }
+        return;
+    }
     float m = -INFINITY;
     for (int k = threadIdx.x; k < n; k += blockDim.x) m = fmaxf(m, row[k] * scale);
-    m = warp_max_f(m);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
-    __syncthreads();
-    m = red[0];
-    for (int w = 1; w < 8; w++) m = fmaxf(m, red[w]);
+    m = at_block_max(m, red);
     float s = 0.f;
     for (int k = threadIdx.x; k < n; k += blockDim.x) s += expf(row[k] * scale - m);
-    s = warp_sum_f(s);
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) red[8 + (threadIdx.x >> 5)] = s;
-    __syncthreads();
-    s = 0.f;
-    for (int w = 0; w < 8; w++) s += red[8 + w];
+    s = at_block_sum(s, red);
     const float L = m + logf(s);
     if (threadIdx.x == 0 && lse) lse[(size_t)(tok0 + q) * Hq + h] = L;
-    for (int k = threadIdx.x; k < zend; k += blockDim.x) {
-        float p = k < n ? expf(row[k] * scale - L) : 0.f;
-        row[k] = p;
-    }
-}
-
-// D[t,h] = sum_d dO[t,h,d] * O[t,h,d]; one warp per (t,h)
-__global__ void at_delta_kernel(const float* __restrict__ dO, const float* __restrict__ O, float* __restrict__ D, int n_th, int hd) {
-    int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (w >= n_th) return;
-    const float* a = dO + (size_t)w * hd; const float* b = O + (size_t)w * hd;
-    float s = 0.f;
-    for (int d = lane; d < hd; d += 32) s += a[d] * b[d];
-    s = warp_sum_f(s);
-    if (lane == 0) D[w] = s;
+    for (int k = threadIdx.x; k < zend; k += blockDim.x) row[k] = k < n ? expf(row[k] * scale - L) : 0.f;
 }
 
 // Backward rows: S (buf_s) and dP (buf_dp) -> P (into buf_s) and dS (into buf_dp); zero past the diagonal up to the row tile's end
@@ -90,11 +110,18 @@ __global__ void __launch_bounds__(256) at_ds_rows(float* __restrict__ buf_s, flo
     }
 }
 
+// D[t,h] = sum_d dO[t,h,d] * O[t,h,d]; one warp per (t,h)
+__global__ void at_delta_kernel(const float* __restrict__ dO, const float* __restrict__ O, float* __restrict__ D, int n_th, int hd) {
+    int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (w >= n_th) return;
+    const float* a = dO + (size_t)w * hd; const float* b = O + (size_t)w * hd;
+    float s = 0.f;
+    for (int d = lane; d < hd; d += 32) s += a[d] * b[d];
+    s = warp_sum_f(s);
+    if (lane == 0) D[w] = s;
+}
+
 // ---------------------------------------------------------------------------------------------
-struct AtPlan {
-    int T, Hq, Hkv, hd, qd, kvd, g;
-    const int* seq; int nseq;
-};
 
 static bool at_eligible(sb_ctx_t* c, int T, int Hq, int Hkv, int hd) {
     int mode = c->pub.use_bf16 ? SB_GEMM_BF16 : c->gemm_mode;
@@ -128,9 +155,15 @@ static TcOperand op_scratch(const float* x, int S, int Sp, int nb, int mn) {
 }
 
 static bool at_gemm(sb_ctx_t* c, const TcOperand& A, const TcOperand& B, float* C, long ldc, long cbs, int M, int N, int K,
-                    int acc, int nb, int causal) {
+                    int acc, int nb, int causal, const TcEpi* epi = nullptr) {
     TcProblem p; p.A = A; p.B = B; p.C = C; p.ldc = ldc; p.c_batch_stride = cbs; p.M = M; p.N = N; p.K = K; p.acc = acc; p.nbatch = nb; p.causal = causal;
+    if (epi) p.epi = *epi; else memset(&p.epi, 0, sizeof p.epi);
     return tc_launch(c, p, 3);
+}
+// per-(token, head) vector (lse or D, laid out [token][Hq]) as seen by a launch over heads head0, head0+step, ...
+static TcEpi at_epi(int mode, float scale, const float* vec, int tok0, int Hq, int head0, int head_step, const float* aux) {
+    TcEpi e; e.mode = mode; e.scale = scale; e.vec = vec + (size_t)tok0 * Hq + head0; e.vec_row_stride = Hq; e.vec_batch_stride = head_step; e.aux = aux;
+    return e;
 }
 
 // heads per launch: as many as keep the causal part of their score scratch inside the budget
@@ -247,12 +280,24 @@ extern "C" int sb_attention_tc_backward(sb_ctx_t* c, const float* Q, const float
             for (int i0 = 0; i0 < Hkv && ok; i0 += G) {
                 const int nb = min(G, Hkv - i0), qh0 = r + i0 * g;
                 const long sb = (long)Sp * Sp;
-                ok = ok && at_gemm(c, op_tokens(Q, t0, S, qd, Hq, hd, qh0, g), op_tokens(K, t0, S, kvd, Hkv, hd, i0, 1),
-                                   b0, Sp, sb, S, S, hd, 0, nb, TC_CAUSAL_SKIP_UPPER);                                    // S
-                ok = ok && at_gemm(c, op_tokens(dO, t0, S, qd, Hq, hd, qh0, g), op_tokens(V, t0, S, kvd, Hkv, hd, i0, 1),
-                                   b1, Sp, sb, S, S, hd, 0, nb, TC_CAUSAL_SKIP_UPPER);                                    // dP
-                at_ds_rows<<<dim3(S, nb), 256, 0, s>>>(b0, b1, lse, D, S, Sp, Hq, qh0, g, t0, scale);                    // P -> b0, dS -> b1
-                c->launches++;
+                static int fused = -1;
+                if (fused < 0) { const char* e = getenv("SERAPH_B200_ATTN_FUSED"); fused = (e && e[0] == '0') ? 0 : 1; }      // measured on one device: 79 ms fused against 83 ms per step
+                if (fused) {
+                    // P = exp(S*scale - lse) and dS = P o (dP - D) * scale come straight out of the two products' epilogues
+                    const TcEpi e_p = at_epi(TC_EPI_EXP, scale, lse, t0, Hq, qh0, g, nullptr);
+                    const TcEpi e_ds = at_epi(TC_EPI_DS, scale, D, t0, Hq, qh0, g, b0);
+                    ok = ok && at_gemm(c, op_tokens(Q, t0, S, qd, Hq, hd, qh0, g), op_tokens(K, t0, S, kvd, Hkv, hd, i0, 1),
+                                       b0, Sp, sb, S, S, hd, 0, nb, TC_CAUSAL_SKIP_UPPER, &e_p);                          // P
+                    ok = ok && at_gemm(c, op_tokens(dO, t0, S, qd, Hq, hd, qh0, g), op_tokens(V, t0, S, kvd, Hkv, hd, i0, 1),
+                                       b1, Sp, sb, S, S, hd, 0, nb, TC_CAUSAL_SKIP_UPPER, &e_ds);                         // dS
+                } else {
+                    ok = ok && at_gemm(c, op_tokens(Q, t0, S, qd, Hq, hd, qh0, g), op_tokens(K, t0, S, kvd, Hkv, hd, i0, 1),
+                                       b0, Sp, sb, S, S, hd, 0, nb, TC_CAUSAL_SKIP_UPPER);                                // S
+                    ok = ok && at_gemm(c, op_tokens(dO, t0, S, qd, Hq, hd, qh0, g), op_tokens(V, t0, S, kvd, Hkv, hd, i0, 1),
+                                       b1, Sp, sb, S, S, hd, 0, nb, TC_CAUSAL_SKIP_UPPER);                                // dP
+                    at_ds_rows<<<dim3(S, nb), 256, 0, s>>>(b0, b1, lse, D, S, Sp, Hq, qh0, g, t0, scale);                // P -> b0, dS -> b1
+                    c->launches++;
+                }
                 const int acc = (r > 0 || accumulate_kv) ? 1 : 0;
                 ok = ok && at_gemm(c, op_scratch(b1, S, Sp, nb, 0), op_tokens_mn(K, t0, kvd, Hkv, hd, i0, 1),
                                    dQ + (size_t)t0 * qd + (size_t)qh0 * hd, qd, (long)g * hd, S, hd, S, 0, nb, TC_CAUSAL_K_UPTO_M);   // dQ = dS K

@@ -52,6 +52,7 @@ extern "C" int sb_gemm_tc(sb_ctx_t* c, const float* A, const float* B, float* C,
     if ((a_kmajor || b_kmajor) && (K & 3)) return 1;                     // in-place K-major rows need a 16-byte pitch
     const bool x3 = (mode == SB_GEMM_FP32X3);
     TcProblem p;
+    memset(&p.epi, 0, sizeof p.epi);
     p.C = C; p.ldc = N; p.c_batch_stride = 0; p.M = M; p.N = N; p.K = K; p.acc = acc; p.nbatch = 1; p.causal = TC_CAUSAL_NONE;
     // direct path: the pair kernel on the caller's arrays (rows of either layout must be 16-byte multiples)
     if (c->gemm_pair && M > 128 && N > 128 && (a_kmajor ? (K & 3) == 0 : (M & 3) == 0) && (b_kmajor ? (K & 3) == 0 : (N & 3) == 0)) {

@@ -67,10 +67,20 @@ struct TcOperand {
     int c2_dim; long c2_stride;          // third tensor-map dimension (floats); c2_dim = 1 for a plain matrix
     int c2_base, c2_step;                // slot of batch b = c2_base + b*c2_step
 };
+// What the epilogue writes for an accumulator value x at (row, col) of batch b (attention's score-sized products):
+//   TC_EPI_EXP  col <= row ? exp(x*scale - vec[row*vec_row_stride + b*vec_batch_stride]) : 0      (P from S and the log-sum-exp)
+//   TC_EPI_DS   aux[row][col] * (x - vec[...]) * scale, aux laid out like C                        (dS from dP, P and D)
+enum { TC_EPI_PLAIN = 0, TC_EPI_EXP, TC_EPI_DS };
+struct TcEpi {
+    int mode; float scale;
+    const float* vec; long vec_row_stride, vec_batch_stride;
+    const float* aux;
+};
 struct TcProblem {
     TcOperand A, B;
     float* C; long ldc; long c_batch_stride;
     int M, N, K, acc, nbatch, causal;
+    TcEpi epi;
 };
 
 // --------------------------------------------------------------------------- PTX helpers
@@ -238,7 +248,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
                const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
                float* __restrict__ Cbase, long ldc, long c_batch_stride, int M, int N, int K, int acc, int causal,
                int a_c2_base, int a_c2_step, int b_c2_base, int b_c2_step, int swap_mask,
-               int split_full, int split_s, float* __restrict__ partial, int* status) {
+               int split_full, int split_s, float* __restrict__ partial, const TcEpi epi, int* status) {
     constexpr int SWZ = BK * 4;
     constexpr int BROWS = BN / CTAS;                             // B rows this CTA loads
     constexpr int TILE_M = TC_BM * CTAS;
@@ -270,6 +280,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
     const bool split = split_s > 1 && tile_id >= split_full;
     if (split) { const int t = tile_id - split_full; piece = t % split_s; tile_id = split_full + t / split_s; }
     tc_raster(tile_id, tiles_m, tiles_n, TC_GROUP_M / CTAS, &m_tile, &n_tile);
+    if (causal == TC_CAUSAL_K_UPTO_M) m_tile = tiles_m - 1 - m_tile;      // longest k ranges first, so the last wave is made of short tiles
     const int m0 = m_tile * TILE_M + (int)rank * TC_BM, n0 = n_tile * BN;      // this CTA's rows of A and C; the tile's columns
     const int nb0 = n0 + (int)rank * BROWS;                                     // this CTA's rows of B
     int kb_begin = 0, kb_end = (K + BK - 1) / BK;
@@ -481,26 +492,80 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
             const long ld = split ? (long)BN : ldc;
             const int rows_valid = split ? TC_BM : M - m0, cols_valid = split ? BN : N - n0;
             const int accf = split ? 0 : acc;
-            const bool vec = ((ld & 3) == 0) && ((((uintptr_t)dst) & 15) == 0);
-            for (int r = ew; r < TC_BM; r += TC_EPI_WARPS) {
-                if (r >= rows_valid) break;
-                const float* srow = stage + (size_t)r * SLD;
-                float* crow = dst + (size_t)r * ld;
-                if (vec) {
+            const int emode = split ? TC_EPI_PLAIN : epi.mode;
+            const bool vec = ((ld & 3) == 0) && ((((uintptr_t)dst) & 15) == 0) && (emode != TC_EPI_DS || (((uintptr_t)epi.aux) & 15) == 0);
+            constexpr int RPW = TC_BM / TC_EPI_WARPS;            // rows per epilogue warp
+            constexpr int NH = (BN + 127) / 128;                 // float4 per lane and row
+            // per-row vector entries of this warp's rows, fetched together (one latency, not one per row)
+            float rowv[RPW];
 #pragma unroll
-                    for (int h = 0; h < (BN + 127) / 128; h++) {
-                        const int col = (h * 32 + lane) * 4;
-                        if (col < BN && col + 3 < cols_valid) {
-                            float4 v = *(const float4*)(srow + col);
-                            if (accf) { float4 o = *(const float4*)(crow + col); v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
-                            *(float4*)(crow + col) = v;
-                        } else if (col < BN) {
-                            for (int j = 0; j < 4; j++) if (col + j < cols_valid) crow[col + j] = accf ? crow[col + j] + srow[col + j] : srow[col + j];
+            for (int i = 0; i < RPW; i++) {
+                const int r = ew + i * TC_EPI_WARPS;
+                rowv[i] = (emode != TC_EPI_PLAIN && r < rows_valid)
+                              ? epi.vec[(size_t)(m0 + r) * epi.vec_row_stride + (size_t)batch * epi.vec_batch_stride] : 0.f;
+            }
+            const float* abase = emode == TC_EPI_DS ? epi.aux + (size_t)batch * c_batch_stride + (size_t)m0 * ldc + n0 : nullptr;
+#pragma unroll
+            for (int i0 = 0; i0 < RPW; i0 += 4) {
+                // what the rows need from global memory (P for dS, or the old C when accumulating) is in flight for four rows together
+                float4 av[4][NH];
+                const float* pbase = emode == TC_EPI_DS ? abase : dst;
+                const long pld = emode == TC_EPI_DS ? ldc : ld;
+                if ((emode == TC_EPI_DS || accf) && vec) {
+#pragma unroll
+                    for (int ii = 0; ii < 4; ii++) {
+                        const int r = ew + (i0 + ii) * TC_EPI_WARPS;
+#pragma unroll
+                        for (int h = 0; h < NH; h++) {
+                            const int col = (h * 32 + lane) * 4;
+                            av[ii][h] = (r < rows_valid && col < BN && col + 3 < cols_valid) ? *(const float4*)(pbase + (size_t)r * pld + col)
+                                                                                              : make_float4(0.f, 0.f, 0.f, 0.f);
                         }
                     }
-                } else {
-                    for (int col = lane; col < BN && col < cols_valid; col += 32)
-                        crow[col] = accf ? crow[col] + srow[col] : srow[col];
+                }
+#pragma unroll
+                for (int ii = 0; ii < 4; ii++) {
+                    const int r = ew + (i0 + ii) * TC_EPI_WARPS;
+                    if (r >= rows_valid) break;
+                    const float* srow = stage + (size_t)r * SLD;
+                    float* crow = dst + (size_t)r * ld;
+                    const int grow = m0 + r;
+                    const float rv = rowv[i0 + ii];
+                    const float* arow = emode == TC_EPI_DS ? abase + (size_t)r * ldc : nullptr;
+                    if (vec) {
+#pragma unroll
+                        for (int h = 0; h < NH; h++) {
+                            const int col = (h * 32 + lane) * 4;
+                            if (col < BN && col + 3 < cols_valid) {
+                                float4 v = *(const float4*)(srow + col);
+                                if (emode == TC_EPI_EXP) {
+                                    const int k0 = n0 + col;
+                                    v.x = k0 <= grow ? expf(v.x * epi.scale - rv) : 0.f;     v.y = k0 + 1 <= grow ? expf(v.y * epi.scale - rv) : 0.f;
+                                    v.z = k0 + 2 <= grow ? expf(v.z * epi.scale - rv) : 0.f; v.w = k0 + 3 <= grow ? expf(v.w * epi.scale - rv) : 0.f;
+                                } else if (emode == TC_EPI_DS) {
+                                    const float4 pv = av[ii][h];
+                                    v.x = pv.x * (v.x - rv) * epi.scale; v.y = pv.y * (v.y - rv) * epi.scale;
+                                    v.z = pv.z * (v.z - rv) * epi.scale; v.w = pv.w * (v.w - rv) * epi.scale;
+                                }
+                                if (accf && emode != TC_EPI_DS) { const float4 o = av[ii][h]; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+                                *(float4*)(crow + col) = v;
+                            } else if (col < BN) {
+                                for (int j = 0; j < 4; j++) if (col + j < cols_valid) {
+                                    float x = srow[col + j];
+                                    if (emode == TC_EPI_EXP) x = n0 + col + j <= grow ? expf(x * epi.scale - rv) : 0.f;
+                                    else if (emode == TC_EPI_DS) x = arow[col + j] * (x - rv) * epi.scale;
+                                    crow[col + j] = accf ? crow[col + j] + x : x;
+                                }
+                            }
+                        }
+                    } else {
+                        for (int col = lane; col < BN && col < cols_valid; col += 32) {
+                            float x = srow[col];
+                            if (emode == TC_EPI_EXP) x = n0 + col <= grow ? expf(x * epi.scale - rv) : 0.f;
+                            else if (emode == TC_EPI_DS) x = arow[col] * (x - rv) * epi.scale;
+                            crow[col] = accf ? crow[col] + x : x;
+                        }
+                    }
                 }
             }
         }
@@ -714,12 +779,12 @@ static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
         at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
         cfg.attrs = at; cfg.numAttrs = 1;
         if (cudaLaunchKernelEx(&cfg, kern, mAh, mAl, mBh, mBl, p.C, p.ldc, p.c_batch_stride, p.M, p.N, p.K, p.acc, p.causal,
-                               p.A.c2_base, p.A.c2_step, p.B.c2_base, p.B.c2_step, swap_mask, split_full, split_s, partial,
+                               p.A.c2_base, p.A.c2_step, p.B.c2_base, p.B.c2_step, swap_mask, split_full, split_s, partial, p.epi,
                                c->d_status) != cudaSuccess) return false;
     } else {
         kern<<<grid, THREADS, smem, (cudaStream_t)c->pub.stream>>>(mAh, mAl, mBh, mBl, p.C, p.ldc, p.c_batch_stride, p.M, p.N, p.K, p.acc,
                                                                      p.causal, p.A.c2_base, p.A.c2_step, p.B.c2_base, p.B.c2_step,
-                                                                     swap_mask, split_full, split_s, partial, c->d_status);
+                                                                     swap_mask, split_full, split_s, partial, p.epi, c->d_status);
     }
     c->launches++;
     if (split_s > 1) {

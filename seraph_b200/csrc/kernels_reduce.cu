@@ -158,69 +158,88 @@ __global__ void __launch_bounds__(RB_THREADS) rmsnorm_warp_kernel(const float* _
     }
 }
 
-template <int NV>
-__global__ void __launch_bounds__(RB_THREADS) rmsnorm_bwd_warp_kernel(const float* __restrict__ x, const float* __restrict__ w,
-                                                                      const float* __restrict__ dy, const float* resid, float* dx,
-                                                                      float* __restrict__ partial, int rows, int cols, float eps) {
-    const int lane = threadIdx.x & 31, warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
-    const int c4 = cols >> 2;
-    float4 acc[NV];
+// RMSNorm backward, four rows per pass of a 256-thread CTA.  Thread t owns the float4 column chunks t, t+256, ...
+// (NC of them) of every row the CTA visits, so its dscale partial stays in NC float4 registers; the x, dy and
+// residual chunks of four rows are requested together, the eight row sums (sum x^2 and sum dy*w*x of each row)
+// go through one CTA reduction, and two CTAs share an SM.  One dscale partial row per CTA, summed in CTA order.
+#define RNB_ROWS 4
+template <int NC>
+__global__ void __launch_bounds__(RB_THREADS, 2) rmsnorm_bwd_rows4_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                                          const float* __restrict__ dy, const float* resid, float* dx,
+                                                                          float* __restrict__ partial, int rows, int cols, float eps) {
+    __shared__ float s_red[RB_THREADS / 32][2 * RNB_ROWS];
+    __shared__ float s_tot[2 * RNB_ROWS];
+    const int c4 = cols >> 2, lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    float4 acc[NC], sc[NC];
 #pragma unroll
-    for (int i = 0; i < NV; i++) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int r = warp; r < rows; r += nwarps) {
-        const float4* xr = (const float4*)(x + (size_t)r * cols); const float4* gr = (const float4*)(dy + (size_t)r * cols);
-        float4 v[NV], g[NV];
-        float ss = 0.f, cp = 0.f;
-#pragma unroll
-        for (int i = 0; i < NV; i++) {
-            int j = lane + 32 * i;
-            if (j < c4) { v[i] = xr[j]; g[i] = gr[j]; } else { v[i] = make_float4(0.f, 0.f, 0.f, 0.f); g[i] = v[i]; }
-        }
-#pragma unroll
-        for (int i = 0; i < NV; i++) {
-            int j = lane + 32 * i;
-            if (j < c4) {
-                float4 s = ((const float4*)w)[j];
-                ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
-                cp += g[i].x * s.x * v[i].x + g[i].y * s.y * v[i].y + g[i].z * s.z * v[i].z + g[i].w * s.w * v[i].w;
-            }
-        }
-        ss = warp_sum(ss); cp = warp_sum(cp);
-        const float inv = 1.0f / sqrtf(ss / cols + eps);
-        const float k = inv * inv * inv / cols * cp;
-        float4* dr = (float4*)(dx + (size_t)r * cols); const float4* rr = resid ? (const float4*)(resid + (size_t)r * cols) : nullptr;
-#pragma unroll
-        for (int i = 0; i < NV; i++) {
-            int j = lane + 32 * i;
-            if (j < c4) {
-                float4 s = ((const float4*)w)[j], o;
-                acc[i].x += g[i].x * v[i].x * inv; acc[i].y += g[i].y * v[i].y * inv; acc[i].z += g[i].z * v[i].z * inv; acc[i].w += g[i].w * v[i].w * inv;
-                o.x = g[i].x * s.x * inv - v[i].x * k; o.y = g[i].y * s.y * inv - v[i].y * k;
-                o.z = g[i].z * s.z * inv - v[i].z * k; o.w = g[i].w * s.w * inv - v[i].w * k;
-                if (rr) { float4 q = rr[j]; o.x += q.x; o.y += q.y; o.z += q.z; o.w += q.w; }
-                dr[j] = o;
-            }
-        }
+    for (int i = 0; i < NC; i++) {
+        acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        const int j = threadIdx.x + RB_THREADS * i;
+        sc[i] = j < c4 ? ((const float4*)w)[j] : acc[i];
     }
-    // the warps of the CTA add their partials in warp order in shared memory: one partial row per CTA
-    extern __shared__ float4 s_acc[];
-    const int wib = threadIdx.x >> 5;
-    for (int w = 0; w < RB_THREADS / 32; w++) {
-        if (wib == w) {
+    const int ngroups = (rows + RNB_ROWS - 1) / RNB_ROWS;
+    for (int gidx = blockIdx.x; gidx < ngroups; gidx += gridDim.x) {
+        const int r0 = gidx * RNB_ROWS;
+        float4 v[RNB_ROWS][NC], g[RNB_ROWS][NC], q[RNB_ROWS][NC];
 #pragma unroll
-            for (int i = 0; i < NV; i++) {
-                int j = lane + 32 * i;
+        for (int rr = 0; rr < RNB_ROWS; rr++)
+#pragma unroll
+            for (int i = 0; i < NC; i++) {
+                const int j = threadIdx.x + RB_THREADS * i;
+                const bool in = r0 + rr < rows && j < c4;
+                const size_t o = (size_t)(r0 + rr) * c4 + j;
+                v[rr][i] = in ? ((const float4*)x)[o] : make_float4(0.f, 0.f, 0.f, 0.f);
+                g[rr][i] = in ? ((const float4*)dy)[o] : make_float4(0.f, 0.f, 0.f, 0.f);
+                q[rr][i] = (in && resid) ? ((const float4*)resid)[o] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        float part[2 * RNB_ROWS];
+#pragma unroll
+        for (int rr = 0; rr < RNB_ROWS; rr++) {
+            float ss = 0.f, cp = 0.f;
+#pragma unroll
+            for (int i = 0; i < NC; i++) {
+                ss += v[rr][i].x * v[rr][i].x + v[rr][i].y * v[rr][i].y + v[rr][i].z * v[rr][i].z + v[rr][i].w * v[rr][i].w;
+                cp += g[rr][i].x * sc[i].x * v[rr][i].x + g[rr][i].y * sc[i].y * v[rr][i].y + g[rr][i].z * sc[i].z * v[rr][i].z +
+                      g[rr][i].w * sc[i].w * v[rr][i].w;
+            }
+            part[2 * rr] = warp_sum(ss); part[2 * rr + 1] = warp_sum(cp);
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int k = 0; k < 2 * RNB_ROWS; k++) s_red[wib][k] = part[k];
+        }
+        __syncthreads();
+        if (threadIdx.x < 2 * RNB_ROWS) {
+            float t = 0.f;
+#pragma unroll
+            for (int wv = 0; wv < RB_THREADS / 32; wv++) t += s_red[wv][threadIdx.x];
+            s_tot[threadIdx.x] = t;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int rr = 0; rr < RNB_ROWS; rr++) {
+            if (r0 + rr >= rows) break;
+            const float inv = 1.0f / sqrtf(s_tot[2 * rr] / cols + eps);
+            const float k = inv * inv * inv / cols * s_tot[2 * rr + 1];
+#pragma unroll
+            for (int i = 0; i < NC; i++) {
+                const int j = threadIdx.x + RB_THREADS * i;
                 if (j < c4) {
-                    float4 a = acc[i];
-                    if (w > 0) { float4 o = s_acc[j]; a.x += o.x; a.y += o.y; a.z += o.z; a.w += o.w; }
-                    s_acc[j] = a;
+                    float4 o;
+                    acc[i].x += g[rr][i].x * v[rr][i].x * inv; acc[i].y += g[rr][i].y * v[rr][i].y * inv;
+                    acc[i].z += g[rr][i].z * v[rr][i].z * inv; acc[i].w += g[rr][i].w * v[rr][i].w * inv;
+                    o.x = g[rr][i].x * sc[i].x * inv - v[rr][i].x * k + q[rr][i].x; o.y = g[rr][i].y * sc[i].y * inv - v[rr][i].y * k + q[rr][i].y;
+                    o.z = g[rr][i].z * sc[i].z * inv - v[rr][i].z * k + q[rr][i].z; o.w = g[rr][i].w * sc[i].w * inv - v[rr][i].w * k + q[rr][i].w;
+                    ((float4*)dx)[(size_t)(r0 + rr) * c4 + j] = o;
                 }
             }
         }
-        __syncthreads();
     }
-    float4* pr = (float4*)(partial + (size_t)blockIdx.x * cols);
-    for (int j = threadIdx.x; j < c4; j += blockDim.x) pr[j] = s_acc[j];
+#pragma unroll
+    for (int i = 0; i < NC; i++) {
+        const int j = threadIdx.x + RB_THREADS * i;
+        if (j < c4) ((float4*)(partial + (size_t)blockIdx.x * cols))[j] = acc[i];
+    }
 }
 
 // dscale[c] += sum over partial rows of partial[b][c], in a fixed order: 32 columns per CTA, the rows
@@ -512,16 +531,14 @@ void sb_rmsnorm_backward(sb_ctx_t* c, const float* x, const float* w, const floa
     if (cols > RB_THREADS * 4 * RN_MAX_SWEEP || (cols % 4 != 0 && cols > RB_THREADS * RN_MAX_SWEEP * 4)) { sb_set_status(c, SB_ERR_SIZE); return; }
     int vec = (cols % 4 == 0) && aligned16(x) && aligned16(w) && aligned16(dy) && aligned16(dx_out) && (!resid || aligned16(resid));
     if (vec && cols <= 2048 && rows >= 64) {
-        // warp per row, rows kept in registers; one dscale partial per CTA, summed in CTA order
-        int wgrid = (rows + 7) / 8; if (wgrid > sm_count(c)) wgrid = sm_count(c);
+        // four rows per CTA pass, two CTAs per SM; one dscale partial per CTA, summed in CTA order
+        int wgrid = (rows + RNB_ROWS - 1) / RNB_ROWS; if (wgrid > 2 * sm_count(c)) wgrid = 2 * sm_count(c);
         float* partial = (float*)sb_scratch(c, (size_t)wgrid * cols * sizeof(float));
         if (!partial) return;
         cudaStream_t st = (cudaStream_t)c->pub.stream;
-        size_t sm = (size_t)cols * sizeof(float);
         int tk = sb_tick_begin(c, SB_CLS_NORM_BWD);
-        if (cols <= 512)       rmsnorm_bwd_warp_kernel<4><<<wgrid, RB_THREADS, sm, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
-        else if (cols <= 1024) rmsnorm_bwd_warp_kernel<8><<<wgrid, RB_THREADS, sm, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
-        else                   rmsnorm_bwd_warp_kernel<16><<<wgrid, RB_THREADS, sm, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
+        if (cols <= 1024) rmsnorm_bwd_rows4_kernel<1><<<wgrid, RB_THREADS, 0, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
+        else              rmsnorm_bwd_rows4_kernel<2><<<wgrid, RB_THREADS, 0, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
         colsum_partials_kernel<<<(cols + 31) / 32, 256, 0, st>>>(partial, dscale, wgrid, cols);
         sb_tick_end(c, tk, 0.0, (resid ? 16.0 : 12.0) * rows * cols);
         c->launches += 2;

@@ -24,8 +24,8 @@
 // CTA: tile 128 x BN, ring of STAGES shared-memory stages of BK floats of k (one swizzle span).
 // Warp 0 = TMA producer, warp 1 = MMA issuer (one elected lane each; warp 1 owns the TMEM
 // allocation), warps 2-9 = epilogue: two warps per TMEM lane quarter, BN/2 columns each.
-// The finished tile is staged in the (by then idle) operand stages so that global stores are
-// whole rows.  Every mbarrier wait is bounded: a wait that runs out sets the status word, the
+// The finished tile is staged in the (by then idle) operand stages and leaves row by row
+// through bulk copies (cp.async.bulk, or its f32 add form when accumulating into C).  Every mbarrier wait is bounded: a wait that runs out sets the status word, the
 // CTA drains, frees its TMEM and returns, and the host reports SB_ERR_TIMEOUT.
 //
 // Causal modes (attention; rows/columns are positions inside one sequence):
@@ -474,99 +474,113 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
             }
         }
         if (!ok && lane == 0) atomicExch(status, SB_ERR_TIMEOUT);
-        // The last chunk has arrived, so every MMA has finished reading the operand stages: their
-        // shared memory now stages the 128 x BN tile and the global stores are whole contiguous rows.
+        // The last chunk has arrived, so every MMA has finished reading the operand stages: their shared
+        // memory now stages the 128 x BN tile, and whole rows leave through the bulk-copy engine (a plain copy,
+        // or an f32 add into C when accumulating: every element of C is touched by one CTA, so the sum does not
+        // depend on timing).  Measured: warps storing the tile themselves took 16 us per tile, the bulk copies 2 us.
         constexpr int SLD = BN + 4;                   // padded row pitch (floats): conflict-free 16-byte accesses
+        constexpr int RPW = TC_BM / TC_EPI_WARPS;     // rows per epilogue warp in the row-wise passes
+        constexpr int NH = (BN + 127) / 128;          // float4 per lane and row
         float* stage = (float*)smem;
+        // destination: the tile's place in C, or (a piece of a split tile) its own block of `partial`
+        float* dst = split ? partial + ((size_t)((tile_id - split_full) * split_s + piece) * CTAS + rank) * (size_t)(TC_BM * BN)
+                           : C + (size_t)m0 * ldc + n0;
+        const long ld = split ? (long)BN : ldc;
+        const int rows_valid = split ? TC_BM : M - m0, cols_valid = split ? BN : N - n0;
+        const int accf = split ? 0 : acc;
+        const int emode = split ? TC_EPI_PLAIN : epi.mode;
+        const bool vec = ((ld & 3) == 0) && ((((uintptr_t)dst) & 15) == 0) && (emode != TC_EPI_DS || (((uintptr_t)epi.aux) & 15) == 0);
+        const bool bulk = vec && (cols_valid >= BN || (cols_valid & 3) == 0);      // rows are 16-byte multiples at 16-byte addresses
         {
-            float* srow = stage + (size_t)(q * 32 + lane) * SLD + col0;
+            // each thread holds one row of the tile; TC_EPI_EXP: P = exp(S*scale - lse[row]), zero past the diagonal
+            const int r = q * 32 + lane, grow = m0 + r;
+            float rv = 0.f;
+            if (emode == TC_EPI_EXP && r < rows_valid) rv = epi.vec[(size_t)grow * epi.vec_row_stride + (size_t)batch * epi.vec_batch_stride];
+            float* srow = stage + (size_t)r * SLD + col0;
+            if (emode == TC_EPI_EXP) {
+                const int kmax = grow - (n0 + col0);          // columns j <= kmax are on or below the diagonal
 #pragma unroll
-            for (int j = 0; j < COLS_PER_WARP; j += 4)
-                *(float4*)(srow + j) = make_float4(accr[j], accr[j + 1], accr[j + 2], accr[j + 3]);
+                for (int j = 0; j < COLS_PER_WARP; j += 4) {
+                    float4 v;
+                    v.x = j <= kmax ? expf(accr[j] * epi.scale - rv) : 0.f;         v.y = j + 1 <= kmax ? expf(accr[j + 1] * epi.scale - rv) : 0.f;
+                    v.z = j + 2 <= kmax ? expf(accr[j + 2] * epi.scale - rv) : 0.f; v.w = j + 3 <= kmax ? expf(accr[j + 3] * epi.scale - rv) : 0.f;
+                    *(float4*)(srow + j) = v;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < COLS_PER_WARP; j += 4)
+                    *(float4*)(srow + j) = make_float4(accr[j], accr[j + 1], accr[j + 2], accr[j + 3]);
+            }
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * TC_EPI_WARPS) : "memory");      // epilogue warps only
-        if (ok) {
-            // destination: the tile's place in C, or (a piece of a split tile) its own block of `partial`
-            float* dst = split ? partial + ((size_t)((tile_id - split_full) * split_s + piece) * CTAS + rank) * (size_t)(TC_BM * BN)
-                               : C + (size_t)m0 * ldc + n0;
-            const long ld = split ? (long)BN : ldc;
-            const int rows_valid = split ? TC_BM : M - m0, cols_valid = split ? BN : N - n0;
-            const int accf = split ? 0 : acc;
-            const int emode = split ? TC_EPI_PLAIN : epi.mode;
-            const bool vec = ((ld & 3) == 0) && ((((uintptr_t)dst) & 15) == 0) && (emode != TC_EPI_DS || (((uintptr_t)epi.aux) & 15) == 0);
-            constexpr int RPW = TC_BM / TC_EPI_WARPS;            // rows per epilogue warp
-            constexpr int NH = (BN + 127) / 128;                 // float4 per lane and row
-            // per-row vector entries of this warp's rows, fetched together (one latency, not one per row)
+        if (bulk && emode != TC_EPI_DS) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the bulk copies read these writes
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * TC_EPI_WARPS) : "memory");                              // epilogue warps only
+        if (ok && emode == TC_EPI_DS) {
+            // dS = P o (dP - D[row]) * scale, row-wise in the staged tile (P is read with whole-row accesses, four rows in flight)
             float rowv[RPW];
 #pragma unroll
             for (int i = 0; i < RPW; i++) {
                 const int r = ew + i * TC_EPI_WARPS;
-                rowv[i] = (emode != TC_EPI_PLAIN && r < rows_valid)
-                              ? epi.vec[(size_t)(m0 + r) * epi.vec_row_stride + (size_t)batch * epi.vec_batch_stride] : 0.f;
+                rowv[i] = r < rows_valid ? epi.vec[(size_t)(m0 + r) * epi.vec_row_stride + (size_t)batch * epi.vec_batch_stride] : 0.f;
             }
-            const float* abase = emode == TC_EPI_DS ? epi.aux + (size_t)batch * c_batch_stride + (size_t)m0 * ldc + n0 : nullptr;
+            const float* abase = epi.aux + (size_t)batch * c_batch_stride + (size_t)m0 * ldc + n0;
 #pragma unroll
             for (int i0 = 0; i0 < RPW; i0 += 4) {
-                // what the rows need from global memory (P for dS, or the old C when accumulating) is in flight for four rows together
                 float4 av[4][NH];
-                const float* pbase = emode == TC_EPI_DS ? abase : dst;
-                const long pld = emode == TC_EPI_DS ? ldc : ld;
-                if ((emode == TC_EPI_DS || accf) && vec) {
 #pragma unroll
-                    for (int ii = 0; ii < 4; ii++) {
-                        const int r = ew + (i0 + ii) * TC_EPI_WARPS;
+                for (int ii = 0; ii < 4; ii++) {
+                    const int r = ew + (i0 + ii) * TC_EPI_WARPS;
 #pragma unroll
-                        for (int h = 0; h < NH; h++) {
-                            const int col = (h * 32 + lane) * 4;
-                            av[ii][h] = (r < rows_valid && col < BN && col + 3 < cols_valid) ? *(const float4*)(pbase + (size_t)r * pld + col)
-                                                                                              : make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int h = 0; h < NH; h++) {
+                        const int col = (h * 32 + lane) * 4;
+                        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (r < rows_valid && col < BN) {
+                            const float* ap = abase + (size_t)r * ldc + col;
+                            if (vec && col + 3 < cols_valid) t = *(const float4*)ap;
+                            else { if (col < cols_valid) t.x = ap[0]; if (col + 1 < cols_valid) t.y = ap[1]; if (col + 2 < cols_valid) t.z = ap[2]; if (col + 3 < cols_valid) t.w = ap[3]; }
                         }
+                        av[ii][h] = t;
                     }
                 }
 #pragma unroll
                 for (int ii = 0; ii < 4; ii++) {
                     const int r = ew + (i0 + ii) * TC_EPI_WARPS;
-                    if (r >= rows_valid) break;
-                    const float* srow = stage + (size_t)r * SLD;
-                    float* crow = dst + (size_t)r * ld;
-                    const int grow = m0 + r;
                     const float rv = rowv[i0 + ii];
-                    const float* arow = emode == TC_EPI_DS ? abase + (size_t)r * ldc : nullptr;
-                    if (vec) {
 #pragma unroll
-                        for (int h = 0; h < NH; h++) {
-                            const int col = (h * 32 + lane) * 4;
-                            if (col < BN && col + 3 < cols_valid) {
-                                float4 v = *(const float4*)(srow + col);
-                                if (emode == TC_EPI_EXP) {
-                                    const int k0 = n0 + col;
-                                    v.x = k0 <= grow ? expf(v.x * epi.scale - rv) : 0.f;     v.y = k0 + 1 <= grow ? expf(v.y * epi.scale - rv) : 0.f;
-                                    v.z = k0 + 2 <= grow ? expf(v.z * epi.scale - rv) : 0.f; v.w = k0 + 3 <= grow ? expf(v.w * epi.scale - rv) : 0.f;
-                                } else if (emode == TC_EPI_DS) {
-                                    const float4 pv = av[ii][h];
-                                    v.x = pv.x * (v.x - rv) * epi.scale; v.y = pv.y * (v.y - rv) * epi.scale;
-                                    v.z = pv.z * (v.z - rv) * epi.scale; v.w = pv.w * (v.w - rv) * epi.scale;
-                                }
-                                if (accf && emode != TC_EPI_DS) { const float4 o = av[ii][h]; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
-                                *(float4*)(crow + col) = v;
-                            } else if (col < BN) {
-                                for (int j = 0; j < 4; j++) if (col + j < cols_valid) {
-                                    float x = srow[col + j];
-                                    if (emode == TC_EPI_EXP) x = n0 + col + j <= grow ? expf(x * epi.scale - rv) : 0.f;
-                                    else if (emode == TC_EPI_DS) x = arow[col + j] * (x - rv) * epi.scale;
-                                    crow[col + j] = accf ? crow[col + j] + x : x;
-                                }
-                            }
-                        }
-                    } else {
-                        for (int col = lane; col < BN && col < cols_valid; col += 32) {
-                            float x = srow[col];
-                            if (emode == TC_EPI_EXP) x = n0 + col <= grow ? expf(x * epi.scale - rv) : 0.f;
-                            else if (emode == TC_EPI_DS) x = arow[col] * (x - rv) * epi.scale;
-                            crow[col] = accf ? crow[col] + x : x;
+                    for (int h = 0; h < NH; h++) {
+                        const int col = (h * 32 + lane) * 4;
+                        if (col < BN) {
+                            float4* sp = (float4*)(stage + (size_t)r * SLD + col);
+                            float4 v = *sp; const float4 pv = av[ii][h];
+                            v.x = pv.x * (v.x - rv) * epi.scale; v.y = pv.y * (v.y - rv) * epi.scale;
+                            v.z = pv.z * (v.z - rv) * epi.scale; v.w = pv.w * (v.w - rv) * epi.scale;
+                            *sp = v;
                         }
                     }
                 }
+            }
+            if (bulk) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();                              // a warp copies out the rows it has just transformed
+        }
+        if (ok && bulk) {
+            const uint32_t bytes = (uint32_t)min(cols_valid, BN) * 4u;
+            if (lane < RPW) {
+                const int r = ew + lane * TC_EPI_WARPS;
+                if (r < rows_valid) {
+                    const uint32_t src = smem_u32(stage + (size_t)r * SLD);
+                    float* gp = dst + (size_t)r * ld;
+                    if (accf) asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(gp), "r"(src), "r"(bytes) : "memory");
+                    else      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gp), "r"(src), "r"(bytes) : "memory");
+                }
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            }
+        } else if (ok) {
+            // ragged or unaligned rows: the warps store the (already transformed) tile themselves
+            for (int r = ew; r < TC_BM && r < rows_valid; r += TC_EPI_WARPS) {
+                const float* srow = stage + (size_t)r * SLD;
+                float* crow = dst + (size_t)r * ld;
+                for (int col = lane; col < BN && col < cols_valid; col += 32)
+                    crow[col] = accf ? crow[col] + srow[col] : srow[col];
             }
         }
         tc_fence_before();

@@ -61,26 +61,32 @@ __global__ void __launch_bounds__(256) at_softmax_rows(float* __restrict__ Sb, f
     float* row = Sb + ((size_t)i * Sp + q) * Sp;
     const int n = q + 1, zend = min(Sp, (q / AT_ROWTILE + 1) * AT_ROWTILE);
     if (n <= 256 * AT_SM_REGS) {
+        const int nj = (n + 255) >> 8, zj = (zend + 255) >> 8;      // passes of 256 columns that hold scores / that are written
         float v[AT_SM_REGS];
         float m = -INFINITY;
 #pragma unroll
         for (int j = 0; j < AT_SM_REGS; j++) {
-            const int k = threadIdx.x + 256 * j;
-            v[j] = k < n ? row[k] * scale : -INFINITY;
-            m = fmaxf(m, v[j]);
+            v[j] = -INFINITY;
+            if (j < nj) {
+                const int k = threadIdx.x + 256 * j;
+                if (k < n) v[j] = row[k] * scale;
+                m = fmaxf(m, v[j]);
+            }
         }
         m = at_block_max(m, red);
         float s = 0.f;
 #pragma unroll
-        for (int j = 0; j < AT_SM_REGS; j++) s += expf(v[j] - m);                          // exp(-inf) = 0 beyond the row
+        for (int j = 0; j < AT_SM_REGS; j++)
+            if (j < nj) { v[j] = expf(v[j] - m); s += v[j]; }                               // exp(-inf) = 0 beyond the row
         s = at_block_sum(s, red);
-        const float L = m + logf(s);
-        if (threadIdx.x == 0 && lse) lse[(size_t)(tok0 + q) * Hq + h] = L;
+        if (threadIdx.x == 0 && lse) lse[(size_t)(tok0 + q) * Hq + h] = m + logf(s);
+        const float inv = 1.0f / s;
 #pragma unroll
-        for (int j = 0; j < AT_SM_REGS; j++) {
-            const int k = threadIdx.x + 256 * j;
-            if (k < zend) row[k] = expf(v[j] - L);                                          // 0 past the diagonal
-        }
+        for (int j = 0; j < AT_SM_REGS; j++)
+            if (j < zj) {
+                const int k = threadIdx.x + 256 * j;
+                if (k < zend) row[k] = j < nj ? v[j] * inv : 0.f;                           // 0 past the diagonal
+            }
         return;
     }
     float m = -INFINITY;

@@ -38,6 +38,15 @@ WORKLOADS = {
 }
 
 
+def gemm_traffic(cfg, T):
+    """DRAM bytes of one launch of the dominant kernel: the FFN gate projection (M = T, N = ffn, K = hidden).
+    One ncu capture of that launch at T = 4096, hidden 2048, ffn 6144 read 148.1 MB and wrote 73.6 MB of DRAM,
+    1.20 times its algorithmic 4*(M*K + N*K + M*N) bytes (summary under profiles/); a full-size launch is too
+    long a capture, so that ratio is applied to the algorithmic bytes of the launch at this workload's T."""
+    alg = 4.0 * (T * cfg.d + cfg.F * cfg.d + T * cfg.F)
+    return 1.20 * alg
+
+
 def peaks():
     try:
         p = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -234,9 +243,11 @@ def run_ours(args):
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": "gemm", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
-                         "frac": (achieved / tf32_peak) if achieved else None, "traffic": None,
+                         "frac": (achieved / tf32_peak) if achieved else None, "traffic": gemm_traffic(cfg, T),
                          "peak_note": f"{pk_kind} bf16 sustained {pk['bf16_tflops_sustained']} TFLOP/s halved for TF32 operands; "
-                                      "achieved counts useful FLOPs (2MNK), the FP32-accurate mode issues 3x that on the tensor pipe",
+                                      "achieved counts useful FLOPs (2MNK) per launch over the step's GEMM launches, the FP32-accurate mode "
+                                      "issues 3x that on the tensor pipe; traffic = DRAM bytes of one FFN gate-projection launch "
+                                      "(ncu capture at T=4096 scaled by algorithmic bytes)",
                          "share_of_step": (g.get("ms_per_step", 0) / (ms / args.steps)) if g else None},
             "per_class": per_class,
         }

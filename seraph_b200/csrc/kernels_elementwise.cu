@@ -143,27 +143,48 @@ __global__ void rope_table_kernel(float2* tab, int max_pos, int half, int hd, fl
     tab[i] = make_float2(cosf(ang), sinf(ang));
 }
 
-// Interleaved-pair rotation, forward or transposed.  One float4 = two pairs.
-__global__ void __launch_bounds__(EW_THREADS) rope_kernel(const float* __restrict__ in, float* __restrict__ out,
+// Interleaved-pair rotation, forward or transposed, in one launch over one or two token-major tensors (q with Hq
+// heads and, when k is given, k with Hkv heads: a training step rotates both at the same point, and one launch of
+// twice the bytes amortises the launch and its tail).  One float4 = two pairs; the two (cos, sin) entries of a
+// float4 are one 16-byte table read.  Four float4 per thread are in flight together; indices are 32-bit (the
+// launcher takes the pair kernel beyond 2^31 float4).
+#define ROPE_UNROLL 4
+__global__ void __launch_bounds__(EW_THREADS) rope_kernel(const float* qin, float* qout, const float* kin, float* kout,
                                                           const uint32_t* __restrict__ pos_ids, const float2* __restrict__ tab,
-                                                          int T, int H, int hd, int backward) {
-    int half = hd >> 1, quads = hd >> 2;
-    size_t total = (size_t)T * H * quads;
-    size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = tid; i < total; i += nth) {
-        int qd = (int)(i % quads); size_t th = i / quads; int t = (int)(th / H);
-        int pos = (int)pos_ids[t];
-        float4 x = ((const float4*)in)[i];
-        float2 cs0 = tab[(size_t)pos * half + 2 * qd], cs1 = tab[(size_t)pos * half + 2 * qd + 1];
-        float4 r;
-        if (!backward) {
-            r.x = x.x * cs0.x - x.y * cs0.y; r.y = x.x * cs0.y + x.y * cs0.x;
-            r.z = x.z * cs1.x - x.w * cs1.y; r.w = x.z * cs1.y + x.w * cs1.x;
-        } else {
-            r.x = x.x * cs0.x + x.y * cs0.y; r.y = -x.x * cs0.y + x.y * cs0.x;
-            r.z = x.z * cs1.x + x.w * cs1.y; r.w = -x.z * cs1.y + x.w * cs1.x;
+                                                          int T, int Hq, int Hkv, int hd, int backward) {
+    const uint32_t quads = (uint32_t)hd >> 2, rq = (uint32_t)Hq * quads, rk = kin ? (uint32_t)Hkv * quads : 0u, row_quads = rq + rk;
+    const uint32_t total = (uint32_t)T * row_quads;
+    const uint32_t nth = gridDim.x * blockDim.x;
+    for (uint32_t base = blockIdx.x * blockDim.x + threadIdx.x; base < total; base += nth * ROPE_UNROLL) {
+        float4 x[ROPE_UNROLL], cs[ROPE_UNROLL];
+        float4* dst[ROPE_UNROLL];
+#pragma unroll
+        for (int u = 0; u < ROPE_UNROLL; u++) {
+            const uint32_t i = base + u * nth;
+            dst[u] = nullptr;
+            if (i < total) {
+                const uint32_t t = i / row_quads, rem = i - t * row_quads;
+                const bool isq = rem < rq;
+                const uint32_t w = isq ? rem : rem - rq;
+                x[u] = isq ? ((const float4*)qin)[(size_t)t * rq + w] : ((const float4*)kin)[(size_t)t * rk + w];
+                dst[u] = isq ? (float4*)qout + (size_t)t * rq + w : (float4*)kout + (size_t)t * rk + w;
+                cs[u] = ((const float4*)tab)[(size_t)pos_ids[t] * quads + w % quads];      // {cos0, sin0, cos1, sin1}
+            }
         }
-        ((float4*)out)[i] = r;
+#pragma unroll
+        for (int u = 0; u < ROPE_UNROLL; u++) {
+            if (dst[u]) {
+                float4 r;
+                if (!backward) {
+                    r.x = x[u].x * cs[u].x - x[u].y * cs[u].y; r.y = x[u].x * cs[u].y + x[u].y * cs[u].x;
+                    r.z = x[u].z * cs[u].z - x[u].w * cs[u].w; r.w = x[u].z * cs[u].w + x[u].w * cs[u].z;
+                } else {
+                    r.x = x[u].x * cs[u].x + x[u].y * cs[u].y; r.y = -x[u].x * cs[u].y + x[u].y * cs[u].x;
+                    r.z = x[u].z * cs[u].z + x[u].w * cs[u].w; r.w = -x[u].z * cs[u].w + x[u].w * cs[u].z;
+                }
+                *dst[u] = r;
+            }
+        }
     }
 }
 
@@ -236,30 +257,53 @@ void sb_seq_index(sb_ctx_t* c, const uint32_t* seq_starts, int B, int T, uint32_
     c->launches++;
 }
 
+// (re)builds the cos/sin table when the position range, head size or theta changed; false on allocation failure
+static bool rope_ensure_table(sb_ctx_t* c, int hd, float theta, int max_pos) {
+    const int half = hd / 2;
+    if (c->rope_tab && c->rope_tab_pos >= max_pos && c->rope_tab_hd == hd && c->rope_tab_theta == theta) return true;
+    cudaStreamSynchronize((cudaStream_t)c->pub.stream);
+    if (c->rope_tab) cudaFree(c->rope_tab);
+    c->rope_tab = NULL;
+    int cap = max_pos < 1024 ? 1024 : max_pos;
+    if (sb_check(c, cudaMalloc(&c->rope_tab, (size_t)cap * half * sizeof(float2)), "rope table")) return false;
+    c->rope_tab_pos = cap; c->rope_tab_hd = hd; c->rope_tab_theta = theta;
+    int n = cap * half;
+    rope_table_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)c->pub.stream>>>((float2*)c->rope_tab, cap, half, hd, theta);
+    c->launches++;
+    return true;
+}
+
 void sb_rope(sb_ctx_t* c, const float* in, float* out, const uint32_t* pos_ids, int T, int H, int hd, float theta,
              int max_pos, int backward) {
     if (T <= 0 || H <= 0 || hd < 2) return;
     int half = hd / 2;
-    if (!c->rope_tab || c->rope_tab_pos < max_pos || c->rope_tab_hd != hd || c->rope_tab_theta != theta) {
-        cudaStreamSynchronize((cudaStream_t)c->pub.stream);
-        if (c->rope_tab) cudaFree(c->rope_tab);
-        c->rope_tab = NULL;
-        int cap = max_pos < 1024 ? 1024 : max_pos;
-        if (sb_check(c, cudaMalloc(&c->rope_tab, (size_t)cap * half * sizeof(float2)), "rope table")) return;
-        c->rope_tab_pos = cap; c->rope_tab_hd = hd; c->rope_tab_theta = theta;
-        int n = cap * half;
-        rope_table_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)c->pub.stream>>>((float2*)c->rope_tab, cap, half, hd, theta);
-        c->launches++;
-    }
+    if (!rope_ensure_table(c, hd, theta, max_pos)) return;
     int tk = sb_tick_begin(c, SB_CLS_ROPE);
-    if ((hd & 3) == 0 && aligned16(in) && aligned16(out)) {
-        size_t work = (size_t)T * H * (hd / 4);
-        rope_kernel<<<ew_grid(c, work), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(in, out, pos_ids, (const float2*)c->rope_tab, T, H, hd, backward);
+    if ((hd & 3) == 0 && aligned16(in) && aligned16(out) && aligned16(c->rope_tab) && (double)T * H * (hd / 4) < 2147483648.0) {
+        size_t work = ((size_t)T * H * (hd / 4) + ROPE_UNROLL - 1) / ROPE_UNROLL;
+        rope_kernel<<<ew_grid(c, work), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(in, out, nullptr, nullptr, pos_ids, (const float2*)c->rope_tab, T, H, 0, hd, backward);
     } else {
         size_t work = (size_t)T * H * half;
         rope_pair_kernel<<<ew_grid(c, work), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(in, out, pos_ids, (const float2*)c->rope_tab, T, H, hd, backward);
     }
     sb_tick_end(c, tk, 0.0, 8.0 * T * H * hd);
+    c->launches++;
+}
+
+// q and k rotated in place by one launch when the fast path applies, else by two calls of sb_rope
+void sb_rope2(sb_ctx_t* c, float* q, float* k, const uint32_t* pos_ids, int T, int Hq, int Hkv, int hd, float theta, int max_pos, int backward) {
+    if (T <= 0) return;
+    const double nq = (double)T * (Hq + Hkv) * (hd / 4);
+    if ((hd & 3) || !aligned16(q) || !aligned16(k) || nq >= 2147483648.0) {
+        sb_rope(c, q, q, pos_ids, T, Hq, hd, theta, max_pos, backward);
+        sb_rope(c, k, k, pos_ids, T, Hkv, hd, theta, max_pos, backward);
+        return;
+    }
+    if (!rope_ensure_table(c, hd, theta, max_pos)) return;
+    int tk = sb_tick_begin(c, SB_CLS_ROPE);
+    size_t work = ((size_t)nq + ROPE_UNROLL - 1) / ROPE_UNROLL;
+    rope_kernel<<<ew_grid(c, work), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(q, q, k, k, pos_ids, (const float2*)c->rope_tab, T, Hq, Hkv, hd, backward);
+    sb_tick_end(c, tk, 0.0, 8.0 * T * (Hq + Hkv) * hd);
     c->launches++;
 }
 

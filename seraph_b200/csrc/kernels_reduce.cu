@@ -158,18 +158,86 @@ __global__ void __launch_bounds__(RB_THREADS) rmsnorm_warp_kernel(const float* _
     }
 }
 
-// RMSNorm backward, four rows per pass of a 256-thread CTA.  Thread t owns the float4 column chunks t, t+256, ...
-// (NC of them) of every row the CTA visits, so its dscale partial stays in NC float4 registers; the x, dy and
-// residual chunks of four rows are requested together, the eight row sums (sum x^2 and sum dy*w*x of each row)
-// go through one CTA reduction, and two CTAs share an SM.  One dscale partial row per CTA, summed in CTA order.
-#define RNB_ROWS 4
+// RMSNorm backward for a 256-thread CTA that visits row groups of RNB_ROWS rows.  Thread t owns the float4 column
+// chunks t, t+256, ... (NC of them) of every row the CTA visits, so its dscale partial stays in NC float4
+// registers.  The loads of the next group (x, dy, residual) are issued before the current group is reduced,
+// so memory requests are in flight during the two CTA-wide reductions (sum x^2 and sum dy*w*x of each row);
+// two CTAs share an SM.  One dscale partial row per CTA, summed in CTA order by colsum_partials_kernel.
+#define RNB_ROWS 2
 template <int NC>
-__global__ void __launch_bounds__(RB_THREADS, 2) rmsnorm_bwd_rows4_kernel(const float* __restrict__ x, const float* __restrict__ w,
-                                                                          const float* __restrict__ dy, const float* resid, float* dx,
-                                                                          float* __restrict__ partial, int rows, int cols, float eps) {
-    __shared__ float s_red[RB_THREADS / 32][2 * RNB_ROWS];
-    __shared__ float s_tot[2 * RNB_ROWS];
-    const int c4 = cols >> 2, lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+struct RnbSet { float4 v[RNB_ROWS][NC], g[RNB_ROWS][NC], q[RNB_ROWS][NC]; };
+
+template <int NC>
+__device__ __forceinline__ void rnb_load(RnbSet<NC>& s, const float* __restrict__ x, const float* __restrict__ dy, const float* resid,
+                                         int r0, int rows, int c4) {
+#pragma unroll
+    for (int rr = 0; rr < RNB_ROWS; rr++)
+#pragma unroll
+        for (int i = 0; i < NC; i++) {
+            const int j = threadIdx.x + RB_THREADS * i;
+            const bool in = r0 + rr < rows && j < c4;
+            const size_t o = (size_t)(r0 + rr) * c4 + j;
+            s.v[rr][i] = in ? ((const float4*)x)[o] : make_float4(0.f, 0.f, 0.f, 0.f);
+            s.g[rr][i] = in ? ((const float4*)dy)[o] : make_float4(0.f, 0.f, 0.f, 0.f);
+            s.q[rr][i] = (in && resid) ? ((const float4*)resid)[o] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+}
+
+template <int NC>
+__device__ __forceinline__ void rnb_compute(const RnbSet<NC>& s, const float4 (&sc)[NC], float4 (&acc)[NC], float* dx, int r0, int rows,
+                                            int cols, int c4, float eps, float (*s_red)[2 * RNB_ROWS], float* s_tot) {
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    float part[2 * RNB_ROWS];
+#pragma unroll
+    for (int rr = 0; rr < RNB_ROWS; rr++) {
+        float ss = 0.f, cp = 0.f;
+#pragma unroll
+        for (int i = 0; i < NC; i++) {
+            const float4 v = s.v[rr][i], g = s.g[rr][i];
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            cp += g.x * sc[i].x * v.x + g.y * sc[i].y * v.y + g.z * sc[i].z * v.z + g.w * sc[i].w * v.w;
+        }
+        part[2 * rr] = warp_sum(ss); part[2 * rr + 1] = warp_sum(cp);
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < 2 * RNB_ROWS; k++) s_red[wib][k] = part[k];
+    }
+    __syncthreads();
+    if (threadIdx.x < 2 * RNB_ROWS) {
+        float t = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < RB_THREADS / 32; wv++) t += s_red[wv][threadIdx.x];
+        s_tot[threadIdx.x] = t;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int rr = 0; rr < RNB_ROWS; rr++) {
+        if (r0 + rr >= rows) break;
+        const float inv = 1.0f / sqrtf(s_tot[2 * rr] / cols + eps);
+        const float k = inv * inv * inv / cols * s_tot[2 * rr + 1];
+#pragma unroll
+        for (int i = 0; i < NC; i++) {
+            const int j = threadIdx.x + RB_THREADS * i;
+            if (j < c4) {
+                const float4 v = s.v[rr][i], g = s.g[rr][i], q = s.q[rr][i];
+                float4 o;
+                acc[i].x += g.x * v.x * inv; acc[i].y += g.y * v.y * inv; acc[i].z += g.z * v.z * inv; acc[i].w += g.w * v.w * inv;
+                o.x = g.x * sc[i].x * inv - v.x * k + q.x; o.y = g.y * sc[i].y * inv - v.y * k + q.y;
+                o.z = g.z * sc[i].z * inv - v.z * k + q.z; o.w = g.w * sc[i].w * inv - v.w * k + q.w;
+                ((float4*)dx)[(size_t)(r0 + rr) * c4 + j] = o;
+            }
+        }
+    }
+}
+
+template <int NC>
+__global__ void __launch_bounds__(RB_THREADS, 2) rmsnorm_bwd_rows_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                                         const float* __restrict__ dy, const float* resid, float* dx,
+                                                                         float* __restrict__ partial, int rows, int cols, float eps) {
+    __shared__ float s_red[2][RB_THREADS / 32][2 * RNB_ROWS];
+    __shared__ float s_tot[2][2 * RNB_ROWS];
+    const int c4 = cols >> 2;
     float4 acc[NC], sc[NC];
 #pragma unroll
     for (int i = 0; i < NC; i++) {
@@ -177,63 +245,18 @@ __global__ void __launch_bounds__(RB_THREADS, 2) rmsnorm_bwd_rows4_kernel(const 
         const int j = threadIdx.x + RB_THREADS * i;
         sc[i] = j < c4 ? ((const float4*)w)[j] : acc[i];
     }
-    const int ngroups = (rows + RNB_ROWS - 1) / RNB_ROWS;
-    for (int gidx = blockIdx.x; gidx < ngroups; gidx += gridDim.x) {
-        const int r0 = gidx * RNB_ROWS;
-        float4 v[RNB_ROWS][NC], g[RNB_ROWS][NC], q[RNB_ROWS][NC];
-#pragma unroll
-        for (int rr = 0; rr < RNB_ROWS; rr++)
-#pragma unroll
-            for (int i = 0; i < NC; i++) {
-                const int j = threadIdx.x + RB_THREADS * i;
-                const bool in = r0 + rr < rows && j < c4;
-                const size_t o = (size_t)(r0 + rr) * c4 + j;
-                v[rr][i] = in ? ((const float4*)x)[o] : make_float4(0.f, 0.f, 0.f, 0.f);
-                g[rr][i] = in ? ((const float4*)dy)[o] : make_float4(0.f, 0.f, 0.f, 0.f);
-                q[rr][i] = (in && resid) ? ((const float4*)resid)[o] : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-        float part[2 * RNB_ROWS];
-#pragma unroll
-        for (int rr = 0; rr < RNB_ROWS; rr++) {
-            float ss = 0.f, cp = 0.f;
-#pragma unroll
-            for (int i = 0; i < NC; i++) {
-                ss += v[rr][i].x * v[rr][i].x + v[rr][i].y * v[rr][i].y + v[rr][i].z * v[rr][i].z + v[rr][i].w * v[rr][i].w;
-                cp += g[rr][i].x * sc[i].x * v[rr][i].x + g[rr][i].y * sc[i].y * v[rr][i].y + g[rr][i].z * sc[i].z * v[rr][i].z +
-                      g[rr][i].w * sc[i].w * v[rr][i].w;
-            }
-            part[2 * rr] = warp_sum(ss); part[2 * rr + 1] = warp_sum(cp);
-        }
-        if (lane == 0) {
-#pragma unroll
-            for (int k = 0; k < 2 * RNB_ROWS; k++) s_red[wib][k] = part[k];
-        }
-        __syncthreads();
-        if (threadIdx.x < 2 * RNB_ROWS) {
-            float t = 0.f;
-#pragma unroll
-            for (int wv = 0; wv < RB_THREADS / 32; wv++) t += s_red[wv][threadIdx.x];
-            s_tot[threadIdx.x] = t;
-        }
-        __syncthreads();
-#pragma unroll
-        for (int rr = 0; rr < RNB_ROWS; rr++) {
-            if (r0 + rr >= rows) break;
-            const float inv = 1.0f / sqrtf(s_tot[2 * rr] / cols + eps);
-            const float k = inv * inv * inv / cols * s_tot[2 * rr + 1];
-#pragma unroll
-            for (int i = 0; i < NC; i++) {
-                const int j = threadIdx.x + RB_THREADS * i;
-                if (j < c4) {
-                    float4 o;
-                    acc[i].x += g[rr][i].x * v[rr][i].x * inv; acc[i].y += g[rr][i].y * v[rr][i].y * inv;
-                    acc[i].z += g[rr][i].z * v[rr][i].z * inv; acc[i].w += g[rr][i].w * v[rr][i].w * inv;
-                    o.x = g[rr][i].x * sc[i].x * inv - v[rr][i].x * k + q[rr][i].x; o.y = g[rr][i].y * sc[i].y * inv - v[rr][i].y * k + q[rr][i].y;
-                    o.z = g[rr][i].z * sc[i].z * inv - v[rr][i].z * k + q[rr][i].z; o.w = g[rr][i].w * sc[i].w * inv - v[rr][i].w * k + q[rr][i].w;
-                    ((float4*)dx)[(size_t)(r0 + rr) * c4 + j] = o;
-                }
-            }
-        }
+    const int ngroups = (rows + RNB_ROWS - 1) / RNB_ROWS, stride = gridDim.x;
+    RnbSet<NC> a, b;
+    int gidx = blockIdx.x;
+    if (gidx < ngroups) rnb_load<NC>(a, x, dy, resid, gidx * RNB_ROWS, rows, c4);
+    while (gidx < ngroups) {
+        if (gidx + stride < ngroups) rnb_load<NC>(b, x, dy, resid, (gidx + stride) * RNB_ROWS, rows, c4);
+        rnb_compute<NC>(a, sc, acc, dx, gidx * RNB_ROWS, rows, cols, c4, eps, s_red[0], s_tot[0]);
+        gidx += stride;
+        if (gidx >= ngroups) break;
+        if (gidx + stride < ngroups) rnb_load<NC>(a, x, dy, resid, (gidx + stride) * RNB_ROWS, rows, c4);
+        rnb_compute<NC>(b, sc, acc, dx, gidx * RNB_ROWS, rows, cols, c4, eps, s_red[1], s_tot[1]);
+        gidx += stride;
     }
 #pragma unroll
     for (int i = 0; i < NC; i++) {
@@ -242,28 +265,34 @@ __global__ void __launch_bounds__(RB_THREADS, 2) rmsnorm_bwd_rows4_kernel(const 
     }
 }
 
-// dscale[c] += sum over partial rows of partial[b][c], in a fixed order: 32 columns per CTA, the rows
-// dealt to 8 row groups (group g takes rows g, g+8, ...), the 8 group sums then added in group order.
-__global__ void __launch_bounds__(256) colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ dscale, int nblocks, int cols) {
-    __shared__ float s_part[8][32];
+// dscale[c] += sum over partial rows of partial[b][c], in a fixed order: 32 columns per CTA, the rows dealt to
+// 32 row groups (group g takes rows g, g+32, ...; ten independent loads are in flight per thread), the 32 group
+// sums then added in group order.
+#define CS_GROUPS 32
+#define CS_BATCH 10
+__global__ void __launch_bounds__(32 * CS_GROUPS) colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ dscale, int nblocks, int cols) {
+    __shared__ float s_part[CS_GROUPS][33];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const int cidx = blockIdx.x * 32 + tx;
     float s = 0.f;
     if (cidx < cols) {
-        int b = ty;
-        for (; b + 24 < nblocks; b += 32) {
-            float a0 = partial[(size_t)b * cols + cidx], a1 = partial[(size_t)(b + 8) * cols + cidx];
-            float a2 = partial[(size_t)(b + 16) * cols + cidx], a3 = partial[(size_t)(b + 24) * cols + cidx];
-            s += a0; s += a1; s += a2; s += a3;
+        for (int b0 = ty; b0 < nblocks; b0 += CS_GROUPS * CS_BATCH) {
+            float v[CS_BATCH];
+#pragma unroll
+            for (int i = 0; i < CS_BATCH; i++) {
+                const int b = b0 + i * CS_GROUPS;
+                v[i] = b < nblocks ? partial[(size_t)b * cols + cidx] : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < CS_BATCH; i++) s += v[i];
         }
-        for (; b < nblocks; b += 8) s += partial[(size_t)b * cols + cidx];
     }
     s_part[ty][tx] = s;
     __syncthreads();
     if (ty == 0 && cidx < cols) {
         float t = s_part[0][tx];
 #pragma unroll
-        for (int g = 1; g < 8; g++) t += s_part[g][tx];
+        for (int g = 1; g < CS_GROUPS; g++) t += s_part[g][tx];
         dscale[cidx] += t;
     }
 }
@@ -498,8 +527,9 @@ void sb_rmsnorm(sb_ctx_t* c, const float* x, const float* w, float* y, int rows,
     int vec = (cols % 4 == 0) && aligned16(x) && aligned16(w) && aligned16(y);
     int tk = sb_tick_begin(c, SB_CLS_NORM_FWD);
     if (vec && cols <= 4096 && rows >= 64) {
-        // warp per row: 8 rows per CTA
-        int wgrid = (rows + 7) / 8; if (wgrid > sm_count(c) * 8) wgrid = sm_count(c) * 8;
+        // warp per row, 8 warps per CTA, two CTAs resident per SM: every warp gets the same number of rows (no tail)
+        int wgrid = (rows + 7) / 8;
+        { int cap = sm_count(c) * 2, k = (wgrid + cap - 1) / cap; wgrid = (wgrid + k - 1) / k; }
         cudaStream_t st = (cudaStream_t)c->pub.stream;
         if (cols <= 512)       rmsnorm_warp_kernel<4><<<wgrid, RB_THREADS, 0, st>>>(x, w, y, rows, cols, eps);
         else if (cols <= 1024) rmsnorm_warp_kernel<8><<<wgrid, RB_THREADS, 0, st>>>(x, w, y, rows, cols, eps);
@@ -520,7 +550,7 @@ void sb_rmsnorm_backward_with_partials(sb_ctx_t* c, const float* x, const float*
     cudaStream_t s = (cudaStream_t)c->pub.stream;
     int tk = sb_tick_begin(c, SB_CLS_NORM_BWD);
     rmsnorm_bwd_kernel<<<grid, RB_THREADS, 0, s>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps, vec);
-    colsum_partials_kernel<<<(cols + 31) / 32, 256, 0, s>>>(partial, dscale, grid, cols);
+    colsum_partials_kernel<<<(cols + 31) / 32, 32 * CS_GROUPS, 0, s>>>(partial, dscale, grid, cols);
     sb_tick_end(c, tk, 0.0, (resid ? 16.0 : 12.0) * rows * cols);
     c->launches += 2;
 }
@@ -531,15 +561,15 @@ void sb_rmsnorm_backward(sb_ctx_t* c, const float* x, const float* w, const floa
     if (cols > RB_THREADS * 4 * RN_MAX_SWEEP || (cols % 4 != 0 && cols > RB_THREADS * RN_MAX_SWEEP * 4)) { sb_set_status(c, SB_ERR_SIZE); return; }
     int vec = (cols % 4 == 0) && aligned16(x) && aligned16(w) && aligned16(dy) && aligned16(dx_out) && (!resid || aligned16(resid));
     if (vec && cols <= 2048 && rows >= 64) {
-        // four rows per CTA pass, two CTAs per SM; one dscale partial per CTA, summed in CTA order
+        // row groups with the next group's loads in flight, two CTAs per SM; one dscale partial per CTA, summed in CTA order
         int wgrid = (rows + RNB_ROWS - 1) / RNB_ROWS; if (wgrid > 2 * sm_count(c)) wgrid = 2 * sm_count(c);
         float* partial = (float*)sb_scratch(c, (size_t)wgrid * cols * sizeof(float));
         if (!partial) return;
         cudaStream_t st = (cudaStream_t)c->pub.stream;
         int tk = sb_tick_begin(c, SB_CLS_NORM_BWD);
-        if (cols <= 1024) rmsnorm_bwd_rows4_kernel<1><<<wgrid, RB_THREADS, 0, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
-        else              rmsnorm_bwd_rows4_kernel<2><<<wgrid, RB_THREADS, 0, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
-        colsum_partials_kernel<<<(cols + 31) / 32, 256, 0, st>>>(partial, dscale, wgrid, cols);
+        if (cols <= 1024) rmsnorm_bwd_rows_kernel<1><<<wgrid, RB_THREADS, 0, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
+        else              rmsnorm_bwd_rows_kernel<2><<<wgrid, RB_THREADS, 0, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
+        colsum_partials_kernel<<<(cols + 31) / 32, 32 * CS_GROUPS, 0, st>>>(partial, dscale, wgrid, cols);
         sb_tick_end(c, tk, 0.0, (resid ? 16.0 : 12.0) * rows * cols);
         c->launches += 2;
         return;
@@ -723,7 +753,7 @@ extern "C" int seraph_b200_rmsnorm_backward_static(const float* input, const flo
     // every CTA overwrites its whole row of partials before the column sum reads it,
     // so nothing left over from an earlier call is ever read and no clearing is needed
     rmsnorm_bwd_kernel<<<grid, RB_THREADS, 0, s>>>(input, scale, grad_output, nullptr, grad_input, partial, rows, cols, eps, vec);
-    colsum_partials_kernel<<<(cols + 31) / 32, 256, 0, s>>>(partial, grad_scale, grid, cols);
+    colsum_partials_kernel<<<(cols + 31) / 32, 32 * CS_GROUPS, 0, s>>>(partial, grad_scale, grid, cols);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         fprintf(stderr, "seraph_b200_rmsnorm_backward_static: launch failed: %s\n", cudaGetErrorString(e));

@@ -135,6 +135,7 @@ void sb_mul_backward(sb_ctx_t*, const float* A, const float* B, const float* dC,
 void sb_swiglu(sb_ctx_t*, const float* gate, const float* up, float* out, size_t n);
 void sb_swiglu_backward(sb_ctx_t*, const float* gate, const float* up, const float* dout, float* dgate, float* dup, size_t n);
 void sb_seq_index(sb_ctx_t*, const uint32_t* seq_starts, int B, int T, uint32_t* pos_ids, uint32_t* seq_ids);
+void sb_rope2(sb_ctx_t*, float* q, float* k, const uint32_t* pos_ids, int T, int Hq, int Hkv, int hd, float theta, int max_pos, int backward);
 void sb_rope(sb_ctx_t*, const float* in, float* out, const uint32_t* pos_ids, int T, int H, int hd, float theta,
              int max_pos, int backward);
 void sb_attention(sb_ctx_t*, const float* Q, const float* K, const float* V, float* out, float* lse,

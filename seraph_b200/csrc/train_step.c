@@ -413,8 +413,7 @@ static void forward_pass(sb_ctx_t* c, int T, int max_seq, float theta, int use_l
         linear_fwd(c, use_lora, l, 0, a->x_norm_attn, c->W + o->q, a->q, T, d, qd, 0);
         linear_fwd(c, use_lora, l, 1, a->x_norm_attn, c->W + o->k, a->k, T, d, kvd, 0);
         linear_fwd(c, use_lora, l, 2, a->x_norm_attn, c->W + o->v, a->v, T, d, kvd, 0);
-        sb_rope(c, a->q, a->q, c->pos_ids, T, c->Hq, c->hd, theta, max_seq, 0);
-        sb_rope(c, a->k, a->k, c->pos_ids, T, c->Hkv, c->hd, theta, max_seq, 0);
+        sb_rope2(c, a->q, a->k, c->pos_ids, T, c->Hq, c->Hkv, c->hd, theta, max_seq, 0);
         sb_attention(c, a->q, a->k, a->v, a->attn_out, a->lse, c->seq_starts, c->seq_ids, T, c->Hq, c->Hkv, c->hd);
         sb_copy(c, a->post_attn_in, a->layer_in, Td * sizeof(float));
         linear_fwd(c, use_lora, l, 3, a->attn_out, c->W + o->o, a->post_attn_in, T, qd, d, 1);
@@ -461,8 +460,7 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
         if (!full) lora_bwd(c, l, 3, gh, a->attn_out, c->g_attn, T);
         sb_attention_backward(c, a->q, a->k, a->v, a->attn_out, a->lse, c->g_attn, c->g_q, c->g_k, c->g_v, 0,
                               c->seq_starts, c->seq_ids, B, T, c->Hq, c->Hkv, c->hd);
-        sb_rope(c, c->g_q, c->g_q, c->pos_ids, T, c->Hq, c->hd, theta, max_seq, 1);
-        sb_rope(c, c->g_k, c->g_k, c->pos_ids, T, c->Hkv, c->hd, theta, max_seq, 1);
+        sb_rope2(c, c->g_q, c->g_k, c->pos_ids, T, c->Hq, c->Hkv, c->hd, theta, max_seq, 1);
         if (full) {
             sb_gemm(c, c->g_q, a->x_norm_attn, Gd + o->q, qd, d, T, 1, 0, 1);
             sb_gemm(c, c->g_k, a->x_norm_attn, Gd + o->k, kvd, d, T, 1, 0, 1);

@@ -166,6 +166,11 @@ int seraph_b200_set_gemm_pair(cuda_train_context_t* ctx, int on);
  * pieces of the k range that fill the machine and are added in a fixed order;
  * 0: whole tiles only. */
 int seraph_b200_set_gemm_tail_split(cuda_train_context_t* ctx, int on);
+/* Attention backward on the tensor cores: 0 (default) P and dS are made by a
+ * streaming kernel from the stored scores; 1: by the epilogues of the two score
+ * products (fewer bytes, but measured slower: the epilogue is what bounds the
+ * short products). */
+int seraph_b200_set_attn_fused(cuda_train_context_t* ctx, int on);
 /* 0 (default): LoRA steps leave the adapters' own term out of dX, as the
  * reference does; 1: full chain rule, dX += s (dY B) A. */
 int seraph_b200_set_lora_exact(cuda_train_context_t* ctx, int exact);

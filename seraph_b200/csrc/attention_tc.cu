@@ -286,8 +286,7 @@ extern "C" int sb_attention_tc_backward(sb_ctx_t* c, const float* Q, const float
             for (int i0 = 0; i0 < Hkv && ok; i0 += G) {
                 const int nb = min(G, Hkv - i0), qh0 = r + i0 * g;
                 const long sb = (long)Sp * Sp;
-                static int fused = -1;
-                if (fused < 0) { const char* e = getenv("SERAPH_B200_ATTN_FUSED"); fused = (e && e[0] == '0') ? 0 : 1; }      // measured on one device: 79 ms fused against 83 ms per step
+                const int fused = c->attn_fused;
                 if (fused) {
                     // P = exp(S*scale - lse) and dS = P o (dP - D) * scale come straight out of the two products' epilogues
                     const TcEpi e_p = at_epi(TC_EPI_EXP, scale, lse, t0, Hq, qh0, g, nullptr);

@@ -79,6 +79,7 @@ cuda_train_context_t* cuda_train_init(int device_id) {
     c->magic = SB_MAGIC;
     c->gemm_mode = SB_GEMM_FP32X3;
     { const char* e = getenv("SERAPH_B200_GEMM_PAIR"); c->gemm_pair = (e && e[0] == '0') ? 0 : 1; }
+    { const char* e = getenv("SERAPH_B200_ATTN_FUSED"); c->attn_fused = (e && e[0] == '1') ? 1 : 0; }
     { const char* e = getenv("SERAPH_B200_GEMM_TAIL_SPLIT"); c->gemm_tail_split = (e && e[0] == '0') ? 0 : 1; }
     c->dp_world = 1;
     cuda_train_context_t* p = &c->pub;
@@ -269,6 +270,13 @@ int seraph_b200_set_gemm_pair(cuda_train_context_t* ctx, int on) {
     sb_ctx_t* c = sb_priv(ctx);
     if (!c) return SB_ERR_ARG;
     c->gemm_pair = on ? 1 : 0;
+    return SB_OK;
+}
+
+int seraph_b200_set_attn_fused(cuda_train_context_t* ctx, int on) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c) return SB_ERR_ARG;
+    c->attn_fused = on ? 1 : 0;
     return SB_OK;
 }
 

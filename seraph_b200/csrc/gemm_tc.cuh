@@ -52,7 +52,7 @@
 // converters, 4-11 epilogue, 14-15 idle; the epilogue warpgroups take the registers the others give up.
 #define TC_CONV_THREADS 512
 #define TC_REGS_LIGHT 72
-#define TC_REGS_EPI 176
+#define TC_REGS_EPI 184
 #define TC_GROUP_M 16
 #define TC_CHUNK_K 32
 #define TC_SPIN_CYCLES 4000000000ll      // ~2 s at 2 GHz: far beyond any legitimate wait
@@ -242,13 +242,74 @@ __device__ __forceinline__ float tf32_lo(float x) {
 // pieces instead of leaving most SMs idle behind a few whole tiles.  A piece writes its 128 x BN
 // block to `partial`; tc_splitk_fixup_kernel adds the pieces in piece order, so the result does not
 // depend on timing.
+// One unit of work of a launch: a tile of one batch entry, or one k piece of a split tile.
+struct TcWork {
+    int m0, n0, nb0;            // this CTA's first row of A and C, the tile's first column, this CTA's first row of B
+    int kb_begin, num_kb;       // k range in blocks of BK
+    int batch, slot;            // batch entry; index of the piece's block in the split workspace
+    bool split;
+};
+
+// Decodes work item `item` (identically in every thread of the pair); false = nothing to compute (a tile above the
+// causal diagonal).  Items are ordered tile-major, batch entry fastest, so that with causal k ranges the longest
+// tiles of all batch entries come first.  tri: the tiles on or below the diagonal of a square tile grid are
+// enumerated directly (row m holds m+1 tiles).
+template <int BN, int BK, int CTAS>
+__device__ __forceinline__ bool tc_work(int item, int rank, int M, int N, int K, int causal, int nbatch, int split_full, int split_s,
+                                        int tri, TcWork& w) {
+    constexpr int TILE_M = TC_BM * CTAS, BROWS = BN / CTAS;
+    constexpr int KB_PER_CHUNK = TC_CHUNK_K / BK > 0 ? TC_CHUNK_K / BK : 1;
+    const int tiles_m = (M + TILE_M - 1) / TILE_M, tiles_n = (N + BN - 1) / BN;
+    const int gt = item / nbatch;
+    w.batch = item - gt * nbatch;
+    int tile_id = gt, piece = 0;
+    w.split = split_s > 1 && gt >= split_full;
+    w.slot = 0;
+    if (w.split) { const int t = gt - split_full; piece = t % split_s; tile_id = split_full + t / split_s; w.slot = t; }
+    int m_tile, n_tile;
+    if (tri) {
+        m_tile = (int)((sqrtf(8.0f * (float)tile_id + 1.0f) - 1.0f) * 0.5f);
+        while ((m_tile + 1) * (m_tile + 2) / 2 <= tile_id) m_tile++;
+        while (m_tile * (m_tile + 1) / 2 > tile_id) m_tile--;
+        n_tile = tile_id - m_tile * (m_tile + 1) / 2;
+    } else {
+        tc_raster(tile_id, tiles_m, tiles_n, TC_GROUP_M / CTAS, &m_tile, &n_tile);
+    }
+    if (causal == TC_CAUSAL_K_UPTO_M) m_tile = tiles_m - 1 - m_tile;      // longest k ranges first
+    const int tm0 = m_tile * TILE_M;
+    w.m0 = tm0 + rank * TC_BM; w.n0 = n_tile * BN; w.nb0 = w.n0 + rank * BROWS;
+    int kb_begin = 0, kb_end = (K + BK - 1) / BK;
+    // causal structure: whole-tile skips and the k range, the same for both CTAs of a pair
+    if (causal == TC_CAUSAL_SKIP_UPPER && w.n0 > tm0 + TILE_M - 1) return false;
+    if (causal == TC_CAUSAL_SKIP_LOWER && w.n0 + BN - 1 < tm0) return false;
+    if (causal == TC_CAUSAL_K_UPTO_M) kb_end = min(kb_end, (tm0 + TILE_M + BK - 1) / BK);
+    if (causal == TC_CAUSAL_K_FROM_M) kb_begin = min(kb_end, tm0 / BK);
+    if (w.split) {
+        const int per = ((kb_end + split_s - 1) / split_s + KB_PER_CHUNK - 1) / KB_PER_CHUNK * KB_PER_CHUNK;
+        kb_begin = min(kb_end, piece * per);
+        kb_end = min(kb_end, kb_begin + per);
+    }
+    w.kb_begin = kb_begin; w.num_kb = kb_end - kb_begin;
+    return true;
+}
+// item of cluster `cid` in round k of a launch with G clusters; snake: odd rounds run backwards, so a cluster that
+// got a long item in one round gets a short one in the next (items are ordered longest first)
+__device__ __forceinline__ int tc_item(int k, int cid, int G, int snake) { return k * G + ((snake && (k & 1)) ? G - 1 - cid : cid); }
+
+#define TC_STG_ROWS 64          // rows of the output staging buffer: two TMEM lane quarters at a time
+
+// The kernel is persistent: a launch has at most one CTA (pair) per SM (pair), and each walks over its work items.
+// Barriers, tensor memory and the operand ring live across items, so while the epilogue warps write one tile out
+// (through a small dedicated staging buffer, 32 rows at a time) the producer, the converters and the MMA warp are
+// already working on the next item: only the epilogue itself is left of the per-tile overhead.
 template <int BN, int BK, int NTERMS, int STAGES, int CTAS, bool AMN, bool BMN>
 __global__ void __launch_bounds__((CTAS == 2 && NTERMS == 3) ? TC_CONV_THREADS : TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
                float* __restrict__ Cbase, long ldc, long c_batch_stride, int M, int N, int K, int acc, int causal,
                int a_c2_base, int a_c2_step, int b_c2_base, int b_c2_step, int swap_mask,
-               int split_full, int split_s, float* __restrict__ partial, const TcEpi epi, int* status) {
+               int split_full, int split_s, float* __restrict__ partial, const TcEpi epi,
+               int nbatch, int total_items, int snake, int tri, int store_warps, int* status) {
     constexpr int SWZ = BK * 4;
     constexpr int BROWS = BN / CTAS;                             // B rows this CTA loads
     constexpr int TILE_M = TC_BM * CTAS;
@@ -261,51 +322,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
     constexpr uint32_t TMEM_COLS = 2 * BN;                       // two accumulator buffers
     constexpr int KB_PER_CHUNK = TC_CHUNK_K / BK;
     constexpr int COLS_PER_WARP = BN / (TC_EPI_WARPS / 4);       // 128 or 64 register accumulators per epilogue thread
+    constexpr int SLD = BN + 4;                                  // padded row pitch of the staging buffer (floats)
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+    float* stg = (float*)(smem + STAGES * STAGE_BYTES);
+    uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES + TC_STG_ROWS * SLD * 4);
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;          // [2] MMA -> epilogue
     uint64_t* acc_empty = acc_full + 2;           // [2] epilogue -> MMA
     uint64_t* conv = acc_empty + 2;               // [STAGES] converter warps -> MMA (leader's copy is the one used)
-    uint32_t* tmem_slot = (uint32_t*)(conv + STAGES);
+    uint64_t* stg_full = conv + STAGES;           // [2] epilogue warps -> store warps: a 32-row half of the staging buffer is written
+    uint64_t* stg_go = stg_full + 2;              // [4] store warps -> the epilogue warps of one lane quarter: its half is free for it
+    uint32_t* tmem_slot = (uint32_t*)(stg_go + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int batch = blockIdx.y;
     const uint32_t rank = CTAS == 2 ? cluster_ctarank() : 0u;
     const bool leader = rank == 0;
-    const int tiles_m = (M + TILE_M - 1) / TILE_M, tiles_n = (N + BN - 1) / BN;
-    int m_tile, n_tile;
-    int tile_id = blockIdx.x / CTAS, piece = 0;
-    const bool split = split_s > 1 && tile_id >= split_full;
-    if (split) { const int t = tile_id - split_full; piece = t % split_s; tile_id = split_full + t / split_s; }
-    tc_raster(tile_id, tiles_m, tiles_n, TC_GROUP_M / CTAS, &m_tile, &n_tile);
-    if (causal == TC_CAUSAL_K_UPTO_M) m_tile = tiles_m - 1 - m_tile;      // longest k ranges first, so the last wave is made of short tiles
-    const int m0 = m_tile * TILE_M + (int)rank * TC_BM, n0 = n_tile * BN;      // this CTA's rows of A and C; the tile's columns
-    const int nb0 = n0 + (int)rank * BROWS;                                     // this CTA's rows of B
-    int kb_begin = 0, kb_end = (K + BK - 1) / BK;
-    {
-        // causal structure: whole-tile skips and the k range, the same for both CTAs of a pair
-        const int tm0 = m_tile * TILE_M;
-        if (causal == TC_CAUSAL_SKIP_UPPER && n0 > tm0 + TILE_M - 1) return;
-        if (causal == TC_CAUSAL_SKIP_LOWER && n0 + BN - 1 < tm0) return;
-        if (causal == TC_CAUSAL_K_UPTO_M) kb_end = min(kb_end, (tm0 + TILE_M + BK - 1) / BK);
-        if (causal == TC_CAUSAL_K_FROM_M) kb_begin = min(kb_end, tm0 / BK);
-    }
-    if (split) {
-        const int per = ((kb_end + split_s - 1) / split_s + KB_PER_CHUNK - 1) / KB_PER_CHUNK * KB_PER_CHUNK;
-        kb_begin = min(kb_end, piece * per);
-        kb_end = min(kb_end, kb_begin + per);
-    }
-    const int num_kb = kb_end - kb_begin;
-    const int num_chunks = (num_kb + KB_PER_CHUNK - 1) / KB_PER_CHUNK;
-    float* C = Cbase + (size_t)batch * c_batch_stride;
-    const int a_c2 = a_c2_base + batch * a_c2_step, b_c2 = b_c2_base + batch * b_c2_step;
+    const int cid = blockIdx.x / CTAS, G = gridDim.x / CTAS;
+    const int rounds = (total_items + G - 1) / G;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], TC_EPI_WARPS * CTAS); }
         if (CONV) for (int s = 0; s < STAGES; s++) mbar_init(&conv[s], TC_CONV_WARPS * CTAS);
+        for (int b = 0; b < 2; b++) mbar_init(&stg_full[b], TC_EPI_WARPS / 4);
+        for (int b = 0; b < 4; b++) mbar_init(&stg_go[b], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -333,29 +374,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (elect_one()) {
-            for (int it = 0; it < num_kb && ok; it++) {
-                const int s = it % STAGES, kb = kb_begin + it;
-                ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1);
-                if (!ok) break;
-                uint8_t* st = smem + s * STAGE_BYTES;
-                const bool swa = (swap_mask & 1) != 0, swb = (swap_mask & 2) != 0;
-                if (CONV) {
-                    // each CTA's hi tiles land on its own barrier; its converter warps take it from there
-                    mbar_expect_tx(&full[s], HI_BYTES);
-                    tc_load_operand<false, AMN, BK, TC_BM>(st, &tmAh, &full[s], 0, kb, m0, a_c2, swa);
-                    tc_load_operand<false, BMN, BK, BROWS>(st + A_BYTES, &tmBh, &full[s], 0, kb, nb0, b_c2, swb);
-                } else if (CTAS == 2) {
-                    if (leader) mbar_expect_tx(&full[s], STAGE_BYTES * CTAS);      // the pair's bytes all land on the leader's barrier
-                    const uint32_t fb = mapa_u32(smem_u32(&full[s]), 0);
-                    tc_load_operand<true, AMN, BK, TC_BM>(st, &tmAh, nullptr, fb, kb, m0, a_c2, swa);
-                    tc_load_operand<true, BMN, BK, BROWS>(st + A_BYTES, &tmBh, nullptr, fb, kb, nb0, b_c2, swb);
-                } else {
-                    mbar_expect_tx(&full[s], STAGE_BYTES);
-                    tc_load_operand<false, false, BK, TC_BM>(st, &tmAh, &full[s], 0, kb, m0, a_c2, swa);
-                    tc_load_operand<false, false, BK, BROWS>(st + A_BYTES, &tmBh, &full[s], 0, kb, nb0, b_c2, swb);
-                    if (NTERMS == 3) {
-                        tc_load_operand<false, false, BK, TC_BM>(st + HI_BYTES, &tmAl, &full[s], 0, kb, m0, a_c2, swa);
-                        tc_load_operand<false, false, BK, BROWS>(st + HI_BYTES + A_BYTES, &tmBl, &full[s], 0, kb, nb0, b_c2, swb);
+            const bool swa = (swap_mask & 1) != 0, swb = (swap_mask & 2) != 0;
+            uint32_t git = 0;                      // k blocks issued so far, over all items
+            for (int k = 0; k < rounds && ok; k++) {
+                const int item = tc_item(k, cid, G, snake);
+                TcWork w;
+                if (item >= total_items || !tc_work<BN, BK, CTAS>(item, (int)rank, M, N, K, causal, nbatch, split_full, split_s, tri, w)) continue;
+                const int a_c2 = a_c2_base + w.batch * a_c2_step, b_c2 = b_c2_base + w.batch * b_c2_step;
+                for (int it = 0; it < w.num_kb && ok; it++, git++) {
+                    const int s = git % STAGES, kb = w.kb_begin + it;
+                    ok = mbar_wait(&empty[s], ((git / STAGES) & 1) ^ 1);
+                    if (!ok) break;
+                    uint8_t* st = smem + s * STAGE_BYTES;
+                    if (CONV) {
+                        // each CTA's hi tiles land on its own barrier; its converter warps take it from there
+                        mbar_expect_tx(&full[s], HI_BYTES);
+                        tc_load_operand<false, AMN, BK, TC_BM>(st, &tmAh, &full[s], 0, kb, w.m0, a_c2, swa);
+                        tc_load_operand<false, BMN, BK, BROWS>(st + A_BYTES, &tmBh, &full[s], 0, kb, w.nb0, b_c2, swb);
+                    } else if (CTAS == 2) {
+                        if (leader) mbar_expect_tx(&full[s], STAGE_BYTES * CTAS);      // the pair's bytes all land on the leader's barrier
+                        const uint32_t fb = mapa_u32(smem_u32(&full[s]), 0);
+                        tc_load_operand<true, AMN, BK, TC_BM>(st, &tmAh, nullptr, fb, kb, w.m0, a_c2, swa);
+                        tc_load_operand<true, BMN, BK, BROWS>(st + A_BYTES, &tmBh, nullptr, fb, kb, w.nb0, b_c2, swb);
+                    } else {
+                        mbar_expect_tx(&full[s], STAGE_BYTES);
+                        tc_load_operand<false, false, BK, TC_BM>(st, &tmAh, &full[s], 0, kb, w.m0, a_c2, swa);
+                        tc_load_operand<false, false, BK, BROWS>(st + A_BYTES, &tmBh, &full[s], 0, kb, w.nb0, b_c2, swb);
+                        if (NTERMS == 3) {
+                            tc_load_operand<false, false, BK, TC_BM>(st + HI_BYTES, &tmAl, &full[s], 0, kb, w.m0, a_c2, swa);
+                            tc_load_operand<false, false, BK, BROWS>(st + HI_BYTES + A_BYTES, &tmBl, &full[s], 0, kb, w.nb0, b_c2, swb);
+                        }
                     }
                 }
             }
@@ -364,50 +412,57 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (leader && elect_one()) {
-            // instruction descriptor: D = F32, A = B = TF32, both K-major, N and M of the tile
+            // instruction descriptor: D = F32, A = B = TF32, majors of the operands, N and M of the tile
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((AMN ? 1u : 0u) << 15) | ((BMN ? 1u : 0u) << 16) |
                                    ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
-            int it = 0;
-            for (int ch = 0; ch < num_chunks && ok; ch++) {
-                const int buf = ch & 1;
-                ok = mbar_wait(&acc_empty[buf], ((ch >> 1) & 1) ^ 1);      // epilogue has drained this buffer
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
-                const int it_end = min(it + KB_PER_CHUNK, num_kb);
-                bool first = true;
-                for (; it < it_end && ok; it++) {
-                    const int s = it % STAGES;
-                    ok = mbar_wait(CONV ? &conv[s] : &full[s], (it / STAGES) & 1);
+            uint32_t git = 0, gch = 0;             // k blocks and chunks consumed so far, over all items
+            for (int k = 0; k < rounds && ok; k++) {
+                const int item = tc_item(k, cid, G, snake);
+                TcWork w;
+                if (item >= total_items || !tc_work<BN, BK, CTAS>(item, (int)rank, M, N, K, causal, nbatch, split_full, split_s, tri, w)) continue;
+                int it = 0;
+                const int num_chunks = (w.num_kb + KB_PER_CHUNK - 1) / KB_PER_CHUNK;
+                for (int ch = 0; ch < num_chunks && ok; ch++, gch++) {
+                    const int buf = gch & 1;
+                    ok = mbar_wait(&acc_empty[buf], ((gch >> 1) & 1) ^ 1);      // epilogue has drained this buffer
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-                    const uint64_t ah = AMN ? make_mnmajor_desc<BK>(sa) : make_kmajor_desc<SWZ>(sa);
-                    const uint64_t bh = BMN ? make_mnmajor_desc<BK>(sa + A_BYTES) : make_kmajor_desc<SWZ>(sa + A_BYTES);
-                    const uint64_t al = AMN ? make_mnmajor_desc<BK>(sa + HI_BYTES) : make_kmajor_desc<SWZ>(sa + HI_BYTES);
-                    const uint64_t bl = BMN ? make_mnmajor_desc<BK>(sa + HI_BYTES + A_BYTES) : make_kmajor_desc<SWZ>(sa + HI_BYTES + A_BYTES);
+                    const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                    const int it_end = min(it + KB_PER_CHUNK, w.num_kb);
+                    bool first = true;
+                    for (; it < it_end && ok; it++, git++) {
+                        const int s = git % STAGES;
+                        ok = mbar_wait(CONV ? &conv[s] : &full[s], (git / STAGES) & 1);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+                        const uint64_t ah = AMN ? make_mnmajor_desc<BK>(sa) : make_kmajor_desc<SWZ>(sa);
+                        const uint64_t bh = BMN ? make_mnmajor_desc<BK>(sa + A_BYTES) : make_kmajor_desc<SWZ>(sa + A_BYTES);
+                        const uint64_t al = AMN ? make_mnmajor_desc<BK>(sa + HI_BYTES) : make_kmajor_desc<SWZ>(sa + HI_BYTES);
+                        const uint64_t bl = BMN ? make_mnmajor_desc<BK>(sa + HI_BYTES + A_BYTES) : make_kmajor_desc<SWZ>(sa + HI_BYTES + A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / 8; k++) {
-                        // 8 floats of k, in 16-byte units: 32 bytes along a K-major row, 8 k-rows of 128 bytes in an MN-major tile
-                        const uint64_t adva = (uint64_t)(AMN ? k * 64 : k * 2), advb = (uint64_t)(BMN ? k * 64 : k * 2);
-                        if (CTAS == 2) {
-                            tc_mma_tf32_pair(tmem_d, ah + adva, bh + advb, idesc, first ? 0u : 1u);
-                            if (NTERMS == 3) {
-                                tc_mma_tf32_pair(tmem_d, al + adva, bh + advb, idesc, 1);
-                                tc_mma_tf32_pair(tmem_d, ah + adva, bl + advb, idesc, 1);
+                        for (int kk = 0; kk < BK / 8; kk++) {
+                            // 8 floats of k, in 16-byte units: 32 bytes along a K-major row, 8 k-rows of 128 bytes in an MN-major tile
+                            const uint64_t adva = (uint64_t)(AMN ? kk * 64 : kk * 2), advb = (uint64_t)(BMN ? kk * 64 : kk * 2);
+                            if (CTAS == 2) {
+                                tc_mma_tf32_pair(tmem_d, ah + adva, bh + advb, idesc, first ? 0u : 1u);
+                                if (NTERMS == 3) {
+                                    tc_mma_tf32_pair(tmem_d, al + adva, bh + advb, idesc, 1);
+                                    tc_mma_tf32_pair(tmem_d, ah + adva, bl + advb, idesc, 1);
+                                }
+                            } else {
+                                tc_mma_tf32(tmem_d, ah + adva, bh + advb, idesc, first ? 0u : 1u);
+                                if (NTERMS == 3) {
+                                    tc_mma_tf32(tmem_d, al + adva, bh + advb, idesc, 1);
+                                    tc_mma_tf32(tmem_d, ah + adva, bl + advb, idesc, 1);
+                                }
                             }
-                        } else {
-                            tc_mma_tf32(tmem_d, ah + adva, bh + advb, idesc, first ? 0u : 1u);
-                            if (NTERMS == 3) {
-                                tc_mma_tf32(tmem_d, al + adva, bh + advb, idesc, 1);
-                                tc_mma_tf32(tmem_d, ah + adva, bl + advb, idesc, 1);
-                            }
+                            first = false;
                         }
-                        first = false;
+                        if (CTAS == 2) tc_commit_pair(&empty[s]); else tc_commit(&empty[s]);      // stage reusable once these MMAs have read it
                     }
-                    if (CTAS == 2) tc_commit_pair(&empty[s]); else tc_commit(&empty[s]);      // stage reusable once these MMAs have read it
+                    if (CTAS == 2) tc_commit_pair(&acc_full[buf]); else tc_commit(&acc_full[buf]); // chunk complete (also releases the epilogue on a time-out)
                 }
-                if (CTAS == 2) tc_commit_pair(&acc_full[buf]); else tc_commit(&acc_full[buf]); // chunk complete (also releases the epilogue on a time-out)
             }
             if (!ok) atomicExch(status, SB_ERR_TIMEOUT);
         }
@@ -419,170 +474,254 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
             constexpr int UNR = PER % 8 == 0 ? 8 : (PER % 6 == 0 ? 6 : 4);
             static_assert(N4 % (32 * TC_CONV_WARPS) == 0 && PER % UNR == 0, "stage size against the converter's unroll");
             const uint32_t cb_base = mapa_u32(smem_u32(&conv[0]), 0);
-            for (int it = 0; it < num_kb && ok; it++) {
-                const int s = it % STAGES;
-                ok = mbar_wait(&full[s], (it / STAGES) & 1);
-                if (!ok) break;
-                const float4* src = (const float4*)(smem + s * STAGE_BYTES);
-                float4* dst = (float4*)(smem + s * STAGE_BYTES + HI_BYTES);
+            uint32_t git = 0;
+            for (int k = 0; k < rounds && ok; k++) {
+                const int item = tc_item(k, cid, G, snake);
+                TcWork w;
+                if (item >= total_items || !tc_work<BN, BK, CTAS>(item, (int)rank, M, N, K, causal, nbatch, split_full, split_s, tri, w)) continue;
+                for (int it = 0; it < w.num_kb && ok; it++, git++) {
+                    const int s = git % STAGES;
+                    ok = mbar_wait(&full[s], (git / STAGES) & 1);
+                    if (!ok) break;
+                    const float4* src = (const float4*)(smem + s * STAGE_BYTES);
+                    float4* dst = (float4*)(smem + s * STAGE_BYTES + HI_BYTES);
 #pragma unroll
-                for (int b = 0; b < PER; b += UNR) {
-                    float4 v[UNR];
+                    for (int b = 0; b < PER; b += UNR) {
+                        float4 v[UNR];
 #pragma unroll
-                    for (int j = 0; j < UNR; j++) v[j] = src[(cw * PER + b + j) * 32 + lane];
+                        for (int j = 0; j < UNR; j++) v[j] = src[(cw * PER + b + j) * 32 + lane];
 #pragma unroll
-                    for (int j = 0; j < UNR; j++)
-                        dst[(cw * PER + b + j) * 32 + lane] = make_float4(tf32_lo(v[j].x), tf32_lo(v[j].y), tf32_lo(v[j].z), tf32_lo(v[j].w));
+                        for (int j = 0; j < UNR; j++)
+                            dst[(cw * PER + b + j) * 32 + lane] = make_float4(tf32_lo(v[j].x), tf32_lo(v[j].y), tf32_lo(v[j].z), tf32_lo(v[j].w));
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the MMA reads these writes through the async proxy
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(cb_base + (uint32_t)(s * 8));
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the MMA reads these writes through the async proxy
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(cb_base + (uint32_t)(s * 8));
             }
+            if (!ok && lane == 0) atomicExch(status, SB_ERR_TIMEOUT);
+        }
+        // ---------------- store warps (warps 14 and 15 of the FP32-accurate pair kernel, plain tiles only) ----------------
+        // Each owns one 32-row half of the staging buffer, used in turn by lane quarters b and b+2: when the two epilogue warps
+        // of a quarter have written it, every lane sends one row to memory with a bulk copy, and once the copies have read it
+        // the half is handed to the other quarter (one barrier per quarter, so a waiter is never more than one phase behind).
+        // The epilogue warps thus only write their registers out and go back to the next tile's accumulator chunks.
+        if (CONV && store_warps && warp >= 14) {
+            const int b = warp - 14;
+            uint32_t tcount = 0;
+            bool issued = false;
+            for (int k = 0; k < rounds && ok; k++) {
+                const int item = tc_item(k, cid, G, snake);
+                TcWork w;
+                if (item >= total_items || !tc_work<BN, BK, CTAS>(item, (int)rank, M, N, K, causal, nbatch, split_full, split_s, tri, w)) continue;
+                float* C = Cbase + (size_t)w.batch * c_batch_stride;
+                float* dst = w.split ? partial + ((size_t)w.slot * CTAS + rank) * (size_t)(TC_BM * BN) : C + (size_t)w.m0 * ldc + w.n0;
+                const long ld = w.split ? (long)BN : ldc;
+                const int rows_valid = w.split ? TC_BM : M - w.m0, cols_valid = w.split ? BN : N - w.n0;
+                const int accf = w.split ? 0 : acc;
+                const uint32_t bytes = (uint32_t)min(cols_valid, BN) * 4u;
+                for (int qq = b; qq < 4 && ok; qq += 2) {
+                    const uint32_t u = (tcount * 4 + (uint32_t)qq) >> 1;           // how many times this half has been used before
+                    ok = mbar_wait(&stg_full[b], u & 1);
+                    if (!ok) break;
+                    const int r = qq * 32 + lane;
+                    if (r < rows_valid) {
+                        const uint32_t src = smem_u32(stg + (size_t)(b * 32 + lane) * SLD);
+                        float* gp = dst + (size_t)r * ld;
+                        if (accf) asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(gp), "r"(src), "r"(bytes) : "memory");
+                        else      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gp), "r"(src), "r"(bytes) : "memory");
+                    }
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    issued = true;
+                    __syncwarp();
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&stg_go[qq ^ 2])) : "memory");
+                }
+                tcount++;
+            }
+            if (issued) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");      // every row has reached memory
             if (!ok && lane == 0) atomicExch(status, SB_ERR_TIMEOUT);
         }
     }
     } else {
-        // ---------------- epilogue: TMEM chunks -> register accumulators -> shared -> global ----------------
+        // ---------------- epilogue: TMEM chunks -> register accumulators -> staging -> global ----------------
         if (CONV) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(TC_REGS_EPI));          // whole warpgroups 1 and 2
         const int ew = warp - EPI0;                   // 0..7
         const int q = warp & 3;                       // TMEM lane quarter this warp may read
         const int col0 = (ew >> 2) * COLS_PER_WARP;   // which half of the tile's columns
-        float accr[COLS_PER_WARP];
+        constexpr int RPP = TC_STG_ROWS / TC_EPI_WARPS;      // rows per warp and pass in the row-wise work (8)
+        constexpr int RB = 4;                                // of which this many are in flight together in the dS transform
+        constexpr int NH = (BN + 127) / 128;                 // float4 per lane and row
+        uint32_t gch = 0, tcount = 0;           // chunks drained and tiles written so far, over all items
+        bool issued = false;
+        for (int k = 0; k < rounds && ok; k++) {
+            const int item = tc_item(k, cid, G, snake);
+            TcWork w;
+            if (item >= total_items || !tc_work<BN, BK, CTAS>(item, (int)rank, M, N, K, causal, nbatch, split_full, split_s, tri, w)) continue;
+            const int num_chunks = (w.num_kb + KB_PER_CHUNK - 1) / KB_PER_CHUNK;
+            float accr[COLS_PER_WARP];
 #pragma unroll
-        for (int j = 0; j < COLS_PER_WARP; j++) accr[j] = 0.f;
-        for (int ch = 0; ch < num_chunks && ok; ch++) {
-            const int buf = ch & 1;
-            ok = mbar_wait(&acc_full[buf], (ch >> 1) & 1);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + col0);
+            for (int j = 0; j < COLS_PER_WARP; j++) accr[j] = 0.f;
+            for (int ch = 0; ch < num_chunks && ok; ch++, gch++) {
+                const int buf = gch & 1;
+                ok = mbar_wait(&acc_full[buf], (gch >> 1) & 1);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + col0);
 #pragma unroll
-            for (int g = 0; g < COLS_PER_WARP / 32; g++) {
-                uint32_t r[32];
-                tc_ld32(taddr + (uint32_t)(g * 32), r);
-                if (g == COLS_PER_WARP / 32 - 1) {
-                    // the buffer is in registers: hand it back to the MMA warp before the adds
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if (CTAS == 2) mbar_arrive_cluster(mapa_u32(smem_u32(&acc_empty[buf]), 0));
-                        else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
+                for (int g = 0; g < COLS_PER_WARP / 32; g++) {
+                    uint32_t r[32];
+                    tc_ld32(taddr + (uint32_t)(g * 32), r);
+                    if (g == COLS_PER_WARP / 32 - 1) {
+                        // the buffer is in registers: hand it back to the MMA warp before the adds
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (CTAS == 2) mbar_arrive_cluster(mapa_u32(smem_u32(&acc_empty[buf]), 0));
+                            else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
+                        }
                     }
-                }
 #pragma unroll
-                for (int j = 0; j < 32; j++) accr[g * 32 + j] += __uint_as_float(r[j]);
+                    for (int j = 0; j < 32; j++) accr[g * 32 + j] += __uint_as_float(r[j]);
+                }
             }
-        }
-        if (!ok && lane == 0) atomicExch(status, SB_ERR_TIMEOUT);
-        // The last chunk has arrived, so every MMA has finished reading the operand stages: their shared
-        // memory now stages the 128 x BN tile, and whole rows leave through the bulk-copy engine (a plain copy,
-        // or an f32 add into C when accumulating: every element of C is touched by one CTA, so the sum does not
-        // depend on timing).  Measured: warps storing the tile themselves took 16 us per tile, the bulk copies 2 us.
-        constexpr int SLD = BN + 4;                   // padded row pitch (floats): conflict-free 16-byte accesses
-        constexpr int RPW = TC_BM / TC_EPI_WARPS;     // rows per epilogue warp in the row-wise passes
-        constexpr int NH = (BN + 127) / 128;          // float4 per lane and row
-        float* stage = (float*)smem;
-        // destination: the tile's place in C, or (a piece of a split tile) its own block of `partial`
-        float* dst = split ? partial + ((size_t)((tile_id - split_full) * split_s + piece) * CTAS + rank) * (size_t)(TC_BM * BN)
-                           : C + (size_t)m0 * ldc + n0;
-        const long ld = split ? (long)BN : ldc;
-        const int rows_valid = split ? TC_BM : M - m0, cols_valid = split ? BN : N - n0;
-        const int accf = split ? 0 : acc;
-        const int emode = split ? TC_EPI_PLAIN : epi.mode;
-        const bool vec = ((ld & 3) == 0) && ((((uintptr_t)dst) & 15) == 0) && (emode != TC_EPI_DS || (((uintptr_t)epi.aux) & 15) == 0);
-        const bool bulk = vec && (cols_valid >= BN || (cols_valid & 3) == 0);      // rows are 16-byte multiples at 16-byte addresses
-        {
-            // each thread holds one row of the tile; TC_EPI_EXP: P = exp(S*scale - lse[row]), zero past the diagonal
-            const int r = q * 32 + lane, grow = m0 + r;
-            float rv = 0.f;
-            if (emode == TC_EPI_EXP && r < rows_valid) rv = epi.vec[(size_t)grow * epi.vec_row_stride + (size_t)batch * epi.vec_batch_stride];
-            float* srow = stage + (size_t)r * SLD + col0;
-            if (emode == TC_EPI_EXP) {
-                const int kmax = grow - (n0 + col0);          // columns j <= kmax are on or below the diagonal
-#pragma unroll
-                for (int j = 0; j < COLS_PER_WARP; j += 4) {
-                    float4 v;
-                    v.x = j <= kmax ? expf(accr[j] * epi.scale - rv) : 0.f;         v.y = j + 1 <= kmax ? expf(accr[j + 1] * epi.scale - rv) : 0.f;
-                    v.z = j + 2 <= kmax ? expf(accr[j + 2] * epi.scale - rv) : 0.f; v.w = j + 3 <= kmax ? expf(accr[j + 3] * epi.scale - rv) : 0.f;
-                    *(float4*)(srow + j) = v;
-                }
-            } else {
+            if (CONV && store_warps) {
+                // plain tile: write this warp's rows into its quarter's half of the staging buffer and hand it to the store warp
+                const int b = q & 1;
+                // quarters 0 and 1 use their half first in every tile (free once quarter q+2 of the previous tile has left it),
+                // quarters 2 and 3 after quarter q-2 of the same tile
+                ok = ok && mbar_wait(&stg_go[q], q < 2 ? ((tcount & 1) ^ 1) : (tcount & 1));
+                if (!ok) break;
+                float* srow = stg + (size_t)(b * 32 + lane) * SLD + col0;
 #pragma unroll
                 for (int j = 0; j < COLS_PER_WARP; j += 4)
                     *(float4*)(srow + j) = make_float4(accr[j], accr[j + 1], accr[j + 2], accr[j + 3]);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");              // the bulk copies read these writes
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&stg_full[b])) : "memory");
+                tcount++;
+                continue;
             }
-        }
-        if (bulk && emode != TC_EPI_DS) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the bulk copies read these writes
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * TC_EPI_WARPS) : "memory");                              // epilogue warps only
-        if (ok && emode == TC_EPI_DS) {
-            // dS = P o (dP - D[row]) * scale, row-wise in the staged tile (P is read with whole-row accesses, four rows in flight)
-            float rowv[RPW];
-#pragma unroll
-            for (int i = 0; i < RPW; i++) {
-                const int r = ew + i * TC_EPI_WARPS;
-                rowv[i] = r < rows_valid ? epi.vec[(size_t)(m0 + r) * epi.vec_row_stride + (size_t)batch * epi.vec_batch_stride] : 0.f;
+            {
+                // a bounded wait may have run out in some warps only: all eight agree before the barriers of the store passes
+                int okall, okin = ok ? 1 : 0;
+                asm volatile("{\n\t.reg .pred pin, pout;\n\tsetp.ne.s32 pin, %1, 0;\n\tbar.red.and.pred pout, 1, %2, pin;\n\tselp.s32 %0, 1, 0, pout;\n\t}"
+                             : "=r"(okall) : "r"(okin), "n"(32 * TC_EPI_WARPS) : "memory");
+                if (!okall) { if (ok) ok = false; break; }
             }
-            const float* abase = epi.aux + (size_t)batch * c_batch_stride + (size_t)m0 * ldc + n0;
-#pragma unroll
-            for (int i0 = 0; i0 < RPW; i0 += 4) {
-                float4 av[4][NH];
-#pragma unroll
-                for (int ii = 0; ii < 4; ii++) {
-                    const int r = ew + (i0 + ii) * TC_EPI_WARPS;
-#pragma unroll
-                    for (int h = 0; h < NH; h++) {
-                        const int col = (h * 32 + lane) * 4;
-                        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (r < rows_valid && col < BN) {
-                            const float* ap = abase + (size_t)r * ldc + col;
-                            if (vec && col + 3 < cols_valid) t = *(const float4*)ap;
-                            else { if (col < cols_valid) t.x = ap[0]; if (col + 1 < cols_valid) t.y = ap[1]; if (col + 2 < cols_valid) t.z = ap[2]; if (col + 3 < cols_valid) t.w = ap[3]; }
-                        }
-                        av[ii][h] = t;
-                    }
-                }
-#pragma unroll
-                for (int ii = 0; ii < 4; ii++) {
-                    const int r = ew + (i0 + ii) * TC_EPI_WARPS;
-                    const float rv = rowv[i0 + ii];
-#pragma unroll
-                    for (int h = 0; h < NH; h++) {
-                        const int col = (h * 32 + lane) * 4;
-                        if (col < BN) {
-                            float4* sp = (float4*)(stage + (size_t)r * SLD + col);
-                            float4 v = *sp; const float4 pv = av[ii][h];
-                            v.x = pv.x * (v.x - rv) * epi.scale; v.y = pv.y * (v.y - rv) * epi.scale;
-                            v.z = pv.z * (v.z - rv) * epi.scale; v.w = pv.w * (v.w - rv) * epi.scale;
-                            *sp = v;
-                        }
-                    }
-                }
-            }
-            if (bulk) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();                              // a warp copies out the rows it has just transformed
-        }
-        if (ok && bulk) {
+            // The tile leaves 32 rows (one TMEM lane quarter) at a time through the staging buffer: the two warps that hold
+            // the quarter write it (with the exp transform if asked), all eight warps do the row-wise work on it (the dS
+            // transform, which reads a second matrix), and whole rows go out as bulk copies (an f32 add into C when
+            // accumulating: every element of C is touched by one CTA, so the sum does not depend on timing).
+            // Measured: warps storing the tile themselves took 16 us per tile, the bulk copies 2 us.
+            float* C = Cbase + (size_t)w.batch * c_batch_stride;
+            // destination: the tile's place in C, or (a piece of a split tile) its own block of `partial`
+            float* dst = w.split ? partial + ((size_t)w.slot * CTAS + rank) * (size_t)(TC_BM * BN) : C + (size_t)w.m0 * ldc + w.n0;
+            const long ld = w.split ? (long)BN : ldc;
+            const int rows_valid = w.split ? TC_BM : M - w.m0, cols_valid = w.split ? BN : N - w.n0;
+            const int accf = w.split ? 0 : acc;
+            const int emode = w.split ? TC_EPI_PLAIN : epi.mode;
+            const bool vec = ((ld & 3) == 0) && ((((uintptr_t)dst) & 15) == 0) && (emode != TC_EPI_DS || (((uintptr_t)epi.aux) & 15) == 0);
+            const bool bulk = vec && (cols_valid >= BN || (cols_valid & 3) == 0);      // rows are 16-byte multiples at 16-byte addresses
             const uint32_t bytes = (uint32_t)min(cols_valid, BN) * 4u;
-            if (lane < RPW) {
-                const int r = ew + lane * TC_EPI_WARPS;
-                if (r < rows_valid) {
-                    const uint32_t src = smem_u32(stage + (size_t)r * SLD);
-                    float* gp = dst + (size_t)r * ld;
-                    if (accf) asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(gp), "r"(src), "r"(bytes) : "memory");
-                    else      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gp), "r"(src), "r"(bytes) : "memory");
+            const float* abase = emode == TC_EPI_DS ? epi.aux + (size_t)w.batch * c_batch_stride + (size_t)w.m0 * ldc + w.n0 : nullptr;
+#pragma unroll 1
+            for (int p = 0; p < TC_BM / TC_STG_ROWS; p++) {
+                // the copies of the previous pass must have read the staging buffer before it is written again
+                if (issued && lane < RPP) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * TC_EPI_WARPS) : "memory");                                  // epilogue warps only
+                if ((q >> 1) == p) {
+                    // each thread holds one row of the tile; TC_EPI_EXP: P = exp(S*scale - lse[row]), zero past the diagonal
+                    const int r = q * 32 + lane, grow = w.m0 + r;
+                    float* srow = stg + (size_t)((q & 1) * 32 + lane) * SLD + col0;
+                    if (emode == TC_EPI_EXP) {
+                        const float rv = r < rows_valid ? epi.vec[(size_t)grow * epi.vec_row_stride + (size_t)w.batch * epi.vec_batch_stride] : 0.f;
+                        const int kmax = grow - (w.n0 + col0);        // columns j <= kmax are on or below the diagonal
+#pragma unroll
+                        for (int j = 0; j < COLS_PER_WARP; j += 4) {
+                            float4 v;
+                            v.x = j <= kmax ? expf(accr[j] * epi.scale - rv) : 0.f;         v.y = j + 1 <= kmax ? expf(accr[j + 1] * epi.scale - rv) : 0.f;
+                            v.z = j + 2 <= kmax ? expf(accr[j + 2] * epi.scale - rv) : 0.f; v.w = j + 3 <= kmax ? expf(accr[j + 3] * epi.scale - rv) : 0.f;
+                            *(float4*)(srow + j) = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < COLS_PER_WARP; j += 4)
+                            *(float4*)(srow + j) = make_float4(accr[j], accr[j + 1], accr[j + 2], accr[j + 3]);
+                    }
+                    if (bulk && emode != TC_EPI_DS) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the bulk copies read these writes
                 }
-                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-            }
-        } else if (ok) {
-            // ragged or unaligned rows: the warps store the (already transformed) tile themselves
-            for (int r = ew; r < TC_BM && r < rows_valid; r += TC_EPI_WARPS) {
-                const float* srow = stage + (size_t)r * SLD;
-                float* crow = dst + (size_t)r * ld;
-                for (int col = lane; col < BN && col < cols_valid; col += 32)
-                    crow[col] = accf ? crow[col] + srow[col] : srow[col];
+                asm volatile("bar.sync 1, %0;" ::"n"(32 * TC_EPI_WARPS) : "memory");                                  // epilogue warps only
+                const int i0 = ew * RPP;                    // this warp's rows of the staged rows
+                const int prow = p * TC_STG_ROWS;           // first tile row of this pass
+                if (emode == TC_EPI_DS) {
+                    // dS = P o (dP - D[row]) * scale, row-wise in the staged rows (P is read with whole-row accesses)
+#pragma unroll
+                    for (int ib = 0; ib < RPP; ib += RB) {
+                        float4 av[RB][NH];
+                        float rowv[RB];
+#pragma unroll
+                        for (int ii = 0; ii < RB; ii++) {
+                            const int r = prow + i0 + ib + ii;
+                            rowv[ii] = r < rows_valid ? epi.vec[(size_t)(w.m0 + r) * epi.vec_row_stride + (size_t)w.batch * epi.vec_batch_stride] : 0.f;
+#pragma unroll
+                            for (int h = 0; h < NH; h++) {
+                                const int col = (h * 32 + lane) * 4;
+                                float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+                                if (r < rows_valid && col < BN) {
+                                    const float* ap = abase + (size_t)r * ldc + col;
+                                    if (vec && col + 3 < cols_valid) t = *(const float4*)ap;
+                                    else { if (col < cols_valid) t.x = ap[0]; if (col + 1 < cols_valid) t.y = ap[1]; if (col + 2 < cols_valid) t.z = ap[2]; if (col + 3 < cols_valid) t.w = ap[3]; }
+                                }
+                                av[ii][h] = t;
+                            }
+                        }
+#pragma unroll
+                        for (int ii = 0; ii < RB; ii++) {
+                            const float rv = rowv[ii];
+#pragma unroll
+                            for (int h = 0; h < NH; h++) {
+                                const int col = (h * 32 + lane) * 4;
+                                if (col < BN) {
+                                    float4* sp = (float4*)(stg + (size_t)(i0 + ib + ii) * SLD + col);
+                                    float4 v = *sp; const float4 pv = av[ii][h];
+                                    v.x = pv.x * (v.x - rv) * epi.scale; v.y = pv.y * (v.y - rv) * epi.scale;
+                                    v.z = pv.z * (v.z - rv) * epi.scale; v.w = pv.w * (v.w - rv) * epi.scale;
+                                    *sp = v;
+                                }
+                            }
+                        }
+                    }
+                    if (bulk) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();                          // a warp copies out the rows it has just transformed
+                }
+                if (bulk) {
+                    if (lane < RPP) {
+                        const int r = prow + i0 + lane;
+                        if (r < rows_valid) {
+                            const uint32_t src = smem_u32(stg + (size_t)(i0 + lane) * SLD);
+                            float* gp = dst + (size_t)r * ld;
+                            if (accf) asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(gp), "r"(src), "r"(bytes) : "memory");
+                            else      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gp), "r"(src), "r"(bytes) : "memory");
+                        }
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");       // one group per pass and lane, also when the row is outside C
+                        issued = true;
+                    }
+                } else {
+                    // ragged or unaligned rows: the warps store the (already transformed) rows themselves
+                    for (int ii = 0; ii < RPP; ii++) {
+                        const int r = prow + i0 + ii;
+                        if (r >= rows_valid) break;
+                        const float* srow = stg + (size_t)(i0 + ii) * SLD;
+                        float* crow = dst + (size_t)r * ld;
+                        for (int col = lane; col < BN && col < cols_valid; col += 32)
+                            crow[col] = accf ? crow[col] + srow[col] : srow[col];
+                    }
+                }
             }
         }
+        if (!ok && lane == 0) atomicExch(status, SB_ERR_TIMEOUT);
+        if (issued) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");              // every row has reached memory
         tc_fence_before();
     }
     __syncthreads();
@@ -736,6 +875,8 @@ static bool tc_make_map(CUtensorMap* m, const float* base, const TcOperand& op, 
     return true;
 }
 
+static inline bool tc_aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
+
 template <int BN, int BK, int NTERMS, int STAGES, int CTAS = 1, bool AMN = false, bool BMN = false>
 static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
     CUtensorMap mAh, mAl, mBh, mBl;
@@ -745,10 +886,10 @@ static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
     if (NTERMS == 3 && !CONV) { if (!tc_make_map(&mAl, p.A.lo, p.A, p.K, BK, TC_BM) || !tc_make_map(&mBl, p.B.lo, p.B, p.K, BK, BROWS)) return false; }
     else { mAl = mAh; mBl = mBh; }
     constexpr int STAGE_BYTES = (NTERMS == 3 ? 2 : 1) * (TC_BM + BROWS) * BK * 4;
-    constexpr size_t tile_bytes = (size_t)TC_BM * (BN + 4) * 4;
+    constexpr size_t stg_bytes = (size_t)TC_STG_ROWS * (BN + 4) * 4;
     constexpr size_t ring_bytes = (size_t)STAGES * STAGE_BYTES;
-    static_assert(tile_bytes <= ring_bytes, "the output tile is staged in the operand ring");
-    size_t smem = ring_bytes + 1024 + 256;
+    constexpr size_t smem = ring_bytes + stg_bytes + 1024 + 512;      // ring, output staging, alignment slack, barriers
+    static_assert(smem <= 232448, "shared memory of one CTA");
     auto kern = gemm_tc_kernel<BN, BK, NTERMS, STAGES, CTAS, AMN, BMN>;
     constexpr int THREADS = CONV ? TC_CONV_THREADS : TC_THREADS;
     static bool attr_set = false;
@@ -756,24 +897,27 @@ static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
         attr_set = true;
     }
-    const int tiles = ((p.N + BN - 1) / BN) * ((p.M + TC_BM * CTAS - 1) / (TC_BM * CTAS));
+    const int tiles_m = (p.M + TC_BM * CTAS - 1) / (TC_BM * CTAS), tiles_n = (p.N + BN - 1) / BN;
+    // square tile grid with everything above the diagonal skipped: only the tiles on or below it are enumerated
+    const int tri = (p.causal == TC_CAUSAL_SKIP_UPPER && BN == TC_BM * CTAS && tiles_m == tiles_n) ? 1 : 0;
+    const int tiles = tri ? tiles_m * (tiles_m + 1) / 2 : tiles_m * tiles_n;
+    const int slots = (c->pub.gpu_sm_count > 0 ? c->pub.gpu_sm_count : 148) / CTAS;
     // tail split: cut the tiles of the last, partly filled wave into k pieces that fill it
     int split_full = tiles, split_s = 1;
     float* partial = nullptr;
     if (c->gemm_tail_split && p.nbatch <= 1 && p.causal == TC_CAUSAL_NONE) {
-        const int slots = (c->pub.gpu_sm_count > 0 ? c->pub.gpu_sm_count : 148) / CTAS;
         const int full = tiles / slots * slots, rem = tiles - full;
         constexpr int KB_PER_CHUNK = TC_CHUNK_K / BK > 0 ? TC_CHUNK_K / BK : 1;
         const int num_kb = (p.K + BK - 1) / BK;
-        // measured: a CTA's prologue and epilogue cost about as much as 256 floats of k (9 us against 0.49 us per
-        // 16 floats), the fix-up pass about as much again; costs below are in tile times
-        const double ovh = 16.0 * 16 / BK / num_kb;
+        // an item's epilogue costs about as much as 96 floats of k (3 us against 0.49 us per 16 floats), the fix-up
+        // pass about as much as 256; costs below are in tile times
+        const double ovh = 6.0 * 16 / BK / num_kb, fix = 16.0 * 16 / BK / num_kb;
         double best = rem > 0 ? 1.0 + ovh : 0.0;
         for (int s = 2; s <= 8 && rem > 0; s++) {
             const int per = ((num_kb + s - 1) / s + KB_PER_CHUNK - 1) / KB_PER_CHUNK * KB_PER_CHUNK;
             if (per * (s - 1) >= num_kb || per * BK < 128) continue;      // an empty or very short piece
             const int waves = (rem * s + slots - 1) / slots;
-            const double cost = waves * ((double)per / num_kb + ovh) + ovh;
+            const double cost = waves * ((double)per / num_kb + ovh) + fix;
             if (cost < best - 0.05) { best = cost; split_s = s; }
         }
         if (split_s > 1) {
@@ -783,8 +927,20 @@ static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
         }
     }
     const int grid_tiles = split_full + (tiles - split_full) * split_s;
-    dim3 grid((unsigned)(grid_tiles * CTAS), (unsigned)(p.nbatch > 0 ? p.nbatch : 1));
+    const int nbatch = p.nbatch > 0 ? p.nbatch : 1;
+    const int total_items = grid_tiles * nbatch;
+    // causal k ranges: items are ordered longest first and dealt to half as many clusters in snake order
+    static int snake_on = -1;
+    if (snake_on < 0) { const char* e = getenv("SERAPH_B200_GEMM_SNAKE"); snake_on = (e && e[0] == '0') ? 0 : 1; }
+    const int snake = (snake_on && (p.causal == TC_CAUSAL_K_UPTO_M || p.causal == TC_CAUSAL_K_FROM_M)) ? 1 : 0;
+    int G = snake ? (total_items + 1) / 2 : total_items;
+    if (G > slots) G = slots;
+    if (G < 1) G = 1;
+    dim3 grid((unsigned)(G * CTAS), 1u);
     const int swap_mask = (tc_swapped(p.A) ? 1 : 0) | (tc_swapped(p.B) ? 2 : 0);
+    // plain tiles whose rows are 16-byte multiples at 16-byte addresses leave through the store warps
+    const int store_warps = (CONV && p.epi.mode == TC_EPI_PLAIN && (p.ldc & 3) == 0 && (p.N & 3) == 0 && (p.c_batch_stride & 3) == 0 &&
+                             tc_aligned16(p.C)) ? 1 : 0;
     if (CTAS == 2) {
         cudaLaunchConfig_t cfg;
         memset(&cfg, 0, sizeof cfg);
@@ -795,11 +951,12 @@ static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
         cfg.attrs = at; cfg.numAttrs = 1;
         if (cudaLaunchKernelEx(&cfg, kern, mAh, mAl, mBh, mBl, p.C, p.ldc, p.c_batch_stride, p.M, p.N, p.K, p.acc, p.causal,
                                p.A.c2_base, p.A.c2_step, p.B.c2_base, p.B.c2_step, swap_mask, split_full, split_s, partial, p.epi,
-                               c->d_status) != cudaSuccess) return false;
+                               nbatch, total_items, snake, tri, store_warps, c->d_status) != cudaSuccess) return false;
     } else {
         kern<<<grid, THREADS, smem, (cudaStream_t)c->pub.stream>>>(mAh, mAl, mBh, mBl, p.C, p.ldc, p.c_batch_stride, p.M, p.N, p.K, p.acc,
                                                                      p.causal, p.A.c2_base, p.A.c2_step, p.B.c2_base, p.B.c2_step,
-                                                                     swap_mask, split_full, split_s, partial, p.epi, c->d_status);
+                                                                     swap_mask, split_full, split_s, partial, p.epi,
+                                                                     nbatch, total_items, snake, tri, store_warps, c->d_status);
     }
     c->launches++;
     if (split_s > 1) {
@@ -820,16 +977,16 @@ static bool tc_launch(sb_ctx_t* c, const TcProblem& p, int nterms) {
         const int lay = (p.A.mn ? 1 : 0) | (p.B.mn ? 2 : 0);
         if (p.N > 128) {
             if (nterms == 3) switch (lay) {
-                case 0: return tc_launch_t<256, 16, 3, 6, 2, false, false>(c, p);
-                case 1: return tc_launch_t<256, 16, 3, 6, 2, true, false>(c, p);
-                case 2: return tc_launch_t<256, 16, 3, 6, 2, false, true>(c, p);
-                default: return tc_launch_t<256, 16, 3, 6, 2, true, true>(c, p);
+                case 0: return tc_launch_t<256, 16, 3, 5, 2, false, false>(c, p);
+                case 1: return tc_launch_t<256, 16, 3, 5, 2, true, false>(c, p);
+                case 2: return tc_launch_t<256, 16, 3, 5, 2, false, true>(c, p);
+                default: return tc_launch_t<256, 16, 3, 5, 2, true, true>(c, p);
             }
             switch (lay) {
-                case 0: return tc_launch_t<256, 32, 1, 6, 2, false, false>(c, p);
-                case 1: return tc_launch_t<256, 32, 1, 6, 2, true, false>(c, p);
-                case 2: return tc_launch_t<256, 32, 1, 6, 2, false, true>(c, p);
-                default: return tc_launch_t<256, 32, 1, 6, 2, true, true>(c, p);
+                case 0: return tc_launch_t<256, 32, 1, 5, 2, false, false>(c, p);
+                case 1: return tc_launch_t<256, 32, 1, 5, 2, true, false>(c, p);
+                case 2: return tc_launch_t<256, 32, 1, 5, 2, false, true>(c, p);
+                default: return tc_launch_t<256, 32, 1, 5, 2, true, true>(c, p);
             }
         }
         // narrow outputs (attention's products with V, K, Q, dO: N = head_dim): 256 x 128 tiles
@@ -847,11 +1004,10 @@ static bool tc_launch(sb_ctx_t* c, const TcProblem& p, int nterms) {
         }
     }
     if (p.A.mn || p.B.mn || (nterms == 3 && (!p.A.lo || !p.B.lo))) return false;    // only the pair kernel takes these
-    if (p.N > 128) return nterms == 3 ? tc_launch_t<256, 16, 3, 4>(c, p) : tc_launch_t<256, 32, 1, 4>(c, p);
-    return nterms == 3 ? tc_launch_t<128, 16, 3, 6>(c, p) : tc_launch_t<128, 32, 1, 6>(c, p);
+    if (p.N > 128) return nterms == 3 ? tc_launch_t<256, 16, 3, 3>(c, p) : tc_launch_t<256, 32, 1, 3>(c, p);
+    return nterms == 3 ? tc_launch_t<128, 16, 3, 5>(c, p) : tc_launch_t<128, 32, 1, 5>(c, p);
 }
 
-static inline bool tc_aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
 static inline int tc_ew_blocks(sb_ctx_t* c, size_t items) {
     size_t b = (items + 255) / 256, cap = (size_t)(c->pub.gpu_sm_count > 0 ? c->pub.gpu_sm_count : 148) * 8;
     return (int)(b > cap ? cap : (b ? b : 1));

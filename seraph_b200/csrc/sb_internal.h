@@ -53,6 +53,7 @@ typedef struct sb_ctx {
     int status;                      /* last host-side status */
     int* d_status;                   /* device status word (bounds checks, bounded waits) */
     int gemm_mode;                   /* SB_GEMM_* (use_bf16 in pub overrides to BF16) */
+    int attn_fused;                  /* 1: P and dS of the attention backward come out of the score products' epilogues */
     int gemm_tail_split;             /* 1: tiles of the last partial wave are cut into k pieces */
     int gemm_pair;                   /* 1: plain GEMMs run on CTA pairs (cta_group::2), 0: one CTA per tile */
     int lora_exact;                  /* 0: reference behaviour (adapter dX term left out), 1: full chain rule */

@@ -154,8 +154,11 @@ ATT_CASES = [
 ]
 
 
+@pytest.mark.parametrize("fused", [0, 1])
 @pytest.mark.parametrize("ss,Hq,Hkv,hd", ATT_CASES)
-def test_attention_forward_backward(ctx, ss, Hq, Hkv, hd):
+def test_attention_forward_backward(ctx, ss, Hq, Hkv, hd, fused):
+    """fused = 1: P and dS of the backward come out of the score products' epilogues instead of a streaming kernel."""
+    ctx.set_attn_fused(fused)
     ss = np.array(ss, np.uint32)
     T, B = int(ss[-1]), len(ss) - 1
     r = rng(T + Hq + hd)
@@ -183,6 +186,7 @@ def test_attention_forward_backward(ctx, ss, Hq, Hkv, hd):
     ctx.lib.cuda_train_batch_attention_backward_packed(ctx.h, bq.b, bk.b, bv.b, bout.b, blse.b, bdo.b, bdq.b, bdk2.b, bdv2.b, bs.b,
                                                        T, B, Hq, Hkv, hd, int(np.diff(ss).max()))
     assert np.array_equal(bdq.numpy(), dq1) and np.array_equal(bdk2.numpy(), dk1) and np.array_equal(bdv2.numpy(), dv1)
+    ctx.set_attn_fused(0)
     ctx.release(bq, bk, bv, bdo, bs, bout, blse, bdq, bdk, bdv, bdk2, bdv2)
 
 

@@ -909,9 +909,9 @@ static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
         const int full = tiles / slots * slots, rem = tiles - full;
         constexpr int KB_PER_CHUNK = TC_CHUNK_K / BK > 0 ? TC_CHUNK_K / BK : 1;
         const int num_kb = (p.K + BK - 1) / BK;
-        // an item's epilogue costs about as much as 96 floats of k (3 us against 0.49 us per 16 floats), the fix-up
-        // pass about as much as 256; costs below are in tile times
-        const double ovh = 6.0 * 16 / BK / num_kb, fix = 16.0 * 16 / BK / num_kb;
+        // an item's epilogue costs about as much as 160 floats of k (5.3 us against 0.52 us per 16 floats, measured with a
+        // K sweep), the fix-up pass about as much as 256; costs below are in tile times
+        const double ovh = 10.0 * 16 / BK / num_kb, fix = 16.0 * 16 / BK / num_kb;
         double best = rem > 0 ? 1.0 + ovh : 0.0;
         for (int s = 2; s <= 8 && rem > 0; s++) {
             const int per = ((num_kb + s - 1) / s + KB_PER_CHUNK - 1) / KB_PER_CHUNK * KB_PER_CHUNK;

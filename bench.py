@@ -231,10 +231,10 @@ def run_ours(args):
             "metric": "train tokens/sec (fwd+bwd+AdamW)", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": n_warm, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32" if args.gemm_mode in (0, 3) else ("tf32" if args.gemm_mode == 1 else "bf16"),
+            "dtype": "f32" if args.gemm_mode in (0, 3, 4) else ("tf32" if args.gemm_mode == 1 else "bf16"),
             "data": "synthetic",
             "config": {"workload": args.workload, "tokens_per_rank": T, "global_tokens": T * world,
-                       "parallelism": f"dp{world}", "gemm_mode": ["fp32x3_tcgen05", "tf32_tcgen05", "bf16_tcgen05", "fp32_cuda_cores"][args.gemm_mode],
+                       "parallelism": f"dp{world}", "gemm_mode": ["fp32x3_tcgen05", "tf32_tcgen05", "bf16_tcgen05", "fp32_cuda_cores", "fp32_f16x3_tcgen05"][args.gemm_mode],
                        "l2": "working set per step (weights 6.9 GB + activations) far exceeds the 126 MB L2; no flush needed",
                        "optimizer": "AdamW lr 3.14e-4 (reference warm-up), betas 0.9/0.999, wd 0.01, no clip (the reference has none)"},
             "loss": loss_res, "loss_first": loss0,
@@ -336,7 +336,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=list(WORKLOADS)[0],
                     help="a key of WORKLOADS or its index (0 = the benchmark configuration, 1 = profiling slice, 2 = 33M model)")
-    ap.add_argument("--gemm-mode", type=int, default=0, help="0 FP32-accurate tensor cores (default), 1 TF32, 2 BF16, 3 CUDA cores")
+    ap.add_argument("--gemm-mode", type=int, default=0, help="0 FP32-accurate tensor cores (default), 1 TF32, 2 BF16, 3 CUDA cores, 4 FP32-accurate with FP16 parts where possible")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--short-warmup", action="store_true", help="honour --warmup below 3 (profiler captures only; not a valid bench number)")
     args = ap.parse_args()

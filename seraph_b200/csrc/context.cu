@@ -261,7 +261,7 @@ int seraph_b200_last_status(cuda_train_context_t* ctx) {
 
 int seraph_b200_set_gemm_mode(cuda_train_context_t* ctx, int mode) {
     sb_ctx_t* c = sb_priv(ctx);
-    if (!c || mode < 0 || mode > 3) return SB_ERR_ARG;
+    if (!c || mode < 0 || mode > 4) return SB_ERR_ARG;
     c->gemm_mode = mode;
     return SB_OK;
 }

@@ -50,9 +50,10 @@ extern "C" int sb_gemm_tc(sb_ctx_t* c, const float* A, const float* B, float* C,
     bool a_kmajor = !tA;       // tA: A is [K,M]
     bool b_kmajor = tB != 0;   // !tB: B is [K,N]
     if ((a_kmajor || b_kmajor) && (K & 3)) return 1;                     // in-place K-major rows need a 16-byte pitch
-    const bool x3 = (mode == SB_GEMM_FP32X3);
+    const bool x3 = (mode == SB_GEMM_FP32X3 || mode == SB_GEMM_FP16X3);
     TcProblem p;
     memset(&p.epi, 0, sizeof p.epi);
+    p.amax = nullptr;
     p.C = C; p.ldc = N; p.c_batch_stride = 0; p.M = M; p.N = N; p.K = K; p.acc = acc; p.nbatch = 1; p.causal = TC_CAUSAL_NONE;
     // direct path: the pair kernel on the caller's arrays (rows of either layout must be 16-byte multiples)
     if (c->gemm_pair && M > 128 && N > 128 && (a_kmajor ? (K & 3) == 0 : (M & 3) == 0) && (b_kmajor ? (K & 3) == 0 : (N & 3) == 0)) {
@@ -60,6 +61,16 @@ extern "C" int sb_gemm_tc(sb_ctx_t* c, const float* A, const float* B, float* C,
         p.B.hi = B; p.B.lo = nullptr; p.B.rows = N; p.B.mn = b_kmajor ? 0 : 1; p.B.pitch = b_kmajor ? K : N;
         p.A.c2_dim = p.B.c2_dim = 1; p.A.c2_stride = p.B.c2_stride = 0; p.A.c2_base = p.B.c2_base = 0; p.A.c2_step = p.B.c2_step = 0;
         int tg = sb_tick_begin(c, SB_CLS_GEMM);
+        if (mode == SB_GEMM_FP16X3 && a_kmajor && b_kmajor && N > 128) {
+            // FP16 split: the operands' largest magnitudes first (one launch over both)
+            if (!c->d_amax && sb_check(c, cudaMalloc(&c->d_amax, 2 * sizeof(float)), "amax alloc")) return 1;
+            cudaStream_t st = (cudaStream_t)c->pub.stream;
+            cudaMemsetAsync(c->d_amax, 0, 2 * sizeof(float), st);
+            tc_amax_kernel<<<dim3(tc_ew_blocks(c, ((size_t)(M > N ? M : N) * K) / 4), 2), 256, 0, st>>>(A, (size_t)M * K / 4, B, (size_t)N * K / 4,
+                                                                                                         (unsigned*)c->d_amax);
+            c->launches++;
+            p.amax = c->d_amax;
+        }
         bool ok = tc_launch(c, p, x3 ? 3 : 1);
         sb_tick_end(c, tg, 2.0 * M * N * K, 4.0 * ((double)M * K + (double)N * K + (double)M * N * (acc ? 2 : 1)));
         if (!ok) { sb_set_status(c, SB_ERR_CUDA); return 1; }

@@ -37,6 +37,7 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <cuda_fp16.h>
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
@@ -81,6 +82,7 @@ struct TcProblem {
     float* C; long ldc; long c_batch_stride;
     int M, N, K, acc, nbatch, causal;
     TcEpi epi;
+    const float* amax;       // FP16 split: device floats {max |A|, max |B|}; NULL = TF32 split
 };
 
 // --------------------------------------------------------------------------- PTX helpers
@@ -134,6 +136,19 @@ __device__ __forceinline__ void tc_mma_tf32_pair(uint32_t tmem_d, uint64_t adesc
                  "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+__device__ __forceinline__ void tc_mma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// FP16 split: power-of-two exponent s with amax * 2^s in [2^14, 2^15) (0 for an all-zero operand); 2^s as a float
+__device__ __forceinline__ int tc_f16_shift(float amax) {
+    const int e = (int)((__float_as_uint(amax) >> 23) & 255u) - 127;
+    if (amax == 0.f || e < -100) return 0;
+    const int sh = 14 - e;
+    return sh < -100 ? -100 : (sh > 100 ? 100 : sh);
+}
+__device__ __forceinline__ float tc_pow2(int sh) { return __uint_as_float((uint32_t)(127 + sh) << 23); }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
 }
@@ -185,7 +200,7 @@ __device__ __forceinline__ uint64_t make_kmajor_desc(uint32_t smem_addr) {
     d |= (uint64_t)1 << 16;                                      // leading byte offset (unused for swizzled K-major)
     d |= (uint64_t)(((8 * SWZ) >> 4) & 0x3fff) << 32;            // stride byte offset: one 8-row group
     d |= (uint64_t)1 << 46;                                      // descriptor version for sm_100
-    d |= (uint64_t)(SWZ == 128 ? 2 : 4) << 61;                   // swizzle mode: 128B = 2, 64B = 4
+    d |= (uint64_t)(SWZ == 128 ? 2 : (SWZ == 64 ? 4 : 6)) << 61; // swizzle mode: 128B = 2, 64B = 4, 32B = 6
     return d;
 }
 
@@ -302,14 +317,19 @@ __device__ __forceinline__ int tc_item(int k, int cid, int G, int snake) { retur
 // Barriers, tensor memory and the operand ring live across items, so while the epilogue warps write one tile out
 // (through a small dedicated staging buffer, 32 rows at a time) the producer, the converters and the MMA warp are
 // already working on the next item: only the epilogue itself is left of the per-tile overhead.
-template <int BN, int BK, int NTERMS, int STAGES, int CTAS, bool AMN, bool BMN>
+// F16 (FP32-accurate pair kernel, K-major operands): the hi/lo parts are FP16 instead of TF32.  Each operand is scaled
+// by a power of two that brings its largest magnitude to [2^14, 2^15) (amax[0] for A, amax[1] for B, computed by
+// tc_amax_kernel before the launch), h1 = fp16(x'), h2 = fp16(x' - h1): 22+ significant bits like the TF32 split, but the
+// three MMAs per k block are kind::f16 with K = 16, half the tensor-core cycles.  The converter warps write the two
+// 16-bit tiles (32-byte rows, 32-byte swizzle) from the landed FP32 stage; the epilogue undoes the scales.
+template <int BN, int BK, int NTERMS, int STAGES, int CTAS, bool AMN, bool BMN, bool F16 = false>
 __global__ void __launch_bounds__((CTAS == 2 && NTERMS == 3) ? TC_CONV_THREADS : TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
                float* __restrict__ Cbase, long ldc, long c_batch_stride, int M, int N, int K, int acc, int causal,
                int a_c2_base, int a_c2_step, int b_c2_base, int b_c2_step, int swap_mask,
                int split_full, int split_s, float* __restrict__ partial, const TcEpi epi,
-               int nbatch, int total_items, int snake, int tri, int store_warps, int* status) {
+               int nbatch, int total_items, int snake, int tri, int store_warps, const float* __restrict__ amax, int* status) {
     constexpr int SWZ = BK * 4;
     constexpr int BROWS = BN / CTAS;                             // B rows this CTA loads
     constexpr int TILE_M = TC_BM * CTAS;
@@ -317,10 +337,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
     constexpr int HI_BYTES = A_BYTES + B_BYTES;
     constexpr int STAGE_BYTES = (NTERMS == 3 ? 2 : 1) * HI_BYTES;
     constexpr bool CONV = (CTAS == 2 && NTERMS == 3);            // lo parts made in the kernel
+    static_assert(!F16 || (CONV && !AMN && !BMN && BK == 16), "FP16 split: FP32-accurate pair kernel, K-major operands");
+    constexpr int HA_BYTES = TC_BM * BK * 2, HB_BYTES = BROWS * BK * 2;      // 16-bit tiles of the FP16 split
+    static_assert(!F16 || 2 * (HA_BYTES + HB_BYTES) == HI_BYTES, "the two 16-bit parts take the place of the lo stage");
     static_assert(CTAS == 2 || (!AMN && !BMN), "MN-major operands: CTA-pair kernel only");
     static_assert(BROWS % 32 == 0, "an MN-major tile is made of boxes of 32 rows");
     constexpr uint32_t TMEM_COLS = 2 * BN;                       // two accumulator buffers
-    constexpr int KB_PER_CHUNK = TC_CHUNK_K / BK;
+    constexpr int KB_PER_CHUNK = (F16 ? 2 : 1) * TC_CHUNK_K / BK;     // twelve MMAs per accumulation chunk either way
     constexpr int COLS_PER_WARP = BN / (TC_EPI_WARPS / 4);       // 128 or 64 register accumulators per epilogue thread
     constexpr int SLD = BN + 4;                                  // padded row pitch of the staging buffer (floats)
     extern __shared__ uint8_t smem_raw[];
@@ -413,7 +436,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
         // ---------------- MMA issuer ----------------
         if (leader && elect_one()) {
             // instruction descriptor: D = F32, A = B = TF32, majors of the operands, N and M of the tile
-            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((AMN ? 1u : 0u) << 15) | ((BMN ? 1u : 0u) << 16) |
+            // (kind::f16: A = B = F16, format code 0)
+            const uint32_t idesc = (1u << 4) | ((F16 ? 0u : 2u) << 7) | ((F16 ? 0u : 2u) << 10) | ((AMN ? 1u : 0u) << 15) | ((BMN ? 1u : 0u) << 16) |
                                    ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
             uint32_t git = 0, gch = 0;             // k blocks and chunks consumed so far, over all items
             for (int k = 0; k < rounds && ok; k++) {
@@ -436,6 +460,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
                         if (!ok) break;
                         tc_fence_after();
                         const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+                        if (F16) {
+                            // 16-bit tiles after the FP32 landing area: h1 A, h1 B, h2 A, h2 B; one K = 16 MMA per term
+                            const uint64_t a1 = make_kmajor_desc<32>(sa + HI_BYTES), b1 = make_kmajor_desc<32>(sa + HI_BYTES + HA_BYTES);
+                            const uint64_t a2 = make_kmajor_desc<32>(sa + HI_BYTES + HA_BYTES + HB_BYTES);
+                            const uint64_t b2 = make_kmajor_desc<32>(sa + HI_BYTES + 2 * HA_BYTES + HB_BYTES);
+                            tc_mma_f16_pair(tmem_d, a1, b1, idesc, first ? 0u : 1u);
+                            tc_mma_f16_pair(tmem_d, a2, b1, idesc, 1);
+                            tc_mma_f16_pair(tmem_d, a1, b2, idesc, 1);
+                            first = false;
+                            tc_commit_pair(&empty[s]);
+                            continue;
+                        }
                         const uint64_t ah = AMN ? make_mnmajor_desc<BK>(sa) : make_kmajor_desc<SWZ>(sa);
                         const uint64_t bh = BMN ? make_mnmajor_desc<BK>(sa + A_BYTES) : make_kmajor_desc<SWZ>(sa + A_BYTES);
                         const uint64_t al = AMN ? make_mnmajor_desc<BK>(sa + HI_BYTES) : make_kmajor_desc<SWZ>(sa + HI_BYTES);
@@ -474,6 +510,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
             constexpr int UNR = PER % 8 == 0 ? 8 : (PER % 6 == 0 ? 6 : 4);
             static_assert(N4 % (32 * TC_CONV_WARPS) == 0 && PER % UNR == 0, "stage size against the converter's unroll");
             const uint32_t cb_base = mapa_u32(smem_u32(&conv[0]), 0);
+            const float scale_a = F16 ? tc_pow2(tc_f16_shift(amax[0])) : 1.f, scale_b = F16 ? tc_pow2(tc_f16_shift(amax[1])) : 1.f;
             uint32_t git = 0;
             for (int k = 0; k < rounds && ok; k++) {
                 const int item = tc_item(k, cid, G, snake);
@@ -483,6 +520,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
                     const int s = git % STAGES;
                     ok = mbar_wait(&full[s], (git / STAGES) & 1);
                     if (!ok) break;
+                    if (F16) {
+                        // item = (row, half of the 16 k): two 16-byte chunks of FP32 (64-byte rows, 64-byte swizzle) become one
+                        // 16-byte chunk of h1 and one of h2 (32-byte rows, 32-byte swizzle)
+                        constexpr int NI = (TC_BM + BROWS) * 2;
+                        static_assert(NI % (32 * TC_CONV_WARPS) == 0, "items per converter thread");
+                        const uint8_t* stb = smem + s * STAGE_BYTES;
+#pragma unroll
+                        for (int jj = 0; jj < NI / (32 * TC_CONV_WARPS); jj++) {
+                            int item = jj * (32 * TC_CONV_WARPS) + cw * 32 + lane;
+                            const bool isb = item >= 2 * TC_BM;
+                            if (isb) item -= 2 * TC_BM;
+                            const int r = item >> 1, half = item & 1;
+                            const uint8_t* srow = stb + (isb ? A_BYTES : 0) + r * 64;
+                            const int sw = (r >> 1) & 3;
+                            const float4 x0 = *(const float4*)(srow + (((2 * half) ^ sw) << 4));
+                            const float4 x1 = *(const float4*)(srow + (((2 * half + 1) ^ sw) << 4));
+                            const float sc = isb ? scale_b : scale_a;
+                            const float v[8] = {x0.x * sc, x0.y * sc, x0.z * sc, x0.w * sc, x1.x * sc, x1.y * sc, x1.z * sc, x1.w * sc};
+                            __half2 h1[4], h2[4];
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                h1[e] = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
+                                const float2 back = __half22float2(h1[e]);
+                                h2[e] = __floats2half2_rn(v[2 * e] - back.x, v[2 * e + 1] - back.y);
+                            }
+                            uint8_t* d1 = (uint8_t*)stb + HI_BYTES + (isb ? HA_BYTES : 0) + r * 32 + ((half ^ ((r >> 2) & 1)) << 4);
+                            uint8_t* d2 = d1 + HA_BYTES + HB_BYTES;
+                            uint4 u1, u2;
+                            u1.x = *(const uint32_t*)&h1[0]; u1.y = *(const uint32_t*)&h1[1]; u1.z = *(const uint32_t*)&h1[2]; u1.w = *(const uint32_t*)&h1[3];
+                            u2.x = *(const uint32_t*)&h2[0]; u2.y = *(const uint32_t*)&h2[1]; u2.z = *(const uint32_t*)&h2[2]; u2.w = *(const uint32_t*)&h2[3];
+                            *(uint4*)d1 = u1;
+                            *(uint4*)d2 = u2;
+                        }
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(cb_base + (uint32_t)(s * 8));
+                        continue;
+                    }
                     const float4* src = (const float4*)(smem + s * STAGE_BYTES);
                     float4* dst = (float4*)(smem + s * STAGE_BYTES + HI_BYTES);
 #pragma unroll
@@ -584,6 +659,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
 #pragma unroll
                     for (int j = 0; j < 32; j++) accr[g * 32 + j] += __uint_as_float(r[j]);
                 }
+            }
+            if (F16) {
+                // undo the operands' power-of-two scales (two exact multiplications: the product of both may leave the float range)
+                const float ua = tc_pow2(-tc_f16_shift(amax[0])), ub = tc_pow2(-tc_f16_shift(amax[1]));
+#pragma unroll
+                for (int j = 0; j < COLS_PER_WARP; j++) accr[j] = accr[j] * ua * ub;
             }
             if (CONV && store_warps) {
                 // plain tile: write this warp's rows into its quarter's half of the staging buffer and hand it to the store warp
@@ -772,6 +853,26 @@ static __global__ void __launch_bounds__(256) tc_splitk_fixup_kernel(const float
     }
 }
 
+// max |x| of two operands (blockIdx.y selects), as float bits through an integer atomicMax (order-free); out zeroed before
+static __global__ void __launch_bounds__(256) tc_amax_kernel(const float* __restrict__ a, size_t na4, const float* __restrict__ b, size_t nb4,
+                                                             unsigned* __restrict__ out) {
+    const float4* x = (const float4*)(blockIdx.y ? b : a);
+    const size_t n4 = blockIdx.y ? nb4 : na4;
+    float m = 0.f;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        const float4 v = x[i];
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    }
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    __shared__ float red[8];
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; w++) m = fmaxf(m, red[w]);
+        atomicMax(out + blockIdx.y, __float_as_uint(m));
+    }
+}
+
 // --------------------------------------------------------------------------- operand preparation kernels
 // lo[i] = x[i] - tf32_trunc(x[i]);  8 bytes per element
 static __global__ void __launch_bounds__(256) split_lo_kernel(const float* __restrict__ x, float* __restrict__ lo, size_t n4) {
@@ -877,7 +978,7 @@ static bool tc_make_map(CUtensorMap* m, const float* base, const TcOperand& op, 
 
 static inline bool tc_aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
 
-template <int BN, int BK, int NTERMS, int STAGES, int CTAS = 1, bool AMN = false, bool BMN = false>
+template <int BN, int BK, int NTERMS, int STAGES, int CTAS = 1, bool AMN = false, bool BMN = false, bool F16 = false>
 static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
     CUtensorMap mAh, mAl, mBh, mBl;
     constexpr int BROWS = BN / CTAS;
@@ -890,7 +991,7 @@ static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
     constexpr size_t ring_bytes = (size_t)STAGES * STAGE_BYTES;
     constexpr size_t smem = ring_bytes + stg_bytes + 1024 + 512;      // ring, output staging, alignment slack, barriers
     static_assert(smem <= 232448, "shared memory of one CTA");
-    auto kern = gemm_tc_kernel<BN, BK, NTERMS, STAGES, CTAS, AMN, BMN>;
+    auto kern = gemm_tc_kernel<BN, BK, NTERMS, STAGES, CTAS, AMN, BMN, F16>;
     constexpr int THREADS = CONV ? TC_CONV_THREADS : TC_THREADS;
     static bool attr_set = false;
     if (!attr_set) {
@@ -951,12 +1052,12 @@ static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
         cfg.attrs = at; cfg.numAttrs = 1;
         if (cudaLaunchKernelEx(&cfg, kern, mAh, mAl, mBh, mBl, p.C, p.ldc, p.c_batch_stride, p.M, p.N, p.K, p.acc, p.causal,
                                p.A.c2_base, p.A.c2_step, p.B.c2_base, p.B.c2_step, swap_mask, split_full, split_s, partial, p.epi,
-                               nbatch, total_items, snake, tri, store_warps, c->d_status) != cudaSuccess) return false;
+                               nbatch, total_items, snake, tri, store_warps, p.amax, c->d_status) != cudaSuccess) return false;
     } else {
         kern<<<grid, THREADS, smem, (cudaStream_t)c->pub.stream>>>(mAh, mAl, mBh, mBl, p.C, p.ldc, p.c_batch_stride, p.M, p.N, p.K, p.acc,
                                                                      p.causal, p.A.c2_base, p.A.c2_step, p.B.c2_base, p.B.c2_step,
                                                                      swap_mask, split_full, split_s, partial, p.epi,
-                                                                     nbatch, total_items, snake, tri, store_warps, c->d_status);
+                                                                     nbatch, total_items, snake, tri, store_warps, p.amax, c->d_status);
     }
     c->launches++;
     if (split_s > 1) {
@@ -976,6 +1077,7 @@ static bool tc_launch(sb_ctx_t* c, const TcProblem& p, int nterms) {
     if (c->gemm_pair && raw) {
         const int lay = (p.A.mn ? 1 : 0) | (p.B.mn ? 2 : 0);
         if (p.N > 128) {
+            if (nterms == 3 && p.amax && lay == 0) return tc_launch_t<256, 16, 3, 5, 2, false, false, true>(c, p);
             if (nterms == 3) switch (lay) {
                 case 0: return tc_launch_t<256, 16, 3, 5, 2, false, false>(c, p);
                 case 1: return tc_launch_t<256, 16, 3, 5, 2, true, false>(c, p);

@@ -38,7 +38,8 @@ enum {
     SB_GEMM_FP32X3 = 0,  /* tcgen05 kind::tf32, hi/lo split, 3 MMAs per k-block: FP32-level accuracy (default) */
     SB_GEMM_TF32   = 1,  /* tcgen05 kind::tf32, one MMA per k-block */
     SB_GEMM_BF16   = 2,  /* tcgen05 kind::f16 on BF16 copies (use_bf16) */
-    SB_GEMM_SIMT   = 3   /* FP32 FMA on CUDA cores */
+    SB_GEMM_SIMT   = 3,  /* FP32 FMA on CUDA cores */
+    SB_GEMM_FP16X3 = 4   /* like FP32X3, but K-major products split into scaled FP16 parts (kind::f16): same accuracy, half the MMA cycles */
 };
 
 typedef struct { size_t q, k, v, o, gate, up, down, in_norm, post_norm; } sb_layer_off_t;
@@ -53,6 +54,7 @@ typedef struct sb_ctx {
     int status;                      /* last host-side status */
     int* d_status;                   /* device status word (bounds checks, bounded waits) */
     int gemm_mode;                   /* SB_GEMM_* (use_bf16 in pub overrides to BF16) */
+    float* d_amax;                   /* two floats: max |A|, max |B| of the GEMM being launched (FP16 split) */
     int attn_fused;                  /* 1: P and dS of the attention backward come out of the score products' epilogues */
     int gemm_tail_split;             /* 1: tiles of the last partial wave are cut into k pieces */
     int gemm_pair;                   /* 1: plain GEMMs run on CTA pairs (cta_group::2), 0: one CTA per tile */

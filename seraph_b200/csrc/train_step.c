@@ -739,6 +739,7 @@ void cuda_train_free(cuda_train_context_t* ctx) {
         for (int i = 0; i < 5; i++) cudaEventDestroy((cudaEvent_t)c->side_ev[i]);
     }
     if (c->rope_tab) cudaFree(c->rope_tab);
+    if (c->d_amax) cudaFree(c->d_amax);
     if (c->d_status) cudaFree(c->d_status);
     if (c->d_loss) cudaFree(c->d_loss);
     if (c->h_pinned) cudaFreeHost(c->h_pinned);

@@ -142,21 +142,21 @@ static bool at_eligible(sb_ctx_t* c, int T, int Hq, int Hkv, int hd) {
 // K-major view of [token, heads*hd] rows: rows = tokens of the sequence, k = the head's hd columns, slot = head
 static TcOperand op_tokens(const float* x, int tok0, int S, int row_pitch, int nheads, int hd, int slot_base, int slot_step) {
     TcOperand o;
-    o.hi = x + (size_t)tok0 * row_pitch; o.lo = nullptr;
+    o.hi = x + (size_t)tok0 * row_pitch; o.lo = nullptr; o.h1 = o.h2 = nullptr;
     o.mn = 0; o.rows = S; o.pitch = row_pitch; o.c2_dim = nheads; o.c2_stride = hd; o.c2_base = slot_base; o.c2_step = slot_step;
     return o;
 }
 // MN-major view of the same rows: k = tokens of the sequence, rows = the head's hd columns (contiguous), slot = head
 static TcOperand op_tokens_mn(const float* x, int tok0, int row_pitch, int nheads, int hd, int slot_base, int slot_step) {
     TcOperand o;
-    o.hi = x + (size_t)tok0 * row_pitch; o.lo = nullptr;
+    o.hi = x + (size_t)tok0 * row_pitch; o.lo = nullptr; o.h1 = o.h2 = nullptr;
     o.mn = 1; o.rows = hd; o.pitch = row_pitch; o.c2_dim = nheads; o.c2_stride = hd; o.c2_base = slot_base; o.c2_step = slot_step;
     return o;
 }
 // score scratch [head][query][key]: K-major = rows are queries, k runs over keys; mn = rows are keys, k runs over queries
 static TcOperand op_scratch(const float* x, int S, int Sp, int nb, int mn) {
     TcOperand o;
-    o.hi = x; o.lo = nullptr; o.mn = mn; o.rows = S; o.pitch = Sp; o.c2_dim = nb; o.c2_stride = (long)Sp * Sp; o.c2_base = 0; o.c2_step = 1;
+    o.hi = x; o.lo = nullptr; o.h1 = o.h2 = nullptr; o.mn = mn; o.rows = S; o.pitch = Sp; o.c2_dim = nb; o.c2_stride = (long)Sp * Sp; o.c2_base = 0; o.c2_step = 1;
     return o;
 }
 
@@ -164,6 +164,7 @@ static bool at_gemm(sb_ctx_t* c, const TcOperand& A, const TcOperand& B, float* 
                     int acc, int nb, int causal, const TcEpi* epi = nullptr) {
     TcProblem p; p.A = A; p.B = B; p.C = C; p.ldc = ldc; p.c_batch_stride = cbs; p.M = M; p.N = N; p.K = K; p.acc = acc; p.nbatch = nb; p.causal = causal;
     if (epi) p.epi = *epi; else memset(&p.epi, 0, sizeof p.epi);
+    p.amax = nullptr;
     return tc_launch(c, p, 3);
 }
 // per-(token, head) vector (lse or D, laid out [token][Hq]) as seen by a launch over heads head0, head0+step, ...

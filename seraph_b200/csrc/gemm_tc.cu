@@ -15,7 +15,7 @@
 // Bring one operand to K-major [rows, K].  `kmajor`: the caller's array already is [rows, K] row-major.
 static bool prep_operand(sb_ctx_t* c, const float* src, int rows, int K, bool kmajor, bool want_lo, int slot, TcOperand* op) {
     cudaStream_t s = (cudaStream_t)c->pub.stream;
-    op->mn = 0; op->rows = rows; op->c2_dim = 1; op->c2_stride = 0; op->c2_base = 0; op->c2_step = 0; op->lo = nullptr;
+    op->mn = 0; op->h1 = op->h2 = nullptr; op->rows = rows; op->c2_dim = 1; op->c2_stride = 0; op->c2_base = 0; op->c2_step = 0; op->lo = nullptr;
     if (kmajor) {
         op->hi = src; op->pitch = K;
         if (want_lo) {
@@ -61,15 +61,22 @@ extern "C" int sb_gemm_tc(sb_ctx_t* c, const float* A, const float* B, float* C,
         p.B.hi = B; p.B.lo = nullptr; p.B.rows = N; p.B.mn = b_kmajor ? 0 : 1; p.B.pitch = b_kmajor ? K : N;
         p.A.c2_dim = p.B.c2_dim = 1; p.A.c2_stride = p.B.c2_stride = 0; p.A.c2_base = p.B.c2_base = 0; p.A.c2_step = p.B.c2_step = 0;
         int tg = sb_tick_begin(c, SB_CLS_GEMM);
-        if (mode == SB_GEMM_FP16X3 && a_kmajor && b_kmajor && N > 128) {
-            // FP16 split: the operands' largest magnitudes first (one launch over both)
+        p.A.h1 = p.A.h2 = p.B.h1 = p.B.h2 = nullptr;
+        if (mode == SB_GEMM_FP16X3 && N > 128 && (a_kmajor ? (K & 7) == 0 : (M & 7) == 0) && (b_kmajor ? (K & 7) == 0 : (N & 7) == 0)) {
+            // FP16 split: the operands' largest magnitudes, then their two FP16 parts (one launch each over both operands)
             if (!c->d_amax && sb_check(c, cudaMalloc(&c->d_amax, 2 * sizeof(float)), "amax alloc")) return 1;
+            const size_t na = (size_t)M * K, nb = (size_t)N * K;
+            __half* ha = (__half*)sb_gemm_stage(c, 0, na * 2 * sizeof(__half));
+            __half* hb = (__half*)sb_gemm_stage(c, 1, nb * 2 * sizeof(__half));
+            if (!ha || !hb) return 1;
             cudaStream_t st = (cudaStream_t)c->pub.stream;
             cudaMemsetAsync(c->d_amax, 0, 2 * sizeof(float), st);
-            tc_amax_kernel<<<dim3(tc_ew_blocks(c, ((size_t)(M > N ? M : N) * K) / 4), 2), 256, 0, st>>>(A, (size_t)M * K / 4, B, (size_t)N * K / 4,
-                                                                                                         (unsigned*)c->d_amax);
-            c->launches++;
+            const dim3 pg(tc_ew_blocks(c, (na > nb ? na : nb) / 4), 2);
+            tc_amax_kernel<<<pg, 256, 0, st>>>(A, na / 4, B, nb / 4, (unsigned*)c->d_amax);
+            tc_split_f16_kernel<<<pg, 256, 0, st>>>(A, na / 4, ha, ha + na, B, nb / 4, hb, hb + nb, c->d_amax);
+            c->launches += 2;
             p.amax = c->d_amax;
+            p.A.h1 = ha; p.A.h2 = ha + na; p.B.h1 = hb; p.B.h2 = hb + nb;
         }
         bool ok = tc_launch(c, p, x3 ? 3 : 1);
         sb_tick_end(c, tg, 2.0 * M * N * K, 4.0 * ((double)M * K + (double)N * K + (double)M * N * (acc ? 2 : 1)));

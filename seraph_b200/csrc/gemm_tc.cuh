@@ -65,6 +65,7 @@ struct TcOperand {
     int rows;                            // M or N
     long pitch;                          // floats between rows (mn: between k-rows)
     int mn;                              // 1: the array is [K, rows], rows contiguous (CTA-pair kernel only)
+    const void* h1; const void* h2;      // prepared FP16 parts (same layout as hi), or NULL
     int c2_dim; long c2_stride;          // third tensor-map dimension (floats); c2_dim = 1 for a plain matrix
     int c2_base, c2_step;                // slot of batch b = c2_base + b*c2_step
 };
@@ -156,15 +157,17 @@ template <bool PAIRBAR>
 __device__ __forceinline__ void tc_load_box(void* dst, const CUtensorMap* map, uint64_t* bar, uint32_t bar_cluster, int c0, int c1, int c2) {
     if (PAIRBAR) tma_load_3d_pair(dst, map, bar_cluster, c0, c1, c2); else tma_load_3d(dst, map, bar, c0, c1, c2);
 }
-// one operand tile of a stage: K-major = one box {BK, rows}; MN-major = ROWS/32 boxes {32 rows, BK} of BK*128 bytes each
-template <bool PAIRBAR, bool MN, int BK, int ROWS>
+// one operand tile of a stage: K-major = one box {BK, rows}; MN-major = boxes {128 bytes of rows, BK} of BK*128 bytes each
+// (32 rows of FP32, 64 rows of FP16); BK = k elements per stage
+template <bool PAIRBAR, bool MN, int BK, int ROWS, int ELT = 4>
 __device__ __forceinline__ void tc_load_operand(uint8_t* dst, const CUtensorMap* map, uint64_t* bar, uint32_t bar_cluster,
                                                 int kb, int row0, int c2, bool swapped) {
     if (MN) {
         // {row, k, slot}, or {row, slot, k} when the slot stride is smaller than the k-row pitch
+        constexpr int RPB = 128 / ELT;
 #pragma unroll
-        for (int j = 0; j < ROWS / 32; j++)
-            tc_load_box<PAIRBAR>(dst + j * BK * 128, map, bar, bar_cluster, row0 + 32 * j, swapped ? c2 : kb * BK, swapped ? kb * BK : c2);
+        for (int j = 0; j < ROWS / RPB; j++)
+            tc_load_box<PAIRBAR>(dst + j * BK * 128, map, bar, bar_cluster, row0 + RPB * j, swapped ? c2 : kb * BK, swapped ? kb * BK : c2);
     } else {
         // a map whose slot stride is smaller than its row pitch is encoded as {k, slot, row}
         tc_load_box<PAIRBAR>(dst, map, bar, bar_cluster, kb * BK, swapped ? c2 : row0, swapped ? row0 : c2);
@@ -227,6 +230,18 @@ __device__ __forceinline__ uint64_t make_mnmajor_desc(uint32_t smem_addr) {
     d |= (uint64_t)((512 >> 4) & 0x3fff) << 32;                  // stride byte offset: next 4 k-rows
     d |= (uint64_t)1 << 46;
     d |= (uint64_t)1 << 61;                                      // 128-byte swizzle, 32-byte base
+    return d;
+}
+// shared-memory matrix descriptor, MN-major 16-bit operand: atoms of 8 k-rows x 128 bytes (64 halfs of M or N) in the
+// 128-byte swizzle (TMA: SWIZZLE_128B); the next 8 k-rows follow 1024 bytes later, the atoms of the next 64 rows BKE*128 bytes later
+template <int BKE>
+__device__ __forceinline__ uint64_t make_mn16_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
+    d |= (uint64_t)(((BKE * 128) >> 4) & 0x3fff) << 16;          // leading byte offset: next 64 rows
+    d |= (uint64_t)((1024 >> 4) & 0x3fff) << 32;                 // stride byte offset: next 8 k-rows
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;                                      // 128-byte swizzle
     return d;
 }
 // lo part of the hi/lo split: x minus the 19 leading bits the tensor core reads, plus half a TF32 ulp
@@ -322,7 +337,10 @@ __device__ __forceinline__ int tc_item(int k, int cid, int G, int snake) { retur
 // tc_amax_kernel before the launch), h1 = fp16(x'), h2 = fp16(x' - h1): 22+ significant bits like the TF32 split, but the
 // three MMAs per k block are kind::f16 with K = 16, half the tensor-core cycles.  The converter warps write the two
 // 16-bit tiles (32-byte rows, 32-byte swizzle) from the landed FP32 stage; the epilogue undoes the scales.
-template <int BN, int BK, int NTERMS, int STAGES, int CTAS, bool AMN, bool BMN, bool F16 = false>
+// PREP (with F16): the two FP16 parts of both operands were written to memory beforehand (tc_split_f16_kernel, same
+// layouts as the FP32 arrays) and TMA brings them in directly, 32 k elements per stage; no warp converts anything, the
+// tensor pipe is the only consumer of the stages.  Either operand may be K-major or MN-major.
+template <int BN, int BK, int NTERMS, int STAGES, int CTAS, bool AMN, bool BMN, bool F16 = false, bool PREP = false>
 __global__ void __launch_bounds__((CTAS == 2 && NTERMS == 3) ? TC_CONV_THREADS : TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
@@ -337,13 +355,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
     constexpr int HI_BYTES = A_BYTES + B_BYTES;
     constexpr int STAGE_BYTES = (NTERMS == 3 ? 2 : 1) * HI_BYTES;
     constexpr bool CONV = (CTAS == 2 && NTERMS == 3);            // lo parts made in the kernel
-    static_assert(!F16 || (CONV && !AMN && !BMN && BK == 16), "FP16 split: FP32-accurate pair kernel, K-major operands");
+    static_assert(!F16 || (CONV && BK == 16 && (PREP || (!AMN && !BMN))), "FP16 split: FP32-accurate pair kernel; converted in the kernel: K-major operands");
+    static_assert(F16 || !PREP, "prepared parts: FP16 split only");
+    constexpr bool CONVERT = CONV && !PREP;                      // converter warps at work
+    constexpr int BKE = PREP ? 2 * BK : BK;                      // k elements per stage (PREP: 64-byte rows of halfs)
     constexpr int HA_BYTES = TC_BM * BK * 2, HB_BYTES = BROWS * BK * 2;      // 16-bit tiles of the FP16 split
     static_assert(!F16 || 2 * (HA_BYTES + HB_BYTES) == HI_BYTES, "the two 16-bit parts take the place of the lo stage");
     static_assert(CTAS == 2 || (!AMN && !BMN), "MN-major operands: CTA-pair kernel only");
     static_assert(BROWS % 32 == 0, "an MN-major tile is made of boxes of 32 rows");
     constexpr uint32_t TMEM_COLS = 2 * BN;                       // two accumulator buffers
-    constexpr int KB_PER_CHUNK = (F16 ? 2 : 1) * TC_CHUNK_K / BK;     // twelve MMAs per accumulation chunk either way
+    constexpr int KB_PER_CHUNK = (F16 ? 2 : 1) * TC_CHUNK_K / BKE;    // twelve MMAs per accumulation chunk either way
     constexpr int COLS_PER_WARP = BN / (TC_EPI_WARPS / 4);       // 128 or 64 register accumulators per epilogue thread
     constexpr int SLD = BN + 4;                                  // padded row pitch of the staging buffer (floats)
     extern __shared__ uint8_t smem_raw[];
@@ -402,14 +423,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
             for (int k = 0; k < rounds && ok; k++) {
                 const int item = tc_item(k, cid, G, snake);
                 TcWork w;
-                if (item >= total_items || !tc_work<BN, BK, CTAS>(item, (int)rank, M, N, K, causal, nbatch, split_full, split_s, tri, w)) continue;
+                if (item >= total_items || !tc_work<BN, BKE, CTAS>(item, (int)rank, M, N, K, causal, nbatch, split_full, split_s, tri, w)) continue;
                 const int a_c2 = a_c2_base + w.batch * a_c2_step, b_c2 = b_c2_base + w.batch * b_c2_step;
                 for (int it = 0; it < w.num_kb && ok; it++, git++) {
                     const int s = git % STAGES, kb = w.kb_begin + it;
                     ok = mbar_wait(&empty[s], ((git / STAGES) & 1) ^ 1);
                     if (!ok) break;
                     uint8_t* st = smem + s * STAGE_BYTES;
-                    if (CONV) {
+                    if (PREP) {
+                        // four 16-bit tiles per CTA (h1 A, h1 B, h2 A, h2 B), the pair's bytes all land on the leader's barrier
+                        if (leader) mbar_expect_tx(&full[s], STAGE_BYTES * CTAS);
+                        const uint32_t fb = mapa_u32(smem_u32(&full[s]), 0);
+                        tc_load_operand<true, AMN, BKE, TC_BM, 2>(st, &tmAh, nullptr, fb, kb, w.m0, a_c2, swa);
+                        tc_load_operand<true, BMN, BKE, BROWS, 2>(st + A_BYTES, &tmBh, nullptr, fb, kb, w.nb0, b_c2, swb);
+                        tc_load_operand<true, AMN, BKE, TC_BM, 2>(st + HI_BYTES, &tmAl, nullptr, fb, kb, w.m0, a_c2, swa);
+                        tc_load_operand<true, BMN, BKE, BROWS, 2>(st + HI_BYTES + A_BYTES, &tmBl, nullptr, fb, kb, w.nb0, b_c2, swb);
+                    } else if (CONV) {
                         // each CTA's hi tiles land on its own barrier; its converter warps take it from there
                         mbar_expect_tx(&full[s], HI_BYTES);
                         tc_load_operand<false, AMN, BK, TC_BM>(st, &tmAh, &full[s], 0, kb, w.m0, a_c2, swa);
@@ -443,7 +472,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
             for (int k = 0; k < rounds && ok; k++) {
                 const int item = tc_item(k, cid, G, snake);
                 TcWork w;
-                if (item >= total_items || !tc_work<BN, BK, CTAS>(item, (int)rank, M, N, K, causal, nbatch, split_full, split_s, tri, w)) continue;
+                if (item >= total_items || !tc_work<BN, BKE, CTAS>(item, (int)rank, M, N, K, causal, nbatch, split_full, split_s, tri, w)) continue;
                 int it = 0;
                 const int num_chunks = (w.num_kb + KB_PER_CHUNK - 1) / KB_PER_CHUNK;
                 for (int ch = 0; ch < num_chunks && ok; ch++, gch++) {
@@ -456,10 +485,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
                     bool first = true;
                     for (; it < it_end && ok; it++, git++) {
                         const int s = git % STAGES;
-                        ok = mbar_wait(CONV ? &conv[s] : &full[s], (git / STAGES) & 1);
+                        ok = mbar_wait(CONVERT ? &conv[s] : &full[s], (git / STAGES) & 1);
                         if (!ok) break;
                         tc_fence_after();
                         const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+                        if (PREP) {
+                            // stage = h1 A, h1 B, h2 A, h2 B (the FP32 tiles' sizes and places); two K = 16 MMAs per term
+                            const uint64_t a1 = AMN ? make_mn16_desc<BKE>(sa) : make_kmajor_desc<SWZ>(sa);
+                            const uint64_t b1 = BMN ? make_mn16_desc<BKE>(sa + A_BYTES) : make_kmajor_desc<SWZ>(sa + A_BYTES);
+                            const uint64_t a2 = AMN ? make_mn16_desc<BKE>(sa + HI_BYTES) : make_kmajor_desc<SWZ>(sa + HI_BYTES);
+                            const uint64_t b2 = BMN ? make_mn16_desc<BKE>(sa + HI_BYTES + A_BYTES) : make_kmajor_desc<SWZ>(sa + HI_BYTES + A_BYTES);
+#pragma unroll
+                            for (int kk = 0; kk < BKE / 16; kk++) {
+                                // 16 halfs of k, in 16-byte units: 32 bytes along a K-major row, 16 k-rows of 128 bytes in an MN-major tile
+                                const uint64_t adva = (uint64_t)(AMN ? kk * 128 : kk * 2), advb = (uint64_t)(BMN ? kk * 128 : kk * 2);
+                                tc_mma_f16_pair(tmem_d, a1 + adva, b1 + advb, idesc, first ? 0u : 1u);
+                                tc_mma_f16_pair(tmem_d, a2 + adva, b1 + advb, idesc, 1);
+                                tc_mma_f16_pair(tmem_d, a1 + adva, b2 + advb, idesc, 1);
+                                first = false;
+                            }
+                            tc_commit_pair(&empty[s]);
+                            continue;
+                        }
                         if (F16) {
                             // 16-bit tiles after the FP32 landing area: h1 A, h1 B, h2 A, h2 B; one K = 16 MMA per term
                             const uint64_t a1 = make_kmajor_desc<32>(sa + HI_BYTES), b1 = make_kmajor_desc<32>(sa + HI_BYTES + HA_BYTES);
@@ -504,7 +551,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
         }
     } else {
         // ---------------- converter (CTA-pair FP32-accurate kernel): lo = x - trunc_tf32(x) beside each landed hi stage ----------------
-        if (CONV && cw >= 0) {
+        if (CONVERT && cw >= 0) {
             constexpr int N4 = HI_BYTES / 16;
             constexpr int PER = N4 / (32 * TC_CONV_WARPS);
             constexpr int UNR = PER % 8 == 0 ? 8 : (PER % 6 == 0 ? 6 : 4);
@@ -515,7 +562,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
             for (int k = 0; k < rounds && ok; k++) {
                 const int item = tc_item(k, cid, G, snake);
                 TcWork w;
-                if (item >= total_items || !tc_work<BN, BK, CTAS>(item, (int)rank, M, N, K, causal, nbatch, split_full, split_s, tri, w)) continue;
+                if (item >= total_items || !tc_work<BN, BKE, CTAS>(item, (int)rank, M, N, K, causal, nbatch, split_full, split_s, tri, w)) continue;
                 for (int it = 0; it < w.num_kb && ok; it++, git++) {
                     const int s = git % STAGES;
                     ok = mbar_wait(&full[s], (git / STAGES) & 1);
@@ -588,7 +635,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
             for (int k = 0; k < rounds && ok; k++) {
                 const int item = tc_item(k, cid, G, snake);
                 TcWork w;
-                if (item >= total_items || !tc_work<BN, BK, CTAS>(item, (int)rank, M, N, K, causal, nbatch, split_full, split_s, tri, w)) continue;
+                if (item >= total_items || !tc_work<BN, BKE, CTAS>(item, (int)rank, M, N, K, causal, nbatch, split_full, split_s, tri, w)) continue;
                 float* C = Cbase + (size_t)w.batch * c_batch_stride;
                 float* dst = w.split ? partial + ((size_t)w.slot * CTAS + rank) * (size_t)(TC_BM * BN) : C + (size_t)w.m0 * ldc + w.n0;
                 const long ld = w.split ? (long)BN : ldc;
@@ -632,7 +679,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
         for (int k = 0; k < rounds && ok; k++) {
             const int item = tc_item(k, cid, G, snake);
             TcWork w;
-            if (item >= total_items || !tc_work<BN, BK, CTAS>(item, (int)rank, M, N, K, causal, nbatch, split_full, split_s, tri, w)) continue;
+            if (item >= total_items || !tc_work<BN, BKE, CTAS>(item, (int)rank, M, N, K, causal, nbatch, split_full, split_s, tri, w)) continue;
             const int num_chunks = (w.num_kb + KB_PER_CHUNK - 1) / KB_PER_CHUNK;
             float accr[COLS_PER_WARP];
 #pragma unroll
@@ -873,6 +920,26 @@ static __global__ void __launch_bounds__(256) tc_amax_kernel(const float* __rest
     }
 }
 
+// FP16 parts of two operands (blockIdx.y selects): x' = x * 2^shift(amax), h1 = fp16(x'), h2 = fp16(x' - h1); layout kept
+static __global__ void __launch_bounds__(256) tc_split_f16_kernel(const float* __restrict__ a, size_t na4, __half* __restrict__ a1, __half* __restrict__ a2,
+                                                                  const float* __restrict__ b, size_t nb4, __half* __restrict__ b1, __half* __restrict__ b2,
+                                                                  const float* __restrict__ amax) {
+    const float4* x = (const float4*)(blockIdx.y ? b : a);
+    const size_t n4 = blockIdx.y ? nb4 : na4;
+    uint2* o1 = (uint2*)(blockIdx.y ? b1 : a1); uint2* o2 = (uint2*)(blockIdx.y ? b2 : a2);
+    const float sc = tc_pow2(tc_f16_shift(amax[blockIdx.y]));
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        const float4 v = x[i];
+        const float p0 = v.x * sc, p1 = v.y * sc, p2 = v.z * sc, p3 = v.w * sc;
+        const __half2 ha = __floats2half2_rn(p0, p1), hb = __floats2half2_rn(p2, p3);
+        const float2 fa = __half22float2(ha), fb = __half22float2(hb);
+        const __half2 la = __floats2half2_rn(p0 - fa.x, p1 - fa.y), lb = __floats2half2_rn(p2 - fb.x, p3 - fb.y);
+        uint2 u1, u2;
+        u1.x = *(const uint32_t*)&ha; u1.y = *(const uint32_t*)&hb; u2.x = *(const uint32_t*)&la; u2.y = *(const uint32_t*)&lb;
+        o1[i] = u1; o2[i] = u2;
+    }
+}
+
 // --------------------------------------------------------------------------- operand preparation kernels
 // lo[i] = x[i] - tf32_trunc(x[i]);  8 bytes per element
 static __global__ void __launch_bounds__(256) split_lo_kernel(const float* __restrict__ x, float* __restrict__ lo, size_t n4) {
@@ -925,15 +992,18 @@ static inline bool tc_swapped(const TcOperand& op) { return op.c2_dim > 1 && op.
 // Encoding a tensor map costs a few microseconds on the host and a training step re-issues the same
 // (pointer, shape) combinations every layer and every step, so encoded maps are kept in a small
 // direct-mapped cache keyed by everything that goes into the encoding.
-struct TcMapKey { const float* base; long pitch, c2_stride; int K, rows, c2_dim, BK, box_rows, mn; };
+struct TcMapKey { const void* base; long pitch, c2_stride; int K, rows, c2_dim, BK, box_rows, mn, elt; };
 struct TcMapEntry { TcMapKey key; CUtensorMap map; bool valid; };
 #define TC_MAP_CACHE 8192
 static TcMapEntry* g_tc_map_cache = nullptr;
 
 // 3-D FP32 tensor {K, rows, slots} (or {K, slots, rows}); box = BK x box_rows x 1; reads beyond the extents give zero
-static bool tc_make_map(CUtensorMap* m, const float* base, const TcOperand& op, int K, int BK, int box_rows) {
+// elt = 2: the same for an FP16 array of the same shape (BK halfs per box; MN-major boxes are 64 rows, plain 128-byte swizzle)
+static bool tc_make_map(CUtensorMap* m, const void* base, const TcOperand& op, int K, int BK, int box_rows, int elt = 4) {
     TcMapKey key;
     memset(&key, 0, sizeof key);
+    key.elt = elt;
+    const CUtensorMapDataType dt = elt == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
     key.base = base; key.pitch = op.pitch; key.c2_stride = op.c2_dim > 1 ? op.c2_stride : 0; key.K = K; key.rows = op.rows;
     key.c2_dim = op.c2_dim > 1 ? op.c2_dim : 1; key.BK = BK; key.box_rows = box_rows; key.mn = op.mn;
     if (!g_tc_map_cache) g_tc_map_cache = (TcMapEntry*)calloc(TC_MAP_CACHE, sizeof(TcMapEntry));
@@ -949,27 +1019,28 @@ static bool tc_make_map(CUtensorMap* m, const float* base, const TcOperand& op, 
         // the array is [K, rows] with rows contiguous: {rows, K, 1}, boxes of 32 floats x BK k-rows, 128-byte swizzle of 32-byte units
         const bool swm = tc_swapped(op);
         const cuuint64_t nsl = (cuuint64_t)(op.c2_dim > 1 ? op.c2_dim : 1);
-        const cuuint64_t krow = (cuuint64_t)op.pitch * sizeof(float);
-        const cuuint64_t sl = op.c2_dim > 1 ? (cuuint64_t)op.c2_stride * sizeof(float) : krow * (cuuint64_t)K;
+        const cuuint64_t krow = (cuuint64_t)op.pitch * elt;
+        const cuuint64_t sl = op.c2_dim > 1 ? (cuuint64_t)op.c2_stride * elt : krow * (cuuint64_t)K;
         cuuint64_t dims[3] = {(cuuint64_t)op.rows, swm ? nsl : (cuuint64_t)K, swm ? (cuuint64_t)K : nsl};
         cuuint64_t strides[2] = {swm ? sl : krow, swm ? krow : sl};
-        cuuint32_t box[3] = {32u, swm ? 1u : (cuuint32_t)BK, swm ? (cuuint32_t)BK : 1u};
+        cuuint32_t box[3] = {(cuuint32_t)(128 / elt), swm ? 1u : (cuuint32_t)BK, swm ? (cuuint32_t)BK : 1u};
         cuuint32_t estr[3] = {1, 1, 1};
-        CUresult r = g_tc_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                 CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        CUresult r = g_tc_encode(m, dt, 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 elt == 2 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return false;
         if (e) { e->key = key; e->map = *m; e->valid = true; }
         return true;
     }
     const bool sw = tc_swapped(op);
     const cuuint64_t nslot = (cuuint64_t)(op.c2_dim > 0 ? op.c2_dim : 1);
-    const cuuint64_t slot_stride = (cuuint64_t)(op.c2_dim > 1 ? op.c2_stride : (long)op.pitch * op.rows) * sizeof(float);
+    const cuuint64_t slot_stride = (cuuint64_t)(op.c2_dim > 1 ? op.c2_stride : (long)op.pitch * op.rows) * elt;
     cuuint64_t dims[3] = {(cuuint64_t)K, sw ? nslot : (cuuint64_t)op.rows, sw ? (cuuint64_t)op.rows : nslot};
-    cuuint64_t strides[2] = {sw ? slot_stride : (cuuint64_t)op.pitch * sizeof(float), sw ? (cuuint64_t)op.pitch * sizeof(float) : slot_stride};
+    cuuint64_t strides[2] = {sw ? slot_stride : (cuuint64_t)op.pitch * elt, sw ? (cuuint64_t)op.pitch * elt : slot_stride};
     cuuint32_t box[3] = {(cuuint32_t)BK, sw ? 1u : (cuuint32_t)box_rows, sw ? (cuuint32_t)box_rows : 1u};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = g_tc_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                             BK * 4 == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    CUresult r = g_tc_encode(m, dt, 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             BK * elt == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return false;
     if (e) { e->key = key; e->map = *m; e->valid = true; }
@@ -978,20 +1049,25 @@ static bool tc_make_map(CUtensorMap* m, const float* base, const TcOperand& op, 
 
 static inline bool tc_aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
 
-template <int BN, int BK, int NTERMS, int STAGES, int CTAS = 1, bool AMN = false, bool BMN = false, bool F16 = false>
+template <int BN, int BK, int NTERMS, int STAGES, int CTAS = 1, bool AMN = false, bool BMN = false, bool F16 = false, bool PREP = false>
 static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
     CUtensorMap mAh, mAl, mBh, mBl;
     constexpr int BROWS = BN / CTAS;
     constexpr bool CONV = (CTAS == 2 && NTERMS == 3);
+    constexpr int BKE = PREP ? 2 * BK : BK;
+    if (PREP) {
+        if (!tc_make_map(&mAh, p.A.h1, p.A, p.K, BKE, TC_BM, 2) || !tc_make_map(&mBh, p.B.h1, p.B, p.K, BKE, BROWS, 2) ||
+            !tc_make_map(&mAl, p.A.h2, p.A, p.K, BKE, TC_BM, 2) || !tc_make_map(&mBl, p.B.h2, p.B, p.K, BKE, BROWS, 2)) return false;
+    } else
     if (!tc_make_map(&mAh, p.A.hi, p.A, p.K, BK, TC_BM) || !tc_make_map(&mBh, p.B.hi, p.B, p.K, BK, BROWS)) return false;
-    if (NTERMS == 3 && !CONV) { if (!tc_make_map(&mAl, p.A.lo, p.A, p.K, BK, TC_BM) || !tc_make_map(&mBl, p.B.lo, p.B, p.K, BK, BROWS)) return false; }
-    else { mAl = mAh; mBl = mBh; }
+    if (!PREP && NTERMS == 3 && !CONV) { if (!tc_make_map(&mAl, p.A.lo, p.A, p.K, BK, TC_BM) || !tc_make_map(&mBl, p.B.lo, p.B, p.K, BK, BROWS)) return false; }
+    else if (!PREP) { mAl = mAh; mBl = mBh; }
     constexpr int STAGE_BYTES = (NTERMS == 3 ? 2 : 1) * (TC_BM + BROWS) * BK * 4;
     constexpr size_t stg_bytes = (size_t)TC_STG_ROWS * (BN + 4) * 4;
     constexpr size_t ring_bytes = (size_t)STAGES * STAGE_BYTES;
     constexpr size_t smem = ring_bytes + stg_bytes + 1024 + 512;      // ring, output staging, alignment slack, barriers
     static_assert(smem <= 232448, "shared memory of one CTA");
-    auto kern = gemm_tc_kernel<BN, BK, NTERMS, STAGES, CTAS, AMN, BMN, F16>;
+    auto kern = gemm_tc_kernel<BN, BK, NTERMS, STAGES, CTAS, AMN, BMN, F16, PREP>;
     constexpr int THREADS = CONV ? TC_CONV_THREADS : TC_THREADS;
     static bool attr_set = false;
     if (!attr_set) {
@@ -1008,15 +1084,15 @@ static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
     float* partial = nullptr;
     if (c->gemm_tail_split && p.nbatch <= 1 && p.causal == TC_CAUSAL_NONE) {
         const int full = tiles / slots * slots, rem = tiles - full;
-        constexpr int KB_PER_CHUNK = TC_CHUNK_K / BK > 0 ? TC_CHUNK_K / BK : 1;
-        const int num_kb = (p.K + BK - 1) / BK;
+        constexpr int KB_PER_CHUNK = TC_CHUNK_K / BKE > 0 ? TC_CHUNK_K / BKE : 1;
+        const int num_kb = (p.K + BKE - 1) / BKE;
         // an item's epilogue costs about as much as 160 floats of k (5.3 us against 0.52 us per 16 floats, measured with a
         // K sweep), the fix-up pass about as much as 256; costs below are in tile times
-        const double ovh = 10.0 * 16 / BK / num_kb, fix = 16.0 * 16 / BK / num_kb;
+        const double ovh = 10.0 * 16 / BKE / num_kb, fix = 16.0 * 16 / BKE / num_kb;
         double best = rem > 0 ? 1.0 + ovh : 0.0;
         for (int s = 2; s <= 8 && rem > 0; s++) {
             const int per = ((num_kb + s - 1) / s + KB_PER_CHUNK - 1) / KB_PER_CHUNK * KB_PER_CHUNK;
-            if (per * (s - 1) >= num_kb || per * BK < 128) continue;      // an empty or very short piece
+            if (per * (s - 1) >= num_kb || per * BKE < 128) continue;     // an empty or very short piece
             const int waves = (rem * s + slots - 1) / slots;
             const double cost = waves * ((double)per / num_kb + ovh) + fix;
             if (cost < best - 0.05) { best = cost; split_s = s; }
@@ -1077,7 +1153,12 @@ static bool tc_launch(sb_ctx_t* c, const TcProblem& p, int nterms) {
     if (c->gemm_pair && raw) {
         const int lay = (p.A.mn ? 1 : 0) | (p.B.mn ? 2 : 0);
         if (p.N > 128) {
-            if (nterms == 3 && p.amax && lay == 0) return tc_launch_t<256, 16, 3, 5, 2, false, false, true>(c, p);
+            if (nterms == 3 && p.amax && p.A.h1 && p.B.h1) switch (lay) {
+                case 0: return tc_launch_t<256, 16, 3, 5, 2, false, false, true, true>(c, p);
+                case 1: return tc_launch_t<256, 16, 3, 5, 2, true, false, true, true>(c, p);
+                case 2: return tc_launch_t<256, 16, 3, 5, 2, false, true, true, true>(c, p);
+                default: return tc_launch_t<256, 16, 3, 5, 2, true, true, true, true>(c, p);
+            }
             if (nterms == 3) switch (lay) {
                 case 0: return tc_launch_t<256, 16, 3, 5, 2, false, false>(c, p);
                 case 1: return tc_launch_t<256, 16, 3, 5, 2, true, false>(c, p);

@@ -336,7 +336,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=list(WORKLOADS)[0],
                     help="a key of WORKLOADS or its index (0 = the benchmark configuration, 1 = profiling slice, 2 = 33M model)")
-    ap.add_argument("--gemm-mode", type=int, default=0, help="0 FP32-accurate tensor cores (default), 1 TF32, 2 BF16, 3 CUDA cores, 4 FP32-accurate with FP16 parts where possible")
+    ap.add_argument("--gemm-mode", type=int, default=4, help="4 FP32-accurate tensor cores, FP16 parts where possible (default), 0 FP32-accurate with TF32 parts, 1 TF32, 2 BF16, 3 CUDA cores")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--short-warmup", action="store_true", help="honour --warmup below 3 (profiler captures only; not a valid bench number)")
     args = ap.parse_args()

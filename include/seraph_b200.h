@@ -155,9 +155,12 @@ void cuda_profiler_set_log(cuda_profiler_t* prof, void* file_ptr);
  * bounded wait ran out, 6 NCCL error, 7 size beyond a fixed capacity.
  * Synchronises the stream, reads the device status word, clears both. */
 int seraph_b200_last_status(cuda_train_context_t* ctx);
-/* GEMM arithmetic: 0 = FP32-accurate on tensor cores (three TF32 passes on a
- * hi/lo split, default), 1 = single-pass TF32, 2 = BF16 (also selected by
- * ctx->use_bf16), 3 = FP32 FMA on CUDA cores. */
+/* GEMM arithmetic.  4 (default) = FP32-accurate on tensor cores: plain products
+ * from two FP16 parts per operand (power-of-two scale per operand, three
+ * kind::f16 passes), attention's products and small or unaligned shapes from
+ * a TF32 hi/lo split (three kind::tf32 passes); 0 = the TF32 split everywhere;
+ * 1 = single-pass TF32; 2 = reduced precision as selected by ctx->use_bf16
+ * (runs the single-pass kernel); 3 = FP32 FMA on CUDA cores. */
 int seraph_b200_set_gemm_mode(cuda_train_context_t* ctx, int mode);
 /* 1 (default): tensor-core GEMMs of plain matrices run on pairs of CTAs that
  * share one 256-row MMA (half of each B tile per CTA); 0: one CTA per tile. */

@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(HERE, "libseraph_b200.so")
 
 STATUS = {0: "ok", 1: "bad argument", 2: "CUDA error", 3: "out of memory", 4: "token id outside vocabulary",
           5: "bounded wait ran out", 6: "NCCL error", 7: "size beyond capacity"}
-GEMM_FP32X3, GEMM_TF32, GEMM_BF16, GEMM_SIMT = 0, 1, 2, 3
+GEMM_FP32X3, GEMM_TF32, GEMM_BF16, GEMM_SIMT, GEMM_FP16X3 = 0, 1, 2, 3, 4      # 4 is the library's default
 
 
 class CudaBuffer(C.Structure):

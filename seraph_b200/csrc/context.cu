@@ -77,7 +77,7 @@ cuda_train_context_t* cuda_train_init(int device_id) {
     cudaStream_t s;
     if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) { free(c); return NULL; }
     c->magic = SB_MAGIC;
-    c->gemm_mode = SB_GEMM_FP32X3;
+    c->gemm_mode = SB_GEMM_FP16X3;
     { const char* e = getenv("SERAPH_B200_GEMM_PAIR"); c->gemm_pair = (e && e[0] == '0') ? 0 : 1; }
     { const char* e = getenv("SERAPH_B200_ATTN_FUSED"); c->attn_fused = (e && e[0] == '1') ? 1 : 0; }
     { const char* e = getenv("SERAPH_B200_GEMM_TAIL_SPLIT"); c->gemm_tail_split = (e && e[0] == '0') ? 0 : 1; }

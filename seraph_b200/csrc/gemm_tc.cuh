@@ -332,11 +332,11 @@ __device__ __forceinline__ int tc_item(int k, int cid, int G, int snake) { retur
 // Barriers, tensor memory and the operand ring live across items, so while the epilogue warps write one tile out
 // (through a small dedicated staging buffer, 32 rows at a time) the producer, the converters and the MMA warp are
 // already working on the next item: only the epilogue itself is left of the per-tile overhead.
-// F16 (FP32-accurate pair kernel, K-major operands): the hi/lo parts are FP16 instead of TF32.  Each operand is scaled
-// by a power of two that brings its largest magnitude to [2^14, 2^15) (amax[0] for A, amax[1] for B, computed by
-// tc_amax_kernel before the launch), h1 = fp16(x'), h2 = fp16(x' - h1): 22+ significant bits like the TF32 split, but the
-// three MMAs per k block are kind::f16 with K = 16, half the tensor-core cycles.  The converter warps write the two
-// 16-bit tiles (32-byte rows, 32-byte swizzle) from the landed FP32 stage; the epilogue undoes the scales.
+// F16 + PREP (FP32-accurate pair kernel): the hi/lo parts are FP16 instead of TF32.  Each operand is scaled by a power
+// of two that brings its largest magnitude to [2^14, 2^15) (amax[0] for A, amax[1] for B, from tc_amax_kernel),
+// h1 = fp16(x'), h2 = fp16(x' - h1): 22+ significant bits like the TF32 split, but the three MMAs per 16 k are kind::f16,
+// half the tensor-core cycles; the epilogue undoes the scales.  Converting in the kernel (tried: converter warps writing
+// the 16-bit tiles from the landed FP32 stage) is bound by the converter warps and no faster than the TF32 split.
 // PREP (with F16): the two FP16 parts of both operands were written to memory beforehand (tc_split_f16_kernel, same
 // layouts as the FP32 arrays) and TMA brings them in directly, 32 k elements per stage; no warp converts anything, the
 // tensor pipe is the only consumer of the stages.  Either operand may be K-major or MN-major.
@@ -355,12 +355,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
     constexpr int HI_BYTES = A_BYTES + B_BYTES;
     constexpr int STAGE_BYTES = (NTERMS == 3 ? 2 : 1) * HI_BYTES;
     constexpr bool CONV = (CTAS == 2 && NTERMS == 3);            // lo parts made in the kernel
-    static_assert(!F16 || (CONV && BK == 16 && (PREP || (!AMN && !BMN))), "FP16 split: FP32-accurate pair kernel; converted in the kernel: K-major operands");
-    static_assert(F16 || !PREP, "prepared parts: FP16 split only");
+    static_assert(F16 == PREP, "the FP16 split works on prepared parts");
+    static_assert(!F16 || (CONV && BK == 16), "FP16 split: FP32-accurate pair kernel");
     constexpr bool CONVERT = CONV && !PREP;                      // converter warps at work
     constexpr int BKE = PREP ? 2 * BK : BK;                      // k elements per stage (PREP: 64-byte rows of halfs)
-    constexpr int HA_BYTES = TC_BM * BK * 2, HB_BYTES = BROWS * BK * 2;      // 16-bit tiles of the FP16 split
-    static_assert(!F16 || 2 * (HA_BYTES + HB_BYTES) == HI_BYTES, "the two 16-bit parts take the place of the lo stage");
     static_assert(CTAS == 2 || (!AMN && !BMN), "MN-major operands: CTA-pair kernel only");
     static_assert(BROWS % 32 == 0, "an MN-major tile is made of boxes of 32 rows");
     constexpr uint32_t TMEM_COLS = 2 * BN;                       // two accumulator buffers
@@ -507,18 +505,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
                             tc_commit_pair(&empty[s]);
                             continue;
                         }
-                        if (F16) {
-                            // 16-bit tiles after the FP32 landing area: h1 A, h1 B, h2 A, h2 B; one K = 16 MMA per term
-                            const uint64_t a1 = make_kmajor_desc<32>(sa + HI_BYTES), b1 = make_kmajor_desc<32>(sa + HI_BYTES + HA_BYTES);
-                            const uint64_t a2 = make_kmajor_desc<32>(sa + HI_BYTES + HA_BYTES + HB_BYTES);
-                            const uint64_t b2 = make_kmajor_desc<32>(sa + HI_BYTES + 2 * HA_BYTES + HB_BYTES);
-                            tc_mma_f16_pair(tmem_d, a1, b1, idesc, first ? 0u : 1u);
-                            tc_mma_f16_pair(tmem_d, a2, b1, idesc, 1);
-                            tc_mma_f16_pair(tmem_d, a1, b2, idesc, 1);
-                            first = false;
-                            tc_commit_pair(&empty[s]);
-                            continue;
-                        }
                         const uint64_t ah = AMN ? make_mnmajor_desc<BK>(sa) : make_kmajor_desc<SWZ>(sa);
                         const uint64_t bh = BMN ? make_mnmajor_desc<BK>(sa + A_BYTES) : make_kmajor_desc<SWZ>(sa + A_BYTES);
                         const uint64_t al = AMN ? make_mnmajor_desc<BK>(sa + HI_BYTES) : make_kmajor_desc<SWZ>(sa + HI_BYTES);
@@ -557,7 +543,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
             constexpr int UNR = PER % 8 == 0 ? 8 : (PER % 6 == 0 ? 6 : 4);
             static_assert(N4 % (32 * TC_CONV_WARPS) == 0 && PER % UNR == 0, "stage size against the converter's unroll");
             const uint32_t cb_base = mapa_u32(smem_u32(&conv[0]), 0);
-            const float scale_a = F16 ? tc_pow2(tc_f16_shift(amax[0])) : 1.f, scale_b = F16 ? tc_pow2(tc_f16_shift(amax[1])) : 1.f;
             uint32_t git = 0;
             for (int k = 0; k < rounds && ok; k++) {
                 const int item = tc_item(k, cid, G, snake);
@@ -567,44 +552,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
                     const int s = git % STAGES;
                     ok = mbar_wait(&full[s], (git / STAGES) & 1);
                     if (!ok) break;
-                    if (F16) {
-                        // item = (row, half of the 16 k): two 16-byte chunks of FP32 (64-byte rows, 64-byte swizzle) become one
-                        // 16-byte chunk of h1 and one of h2 (32-byte rows, 32-byte swizzle)
-                        constexpr int NI = (TC_BM + BROWS) * 2;
-                        static_assert(NI % (32 * TC_CONV_WARPS) == 0, "items per converter thread");
-                        const uint8_t* stb = smem + s * STAGE_BYTES;
-#pragma unroll
-                        for (int jj = 0; jj < NI / (32 * TC_CONV_WARPS); jj++) {
-                            int item = jj * (32 * TC_CONV_WARPS) + cw * 32 + lane;
-                            const bool isb = item >= 2 * TC_BM;
-                            if (isb) item -= 2 * TC_BM;
-                            const int r = item >> 1, half = item & 1;
-                            const uint8_t* srow = stb + (isb ? A_BYTES : 0) + r * 64;
-                            const int sw = (r >> 1) & 3;
-                            const float4 x0 = *(const float4*)(srow + (((2 * half) ^ sw) << 4));
-                            const float4 x1 = *(const float4*)(srow + (((2 * half + 1) ^ sw) << 4));
-                            const float sc = isb ? scale_b : scale_a;
-                            const float v[8] = {x0.x * sc, x0.y * sc, x0.z * sc, x0.w * sc, x1.x * sc, x1.y * sc, x1.z * sc, x1.w * sc};
-                            __half2 h1[4], h2[4];
-#pragma unroll
-                            for (int e = 0; e < 4; e++) {
-                                h1[e] = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
-                                const float2 back = __half22float2(h1[e]);
-                                h2[e] = __floats2half2_rn(v[2 * e] - back.x, v[2 * e + 1] - back.y);
-                            }
-                            uint8_t* d1 = (uint8_t*)stb + HI_BYTES + (isb ? HA_BYTES : 0) + r * 32 + ((half ^ ((r >> 2) & 1)) << 4);
-                            uint8_t* d2 = d1 + HA_BYTES + HB_BYTES;
-                            uint4 u1, u2;
-                            u1.x = *(const uint32_t*)&h1[0]; u1.y = *(const uint32_t*)&h1[1]; u1.z = *(const uint32_t*)&h1[2]; u1.w = *(const uint32_t*)&h1[3];
-                            u2.x = *(const uint32_t*)&h2[0]; u2.y = *(const uint32_t*)&h2[1]; u2.z = *(const uint32_t*)&h2[2]; u2.w = *(const uint32_t*)&h2[3];
-                            *(uint4*)d1 = u1;
-                            *(uint4*)d2 = u2;
-                        }
-                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive_cluster(cb_base + (uint32_t)(s * 8));
-                        continue;
-                    }
                     const float4* src = (const float4*)(smem + s * STAGE_BYTES);
                     float4* dst = (float4*)(smem + s * STAGE_BYTES + HI_BYTES);
 #pragma unroll

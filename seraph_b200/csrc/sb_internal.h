@@ -35,11 +35,12 @@ enum { SB_CLS_GEMM = 0, SB_CLS_GEMM_PREP, SB_CLS_ATTN_FWD, SB_CLS_ATTN_BWD, SB_C
 
 /* GEMM arithmetic modes */
 enum {
-    SB_GEMM_FP32X3 = 0,  /* tcgen05 kind::tf32, hi/lo split, 3 MMAs per k-block: FP32-level accuracy (default) */
+    SB_GEMM_FP32X3 = 0,  /* tcgen05 kind::tf32, hi/lo split, 3 MMAs per k-block: FP32-level accuracy */
     SB_GEMM_TF32   = 1,  /* tcgen05 kind::tf32, one MMA per k-block */
     SB_GEMM_BF16   = 2,  /* tcgen05 kind::f16 on BF16 copies (use_bf16) */
     SB_GEMM_SIMT   = 3,  /* FP32 FMA on CUDA cores */
-    SB_GEMM_FP16X3 = 4   /* like FP32X3, but K-major products split into scaled FP16 parts (kind::f16): same accuracy, half the MMA cycles */
+    SB_GEMM_FP16X3 = 4   /* default: FP32-level accuracy from scaled FP16 hi/lo parts (kind::f16, half the MMA cycles of FP32X3) for the plain
+                            products; attention's products and shapes the FP16 path does not take run as FP32X3 */
 };
 
 typedef struct { size_t q, k, v, o, gate, up, down, in_norm, post_norm; } sb_layer_off_t;

@@ -45,7 +45,7 @@ def test_tc_gemm_matches_oracle(ctx, M, N, K, tA, tB, acc, mode, pair):
     n0 = ctx.launches()
     ctx.lib.cuda_train_matmul_transpose(ctx.h, a.b, b.b, c.b, M, N, K, tA, tB, acc)
     out = c.numpy(shape=(M, N))
-    ctx.set_gemm_mode(0)
+    ctx.set_gemm_mode(4)
     ctx.set_gemm_pair(1)
     ctx.check()
     assert ctx.launches() > n0

@@ -16,7 +16,7 @@ TOL = 1e-5
 def ctx():
     from seraph_b200 import api
     c = api.Context(0)
-    c.set_gemm_mode(api.GEMM_FP32X3)
+    c.set_gemm_mode(api.GEMM_FP16X3)
     yield c
     c.close()
 
@@ -59,7 +59,7 @@ def test_matmul_simt_mode_matches(ctx):
     a, b, c = ctx.upload(A), ctx.upload(B), ctx.zeros(M * N)
     ctx.set_gemm_mode(api.GEMM_SIMT)
     ctx.lib.cuda_train_matmul(ctx.h, a.b, b.b, c.b, M, N, K)
-    ctx.set_gemm_mode(api.GEMM_FP32X3)
+    ctx.set_gemm_mode(api.GEMM_FP16X3)
     assert rel_l2(c.numpy(shape=(M, N)), ref) < TOL
     ctx.release(a, b, c)
 

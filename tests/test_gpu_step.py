@@ -52,7 +52,7 @@ def run_full_step(ctx, cfg, params, tok, ss, lr=3.14e-4, accum=1, steps=1):
     return out
 
 
-@pytest.mark.parametrize("mode", [0, 3])      # FP32-accurate tensor-core mode, CUDA-core FP32 mode
+@pytest.mark.parametrize("mode", [4, 0, 3])      # FP32-accurate tensor-core modes (FP16 parts = default, TF32 parts), CUDA-core FP32 mode
 def test_tiny_full_step_matches_oracle(ctx, mode):
     cfg = TINY
     ctx.set_gemm_mode(mode)
@@ -176,16 +176,19 @@ def test_lora_default_adapters_q_and_v_only(ctx):
 
 
 def test_c1_step_matches_oracle(ctx):
-    """Config 1 of the baseline: 33M-class Llama-style decoder, 8 x 256 tokens, all gradients."""
+    """Config 1 of the baseline: 33M-class Llama-style decoder, 8 x 256 tokens, all gradients; in the default GEMM mode
+    (FP16 hi/lo parts) and with TF32 parts.  Bound: 1e-5 relative L2 per gradient tensor against the FP64-accumulate oracle."""
     cfg = C1
     p = cfg.init_params(1234)
     ss = list(range(0, 2049, 256))
     tok = tokens_for(cfg, 2048, 99)
     ref = O.train_step(cfg, p, tok, ss)
-    got = run_full_step(ctx, cfg, p, tok, ss)
-    assert abs(got["loss"][0] - ref["loss"]) < 1e-5 * abs(ref["loss"])
-    worst = check_grads(cfg, got["grads"], ref["grads"])
-    print("C1 worst gradient rel-L2:", worst)
+    for mode in (4, 0):
+        ctx.set_gemm_mode(mode)
+        got = run_full_step(ctx, cfg, p, tok, ss)
+        assert abs(got["loss"][0] - ref["loss"]) < 1e-5 * abs(ref["loss"])
+        worst = check_grads(cfg, got["grads"], ref["grads"])
+        print("C1 worst gradient rel-L2, GEMM mode", mode, ":", worst)
 
 
 def test_golden_reference_cuda_vectors(ctx):

@@ -164,7 +164,7 @@ static bool at_gemm(sb_ctx_t* c, const TcOperand& A, const TcOperand& B, float* 
                     int acc, int nb, int causal, const TcEpi* epi = nullptr) {
     TcProblem p; p.A = A; p.B = B; p.C = C; p.ldc = ldc; p.c_batch_stride = cbs; p.M = M; p.N = N; p.K = K; p.acc = acc; p.nbatch = nb; p.causal = causal;
     if (epi) p.epi = *epi; else memset(&p.epi, 0, sizeof p.epi);
-    p.amax = nullptr;
+    p.amax_a = p.amax_b = nullptr;
     return tc_launch(c, p, 3);
 }
 // per-(token, head) vector (lse or D, laid out [token][Hq]) as seen by a launch over heads head0, head0+step, ...

@@ -41,6 +41,40 @@ static bool prep_operand(sb_ctx_t* c, const float* src, int rows, int K, bool km
     return true;
 }
 
+// Slot holding (or about to hold) the FP16 parts of operand x[n].  Inside a keep region the six kept slots are searched
+// first and the least recently used one is taken on a miss; outside, the call's own slot `own` is used.  *fresh: the
+// parts must be made.  Returns the slot index, -1 on allocation failure.
+static int f16_slot(sb_ctx_t* c, const float* x, size_t n, int own, bool* fresh) {
+    if (!c->d_amax && sb_check(c, cudaMalloc(&c->d_amax, 8 * sizeof(float)), "amax alloc")) return -1;
+    int s = own;
+    *fresh = true;
+    if (c->f16_keep) {
+        int lru = 0;
+        for (int i = 0; i < 6; i++) {
+            if (c->f16_slot[i].valid && c->f16_slot[i].ptr == x && c->f16_slot[i].n == n) { c->f16_slot[i].stamp = ++c->f16_clock; *fresh = false; return i; }
+            if (!c->f16_slot[i].valid) { lru = i; break; }
+            if (c->f16_slot[i].stamp < c->f16_slot[lru].stamp) lru = i;
+        }
+        s = lru;
+    }
+    const size_t need = n * 2 * sizeof(__half);
+    if (c->f16_slot[s].cap < need) {
+        cudaStreamSynchronize((cudaStream_t)c->pub.stream);
+        if (c->f16_slot[s].h) cudaFree(c->f16_slot[s].h);
+        c->f16_slot[s].h = NULL; c->f16_slot[s].cap = 0;
+        if (sb_check(c, cudaMalloc(&c->f16_slot[s].h, need), "FP16 parts alloc")) { c->status = SB_ERR_OOM; return -1; }
+        c->f16_slot[s].cap = need;
+    }
+    c->f16_slot[s].ptr = x; c->f16_slot[s].n = n; c->f16_slot[s].valid = c->f16_keep ? 1 : 0; c->f16_slot[s].stamp = ++c->f16_clock;
+    return s;
+}
+
+extern "C" void sb_gemm_keep_begin(sb_ctx_t* c) { c->f16_keep = 1; }
+extern "C" void sb_gemm_keep_end(sb_ctx_t* c) {
+    c->f16_keep = 0;
+    for (int i = 0; i < 8; i++) c->f16_slot[i].valid = 0;
+}
+
 extern "C" int sb_gemm_tc(sb_ctx_t* c, const float* A, const float* B, float* C, int M, int N, int K, int tA, int tB, int acc, int mode) {
     if (K <= 0 || M < 32 || N < 32) return 1;
     if ((double)M * N * K < (double)(1 << 21)) return 1;                 // too small to pay for the pipeline
@@ -53,31 +87,41 @@ extern "C" int sb_gemm_tc(sb_ctx_t* c, const float* A, const float* B, float* C,
     const bool x3 = (mode == SB_GEMM_FP32X3 || mode == SB_GEMM_FP16X3);
     TcProblem p;
     memset(&p.epi, 0, sizeof p.epi);
-    p.amax = nullptr;
+    p.amax_a = p.amax_b = nullptr;
     p.C = C; p.ldc = N; p.c_batch_stride = 0; p.M = M; p.N = N; p.K = K; p.acc = acc; p.nbatch = 1; p.causal = TC_CAUSAL_NONE;
     // direct path: the pair kernel on the caller's arrays (rows of either layout must be 16-byte multiples)
     if (c->gemm_pair && M > 128 && N > 128 && (a_kmajor ? (K & 3) == 0 : (M & 3) == 0) && (b_kmajor ? (K & 3) == 0 : (N & 3) == 0)) {
         p.A.hi = A; p.A.lo = nullptr; p.A.rows = M; p.A.mn = a_kmajor ? 0 : 1; p.A.pitch = a_kmajor ? K : M;
         p.B.hi = B; p.B.lo = nullptr; p.B.rows = N; p.B.mn = b_kmajor ? 0 : 1; p.B.pitch = b_kmajor ? K : N;
         p.A.c2_dim = p.B.c2_dim = 1; p.A.c2_stride = p.B.c2_stride = 0; p.A.c2_base = p.B.c2_base = 0; p.A.c2_step = p.B.c2_step = 0;
-        int tg = sb_tick_begin(c, SB_CLS_GEMM);
         p.A.h1 = p.A.h2 = p.B.h1 = p.B.h2 = nullptr;
         if (mode == SB_GEMM_FP16X3 && N > 128 && (a_kmajor ? (K & 7) == 0 : (M & 7) == 0) && (b_kmajor ? (K & 7) == 0 : (N & 7) == 0)) {
-            // FP16 split: the operands' largest magnitudes, then their two FP16 parts (one launch each over both operands)
-            if (!c->d_amax && sb_check(c, cudaMalloc(&c->d_amax, 2 * sizeof(float)), "amax alloc")) return 1;
+            // FP16 split: each operand's largest magnitude, then its two FP16 parts (skipped for an operand whose parts are kept)
             const size_t na = (size_t)M * K, nb = (size_t)N * K;
-            __half* ha = (__half*)sb_gemm_stage(c, 0, na * 2 * sizeof(__half));
-            __half* hb = (__half*)sb_gemm_stage(c, 1, nb * 2 * sizeof(__half));
-            if (!ha || !hb) return 1;
-            cudaStream_t st = (cudaStream_t)c->pub.stream;
-            cudaMemsetAsync(c->d_amax, 0, 2 * sizeof(float), st);
-            const dim3 pg(tc_ew_blocks(c, (na > nb ? na : nb) / 4), 2);
-            tc_amax_kernel<<<pg, 256, 0, st>>>(A, na / 4, B, nb / 4, (unsigned*)c->d_amax);
-            tc_split_f16_kernel<<<pg, 256, 0, st>>>(A, na / 4, ha, ha + na, B, nb / 4, hb, hb + nb, c->d_amax);
-            c->launches += 2;
-            p.amax = c->d_amax;
+            bool fa = false, fb = false;
+            const int sa = f16_slot(c, A, na, 6, &fa), sb = f16_slot(c, B, nb, 7, &fb);
+            if (sa < 0 || sb < 0) return 1;
+            __half* ha = (__half*)c->f16_slot[sa].h; __half* hb = (__half*)c->f16_slot[sb].h;
+            float* ma = c->d_amax + sa; float* mb = c->d_amax + sb;
+            if (fa || fb) {
+                cudaStream_t st = (cudaStream_t)c->pub.stream;
+                int tp = sb_tick_begin(c, SB_CLS_GEMM_PREP);
+                // the operands that need their parts made: first (and maybe second) argument set of the kernels
+                const float* x0 = fa ? A : B; const size_t n0 = fa ? na : nb; __half* h0 = fa ? ha : hb; float* m0 = fa ? ma : mb;
+                const bool two = fa && fb;
+                cudaMemsetAsync(m0, 0, sizeof(float), st);
+                if (two) cudaMemsetAsync(mb, 0, sizeof(float), st);
+                const size_t nmax = two ? (na > nb ? na : nb) : n0;
+                const dim3 pg(tc_ew_blocks(c, nmax / 4), two ? 2 : 1);
+                tc_amax_kernel<<<pg, 256, 0, st>>>(x0, n0 / 4, (unsigned*)m0, B, nb / 4, (unsigned*)mb);
+                tc_split_f16_kernel<<<pg, 256, 0, st>>>(x0, n0 / 4, h0, h0 + n0, m0, B, nb / 4, hb, hb + nb, mb);
+                c->launches += 2;
+                sb_tick_end(c, tp, 0.0, 12.0 * (double)((fa ? na : 0) + (fb ? nb : 0)));
+            }
+            p.amax_a = ma; p.amax_b = mb;
             p.A.h1 = ha; p.A.h2 = ha + na; p.B.h1 = hb; p.B.h2 = hb + nb;
         }
+        int tg = sb_tick_begin(c, SB_CLS_GEMM);
         bool ok = tc_launch(c, p, x3 ? 3 : 1);
         sb_tick_end(c, tg, 2.0 * M * N * K, 4.0 * ((double)M * K + (double)N * K + (double)M * N * (acc ? 2 : 1)));
         if (!ok) { sb_set_status(c, SB_ERR_CUDA); return 1; }

@@ -83,7 +83,7 @@ struct TcProblem {
     float* C; long ldc; long c_batch_stride;
     int M, N, K, acc, nbatch, causal;
     TcEpi epi;
-    const float* amax;       // FP16 split: device floats {max |A|, max |B|}; NULL = TF32 split
+    const float* amax_a; const float* amax_b;      // FP16 split: device floats max |A|, max |B|; NULL = TF32 split
 };
 
 // --------------------------------------------------------------------------- PTX helpers
@@ -347,7 +347,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
                float* __restrict__ Cbase, long ldc, long c_batch_stride, int M, int N, int K, int acc, int causal,
                int a_c2_base, int a_c2_step, int b_c2_base, int b_c2_step, int swap_mask,
                int split_full, int split_s, float* __restrict__ partial, const TcEpi epi,
-               int nbatch, int total_items, int snake, int tri, int store_warps, const float* __restrict__ amax, int* status) {
+               int nbatch, int total_items, int snake, int tri, int store_warps, const float* __restrict__ amax_a, const float* __restrict__ amax_b, int* status) {
     constexpr int SWZ = BK * 4;
     constexpr int BROWS = BN / CTAS;                             // B rows this CTA loads
     constexpr int TILE_M = TC_BM * CTAS;
@@ -656,7 +656,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
             }
             if (F16) {
                 // undo the operands' power-of-two scales (two exact multiplications: the product of both may leave the float range)
-                const float ua = tc_pow2(-tc_f16_shift(amax[0])), ub = tc_pow2(-tc_f16_shift(amax[1]));
+                const float ua = tc_pow2(-tc_f16_shift(*amax_a)), ub = tc_pow2(-tc_f16_shift(*amax_b));
 #pragma unroll
                 for (int j = 0; j < COLS_PER_WARP; j++) accr[j] = accr[j] * ua * ub;
             }
@@ -847,9 +847,9 @@ static __global__ void __launch_bounds__(256) tc_splitk_fixup_kernel(const float
     }
 }
 
-// max |x| of two operands (blockIdx.y selects), as float bits through an integer atomicMax (order-free); out zeroed before
-static __global__ void __launch_bounds__(256) tc_amax_kernel(const float* __restrict__ a, size_t na4, const float* __restrict__ b, size_t nb4,
-                                                             unsigned* __restrict__ out) {
+// max |x| of up to two operands (blockIdx.y selects), as float bits through an integer atomicMax (order-free); outputs zeroed before
+static __global__ void __launch_bounds__(256) tc_amax_kernel(const float* __restrict__ a, size_t na4, unsigned* __restrict__ oa,
+                                                             const float* __restrict__ b, size_t nb4, unsigned* __restrict__ ob) {
     const float4* x = (const float4*)(blockIdx.y ? b : a);
     const size_t n4 = blockIdx.y ? nb4 : na4;
     float m = 0.f;
@@ -863,18 +863,19 @@ static __global__ void __launch_bounds__(256) tc_amax_kernel(const float* __rest
     __syncthreads();
     if (threadIdx.x == 0) {
         for (int w = 1; w < 8; w++) m = fmaxf(m, red[w]);
-        atomicMax(out + blockIdx.y, __float_as_uint(m));
+        atomicMax(blockIdx.y ? ob : oa, __float_as_uint(m));
     }
 }
 
-// FP16 parts of two operands (blockIdx.y selects): x' = x * 2^shift(amax), h1 = fp16(x'), h2 = fp16(x' - h1); layout kept
+// FP16 parts of up to two operands (blockIdx.y selects): x' = x * 2^shift(amax), h1 = fp16(x'), h2 = fp16(x' - h1); layout kept
 static __global__ void __launch_bounds__(256) tc_split_f16_kernel(const float* __restrict__ a, size_t na4, __half* __restrict__ a1, __half* __restrict__ a2,
+                                                                  const float* __restrict__ amax_a,
                                                                   const float* __restrict__ b, size_t nb4, __half* __restrict__ b1, __half* __restrict__ b2,
-                                                                  const float* __restrict__ amax) {
+                                                                  const float* __restrict__ amax_b) {
     const float4* x = (const float4*)(blockIdx.y ? b : a);
     const size_t n4 = blockIdx.y ? nb4 : na4;
     uint2* o1 = (uint2*)(blockIdx.y ? b1 : a1); uint2* o2 = (uint2*)(blockIdx.y ? b2 : a2);
-    const float sc = tc_pow2(tc_f16_shift(amax[blockIdx.y]));
+    const float sc = tc_pow2(tc_f16_shift(blockIdx.y ? *amax_b : *amax_a));
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
         const float4 v = x[i];
         const float p0 = v.x * sc, p1 = v.y * sc, p2 = v.z * sc, p3 = v.w * sc;
@@ -1075,12 +1076,12 @@ static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
         cfg.attrs = at; cfg.numAttrs = 1;
         if (cudaLaunchKernelEx(&cfg, kern, mAh, mAl, mBh, mBl, p.C, p.ldc, p.c_batch_stride, p.M, p.N, p.K, p.acc, p.causal,
                                p.A.c2_base, p.A.c2_step, p.B.c2_base, p.B.c2_step, swap_mask, split_full, split_s, partial, p.epi,
-                               nbatch, total_items, snake, tri, store_warps, p.amax, c->d_status) != cudaSuccess) return false;
+                               nbatch, total_items, snake, tri, store_warps, p.amax_a, p.amax_b, c->d_status) != cudaSuccess) return false;
     } else {
         kern<<<grid, THREADS, smem, (cudaStream_t)c->pub.stream>>>(mAh, mAl, mBh, mBl, p.C, p.ldc, p.c_batch_stride, p.M, p.N, p.K, p.acc,
                                                                      p.causal, p.A.c2_base, p.A.c2_step, p.B.c2_base, p.B.c2_step,
                                                                      swap_mask, split_full, split_s, partial, p.epi,
-                                                                     nbatch, total_items, snake, tri, store_warps, p.amax, c->d_status);
+                                                                     nbatch, total_items, snake, tri, store_warps, p.amax_a, p.amax_b, c->d_status);
     }
     c->launches++;
     if (split_s > 1) {
@@ -1100,7 +1101,7 @@ static bool tc_launch(sb_ctx_t* c, const TcProblem& p, int nterms) {
     if (c->gemm_pair && raw) {
         const int lay = (p.A.mn ? 1 : 0) | (p.B.mn ? 2 : 0);
         if (p.N > 128) {
-            if (nterms == 3 && p.amax && p.A.h1 && p.B.h1) switch (lay) {
+            if (nterms == 3 && p.amax_a && p.amax_b && p.A.h1 && p.B.h1) switch (lay) {
                 case 0: return tc_launch_t<256, 16, 3, 5, 2, false, false, true, true>(c, p);
                 case 1: return tc_launch_t<256, 16, 3, 5, 2, true, false, true, true>(c, p);
                 case 2: return tc_launch_t<256, 16, 3, 5, 2, false, true, true, true>(c, p);

@@ -55,7 +55,10 @@ typedef struct sb_ctx {
     int status;                      /* last host-side status */
     int* d_status;                   /* device status word (bounds checks, bounded waits) */
     int gemm_mode;                   /* SB_GEMM_* (use_bf16 in pub overrides to BF16) */
-    float* d_amax;                   /* two floats: max |A|, max |B| of the GEMM being launched (FP16 split) */
+    float* d_amax;                   /* FP16 split: max |x| of the operand held by each part slot */
+    struct { void* h; size_t cap; const float* ptr; size_t n; unsigned stamp; int valid; } f16_slot[8];   /* FP16 parts of GEMM operands: 0-5 kept across
+                                        calls inside a keep region (train_step.c marks runs of GEMMs that share operands), 6-7 for one call */
+    int f16_keep; unsigned f16_clock;
     int attn_fused;                  /* 1: P and dS of the attention backward come out of the score products' epilogues */
     int gemm_tail_split;             /* 1: tiles of the last partial wave are cut into k pieces */
     int gemm_pair;                   /* 1: plain GEMMs run on CTA pairs (cta_group::2), 0: one CTA per tile */
@@ -139,6 +142,10 @@ void sb_mul_backward(sb_ctx_t*, const float* A, const float* B, const float* dC,
 void sb_swiglu(sb_ctx_t*, const float* gate, const float* up, float* out, size_t n);
 void sb_swiglu_backward(sb_ctx_t*, const float* gate, const float* up, const float* dout, float* dgate, float* dup, size_t n);
 void sb_seq_index(sb_ctx_t*, const uint32_t* seq_starts, int B, int T, uint32_t* pos_ids, uint32_t* seq_ids);
+/* Between begin and end the FP16 parts of GEMM operands are kept and reused by later calls on the same array; the caller
+ * guarantees that no operand array is written inside the region. */
+void sb_gemm_keep_begin(sb_ctx_t*);
+void sb_gemm_keep_end(sb_ctx_t*);
 void sb_rope2(sb_ctx_t*, float* q, float* k, const uint32_t* pos_ids, int T, int Hq, int Hkv, int hd, float theta, int max_pos, int backward);
 void sb_rope(sb_ctx_t*, const float* in, float* out, const uint32_t* pos_ids, int T, int H, int hd, float theta,
              int max_pos, int backward);

@@ -410,16 +410,21 @@ static void forward_pass(sb_ctx_t* c, int T, int max_seq, float theta, int use_l
         sb_layer_act_t* a = &c->act[l];
         float* next_in = (l + 1 < L) ? c->act[l + 1].layer_in : c->final_in;
         sb_rmsnorm(c, a->layer_in, c->W + o->in_norm, a->x_norm_attn, T, d, RMS_EPS);
+        /* runs of products that share an operand keep its prepared parts (not with adapters: their scratch is rewritten in between) */
+        if (!use_lora) sb_gemm_keep_begin(c);
         linear_fwd(c, use_lora, l, 0, a->x_norm_attn, c->W + o->q, a->q, T, d, qd, 0);
         linear_fwd(c, use_lora, l, 1, a->x_norm_attn, c->W + o->k, a->k, T, d, kvd, 0);
         linear_fwd(c, use_lora, l, 2, a->x_norm_attn, c->W + o->v, a->v, T, d, kvd, 0);
+        sb_gemm_keep_end(c);
         sb_rope2(c, a->q, a->k, c->pos_ids, T, c->Hq, c->Hkv, c->hd, theta, max_seq, 0);
         sb_attention(c, a->q, a->k, a->v, a->attn_out, a->lse, c->seq_starts, c->seq_ids, T, c->Hq, c->Hkv, c->hd);
         sb_copy(c, a->post_attn_in, a->layer_in, Td * sizeof(float));
         linear_fwd(c, use_lora, l, 3, a->attn_out, c->W + o->o, a->post_attn_in, T, qd, d, 1);
         sb_rmsnorm(c, a->post_attn_in, c->W + o->post_norm, a->x_norm_ffn, T, d, RMS_EPS);
+        if (!use_lora) sb_gemm_keep_begin(c);
         linear_fwd(c, use_lora, l, 4, a->x_norm_ffn, c->W + o->gate, a->gate, T, d, F, 0);
         linear_fwd(c, use_lora, l, 5, a->x_norm_ffn, c->W + o->up, a->up, T, d, F, 0);
+        sb_gemm_keep_end(c);
         sb_swiglu(c, a->gate, a->up, a->ffn_hidden, (size_t)T * F);
         sb_copy(c, next_in, a->post_attn_in, Td * sizeof(float));
         linear_fwd(c, use_lora, l, 6, a->ffn_hidden, c->W + o->down, next_in, T, F, d, 1);
@@ -435,33 +440,42 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
     float* Gd = full ? c->G : NULL;
     float* norm_sink = c->g_tmp;                 /* LoRA mode: norm-scale gradients are discarded */
     if (!full) sb_memset(c, norm_sink, 0, (size_t)d * sizeof(float));
+    if (full) sb_gemm_keep_begin(c);
     sb_gemm(c, c->dlogits, c->W, gx, T, d, V, 0, 0, 0);
     if (full) sb_gemm(c, c->dlogits, c->hidden_norm, Gd, V, d, T, 1, 0, 1);
+    sb_gemm_keep_end(c);
     sb_rmsnorm_backward(c, c->final_in, c->W + (size_t)V * d, gx, NULL, gh, full ? Gd + (size_t)V * d : norm_sink, T, d, RMS_EPS);
     for (int l = L - 1; l >= 0; l--) {
         const sb_layer_off_t* o = &c->off[l];
         sb_layer_act_t* a = &c->act[l];
         /* FFN */
+        if (full) sb_gemm_keep_begin(c);
         if (full) sb_gemm(c, gh, a->ffn_hidden, Gd + o->down, d, F, T, 1, 0, 1);
         sb_gemm(c, gh, c->W + o->down, c->g_ffn, T, F, d, 0, 0, 0);
+        sb_gemm_keep_end(c);
         if (!full) lora_bwd(c, l, 6, gh, a->ffn_hidden, c->g_ffn, T);
         sb_swiglu_backward(c, a->gate, a->up, c->g_ffn, c->g_gate, c->g_up, (size_t)T * F);
         if (full) {
+            sb_gemm_keep_begin(c);
             sb_gemm(c, c->g_gate, a->x_norm_ffn, Gd + o->gate, F, d, T, 1, 0, 1);
             sb_gemm(c, c->g_up, a->x_norm_ffn, Gd + o->up, F, d, T, 1, 0, 1);
         }
         sb_gemm(c, c->g_gate, c->W + o->gate, gx, T, d, F, 0, 0, 0);
         sb_gemm(c, c->g_up, c->W + o->up, gx, T, d, F, 0, 0, 1);
+        sb_gemm_keep_end(c);
         if (!full) { lora_bwd(c, l, 4, c->g_gate, a->x_norm_ffn, gx, T); lora_bwd(c, l, 5, c->g_up, a->x_norm_ffn, gx, T); }
         sb_rmsnorm_backward(c, a->post_attn_in, c->W + o->post_norm, gx, gh, gh, full ? Gd + o->post_norm : norm_sink, T, d, RMS_EPS);
         /* attention */
+        if (full) sb_gemm_keep_begin(c);
         if (full) sb_gemm(c, gh, a->attn_out, Gd + o->o, d, qd, T, 1, 0, 1);
         sb_gemm(c, gh, c->W + o->o, c->g_attn, T, qd, d, 0, 0, 0);
+        sb_gemm_keep_end(c);
         if (!full) lora_bwd(c, l, 3, gh, a->attn_out, c->g_attn, T);
         sb_attention_backward(c, a->q, a->k, a->v, a->attn_out, a->lse, c->g_attn, c->g_q, c->g_k, c->g_v, 0,
                               c->seq_starts, c->seq_ids, B, T, c->Hq, c->Hkv, c->hd);
         sb_rope2(c, c->g_q, c->g_k, c->pos_ids, T, c->Hq, c->Hkv, c->hd, theta, max_seq, 1);
         if (full) {
+            sb_gemm_keep_begin(c);
             sb_gemm(c, c->g_q, a->x_norm_attn, Gd + o->q, qd, d, T, 1, 0, 1);
             sb_gemm(c, c->g_k, a->x_norm_attn, Gd + o->k, kvd, d, T, 1, 0, 1);
             sb_gemm(c, c->g_v, a->x_norm_attn, Gd + o->v, kvd, d, T, 1, 0, 1);
@@ -469,6 +483,7 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
         sb_gemm(c, c->g_q, c->W + o->q, gx, T, d, qd, 0, 0, 0);
         sb_gemm(c, c->g_k, c->W + o->k, gx, T, d, kvd, 0, 0, 1);
         sb_gemm(c, c->g_v, c->W + o->v, gx, T, d, kvd, 0, 0, 1);
+        sb_gemm_keep_end(c);
         if (!full) { lora_bwd(c, l, 0, c->g_q, a->x_norm_attn, gx, T); lora_bwd(c, l, 1, c->g_k, a->x_norm_attn, gx, T); lora_bwd(c, l, 2, c->g_v, a->x_norm_attn, gx, T); }
         sb_rmsnorm_backward(c, a->layer_in, c->W + o->in_norm, gx, gh, gh, full ? Gd + o->in_norm : norm_sink, T, d, RMS_EPS);
         if (reduce) {
@@ -740,6 +755,7 @@ void cuda_train_free(cuda_train_context_t* ctx) {
     }
     if (c->rope_tab) cudaFree(c->rope_tab);
     if (c->d_amax) cudaFree(c->d_amax);
+    for (int i = 0; i < 8; i++) if (c->f16_slot[i].h) cudaFree(c->f16_slot[i].h);
     if (c->d_status) cudaFree(c->d_status);
     if (c->d_loss) cudaFree(c->d_loss);
     if (c->h_pinned) cudaFreeHost(c->h_pinned);

@@ -38,13 +38,14 @@ WORKLOADS = {
 }
 
 
-def gemm_traffic(cfg, T):
+def gemm_traffic(cfg, T, f16=True):
     """DRAM bytes of one launch of the dominant kernel: the FFN gate projection (M = T, N = ffn, K = hidden).
-    One ncu capture of that launch at T = 4096, hidden 2048, ffn 6144 read 148.1 MB and wrote 73.6 MB of DRAM,
-    1.20 times its algorithmic 4*(M*K + N*K + M*N) bytes (summary under profiles/); a full-size launch is too
-    long a capture, so that ratio is applied to the algorithmic bytes of the launch at this workload's T."""
+    One ncu capture of that launch at T = 4096, hidden 2048, ffn 6144 read 161.7 MB and wrote 83.5 MB of DRAM in the
+    default mode (1.33 times its algorithmic 4*(M*K + N*K + M*N) bytes; with TF32 parts 151.4 + 75.1 MB, 1.23 times;
+    summaries under profiles/); a full-size launch is too long a capture, so that ratio is applied to the algorithmic
+    bytes of the launch at this workload's T."""
     alg = 4.0 * (T * cfg.d + cfg.F * cfg.d + T * cfg.F)
-    return 1.20 * alg
+    return (1.33 if f16 else 1.23) * alg
 
 
 def peaks():
@@ -245,7 +246,7 @@ def run_ours(args):
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": "gemm", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
-                         "frac": (achieved / tf32_peak) if achieved else None, "traffic": gemm_traffic(cfg, T),
+                         "frac": (achieved / tf32_peak) if achieved else None, "traffic": gemm_traffic(cfg, T, f16_mode),
                          "peak_note": (f"{pk_kind} bf16 sustained {pk['bf16_tflops_sustained']} TFLOP/s (FP16 MMAs run at the BF16 rate)"
                                        if f16_mode else
                                        f"{pk_kind} bf16 sustained {pk['bf16_tflops_sustained']} TFLOP/s halved for TF32 operands") +

@@ -54,11 +54,21 @@ __device__ __forceinline__ float at_block_sum(float v, float* red) {
     __syncthreads();
     return s;
 }
+// x * 2^14 (P lies in [0, 1]) or x * sc as two FP16 parts: h1 = fp16(x'), h2 = fp16(x' - h1)
+__device__ __forceinline__ void at_put_parts(__half* __restrict__ h1, __half* __restrict__ h2, size_t idx, float xs) {
+    const __half a = __float2half_rn(xs);
+    h1[idx] = a; h2[idx] = __float2half_rn(xs - __half2float(a));
+}
+#define AT_P_SCALE 16384.0f
+
+// P1/P2 given: P is written as its two FP16 parts (scale 2^14) to those arrays instead of in place
 __global__ void __launch_bounds__(256) at_softmax_rows(float* __restrict__ Sb, float* __restrict__ lse,
-                                                       int S, int Sp, int Hq, int head0, int head_step, int tok0, float scale) {
+                                                       int S, int Sp, int Hq, int head0, int head_step, int tok0, float scale,
+                                                       __half* __restrict__ P1, __half* __restrict__ P2) {
     __shared__ float red[8];
     const int q = blockIdx.x, i = blockIdx.y, h = head0 + i * head_step;
     float* row = Sb + ((size_t)i * Sp + q) * Sp;
+    const size_t rbase = ((size_t)i * Sp + q) * Sp;
     const int n = q + 1, zend = min(Sp, (q / AT_ROWTILE + 1) * AT_ROWTILE);
     if (n <= 256 * AT_SM_REGS) {
         const int nj = (n + 255) >> 8, zj = (zend + 255) >> 8;      // passes of 256 columns that hold scores / that are written
@@ -85,7 +95,10 @@ __global__ void __launch_bounds__(256) at_softmax_rows(float* __restrict__ Sb, f
         for (int j = 0; j < AT_SM_REGS; j++)
             if (j < zj) {
                 const int k = threadIdx.x + 256 * j;
-                if (k < zend) row[k] = j < nj ? v[j] * inv : 0.f;                           // 0 past the diagonal
+                if (k < zend) {                                                             // 0 past the diagonal
+                    const float pv = j < nj ? v[j] * inv : 0.f;
+                    if (P1) at_put_parts(P1, P2, rbase + k, pv * AT_P_SCALE); else row[k] = pv;
+                }
             }
         return;
     }
@@ -97,23 +110,48 @@ __global__ void __launch_bounds__(256) at_softmax_rows(float* __restrict__ Sb, f
     s = at_block_sum(s, red);
     const float L = m + logf(s);
     if (threadIdx.x == 0 && lse) lse[(size_t)(tok0 + q) * Hq + h] = L;
-    for (int k = threadIdx.x; k < zend; k += blockDim.x) row[k] = k < n ? expf(row[k] * scale - L) : 0.f;
+    for (int k = threadIdx.x; k < zend; k += blockDim.x) {
+        const float pv = k < n ? expf(row[k] * scale - L) : 0.f;
+        if (P1) at_put_parts(P1, P2, rbase + k, pv * AT_P_SCALE); else row[k] = pv;
+    }
 }
 
 // Backward rows: S (buf_s) and dP (buf_dp) -> P (into buf_s) and dS (into buf_dp); zero past the diagonal up to the row tile's end
+// P1..dS2 given: both are written as FP16 parts (P with scale 2^14, dS with the power of two that brings *ds_bound to [2^14, 2^15))
 __global__ void __launch_bounds__(256) at_ds_rows(float* __restrict__ buf_s, float* __restrict__ buf_dp, const float* __restrict__ lse,
                                                   const float* __restrict__ D, int S, int Sp, int Hq, int head0, int head_step,
-                                                  int tok0, float scale) {
+                                                  int tok0, float scale, __half* __restrict__ P1, __half* __restrict__ P2,
+                                                  __half* __restrict__ dS1, __half* __restrict__ dS2, const float* __restrict__ ds_bound) {
     const int q = blockIdx.x, i = blockIdx.y, h = head0 + i * head_step;
     float* srow = buf_s + ((size_t)i * Sp + q) * Sp;
     float* drow = buf_dp + ((size_t)i * Sp + q) * Sp;
     const float L = lse[(size_t)(tok0 + q) * Hq + h], Dq = D[(size_t)(tok0 + q) * Hq + h];
     const int zend = min(Sp, (q / AT_ROWTILE + 1) * AT_ROWTILE);
+    const size_t rbase = ((size_t)i * Sp + q) * Sp;
+    const float dsc = P1 ? tc_pow2(tc_f16_shift(*ds_bound)) : 1.f;
     for (int k = threadIdx.x; k < zend; k += blockDim.x) {
         float p = 0.f, ds = 0.f;
         if (k <= q) { p = expf(srow[k] * scale - L); ds = p * (drow[k] - Dq) * scale; }
-        srow[k] = p; drow[k] = ds;
+        if (P1) { at_put_parts(P1, P2, rbase + k, p * AT_P_SCALE); at_put_parts(dS1, dS2, rbase + k, ds * dsc); }
+        else { srow[k] = p; drow[k] = ds; }
     }
+}
+
+// largest row norm of x[n_rows, hd] (one warp per row), as float bits through an integer atomicMax; out zeroed before
+__global__ void at_rownorm_max_kernel(const float* __restrict__ x, int n_rows, int hd, unsigned* __restrict__ out) {
+    int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (w >= n_rows) return;
+    const float* a = x + (size_t)w * hd;
+    float s = 0.f;
+    for (int d = lane; d < hd; d += 32) s += a[d] * a[d];
+    s = warp_sum_f(s);
+    if (lane == 0) atomicMax(out, __float_as_uint(sqrtf(s)));
+}
+// consts[0] = 1 (the largest possible P); consts[1] = 2 * max|dO row| * max|V row| * scale >= |dS| everywhere:
+// |dP| = |dO_q . V_k| <= the product of the norms, D_q is a convex combination of the dP_qk, P <= 1
+__global__ void at_consts_kernel(float* consts, const float* norms, float scale) {
+    consts[0] = 1.0f;
+    consts[1] = 2.0f * norms[0] * norms[1] * scale;
 }
 
 // D[t,h] = sum_d dO[t,h,d] * O[t,h,d]; one warp per (t,h)
@@ -129,6 +167,11 @@ __global__ void at_delta_kernel(const float* __restrict__ dO, const float* __res
 
 // ---------------------------------------------------------------------------------------------
 
+// FP16 parts for the attention products: the default GEMM mode, head sizes that fill whole 32-element k blocks
+static bool at_f16(sb_ctx_t* c, int hd) {
+    int mode = c->pub.use_bf16 ? SB_GEMM_BF16 : c->gemm_mode;
+    return mode == SB_GEMM_FP16X3 && (hd % 32) == 0 && !c->attn_fused;
+}
 static bool at_eligible(sb_ctx_t* c, int T, int Hq, int Hkv, int hd) {
     int mode = c->pub.use_bf16 ? SB_GEMM_BF16 : c->gemm_mode;
     if (mode == SB_GEMM_SIMT || !c->gemm_pair) return false;
@@ -139,33 +182,48 @@ static bool at_eligible(sb_ctx_t* c, int T, int Hq, int Hkv, int hd) {
     return tc_load_encode();
 }
 
+// FP16 parts of a token-major tensor (made once per attention call), or of a score matrix
+struct AtParts { const __half* h1; const __half* h2; const float* amax; };
+static const AtParts AT_NOPARTS = {nullptr, nullptr, nullptr};
+
 // K-major view of [token, heads*hd] rows: rows = tokens of the sequence, k = the head's hd columns, slot = head
-static TcOperand op_tokens(const float* x, int tok0, int S, int row_pitch, int nheads, int hd, int slot_base, int slot_step) {
+static TcOperand op_tokens(const float* x, const AtParts& pt, int tok0, int S, int row_pitch, int nheads, int hd, int slot_base, int slot_step) {
     TcOperand o;
-    o.hi = x + (size_t)tok0 * row_pitch; o.lo = nullptr; o.h1 = o.h2 = nullptr;
+    o.hi = x + (size_t)tok0 * row_pitch; o.lo = nullptr;
+    o.h1 = pt.h1 ? pt.h1 + (size_t)tok0 * row_pitch : nullptr; o.h2 = pt.h2 ? pt.h2 + (size_t)tok0 * row_pitch : nullptr;
     o.mn = 0; o.rows = S; o.pitch = row_pitch; o.c2_dim = nheads; o.c2_stride = hd; o.c2_base = slot_base; o.c2_step = slot_step;
     return o;
 }
 // MN-major view of the same rows: k = tokens of the sequence, rows = the head's hd columns (contiguous), slot = head
-static TcOperand op_tokens_mn(const float* x, int tok0, int row_pitch, int nheads, int hd, int slot_base, int slot_step) {
-    TcOperand o;
-    o.hi = x + (size_t)tok0 * row_pitch; o.lo = nullptr; o.h1 = o.h2 = nullptr;
-    o.mn = 1; o.rows = hd; o.pitch = row_pitch; o.c2_dim = nheads; o.c2_stride = hd; o.c2_base = slot_base; o.c2_step = slot_step;
+static TcOperand op_tokens_mn(const float* x, const AtParts& pt, int tok0, int row_pitch, int nheads, int hd, int slot_base, int slot_step) {
+    TcOperand o = op_tokens(x, pt, tok0, hd, row_pitch, nheads, hd, slot_base, slot_step);
+    o.mn = 1;
     return o;
 }
 // score scratch [head][query][key]: K-major = rows are queries, k runs over keys; mn = rows are keys, k runs over queries
-static TcOperand op_scratch(const float* x, int S, int Sp, int nb, int mn) {
+static TcOperand op_scratch(const float* x, const AtParts& pt, int S, int Sp, int nb, int mn) {
     TcOperand o;
-    o.hi = x; o.lo = nullptr; o.h1 = o.h2 = nullptr; o.mn = mn; o.rows = S; o.pitch = Sp; o.c2_dim = nb; o.c2_stride = (long)Sp * Sp; o.c2_base = 0; o.c2_step = 1;
+    o.hi = x; o.lo = nullptr; o.h1 = pt.h1; o.h2 = pt.h2; o.mn = mn; o.rows = S; o.pitch = Sp; o.c2_dim = nb; o.c2_stride = (long)Sp * Sp; o.c2_base = 0; o.c2_step = 1;
     return o;
 }
 
 static bool at_gemm(sb_ctx_t* c, const TcOperand& A, const TcOperand& B, float* C, long ldc, long cbs, int M, int N, int K,
-                    int acc, int nb, int causal, const TcEpi* epi = nullptr) {
+                    int acc, int nb, int causal, const TcEpi* epi = nullptr, const float* amax_a = nullptr, const float* amax_b = nullptr) {
     TcProblem p; p.A = A; p.B = B; p.C = C; p.ldc = ldc; p.c_batch_stride = cbs; p.M = M; p.N = N; p.K = K; p.acc = acc; p.nbatch = nb; p.causal = causal;
     if (epi) p.epi = *epi; else memset(&p.epi, 0, sizeof p.epi);
-    p.amax_a = p.amax_b = nullptr;
+    p.amax_a = amax_a; p.amax_b = amax_b;
     return tc_launch(c, p, 3);
+}
+// FP16 parts of x[n] into h[0..n) and h[n..2n), its largest magnitude into *amax
+static AtParts at_make_parts(sb_ctx_t* c, const float* x, size_t n, __half* h, float* amax) {
+    cudaStream_t st = (cudaStream_t)c->pub.stream;
+    cudaMemsetAsync(amax, 0, sizeof(float), st);
+    const dim3 pg(tc_ew_blocks(c, n / 4), 1);
+    tc_amax_kernel<<<pg, 256, 0, st>>>(x, n / 4, (unsigned*)amax, nullptr, 0, nullptr);
+    tc_split_f16_kernel<<<pg, 256, 0, st>>>(x, n / 4, h, h + n, amax, nullptr, 0, nullptr, nullptr, nullptr);
+    c->launches += 2;
+    AtParts p = {h, h + n, amax};
+    return p;
 }
 // per-(token, head) vector (lse or D, laid out [token][Hq]) as seen by a launch over heads head0, head0+step, ...
 static TcEpi at_epi(int mode, float scale, const float* vec, int tok0, int Hq, int head0, int head_step, const float* aux) {
@@ -222,11 +280,28 @@ extern "C" int sb_attention_tc_forward(sb_ctx_t* c, const float* Q, const float*
     int Smax = 0;
     for (int b = 0; b < c->h_seq_n; b++) Smax = max(Smax, c->h_seq[b + 1] - c->h_seq[b]);
     const int Sp = round_up(Smax, AT_ROWTILE);                       // one pitch for all sequences of the call
-    const int G = at_group(Sp, 1, Hkv);
+    // FP16 parts (the default GEMM mode): Q, K, V are split once here, P is written as parts by the softmax kernel
+    const bool f16 = at_f16(c, hd);
+    const int G = at_group(Sp, f16 ? 2 : 1, Hkv);
     const size_t n_s = (size_t)G * Sp * Sp;
-    float* Sb0 = (float*)sb_gemm_stage(c, 3, AT_SIDE * n_s * sizeof(float));
+    const size_t per_stream = f16 ? 2 * n_s : n_s;                   // floats: S, then (FP16) the two parts of P
+    float* Sb0 = (float*)sb_gemm_stage(c, 3, AT_SIDE * per_stream * sizeof(float));
     if (!Sb0) return 1;
+    const size_t n_q = (size_t)T * qd, n_kv = (size_t)T * kvd;
+    AtParts pq = AT_NOPARTS, pk = AT_NOPARTS, pv = AT_NOPARTS;
+    float* consts = nullptr;
     int tk = sb_tick_begin(c, SB_CLS_ATTN_FWD);
+    if (f16) {
+        float* st0 = (float*)sb_gemm_stage(c, 2, (n_q + 2 * n_kv) * 2 * sizeof(__half) + 64 * sizeof(float));
+        if (!st0) return 1;
+        consts = st0;                                            // [0] 1.0, [1] dS bound, [2..] norms, [8..] amax of Q, K, V, dO
+        __half* hb = (__half*)(st0 + 64);
+        pq = at_make_parts(c, Q, n_q, hb, consts + 8);
+        pk = at_make_parts(c, K, n_kv, hb + 2 * n_q, consts + 9);
+        pv = at_make_parts(c, V, n_kv, hb + 2 * n_q + 2 * n_kv, consts + 10);
+        at_consts_kernel<<<1, 1, 0, (cudaStream_t)c->pub.stream>>>(consts, consts + 2, scale);       // only consts[0] is used here
+        c->launches++;
+    }
     bool ok = true;
     double flops = 0;
     void* main_stream = c->pub.stream;
@@ -237,16 +312,19 @@ extern "C" int sb_attention_tc_forward(sb_ctx_t* c, const float* Q, const float*
         flops += 2.0 * Hq * (double)S * S * hd;
         if (ns > 1) c->pub.stream = c->side_stream[b % ns];
         cudaStream_t s = (cudaStream_t)c->pub.stream;
-        float* Sb = Sb0 + (size_t)(b % ns) * n_s;
+        float* Sb = Sb0 + (size_t)(b % ns) * per_stream;
+        __half* P1 = f16 ? (__half*)(Sb + n_s) : nullptr; __half* P2 = f16 ? P1 + n_s : nullptr;
+        const AtParts pp = {P1, P2, consts};
         for (int r = 0; r < g && ok; r++)
             for (int i0 = 0; i0 < Hkv && ok; i0 += G) {
                 const int nb = min(G, Hkv - i0), qh0 = r + i0 * g;
-                ok = ok && at_gemm(c, op_tokens(Q, t0, S, qd, Hq, hd, qh0, g), op_tokens(K, t0, S, kvd, Hkv, hd, i0, 1),
-                                   Sb, Sp, (long)Sp * Sp, S, S, hd, 0, nb, TC_CAUSAL_SKIP_UPPER);
-                at_softmax_rows<<<dim3(S, nb), 256, 0, s>>>(Sb, lse, S, Sp, Hq, qh0, g, t0, scale);
+                ok = ok && at_gemm(c, op_tokens(Q, pq, t0, S, qd, Hq, hd, qh0, g), op_tokens(K, pk, t0, S, kvd, Hkv, hd, i0, 1),
+                                   Sb, Sp, (long)Sp * Sp, S, S, hd, 0, nb, TC_CAUSAL_SKIP_UPPER, nullptr, pq.amax, pk.amax);
+                at_softmax_rows<<<dim3(S, nb), 256, 0, s>>>(Sb, lse, S, Sp, Hq, qh0, g, t0, scale, P1, P2);
                 c->launches++;
-                ok = ok && at_gemm(c, op_scratch(Sb, S, Sp, nb, 0), op_tokens_mn(V, t0, kvd, Hkv, hd, i0, 1),
-                                   O + (size_t)t0 * qd + (size_t)qh0 * hd, qd, (long)g * hd, S, hd, S, 0, nb, TC_CAUSAL_K_UPTO_M);
+                ok = ok && at_gemm(c, op_scratch(Sb, pp, S, Sp, nb, 0), op_tokens_mn(V, pv, t0, kvd, Hkv, hd, i0, 1),
+                                   O + (size_t)t0 * qd + (size_t)qh0 * hd, qd, (long)g * hd, S, hd, S, 0, nb, TC_CAUSAL_K_UPTO_M,
+                                   nullptr, f16 ? consts : nullptr, pv.amax);
             }
     }
     at_join(c, ns, main_stream);
@@ -264,14 +342,35 @@ extern "C" int sb_attention_tc_backward(sb_ctx_t* c, const float* Q, const float
     int Smax = 0;
     for (int b = 0; b < c->h_seq_n; b++) Smax = max(Smax, c->h_seq[b + 1] - c->h_seq[b]);
     const int Sp = round_up(Smax, AT_ROWTILE);
-    const int G = at_group(Sp, 2, Hkv);
+    // FP16 parts (the default GEMM mode): Q, K, V, dO are split once here, P and dS are written as parts by at_ds_rows
+    const bool f16 = at_f16(c, hd);
+    const int G = at_group(Sp, f16 ? 4 : 2, Hkv);
     const size_t n_s = (size_t)G * Sp * Sp;
-    float* D = (float*)sb_gemm_stage(c, 2, ((size_t)T * Hq + 64) * sizeof(float));
-    float* bb = (float*)sb_gemm_stage(c, 3, AT_SIDE * 2 * n_s * sizeof(float));
-    if (!D || !bb) return 1;
+    const size_t per_stream = f16 ? 4 * n_s : 2 * n_s;               // floats: S, dP, then (FP16) the parts of P and of dS
+    const size_t n_q = (size_t)T * qd, n_kv = (size_t)T * kvd;
+    const size_t d_floats = ((size_t)T * Hq + 63) & ~(size_t)63;
+    float* st0 = (float*)sb_gemm_stage(c, 2, (d_floats + 64) * sizeof(float) + (f16 ? (2 * n_q + 2 * n_kv) * 2 * sizeof(__half) : 0));
+    float* bb = (float*)sb_gemm_stage(c, 3, AT_SIDE * per_stream * sizeof(float));
+    if (!st0 || !bb) return 1;
+    float* D = st0;
+    float* consts = st0 + d_floats;                                  // [0] 1.0, [1] dS bound, [2] max |dO row|, [3] max |V row|, [8..11] amax of Q, K, V, dO
+    AtParts pq = AT_NOPARTS, pk = AT_NOPARTS, pv = AT_NOPARTS, pdo = AT_NOPARTS;
+    cudaStream_t s0 = (cudaStream_t)c->pub.stream;
     int tk = sb_tick_begin(c, SB_CLS_ATTN_BWD);
-    at_delta_kernel<<<(T * Hq * 32 + 255) / 256, 256, 0, (cudaStream_t)c->pub.stream>>>(dO, O, D, T * Hq, hd);
+    at_delta_kernel<<<(T * Hq * 32 + 255) / 256, 256, 0, s0>>>(dO, O, D, T * Hq, hd);
     c->launches++;
+    if (f16) {
+        __half* hb = (__half*)(consts + 64);
+        pq = at_make_parts(c, Q, n_q, hb, consts + 8);
+        pk = at_make_parts(c, K, n_kv, hb + 2 * n_q, consts + 9);
+        pv = at_make_parts(c, V, n_kv, hb + 2 * n_q + 2 * n_kv, consts + 10);
+        pdo = at_make_parts(c, dO, n_q, hb + 2 * n_q + 4 * n_kv, consts + 11);
+        cudaMemsetAsync(consts + 2, 0, 2 * sizeof(float), s0);
+        at_rownorm_max_kernel<<<(T * Hq * 32 + 255) / 256, 256, 0, s0>>>(dO, T * Hq, hd, (unsigned*)(consts + 2));
+        at_rownorm_max_kernel<<<(T * Hkv * 32 + 255) / 256, 256, 0, s0>>>(V, T * Hkv, hd, (unsigned*)(consts + 3));
+        at_consts_kernel<<<1, 1, 0, s0>>>(consts, consts + 2, scale);
+        c->launches += 3;
+    }
     bool ok = true;
     double flops = 0;
     void* main_stream = c->pub.stream;
@@ -282,35 +381,40 @@ extern "C" int sb_attention_tc_backward(sb_ctx_t* c, const float* Q, const float
         flops += 5.0 * Hq * (double)S * S * hd;
         if (ns > 1) c->pub.stream = c->side_stream[b % ns];
         cudaStream_t s = (cudaStream_t)c->pub.stream;
-        float* b0 = bb + (size_t)(b % ns) * 2 * n_s; float* b1 = b0 + n_s;
+        float* b0 = bb + (size_t)(b % ns) * per_stream; float* b1 = b0 + n_s;
+        __half* P1 = f16 ? (__half*)(b0 + 2 * n_s) : nullptr; __half* P2 = f16 ? P1 + n_s : nullptr;
+        __half* dS1 = f16 ? P2 + n_s : nullptr; __half* dS2 = f16 ? dS1 + n_s : nullptr;
+        const AtParts pp = {P1, P2, consts}, pds = {dS1, dS2, f16 ? consts + 1 : nullptr};
         for (int r = 0; r < g && ok; r++)
             for (int i0 = 0; i0 < Hkv && ok; i0 += G) {
                 const int nb = min(G, Hkv - i0), qh0 = r + i0 * g;
                 const long sb = (long)Sp * Sp;
-                const int fused = c->attn_fused;
-                if (fused) {
-                    // P = exp(S*scale - lse) and dS = P o (dP - D) * scale come straight out of the two products' epilogues
+                if (c->attn_fused) {
+                    // P = exp(S*scale - lse) and dS = P o (dP - D) * scale come straight out of the two products' epilogues (TF32 parts)
                     const TcEpi e_p = at_epi(TC_EPI_EXP, scale, lse, t0, Hq, qh0, g, nullptr);
                     const TcEpi e_ds = at_epi(TC_EPI_DS, scale, D, t0, Hq, qh0, g, b0);
-                    ok = ok && at_gemm(c, op_tokens(Q, t0, S, qd, Hq, hd, qh0, g), op_tokens(K, t0, S, kvd, Hkv, hd, i0, 1),
+                    ok = ok && at_gemm(c, op_tokens(Q, AT_NOPARTS, t0, S, qd, Hq, hd, qh0, g), op_tokens(K, AT_NOPARTS, t0, S, kvd, Hkv, hd, i0, 1),
                                        b0, Sp, sb, S, S, hd, 0, nb, TC_CAUSAL_SKIP_UPPER, &e_p);                          // P
-                    ok = ok && at_gemm(c, op_tokens(dO, t0, S, qd, Hq, hd, qh0, g), op_tokens(V, t0, S, kvd, Hkv, hd, i0, 1),
+                    ok = ok && at_gemm(c, op_tokens(dO, AT_NOPARTS, t0, S, qd, Hq, hd, qh0, g), op_tokens(V, AT_NOPARTS, t0, S, kvd, Hkv, hd, i0, 1),
                                        b1, Sp, sb, S, S, hd, 0, nb, TC_CAUSAL_SKIP_UPPER, &e_ds);                         // dS
                 } else {
-                    ok = ok && at_gemm(c, op_tokens(Q, t0, S, qd, Hq, hd, qh0, g), op_tokens(K, t0, S, kvd, Hkv, hd, i0, 1),
-                                       b0, Sp, sb, S, S, hd, 0, nb, TC_CAUSAL_SKIP_UPPER);                                // S
-                    ok = ok && at_gemm(c, op_tokens(dO, t0, S, qd, Hq, hd, qh0, g), op_tokens(V, t0, S, kvd, Hkv, hd, i0, 1),
-                                       b1, Sp, sb, S, S, hd, 0, nb, TC_CAUSAL_SKIP_UPPER);                                // dP
-                    at_ds_rows<<<dim3(S, nb), 256, 0, s>>>(b0, b1, lse, D, S, Sp, Hq, qh0, g, t0, scale);                // P -> b0, dS -> b1
+                    ok = ok && at_gemm(c, op_tokens(Q, pq, t0, S, qd, Hq, hd, qh0, g), op_tokens(K, pk, t0, S, kvd, Hkv, hd, i0, 1),
+                                       b0, Sp, sb, S, S, hd, 0, nb, TC_CAUSAL_SKIP_UPPER, nullptr, pq.amax, pk.amax);     // S
+                    ok = ok && at_gemm(c, op_tokens(dO, pdo, t0, S, qd, Hq, hd, qh0, g), op_tokens(V, pv, t0, S, kvd, Hkv, hd, i0, 1),
+                                       b1, Sp, sb, S, S, hd, 0, nb, TC_CAUSAL_SKIP_UPPER, nullptr, pdo.amax, pv.amax);    // dP
+                    at_ds_rows<<<dim3(S, nb), 256, 0, s>>>(b0, b1, lse, D, S, Sp, Hq, qh0, g, t0, scale, P1, P2, dS1, dS2, consts + 1);   // P, dS
                     c->launches++;
                 }
                 const int acc = (r > 0 || accumulate_kv) ? 1 : 0;
-                ok = ok && at_gemm(c, op_scratch(b1, S, Sp, nb, 0), op_tokens_mn(K, t0, kvd, Hkv, hd, i0, 1),
-                                   dQ + (size_t)t0 * qd + (size_t)qh0 * hd, qd, (long)g * hd, S, hd, S, 0, nb, TC_CAUSAL_K_UPTO_M);   // dQ = dS K
-                ok = ok && at_gemm(c, op_scratch(b0, S, Sp, nb, 1), op_tokens_mn(dO, t0, qd, Hq, hd, qh0, g),
-                                   dV + (size_t)t0 * kvd + (size_t)i0 * hd, kvd, hd, S, hd, S, acc, nb, TC_CAUSAL_K_FROM_M);          // dV += P^T dO
-                ok = ok && at_gemm(c, op_scratch(b1, S, Sp, nb, 1), op_tokens_mn(Q, t0, qd, Hq, hd, qh0, g),
-                                   dK + (size_t)t0 * kvd + (size_t)i0 * hd, kvd, hd, S, hd, S, acc, nb, TC_CAUSAL_K_FROM_M);          // dK += dS^T Q
+                ok = ok && at_gemm(c, op_scratch(b1, pds, S, Sp, nb, 0), op_tokens_mn(K, pk, t0, kvd, Hkv, hd, i0, 1),
+                                   dQ + (size_t)t0 * qd + (size_t)qh0 * hd, qd, (long)g * hd, S, hd, S, 0, nb, TC_CAUSAL_K_UPTO_M,
+                                   nullptr, pds.amax, pk.amax);                                                                       // dQ = dS K
+                ok = ok && at_gemm(c, op_scratch(b0, pp, S, Sp, nb, 1), op_tokens_mn(dO, pdo, t0, qd, Hq, hd, qh0, g),
+                                   dV + (size_t)t0 * kvd + (size_t)i0 * hd, kvd, hd, S, hd, S, acc, nb, TC_CAUSAL_K_FROM_M,
+                                   nullptr, f16 ? consts : nullptr, pdo.amax);                                                        // dV += P^T dO
+                ok = ok && at_gemm(c, op_scratch(b1, pds, S, Sp, nb, 1), op_tokens_mn(Q, pq, t0, qd, Hq, hd, qh0, g),
+                                   dK + (size_t)t0 * kvd + (size_t)i0 * hd, kvd, hd, S, hd, S, acc, nb, TC_CAUSAL_K_FROM_M,
+                                   nullptr, pds.amax, pq.amax);                                                                       // dK += dS^T Q
             }
     }
     at_join(c, ns, main_stream);

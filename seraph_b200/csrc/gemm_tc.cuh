@@ -1121,6 +1121,12 @@ static bool tc_launch(sb_ctx_t* c, const TcProblem& p, int nterms) {
             }
         }
         // narrow outputs (attention's products with V, K, Q, dO: N = head_dim): 256 x 128 tiles
+        if (nterms == 3 && p.amax_a && p.amax_b && p.A.h1 && p.B.h1) switch (lay) {
+            case 0: return tc_launch_t<128, 16, 3, 8, 2, false, false, true, true>(c, p);
+            case 1: return tc_launch_t<128, 16, 3, 8, 2, true, false, true, true>(c, p);
+            case 2: return tc_launch_t<128, 16, 3, 8, 2, false, true, true, true>(c, p);
+            default: return tc_launch_t<128, 16, 3, 8, 2, true, true, true, true>(c, p);
+        }
         if (nterms == 3) switch (lay) {
             case 0: return tc_launch_t<128, 16, 3, 8, 2, false, false>(c, p);
             case 1: return tc_launch_t<128, 16, 3, 8, 2, true, false>(c, p);

@@ -1036,7 +1036,8 @@ static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
         const int num_kb = (p.K + BKE - 1) / BKE;
         // an item's epilogue costs about as much as 160 floats of k (5.3 us against 0.52 us per 16 floats, measured with a
         // K sweep), the fix-up pass about as much as 256; costs below are in tile times
-        const double ovh = 10.0 * 16 / BKE / num_kb, fix = 16.0 * 16 / BKE / num_kb;
+        // (FP16 parts: a stage of 32 k takes 0.27 us, so the same epilogue is worth 20 stages)
+        const double ovh = (F16 ? 20.0 : 10.0 * 16 / BKE) / num_kb, fix = (F16 ? 30.0 : 16.0 * 16 / BKE) / num_kb;
         double best = rem > 0 ? 1.0 + ovh : 0.0;
         for (int s = 2; s <= 8 && rem > 0; s++) {
             const int per = ((num_kb + s - 1) / s + KB_PER_CHUNK - 1) / KB_PER_CHUNK * KB_PER_CHUNK;

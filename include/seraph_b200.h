@@ -169,6 +169,11 @@ int seraph_b200_set_gemm_pair(cuda_train_context_t* ctx, int on);
  * pieces of the k range that fill the machine and are added in a fixed order;
  * 0: whole tiles only. */
 int seraph_b200_set_gemm_tail_split(cuda_train_context_t* ctx, int on);
+/* 1 (default; SERAPH_B200_PARTS_CACHE=0 turns it off): inside one training or evaluation call the FP16 parts of the
+ * weights and of the activations saved for the backward pass are made at their first use and shared by every later
+ * product of the call that reads the same tensor (arena of 4 bytes per element, taken only while an eighth of the
+ * device stays free); 0: every product or run of products prepares its own operands.  Results are identical. */
+int seraph_b200_set_parts_cache(cuda_train_context_t* ctx, int on);
 /* Attention backward on the tensor cores: 0 (default) P and dS are made by a
  * streaming kernel from the stored scores; 1: by the epilogues of the two score
  * products (fewer bytes, but measured slower: the epilogue is what bounds the

@@ -217,6 +217,11 @@ static bool at_gemm(sb_ctx_t* c, const TcOperand& A, const TcOperand& B, float* 
 // FP16 parts of x[n] into h[0..n) and h[n..2n), its largest magnitude into *amax
 static AtParts at_make_parts(sb_ctx_t* c, const float* x, size_t n, __half* h, float* amax) {
     cudaStream_t st = (cudaStream_t)c->pub.stream;
+    void* kept; float* kept_amax; int fresh;
+    if (sb_parts_find(c, x, n, &kept, &kept_amax, &fresh)) {          // q, k, v of a training step: made in the forward pass, read again here
+        h = (__half*)kept; amax = kept_amax;
+        if (!fresh) { AtParts p = {h, h + n, amax}; return p; }
+    }
     cudaMemsetAsync(amax, 0, sizeof(float), st);
     const dim3 pg(tc_ew_blocks(c, n / 4), 1);
     tc_amax_kernel<<<pg, 256, 0, st>>>(x, n / 4, (unsigned*)amax, nullptr, 0, nullptr);

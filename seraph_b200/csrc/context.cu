@@ -81,6 +81,7 @@ cuda_train_context_t* cuda_train_init(int device_id) {
     { const char* e = getenv("SERAPH_B200_GEMM_PAIR"); c->gemm_pair = (e && e[0] == '0') ? 0 : 1; }
     { const char* e = getenv("SERAPH_B200_ATTN_FUSED"); c->attn_fused = (e && e[0] == '1') ? 1 : 0; }
     { const char* e = getenv("SERAPH_B200_GEMM_TAIL_SPLIT"); c->gemm_tail_split = (e && e[0] == '0') ? 0 : 1; }
+    { const char* e = getenv("SERAPH_B200_PARTS_CACHE"); c->parts_cache = (e && e[0] == '0') ? 0 : 1; }
     c->dp_world = 1;
     cuda_train_context_t* p = &c->pub;
     p->device_id = device_id; p->stream = s; p->initialized = 1;
@@ -284,6 +285,13 @@ int seraph_b200_set_gemm_tail_split(cuda_train_context_t* ctx, int on) {
     sb_ctx_t* c = sb_priv(ctx);
     if (!c) return SB_ERR_ARG;
     c->gemm_tail_split = on ? 1 : 0;
+    return SB_OK;
+}
+
+int seraph_b200_set_parts_cache(cuda_train_context_t* ctx, int on) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c) return SB_ERR_ARG;
+    c->parts_cache = on ? 1 : 0;
     return SB_OK;
 }
 

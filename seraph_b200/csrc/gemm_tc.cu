@@ -69,6 +69,100 @@ static int f16_slot(sb_ctx_t* c, const float* x, size_t n, int own, bool* fresh)
     return s;
 }
 
+// ---- step-scoped parts of registered tensors --------------------------------------------------------------------
+// Weights and the activations the forward pass saves for the backward pass are read by several products of one step
+// (a weight by its forward product and by the input gradient; a saved activation by the forward product and by the
+// weight gradient).  The step driver registers them; their parts live in one arena at fixed offsets and are made at
+// the first use inside a step.  Nothing is valid across steps: the caller may write any of these tensors between calls.
+static size_t parts_hash_of(const float* p, int cap) { return (size_t)(((uintptr_t)p >> 8) * 0x9E3779B97F4A7C15ull >> 20) & (size_t)(cap - 1); }
+static void parts_rehash(sb_ctx_t* c) {
+    for (int i = 0; i < c->parts_hash_cap; i++) c->parts_hash[i] = -1;
+    for (int i = 0; i < c->parts_n; i++) {
+        size_t h = parts_hash_of(c->parts_tab[i].ptr, c->parts_hash_cap);
+        while (c->parts_hash[h] >= 0) h = (h + 1) & (size_t)(c->parts_hash_cap - 1);
+        c->parts_hash[h] = i;
+    }
+}
+static void parts_drop_arena(sb_ctx_t* c) {
+    if (c->parts_arena || c->parts_amax) cudaStreamSynchronize((cudaStream_t)c->pub.stream);
+    if (c->parts_arena) cudaFree(c->parts_arena);
+    if (c->parts_amax) cudaFree(c->parts_amax);
+    c->parts_arena = NULL; c->parts_arena_halves = 0; c->parts_amax = NULL; c->parts_amax_cap = 0;
+    c->parts_gen++;
+}
+extern "C" void sb_parts_register(sb_ctx_t* c, int kind, const float* p, size_t n) {
+    if (!p || !n || (n & 7)) return;
+    if (c->parts_n == c->parts_cap) {
+        int cap = c->parts_cap ? 2 * c->parts_cap : 256;
+        sb_parts_entry_t* t = (sb_parts_entry_t*)realloc(c->parts_tab, (size_t)cap * sizeof *t);
+        if (!t) return;
+        c->parts_tab = t; c->parts_cap = cap;
+    }
+    if (2 * (c->parts_n + 1) > c->parts_hash_cap) {
+        int cap = c->parts_hash_cap ? 2 * c->parts_hash_cap : 1024;
+        int* h = (int*)realloc(c->parts_hash, (size_t)cap * sizeof(int));
+        if (!h) return;
+        c->parts_hash = h; c->parts_hash_cap = cap;
+        parts_rehash(c);
+    }
+    sb_parts_entry_t* e = &c->parts_tab[c->parts_n];
+    e->ptr = p; e->n = n; e->cur = 0; e->off = c->parts_total; e->gen = 0; e->kind = kind;
+    c->parts_total += (2 * n + 63) & ~(size_t)63;                    // every tensor's parts start on a 128-byte boundary
+    size_t h = parts_hash_of(p, c->parts_hash_cap);
+    while (c->parts_hash[h] >= 0) h = (h + 1) & (size_t)(c->parts_hash_cap - 1);
+    c->parts_hash[h] = c->parts_n++;
+    if (c->parts_arena) parts_drop_arena(c);                          // laid out again at the next use
+}
+extern "C" void sb_parts_unregister(sb_ctx_t* c, int kind) {
+    int m = 0; size_t total = 0;
+    for (int i = 0; i < c->parts_n; i++) {
+        if (c->parts_tab[i].kind == kind) continue;
+        c->parts_tab[m] = c->parts_tab[i];
+        c->parts_tab[m].off = total; total += (2 * c->parts_tab[m].n + 63) & ~(size_t)63;
+        m++;
+    }
+    if (m == c->parts_n) return;
+    c->parts_n = m; c->parts_total = total;
+    if (c->parts_hash) parts_rehash(c);
+    parts_drop_arena(c);
+}
+extern "C" void sb_parts_open(sb_ctx_t* c) { c->parts_gen++; c->parts_open = 1; }
+extern "C" void sb_parts_close(sb_ctx_t* c) { c->parts_gen++; c->parts_open = 0; }
+extern "C" void sb_parts_free(sb_ctx_t* c) {
+    parts_drop_arena(c);
+    free(c->parts_tab); free(c->parts_hash);
+    c->parts_tab = NULL; c->parts_hash = NULL; c->parts_n = c->parts_cap = c->parts_hash_cap = 0; c->parts_total = 0;
+}
+extern "C" int sb_parts_find(sb_ctx_t* c, const float* x, size_t n, void** hout, float** amax, int* fresh) {
+    if (!c->parts_cache || !c->parts_open || !c->parts_n) return 0;
+    size_t h = parts_hash_of(x, c->parts_hash_cap);
+    int idx;
+    while ((idx = c->parts_hash[h]) >= 0 && c->parts_tab[idx].ptr != x) h = (h + 1) & (size_t)(c->parts_hash_cap - 1);
+    if (idx < 0 || c->parts_tab[idx].n < n || (n & 7)) return 0;          // n below the registered size: a step on fewer tokens
+    if (!c->parts_arena) {
+        // the arena must leave an eighth of the device for the scratch areas that are sized later
+        size_t fr = 0, tot = 0;
+        const size_t bytes = c->parts_total * sizeof(__half);
+        cudaStreamSynchronize((cudaStream_t)c->pub.stream);
+        if (cudaMemGetInfo(&fr, &tot) != cudaSuccess || fr < bytes || fr - bytes < tot / 8 ||
+            cudaMalloc(&c->parts_arena, bytes) != cudaSuccess ||
+            cudaMalloc((void**)&c->parts_amax, (size_t)c->parts_n * sizeof(float)) != cudaSuccess) {
+            cudaGetLastError();
+            if (c->parts_arena) cudaFree(c->parts_arena);
+            c->parts_arena = NULL; c->parts_amax = NULL;
+            c->parts_cache = 0;                                       // does not fit: every product prepares its own operands
+            return 0;
+        }
+        c->parts_arena_halves = c->parts_total; c->parts_amax_cap = c->parts_n;
+    }
+    sb_parts_entry_t* e = &c->parts_tab[idx];
+    *hout = (__half*)c->parts_arena + e->off;
+    *amax = c->parts_amax + idx;
+    *fresh = e->gen != c->parts_gen || e->cur != n;
+    e->gen = c->parts_gen; e->cur = n;
+    return 1;
+}
+
 extern "C" void sb_gemm_keep_begin(sb_ctx_t* c) { c->f16_keep = 1; }
 extern "C" void sb_gemm_keep_end(sb_ctx_t* c) {
     c->f16_keep = 0;
@@ -99,10 +193,12 @@ extern "C" int sb_gemm_tc(sb_ctx_t* c, const float* A, const float* B, float* C,
             // FP16 split: each operand's largest magnitude, then its two FP16 parts (skipped for an operand whose parts are kept)
             const size_t na = (size_t)M * K, nb = (size_t)N * K;
             bool fa = false, fb = false;
-            const int sa = f16_slot(c, A, na, 6, &fa), sb = f16_slot(c, B, nb, 7, &fb);
-            if (sa < 0 || sb < 0) return 1;
-            __half* ha = (__half*)c->f16_slot[sa].h; __half* hb = (__half*)c->f16_slot[sb].h;
-            float* ma = c->d_amax + sa; float* mb = c->d_amax + sb;
+            __half *ha, *hb; float *ma, *mb;
+            void* hv; int fr;
+            if (sb_parts_find(c, A, na, &hv, &ma, &fr)) { ha = (__half*)hv; fa = fr != 0; }
+            else { const int sa = f16_slot(c, A, na, 6, &fa); if (sa < 0) return 1; ha = (__half*)c->f16_slot[sa].h; ma = c->d_amax + sa; }
+            if (sb_parts_find(c, B, nb, &hv, &mb, &fr)) { hb = (__half*)hv; fb = fr != 0; }
+            else { const int sb = f16_slot(c, B, nb, 7, &fb); if (sb < 0) return 1; hb = (__half*)c->f16_slot[sb].h; mb = c->d_amax + sb; }
             if (fa || fb) {
                 cudaStream_t st = (cudaStream_t)c->pub.stream;
                 int tp = sb_tick_begin(c, SB_CLS_GEMM_PREP);

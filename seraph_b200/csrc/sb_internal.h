@@ -49,6 +49,8 @@ typedef struct {
     float *layer_in, *x_norm_attn, *q, *k, *v, *attn_out, *lse, *post_attn_in, *x_norm_ffn, *gate, *up, *ffn_hidden;
 } sb_layer_act_t;
 
+typedef struct { const float* ptr; size_t n, cur, off; unsigned gen; int kind; } sb_parts_entry_t;   /* n: registered floats, cur: floats of the parts held */
+
 typedef struct sb_ctx {
     cuda_train_context_t pub;        /* MUST stay first */
     uint32_t magic;
@@ -59,6 +61,13 @@ typedef struct sb_ctx {
     struct { void* h; size_t cap; const float* ptr; size_t n; unsigned stamp; int valid; } f16_slot[8];   /* FP16 parts of GEMM operands: 0-5 kept across
                                         calls inside a keep region (train_step.c marks runs of GEMMs that share operands), 6-7 for one call */
     int f16_keep; unsigned f16_clock;
+    /* FP16 parts of registered tensors (weights, saved activations), valid from their first use inside a training or
+       evaluation step until that step returns: made once, then shared by every product of the step that reads the tensor */
+    sb_parts_entry_t* parts_tab;
+    int parts_n, parts_cap; int* parts_hash; int parts_hash_cap;
+    size_t parts_total;              /* halves the registered tensors need */
+    void* parts_arena; size_t parts_arena_halves; float* parts_amax; int parts_amax_cap;
+    unsigned parts_gen; int parts_open; int parts_cache;   /* parts_cache 0: off (switch, or the arena did not fit) */
     int attn_fused;                  /* 1: P and dS of the attention backward come out of the score products' epilogues */
     int gemm_tail_split;             /* 1: tiles of the last partial wave are cut into k pieces */
     int gemm_pair;                   /* 1: plain GEMMs run on CTA pairs (cta_group::2), 0: one CTA per tile */
@@ -146,6 +155,14 @@ void sb_seq_index(sb_ctx_t*, const uint32_t* seq_starts, int B, int T, uint32_t*
  * guarantees that no operand array is written inside the region. */
 void sb_gemm_keep_begin(sb_ctx_t*);
 void sb_gemm_keep_end(sb_ctx_t*);
+/* step-scoped FP16 parts of registered tensors: kind 0 = weights, 1 = saved activations */
+void sb_parts_register(sb_ctx_t*, int kind, const float* p, size_t n);
+void sb_parts_unregister(sb_ctx_t*, int kind);
+void sb_parts_open(sb_ctx_t*);
+void sb_parts_close(sb_ctx_t*);
+void sb_parts_free(sb_ctx_t*);
+/* 1: x[n] is registered and the step is open; *h = its two parts (h, h + n), *amax its scale word, *fresh = parts must be made now */
+int sb_parts_find(sb_ctx_t*, const float* x, size_t n, void** h, float** amax, int* fresh);
 void sb_rope2(sb_ctx_t*, float* q, float* k, const uint32_t* pos_ids, int T, int Hq, int Hkv, int hd, float theta, int max_pos, int backward);
 void sb_rope(sb_ctx_t*, const float* in, float* out, const uint32_t* pos_ids, int T, int H, int hd, float theta,
              int max_pos, int backward);

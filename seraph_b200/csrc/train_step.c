@@ -92,6 +92,7 @@ static void free_view_array(cuda_buffer_t** a, int n) { if (!a) return; for (int
 static void free_model(sb_ctx_t* c) {
     cuda_train_context_t* p = &c->pub;
     int L = c->L;
+    sb_parts_unregister(c, 0);
     if (c->W) cudaFree(c->W);
     if (c->G) cudaFree(c->G);
     if (c->M) cudaFree(c->M);
@@ -230,6 +231,14 @@ static int ensure_model(sb_ctx_t* c, const train_state_t* st, int frozen_base) {
         cudaMemsetAsync(c->M, 0, bytes, S(c));
         cudaMemsetAsync(c->Vv, 0, bytes, S(c));
     }
+    sb_parts_register(c, 0, c->W, (size_t)V * d);
+    for (int l = 0; l < L; l++) {
+        const sb_layer_off_t* o = &c->off[l];
+        sb_parts_register(c, 0, c->W + o->q, (size_t)c->qd * d); sb_parts_register(c, 0, c->W + o->k, (size_t)c->kvd * d);
+        sb_parts_register(c, 0, c->W + o->v, (size_t)c->kvd * d); sb_parts_register(c, 0, c->W + o->o, (size_t)c->qd * d);
+        sb_parts_register(c, 0, c->W + o->gate, (size_t)F * d); sb_parts_register(c, 0, c->W + o->up, (size_t)F * d);
+        sb_parts_register(c, 0, c->W + o->down, (size_t)F * d);
+    }
     for_each_tensor(c, st->full_weights, up_tensor, NULL);
     publish_views(c);
     return sb_check(c, cudaStreamSynchronize(S(c)), "weight upload");
@@ -319,6 +328,7 @@ static int ensure_lora(sb_ctx_t* c, const lora_model_t* m) {
 /* activations                                                               */
 /* ------------------------------------------------------------------------ */
 static void free_activations(sb_ctx_t* c) {
+    sb_parts_unregister(c, 1);
     if (c->act_arena) cudaFree(c->act_arena);
     c->act_arena = NULL; c->act_arena_bytes = 0; c->T_cap = 0;
     free(c->act); c->act = NULL;
@@ -355,6 +365,15 @@ static int ensure_activations(sb_ctx_t* c, int T, int need_logits_grad) {
     TAKE(c->g_q, Tq); TAKE(c->g_attn, Tq); TAKE(c->g_k, Tkv); TAKE(c->g_v, Tkv);
     TAKE(c->g_ffn, TF); TAKE(c->g_gate, TF); TAKE(c->g_up, TF);
 #undef TAKE
+    /* operands of more than one product per step, written once by the forward pass */
+    for (int l = 0; l < c->L; l++) {
+        const sb_layer_act_t* a = &c->act[l];
+        sb_parts_register(c, 1, a->x_norm_attn, (size_t)T * c->d); sb_parts_register(c, 1, a->x_norm_ffn, (size_t)T * c->d);
+        sb_parts_register(c, 1, a->attn_out, (size_t)T * c->qd); sb_parts_register(c, 1, a->ffn_hidden, (size_t)T * c->F);
+        sb_parts_register(c, 1, a->q, (size_t)T * c->qd); sb_parts_register(c, 1, a->k, (size_t)T * c->kvd);
+        sb_parts_register(c, 1, a->v, (size_t)T * c->kvd);
+    }
+    sb_parts_register(c, 1, c->hidden_norm, (size_t)T * c->d);
     return 0;
 }
 
@@ -533,7 +552,7 @@ static float lr_for_step(const train_state_t* st, int accum) {
     return lr / accum;
 }
 
-static float step_common(train_state_t* st, int* tokens, int T, int* seq_starts, int B, cuda_train_context_t* ctx, int full, int train, int resident) {
+static float step_body(train_state_t* st, int* tokens, int T, int* seq_starts, int B, cuda_train_context_t* ctx, int full, int train, int resident) {
     sb_ctx_t* c = sb_priv(ctx);
     if (!st || !st->config || !c || T <= 0 || B <= 0) return -1.0f;
     if (!resident && (!tokens || !seq_starts)) return -1.0f;
@@ -601,6 +620,15 @@ static float step_common(train_state_t* st, int* tokens, int T, int* seq_starts,
     float loss = *h_loss / (float)num_valid;
     if (train && st->debug_nan_check && (isnan(loss) || isinf(loss))) { st->nan_detected = 1; return NAN; }
     return loss;
+}
+
+/* prepared operand parts of weights and saved activations are shared by the products of one call and dropped when it returns */
+static float step_common(train_state_t* st, int* tokens, int T, int* seq_starts, int B, cuda_train_context_t* ctx, int full, int train, int resident) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (c) sb_parts_open(c);
+    float r = step_body(st, tokens, T, seq_starts, B, ctx, full, train, resident);
+    if (c) sb_parts_close(c);
+    return r;
 }
 
 float cuda_train_step_gpu_full_batch(train_state_t* state, int* tokens_packed, int total_tokens, int* seq_starts, int batch_size,
@@ -754,6 +782,7 @@ void cuda_train_free(cuda_train_context_t* ctx) {
         for (int i = 0; i < 5; i++) cudaEventDestroy((cudaEvent_t)c->side_ev[i]);
     }
     if (c->rope_tab) cudaFree(c->rope_tab);
+    sb_parts_free(c);
     if (c->d_amax) cudaFree(c->d_amax);
     for (int i = 0; i < 8; i++) if (c->f16_slot[i].h) cudaFree(c->f16_slot[i].h);
     if (c->d_status) cudaFree(c->d_status);

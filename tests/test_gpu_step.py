@@ -191,6 +191,34 @@ def test_c1_step_matches_oracle(ctx):
         print("C1 worst gradient rel-L2, GEMM mode", mode, ":", worst)
 
 
+def test_operand_parts_kept_within_a_step_change_nothing(ctx):
+    """The FP16 parts of weights and saved activations are made once per call and shared by the call's products.  Three
+    optimizer steps (the weights move between them), then a step on fewer tokens and one on the full batch again: losses,
+    gradients and weights are bit-identical to the run in which every product prepares its own operands."""
+    from seraph_b200 import api
+    cfg = C1
+    p = cfg.init_params(77)
+    ss = list(range(0, 2049, 256))
+    tok = tokens_for(cfg, 2048, 5)
+    runs = []
+    for keep in (1, 0):
+        ctx.set_parts_cache(keep)
+        ctx.lib.seraph_b200_reset_model(ctx.h)
+        st = api.TrainState(cfg, p, lr=1e-2)
+        losses = [api.step_full_batch(ctx, st, tok, ss) for _ in range(3)]
+        losses.append(api.step_full_batch(ctx, st, np.ascontiguousarray(tok[:1024]), ss[:5]))
+        losses.append(api.step_full_batch(ctx, st, tok, ss))
+        ctx.check()
+        ctx.lib.cuda_download_gpu_gradients(ctx.h, st.h)
+        ctx.lib.cuda_download_full_weights(ctx.h, st.h)
+        runs.append((losses, st.get(1), st.get(0)))
+        st.close()
+    ctx.set_parts_cache(1)
+    assert runs[0][0] == runs[1][0], (runs[0][0], runs[1][0])
+    assert np.array_equal(runs[0][1], runs[1][1]) and np.array_equal(runs[0][2], runs[1][2])
+    assert runs[0][0][0] != runs[0][0][2]          # the weights did move
+
+
 def test_golden_reference_cuda_vectors(ctx):
     """Gradients written by the reference's own CUDA backend on a B200
     (tests/golden/make_golden_refcuda.py).  Its float atomics make it

@@ -174,6 +174,10 @@ int seraph_b200_set_gemm_tail_split(cuda_train_context_t* ctx, int on);
  * product of the call that reads the same tensor (arena of 4 bytes per element, taken only while an eighth of the
  * device stays free); 0: every product or run of products prepares its own operands.  Results are identical. */
 int seraph_b200_set_parts_cache(cuda_train_context_t* ctx, int on);
+/* Attention forward of 128-wide heads in the default GEMM mode: 1 = one kernel per call that keeps the scores in
+ * tensor memory and the probabilities in shared memory (online softmax, no score-sized scratch); 0 = score product,
+ * row softmax and value product as separate launches over a score scratch.  SERAPH_B200_ATTN_FLASH sets the default. */
+int seraph_b200_set_attn_flash(cuda_train_context_t* ctx, int on);
 /* Attention backward on the tensor cores: 0 (default) P and dS are made by a
  * streaming kernel from the stored scores; 1: by the epilogues of the two score
  * products (fewer bytes, but measured slower: the epilogue is what bounds the

@@ -290,8 +290,9 @@ extern "C" int sb_attention_tc_forward(sb_ctx_t* c, const float* Q, const float*
     const int G = at_group(Sp, f16 ? 2 : 1, Hkv);
     const size_t n_s = (size_t)G * Sp * Sp;
     const size_t per_stream = f16 ? 2 * n_s : n_s;                   // floats: S, then (FP16) the two parts of P
-    float* Sb0 = (float*)sb_gemm_stage(c, 3, AT_SIDE * per_stream * sizeof(float));
-    if (!Sb0) return 1;
+    const bool one_kernel = f16 && c->attn_flash && hd == 128 && c->h_seq_n <= 240;      // no score scratch at all
+    float* Sb0 = one_kernel ? nullptr : (float*)sb_gemm_stage(c, 3, AT_SIDE * per_stream * sizeof(float));
+    if (!Sb0 && !one_kernel) return 1;
     const size_t n_q = (size_t)T * qd, n_kv = (size_t)T * kvd;
     AtParts pq = AT_NOPARTS, pk = AT_NOPARTS, pv = AT_NOPARTS;
     float* consts = nullptr;
@@ -304,6 +305,16 @@ extern "C" int sb_attention_tc_forward(sb_ctx_t* c, const float* Q, const float*
         pq = at_make_parts(c, Q, n_q, hb, consts + 8);
         pk = at_make_parts(c, K, n_kv, hb + 2 * n_q, consts + 9);
         pv = at_make_parts(c, V, n_kv, hb + 2 * n_q + 2 * n_kv, consts + 10);
+        if (one_kernel) {
+            double fl = 0;
+            for (int b = 0; b < c->h_seq_n; b++) { const double S = c->h_seq[b + 1] - c->h_seq[b]; fl += 2.0 * Hq * S * S * hd; }
+            if (sb_attention_fused_forward(c, pq.h1, pq.h2, pk.h1, pk.h2, pv.h1, pv.h2, pq.amax, pk.amax, pv.amax, O, lse, T, Hq, Hkv, hd) == 0) {
+                sb_tick_end(c, tk, fl, 0.0);
+                return 0;
+            }
+            Sb0 = (float*)sb_gemm_stage(c, 3, AT_SIDE * per_stream * sizeof(float));
+            if (!Sb0) { sb_tick_end(c, tk, 0.0, 0.0); return 1; }
+        }
         at_consts_kernel<<<1, 1, 0, (cudaStream_t)c->pub.stream>>>(consts, consts + 2, scale);       // only consts[0] is used here
         c->launches++;
     }
@@ -402,6 +413,10 @@ extern "C" int sb_attention_tc_backward(sb_ctx_t* c, const float* Q, const float
                                        b0, Sp, sb, S, S, hd, 0, nb, TC_CAUSAL_SKIP_UPPER, &e_p);                          // P
                     ok = ok && at_gemm(c, op_tokens(dO, AT_NOPARTS, t0, S, qd, Hq, hd, qh0, g), op_tokens(V, AT_NOPARTS, t0, S, kvd, Hkv, hd, i0, 1),
                                        b1, Sp, sb, S, S, hd, 0, nb, TC_CAUSAL_SKIP_UPPER, &e_ds);                         // dS
+                } else if (f16 && c->attn_flash && hd == 128 &&
+                           sb_attention_fused_scores(c, pq.h1, pq.h2, pdo.h1, pdo.h2, pk.h1, pk.h2, pv.h1, pv.h2, pq.amax, pk.amax, pv.amax, pdo.amax,
+                                                     consts + 1, lse, D, P1, P2, dS1, dS2, t0, S, Sp, T, Hq, Hkv, hd, qh0, g, nb) == 0) {
+                    // S, dP, P and dS in one kernel: only the parts of P and dS reach memory
                 } else {
                     ok = ok && at_gemm(c, op_tokens(Q, pq, t0, S, qd, Hq, hd, qh0, g), op_tokens(K, pk, t0, S, kvd, Hkv, hd, i0, 1),
                                        b0, Sp, sb, S, S, hd, 0, nb, TC_CAUSAL_SKIP_UPPER, nullptr, pq.amax, pk.amax);     // S

@@ -68,6 +68,7 @@ typedef struct sb_ctx {
     size_t parts_total;              /* halves the registered tensors need */
     void* parts_arena; size_t parts_arena_halves; float* parts_amax; int parts_amax_cap;
     unsigned parts_gen; int parts_open; int parts_cache;   /* parts_cache 0: off (switch, or the arena did not fit) */
+    int attn_flash;                  /* 1: attention forward of 128-wide heads runs as one kernel (no score scratch) */
     int attn_fused;                  /* 1: P and dS of the attention backward come out of the score products' epilogues */
     int gemm_tail_split;             /* 1: tiles of the last partial wave are cut into k pieces */
     int gemm_pair;                   /* 1: plain GEMMs run on CTA pairs (cta_group::2), 0: one CTA per tile */
@@ -193,6 +194,12 @@ void sb_copy(sb_ctx_t*, void* dst, const void* src, size_t bytes);
 /* host copy of the sequence boundaries of the batch the index tables describe */
 int  sb_set_host_seq(sb_ctx_t* c, const int* starts, int B);
 /* tensor-core attention (attention_tc.cu); nonzero = not eligible, caller uses the CUDA-core kernels */
+int  sb_attention_fused_forward(sb_ctx_t*, const void* q1, const void* q2, const void* k1, const void* k2, const void* v1, const void* v2,
+                                const float* amax_q, const float* amax_k, const float* amax_v, float* O, float* lse, int T, int Hq, int Hkv, int hd);
+int  sb_attention_fused_scores(sb_ctx_t*, const void* q1, const void* q2, const void* do1, const void* do2, const void* k1, const void* k2,
+                               const void* v1, const void* v2, const float* amax_q, const float* amax_k, const float* amax_v, const float* amax_do,
+                               const float* ds_bound, const float* lse, const float* D, void* P1, void* P2, void* dS1, void* dS2,
+                               int t0, int S, int Sp, int T, int Hq, int Hkv, int hd, int head0, int head_step, int nb);
 int  sb_attention_tc_forward(sb_ctx_t*, const float* Q, const float* K, const float* V, float* O, float* lse, int T, int Hq, int Hkv, int hd);
 int  sb_attention_tc_backward(sb_ctx_t*, const float* Q, const float* K, const float* V, const float* O, const float* lse, const float* dO,
                               float* dQ, float* dK, float* dV, int accumulate_kv, int T, int Hq, int Hkv, int hd);

@@ -190,6 +190,46 @@ def test_attention_forward_backward(ctx, ss, Hq, Hkv, hd, fused):
     ctx.release(bq, bk, bv, bdo, bs, bout, blse, bdq, bdk, bdv, bdk2, bdv2)
 
 
+@pytest.mark.parametrize("flash", [1, 0])
+@pytest.mark.parametrize("ss,Hq,Hkv", [([0, 257], 4, 1), ([0, 1024], 4, 1), ([0, 100, 420, 1000], 4, 2), ([0, 1, 130, 131, 450], 2, 2),
+                                       ([0, 2048, 2100], 6, 3)])
+def test_attention_head128_one_kernel_paths(ctx, ss, Hq, Hkv, flash):
+    """Head size 128, default GEMM mode.  flash = 1: the forward is one kernel (scores in tensor memory, online softmax)
+    and the backward's S, dP, P, dS come from one kernel that writes only the FP16 parts of P and dS; flash = 0: a launch
+    per product over a score scratch.  Both against the oracle, and bit-reproducible."""
+    hd = 128
+    ss = np.array(ss, np.uint32)
+    T, B = int(ss[-1]), len(ss) - 1
+    r = rng(T + Hq)
+    Q, K, V = f32(r.standard_normal((T, Hq * hd))), f32(r.standard_normal((T, Hkv * hd))), f32(r.standard_normal((T, Hkv * hd)))
+    dO = f32(r.standard_normal((T, Hq * hd)))
+    out_ref, lse_ref = np.empty_like(Q), np.empty((T, Hq), np.float32)
+    O.lib().ref_attention(Q, K, V, out_ref, lse_ref, ss, T, B, Hq, Hkv, hd)
+    dQ_ref, dK_ref, dV_ref = np.empty_like(Q), np.zeros_like(K), np.zeros_like(V)
+    O.lib().ref_attention_backward(Q, K, V, dO, dQ_ref, dK_ref, dV_ref, ss, T, B, Hq, Hkv, hd)
+    bq, bk, bv, bdo, bs = ctx.upload(Q), ctx.upload(K), ctx.upload(V), ctx.upload(dO), ctx.upload(ss)
+    ctx.set_attn_flash(flash)
+    runs = []
+    for rep in range(2):
+        bout, blse = ctx.zeros(Q.size), ctx.zeros(T * Hq)
+        bdq, bdk, bdv = ctx.empty(Q.size), ctx.zeros(K.size), ctx.zeros(V.size)
+        n0 = ctx.launches()
+        ctx.lib.cuda_train_batch_attention_packed(ctx.h, bq.b, bk.b, bv.b, bout.b, blse.b, bs.b, T, B, Hq, Hkv, hd, int(np.diff(ss).max()))
+        ctx.check()
+        if flash:
+            assert ctx.launches() - n0 <= 8      # three operand preparations and the one kernel, not a launch per product
+        ctx.lib.cuda_train_batch_attention_backward_packed(ctx.h, bq.b, bk.b, bv.b, bout.b, blse.b, bdo.b, bdq.b, bdk.b, bdv.b, bs.b,
+                                                           T, B, Hq, Hkv, hd, int(np.diff(ss).max()))
+        ctx.check()
+        runs.append([x.numpy() for x in (bout, blse, bdq, bdk, bdv)])
+        ctx.release(bout, blse, bdq, bdk, bdv)
+    ctx.set_attn_flash(1)
+    errs = [rel_l2(a, b) for a, b in zip(runs[0], (out_ref, lse_ref, dQ_ref, dK_ref, dV_ref))]
+    assert max(errs) < TOL, errs
+    assert all(np.array_equal(a, b) for a, b in zip(runs[0], runs[1]))
+    ctx.release(bq, bk, bv, bdo, bs)
+
+
 def test_attention_unpacked_single_sequence(ctx):
     T, Hq, Hkv, hd = 70, 4, 4, 32
     r = rng(70)

@@ -51,6 +51,55 @@ __device__ __forceinline__ void af_arrive(uint64_t* bar) {
 __device__ __forceinline__ uint32_t af_pack_h2(__half a, __half b) {
     return (uint32_t)__half_as_ushort(a) | ((uint32_t)__half_as_ushort(b) << 16);
 }
+// tensor-memory load of 32 columns without the wait, and the wait for all loads issued so far; the registers of the loads
+// go through the wait as operands so that nothing that reads them is scheduled ahead of it
+__device__ __forceinline__ void af_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+}
+#define AF_REGS32(r) "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), \
+                     "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), \
+                     "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), \
+                     "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+__device__ __forceinline__ void af_ld_wait(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : AF_REGS32(r) :: "memory");
+}
+__device__ __forceinline__ void af_ld_dep(uint32_t (&r)[32]) { asm volatile("" : AF_REGS32(r) :: "memory"); }
+
+__device__ __forceinline__ float af_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+// two values as FP16 parts: hi = the packed roundings of (x0, x1), lo = the packed roundings of what the roundings left
+__device__ __forceinline__ void af_split2(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+    const __half2 h = __floats2half2_rn(x0, x1);
+    const float2 b = __half22float2(h);
+    const __half2 l = __floats2half2_rn(x0 - b.x, x1 - b.y);
+    hi = *(const uint32_t*)&h; lo = *(const uint32_t*)&l;
+}
+
+// 4 x 4 transpose of 16-byte chunks among the four lanes of a quad: afterwards w[t] of lane c is what w[c] of lane t was
+__device__ __forceinline__ uint4 af_shfl_xor4(uint4 v, int m) {
+    v.x = __shfl_xor_sync(0xffffffffu, v.x, m); v.y = __shfl_xor_sync(0xffffffffu, v.y, m);
+    v.z = __shfl_xor_sync(0xffffffffu, v.z, m); v.w = __shfl_xor_sync(0xffffffffu, v.w, m);
+    return v;
+}
+__device__ __forceinline__ void af_quad_transpose(uint4 (&w)[4], int lane) {
+    const bool hi = (lane & 2) != 0, odd = (lane & 1) != 0;
+#pragma unroll
+    for (int s2 = 0; s2 < 2; s2++) {
+        const uint4 recv = af_shfl_xor4(hi ? w[s2] : w[s2 + 2], 2);
+        if (hi) w[s2] = recv; else w[s2 + 2] = recv;
+    }
+#pragma unroll
+    for (int s2 = 0; s2 < 4; s2 += 2) {
+        const uint4 recv = af_shfl_xor4(odd ? w[s2] : w[s2 + 1], 1);
+        if (odd) w[s2] = recv; else w[s2 + 1] = recv;
+    }
+}
 
 __global__ void __launch_bounds__(AF_THREADS, 1)
 at_fused_fwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant__ CUtensorMap mQ2,
@@ -216,16 +265,17 @@ at_fused_fwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_consta
             ok = mbar_wait(&s_full[s], u & 1);
             if (!ok) break;
             tc_fence_after();
-            float y[64];
+            float y[64];                                        // raw scores (the two accumulators added)
             {
                 const uint32_t ta = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(s * 128);
                 uint32_t a[32], c[32];
 #pragma unroll
                 for (int hh = 0; hh < 2; hh++) {
-                    tc_ld32(ta + hh * 32, a);
-                    tc_ld32(ta + 64 + hh * 32, c);
+                    af_ld32_issue(ta + hh * 32, a);
+                    af_ld32_issue(ta + 64 + hh * 32, c);
+                    af_ld_wait(a); af_ld_dep(c);
 #pragma unroll
-                    for (int i = 0; i < 32; i++) y[hh * 32 + i] = (__uint_as_float(a[i]) + __uint_as_float(c[i])) * cs;
+                    for (int i = 0; i < 32; i++) y[hh * 32 + i] = __uint_as_float(a[i]) + __uint_as_float(c[i]);
                 }
             }
             tc_fence_before();
@@ -236,15 +286,17 @@ at_fused_fwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_consta
 #pragma unroll
                 for (int i = 0; i < 64; i++) if (k0 + i > qi) y[i] = -INFINITY;
             }
-            float mx = y[0];
+            float mx4[4] = {y[0], y[1], y[2], y[3]};
 #pragma unroll
-            for (int i = 1; i < 64; i++) mx = fmaxf(mx, y[i]);
+            for (int i = 4; i < 64; i++) mx4[i & 3] = fmaxf(mx4[i & 3], y[i]);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * cs;      // cs > 0
             const float m_new = fmaxf(m, mx);                 // finite from block 0 on: key 0 counts for every row
-            const float alpha = exp2f(m - m_new);
-            float sum = 0.f;
+            const float alpha = af_ex2(m - m_new);
+            const float off = 14.f - m_new;                   // P leaves as P * 2^14
+            float sm4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < 64; i++) { y[i] = exp2f(y[i] - m_new); sum += y[i]; }
-            l = l * alpha + sum;
+            for (int i = 0; i < 64; i++) { y[i] = af_ex2(fmaf(y[i], cs, off)); sm4[i & 3] += y[i]; }
+            l = l * alpha + ((sm4[0] + sm4[1]) + (sm4[2] + sm4[3]));          // in units of 2^-14
             m = m_new;
             // alpha to the O warps (the slot was last read for block j - 2)
             ok = mbar_wait(&pv_empty[s], (u & 1) ^ 1);
@@ -260,10 +312,7 @@ at_fused_fwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_consta
                 uint32_t w1[4], w2[4];
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
-                    const float x0 = y[c8 * 8 + 2 * e] * 16384.f, x1 = y[c8 * 8 + 2 * e + 1] * 16384.f;
-                    const __half h0 = __float2half_rn(x0), h1 = __float2half_rn(x1);
-                    w1[e] = af_pack_h2(h0, h1);
-                    w2[e] = af_pack_h2(__float2half_rn(x0 - __half2float(h0)), __float2half_rn(x1 - __half2float(h1)));
+                    af_split2(y[c8 * 8 + 2 * e], y[c8 * 8 + 2 * e + 1], w1[e], w2[e]);
                 }
                 const int off = ((c8 ^ (r & 7)) << 4);
                 *(uint4*)(prow + off) = make_uint4(w1[0], w1[1], w1[2], w1[3]);
@@ -275,7 +324,7 @@ at_fused_fwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_consta
         }
         if (ok) {
             fin_s[r] = l > 0.f ? 1.0f / l : 0.f;
-            if (lse && qi < S) lse[(size_t)(t0 + qi) * Hq + h] = (m + log2f(l)) * 0.6931471805599453f;
+            if (lse && qi < S) lse[(size_t)(t0 + qi) * Hq + h] = (m + log2f(l) - 14.f) * 0.6931471805599453f;
         }
         __syncwarp();
         if (lane == 0) af_arrive(fin_full);
@@ -294,12 +343,13 @@ at_fused_fwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_consta
             tc_fence_after();
             const float alpha = alpha_s[s * 128 + r];
             const uint32_t ta = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(256 + s * 128 + ch * 64);
+            {
+                uint32_t t[32], t2[32];
+                af_ld32_issue(ta, t);
+                af_ld32_issue(ta + 32, t2);
+                af_ld_wait(t); af_ld_dep(t2);
 #pragma unroll
-            for (int hh = 0; hh < 2; hh++) {
-                uint32_t t[32];
-                tc_ld32(ta + hh * 32, t);
-#pragma unroll
-                for (int i = 0; i < 32; i++) o[hh * 32 + i] = fmaf(o[hh * 32 + i], alpha, __uint_as_float(t[i]));
+                for (int i = 0; i < 32; i++) { o[i] = fmaf(o[i], alpha, __uint_as_float(t[i])); o[32 + i] = fmaf(o[32 + i], alpha, __uint_as_float(t2[i])); }
             }
             tc_fence_before();
             __syncwarp();
@@ -307,7 +357,7 @@ at_fused_fwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_consta
         }
         if (ok) ok = mbar_wait(fin_full, 0);
         if (ok && qi < S) {
-            const float f = fin_s[r] * (1.0f / 16384.f) * tc_pow2(-tc_f16_shift(__ldg(amax_v)));
+            const float f = fin_s[r] * tc_pow2(-tc_f16_shift(__ldg(amax_v)));      // fin = 2^14 / l, O holds P * 2^14 products
             float4* dst = (float4*)(O + (size_t)(t0 + qi) * qd + (size_t)h * AF_HD + ch * 64);
 #pragma unroll
             for (int i = 0; i < 16; i++) dst[i] = make_float4(o[4 * i] * f, o[4 * i + 1] * f, o[4 * i + 2] * f, o[4 * i + 3] * f);
@@ -466,10 +516,11 @@ at_score_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_consta
         const bool live = qi < S;
         const float cs = tc_pow2(-tc_f16_shift(__ldg(amax_q))) * tc_pow2(-tc_f16_shift(__ldg(amax_k))) * (scale * 1.4426950408889634f);
         const float cp = tc_pow2(-tc_f16_shift(__ldg(amax_do))) * tc_pow2(-tc_f16_shift(__ldg(amax_v)));
-        const float dsc = tc_pow2(tc_f16_shift(__ldg(ds_bound))) * scale;
+        const float dsc = tc_pow2(tc_f16_shift(__ldg(ds_bound))) * scale * (1.0f / 16384.f);      // pr holds P * 2^14
         const float L2 = live ? lse[(size_t)(t0 + qi) * Hq + h] * 1.4426950408889634f : 0.f;
         const float Dq = live ? D[(size_t)(t0 + qi) * Hq + h] : 0.f;
-        const size_t rowbase = ((size_t)hb * Sp + qi) * Sp + half * 32;
+        // after the transpose: lane (a, c) = (lane / 4, lane % 4) writes chunk c of the warp's rows 4a + t, t = 0..3
+        const size_t qrowbase = ((size_t)hb * Sp + (size_t)(qb * AF_BQ + q * 32 + 4 * (lane >> 2))) * Sp + half * 32 + (lane & 3) * 8;
         for (int j = 0; j < nz && ok; j++) {
             uint4 w[4][4];                                      // P1, P2, dS1, dS2: 32 halfs each
             if (j < nkv) {
@@ -481,33 +532,30 @@ at_score_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_consta
                 float pr[32];
                 {
                     uint32_t a[32], c[32];
-                    tc_ld32(ta, a);
-                    tc_ld32(ta + 64, c);
-                    const int k0 = j * AF_BKV + half * 32;
-#pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        const float y = (__uint_as_float(a[i]) + __uint_as_float(c[i])) * cs;
-                        pr[i] = (live && k0 + i <= qi) ? exp2f(y - L2) : 0.f;
-                    }
-                    tc_ld32(ta + 128, a);
-                    tc_ld32(ta + 192, c);
+                    uint32_t a2[32], c2[32];
+                    af_ld32_issue(ta, a);
+                    af_ld32_issue(ta + 64, c);
+                    af_ld32_issue(ta + 128, a2);
+                    af_ld32_issue(ta + 192, c2);
+                    af_ld_wait(a); af_ld_dep(c); af_ld_dep(a2); af_ld_dep(c2);
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) af_arrive(&acc_empty[s]);
+                    const int k0 = j * AF_BKV + half * 32;
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        const float y = fmaf(__uint_as_float(a[i]) + __uint_as_float(c[i]), cs, 14.f - L2);
+                        pr[i] = (live && k0 + i <= qi) ? af_ex2(y) : 0.f;                   // P * 2^14
+                    }
                     uint32_t* w0 = (uint32_t*)&w[0][0]; uint32_t* w1 = (uint32_t*)&w[1][0];
                     uint32_t* w2 = (uint32_t*)&w[2][0]; uint32_t* w3 = (uint32_t*)&w[3][0];
 #pragma unroll
                     for (int e = 0; e < 16; e++) {
                         const float p0 = pr[2 * e], p1 = pr[2 * e + 1];
-                        const float d0 = p0 * ((__uint_as_float(a[2 * e]) + __uint_as_float(c[2 * e])) * cp - Dq) * dsc;
-                        const float d1 = p1 * ((__uint_as_float(a[2 * e + 1]) + __uint_as_float(c[2 * e + 1])) * cp - Dq) * dsc;
-                        const float x0 = p0 * 16384.f, x1 = p1 * 16384.f;
-                        const __half h0 = __float2half_rn(x0), h1 = __float2half_rn(x1);
-                        w0[e] = af_pack_h2(h0, h1);
-                        w1[e] = af_pack_h2(__float2half_rn(x0 - __half2float(h0)), __float2half_rn(x1 - __half2float(h1)));
-                        const __half g0 = __float2half_rn(d0), g1 = __float2half_rn(d1);
-                        w2[e] = af_pack_h2(g0, g1);
-                        w3[e] = af_pack_h2(__float2half_rn(d0 - __half2float(g0)), __float2half_rn(d1 - __half2float(g1)));
+                        const float d0 = p0 * ((__uint_as_float(a2[2 * e]) + __uint_as_float(c2[2 * e])) * cp - Dq) * dsc;
+                        const float d1 = p1 * ((__uint_as_float(a2[2 * e + 1]) + __uint_as_float(c2[2 * e + 1])) * cp - Dq) * dsc;
+                        af_split2(p0, p1, w0[e], w1[e]);
+                        af_split2(d0, d1, w2[e], w3[e]);
                     }
                 }
             } else {
@@ -516,10 +564,18 @@ at_score_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_consta
 #pragma unroll
                     for (int i = 0; i < 4; i++) w[a][i] = make_uint4(0, 0, 0, 0);
             }
-            const size_t o = rowbase + (size_t)j * AF_BKV;
-            uint4* o0 = (uint4*)(P1 + o); uint4* o1 = (uint4*)(P2 + o); uint4* o2 = (uint4*)(dS1 + o); uint4* o3 = (uint4*)(dS2 + o);
+            // A lane holds 64 bytes of its own row per array; lanes 4a..4a+3 transpose their 4 x 4 chunks of 16 bytes so that one
+            // store instruction writes whole 64-byte row pieces (8 rows) instead of one chunk in each of 32 rows.
+            if (j < nkv) {
 #pragma unroll
-            for (int i = 0; i < 4; i++) { o0[i] = w[0][i]; o1[i] = w[1][i]; o2[i] = w[2][i]; o3[i] = w[3][i]; }
+                for (int a = 0; a < 4; a++) af_quad_transpose(w[a], lane);
+            }
+            const size_t o = qrowbase + (size_t)j * AF_BKV;
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+                const size_t ot = o + (size_t)t * Sp;
+                *(uint4*)(P1 + ot) = w[0][t]; *(uint4*)(P2 + ot) = w[1][t]; *(uint4*)(dS1 + ot) = w[2][t]; *(uint4*)(dS2 + ot) = w[3][t];
+            }
         }
         if (!ok && lane == 0) atomicExch(status, SB_ERR_TIMEOUT);
     }

@@ -139,13 +139,38 @@ __global__ void __launch_bounds__(256) at_ds_rows(float* __restrict__ buf_s, flo
 
 // largest row norm of x[n_rows, hd] (one warp per row), as float bits through an integer atomicMax; out zeroed before
 __global__ void at_rownorm_max_kernel(const float* __restrict__ x, int n_rows, int hd, unsigned* __restrict__ out) {
-    int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (w >= n_rows) return;
-    const float* a = x + (size_t)w * hd;
-    float s = 0.f;
-    for (int d = lane; d < hd; d += 32) s += a[d] * a[d];
-    s = warp_sum_f(s);
-    if (lane == 0) atomicMax(out, __float_as_uint(sqrtf(s)));
+    const int lane = threadIdx.x & 31, nwarps = (gridDim.x * blockDim.x) >> 5;
+    int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    float best = 0.f;
+    if (hd == 128) {
+        // four rows of 32 float4 per pass and warp, all loads in flight together
+        for (int r0 = w * 4; r0 < n_rows; r0 += nwarps * 4) {
+            float s[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                s[i] = 0.f;
+                if (r0 + i < n_rows) {
+                    const float4 v = __ldg((const float4*)(x + (size_t)(r0 + i) * 128) + lane);
+                    s[i] = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) best = fmaxf(best, warp_sum_f(s[i]));
+        }
+    } else {
+        for (; w < n_rows; w += nwarps) {
+            const float* a = x + (size_t)w * hd;
+            float s = 0.f;
+            for (int d = lane; d < hd; d += 32) s += a[d] * a[d];
+            best = fmaxf(best, warp_sum_f(s));
+        }
+    }
+    if (lane == 0 && best > 0.f) atomicMax(out, __float_as_uint(sqrtf(best)));
+}
+static inline int at_rn_blocks(sb_ctx_t* c, int n_rows) {
+    const int want = (n_rows + 31) / 32;                      // 8 warps x 4 rows per pass
+    const int cap = c->pub.gpu_sm_count * 8;
+    return want < 1 ? 1 : (want < cap ? want : cap);
 }
 // consts[0] = 1 (the largest possible P); consts[1] = 2 * max|dO row| * max|V row| * scale >= |dS| everywhere:
 // |dP| = |dO_q . V_k| <= the product of the norms, D_q is a convex combination of the dP_qk, P <= 1
@@ -382,8 +407,8 @@ extern "C" int sb_attention_tc_backward(sb_ctx_t* c, const float* Q, const float
         pv = at_make_parts(c, V, n_kv, hb + 2 * n_q + 2 * n_kv, consts + 10);
         pdo = at_make_parts(c, dO, n_q, hb + 2 * n_q + 4 * n_kv, consts + 11);
         cudaMemsetAsync(consts + 2, 0, 2 * sizeof(float), s0);
-        at_rownorm_max_kernel<<<(T * Hq * 32 + 255) / 256, 256, 0, s0>>>(dO, T * Hq, hd, (unsigned*)(consts + 2));
-        at_rownorm_max_kernel<<<(T * Hkv * 32 + 255) / 256, 256, 0, s0>>>(V, T * Hkv, hd, (unsigned*)(consts + 3));
+        at_rownorm_max_kernel<<<at_rn_blocks(c, T * Hq), 256, 0, s0>>>(dO, T * Hq, hd, (unsigned*)(consts + 2));
+        at_rownorm_max_kernel<<<at_rn_blocks(c, T * Hkv), 256, 0, s0>>>(V, T * Hkv, hd, (unsigned*)(consts + 3));
         at_consts_kernel<<<1, 1, 0, s0>>>(consts, consts + 2, scale);
         c->launches += 3;
     }

@@ -107,7 +107,7 @@ at_fused_fwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_consta
                     const __grid_constant__ CUtensorMap mV1, const __grid_constant__ CUtensorMap mV2,
                     const __grid_constant__ AfSeqs seqs, float* __restrict__ O, float* __restrict__ lse,
                     const float* __restrict__ amax_q, const float* __restrict__ amax_k, const float* __restrict__ amax_v,
-                    int Hq, int g, int nqb_max, float scale, int* status) {
+                    int Hq, int g, int nqb_max, float scale, int* status, unsigned* amax_o) {
     // which (query block, sequence, head): blocks with the most keys first, the query heads of one K/V head side by side
     const int per_i = seqs.n * Hq;
     const int qb = nqb_max - 1 - (int)blockIdx.x / per_i;
@@ -356,11 +356,20 @@ at_fused_fwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_consta
             if (lane == 0) af_arrive(&pv_empty[s]);
         }
         if (ok) ok = mbar_wait(fin_full, 0);
+        float am = 0.f;
         if (ok && qi < S) {
-            const float f = fin_s[r] * tc_pow2(-tc_f16_shift(__ldg(amax_v)));      // fin = 2^14 / l, O holds P * 2^14 products
+            const float f = fin_s[r] * tc_pow2(-tc_f16_shift(__ldg(amax_v)));      // fin = 1 / l with l in units of 2^-14, O holds (P * 2^14) V' products
             float4* dst = (float4*)(O + (size_t)(t0 + qi) * qd + (size_t)h * AF_HD + ch * 64);
 #pragma unroll
-            for (int i = 0; i < 16; i++) dst[i] = make_float4(o[4 * i] * f, o[4 * i + 1] * f, o[4 * i + 2] * f, o[4 * i + 3] * f);
+            for (int i = 0; i < 16; i++) {
+                const float4 v = make_float4(o[4 * i] * f, o[4 * i + 1] * f, o[4 * i + 2] * f, o[4 * i + 3] * f);
+                dst[i] = v;
+                am = sb_amax4(am, v);
+            }
+        }
+        if (amax_o) {                                          // largest |O|, for the split of the output projection's operand
+            for (int d = 16; d > 0; d >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, d));
+            if (lane == 0 && am > 0.f) atomicMax(amax_o, __float_as_uint(am));
         }
         if (!ok && lane == 0) atomicExch(status, SB_ERR_TIMEOUT);
     }
@@ -624,7 +633,8 @@ extern "C" int sb_attention_fused_forward(sb_ctx_t* c, const void* q1, const voi
     const long blocks = (long)nqb * seqs.n * Hq;
     if (blocks > 0x7fffffffL) return 1;
     at_fused_fwd_kernel<<<(unsigned)blocks, AF_THREADS, AF_SMEM, (cudaStream_t)c->pub.stream>>>(
-        mQ1, mQ2, mK1, mK2, mV1, mV2, seqs, O, lse, amax_q, amax_k, amax_v, Hq, Hq / Hkv, nqb, 1.0f / sqrtf((float)hd), c->d_status);
+        mQ1, mQ2, mK1, mK2, mV1, mV2, seqs, O, lse, amax_q, amax_k, amax_v, Hq, Hq / Hkv, nqb, 1.0f / sqrtf((float)hd), c->d_status,
+        sb_amax_take(c, O, (size_t)T * qd));
     c->launches++;
     return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }

@@ -247,11 +247,16 @@ static AtParts at_make_parts(sb_ctx_t* c, const float* x, size_t n, __half* h, f
         h = (__half*)kept; amax = kept_amax;
         if (!fresh) { AtParts p = {h, h + n, amax}; return p; }
     }
-    cudaMemsetAsync(amax, 0, sizeof(float), st);
     const dim3 pg(tc_ew_blocks(c, n / 4), 1);
-    tc_amax_kernel<<<pg, 256, 0, st>>>(x, n / 4, (unsigned*)amax, nullptr, 0, nullptr);
+    float* left = sb_amax_lookup(c, x, n);                            // the kernel that wrote x may have left its largest magnitude
+    if (left) { amax = left; sb_parts_set_amax(c, x, left); }
+    else {
+        cudaMemsetAsync(amax, 0, sizeof(float), st);
+        tc_amax_kernel<<<pg, 256, 0, st>>>(x, n / 4, (unsigned*)amax, nullptr, 0, nullptr);
+        c->launches++;
+    }
     tc_split_f16_kernel<<<pg, 256, 0, st>>>(x, n / 4, h, h + n, amax, nullptr, 0, nullptr, nullptr, nullptr);
-    c->launches += 2;
+    c->launches++;
     AtParts p = {h, h + n, amax};
     return p;
 }

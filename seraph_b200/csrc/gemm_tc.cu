@@ -126,11 +126,54 @@ extern "C" void sb_parts_unregister(sb_ctx_t* c, int kind) {
     if (c->parts_hash) parts_rehash(c);
     parts_drop_arena(c);
 }
-extern "C" void sb_parts_open(sb_ctx_t* c) { c->parts_gen++; c->parts_open = 1; }
-extern "C" void sb_parts_close(sb_ctx_t* c) { c->parts_gen++; c->parts_open = 0; }
+#define SB_HINT_CAP 4096
+extern "C" void sb_parts_open(sb_ctx_t* c) {
+    c->parts_gen++; c->parts_open = 1;
+    c->hint_n = 0; c->hint_npending = 0;
+    if (c->parts_cache && !c->hint_pool) {
+        c->hint_tab = (decltype(c->hint_tab))calloc(SB_HINT_CAP, sizeof *c->hint_tab);
+        if (!c->hint_tab || cudaMalloc((void**)&c->hint_pool, SB_HINT_CAP * sizeof(float)) != cudaSuccess) { cudaGetLastError(); c->hint_pool = NULL; }
+        c->hint_cap = c->hint_pool ? SB_HINT_CAP : 0;
+    }
+    if (c->hint_pool) cudaMemsetAsync(c->hint_pool, 0, SB_HINT_CAP * sizeof(float), (cudaStream_t)c->pub.stream);
+}
+extern "C" void sb_parts_close(sb_ctx_t* c) { c->parts_gen++; c->parts_open = 0; c->hint_n = 0; c->hint_npending = 0; }
+extern "C" void sb_amax_announce(sb_ctx_t* c, const float* out, size_t n) {
+    if (!c->parts_open || !c->parts_cache || !c->hint_pool) return;
+    if (c->hint_npending >= 4) {                       // announcements nobody took (a launcher without the feature): the oldest goes
+        for (int i = 1; i < 4; i++) c->hint_pending[i - 1] = c->hint_pending[i];
+        c->hint_npending = 3;
+    }
+    c->hint_pending[c->hint_npending].ptr = out; c->hint_pending[c->hint_npending].n = n; c->hint_npending++;
+}
+extern "C" unsigned* sb_amax_take(sb_ctx_t* c, const float* out, size_t n) {
+    for (int i = 0; i < c->hint_npending; i++)
+        if (c->hint_pending[i].ptr == out && c->hint_pending[i].n == n) {
+            c->hint_pending[i] = c->hint_pending[--c->hint_npending];
+            if (c->hint_n >= c->hint_cap) return NULL;
+            c->hint_tab[c->hint_n].ptr = out; c->hint_tab[c->hint_n].n = n;
+            return (unsigned*)(c->hint_pool + c->hint_n++);
+        }
+    return NULL;
+}
+extern "C" float* sb_amax_lookup(sb_ctx_t* c, const float* x, size_t n) {
+    if (!c->parts_open) return NULL;
+    for (int i = c->hint_n - 1; i >= 0; i--)
+        if (c->hint_tab[i].ptr == x) return c->hint_tab[i].n == n ? c->hint_pool + i : NULL;      // the latest writer decides
+    return NULL;
+}
+extern "C" void sb_parts_set_amax(sb_ctx_t* c, const float* x, float* word) {
+    if (!c->parts_cache || !c->parts_open || !c->parts_n) return;
+    size_t h = parts_hash_of(x, c->parts_hash_cap);
+    int idx;
+    while ((idx = c->parts_hash[h]) >= 0 && c->parts_tab[idx].ptr != x) h = (h + 1) & (size_t)(c->parts_hash_cap - 1);
+    if (idx >= 0) c->parts_tab[idx].amax_ptr = word;
+}
 extern "C" void sb_parts_free(sb_ctx_t* c) {
     parts_drop_arena(c);
-    free(c->parts_tab); free(c->parts_hash);
+    free(c->parts_tab); free(c->parts_hash); free(c->hint_tab);
+    if (c->hint_pool) cudaFree(c->hint_pool);
+    c->hint_tab = NULL; c->hint_pool = NULL; c->hint_cap = c->hint_n = 0;
     c->parts_tab = NULL; c->parts_hash = NULL; c->parts_n = c->parts_cap = c->parts_hash_cap = 0; c->parts_total = 0;
 }
 extern "C" int sb_parts_find(sb_ctx_t* c, const float* x, size_t n, void** hout, float** amax, int* fresh) {
@@ -157,8 +200,9 @@ extern "C" int sb_parts_find(sb_ctx_t* c, const float* x, size_t n, void** hout,
     }
     sb_parts_entry_t* e = &c->parts_tab[idx];
     *hout = (__half*)c->parts_arena + e->off;
-    *amax = c->parts_amax + idx;
     *fresh = e->gen != c->parts_gen || e->cur != n;
+    if (*fresh) e->amax_ptr = c->parts_amax + idx;
+    *amax = e->amax_ptr;
     e->gen = c->parts_gen; e->cur = n;
     return 1;
 }
@@ -194,25 +238,36 @@ extern "C" int sb_gemm_tc(sb_ctx_t* c, const float* A, const float* B, float* C,
             const size_t na = (size_t)M * K, nb = (size_t)N * K;
             bool fa = false, fb = false;
             __half *ha, *hb; float *ma, *mb;
-            void* hv; int fr;
+            void* hv; int fr; int sa = -1, sb = -1;
             if (sb_parts_find(c, A, na, &hv, &ma, &fr)) { ha = (__half*)hv; fa = fr != 0; }
-            else { const int sa = f16_slot(c, A, na, 6, &fa); if (sa < 0) return 1; ha = (__half*)c->f16_slot[sa].h; ma = c->d_amax + sa; }
+            else { sa = f16_slot(c, A, na, 6, &fa); if (sa < 0) return 1; ha = (__half*)c->f16_slot[sa].h; if (fa) c->f16_slot[sa].amax = c->d_amax + sa; ma = c->f16_slot[sa].amax; }
             if (sb_parts_find(c, B, nb, &hv, &mb, &fr)) { hb = (__half*)hv; fb = fr != 0; }
-            else { const int sb = f16_slot(c, B, nb, 7, &fb); if (sb < 0) return 1; hb = (__half*)c->f16_slot[sb].h; mb = c->d_amax + sb; }
+            else { sb = f16_slot(c, B, nb, 7, &fb); if (sb < 0) return 1; hb = (__half*)c->f16_slot[sb].h; if (fb) c->f16_slot[sb].amax = c->d_amax + sb; mb = c->f16_slot[sb].amax; }
             if (fa || fb) {
                 cudaStream_t st = (cudaStream_t)c->pub.stream;
                 int tp = sb_tick_begin(c, SB_CLS_GEMM_PREP);
-                // the operands that need their parts made: first (and maybe second) argument set of the kernels
-                const float* x0 = fa ? A : B; const size_t n0 = fa ? na : nb; __half* h0 = fa ? ha : hb; float* m0 = fa ? ma : mb;
-                const bool two = fa && fb;
-                cudaMemsetAsync(m0, 0, sizeof(float), st);
-                if (two) cudaMemsetAsync(mb, 0, sizeof(float), st);
-                const size_t nmax = two ? (na > nb ? na : nb) : n0;
-                const dim3 pg(tc_ew_blocks(c, nmax / 4), two ? 2 : 1);
-                tc_amax_kernel<<<pg, 256, 0, st>>>(x0, n0 / 4, (unsigned*)m0, B, nb / 4, (unsigned*)mb);
-                tc_split_f16_kernel<<<pg, 256, 0, st>>>(x0, n0 / 4, h0, h0 + n0, m0, B, nb / 4, hb, hb + nb, mb);
-                c->launches += 2;
-                sb_tick_end(c, tp, 0.0, 12.0 * (double)((fa ? na : 0) + (fb ? nb : 0)));
+                // a producer may have left the operand's largest magnitude behind: then only the split runs for it
+                bool ka = false, kb = false;
+                if (fa) { float* w = sb_amax_lookup(c, A, na); if (w) { ma = w; ka = true; if (sa >= 0) c->f16_slot[sa].amax = w; else sb_parts_set_amax(c, A, w); } }
+                if (fb) { float* w = sb_amax_lookup(c, B, nb); if (w) { mb = w; kb = true; if (sb >= 0) c->f16_slot[sb].amax = w; else sb_parts_set_amax(c, B, w); } }
+                const bool xa = fa && !ka, xb = fb && !kb;             // operands whose amax pass is needed
+                if (xa) cudaMemsetAsync(ma, 0, sizeof(float), st);
+                if (xb) cudaMemsetAsync(mb, 0, sizeof(float), st);
+                if (xa || xb) {
+                    const float* x0 = xa ? A : B; const size_t n0 = xa ? na : nb; float* m0 = xa ? ma : mb;
+                    const bool two = xa && xb;
+                    const dim3 pg(tc_ew_blocks(c, (two ? (na > nb ? na : nb) : n0) / 4), two ? 2 : 1);
+                    tc_amax_kernel<<<pg, 256, 0, st>>>(x0, n0 / 4, (unsigned*)m0, B, nb / 4, (unsigned*)mb);
+                    c->launches++;
+                }
+                {
+                    const float* x0 = fa ? A : B; const size_t n0 = fa ? na : nb; __half* h0 = fa ? ha : hb; float* m0 = fa ? ma : mb;
+                    const bool two = fa && fb;
+                    const dim3 pg(tc_ew_blocks(c, (two ? (na > nb ? na : nb) : n0) / 4), two ? 2 : 1);
+                    tc_split_f16_kernel<<<pg, 256, 0, st>>>(x0, n0 / 4, h0, h0 + n0, m0, B, nb / 4, hb, hb + nb, mb);
+                    c->launches++;
+                }
+                sb_tick_end(c, tp, 0.0, 8.0 * (double)((fa ? na : 0) + (fb ? nb : 0)) + 4.0 * (double)((xa ? na : 0) + (xb ? nb : 0)));
             }
             p.amax_a = ma; p.amax_b = mb;
             p.A.h1 = ha; p.A.h2 = ha + na; p.B.h1 = hb; p.B.h2 = hb + nb;

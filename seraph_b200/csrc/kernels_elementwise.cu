@@ -39,8 +39,9 @@ __device__ __forceinline__ float ew_apply(float a, float b) {
 
 template <int OP, bool BINARY>
 __global__ void __launch_bounds__(EW_THREADS) ew_kernel(const float* __restrict__ a, const float* __restrict__ b,
-                                                        float* __restrict__ c, size_t n, int vec_ok) {
+                                                        float* __restrict__ c, size_t n, int vec_ok, unsigned* amax_out) {
     size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    float am = 0.f;                                       // largest |output| of this thread (asked for by the next GEMM's operand split)
     if (vec_ok) {
         size_t n4 = n >> 2;
         const float4* a4 = (const float4*)a; const float4* b4 = (const float4*)b; float4* c4 = (float4*)c;
@@ -49,11 +50,13 @@ __global__ void __launch_bounds__(EW_THREADS) ew_kernel(const float* __restrict_
             r.x = ew_apply<OP>(x.x, y.x); r.y = ew_apply<OP>(x.y, y.y);
             r.z = ew_apply<OP>(x.z, y.z); r.w = ew_apply<OP>(x.w, y.w);
             c4[i] = r;
+            am = sb_amax4(am, r);
         }
-        for (size_t i = (n4 << 2) + tid; i < n; i += nth) c[i] = ew_apply<OP>(a[i], BINARY ? b[i] : a[i]);
+        for (size_t i = (n4 << 2) + tid; i < n; i += nth) { const float r = ew_apply<OP>(a[i], BINARY ? b[i] : a[i]); c[i] = r; am = fmaxf(am, fabsf(r)); }
     } else {
-        for (size_t i = tid; i < n; i += nth) c[i] = ew_apply<OP>(a[i], BINARY ? b[i] : a[i]);
+        for (size_t i = tid; i < n; i += nth) { const float r = ew_apply<OP>(a[i], BINARY ? b[i] : a[i]); c[i] = r; am = fmaxf(am, fabsf(r)); }
     }
+    sb_block_amax(am, amax_out);
 }
 
 static inline int aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
@@ -63,7 +66,7 @@ static void ew_launch(sb_ctx_t* c, const float* a, const float* b, float* o, siz
     if (!n) return;
     int vec = aligned16(a) && aligned16(o) && (!BINARY || aligned16(b));
     int tk = sb_tick_begin(c, OP == OP_SWIGLU ? SB_CLS_SWIGLU : SB_CLS_OTHER);
-    ew_kernel<OP, BINARY><<<ew_grid(c, (n + 3) / 4), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(a, b, o, n, vec);
+    ew_kernel<OP, BINARY><<<ew_grid(c, (n + 3) / 4), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(a, b, o, n, vec, OP == OP_SWIGLU ? sb_amax_take(c, o, n) : (unsigned*)nullptr);
     sb_tick_end(c, tk, 0.0, (BINARY ? 12.0 : 8.0) * (double)n);
     c->launches++;
 }
@@ -87,8 +90,10 @@ __global__ void __launch_bounds__(EW_THREADS) mul_bwd_kernel(const float* __rest
 // (src/train_cuda.c:2197-2203) without the intermediate tensors.
 __global__ void __launch_bounds__(EW_THREADS) swiglu_bwd_kernel(const float* __restrict__ gate, const float* __restrict__ up,
                                                                 const float* __restrict__ dout, float* __restrict__ dgate,
-                                                                float* __restrict__ dup, size_t n, int vec_ok) {
+                                                                float* __restrict__ dup, size_t n, int vec_ok,
+                                                                unsigned* amax_dgate, unsigned* amax_dup) {
     size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    float amg = 0.f, amu = 0.f;
 #define SWIGLU_BWD_ONE(g, u, d, dg, du) { float sg = sigmoidf_(g); float si = (g) * sg; \
         float dsl = (d) * (u); du = (d) * si; dg = dsl * (sg + (g) * sg * (1.0f - sg)); }
     if (vec_ok) {
@@ -98,11 +103,15 @@ __global__ void __launch_bounds__(EW_THREADS) swiglu_bwd_kernel(const float* __r
             SWIGLU_BWD_ONE(g.x, u.x, d.x, dg.x, du.x) SWIGLU_BWD_ONE(g.y, u.y, d.y, dg.y, du.y)
             SWIGLU_BWD_ONE(g.z, u.z, d.z, dg.z, du.z) SWIGLU_BWD_ONE(g.w, u.w, d.w, dg.w, du.w)
             ((float4*)dgate)[i] = dg; ((float4*)dup)[i] = du;
+            amg = sb_amax4(amg, dg); amu = sb_amax4(amu, du);
         }
-        for (size_t i = (n4 << 2) + tid; i < n; i += nth) SWIGLU_BWD_ONE(gate[i], up[i], dout[i], dgate[i], dup[i])
+        for (size_t i = (n4 << 2) + tid; i < n; i += nth) { SWIGLU_BWD_ONE(gate[i], up[i], dout[i], dgate[i], dup[i]) amg = fmaxf(amg, fabsf(dgate[i])); amu = fmaxf(amu, fabsf(dup[i])); }
     } else {
-        for (size_t i = tid; i < n; i += nth) SWIGLU_BWD_ONE(gate[i], up[i], dout[i], dgate[i], dup[i])
+        for (size_t i = tid; i < n; i += nth) { SWIGLU_BWD_ONE(gate[i], up[i], dout[i], dgate[i], dup[i]) amg = fmaxf(amg, fabsf(dgate[i])); amu = fmaxf(amu, fabsf(dup[i])); }
     }
+    sb_block_amax(amg, amax_dgate);
+    __syncthreads();
+    sb_block_amax(amu, amax_dup);
 }
 
 // out[t,:] = E[tok[t],:]; one CTA per few rows, float4 when d%4==0.  Token ids
@@ -151,7 +160,9 @@ __global__ void rope_table_kernel(float2* tab, int max_pos, int half, int hd, fl
 #define ROPE_UNROLL 4
 __global__ void __launch_bounds__(EW_THREADS) rope_kernel(const float* qin, float* qout, const float* kin, float* kout,
                                                           const uint32_t* __restrict__ pos_ids, const float2* __restrict__ tab,
-                                                          int T, int Hq, int Hkv, int hd, int backward) {
+                                                          int T, int Hq, int Hkv, int hd, int backward,
+                                                          unsigned* amax_q, unsigned* amax_k) {
+    float amq = 0.f, amk = 0.f;
     const uint32_t quads = (uint32_t)hd >> 2, rq = (uint32_t)Hq * quads, rk = kin ? (uint32_t)Hkv * quads : 0u, row_quads = rq + rk;
     const uint32_t total = (uint32_t)T * row_quads;
     const uint32_t nth = gridDim.x * blockDim.x;
@@ -183,9 +194,14 @@ __global__ void __launch_bounds__(EW_THREADS) rope_kernel(const float* qin, floa
                     r.z = x[u].z * cs[u].z + x[u].w * cs[u].w; r.w = -x[u].z * cs[u].w + x[u].w * cs[u].z;
                 }
                 *dst[u] = r;
+                const uint32_t i = base + u * nth;
+                if (i - (i / row_quads) * row_quads < rq) amq = sb_amax4(amq, r); else amk = sb_amax4(amk, r);
             }
         }
     }
+    sb_block_amax(amq, amax_q);
+    __syncthreads();
+    sb_block_amax(amk, amax_k);
 }
 
 // pair-at-a-time variant for head_dim not divisible by 4 or unaligned buffers
@@ -235,7 +251,8 @@ void sb_swiglu_backward(sb_ctx_t* c, const float* gate, const float* up, const f
     if (!n) return;
     int vec = aligned16(gate) && aligned16(up) && aligned16(dout) && aligned16(dgate) && aligned16(dup);
     int tk = sb_tick_begin(c, SB_CLS_SWIGLU);
-    swiglu_bwd_kernel<<<ew_grid(c, (n + 3) / 4), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(gate, up, dout, dgate, dup, n, vec);
+    swiglu_bwd_kernel<<<ew_grid(c, (n + 3) / 4), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(gate, up, dout, dgate, dup, n, vec,
+                                                                                                  sb_amax_take(c, dgate, n), sb_amax_take(c, dup, n));
     sb_tick_end(c, tk, 0.0, 20.0 * (double)n);
     c->launches++;
 }
@@ -281,7 +298,7 @@ void sb_rope(sb_ctx_t* c, const float* in, float* out, const uint32_t* pos_ids, 
     int tk = sb_tick_begin(c, SB_CLS_ROPE);
     if ((hd & 3) == 0 && aligned16(in) && aligned16(out) && aligned16(c->rope_tab) && (double)T * H * (hd / 4) < 2147483648.0) {
         size_t work = ((size_t)T * H * (hd / 4) + ROPE_UNROLL - 1) / ROPE_UNROLL;
-        rope_kernel<<<ew_grid(c, work), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(in, out, nullptr, nullptr, pos_ids, (const float2*)c->rope_tab, T, H, 0, hd, backward);
+        rope_kernel<<<ew_grid(c, work), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(in, out, nullptr, nullptr, pos_ids, (const float2*)c->rope_tab, T, H, 0, hd, backward, nullptr, nullptr);
     } else {
         size_t work = (size_t)T * H * half;
         rope_pair_kernel<<<ew_grid(c, work), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(in, out, pos_ids, (const float2*)c->rope_tab, T, H, hd, backward);
@@ -302,7 +319,8 @@ void sb_rope2(sb_ctx_t* c, float* q, float* k, const uint32_t* pos_ids, int T, i
     if (!rope_ensure_table(c, hd, theta, max_pos)) return;
     int tk = sb_tick_begin(c, SB_CLS_ROPE);
     size_t work = ((size_t)nq + ROPE_UNROLL - 1) / ROPE_UNROLL;
-    rope_kernel<<<ew_grid(c, work), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(q, q, k, k, pos_ids, (const float2*)c->rope_tab, T, Hq, Hkv, hd, backward);
+    rope_kernel<<<ew_grid(c, work), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(q, q, k, k, pos_ids, (const float2*)c->rope_tab, T, Hq, Hkv, hd, backward,
+                                                                                   sb_amax_take(c, q, (size_t)T * Hq * hd), sb_amax_take(c, k, (size_t)T * Hkv * hd));
     sb_tick_end(c, tk, 0.0, 8.0 * T * (Hq + Hkv) * hd);
     c->launches++;
 }

@@ -134,9 +134,10 @@ __global__ void __launch_bounds__(RB_THREADS) rmsnorm_bwd_kernel(const float* __
 // ---------------------------------------------------------------------------
 template <int NV>
 __global__ void __launch_bounds__(RB_THREADS) rmsnorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ w,
-                                                                  float* __restrict__ y, int rows, int cols, float eps) {
+                                                                  float* __restrict__ y, int rows, int cols, float eps, unsigned* amax_out) {
     const int lane = threadIdx.x & 31, warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
     const int c4 = cols >> 2;
+    float am = 0.f;
     for (int r = warp; r < rows; r += nwarps) {
         const float4* xr = (const float4*)(x + (size_t)r * cols);
         float4 v[NV];
@@ -153,9 +154,15 @@ __global__ void __launch_bounds__(RB_THREADS) rmsnorm_warp_kernel(const float* _
 #pragma unroll
         for (int i = 0; i < NV; i++) {
             int j = lane + 32 * i;
-            if (j < c4) { float4 s = ((const float4*)w)[j]; yr[j] = make_float4(v[i].x * inv * s.x, v[i].y * inv * s.y, v[i].z * inv * s.z, v[i].w * inv * s.w); }
+            if (j < c4) {
+                float4 s = ((const float4*)w)[j];
+                const float4 o = make_float4(v[i].x * inv * s.x, v[i].y * inv * s.y, v[i].z * inv * s.z, v[i].w * inv * s.w);
+                yr[j] = o;
+                am = sb_amax4(am, o);
+            }
         }
     }
+    sb_block_amax(am, amax_out);
 }
 
 // RMSNorm backward for a 256-thread CTA that visits row groups of RNB_ROWS rows.  Thread t owns the float4 column
@@ -185,7 +192,7 @@ __device__ __forceinline__ void rnb_load(RnbSet<NC>& s, const float* __restrict_
 
 template <int NC>
 __device__ __forceinline__ void rnb_compute(const RnbSet<NC>& s, const float4 (&sc)[NC], float4 (&acc)[NC], float* dx, int r0, int rows,
-                                            int cols, int c4, float eps, float (*s_red)[2 * RNB_ROWS], float* s_tot) {
+                                            int cols, int c4, float eps, float (*s_red)[2 * RNB_ROWS], float* s_tot, float& am) {
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     float part[2 * RNB_ROWS];
 #pragma unroll
@@ -226,6 +233,7 @@ __device__ __forceinline__ void rnb_compute(const RnbSet<NC>& s, const float4 (&
                 o.x = g.x * sc[i].x * inv - v.x * k + q.x; o.y = g.y * sc[i].y * inv - v.y * k + q.y;
                 o.z = g.z * sc[i].z * inv - v.z * k + q.z; o.w = g.w * sc[i].w * inv - v.w * k + q.w;
                 ((float4*)dx)[(size_t)(r0 + rr) * c4 + j] = o;
+                am = sb_amax4(am, o);
             }
         }
     }
@@ -234,7 +242,8 @@ __device__ __forceinline__ void rnb_compute(const RnbSet<NC>& s, const float4 (&
 template <int NC>
 __global__ void __launch_bounds__(RB_THREADS, 2) rmsnorm_bwd_rows_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                                          const float* __restrict__ dy, const float* resid, float* dx,
-                                                                         float* __restrict__ partial, int rows, int cols, float eps) {
+                                                                         float* __restrict__ partial, int rows, int cols, float eps, unsigned* amax_dx) {
+    float am = 0.f;
     __shared__ float s_red[2][RB_THREADS / 32][2 * RNB_ROWS];
     __shared__ float s_tot[2][2 * RNB_ROWS];
     const int c4 = cols >> 2;
@@ -251,11 +260,11 @@ __global__ void __launch_bounds__(RB_THREADS, 2) rmsnorm_bwd_rows_kernel(const f
     if (gidx < ngroups) rnb_load<NC>(a, x, dy, resid, gidx * RNB_ROWS, rows, c4);
     while (gidx < ngroups) {
         if (gidx + stride < ngroups) rnb_load<NC>(b, x, dy, resid, (gidx + stride) * RNB_ROWS, rows, c4);
-        rnb_compute<NC>(a, sc, acc, dx, gidx * RNB_ROWS, rows, cols, c4, eps, s_red[0], s_tot[0]);
+        rnb_compute<NC>(a, sc, acc, dx, gidx * RNB_ROWS, rows, cols, c4, eps, s_red[0], s_tot[0], am);
         gidx += stride;
         if (gidx >= ngroups) break;
         if (gidx + stride < ngroups) rnb_load<NC>(a, x, dy, resid, (gidx + stride) * RNB_ROWS, rows, c4);
-        rnb_compute<NC>(b, sc, acc, dx, gidx * RNB_ROWS, rows, cols, c4, eps, s_red[1], s_tot[1]);
+        rnb_compute<NC>(b, sc, acc, dx, gidx * RNB_ROWS, rows, cols, c4, eps, s_red[1], s_tot[1], am);
         gidx += stride;
     }
 #pragma unroll
@@ -263,6 +272,7 @@ __global__ void __launch_bounds__(RB_THREADS, 2) rmsnorm_bwd_rows_kernel(const f
         const int j = threadIdx.x + RB_THREADS * i;
         if (j < c4) ((float4*)(partial + (size_t)blockIdx.x * cols))[j] = acc[i];
     }
+    sb_block_amax(am, amax_dx);
 }
 
 // dscale[c] += sum over partial rows of partial[b][c], in a fixed order: 32 columns per CTA, the rows dealt to
@@ -332,8 +342,9 @@ __global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(const float* 
                                                                    float* __restrict__ grad, float* __restrict__ loss_rows,
                                                                    const uint32_t* __restrict__ pos_ids, const uint32_t* __restrict__ seq_ids,
                                                                    const uint32_t* __restrict__ seq_starts,
-                                                                   int T, int V, float inv_valid, int vec, int* status) {
+                                                                   int T, int V, float inv_valid, int vec, int* status, unsigned* amax_grad) {
     __shared__ float redm[32], reds[32];
+    float am = 0.f;
     int r = blockIdx.x;
     if (r >= T) return;
     const float* lr = logits + (size_t)r * V; float* gr = grad + (size_t)r * V;
@@ -375,11 +386,14 @@ __global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(const float* 
         if (tg - b < 4u) { if (tg == b) g.x -= 1.f; else if (tg == b + 1) g.y -= 1.f; else if (tg == b + 2) g.z -= 1.f; else g.w -= 1.f; }
         g.x *= inv_valid; g.y *= inv_valid; g.z *= inv_valid; g.w *= inv_valid;
         ((float4*)gr)[i] = g;
+        am = sb_amax4(am, g);
     } else for (int i = threadIdx.x; i < V; i += blockDim.x) {
         float g = expf(lr[i] - m) * inv;
         if ((uint32_t)i == tg) g -= 1.f;
         gr[i] = g * inv_valid;
+        am = fmaxf(am, fabsf(g * inv_valid));
     }
+    sb_block_amax(am, amax_grad);
 }
 
 // ---------------------------------------------------------------------------
@@ -531,10 +545,11 @@ void sb_rmsnorm(sb_ctx_t* c, const float* x, const float* w, float* y, int rows,
         int wgrid = (rows + 7) / 8;
         { int cap = sm_count(c) * 2, k = (wgrid + cap - 1) / cap; wgrid = (wgrid + k - 1) / k; }
         cudaStream_t st = (cudaStream_t)c->pub.stream;
-        if (cols <= 512)       rmsnorm_warp_kernel<4><<<wgrid, RB_THREADS, 0, st>>>(x, w, y, rows, cols, eps);
-        else if (cols <= 1024) rmsnorm_warp_kernel<8><<<wgrid, RB_THREADS, 0, st>>>(x, w, y, rows, cols, eps);
-        else if (cols <= 2048) rmsnorm_warp_kernel<16><<<wgrid, RB_THREADS, 0, st>>>(x, w, y, rows, cols, eps);
-        else                   rmsnorm_warp_kernel<32><<<wgrid, RB_THREADS, 0, st>>>(x, w, y, rows, cols, eps);
+        unsigned* am = sb_amax_take(c, y, (size_t)rows * cols);
+        if (cols <= 512)       rmsnorm_warp_kernel<4><<<wgrid, RB_THREADS, 0, st>>>(x, w, y, rows, cols, eps, am);
+        else if (cols <= 1024) rmsnorm_warp_kernel<8><<<wgrid, RB_THREADS, 0, st>>>(x, w, y, rows, cols, eps, am);
+        else if (cols <= 2048) rmsnorm_warp_kernel<16><<<wgrid, RB_THREADS, 0, st>>>(x, w, y, rows, cols, eps, am);
+        else                   rmsnorm_warp_kernel<32><<<wgrid, RB_THREADS, 0, st>>>(x, w, y, rows, cols, eps, am);
     } else
     rmsnorm_kernel<<<grid, RB_THREADS, 0, (cudaStream_t)c->pub.stream>>>(x, w, y, rows, cols, eps, vec);
     sb_tick_end(c, tk, 0.0, 8.0 * rows * cols);
@@ -567,8 +582,9 @@ void sb_rmsnorm_backward(sb_ctx_t* c, const float* x, const float* w, const floa
         if (!partial) return;
         cudaStream_t st = (cudaStream_t)c->pub.stream;
         int tk = sb_tick_begin(c, SB_CLS_NORM_BWD);
-        if (cols <= 1024) rmsnorm_bwd_rows_kernel<1><<<wgrid, RB_THREADS, 0, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
-        else              rmsnorm_bwd_rows_kernel<2><<<wgrid, RB_THREADS, 0, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps);
+        unsigned* am = sb_amax_take(c, dx_out, (size_t)rows * cols);
+        if (cols <= 1024) rmsnorm_bwd_rows_kernel<1><<<wgrid, RB_THREADS, 0, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps, am);
+        else              rmsnorm_bwd_rows_kernel<2><<<wgrid, RB_THREADS, 0, st>>>(x, w, dy, resid, dx_out, partial, rows, cols, eps, am);
         colsum_partials_kernel<<<(cols + 31) / 32, 32 * CS_GROUPS, 0, st>>>(partial, dscale, wgrid, cols);
         sb_tick_end(c, tk, 0.0, (resid ? 16.0 : 12.0) * rows * cols);
         c->launches += 2;
@@ -593,7 +609,7 @@ void sb_cross_entropy(sb_ctx_t* c, const float* logits, const uint32_t* targets,
     int vec = (V % 4 == 0) && aligned16(logits) && aligned16(grad);
     int tk = sb_tick_begin(c, SB_CLS_CE);
     cross_entropy_kernel<<<T, CE_THREADS, 0, (cudaStream_t)c->pub.stream>>>(logits, targets, grad, loss_rows, pos_ids, seq_ids,
-                                                                          seq_starts, T, V, 1.0f / (float)num_valid, vec, c->d_status);
+                                                                          seq_starts, T, V, 1.0f / (float)num_valid, vec, c->d_status, sb_amax_take(c, grad, (size_t)T * V));
     sb_tick_end(c, tk, 0.0, 12.0 * T * V);
     c->launches++;
 }

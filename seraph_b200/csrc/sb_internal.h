@@ -49,7 +49,7 @@ typedef struct {
     float *layer_in, *x_norm_attn, *q, *k, *v, *attn_out, *lse, *post_attn_in, *x_norm_ffn, *gate, *up, *ffn_hidden;
 } sb_layer_act_t;
 
-typedef struct { const float* ptr; size_t n, cur, off; unsigned gen; int kind; } sb_parts_entry_t;   /* n: registered floats, cur: floats of the parts held */
+typedef struct { const float* ptr; size_t n, cur, off; unsigned gen; int kind; float* amax_ptr; } sb_parts_entry_t;   /* n: registered floats, cur: floats of the parts held */
 
 typedef struct sb_ctx {
     cuda_train_context_t pub;        /* MUST stay first */
@@ -58,7 +58,7 @@ typedef struct sb_ctx {
     int* d_status;                   /* device status word (bounds checks, bounded waits) */
     int gemm_mode;                   /* SB_GEMM_* (use_bf16 in pub overrides to BF16) */
     float* d_amax;                   /* FP16 split: max |x| of the operand held by each part slot */
-    struct { void* h; size_t cap; const float* ptr; size_t n; unsigned stamp; int valid; } f16_slot[8];   /* FP16 parts of GEMM operands: 0-5 kept across
+    struct { void* h; size_t cap; const float* ptr; size_t n; unsigned stamp; int valid; float* amax; } f16_slot[8];   /* FP16 parts of GEMM operands: 0-5 kept across
                                         calls inside a keep region (train_step.c marks runs of GEMMs that share operands), 6-7 for one call */
     int f16_keep; unsigned f16_clock;
     /* FP16 parts of registered tensors (weights, saved activations), valid from their first use inside a training or
@@ -67,6 +67,10 @@ typedef struct sb_ctx {
     int parts_n, parts_cap; int* parts_hash; int parts_hash_cap;
     size_t parts_total;              /* halves the registered tensors need */
     void* parts_arena; size_t parts_arena_halves; float* parts_amax; int parts_amax_cap;
+    /* largest magnitudes left by the kernels that produce GEMM operands (announced by the step driver, valid inside one step):
+       the operand preparation then skips its own pass over the tensor */
+    struct { const float* ptr; size_t n; } *hint_tab; int hint_n, hint_cap; float* hint_pool;
+    struct { const float* ptr; size_t n; } hint_pending[4]; int hint_npending;
     unsigned parts_gen; int parts_open; int parts_cache;   /* parts_cache 0: off (switch, or the arena did not fit) */
     int attn_flash;                  /* 1: attention forward of 128-wide heads runs as one kernel (no score scratch) */
     int attn_fused;                  /* 1: P and dS of the attention backward come out of the score products' epilogues */
@@ -162,6 +166,13 @@ void sb_parts_unregister(sb_ctx_t*, int kind);
 void sb_parts_open(sb_ctx_t*);
 void sb_parts_close(sb_ctx_t*);
 void sb_parts_free(sb_ctx_t*);
+/* sb_amax_announce: the next kernel that writes out[n] should leave max |out| behind (step driver).  sb_amax_take: called by that
+   kernel's launcher with its output; returns the zeroed device word to raise with atomicMax on float bits, or NULL.
+   sb_amax_lookup: the word of the latest producer of x[n] in this step, or NULL. */
+void sb_amax_announce(sb_ctx_t*, const float* out, size_t n);
+unsigned* sb_amax_take(sb_ctx_t*, const float* out, size_t n);
+float* sb_amax_lookup(sb_ctx_t*, const float* x, size_t n);
+void sb_parts_set_amax(sb_ctx_t*, const float* x, float* word);
 /* 1: x[n] is registered and the step is open; *h = its two parts (h, h + n), *amax its scale word, *fresh = parts must be made now */
 int sb_parts_find(sb_ctx_t*, const float* x, size_t n, void** h, float** amax, int* fresh);
 void sb_rope2(sb_ctx_t*, float* q, float* k, const uint32_t* pos_ids, int T, int Hq, int Hkv, int hd, float theta, int max_pos, int backward);
@@ -211,4 +222,25 @@ void sb_prof_end(sb_ctx_t*, int op, size_t flops, size_t bytes);
 #ifdef __cplusplus
 }
 #endif
+#endif
+
+#ifdef __CUDACC__
+/* Largest magnitude seen by a CTA (each thread passes its own maximum, >= 0) raised into *out with an integer atomicMax on the
+   float bits; every thread of the CTA must call it, CTAs of at most 1024 threads.  out == NULL: nothing happens. */
+static __device__ __forceinline__ void sb_block_amax(float v, unsigned* out) {
+    if (!out) return;
+    __shared__ float sb_amax_red[32];
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    if (lane == 0) sb_amax_red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        v = lane < nw ? sb_amax_red[lane] : 0.f;
+        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+        if (lane == 0 && v > 0.f) atomicMax(out, __float_as_uint(v));
+    }
+}
+static __device__ __forceinline__ float sb_amax4(float m, float4 v) {
+    return fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+}
 #endif

@@ -428,6 +428,7 @@ static void forward_pass(sb_ctx_t* c, int T, int max_seq, float theta, int use_l
         const sb_layer_off_t* o = &c->off[l];
         sb_layer_act_t* a = &c->act[l];
         float* next_in = (l + 1 < L) ? c->act[l + 1].layer_in : c->final_in;
+        sb_amax_announce(c, a->x_norm_attn, Td);           /* producers of GEMM operands leave max |x| behind for the operand split */
         sb_rmsnorm(c, a->layer_in, c->W + o->in_norm, a->x_norm_attn, T, d, RMS_EPS);
         /* runs of products that share an operand keep its prepared parts (not with adapters: their scratch is rewritten in between) */
         if (!use_lora) sb_gemm_keep_begin(c);
@@ -435,19 +436,24 @@ static void forward_pass(sb_ctx_t* c, int T, int max_seq, float theta, int use_l
         linear_fwd(c, use_lora, l, 1, a->x_norm_attn, c->W + o->k, a->k, T, d, kvd, 0);
         linear_fwd(c, use_lora, l, 2, a->x_norm_attn, c->W + o->v, a->v, T, d, kvd, 0);
         sb_gemm_keep_end(c);
+        sb_amax_announce(c, a->q, (size_t)T * qd); sb_amax_announce(c, a->k, (size_t)T * kvd);
         sb_rope2(c, a->q, a->k, c->pos_ids, T, c->Hq, c->Hkv, c->hd, theta, max_seq, 0);
+        sb_amax_announce(c, a->attn_out, (size_t)T * qd);
         sb_attention(c, a->q, a->k, a->v, a->attn_out, a->lse, c->seq_starts, c->seq_ids, T, c->Hq, c->Hkv, c->hd);
         sb_copy(c, a->post_attn_in, a->layer_in, Td * sizeof(float));
         linear_fwd(c, use_lora, l, 3, a->attn_out, c->W + o->o, a->post_attn_in, T, qd, d, 1);
+        sb_amax_announce(c, a->x_norm_ffn, Td);
         sb_rmsnorm(c, a->post_attn_in, c->W + o->post_norm, a->x_norm_ffn, T, d, RMS_EPS);
         if (!use_lora) sb_gemm_keep_begin(c);
         linear_fwd(c, use_lora, l, 4, a->x_norm_ffn, c->W + o->gate, a->gate, T, d, F, 0);
         linear_fwd(c, use_lora, l, 5, a->x_norm_ffn, c->W + o->up, a->up, T, d, F, 0);
         sb_gemm_keep_end(c);
+        sb_amax_announce(c, a->ffn_hidden, (size_t)T * F);
         sb_swiglu(c, a->gate, a->up, a->ffn_hidden, (size_t)T * F);
         sb_copy(c, next_in, a->post_attn_in, Td * sizeof(float));
         linear_fwd(c, use_lora, l, 6, a->ffn_hidden, c->W + o->down, next_in, T, F, d, 1);
     }
+    sb_amax_announce(c, c->hidden_norm, Td);
     sb_rmsnorm(c, c->final_in, c->W + (size_t)c->V * d, c->hidden_norm, T, d, RMS_EPS);
     sb_gemm(c, c->hidden_norm, c->W, c->logits, T, c->V, d, 0, 1, 0);       /* tied LM head */
 }
@@ -463,6 +469,7 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
     sb_gemm(c, c->dlogits, c->W, gx, T, d, V, 0, 0, 0);
     if (full) sb_gemm(c, c->dlogits, c->hidden_norm, Gd, V, d, T, 1, 0, 1);
     sb_gemm_keep_end(c);
+    sb_amax_announce(c, gh, (size_t)T * d);
     sb_rmsnorm_backward(c, c->final_in, c->W + (size_t)V * d, gx, NULL, gh, full ? Gd + (size_t)V * d : norm_sink, T, d, RMS_EPS);
     for (int l = L - 1; l >= 0; l--) {
         const sb_layer_off_t* o = &c->off[l];
@@ -473,6 +480,7 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
         sb_gemm(c, gh, c->W + o->down, c->g_ffn, T, F, d, 0, 0, 0);
         sb_gemm_keep_end(c);
         if (!full) lora_bwd(c, l, 6, gh, a->ffn_hidden, c->g_ffn, T);
+        sb_amax_announce(c, c->g_gate, (size_t)T * F); sb_amax_announce(c, c->g_up, (size_t)T * F);
         sb_swiglu_backward(c, a->gate, a->up, c->g_ffn, c->g_gate, c->g_up, (size_t)T * F);
         if (full) {
             sb_gemm_keep_begin(c);
@@ -483,6 +491,7 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
         sb_gemm(c, c->g_up, c->W + o->up, gx, T, d, F, 0, 0, 1);
         sb_gemm_keep_end(c);
         if (!full) { lora_bwd(c, l, 4, c->g_gate, a->x_norm_ffn, gx, T); lora_bwd(c, l, 5, c->g_up, a->x_norm_ffn, gx, T); }
+        sb_amax_announce(c, gh, (size_t)T * d);
         sb_rmsnorm_backward(c, a->post_attn_in, c->W + o->post_norm, gx, gh, gh, full ? Gd + o->post_norm : norm_sink, T, d, RMS_EPS);
         /* attention */
         if (full) sb_gemm_keep_begin(c);
@@ -492,6 +501,7 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
         if (!full) lora_bwd(c, l, 3, gh, a->attn_out, c->g_attn, T);
         sb_attention_backward(c, a->q, a->k, a->v, a->attn_out, a->lse, c->g_attn, c->g_q, c->g_k, c->g_v, 0,
                               c->seq_starts, c->seq_ids, B, T, c->Hq, c->Hkv, c->hd);
+        sb_amax_announce(c, c->g_q, (size_t)T * qd); sb_amax_announce(c, c->g_k, (size_t)T * kvd);
         sb_rope2(c, c->g_q, c->g_k, c->pos_ids, T, c->Hq, c->Hkv, c->hd, theta, max_seq, 1);
         if (full) {
             sb_gemm_keep_begin(c);
@@ -504,6 +514,7 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
         sb_gemm(c, c->g_v, c->W + o->v, gx, T, d, kvd, 0, 0, 1);
         sb_gemm_keep_end(c);
         if (!full) { lora_bwd(c, l, 0, c->g_q, a->x_norm_attn, gx, T); lora_bwd(c, l, 1, c->g_k, a->x_norm_attn, gx, T); lora_bwd(c, l, 2, c->g_v, a->x_norm_attn, gx, T); }
+        sb_amax_announce(c, gh, (size_t)T * d);
         sb_rmsnorm_backward(c, a->layer_in, c->W + o->in_norm, gx, gh, gh, full ? Gd + o->in_norm : norm_sink, T, d, RMS_EPS);
         if (reduce) {
             if (full) sb_dp_bucket_ready(c, Gd + o->q, o->post_norm + (size_t)d - o->q);
@@ -588,6 +599,7 @@ static float step_body(train_state_t* st, int* tokens, int T, int* seq_starts, i
         else sb_memset(c, c->LG, 0, c->n_lora * sizeof(float));
     }
     forward_pass(c, T, max_seq, theta, use_lora);
+    if (train) sb_amax_announce(c, c->dlogits, (size_t)T * c->V);
     sb_cross_entropy(c, c->logits, c->targets, c->dlogits, c->loss_rows, c->pos_ids, c->seq_ids, c->seq_starts, T, c->V, num_valid);
     sb_reduce_sum(c, c->loss_rows, c->d_loss, (size_t)T);
 

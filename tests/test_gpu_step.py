@@ -191,6 +191,57 @@ def test_c1_step_matches_oracle(ctx):
         print("C1 worst gradient rel-L2, GEMM mode", mode, ":", worst)
 
 
+def test_head128_model_step_matches_oracle(ctx):
+    """A model with 128-wide heads (grouped: 4 query / 2 K-V heads) on ragged sequences: the step runs the fused attention
+    kernels (forward in one kernel, backward scores in one kernel) and every gradient meets the bound."""
+    cfg = O.ModelCfg(V=1024, d=512, L=2, Hq=4, Hkv=2, hd=128, F=1024, theta=1e4)
+    p = cfg.init_params(21, norm_jitter=0.1)
+    ss = [0, 300, 512, 645]
+    tok = tokens_for(cfg, ss[-1], 22)
+    ref = O.train_step(cfg, p, tok, ss)
+    for flash in (1, 0):
+        ctx.set_attn_flash(flash)
+        got = run_full_step(ctx, cfg, p, tok, ss)
+        assert abs(got["loss"][0] - ref["loss"]) < 1e-5 * abs(ref["loss"])
+        worst = check_grads(cfg, got["grads"], ref["grads"])
+        print("128-wide heads, fused attention", flash, "worst gradient rel-L2:", worst)
+    ctx.set_attn_flash(1)
+
+
+def test_c1_lora_step_on_tensor_cores_matches_oracle(ctx):
+    """LoRA step at configuration-1 size (rank 16 on all seven projections, full chain rule): the frozen base runs through
+    the tensor-core products with shared operand parts, the adapters through the small-rank path."""
+    from seraph_b200 import api
+    cfg, rank, alpha, mask = C1, 16, 32.0, 0x7F
+    p = cfg.init_params(31)
+    tens, n = cfg.lora_tensors(rank, mask)
+    lo = (0.02 * np.random.default_rng(32).standard_normal(n)).astype(np.float32)
+    ss = list(range(0, 1025, 256))
+    tok = tokens_for(cfg, 1024, 33)
+    ref = O.train_step(cfg, p, tok, ss, lora=lo, rank=rank, alpha=alpha, mask=mask, lora_exact=1)
+    outs = []
+    for keep in (1, 0):
+        ctx.set_parts_cache(keep)
+        ctx.lib.seraph_b200_reset_model(ctx.h)
+        st = api.TrainState(cfg, p)
+        st.attach_lora(rank, alpha, mask, lo)
+        assert ctx.lib.seraph_b200_set_lora_exact(ctx.h, 1) == 0
+        loss = api.step_lora_batch(ctx, st, tok, ss)
+        ctx.check()
+        ctx.lib.cuda_download_lora_weights(ctx.h, st.lora_ptr())
+        g = st.lora_get(1)
+        outs.append((loss, g))
+        st.close()
+    ctx.set_parts_cache(1)
+    assert ctx.lib.seraph_b200_set_lora_exact(ctx.h, 0) == 0
+    loss, g = outs[0]
+    assert abs(loss - ref["loss"]) < 1e-5 * abs(ref["loss"])
+    for name, shp, off in tens:
+        k = int(np.prod(shp))
+        assert rel_l2(g[off:off + k], ref["grads"][off:off + k]) < TOL, (name, rel_l2(g[off:off + k], ref["grads"][off:off + k]))
+    assert outs[0][0] == outs[1][0] and np.array_equal(outs[0][1], outs[1][1])
+
+
 def test_operand_parts_kept_within_a_step_change_nothing(ctx):
     """The FP16 parts of weights and saved activations are made once per call and shared by the call's products.  Three
     optimizer steps (the weights move between them), then a step on fewer tokens and one on the full batch again: losses,

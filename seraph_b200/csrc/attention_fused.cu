@@ -406,9 +406,18 @@ at_score_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_consta
                     __half* __restrict__ P1, __half* __restrict__ P2, __half* __restrict__ dS1, __half* __restrict__ dS2,
                     const float* __restrict__ amax_q, const float* __restrict__ amax_k, const float* __restrict__ amax_v,
                     const float* __restrict__ amax_do, const float* __restrict__ ds_bound,
-                    int t0, int S, int Sp, int Hq, int g, int head0, int head_step, int nb, int nqb, float scale, int* status) {
-    const int qb = nqb - 1 - (int)blockIdx.x / nb;
-    const int hb = (int)blockIdx.x % nb, h = head0 + hb * head_step;
+                    const __grid_constant__ AfSeqs seqs, int Sp, int Hq, int g, int head0, int head_step, int nb, int nqb, float scale, int* status) {
+    // nb > 0: one sequence, heads head0 + i * head_step, output slot i.  nb == 0: every sequence and head of the call,
+    // output slot ((sequence * g + head % g) * Hkv + head / g), i.e. the Hkv heads of one (sequence, group member) side by side
+    const int nheads = nb > 0 ? nb : Hq;
+    const int per_i = seqs.n * nheads;
+    const int qb = nqb - 1 - (int)blockIdx.x / per_i;
+    const int rem = (int)blockIdx.x % per_i;
+    const int b = rem / nheads, hi = rem % nheads;
+    const int h = nb > 0 ? head0 + hi * head_step : hi;
+    const int hb = nb > 0 ? hi : (b * g + h % g) * (Hq / g) + h / g;
+    const int t0 = seqs.start[b], S = seqs.start[b + 1] - t0;
+    if (qb * AF_BQ >= S) return;
     if (*(volatile int*)status != 0) return;
     const int nkv = min((S + AF_BKV - 1) / AF_BKV, 2 * qb + 2);           // key blocks that hold scores
     const int nz = min(Sp / AF_BKV, 4 * (qb / 2 + 1));                    // key blocks that are written
@@ -639,28 +648,42 @@ extern "C" int sb_attention_fused_forward(sb_ctx_t* c, const void* q1, const voi
     return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
 
-// The backward score kernel for one sequence [t0, t0 + S) and the heads head0, head0 + head_step, ... (nb of them); the parts
-// P1..dS2 are [nb][Sp][Sp].  Returns 0 when launched.
+// The backward score kernel.  nb > 0: one sequence [t0, t0 + S) and the heads head0, head0 + head_step, ... (nb of them), the
+// parts P1..dS2 laid out [nb][Sp][Sp].  nb == 0: every sequence and head of the batch in one launch, parts laid out
+// [sequence][group member][K-V head][Sp][Sp] (t0, S, head0, head_step unused).  Returns 0 when launched.
 extern "C" int sb_attention_fused_scores(sb_ctx_t* c, const void* q1, const void* q2, const void* do1, const void* do2,
                                          const void* k1, const void* k2, const void* v1, const void* v2,
                                          const float* amax_q, const float* amax_k, const float* amax_v, const float* amax_do, const float* ds_bound,
                                          const float* lse, const float* D, void* P1, void* P2, void* dS1, void* dS2,
                                          int t0, int S, int Sp, int T, int Hq, int Hkv, int hd, int head0, int head_step, int nb) {
-    if (hd != AF_HD || S <= 0 || (Sp % 256) || nb <= 0 || !tc_load_encode()) return 1;
+    if (hd != AF_HD || (Sp % 256) || nb < 0 || !tc_load_encode()) return 1;
+    if (nb > 0 && S <= 0) return 1;
+    if (nb == 0 && (c->h_seq_n <= 0 || c->h_seq_n > AF_MAXSEQ)) return 1;
     static bool attr_done = false;
     if (!attr_done) {
         if (cudaFuncSetAttribute(at_score_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AS_SMEM) != cudaSuccess) { cudaGetLastError(); return 1; }
         attr_done = true;
     }
-    const int qd = Hq * hd, kvd = Hkv * hd, nqb = (S + AF_BQ - 1) / AF_BQ;
+    AfSeqs seqs;
+    int Smax = S;
+    if (nb > 0) { seqs.n = 1; seqs.start[0] = t0; seqs.start[1] = t0 + S; }
+    else {
+        seqs.n = c->h_seq_n; Smax = 0;
+        for (int b = 0; b <= c->h_seq_n; b++) seqs.start[b] = c->h_seq[b];
+        for (int b = 0; b < c->h_seq_n; b++) Smax = max(Smax, c->h_seq[b + 1] - c->h_seq[b]);
+        if (Smax <= 0) return 1;
+    }
+    const int qd = Hq * hd, kvd = Hkv * hd, nqb = (Smax + AF_BQ - 1) / AF_BQ;
     CUtensorMap mQ1, mQ2, mD1, mD2, mK1, mK2, mV1, mV2;
     if (!af_make_map(&mQ1, q1, T, qd, AF_BQ) || !af_make_map(&mQ2, q2, T, qd, AF_BQ) ||
         !af_make_map(&mD1, do1, T, qd, AF_BQ) || !af_make_map(&mD2, do2, T, qd, AF_BQ) ||
         !af_make_map(&mK1, k1, T, kvd, AF_BKV) || !af_make_map(&mK2, k2, T, kvd, AF_BKV) ||
         !af_make_map(&mV1, v1, T, kvd, AF_BKV) || !af_make_map(&mV2, v2, T, kvd, AF_BKV)) return 1;
-    at_score_bwd_kernel<<<(unsigned)(nqb * nb), AS_THREADS, AS_SMEM, (cudaStream_t)c->pub.stream>>>(
+    const long blocks = (long)nqb * seqs.n * (nb > 0 ? nb : Hq);
+    if (blocks > 0x7fffffffL) return 1;
+    at_score_bwd_kernel<<<(unsigned)blocks, AS_THREADS, AS_SMEM, (cudaStream_t)c->pub.stream>>>(
         mQ1, mQ2, mD1, mD2, mK1, mK2, mV1, mV2, lse, D, (__half*)P1, (__half*)P2, (__half*)dS1, (__half*)dS2,
-        amax_q, amax_k, amax_v, amax_do, ds_bound, t0, S, Sp, Hq, Hq / Hkv, head0, head_step, nb, nqb, 1.0f / sqrtf((float)hd), c->d_status);
+        amax_q, amax_k, amax_v, amax_do, ds_bound, seqs, Sp, Hq, Hq / Hkv, head0, head_step, nb, nqb, 1.0f / sqrtf((float)hd), c->d_status);
     c->launches++;
     return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }

@@ -25,6 +25,8 @@
 #include "gemm_tc.cuh"
 
 #define AT_ROWTILE 256                            // rows of a CTA pair's tile: P and dS are zeroed up to this boundary past the diagonal
+#define AT_ALL_SCORES_BYTES ((size_t)0)           // > 0: the backward scores of all sequences and heads in one launch when their parts fit this many bytes
+                                                  // (measured slower than a launch per sequence and head group, whose idle SMs the long products of other sequences fill)
 #define AT_SCRATCH_BUDGET (512.0 * 1024 * 1024)   // causal part of the score scratch per launch; measured: fewer, larger launches beat L2 residency
 
 static inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
@@ -396,7 +398,14 @@ extern "C" int sb_attention_tc_backward(sb_ctx_t* c, const float* Q, const float
     const size_t n_q = (size_t)T * qd, n_kv = (size_t)T * kvd;
     const size_t d_floats = ((size_t)T * Hq + 63) & ~(size_t)63;
     float* st0 = (float*)sb_gemm_stage(c, 2, (d_floats + 64) * sizeof(float) + (f16 ? (2 * n_q + 2 * n_kv) * 2 * sizeof(__half) : 0));
-    float* bb = (float*)sb_gemm_stage(c, 3, AT_SIDE * per_stream * sizeof(float));
+    // 128-wide heads, default mode: S, dP, P, dS of every sequence and head come from one launch that leaves only the FP16
+    // parts of P and dS ([sequence][group member][K-V head][Sp][Sp], 8 bytes per score) when they fit the scratch limit
+    const size_t n_all = (size_t)c->h_seq_n * Hq * Sp * Sp;
+    size_t all_limit = AT_ALL_SCORES_BYTES;                          // SERAPH_B200_ATTN_ALL_SCORES_MB overrides (0, the default: one launch per sequence and head group)
+    { const char* e = getenv("SERAPH_B200_ATTN_ALL_SCORES_MB"); if (e && e[0]) all_limit = (size_t)atol(e) << 20; }
+    const bool all_scores = f16 && c->attn_flash && !c->attn_fused && hd == 128 && c->h_seq_n <= 240 && n_all * 8 <= all_limit;
+    const size_t group_bytes = AT_SIDE * per_stream * sizeof(float);
+    float* bb = (float*)sb_gemm_stage(c, 3, all_scores ? (n_all * 8 > group_bytes ? n_all * 8 : group_bytes) : group_bytes);
     if (!st0 || !bb) return 1;
     float* D = st0;
     float* consts = st0 + d_floats;                                  // [0] 1.0, [1] dS bound, [2] max |dO row|, [3] max |V row|, [8..11] amax of Q, K, V, dO
@@ -420,6 +429,13 @@ extern "C" int sb_attention_tc_backward(sb_ctx_t* c, const float* Q, const float
     bool ok = true;
     double flops = 0;
     void* main_stream = c->pub.stream;
+    bool have_all = false;
+    if (all_scores) {
+        __half* a = (__half*)bb;
+        have_all = sb_attention_fused_scores(c, pq.h1, pq.h2, pdo.h1, pdo.h2, pk.h1, pk.h2, pv.h1, pv.h2, pq.amax, pk.amax, pv.amax, pdo.amax,
+                                             consts + 1, lse, D, a, a + n_all, a + 2 * n_all, a + 3 * n_all, 0, 0, Sp, T, Hq, Hkv, hd, 0, 0, 0) == 0;
+    }
+    const int Gl = have_all ? Hkv : G;                               // K-V heads per launch of the long products
     const int ns = at_fork(c, c->h_seq_n);
     for (int b = 0; b < c->h_seq_n && ok; b++) {
         const int t0 = c->h_seq[b], S = c->h_seq[b + 1] - t0;
@@ -427,15 +443,20 @@ extern "C" int sb_attention_tc_backward(sb_ctx_t* c, const float* Q, const float
         flops += 5.0 * Hq * (double)S * S * hd;
         if (ns > 1) c->pub.stream = c->side_stream[b % ns];
         cudaStream_t s = (cudaStream_t)c->pub.stream;
-        float* b0 = bb + (size_t)(b % ns) * per_stream; float* b1 = b0 + n_s;
-        __half* P1 = f16 ? (__half*)(b0 + 2 * n_s) : nullptr; __half* P2 = f16 ? P1 + n_s : nullptr;
-        __half* dS1 = f16 ? P2 + n_s : nullptr; __half* dS2 = f16 ? dS1 + n_s : nullptr;
-        const AtParts pp = {P1, P2, consts}, pds = {dS1, dS2, f16 ? consts + 1 : nullptr};
+        float* b0 = have_all ? bb : bb + (size_t)(b % ns) * per_stream; float* b1 = have_all ? bb : b0 + n_s;
         for (int r = 0; r < g && ok; r++)
-            for (int i0 = 0; i0 < Hkv && ok; i0 += G) {
-                const int nb = min(G, Hkv - i0), qh0 = r + i0 * g;
+            for (int i0 = 0; i0 < Hkv && ok; i0 += Gl) {
+                const int nb = min(Gl, Hkv - i0), qh0 = r + i0 * g;
                 const long sb = (long)Sp * Sp;
-                if (c->attn_fused) {
+                __half* P1 = f16 ? (__half*)(b0 + 2 * n_s) : nullptr; __half* P2 = f16 ? P1 + n_s : nullptr;
+                __half* dS1 = f16 ? P2 + n_s : nullptr; __half* dS2 = f16 ? dS1 + n_s : nullptr;
+                if (have_all) {
+                    P1 = (__half*)bb + ((size_t)(b * g + r) * Hkv) * (size_t)sb; P2 = P1 + n_all; dS1 = P2 + n_all; dS2 = dS1 + n_all;
+                }
+                const AtParts pp = {P1, P2, consts}, pds = {dS1, dS2, f16 ? consts + 1 : nullptr};
+                if (have_all) {
+                    // scores already made
+                } else if (c->attn_fused) {
                     // P = exp(S*scale - lse) and dS = P o (dP - D) * scale come straight out of the two products' epilogues (TF32 parts)
                     const TcEpi e_p = at_epi(TC_EPI_EXP, scale, lse, t0, Hq, qh0, g, nullptr);
                     const TcEpi e_ds = at_epi(TC_EPI_DS, scale, D, t0, Hq, qh0, g, b0);

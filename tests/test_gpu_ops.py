@@ -2,6 +2,8 @@
 the C ABI and compared with the CPU oracle on the same seeded inputs.
 Tolerances: 1e-5 relative L2 for floating point (most ops land near 1e-7),
 bit-exact for integer tables; every kernel must give the same bits twice."""
+import os
+
 import numpy as np
 import pytest
 
@@ -190,13 +192,14 @@ def test_attention_forward_backward(ctx, ss, Hq, Hkv, hd, fused):
     ctx.release(bq, bk, bv, bdo, bs, bout, blse, bdq, bdk, bdv, bdk2, bdv2)
 
 
-@pytest.mark.parametrize("flash", [1, 0])
+@pytest.mark.parametrize("flash", [1, 2, 0])
 @pytest.mark.parametrize("ss,Hq,Hkv", [([0, 257], 4, 1), ([0, 1024], 4, 1), ([0, 100, 420, 1000], 4, 2), ([0, 1, 130, 131, 450], 2, 2),
                                        ([0, 2048, 2100], 6, 3)])
 def test_attention_head128_one_kernel_paths(ctx, ss, Hq, Hkv, flash):
     """Head size 128, default GEMM mode.  flash = 1: the forward is one kernel (scores in tensor memory, online softmax)
-    and the backward's S, dP, P, dS come from one kernel that writes only the FP16 parts of P and dS; flash = 0: a launch
-    per product over a score scratch.  Both against the oracle, and bit-reproducible."""
+    and the backward's S, dP, P, dS come from one kernel launch per sequence and head group that writes only the FP16
+    parts of P and dS (flash = 2: one such launch for the whole call, an option that is measured slower at full size);
+    flash = 0: a launch per product over a score scratch.  Both against the oracle, and bit-reproducible."""
     hd = 128
     ss = np.array(ss, np.uint32)
     T, B = int(ss[-1]), len(ss) - 1
@@ -208,7 +211,9 @@ def test_attention_head128_one_kernel_paths(ctx, ss, Hq, Hkv, flash):
     dQ_ref, dK_ref, dV_ref = np.empty_like(Q), np.zeros_like(K), np.zeros_like(V)
     O.lib().ref_attention_backward(Q, K, V, dO, dQ_ref, dK_ref, dV_ref, ss, T, B, Hq, Hkv, hd)
     bq, bk, bv, bdo, bs = ctx.upload(Q), ctx.upload(K), ctx.upload(V), ctx.upload(dO), ctx.upload(ss)
-    ctx.set_attn_flash(flash)
+    ctx.set_attn_flash(1 if flash else 0)
+    if flash == 2:                                    # backward scores: one launch per call instead of one per sequence and head group
+        os.environ["SERAPH_B200_ATTN_ALL_SCORES_MB"] = "4096"
     runs = []
     for rep in range(2):
         bout, blse = ctx.zeros(Q.size), ctx.zeros(T * Hq)
@@ -224,6 +229,7 @@ def test_attention_head128_one_kernel_paths(ctx, ss, Hq, Hkv, flash):
         runs.append([x.numpy() for x in (bout, blse, bdq, bdk, bdv)])
         ctx.release(bout, blse, bdq, bdk, bdv)
     ctx.set_attn_flash(1)
+    os.environ.pop("SERAPH_B200_ATTN_ALL_SCORES_MB", None)
     errs = [rel_l2(a, b) for a, b in zip(runs[0], (out_ref, lse_ref, dQ_ref, dK_ref, dV_ref))]
     assert max(errs) < TOL, errs
     assert all(np.array_equal(a, b) for a, b in zip(runs[0], runs[1]))

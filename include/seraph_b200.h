@@ -174,6 +174,11 @@ int seraph_b200_set_gemm_tail_split(cuda_train_context_t* ctx, int on);
  * product of the call that reads the same tensor (arena of 4 bytes per element, taken only while an eighth of the
  * device stays free); 0: every product or run of products prepares its own operands.  Results are identical. */
 int seraph_b200_set_parts_cache(cuda_train_context_t* ctx, int on);
+/* cuda_evaluate (include/train_cuda.h:60-64 of the reference, src/train_cuda.c:2812-2846) runs one forward pass per
+ * validation sample there; here it packs samples into passes of up to `tokens` tokens (default 8192, at least
+ * max_seq_len, at most 256 samples; SERAPH_B200_EVAL_BATCH_TOKENS sets the default) and takes every sample's mean loss
+ * from the per-token losses of the pass.  0 = one pass per sample. */
+int seraph_b200_set_eval_batch_tokens(cuda_train_context_t* ctx, int tokens);
 /* Attention forward of 128-wide heads in the default GEMM mode: 1 = one kernel per call that keeps the scores in
  * tensor memory and the probabilities in shared memory (online softmax, no score-sized scratch); 0 = score product,
  * row softmax and value product as separate launches over a score scratch.  SERAPH_B200_ATTN_FLASH sets the default. */

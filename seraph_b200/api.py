@@ -80,7 +80,7 @@ def load():
         "cuda_profiler_set_launch": (None, [vp, i, i, i, i, i, i, i, sz]), "cuda_profiler_set_flops": (None, [vp, i, sz]),
         "cuda_profiler_set_bytes": (None, [vp, i, sz]), "cuda_profiler_sync_and_analyze": (None, [vp, vp]),
         "cuda_profiler_print": (None, [vp]), "cuda_profiler_print_top": (None, [vp, i]), "cuda_profiler_set_log": (None, [vp, vp]),
-        "seraph_b200_last_status": (i, [vp]), "seraph_b200_set_gemm_mode": (i, [vp, i]), "seraph_b200_set_gemm_pair": (i, [vp, i]), "seraph_b200_set_gemm_tail_split": (i, [vp, i]), "seraph_b200_set_parts_cache": (i, [vp, i]), "seraph_b200_set_attn_fused": (i, [vp, i]), "seraph_b200_set_attn_flash": (i, [vp, i]),
+        "seraph_b200_last_status": (i, [vp]), "seraph_b200_set_gemm_mode": (i, [vp, i]), "seraph_b200_set_gemm_pair": (i, [vp, i]), "seraph_b200_set_gemm_tail_split": (i, [vp, i]), "seraph_b200_set_parts_cache": (i, [vp, i]), "seraph_b200_set_attn_fused": (i, [vp, i]), "seraph_b200_set_attn_flash": (i, [vp, i]), "seraph_b200_set_eval_batch_tokens": (i, [vp, i]),
         "seraph_b200_set_lora_exact": (i, [vp, i]), "seraph_b200_set_grad_clip": (i, [vp, f]),
         "seraph_b200_launch_count": (C.c_ulonglong, [vp, i]),
         "seraph_b200_embedding_segments": (i, [vp, i, i, vp, vp, vp]),

@@ -192,6 +192,38 @@ __global__ void at_delta_kernel(const float* __restrict__ dO, const float* __res
     if (lane == 0) D[w] = s;
 }
 
+// The same D for 128-wide heads, together with what the FP16 split of dO and the bound of dS need from the same rows:
+// the largest |dO| (amax) and the largest row norm of dO (norm_max), both raised with integer atomicMax on the float
+// bits (order-free; zeroed before).  One warp per four (t,h) rows, a float4 per lane and row.
+__global__ void __launch_bounds__(256) at_bwd_prep128_kernel(const float* __restrict__ dO, const float* __restrict__ O, float* __restrict__ D,
+                                                             int n_th, unsigned* __restrict__ norm_max, unsigned* __restrict__ amax) {
+    const int lane = threadIdx.x & 31, nwarps = (gridDim.x * blockDim.x) >> 5;
+    float bn = 0.f, ba = 0.f;
+    for (int r0 = ((blockIdx.x * blockDim.x + threadIdx.x) >> 5) * 4; r0 < n_th; r0 += nwarps * 4) {
+        float d[4], n2[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            d[i] = 0.f; n2[i] = 0.f;
+            if (r0 + i < n_th) {
+                const float4 g = __ldg((const float4*)(dO + (size_t)(r0 + i) * 128) + lane);
+                const float4 o = __ldg((const float4*)(O + (size_t)(r0 + i) * 128) + lane);
+                d[i] = g.x * o.x + g.y * o.y + g.z * o.z + g.w * o.w;
+                n2[i] = g.x * g.x + g.y * g.y + g.z * g.z + g.w * g.w;
+                ba = sb_amax4(ba, g);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float ds = warp_sum_f(d[i]);
+            bn = fmaxf(bn, warp_sum_f(n2[i]));
+            if (lane == 0 && r0 + i < n_th) D[r0 + i] = ds;
+        }
+    }
+    sb_block_amax(sqrtf(bn), norm_max);
+    __syncthreads();
+    sb_block_amax(ba, amax);
+}
+
 // ---------------------------------------------------------------------------------------------
 
 // FP16 parts for the attention products: the default GEMM mode, head sizes that fill whole 32-element k blocks
@@ -242,7 +274,7 @@ static bool at_gemm(sb_ctx_t* c, const TcOperand& A, const TcOperand& B, float* 
     return tc_launch(c, p, 3);
 }
 // FP16 parts of x[n] into h[0..n) and h[n..2n), its largest magnitude into *amax
-static AtParts at_make_parts(sb_ctx_t* c, const float* x, size_t n, __half* h, float* amax) {
+static AtParts at_make_parts(sb_ctx_t* c, const float* x, size_t n, __half* h, float* amax, bool amax_known = false) {
     cudaStream_t st = (cudaStream_t)c->pub.stream;
     void* kept; float* kept_amax; int fresh;
     if (sb_parts_find(c, x, n, &kept, &kept_amax, &fresh)) {          // q, k, v of a training step: made in the forward pass, read again here
@@ -252,7 +284,7 @@ static AtParts at_make_parts(sb_ctx_t* c, const float* x, size_t n, __half* h, f
     const dim3 pg(tc_ew_blocks(c, n / 4), 1);
     float* left = sb_amax_lookup(c, x, n);                            // the kernel that wrote x may have left its largest magnitude
     if (left) { amax = left; sb_parts_set_amax(c, x, left); }
-    else {
+    else if (!amax_known) {
         cudaMemsetAsync(amax, 0, sizeof(float), st);
         tc_amax_kernel<<<pg, 256, 0, st>>>(x, n / 4, (unsigned*)amax, nullptr, 0, nullptr);
         c->launches++;
@@ -412,6 +444,11 @@ extern "C" int sb_attention_tc_backward(sb_ctx_t* c, const float* Q, const float
     AtParts pq = AT_NOPARTS, pk = AT_NOPARTS, pv = AT_NOPARTS, pdo = AT_NOPARTS;
     cudaStream_t s0 = (cudaStream_t)c->pub.stream;
     int tk = sb_tick_begin(c, SB_CLS_ATTN_BWD);
+    const bool prep128 = f16 && hd == 128 && tc_aligned16(dO) && tc_aligned16(O);      // D, max |dO| and its largest row norm in one pass
+    if (prep128) {
+        cudaMemsetAsync(consts + 2, 0, 10 * sizeof(float), s0);
+        at_bwd_prep128_kernel<<<at_rn_blocks(c, T * Hq), 256, 0, s0>>>(dO, O, D, T * Hq, (unsigned*)(consts + 2), (unsigned*)(consts + 11));
+    } else
     at_delta_kernel<<<(T * Hq * 32 + 255) / 256, 256, 0, s0>>>(dO, O, D, T * Hq, hd);
     c->launches++;
     if (f16) {
@@ -419,12 +456,15 @@ extern "C" int sb_attention_tc_backward(sb_ctx_t* c, const float* Q, const float
         pq = at_make_parts(c, Q, n_q, hb, consts + 8);
         pk = at_make_parts(c, K, n_kv, hb + 2 * n_q, consts + 9);
         pv = at_make_parts(c, V, n_kv, hb + 2 * n_q + 2 * n_kv, consts + 10);
-        pdo = at_make_parts(c, dO, n_q, hb + 2 * n_q + 4 * n_kv, consts + 11);
-        cudaMemsetAsync(consts + 2, 0, 2 * sizeof(float), s0);
-        at_rownorm_max_kernel<<<at_rn_blocks(c, T * Hq), 256, 0, s0>>>(dO, T * Hq, hd, (unsigned*)(consts + 2));
+        pdo = at_make_parts(c, dO, n_q, hb + 2 * n_q + 4 * n_kv, consts + 11, prep128);
+        if (!prep128) {
+            cudaMemsetAsync(consts + 2, 0, 2 * sizeof(float), s0);
+            at_rownorm_max_kernel<<<at_rn_blocks(c, T * Hq), 256, 0, s0>>>(dO, T * Hq, hd, (unsigned*)(consts + 2));
+            c->launches++;
+        }
         at_rownorm_max_kernel<<<at_rn_blocks(c, T * Hkv), 256, 0, s0>>>(V, T * Hkv, hd, (unsigned*)(consts + 3));
         at_consts_kernel<<<1, 1, 0, s0>>>(consts, consts + 2, scale);
-        c->launches += 3;
+        c->launches += 2;
     }
     bool ok = true;
     double flops = 0;

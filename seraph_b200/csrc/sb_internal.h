@@ -72,6 +72,7 @@ typedef struct sb_ctx {
     struct { const float* ptr; size_t n; } *hint_tab; int hint_n, hint_cap; float* hint_pool;
     struct { const float* ptr; size_t n; } hint_pending[4]; int hint_npending;
     unsigned parts_gen; int parts_open; int parts_cache;   /* parts_cache 0: off (switch, or the arena did not fit) */
+    int eval_batch_tokens;           /* cuda_evaluate packs samples up to this many tokens per forward pass; 0: one sample per pass */
     int attn_flash;                  /* 1: attention forward of 128-wide heads runs as one kernel (no score scratch) */
     int attn_fused;                  /* 1: P and dS of the attention backward come out of the score products' epilogues */
     int gemm_tail_split;             /* 1: tiles of the last partial wave are cut into k pieces */

@@ -668,20 +668,66 @@ float cuda_eval_forward(train_state_t* state, int* tokens, int num_tokens, cuda_
     return step_common(state, tokens, num_tokens, ss, 1, ctx, full, 0, 0);
 }
 
-/* src/train_cuda.c:2812-2846: evenly spaced samples, mean loss, perplexity = exp(mean) */
+/* One packed forward pass over the samples gathered in pk[0..T) / ss[0..B]: every sample's mean loss is added to *total
+ * (and counted in *valid) from the per-token losses of the pass, summed per sample on the host in token order. */
+static void eval_flush(train_state_t* state, cuda_train_context_t* ctx, int* pk, int* ss, int B, int full, float* rows,
+                       double* total, int* valid) {
+    sb_ctx_t* c = sb_priv(ctx);
+    int T = ss[B];
+    if (B <= 0 || T <= 0) return;
+    float loss = step_common(state, pk, T, ss, B, ctx, full, 0, 0);
+    if (loss < 0.0f || isnan(loss)) return;
+    if (cudaMemcpy(rows, c->loss_rows, (size_t)T * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return; }
+    for (int b = 0; b < B; b++) {
+        double sum = 0.0;
+        int n = ss[b + 1] - ss[b];
+        for (int t = ss[b]; t < ss[b + 1] - 1; t++) sum += rows[t];       /* the last token of a sample predicts nothing */
+        float l = (float)(sum / (double)(n - 1));
+        if (l >= 0.0f && !isnan(l)) { *total += l; (*valid)++; }
+    }
+}
+
+/* src/train_cuda.c:2812-2846: evenly spaced samples, mean of the samples' mean losses, perplexity = exp(mean).  The reference
+ * runs one forward pass per sample; here the samples are packed, as many as fit eval_batch_tokens tokens (and at most 256),
+ * into one pass each (seraph_b200_set_eval_batch_tokens(ctx, 0) restores one pass per sample). */
+#define EVAL_MAX_SEQS 256
 float cuda_evaluate(train_state_t* state, int* val_tokens, int num_val_tokens, int* offsets, int num_samples, int max_seq_len,
                     int max_eval_samples, cuda_train_context_t* ctx, float* out_perplexity) {
-    if (!state || !val_tokens || num_samples <= 0 || !ctx) { if (out_perplexity) *out_perplexity = 0.0f; return -1.0f; }
+    if (!state || !val_tokens || !offsets || num_samples <= 0 || !ctx) { if (out_perplexity) *out_perplexity = 0.0f; return -1.0f; }
+    sb_ctx_t* c = sb_priv(ctx);
     int max_eval = max_eval_samples > 0 ? max_eval_samples : num_samples;
     int stride = num_samples > max_eval ? num_samples / max_eval : 1;
+    int budget = c ? c->eval_batch_tokens : 0;
     double total = 0.0; int valid = 0;
+    int* pk = NULL; int* ss = NULL; float* rows = NULL;
+    if (budget > 0) {
+        if (budget < max_seq_len) budget = max_seq_len;
+        pk = (int*)malloc((size_t)budget * sizeof(int));
+        ss = (int*)malloc((EVAL_MAX_SEQS + 1) * sizeof(int));
+        rows = (float*)malloc((size_t)budget * sizeof(float));
+        if (!pk || !ss || !rows) { free(pk); free(ss); free(rows); pk = NULL; budget = 0; }
+    }
+    int full = state->lora == NULL;
+    int B = 0;
+    if (budget > 0) ss[0] = 0;
     for (int s = 0; s < num_samples; s += stride) {
         int start = offsets[s], end = (s + 1 < num_samples) ? offsets[s + 1] : num_val_tokens;
         int n = end - start;
         if (n > max_seq_len) n = max_seq_len;
         if (n < 2) continue;
-        float loss = cuda_eval_forward(state, &val_tokens[start], n, ctx);
-        if (loss >= 0.0f && !isnan(loss)) { total += loss; valid++; }
+        if (budget <= 0) {
+            float loss = cuda_eval_forward(state, &val_tokens[start], n, ctx);
+            if (loss >= 0.0f && !isnan(loss)) { total += loss; valid++; }
+            continue;
+        }
+        if (B == EVAL_MAX_SEQS || ss[B] + n > budget) { eval_flush(state, ctx, pk, ss, B, full, rows, &total, &valid); B = 0; }
+        memcpy(pk + ss[B], &val_tokens[start], (size_t)n * sizeof(int));
+        ss[B + 1] = ss[B] + n;
+        B++;
+    }
+    if (budget > 0) {
+        eval_flush(state, ctx, pk, ss, B, full, rows, &total, &valid);
+        free(pk); free(ss); free(rows);
     }
     float avg = valid > 0 ? (float)(total / valid) : -1.0f;
     if (out_perplexity) *out_perplexity = avg > 0.0f ? expf(avg) : 0.0f;

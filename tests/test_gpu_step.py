@@ -191,6 +191,51 @@ def test_c1_step_matches_oracle(ctx):
         print("C1 worst gradient rel-L2, GEMM mode", mode, ":", worst)
 
 
+def test_evaluate_packs_samples_and_matches_per_sample_passes(ctx):
+    """cuda_evaluate: mean of the samples' mean losses and its exponential.  Packed passes (default), one pass per sample
+    (the reference's loop) and the oracle's forward loss per sample agree; the stride rule for max_eval_samples and the
+    max_seq_len cut are the reference's (src/train_cuda.c:2812-2846)."""
+    import ctypes as C
+    from seraph_b200 import api
+    cfg = TINY
+    p = cfg.init_params(41, norm_jitter=0.1)
+    lens = [9, 2, 17, 1, 24, 5, 30, 12, 3]                # one sample too short to predict anything, one longer than max_seq_len
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    val = tokens_for(cfg, int(offs[-1]), 42)
+    max_seq = 24
+
+    def oracle_mean(sample_ids):
+        tot, cnt = 0.0, 0
+        for s in sample_ids:
+            n = min(lens[s], max_seq)
+            if n < 2:
+                continue
+            t = np.ascontiguousarray(val[offs[s]:offs[s] + n])
+            tot += O.train_step(cfg, p, t, [0, n])["loss"]; cnt += 1
+        return tot / cnt
+
+    st = api.TrainState(cfg, p)
+    ctx.lib.seraph_b200_reset_model(ctx.h)
+    ppl = C.c_float(0)
+    offsets = np.ascontiguousarray(offs[:-1])
+    for max_eval, ids in ((0, range(len(lens))), (4, range(0, len(lens), 2))):
+        ref = oracle_mean(ids)
+        got = {}
+        for budget in (8192, 40, 0):                      # everything in one pass / several passes / one pass per sample
+            assert ctx.lib.seraph_b200_set_eval_batch_tokens(ctx.h, budget) == 0
+            n0 = ctx.launches()
+            got[budget] = ctx.lib.cuda_evaluate(st.h, val.ctypes.data, int(offs[-1]), offsets.ctypes.data, len(lens), max_seq, max_eval,
+                                                ctx.h, C.byref(ppl))
+            ctx.check()
+            got[(budget, "launches")] = ctx.launches() - n0
+            assert abs(got[budget] - ref) < 1e-5 * ref, (budget, got[budget], ref)
+            assert abs(ppl.value - np.exp(got[budget])) < 1e-4 * ppl.value
+        assert got[(8192, "launches")] < got[(0, "launches")]
+    assert ctx.lib.seraph_b200_set_eval_batch_tokens(ctx.h, 8192) == 0
+    assert st.counters() == (0, 0)                        # evaluation leaves the optimizer state alone
+    st.close()
+
+
 def test_head128_model_step_matches_oracle(ctx):
     """A model with 128-wide heads (grouped: 4 query / 2 K-V heads) on ragged sequences: the step runs the fused attention
     kernels (forward in one kernel, backward scores in one kernel) and every gradient meets the bound."""

@@ -174,6 +174,17 @@ int seraph_b200_set_gemm_tail_split(cuda_train_context_t* ctx, int on);
  * product of the call that reads the same tensor (arena of 4 bytes per element, taken only while an eighth of the
  * device stays free); 0: every product or run of products prepares its own operands.  Results are identical. */
 int seraph_b200_set_parts_cache(cuda_train_context_t* ctx, int on);
+/* Q/K normalisation over the whole token row (all heads), in place: y = x / max(sqrt(mean(x^2)), eps).  Replaces
+ * vulkan_qk_norm (include/vulkan_backend.h:600, shaders/qk_norm.comp:30-76; called on Q and K after RoPE,
+ * src/train.c:4688-4689); the reference's CUDA backend has no such kernel.  use_qk_norm == 0: no-op, as there.
+ * rms_out (may be NULL): sqrt(mean(x^2)) of every row before the clamp, [seq_len] floats, for the backward call. */
+void seraph_b200_qk_norm(cuda_train_context_t* ctx, cuda_buffer_t* qk, cuda_buffer_t* rms_out, int seq_len, int num_heads, int head_dim,
+                         int use_qk_norm, float eps);
+/* Backward of the above (the reference has none: its training passes the gradient through unchanged).
+ * rms > eps: grad_in = (grad_out - y * mean(grad_out o y)) / rms; clamp active: grad_in = grad_out / eps.
+ * qk_out and rms are what the forward call left; grad_in may be grad_out. */
+void seraph_b200_qk_norm_backward(cuda_train_context_t* ctx, cuda_buffer_t* qk_out, cuda_buffer_t* rms, cuda_buffer_t* grad_out,
+                                  cuda_buffer_t* grad_in, int seq_len, int num_heads, int head_dim, int use_qk_norm, float eps);
 /* cuda_evaluate (include/train_cuda.h:60-64 of the reference, src/train_cuda.c:2812-2846) runs one forward pass per
  * validation sample there; here it packs samples into passes of up to `tokens` tokens (default 8192, at least
  * max_seq_len, at most 256 samples; SERAPH_B200_EVAL_BATCH_TOKENS sets the default) and takes every sample's mean loss
@@ -272,6 +283,8 @@ void seraph_b200_state_get(train_state_t* st, int which, float* flat);
 void seraph_b200_state_set_counters(train_state_t* st, int optimizer_step, int accumulation_counter);
 void seraph_b200_state_get_counters(train_state_t* st, int* optimizer_step, int* accumulation_counter);
 void seraph_b200_state_set_lr(train_state_t* st, float lr, int accum);
+/* config->use_qk_norm of a state built by seraph_b200_state_create (the reference sets it for --video, src/train.c:7867-7868) */
+void seraph_b200_state_set_qk_norm(train_state_t* st, int on);
 size_t seraph_b200_state_lora_count(train_state_t* st, int rank, int mask);
 int seraph_b200_state_attach_lora(train_state_t* st, int rank, float alpha, int mask, const float* flat);
 void seraph_b200_state_lora_get(train_state_t* st, int which, float* flat);

@@ -322,6 +322,37 @@ void ref_rmsnorm_backward(const float* x, const float* scale, const float* dy, f
     free(acc);
 }
 
+/* shaders/qk_norm.comp:30-76 (called on Q and on K after RoPE, src/train.c:4688-4689): every token row of
+ * [seq_len, num_heads*head_dim] is divided by max(sqrt(mean(x^2)), eps), in place; use_qk_norm == 0 leaves it alone.
+ * rms_out (may be NULL) receives the row's sqrt(mean(x^2)) before the clamp: what a backward pass needs, since the
+ * in-place forward overwrites x. */
+void ref_qk_norm(float* qk, float* rms_out, int seq_len, int num_heads, int head_dim, int use_qk_norm, float eps) {
+    if (!use_qk_norm) return;
+    int n = num_heads * head_dim;
+    for (int t = 0; t < seq_len; t++) {
+        float* r = qk + (size_t)t * n;
+        double rms = sqrt(dotp(r, r, n, 1, 1) / n);
+        if (rms_out) rms_out[t] = (float)rms;
+        double inv = 1.0 / (rms > (double)eps ? rms : (double)eps);
+        for (int i = 0; i < n; i++) r[i] = (float)(r[i] * inv);
+    }
+}
+
+/* The reference has no backward for qk_norm (its training passes the gradient through unchanged).  This is the derivative of
+ * the forward above: with y = x / r, r = sqrt(mean(x^2)) > eps:  dx = (dy - y * mean(dy o y)) / r;  with the clamp active
+ * (r <= eps, y = x / eps):  dx = dy / eps.  y is the forward's output, rms its saved statistic. */
+void ref_qk_norm_backward(const float* y, const float* rms, const float* dy, float* dx, int seq_len, int num_heads, int head_dim,
+                          int use_qk_norm, float eps) {
+    int n = num_heads * head_dim;
+    for (int t = 0; t < seq_len; t++) {
+        const float* yr = y + (size_t)t * n; const float* gr = dy + (size_t)t * n; float* o = dx + (size_t)t * n;
+        if (!use_qk_norm) { for (int i = 0; i < n; i++) o[i] = gr[i]; continue; }
+        if (!(rms[t] > eps)) { for (int i = 0; i < n; i++) o[i] = (float)((double)gr[i] / (double)eps); continue; }
+        double m = dotp(gr, yr, n, 1, 1) / n, inv = 1.0 / (double)rms[t];
+        for (int i = 0; i < n; i++) o[i] = (float)(((double)gr[i] - (double)yr[i] * m) * inv);
+    }
+}
+
 /* src/cuda_train_context.cu:2175-2184 embedding_backward_kernel: dE[tok[t],:] += g[t,:] */
 void ref_embedding_backward(const uint32_t* tok, const float* g, float* dE, int T, int d) {
     for (int t = 0; t < T; t++)

@@ -26,6 +26,8 @@ void ref_embed_lookup(const uint32_t*, const float*, float*, int, int);
 void ref_rmsnorm(const float*, const float*, float*, int, int, float);
 void ref_matmul(const float*, const float*, float*, int, int, int, int, int, int);
 void ref_rope(const float*, float*, const uint32_t*, int, int, int, int, float, int);
+void ref_qk_norm(float*, float*, int, int, int, int, float);
+void ref_qk_norm_backward(const float*, const float*, const float*, float*, int, int, int, int, float);
 void ref_attention(const float*, const float*, const float*, float*, float*, const uint32_t*, int, int, int, int, int);
 void ref_attention_backward(const float*, const float*, const float*, const float*, float*, float*, float*,
                             const uint32_t*, int, int, int, int, int);
@@ -41,7 +43,7 @@ void ref_embedding_backward(const uint32_t*, const float*, float*, int, int);
 void ref_lora_backward(const float*, const float*, const float*, const float*, float*, float*, float*, int, int, int, int, float);
 void ref_lora_forward_add(const float*, float*, const float*, const float*, float*, int, int, int, int, float);
 
-typedef struct { int V, d, L, Hq, Hkv, hd, F; float eps, theta; } ref_cfg_t;
+typedef struct { int V, d, L, Hq, Hkv, hd, F; float eps, theta; int qk_norm; } ref_cfg_t;
 
 typedef struct { size_t q, k, v, o, gate, up, down, in_norm, post_norm; } layer_off_t;
 
@@ -142,6 +144,7 @@ float ref_train_step(const ref_cfg_t* c, const float* P, float* G,
           **c_k = malloc(sizeof(float*) * L), **c_v = malloc(sizeof(float*) * L), **c_att = malloc(sizeof(float*) * L),
           **c_pa = malloc(sizeof(float*) * L), **c_xf = malloc(sizeof(float*) * L), **c_g = malloc(sizeof(float*) * L),
           **c_u = malloc(sizeof(float*) * L), **c_s = malloc(sizeof(float*) * L), **c_fh = malloc(sizeof(float*) * L);
+    float **c_qr = calloc((size_t)L, sizeof(float*)), **c_kr = calloc((size_t)L, sizeof(float*));      /* row statistics of qk_norm */
     float* hidden = fbuf(Td); float* tmp = fbuf(Td); float* ltmp = fbuf((size_t)T * (rank > 0 ? rank : 1));
 
 #define LA(l, a) (lora + lora_off(c, rank, mask, l, a))
@@ -164,6 +167,11 @@ float ref_train_step(const ref_cfg_t* c, const float* P, float* G,
         if (HAS(2)) ref_lora_forward_add(c_xa[l], c_v[l], LA(l, 2), LB(l, 2, d), ltmp, T, d, kvd, rank, ls);
         ref_rope(c_q[l], c_q[l], ss, T, B, Hq, hd, theta, 0);
         ref_rope(c_k[l], c_k[l], ss, T, B, Hkv, hd, theta, 0);
+        if (c->qk_norm) {       /* shaders/qk_norm.comp after RoPE (src/train.c:4688-4689) */
+            c_qr[l] = fbuf((size_t)T); c_kr[l] = fbuf((size_t)T);
+            ref_qk_norm(c_q[l], c_qr[l], T, Hq, hd, 1, eps);
+            ref_qk_norm(c_k[l], c_kr[l], T, Hkv, hd, 1, eps);
+        }
         c_att[l] = fbuf(Tq);
         ref_attention(c_q[l], c_k[l], c_v[l], c_att[l], NULL, ss, T, B, Hq, Hkv, hd);
         ref_matmul(c_att[l], P + o->o, tmp, T, d, qd, 0, 1, 0);
@@ -234,6 +242,10 @@ float ref_train_step(const ref_cfg_t* c, const float* P, float* G,
         LORA_BWD(3, gh, c_att[l], qd, d, ga)
         memset(gk, 0, Tkv * 4); memset(gv, 0, Tkv * 4);
         ref_attention_backward(c_q[l], c_k[l], c_v[l], ga, gq, gk, gv, ss, T, B, Hq, Hkv, hd);
+        if (c->qk_norm) {
+            ref_qk_norm_backward(c_q[l], c_qr[l], gq, gq, T, Hq, hd, 1, eps);
+            ref_qk_norm_backward(c_k[l], c_kr[l], gk, gk, T, Hkv, hd, 1, eps);
+        }
         ref_rope(gq, gq, ss, T, B, Hq, hd, theta, 1);
         ref_rope(gk, gk, ss, T, B, Hkv, hd, theta, 1);
         if (full) {
@@ -258,7 +270,9 @@ float ref_train_step(const ref_cfg_t* c, const float* P, float* G,
     for (int l = 0; l < L; l++) {
         free(c_in[l]); free(c_xa[l]); free(c_q[l]); free(c_k[l]); free(c_v[l]); free(c_att[l]);
         free(c_pa[l]); free(c_xf[l]); free(c_g[l]); free(c_u[l]); free(c_s[l]); free(c_fh[l]);
+        free(c_qr[l]); free(c_kr[l]);
     }
+    free(c_qr); free(c_kr);
     free(c_in); free(c_xa); free(c_q); free(c_k); free(c_v); free(c_att); free(c_pa); free(c_xf);
     free(c_g); free(c_u); free(c_s); free(c_fh);
     free(hidden); free(tmp); free(ltmp); free(final_in); free(hn); free(logits); free(dlog); free(loss_rows);

@@ -80,7 +80,7 @@ def load():
         "cuda_profiler_set_launch": (None, [vp, i, i, i, i, i, i, i, sz]), "cuda_profiler_set_flops": (None, [vp, i, sz]),
         "cuda_profiler_set_bytes": (None, [vp, i, sz]), "cuda_profiler_sync_and_analyze": (None, [vp, vp]),
         "cuda_profiler_print": (None, [vp]), "cuda_profiler_print_top": (None, [vp, i]), "cuda_profiler_set_log": (None, [vp, vp]),
-        "seraph_b200_last_status": (i, [vp]), "seraph_b200_set_gemm_mode": (i, [vp, i]), "seraph_b200_set_gemm_pair": (i, [vp, i]), "seraph_b200_set_gemm_tail_split": (i, [vp, i]), "seraph_b200_set_parts_cache": (i, [vp, i]), "seraph_b200_set_attn_fused": (i, [vp, i]), "seraph_b200_set_attn_flash": (i, [vp, i]), "seraph_b200_set_eval_batch_tokens": (i, [vp, i]),
+        "seraph_b200_last_status": (i, [vp]), "seraph_b200_set_gemm_mode": (i, [vp, i]), "seraph_b200_set_gemm_pair": (i, [vp, i]), "seraph_b200_set_gemm_tail_split": (i, [vp, i]), "seraph_b200_set_parts_cache": (i, [vp, i]), "seraph_b200_set_attn_fused": (i, [vp, i]), "seraph_b200_set_attn_flash": (i, [vp, i]), "seraph_b200_qk_norm": (None, [vp, vp, vp, i, i, i, i, f]), "seraph_b200_qk_norm_backward": (None, [vp, vp, vp, vp, vp, i, i, i, i, f]), "seraph_b200_set_eval_batch_tokens": (i, [vp, i]),
         "seraph_b200_set_lora_exact": (i, [vp, i]), "seraph_b200_set_grad_clip": (i, [vp, f]),
         "seraph_b200_launch_count": (C.c_ulonglong, [vp, i]),
         "seraph_b200_embedding_segments": (i, [vp, i, i, vp, vp, vp]),
@@ -98,7 +98,7 @@ def load():
         "seraph_b200_state_param_count": (sz, [vp]), "seraph_b200_state_set": (None, [vp, i, vp]),
         "seraph_b200_state_get": (None, [vp, i, vp]), "seraph_b200_state_set_counters": (None, [vp, i, i]),
         "seraph_b200_state_get_counters": (None, [vp, C.POINTER(i), C.POINTER(i)]),
-        "seraph_b200_state_set_lr": (None, [vp, f, i]), "seraph_b200_state_lora_count": (sz, [vp, i, i]),
+        "seraph_b200_state_set_lr": (None, [vp, f, i]), "seraph_b200_state_set_qk_norm": (None, [vp, i]), "seraph_b200_state_lora_count": (sz, [vp, i, i]),
         "seraph_b200_state_attach_lora": (i, [vp, i, f, i, vp]), "seraph_b200_state_lora_get": (None, [vp, i, vp]),
     }
     missing = []
@@ -250,6 +250,8 @@ class TrainState:
             assert params.size == self.n, (params.size, self.n)
             self.lib.seraph_b200_state_set(self.h, 0, _p(params))
         self.n_lora = 0
+        if getattr(cfg, "qk_norm", 0):
+            self.lib.seraph_b200_state_set_qk_norm(self.h, 1)
 
     def close(self):
         if self.h:

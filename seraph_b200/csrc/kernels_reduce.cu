@@ -331,6 +331,96 @@ __global__ void __launch_bounds__(RB_THREADS) softmax_kernel(const float* __rest
 }
 
 // ---------------------------------------------------------------------------
+// Q/K normalisation over the whole token row (all heads): y = x / max(sqrt(mean(x^2)), eps), in place
+// (shaders/qk_norm.comp:30-76; the CUDA backend of the reference does not have it), and its backward, which the
+// reference lacks: r > eps: dx = (dy - y * mean(dy o y)) / r;  clamp active: dx = dy / eps.  The forward keeps r per
+// row because it overwrites x.  One warp per row, the row in registers (cols % 4 == 0, cols <= 128 * NV): 8 bytes
+// per element forward, 12 backward.  Other shapes: one CTA per row.
+// ---------------------------------------------------------------------------
+template <int NV>
+__global__ void __launch_bounds__(RB_THREADS) qk_norm_warp_kernel(float* __restrict__ x, float* __restrict__ rms_out, int rows, int cols, float eps) {
+    const int lane = threadIdx.x & 31, warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+    const int c4 = cols >> 2;
+    for (int r = warp; r < rows; r += nwarps) {
+        float4* xr = (float4*)(x + (size_t)r * cols);
+        float4 v[NV];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            const int j = lane + 32 * i;
+            v[i] = j < c4 ? xr[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+            ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+        }
+        ss = warp_sum(ss);
+        const float rms = sqrtf(ss / cols);
+        if (lane == 0 && rms_out) rms_out[r] = rms;
+        const float inv = 1.0f / fmaxf(rms, eps);
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            const int j = lane + 32 * i;
+            if (j < c4) xr[j] = make_float4(v[i].x * inv, v[i].y * inv, v[i].z * inv, v[i].w * inv);
+        }
+    }
+}
+template <int NV>
+__global__ void __launch_bounds__(RB_THREADS) qk_norm_bwd_warp_kernel(const float* __restrict__ y, const float* __restrict__ rms,
+                                                                      const float* dy, float* dx, int rows, int cols, float eps) {
+    const int lane = threadIdx.x & 31, warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+    const int c4 = cols >> 2;
+    for (int r = warp; r < rows; r += nwarps) {
+        const float4* yr = (const float4*)(y + (size_t)r * cols);
+        const float4* gr = (const float4*)(dy + (size_t)r * cols);
+        float4 v[NV], g[NV];
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            const int j = lane + 32 * i;
+            v[i] = j < c4 ? yr[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+            g[i] = j < c4 ? gr[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+            dot += v[i].x * g[i].x + v[i].y * g[i].y + v[i].z * g[i].z + v[i].w * g[i].w;
+        }
+        dot = warp_sum(dot);
+        const float rr = rms[r];
+        const bool live = rr > eps;
+        const float m = live ? dot / cols : 0.f, inv = 1.0f / (live ? rr : eps);
+        float4* o = (float4*)(dx + (size_t)r * cols);
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            const int j = lane + 32 * i;
+            if (j < c4) o[j] = make_float4((g[i].x - v[i].x * m) * inv, (g[i].y - v[i].y * m) * inv, (g[i].z - v[i].z * m) * inv, (g[i].w - v[i].w * m) * inv);
+        }
+    }
+}
+// any shape: one CTA per row, two passes over the row
+__global__ void __launch_bounds__(RB_THREADS) qk_norm_row_kernel(float* __restrict__ x, float* __restrict__ rms_out, const float* __restrict__ rms_in,
+                                                                 const float* dy, float* dx, int rows, int cols, float eps) {
+    __shared__ float red[RB_THREADS / 32];
+    __shared__ float tot;
+    for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+        // forward (dy == NULL): sum of x^2; backward: sum of dy*y (x then holds y)
+        const float* a = x + (size_t)r * cols; const float* b = dy ? dy + (size_t)r * cols : a;
+        float s = 0.f;
+        for (int i = threadIdx.x; i < cols; i += blockDim.x) s += a[i] * b[i];
+        s = warp_sum(s);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+        __syncthreads();
+        if (threadIdx.x == 0) { float t = 0.f; for (int w = 0; w < RB_THREADS / 32; w++) t += red[w]; tot = t; }
+        __syncthreads();
+        if (!dy) {
+            const float rms = sqrtf(tot / cols), inv = 1.0f / fmaxf(rms, eps);
+            if (threadIdx.x == 0 && rms_out) rms_out[r] = rms;
+            for (int i = threadIdx.x; i < cols; i += blockDim.x) x[(size_t)r * cols + i] = a[i] * inv;
+        } else {
+            const float rr = rms_in[r];
+            const bool live = rr > eps;
+            const float m = live ? tot / cols : 0.f, inv = 1.0f / (live ? rr : eps);
+            for (int i = threadIdx.x; i < cols; i += blockDim.x) dx[(size_t)r * cols + i] = (b[i] - a[i] * m) * inv;
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Cross-entropy loss and gradient, packed.  One CTA per row: an online
 // (max,sum) pass over the logits, then one pass that writes the gradient:
 // 12 bytes per logit where the reference's three passes move 20.
@@ -600,6 +690,46 @@ void sb_softmax(sb_ctx_t* c, const float* x, float* y, int rows, int cols) {
     if (rows <= 0 || cols <= 0) return;
     int grid = rows < sm_count(c) * 8 ? rows : sm_count(c) * 8;
     softmax_kernel<<<grid, RB_THREADS, 0, (cudaStream_t)c->pub.stream>>>(x, y, rows, cols);
+    c->launches++;
+}
+
+static int qk_wgrid(sb_ctx_t* c, int rows) {
+    int wgrid = (rows + 7) / 8, cap = sm_count(c) * 2;
+    int k = (wgrid + cap - 1) / cap; if (k < 1) k = 1;
+    return (wgrid + k - 1) / k;
+}
+void sb_qk_norm(sb_ctx_t* c, float* x, float* rms_out, int rows, int cols, float eps) {
+    if (rows <= 0 || cols <= 0) return;
+    cudaStream_t st = (cudaStream_t)c->pub.stream;
+    int tk = sb_tick_begin(c, SB_CLS_NORM_FWD);
+    if ((cols % 4) == 0 && cols <= 4096 && aligned16(x) && rows >= 64) {
+        const int g = qk_wgrid(c, rows);
+        if (cols <= 512)       qk_norm_warp_kernel<4><<<g, RB_THREADS, 0, st>>>(x, rms_out, rows, cols, eps);
+        else if (cols <= 1024) qk_norm_warp_kernel<8><<<g, RB_THREADS, 0, st>>>(x, rms_out, rows, cols, eps);
+        else if (cols <= 2048) qk_norm_warp_kernel<16><<<g, RB_THREADS, 0, st>>>(x, rms_out, rows, cols, eps);
+        else                   qk_norm_warp_kernel<32><<<g, RB_THREADS, 0, st>>>(x, rms_out, rows, cols, eps);
+    } else {
+        int grid = rows < sm_count(c) * 8 ? rows : sm_count(c) * 8;
+        qk_norm_row_kernel<<<grid, RB_THREADS, 0, st>>>(x, rms_out, NULL, NULL, NULL, rows, cols, eps);
+    }
+    sb_tick_end(c, tk, 0.0, 8.0 * rows * cols);
+    c->launches++;
+}
+void sb_qk_norm_backward(sb_ctx_t* c, const float* y, const float* rms, const float* dy, float* dx, int rows, int cols, float eps) {
+    if (rows <= 0 || cols <= 0) return;
+    cudaStream_t st = (cudaStream_t)c->pub.stream;
+    int tk = sb_tick_begin(c, SB_CLS_NORM_BWD);
+    if ((cols % 4) == 0 && cols <= 4096 && aligned16(y) && aligned16(dy) && aligned16(dx) && rows >= 64) {
+        const int g = qk_wgrid(c, rows);
+        if (cols <= 512)       qk_norm_bwd_warp_kernel<4><<<g, RB_THREADS, 0, st>>>(y, rms, dy, dx, rows, cols, eps);
+        else if (cols <= 1024) qk_norm_bwd_warp_kernel<8><<<g, RB_THREADS, 0, st>>>(y, rms, dy, dx, rows, cols, eps);
+        else if (cols <= 2048) qk_norm_bwd_warp_kernel<16><<<g, RB_THREADS, 0, st>>>(y, rms, dy, dx, rows, cols, eps);
+        else                   qk_norm_bwd_warp_kernel<32><<<g, RB_THREADS, 0, st>>>(y, rms, dy, dx, rows, cols, eps);
+    } else {
+        int grid = rows < sm_count(c) * 8 ? rows : sm_count(c) * 8;
+        qk_norm_row_kernel<<<grid, RB_THREADS, 0, st>>>((float*)y, NULL, rms, dy, dx, rows, cols, eps);
+    }
+    sb_tick_end(c, tk, 0.0, 12.0 * rows * cols);
     c->launches++;
 }
 

@@ -246,6 +246,28 @@ void cuda_train_rmsnorm_backward_batch(cuda_train_context_t* ctx, cuda_buffer_t*
     sb_rmsnorm_backward(c, input->data, scale->data, grad_output->data, NULL, grad_input->data, grad_scale->data, rows, cols, eps);
     sb_prof_end(c, op, 0, (size_t)rows * cols * 12);
 }
+// Q or K normalised over the whole token row, in place (include/vulkan_backend.h:600, shaders/qk_norm.comp); rms_out may be NULL
+void seraph_b200_qk_norm(cuda_train_context_t* ctx, cuda_buffer_t* qk, cuda_buffer_t* rms_out, int seq_len, int num_heads, int head_dim,
+                         int use_qk_norm, float eps) {
+    CTX_OR_RETURN(ctx); NEED(qk);
+    if (!use_qk_norm || seq_len <= 0 || num_heads <= 0 || head_dim <= 0) return;
+    int op = sb_prof_begin(c, "qk_norm");
+    sb_qk_norm(c, qk->data, rms_out ? rms_out->data : NULL, seq_len, num_heads * head_dim, eps);
+    sb_prof_end(c, op, 0, (size_t)seq_len * num_heads * head_dim * 8);
+}
+// its backward (the reference has none): qk_out and rms are what the forward call left; grad_in may alias grad_out
+void seraph_b200_qk_norm_backward(cuda_train_context_t* ctx, cuda_buffer_t* qk_out, cuda_buffer_t* rms, cuda_buffer_t* grad_out,
+                                  cuda_buffer_t* grad_in, int seq_len, int num_heads, int head_dim, int use_qk_norm, float eps) {
+    CTX_OR_RETURN(ctx); NEED(qk_out, rms, grad_out, grad_in);
+    if (seq_len <= 0 || num_heads <= 0 || head_dim <= 0) return;
+    if (!use_qk_norm) {
+        if (grad_in->data != grad_out->data) sb_copy(c, grad_in->data, grad_out->data, (size_t)seq_len * num_heads * head_dim * sizeof(float));
+        return;
+    }
+    int op = sb_prof_begin(c, "qk_norm_bwd");
+    sb_qk_norm_backward(c, qk_out->data, rms->data, grad_out->data, grad_in->data, seq_len, num_heads * head_dim, eps);
+    sb_prof_end(c, op, 0, (size_t)seq_len * num_heads * head_dim * 12);
+}
 // grad_K and grad_V are accumulated into (callers zero them first, src/train_cuda.c:2234-2237); grad_Q is written.
 // attn_out and lse must come from the forward call: this implementation always uses the log-sum-exp form.
 void cuda_train_batch_attention_backward(cuda_train_context_t* ctx, cuda_buffer_t* Q, cuda_buffer_t* K, cuda_buffer_t* V,

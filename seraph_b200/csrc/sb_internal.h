@@ -47,6 +47,7 @@ typedef struct { size_t q, k, v, o, gate, up, down, in_norm, post_norm; } sb_lay
 
 typedef struct {
     float *layer_in, *x_norm_attn, *q, *k, *v, *attn_out, *lse, *post_attn_in, *x_norm_ffn, *gate, *up, *ffn_hidden;
+    float *q_rms, *k_rms;            /* per-token sqrt(mean(x^2)) of q and k before their whole-row normalisation (use_qk_norm) */
 } sb_layer_act_t;
 
 typedef struct { const float* ptr; size_t n, cur, off; unsigned gen; int kind; float* amax_ptr; } sb_parts_entry_t;   /* n: registered floats, cur: floats of the parts held */
@@ -90,6 +91,7 @@ typedef struct sb_ctx {
     size_t n_params;
     sb_layer_off_t* off;             /* [L] offsets into the arenas */
     float *W, *G, *M, *Vv;           /* parameter, gradient, Adam m, Adam v arenas (flat order) */
+    int qk_norm;                     /* config->use_qk_norm of the step in flight */
     int frozen_base;                 /* 1: LoRA mode, G/M/Vv not allocated */
 
     /* LoRA adapters: one arena per kind, same flat order as the oracle */
@@ -145,6 +147,8 @@ void sb_tick_end(sb_ctx_t* c, int slot, double flops, double bytes);
 void sb_embed_lookup(sb_ctx_t*, const uint32_t* tok, const float* E, float* out, int T, int d, int V);
 void sb_rmsnorm(sb_ctx_t*, const float* x, const float* w, float* y, int rows, int cols, float eps);
 /* dx = rmsnorm'(x; dy); if resid != NULL, dx_out = resid + dx (fused residual-gradient add) */
+void sb_qk_norm(sb_ctx_t*, float* x, float* rms_out, int rows, int cols, float eps);
+void sb_qk_norm_backward(sb_ctx_t*, const float* y, const float* rms, const float* dy, float* dx, int rows, int cols, float eps);
 void sb_rmsnorm_backward(sb_ctx_t*, const float* x, const float* w, const float* dy, const float* resid,
                          float* dx_out, float* dscale, int rows, int cols, float eps);
 void sb_add(sb_ctx_t*, const float* a, const float* b, float* c, size_t n);

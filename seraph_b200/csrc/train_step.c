@@ -342,7 +342,7 @@ static int ensure_activations(sb_ctx_t* c, int T, int need_logits_grad) {
     free_activations(c);
     size_t Td = r4((size_t)T * c->d), TF = r4((size_t)T * c->F), Tq = r4((size_t)T * c->qd), Tkv = r4((size_t)T * c->kvd);
     size_t TH = r4((size_t)T * c->Hq), TV = r4((size_t)T * c->V);
-    size_t per_layer = 4 * Td + 2 * Tq + 2 * Tkv + TH + 3 * TF;    /* layer_in x_norm_attn post_attn_in x_norm_ffn | q attn_out | k v | lse | gate up ffn_hidden */
+    size_t per_layer = 4 * Td + 2 * Tq + 2 * Tkv + TH + 3 * TF + 2 * r4((size_t)T);    /* layer_in x_norm_attn post_attn_in x_norm_ffn | q attn_out | k v | lse | gate up ffn_hidden */
     size_t shared = 3 * Td /* hidden_norm final_in (+1 spare) */ + 2 * TV + r4((size_t)T)
                   + 3 * Td /* g_hidden g_tmp g_xnorm */ + 2 * Tq + 2 * Tkv + 3 * TF;
     (void)need_logits_grad;
@@ -356,7 +356,7 @@ static int ensure_activations(sb_ctx_t* c, int T, int need_logits_grad) {
     for (int l = 0; l < c->L; l++) {
         sb_layer_act_t* a = &c->act[l];
         TAKE(a->layer_in, Td); TAKE(a->x_norm_attn, Td); TAKE(a->post_attn_in, Td); TAKE(a->x_norm_ffn, Td);
-        TAKE(a->q, Tq); TAKE(a->attn_out, Tq); TAKE(a->k, Tkv); TAKE(a->v, Tkv); TAKE(a->lse, TH);
+        TAKE(a->q, Tq); TAKE(a->attn_out, Tq); TAKE(a->k, Tkv); TAKE(a->v, Tkv); TAKE(a->lse, TH); TAKE(a->q_rms, r4((size_t)T)); TAKE(a->k_rms, r4((size_t)T));
         TAKE(a->gate, TF); TAKE(a->up, TF); TAKE(a->ffn_hidden, TF);
     }
     TAKE(c->hidden_norm, Td); TAKE(c->final_in, Td); TAKE(c->hidden, Td);
@@ -436,8 +436,13 @@ static void forward_pass(sb_ctx_t* c, int T, int max_seq, float theta, int use_l
         linear_fwd(c, use_lora, l, 1, a->x_norm_attn, c->W + o->k, a->k, T, d, kvd, 0);
         linear_fwd(c, use_lora, l, 2, a->x_norm_attn, c->W + o->v, a->v, T, d, kvd, 0);
         sb_gemm_keep_end(c);
-        sb_amax_announce(c, a->q, (size_t)T * qd); sb_amax_announce(c, a->k, (size_t)T * kvd);
+        if (!c->qk_norm) { sb_amax_announce(c, a->q, (size_t)T * qd); sb_amax_announce(c, a->k, (size_t)T * kvd); }
         sb_rope2(c, a->q, a->k, c->pos_ids, T, c->Hq, c->Hkv, c->hd, theta, max_seq, 0);
+        if (c->qk_norm) {
+            /* whole-row normalisation of q and k after RoPE (shaders/qk_norm.comp, src/train.c:4688-4689); the row statistic is kept for the backward pass */
+            sb_qk_norm(c, a->q, a->q_rms, T, qd, RMS_EPS);
+            sb_qk_norm(c, a->k, a->k_rms, T, kvd, RMS_EPS);
+        }
         sb_amax_announce(c, a->attn_out, (size_t)T * qd);
         sb_attention(c, a->q, a->k, a->v, a->attn_out, a->lse, c->seq_starts, c->seq_ids, T, c->Hq, c->Hkv, c->hd);
         sb_copy(c, a->post_attn_in, a->layer_in, Td * sizeof(float));
@@ -501,6 +506,11 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
         if (!full) lora_bwd(c, l, 3, gh, a->attn_out, c->g_attn, T);
         sb_attention_backward(c, a->q, a->k, a->v, a->attn_out, a->lse, c->g_attn, c->g_q, c->g_k, c->g_v, 0,
                               c->seq_starts, c->seq_ids, B, T, c->Hq, c->Hkv, c->hd);
+        if (c->qk_norm) {
+            /* the reference has no backward for qk_norm; this is the derivative of its forward */
+            sb_qk_norm_backward(c, a->q, a->q_rms, c->g_q, c->g_q, T, qd, RMS_EPS);
+            sb_qk_norm_backward(c, a->k, a->k_rms, c->g_k, c->g_k, T, kvd, RMS_EPS);
+        }
         sb_amax_announce(c, c->g_q, (size_t)T * qd); sb_amax_announce(c, c->g_k, (size_t)T * kvd);
         sb_rope2(c, c->g_q, c->g_k, c->pos_ids, T, c->Hq, c->Hkv, c->hd, theta, max_seq, 1);
         if (full) {
@@ -572,6 +582,7 @@ static float step_body(train_state_t* st, int* tokens, int T, int* seq_starts, i
     int num_valid = T - B;
     if (num_valid <= 0) return 0.0f;
     int use_lora = (!full && st->lora != NULL);
+    c->qk_norm = st->config->use_qk_norm ? 1 : 0;
     if (ensure_model(c, st, full ? 0 : (use_lora ? 1 : c->frozen_base))) return -1.0f;
     if (use_lora && ensure_lora(c, st->lora)) return -1.0f;
     if (ensure_activations(c, T, train)) return -1.0f;

@@ -18,7 +18,7 @@ i32p = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
 
 class RefCfg(C.Structure):
     _fields_ = [("V", C.c_int), ("d", C.c_int), ("L", C.c_int), ("Hq", C.c_int), ("Hkv", C.c_int),
-                ("hd", C.c_int), ("F", C.c_int), ("eps", C.c_float), ("theta", C.c_float)]
+                ("hd", C.c_int), ("F", C.c_int), ("eps", C.c_float), ("theta", C.c_float), ("qk_norm", C.c_int)]
 
 
 @dataclass
@@ -32,6 +32,7 @@ class ModelCfg:
     F: int
     theta: float = 10000.0
     eps: float = 1e-5
+    qk_norm: int = 0          # whole-row normalisation of q and k after RoPE (config->use_qk_norm)
 
     @property
     def qd(self):
@@ -42,7 +43,7 @@ class ModelCfg:
         return self.Hkv * self.hd
 
     def c(self):
-        return RefCfg(self.V, self.d, self.L, self.Hq, self.Hkv, self.hd, self.F, self.eps, self.theta)
+        return RefCfg(self.V, self.d, self.L, self.Hq, self.Hkv, self.hd, self.F, self.eps, self.theta, self.qk_norm)
 
     def layer_shapes(self):
         d, F, qd, kvd = self.d, self.F, self.qd, self.kvd
@@ -135,6 +136,8 @@ def lib():
         "ref_mul_backward": (None, [f32p] * 5 + [sz]),
         "ref_rmsnorm_backward": (None, [f32p] * 5 + [C.c_int, C.c_int, C.c_float]),
         "ref_embedding_backward": (None, [u32p, f32p, f32p, C.c_int, C.c_int]),
+        "ref_qk_norm": (None, [f32p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float]),
+        "ref_qk_norm_backward": (None, [f32p] * 4 + [C.c_int] * 4 + [C.c_float]),
         "ref_adamw": (None, [f32p] * 4 + [sz] + [C.c_float] * 5 + [C.c_int]),
         "ref_lora_backward": (None, [f32p] * 7 + [C.c_int] * 4 + [C.c_float]),
         "ref_lora_forward_add": (None, [f32p] * 5 + [C.c_int] * 4 + [C.c_float]),

@@ -250,6 +250,31 @@ def test_attention_unpacked_single_sequence(ctx):
     ctx.release(bq, bk, bv, bo)
 
 
+@pytest.mark.parametrize("T,H,hd,eps", [(300, 16, 128, 1e-5), (129, 8, 128, 1e-5), (70, 3, 10, 1e-5), (40, 4, 16, 1e-5), (256, 8, 64, 50.0),
+                                        (64, 40, 128, 1e-5)])
+def test_qk_norm_forward_and_backward(ctx, T, H, hd, eps):
+    """Whole-row Q/K normalisation (the reference's qk_norm shader) and its backward against the oracle: warp-per-row and
+    CTA-per-row shapes, clamp active (eps = 50), in-place gradient, use_qk_norm = 0 as a no-op."""
+    r = rng(T + H + hd)
+    x, dy = f32(r.standard_normal((T, H * hd))), f32(r.standard_normal((T, H * hd)))
+    y_ref, rms_ref, dx_ref = x.copy(), np.zeros(T, np.float32), np.empty_like(x)
+    O.lib().ref_qk_norm(y_ref, rms_ref.ctypes.data, T, H, hd, 1, eps)
+    O.lib().ref_qk_norm_backward(y_ref, rms_ref, dy, dx_ref, T, H, hd, 1, eps)
+    bx, brms, bdy = ctx.upload(x), ctx.zeros(T), ctx.upload(dy)
+    n0 = ctx.launches()
+    ctx.lib.seraph_b200_qk_norm(ctx.h, bx.b, brms.b, T, H, hd, 1, eps)
+    assert rel_l2(bx.numpy(shape=x.shape), y_ref) < TOL and rel_l2(brms.numpy(), rms_ref) < TOL
+    ctx.lib.seraph_b200_qk_norm_backward(ctx.h, bx.b, brms.b, bdy.b, bdy.b, T, H, hd, 1, eps)       # gradient in place
+    ctx.check()
+    assert ctx.launches() - n0 == 2
+    assert rel_l2(bdy.numpy(shape=x.shape), dx_ref) < TOL
+    # disabled: nothing happens
+    b2 = ctx.upload(x)
+    ctx.lib.seraph_b200_qk_norm(ctx.h, b2.b, None, T, H, hd, 0, eps)
+    assert np.array_equal(b2.numpy(shape=x.shape), x)
+    ctx.release(bx, brms, bdy, b2)
+
+
 @pytest.mark.parametrize("V", [257, 1024, 8192])
 def test_cross_entropy_packed(ctx, V):
     ss = np.array([0, 7, 19, 24], np.uint32)

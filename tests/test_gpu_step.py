@@ -236,6 +236,23 @@ def test_evaluate_packs_samples_and_matches_per_sample_passes(ctx):
     st.close()
 
 
+def test_step_with_qk_norm_matches_oracle(ctx):
+    """config->use_qk_norm = 1: q and k are normalised over the whole token row after RoPE (the reference's qk_norm shader)
+    and the backward pass differentiates through it (the reference does not).  Tiny shape (row kernels) and a 128-wide-head
+    shape (warp-per-row kernels, fused attention)."""
+    import dataclasses
+    for base, ss, seed in ((TINY, TINY_SEQS, 51), (O.ModelCfg(V=1024, d=512, L=2, Hq=4, Hkv=2, hd=128, F=1024, theta=1e4), [0, 300, 512, 645], 52)):
+        cfg = dataclasses.replace(base, qk_norm=1)
+        p = cfg.init_params(seed, norm_jitter=0.1)
+        tok = tokens_for(cfg, ss[-1], seed + 1)
+        ref = O.train_step(cfg, p, tok, ss)
+        got = run_full_step(ctx, cfg, p, tok, ss)
+        assert abs(got["loss"][0] - ref["loss"]) < 1e-5 * abs(ref["loss"])
+        print("qk_norm step, worst gradient rel-L2:", check_grads(cfg, got["grads"], ref["grads"]))
+        off = run_full_step(ctx, base, p, tok, ss)
+        assert abs(off["loss"][0] - got["loss"][0]) > 1e-4
+
+
 def test_head128_model_step_matches_oracle(ctx):
     """A model with 128-wide heads (grouped: 4 query / 2 K-V heads) on ragged sequences: the step runs the fused attention
     kernels (forward in one kernel, backward scores in one kernel) and every gradient meets the bound."""

@@ -115,6 +115,26 @@ def test_full_gradients_match_autograd_float64():
         assert rel_l2(out["grads"][off:off + n], g[off:off + n]) < 2e-6, name
 
 
+def test_full_gradients_with_qk_norm_match_autograd_float64():
+    """config->use_qk_norm: q and k normalised over the whole token row after RoPE.  The reference's training has no
+    backward for it; the oracle step's is the derivative of the forward, checked here against float64 autograd."""
+    import dataclasses
+    cfg = dataclasses.replace(TINY, qk_norm=1)
+    p = cfg.init_params(8, norm_jitter=0.1)
+    tok = tiny_tokens(12)
+    out = O.train_step(cfg, p, tok, TINY_SEQS, want_logits=True)
+    P = TM.unflatten(cfg, p)
+    loss, logits = TM.forward_loss(cfg, P, tok, TINY_SEQS)
+    loss.backward()
+    g = TM.flatten_grads(cfg, P)
+    assert abs(out["loss"] - loss.item()) < 1e-6
+    for name, shp, off in cfg.tensors():
+        n = int(np.prod(shp))
+        assert rel_l2(out["grads"][off:off + n], g[off:off + n]) < 2e-6, name
+    plain = O.train_step(TINY, p, tok, TINY_SEQS)
+    assert abs(plain["loss"] - out["loss"]) > 1e-4          # the switch does something
+
+
 def test_gradient_accumulation_adds():
     cfg = TINY
     p = cfg.init_params(7)
@@ -169,3 +189,28 @@ def test_lora_gradients_match_autograd_float64(exact):
             assert np.linalg.norm(g) == 0, name
         else:
             assert rel_l2(g, ref) < 2e-6, name
+
+
+@pytest.mark.parametrize("eps", [1e-5, 10.0])           # the second makes the clamp active on every row
+def test_qk_norm_forward_follows_shader_and_backward_is_its_derivative(eps):
+    """qk_norm (shaders/qk_norm.comp): y = x / max(sqrt(mean(x^2)), eps) over the whole token row.  The reference has no
+    backward; the oracle's is checked against float64 autograd of the same forward."""
+    T, H, hd = 5, 3, 8
+    r = np.random.default_rng(3)
+    x = r.standard_normal((T, H * hd)).astype(np.float32)
+    dy = r.standard_normal((T, H * hd)).astype(np.float32)
+    y = x.copy(); rms = np.zeros(T, np.float32)
+    O.lib().ref_qk_norm(y, rms.ctypes.data, T, H, hd, 1, eps)
+    xt = torch.tensor(x, dtype=torch.float64, requires_grad=True)
+    rt = torch.sqrt((xt * xt).mean(dim=1, keepdim=True))
+    yt = xt / torch.clamp(rt, min=eps)
+    assert rel_l2(y, yt.detach().numpy()) < 1e-6 and rel_l2(rms, rt.detach().numpy().ravel()) < 1e-6
+    (yt * torch.tensor(dy, dtype=torch.float64)).sum().backward()
+    dx = np.empty_like(x)
+    O.lib().ref_qk_norm_backward(y, rms, dy, dx, T, H, hd, 1, eps)
+    assert rel_l2(dx, xt.grad.numpy()) < 1e-6
+    # disabled: forward leaves the row alone, backward passes the gradient through
+    y2 = x.copy()
+    O.lib().ref_qk_norm(y2, None, T, H, hd, 0, eps)
+    O.lib().ref_qk_norm_backward(y2, rms, dy, dx, T, H, hd, 0, eps)
+    assert np.array_equal(y2, x) and np.array_equal(dx, dy)

@@ -69,8 +69,13 @@ def forward_loss(cfg, P, tokens, seq_starts, lora=None, rank=0, alpha=0.0):
     g = cfg.Hq // cfg.Hkv
     for l in range(cfg.L):
         x = rmsnorm(h, P[f"l{l}.in_norm"], cfg.eps)
-        q = rope(lin(x, f"l{l}.q"), pos, cfg.Hq, cfg.hd, cfg.theta).view(T, cfg.Hq, cfg.hd)
-        k = rope(lin(x, f"l{l}.k"), pos, cfg.Hkv, cfg.hd, cfg.theta).view(T, cfg.Hkv, cfg.hd)
+        q = rope(lin(x, f"l{l}.q"), pos, cfg.Hq, cfg.hd, cfg.theta)
+        k = rope(lin(x, f"l{l}.k"), pos, cfg.Hkv, cfg.hd, cfg.theta)
+        if getattr(cfg, "qk_norm", 0):           # whole-row normalisation after RoPE (shaders/qk_norm.comp)
+            q = q.reshape(T, -1); k = k.reshape(T, -1)
+            q = q / torch.clamp(torch.sqrt((q * q).mean(dim=1, keepdim=True)), min=cfg.eps)
+            k = k / torch.clamp(torch.sqrt((k * k).mean(dim=1, keepdim=True)), min=cfg.eps)
+        q = q.reshape(T, cfg.Hq, cfg.hd); k = k.reshape(T, cfg.Hkv, cfg.hd)
         v = lin(x, f"l{l}.v").view(T, cfg.Hkv, cfg.hd)
         kv_of = (torch.arange(cfg.Hq, device=dev) * cfg.Hkv) // cfg.Hq
         kk, vv = k[:, kv_of], v[:, kv_of]

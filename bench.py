@@ -35,6 +35,7 @@ WORKLOADS = {
     "qwen3-1.7b-shaped full-weight FP32, 4x2048 tokens per rank": (QWEN, 4, 2048),
     "profiling slice: 2 qwen3-1.7b-shaped layers, vocab 16384, 2x2048 tokens": (SLICE, 2, 2048),
     "33M Llama-style full-weight FP32, 8x256 tokens per rank": (SMALL, 8, 256),
+    "profiling slice with use_qk_norm: the same 2 layers, q and k normalised over the token row after RoPE": (dict(SLICE, qk_norm=1), 2, 2048),
 }
 
 

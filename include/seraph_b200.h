@@ -185,6 +185,11 @@ void seraph_b200_qk_norm(cuda_train_context_t* ctx, cuda_buffer_t* qk, cuda_buff
  * qk_out and rms are what the forward call left; grad_in may be grad_out. */
 void seraph_b200_qk_norm_backward(cuda_train_context_t* ctx, cuda_buffer_t* qk_out, cuda_buffer_t* rms, cuda_buffer_t* grad_out,
                                   cuda_buffer_t* grad_in, int seq_len, int num_heads, int head_dim, int use_qk_norm, float eps);
+/* The resident FP32 weights as a BF16 safetensors file: byte for byte what trainable_weights_save_to_safetensors
+ * (src/train.c:433-569) writes from the host copies after cuda_download_full_weights (same header, tensor order and
+ * FP32 -> BF16 truncation), but converted on the GPU (2 bytes per parameter cross to the host, in chunks, while the
+ * previous chunk is written).  The host copies in `state` are not touched.  Returns SB_OK or an SB_ERR_* code. */
+int seraph_b200_save_safetensors(cuda_train_context_t* ctx, train_state_t* state, const char* path);
 /* cuda_evaluate (include/train_cuda.h:60-64 of the reference, src/train_cuda.c:2812-2846) runs one forward pass per
  * validation sample there; here it packs samples into passes of up to `tokens` tokens (default 8192, at least
  * max_seq_len, at most 256 samples; SERAPH_B200_EVAL_BATCH_TOKENS sets the default) and takes every sample's mean loss
@@ -283,6 +288,8 @@ void seraph_b200_state_get(train_state_t* st, int which, float* flat);
 void seraph_b200_state_set_counters(train_state_t* st, int optimizer_step, int accumulation_counter);
 void seraph_b200_state_get_counters(train_state_t* st, int* optimizer_step, int* accumulation_counter);
 void seraph_b200_state_set_lr(train_state_t* st, float lr, int accum);
+/* the state's trainable_weights_t (host FP32 master copies), e.g. for the reference's own checkpoint writer */
+void* seraph_b200_state_weights(train_state_t* st);
 /* config->use_qk_norm of a state built by seraph_b200_state_create (the reference sets it for --video, src/train.c:7867-7868) */
 void seraph_b200_state_set_qk_norm(train_state_t* st, int on);
 size_t seraph_b200_state_lora_count(train_state_t* st, int rank, int mask);

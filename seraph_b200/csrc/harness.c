@@ -112,6 +112,7 @@ void seraph_b200_state_get_counters(train_state_t* st, int* optimizer_step, int*
     if (accumulation_counter) *accumulation_counter = st->accumulation_counter;
 }
 void seraph_b200_state_set_lr(train_state_t* st, float lr, int accum) { st->learning_rate = lr; st->gradient_accumulation_steps = accum; }
+void* seraph_b200_state_weights(train_state_t* st) { return st ? (void*)st->full_weights : NULL; }
 void seraph_b200_state_set_qk_norm(train_state_t* st, int on) { if (st && st->config) st->config->use_qk_norm = on ? 1 : 0; }
 
 /* ---- LoRA ---- */

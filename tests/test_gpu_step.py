@@ -236,6 +236,39 @@ def test_evaluate_packs_samples_and_matches_per_sample_passes(ctx):
     st.close()
 
 
+@pytest.mark.parametrize("which", ["tiny", "c1", "c1-many-chunks"])
+def test_safetensors_export_is_byte_identical_to_the_reference_writer(ctx, which, tmp_path, monkeypatch):
+    """seraph_b200_save_safetensors (BF16 conversion on the GPU, chunked copy) against the reference's own
+    trainable_weights_save_to_safetensors (src/train.c:433-569, compiled from its source) fed with the weights that
+    cuda_download_full_weights brought back after a training step: the two files are equal byte for byte."""
+    import ctypes as C
+    from seraph_b200 import api
+    ref = O.ref_lib("cpu")
+    if ref is None:
+        pytest.skip("oracle/_ref not built (no reference checkout)")
+    cfg, ss = (TINY, TINY_SEQS) if which == "tiny" else (C1, list(range(0, 2049, 256)))
+    if which == "c1-many-chunks":
+        monkeypatch.setenv("SERAPH_B200_CKPT_CHUNK", "1000003")       # ragged chunks through both staging buffers
+    p = cfg.init_params(61, norm_jitter=0.1)
+    tok = tokens_for(cfg, ss[-1], 62)
+    ctx.lib.seraph_b200_reset_model(ctx.h)
+    st = api.TrainState(cfg, p, lr=1e-2)
+    api.step_full_batch(ctx, st, tok, ss)
+    ours, theirs = str(tmp_path / "ours.safetensors"), str(tmp_path / "theirs.safetensors")
+    assert ctx.lib.seraph_b200_save_safetensors(ctx.h, st.h, ours.encode()) == 0
+    ctx.check()
+    ctx.lib.cuda_download_full_weights(ctx.h, st.h)
+    fn = ref.trainable_weights_save_to_safetensors
+    fn.restype, fn.argtypes = None, [C.c_void_p, C.c_char_p]
+    fn(ctx.lib.seraph_b200_state_weights(st.h), theirs.encode())
+    a, b = open(ours, "rb").read(), open(theirs, "rb").read()
+    assert len(a) == len(b) and a == b
+    hlen = int.from_bytes(a[:8], "little")
+    assert len(a) == 8 + hlen + 2 * st.n and b"model.norm.weight" in a[8:8 + hlen]
+    assert not np.array_equal(st.get(0), p)               # the step did move the weights that were exported
+    st.close()
+
+
 def test_step_with_qk_norm_matches_oracle(ctx):
     """config->use_qk_norm = 1: q and k are normalised over the whole token row after RoPE (the reference's qk_norm shader)
     and the backward pass differentiates through it (the reference does not).  Tiny shape (row kernels) and a 128-wide-head

@@ -190,6 +190,10 @@ void seraph_b200_qk_norm_backward(cuda_train_context_t* ctx, cuda_buffer_t* qk_o
  * FP32 -> BF16 truncation), but converted on the GPU (2 bytes per parameter cross to the host, in chunks, while the
  * previous chunk is written).  The host copies in `state` are not touched.  Returns SB_OK or an SB_ERR_* code. */
 int seraph_b200_save_safetensors(cuda_train_context_t* ctx, train_state_t* state, const char* path);
+/* save_checkpoint (src/train.c:7760-7804) for a full-weight state whose weights are resident on the GPU: the
+ * safetensors file as above plus "<path>.state" (current_epoch, current_step, current_loss, optimizer_step).
+ * SB_ERR_ARG for a LoRA state (those go through cuda_download_lora_weights and the reference's lora_save). */
+int seraph_b200_save_checkpoint(cuda_train_context_t* ctx, train_state_t* state, const char* path);
 /* cuda_evaluate (include/train_cuda.h:60-64 of the reference, src/train_cuda.c:2812-2846) runs one forward pass per
  * validation sample there; here it packs samples into passes of up to `tokens` tokens (default 8192, at least
  * max_seq_len, at most 256 samples; SERAPH_B200_EVAL_BATCH_TOKENS sets the default) and takes every sample's mean loss

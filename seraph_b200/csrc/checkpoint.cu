@@ -133,3 +133,21 @@ extern "C" int seraph_b200_save_safetensors(cuda_train_context_t* ctx, train_sta
     if (rc != SB_OK) sb_set_status(c, rc);
     return rc;
 }
+
+// save_checkpoint (src/train.c:7760-7804) for a full-weight state whose weights live on the GPU: the safetensors file
+// as above, then "<path>.state" with current_epoch, current_step, current_loss, optimizer_step (4 + 4 + 4 + 4 bytes).
+// LoRA states are saved by the reference's own lora_save after cuda_download_lora_weights; this returns SB_ERR_ARG for them.
+extern "C" int seraph_b200_save_checkpoint(cuda_train_context_t* ctx, train_state_t* state, const char* path) {
+    if (!state || !path || state->lora) return SB_ERR_ARG;
+    int rc = seraph_b200_save_safetensors(ctx, state, path);
+    if (rc != SB_OK) return rc;
+    char sp[600];
+    if (snprintf(sp, sizeof sp, "%s.state", path) >= (int)sizeof sp) return SB_ERR_ARG;
+    FILE* f = fopen(sp, "wb");
+    if (!f) return SB_ERR_ARG;
+    int ok = fwrite(&state->current_epoch, sizeof(int), 1, f) == 1 && fwrite(&state->current_step, sizeof(int), 1, f) == 1 &&
+             fwrite(&state->current_loss, sizeof(float), 1, f) == 1 && fwrite(&state->optimizer_step, sizeof(int), 1, f) == 1;
+    if (fclose(f) != 0) ok = 0;
+    return ok ? SB_OK : SB_ERR_ARG;
+}
+

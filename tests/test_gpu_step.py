@@ -266,6 +266,13 @@ def test_safetensors_export_is_byte_identical_to_the_reference_writer(ctx, which
     hlen = int.from_bytes(a[:8], "little")
     assert len(a) == 8 + hlen + 2 * st.n and b"model.norm.weight" in a[8:8 + hlen]
     assert not np.array_equal(st.get(0), p)               # the step did move the weights that were exported
+    if which == "tiny":
+        # the whole checkpoint: same file plus "<path>.state" = epoch, step, loss, optimizer step as save_checkpoint writes them
+        ck = str(tmp_path / "ckpt.safetensors")
+        assert ctx.lib.seraph_b200_save_checkpoint(ctx.h, st.h, ck.encode()) == 0
+        assert open(ck, "rb").read() == b
+        raw = open(ck + ".state", "rb").read()
+        assert len(raw) == 16 and int.from_bytes(raw[12:16], "little") == st.counters()[0] == 1
     st.close()
 
 

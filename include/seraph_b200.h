@@ -190,6 +190,11 @@ void seraph_b200_qk_norm_backward(cuda_train_context_t* ctx, cuda_buffer_t* qk_o
  * FP32 -> BF16 truncation), but converted on the GPU (2 bytes per parameter cross to the host, in chunks, while the
  * previous chunk is written).  The host copies in `state` are not touched.  Returns SB_OK or an SB_ERR_* code. */
 int seraph_b200_save_safetensors(cuda_train_context_t* ctx, train_state_t* state, const char* path);
+/* trainable_weights_load_from_safetensors (src/train.c:571-629) into the device: the tensors are read in saved order
+ * (the header is skipped, as there), cross to the GPU as BF16 in chunks and are widened into the resident FP32 weights
+ * (uploading the model from `state` first if it is not resident yet).  Adam moments and the host copies are left as they
+ * are; cuda_download_full_weights refreshes the host side.  Returns SB_OK or an SB_ERR_* code. */
+int seraph_b200_load_safetensors(cuda_train_context_t* ctx, train_state_t* state, const char* path);
 /* save_checkpoint (src/train.c:7760-7804) for a full-weight state whose weights are resident on the GPU: the
  * safetensors file as above plus "<path>.state" (current_epoch, current_step, current_loss, optimizer_step).
  * SB_ERR_ARG for a LoRA state (those go through cuda_download_lora_weights and the reference's lora_save). */

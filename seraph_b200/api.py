@@ -98,7 +98,7 @@ def load():
         "seraph_b200_state_param_count": (sz, [vp]), "seraph_b200_state_set": (None, [vp, i, vp]),
         "seraph_b200_state_get": (None, [vp, i, vp]), "seraph_b200_state_set_counters": (None, [vp, i, i]),
         "seraph_b200_state_get_counters": (None, [vp, C.POINTER(i), C.POINTER(i)]),
-        "seraph_b200_state_set_lr": (None, [vp, f, i]), "seraph_b200_state_set_qk_norm": (None, [vp, i]), "seraph_b200_state_weights": (vp, [vp]), "seraph_b200_save_safetensors": (i, [vp, vp, C.c_char_p]), "seraph_b200_save_checkpoint": (i, [vp, vp, C.c_char_p]), "seraph_b200_state_lora_count": (sz, [vp, i, i]),
+        "seraph_b200_state_set_lr": (None, [vp, f, i]), "seraph_b200_state_set_qk_norm": (None, [vp, i]), "seraph_b200_state_weights": (vp, [vp]), "seraph_b200_save_safetensors": (i, [vp, vp, C.c_char_p]), "seraph_b200_save_checkpoint": (i, [vp, vp, C.c_char_p]), "seraph_b200_load_safetensors": (i, [vp, vp, C.c_char_p]), "seraph_b200_state_lora_count": (sz, [vp, i, i]),
         "seraph_b200_state_attach_lora": (i, [vp, i, f, i, vp]), "seraph_b200_state_lora_get": (None, [vp, i, vp]),
     }
     missing = []

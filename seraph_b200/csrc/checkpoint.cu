@@ -151,3 +151,57 @@ extern "C" int seraph_b200_save_checkpoint(cuda_train_context_t* ctx, train_stat
     return ok ? SB_OK : SB_ERR_ARG;
 }
 
+// ---- the way back: trainable_weights_load_from_safetensors (src/train.c:571-629) skips the header and reads the tensors in
+// the order they were saved, BF16 -> FP32 by a 16-bit shift.  Here the BF16 words go to the GPU in chunks (2 bytes per
+// parameter) and are widened there, straight into the weight arena; the Adam moments and the host copies stay as they are
+// (as in the reference, which loads weights only).
+__global__ void __launch_bounds__(256) unpack_bf16_kernel(const uint16_t* __restrict__ src, float* __restrict__ dst, size_t n) {
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    const size_t n4 = (((uintptr_t)dst & 15) == 0 && ((uintptr_t)src & 7) == 0) ? n >> 2 : 0;
+    for (size_t i = tid; i < n4; i += nth) {
+        const uint2 v = ((const uint2*)src)[i];
+        ((uint4*)dst)[i] = make_uint4(v.x << 16, v.x & 0xffff0000u, v.y << 16, v.y & 0xffff0000u);
+    }
+    for (size_t i = (n4 << 2) + tid; i < n; i += nth) dst[i] = __uint_as_float((uint32_t)src[i] << 16);
+}
+
+extern "C" int seraph_b200_load_safetensors(cuda_train_context_t* ctx, train_state_t* state, const char* path) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c || !state || !state->full_weights || !state->config || !path) return SB_ERR_ARG;
+    if (sb_ensure_full_model(c, state)) return c->status ? c->status : SB_ERR_ARG;
+    FILE* f = fopen(path, "rb");
+    if (!f) { fprintf(stderr, "ERROR: Cannot open %s\n", path); return SB_ERR_ARG; }
+    uint64_t hsize = 0;
+    if (fread(&hsize, sizeof hsize, 1, f) != 1 || fseek(f, (long)hsize, SEEK_CUR) != 0) { fclose(f); return SB_ERR_ARG; }
+    const size_t nE = (size_t)c->V * c->d;
+    struct { size_t begin, n; } seg[3] = {{0, nE}, {c->off[0].q, c->n_params - c->off[0].q}, {nE, (size_t)c->d}};
+    size_t chunk = CK_CHUNK_DEFAULT;
+    { const char* e = getenv("SERAPH_B200_CKPT_CHUNK"); if (e && atol(e) >= 1024) chunk = ((size_t)atol(e) + 3) & ~(size_t)3; }
+    uint16_t* dbuf[2] = {NULL, NULL}; uint16_t* hbuf[2] = {NULL, NULL};
+    cudaEvent_t ev[2] = {NULL, NULL};
+    cudaStream_t st = (cudaStream_t)c->pub.stream;
+    int rc = SB_OK;
+    for (int i = 0; i < 2 && rc == SB_OK; i++)
+        if (cudaMalloc((void**)&dbuf[i], chunk * 2) != cudaSuccess || cudaMallocHost((void**)&hbuf[i], chunk * 2) != cudaSuccess ||
+            cudaEventCreateWithFlags(&ev[i], cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); rc = SB_ERR_OOM; }
+    const int blocks = (c->pub.gpu_sm_count > 0 ? c->pub.gpu_sm_count : 148) * 8;
+    int k = 0;
+    for (int s = 0; s < 3 && rc == SB_OK; s++)
+        for (size_t o = 0; o < seg[s].n && rc == SB_OK; o += chunk, k++) {
+            const size_t n = seg[s].n - o < chunk ? seg[s].n - o : chunk;
+            const int b = k & 1;
+            if (k >= 2 && cudaEventSynchronize(ev[b]) != cudaSuccess) { rc = SB_ERR_CUDA; break; }     // the copy out of this pinned buffer two chunks ago
+            if (fread(hbuf[b], 2, n, f) != n) { fprintf(stderr, "ERROR: Failed to read tensor data\n"); rc = SB_ERR_ARG; break; }
+            cudaMemcpyAsync(dbuf[b], hbuf[b], n * 2, cudaMemcpyHostToDevice, st);
+            cudaEventRecord(ev[b], st);
+            unpack_bf16_kernel<<<blocks, 256, 0, st>>>(dbuf[b], c->W + seg[s].begin + o, n);
+            c->launches++;
+        }
+    cudaStreamSynchronize(st);
+    if (sb_check(c, cudaGetLastError(), "safetensors import")) rc = SB_ERR_CUDA;
+    for (int i = 0; i < 2; i++) { if (dbuf[i]) cudaFree(dbuf[i]); if (hbuf[i]) cudaFreeHost(hbuf[i]); if (ev[i]) cudaEventDestroy(ev[i]); }
+    fclose(f);
+    if (rc != SB_OK) sb_set_status(c, rc);
+    return rc;
+}
+

@@ -163,6 +163,7 @@ void sb_swiglu_backward(sb_ctx_t*, const float* gate, const float* up, const flo
 void sb_seq_index(sb_ctx_t*, const uint32_t* seq_starts, int B, int T, uint32_t* pos_ids, uint32_t* seq_ids);
 /* Between begin and end the FP16 parts of GEMM operands are kept and reused by later calls on the same array; the caller
  * guarantees that no operand array is written inside the region. */
+int sb_ensure_full_model(sb_ctx_t*, const train_state_t* st);
 void sb_gemm_keep_begin(sb_ctx_t*);
 void sb_gemm_keep_end(sb_ctx_t*);
 /* step-scoped FP16 parts of registered tensors: kind 0 = weights, 1 = saved activations */

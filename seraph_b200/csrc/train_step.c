@@ -823,6 +823,12 @@ int seraph_b200_download_logits(cuda_train_context_t* ctx, float* out, int T) {
 
 /* Extension: forget the resident weights, adapters and optimizer state, so that the next step uploads
  * them again from the host state (the reference uploads once per context, src/train_cuda.c:286-291). */
+/* the full-weight model of `st` resident on the device (uploaded from the host copies if it is not yet); 0 on success */
+int sb_ensure_full_model(sb_ctx_t* c, const train_state_t* st) {
+    if (!c || !st || !st->config || !st->full_weights) return 1;
+    return ensure_model(c, st, 0);
+}
+
 int seraph_b200_reset_model(cuda_train_context_t* ctx) {
     sb_ctx_t* c = sb_priv(ctx);
     if (!c) return SB_ERR_ARG;

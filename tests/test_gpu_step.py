@@ -276,6 +276,48 @@ def test_safetensors_export_is_byte_identical_to_the_reference_writer(ctx, which
     st.close()
 
 
+@pytest.mark.parametrize("chunk", [None, "300001"])
+def test_safetensors_load_widens_bf16_on_the_device(ctx, chunk, tmp_path, monkeypatch):
+    """seraph_b200_load_safetensors: a saved file read back into a context that holds other weights (and into one that holds
+    none yet) gives exactly the BF16-truncated weights (bf16_to_f32 of src/train.c:255-260), the reference's own loader
+    agrees value for value, and exporting again reproduces the file."""
+    import ctypes as C
+    from seraph_b200 import api
+    if chunk:
+        monkeypatch.setenv("SERAPH_B200_CKPT_CHUNK", chunk)
+    cfg, ss = C1, list(range(0, 2049, 256))
+    p = cfg.init_params(71, norm_jitter=0.1)
+    ctx.lib.seraph_b200_reset_model(ctx.h)
+    st = api.TrainState(cfg, p)
+    api.step_full_batch(ctx, st, tokens_for(cfg, ss[-1], 72), ss)           # make the model resident
+    path = str(tmp_path / "w.safetensors")
+    assert ctx.lib.seraph_b200_save_safetensors(ctx.h, st.h, path.encode()) == 0
+    ctx.lib.cuda_download_full_weights(ctx.h, st.h)
+    want = (st.get(0).view(np.uint32) & np.uint32(0xFFFF0000)).view(np.float32)
+    st.close()
+    for resident in (True, False):
+        ctx.lib.seraph_b200_reset_model(ctx.h)
+        st2 = api.TrainState(cfg, cfg.init_params(73))                       # other weights
+        if resident:
+            api.step_full_batch(ctx, st2, tokens_for(cfg, ss[-1], 74), ss)
+        assert ctx.lib.seraph_b200_load_safetensors(ctx.h, st2.h, path.encode()) == 0
+        ctx.check()
+        ctx.lib.cuda_download_full_weights(ctx.h, st2.h)
+        assert np.array_equal(st2.get(0).view(np.uint32), want.view(np.uint32))
+        again = str(tmp_path / "again.safetensors")
+        assert ctx.lib.seraph_b200_save_safetensors(ctx.h, st2.h, again.encode()) == 0
+        assert open(again, "rb").read() == open(path, "rb").read()
+        ref = O.ref_lib("cpu")
+        if ref is not None and resident:
+            st3 = api.TrainState(cfg, cfg.init_params(75))
+            fn = ref.trainable_weights_load_from_safetensors
+            fn.restype, fn.argtypes = C.c_int, [C.c_void_p, C.c_char_p]
+            assert fn(ctx.lib.seraph_b200_state_weights(st3.h), path.encode()) == 0
+            assert np.array_equal(st3.get(0).view(np.uint32), want.view(np.uint32))
+            st3.close()
+        st2.close()
+
+
 def test_step_with_qk_norm_matches_oracle(ctx):
     """config->use_qk_norm = 1: q and k are normalised over the whole token row after RoPE (the reference's qk_norm shader)
     and the backward pass differentiates through it (the reference does not).  Tiny shape (row kernels) and a 128-wide-head

@@ -1,7 +1,10 @@
 // attention_tc.cu - causal attention forward and backward on the tcgen05 GEMM kernel.
 //
+// The general path (any head size that is a multiple of 4, either FP32-accurate mode).  For 128-wide heads in the
+// default mode the forward pass and the backward's score products run in the fused kernels of attention_fused.cu
+// instead; the drivers below choose, prepare the operand parts for both, and run the backward's three long products.
 // FP32-accurate attention does not fit one SM's on-chip memory as a single fused kernel at
-// head_dim 128 (every operand needs a hi and a lo part, and five products share them), so the
+// head_dim 128 (every operand needs a hi and a lo part, and five products share them), so here the
 // score-sized matrices of a few heads at a time go through a scratch area; the five contractions
 // run on the tensor cores (CTA-pair kernel: operands taken as they lie in memory, lo parts made in
 // the kernel), whole tiles above the causal diagonal are skipped, and the k range of the products

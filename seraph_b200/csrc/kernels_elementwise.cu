@@ -169,6 +169,7 @@ __global__ void __launch_bounds__(EW_THREADS) rope_kernel(const float* qin, floa
     for (uint32_t base = blockIdx.x * blockDim.x + threadIdx.x; base < total; base += nth * ROPE_UNROLL) {
         float4 x[ROPE_UNROLL], cs[ROPE_UNROLL];
         float4* dst[ROPE_UNROLL];
+        bool inq[ROPE_UNROLL];
 #pragma unroll
         for (int u = 0; u < ROPE_UNROLL; u++) {
             const uint32_t i = base + u * nth;
@@ -176,6 +177,7 @@ __global__ void __launch_bounds__(EW_THREADS) rope_kernel(const float* qin, floa
             if (i < total) {
                 const uint32_t t = i / row_quads, rem = i - t * row_quads;
                 const bool isq = rem < rq;
+                inq[u] = isq;
                 const uint32_t w = isq ? rem : rem - rq;
                 x[u] = isq ? ((const float4*)qin)[(size_t)t * rq + w] : ((const float4*)kin)[(size_t)t * rk + w];
                 dst[u] = isq ? (float4*)qout + (size_t)t * rq + w : (float4*)kout + (size_t)t * rk + w;
@@ -194,8 +196,7 @@ __global__ void __launch_bounds__(EW_THREADS) rope_kernel(const float* qin, floa
                     r.z = x[u].z * cs[u].z + x[u].w * cs[u].w; r.w = -x[u].z * cs[u].w + x[u].w * cs[u].z;
                 }
                 *dst[u] = r;
-                const uint32_t i = base + u * nth;
-                if (i - (i / row_quads) * row_quads < rq) amq = sb_amax4(amq, r); else amk = sb_amax4(amk, r);
+                if (inq[u]) amq = sb_amax4(amq, r); else amk = sb_amax4(amk, r);
             }
         }
     }

@@ -219,6 +219,20 @@ int seraph_b200_set_lora_exact(cuda_train_context_t* ctx, int exact);
 /* Global-norm gradient clipping before AdamW; 0 switches it off (default: the
  * reference clips nothing). */
 int seraph_b200_set_grad_clip(cuda_train_context_t* ctx, float max_norm);
+/* NaN guard of the training step (state->debug_nan_check, src/train_cuda.c:626-645 and :1086-1187): the flags the last
+ * guarded step left in ctx->debug_nan_flags, copied to `out` (at most max_words words); returns the words written.
+ * Index layout as in the reference: [0..9] fixed buffers, [10 + l] hidden after layer l, [10 + L + 5 l + k] grad_attn /
+ * grad_q / grad_k / grad_v of layer l, [10 + 6 L + l] grad_hidden after layer l's backward, [10 + 7 L] embedding weights. */
+int seraph_b200_nan_flags(cuda_train_context_t* ctx, uint32_t* out, int max_words);
+/* Category totals (ms) of a cuda_profiler_t after cuda_profiler_sync_and_analyze: step, matmul, attention, attention_bwd,
+ * rmsnorm, rmsnorm_bwd, cross_entropy, adamw, copy, other; returns the number of recorded ops.  With a profiler attached
+ * (cuda_train_set_profiler, include/cuda_train_context.h:298) the training step's own launches are recorded, one op per
+ * launch under its class name, as well as the calls of the per-op ABI. */
+int seraph_b200_profiler_totals(cuda_profiler_t* profiler, float* out10);
+/* Self-test of the bounded waits inside the tensor-core kernels: a one-warp kernel waits at most limit_cycles (<= 2e9) clock
+ * cycles on a barrier that nothing completes, gives up, and leaves status 5 (bounded wait ran out) for
+ * seraph_b200_last_status; the kernel returns normally and the context stays usable.  *waited_cycles_out: cycles it waited. */
+int seraph_b200_selftest_bounded_wait(cuda_train_context_t* ctx, long long limit_cycles, long long* waited_cycles_out);
 /* Kernels launched by this library on ctx since the last reset. */
 unsigned long long seraph_b200_launch_count(cuda_train_context_t* ctx, int reset);
 /* Integer tables of the last cuda_train_embedding_backward(seq_len=T, vocab=V):
@@ -239,6 +253,8 @@ int seraph_b200_reset_model(cuda_train_context_t* ctx);
  * copied between host and device and the call does not wait for the GPU.  The mean loss of the
  * last step can be read (with a synchronisation) through seraph_b200_last_loss. */
 int seraph_b200_step_full_resident(train_state_t* state, cuda_train_context_t* ctx);
+/* the same for either kind of step: full != 0 the full-weight step, 0 the LoRA step */
+int seraph_b200_step_resident(train_state_t* state, cuda_train_context_t* ctx, int full);
 float seraph_b200_last_loss(cuda_train_context_t* ctx);
 /* Per-class kernel timing with CUDA events on the context's stream.  read() fills
  * out[class*4 + {0 ms, 1 algorithmic FLOPs, 2 algorithmic bytes, 3 launches}] and resets. */
@@ -301,6 +317,9 @@ void seraph_b200_state_set_lr(train_state_t* st, float lr, int accum);
 void* seraph_b200_state_weights(train_state_t* st);
 /* config->use_qk_norm of a state built by seraph_b200_state_create (the reference sets it for --video, src/train.c:7867-7868) */
 void seraph_b200_state_set_qk_norm(train_state_t* st, int on);
+/* state->debug_nan_check (tools/seraph_train_cuda.c --debug-nan) and state->nan_detected */
+void seraph_b200_state_set_debug_nan(train_state_t* st, int on);
+int seraph_b200_state_nan_detected(train_state_t* st);
 size_t seraph_b200_state_lora_count(train_state_t* st, int rank, int mask);
 int seraph_b200_state_attach_lora(train_state_t* st, int rank, float alpha, int mask, const float* flat);
 void seraph_b200_state_lora_get(train_state_t* st, int which, float* flat);

@@ -156,4 +156,49 @@ void refshim_cuda_download(void* p) {
     cuda_download_full_weights(s->cuda, &s->st);
 }
 void* refshim_cuda_ctx(void* p) { return ((shim_t*)p)->cuda; }
+
+/* The reference's packed causal attention on caller arrays: forward with the flash kernel (so that it writes the
+ * log-sum-exp, src/cuda_train_context.cu:1289) and backward with flash_attention_bwd_packed_kernel (:2012) through the
+ * reference's own wrappers (:3107).  Q, dO, O, dQ are [T, Hq*hd]; K, V, dK, dV [T, Hkv*hd]; lse [T, Hq].  dK and dV are
+ * zeroed first (the kernel adds into them with atomics, as src/train_cuda.c:2234-2237 does before calling it).
+ * ms[0], ms[1]: device time of the forward and of the backward call, the mean over `reps` repetitions after one
+ * untimed run.  Returns 0, or -1 when the context or a buffer could not be made. */
+#include <cuda_runtime_api.h>
+int refshim_cuda_attention(int device, const float* Q, const float* K, const float* V, const float* dO, const int* seq_starts,
+                           int B, int T, int Hq, int Hkv, int hd, int max_seq, int reps,
+                           float* O, float* lse, float* dQ, float* dK, float* dV, float* ms) {
+    cuda_train_context_t* c = cuda_train_init(device);
+    if (!c) return -1;
+    c->use_flash_attn = 1;
+    size_t nq = (size_t)T * Hq * hd, nkv = (size_t)T * Hkv * hd, nl = (size_t)T * Hq;
+    cuda_buffer_t* b[12]; size_t sz[12] = {nq, nkv, nkv, nq, nq, nl, nq, nkv, nkv, (size_t)B + 1, 0, 0};
+    int rc = 0;
+    for (int i = 0; i < 10; i++) { b[i] = cuda_train_buffer_create(c, sz[i] * 4); if (!b[i]) rc = -1; }
+    if (rc == 0) {
+        cuda_train_buffer_upload(c, b[0], Q, nq); cuda_train_buffer_upload(c, b[1], K, nkv); cuda_train_buffer_upload(c, b[2], V, nkv);
+        cuda_train_buffer_upload(c, b[3], dO, nq); cuda_train_buffer_upload_u32(c, b[9], (const uint32_t*)seq_starts, (size_t)B + 1);
+        cudaEvent_t e0, e1, e2; cudaEventCreate(&e0); cudaEventCreate(&e1); cudaEventCreate(&e2);
+        float tf = 0.f, tb = 0.f;
+        for (int r = 0; r <= reps; r++) {
+            cuda_train_fill_buffer(c, b[7], 0, nkv * 4); cuda_train_fill_buffer(c, b[8], 0, nkv * 4);
+            cudaEventRecord(e0, (cudaStream_t)c->stream);
+            cuda_train_batch_attention_packed(c, b[0], b[1], b[2], b[4], b[5], b[9], T, B, Hq, Hkv, hd, max_seq);
+            cudaEventRecord(e1, (cudaStream_t)c->stream);
+            cuda_train_batch_attention_backward_packed(c, b[0], b[1], b[2], b[4], b[5], b[3], b[6], b[7], b[8], b[9], T, B, Hq, Hkv, hd, max_seq);
+            cudaEventRecord(e2, (cudaStream_t)c->stream);
+            cuda_train_sync(c);
+            if (cudaGetLastError() != cudaSuccess) { rc = -2; break; }
+            if (r > 0) { float a = 0.f, d = 0.f; cudaEventElapsedTime(&a, e0, e1); cudaEventElapsedTime(&d, e1, e2); tf += a; tb += d; }
+        }
+        if (ms && reps > 0) { ms[0] = tf / reps; ms[1] = tb / reps; }
+        if (rc == 0) {
+            cuda_train_buffer_download(c, b[4], O, nq); cuda_train_buffer_download(c, b[5], lse, nl);
+            cuda_train_buffer_download(c, b[6], dQ, nq); cuda_train_buffer_download(c, b[7], dK, nkv); cuda_train_buffer_download(c, b[8], dV, nkv);
+        }
+        cudaEventDestroy(e0); cudaEventDestroy(e1); cudaEventDestroy(e2);
+    }
+    for (int i = 0; i < 10; i++) if (b[i]) cuda_train_buffer_free(c, b[i]);
+    cuda_train_free(c);
+    return rc;
+}
 #endif

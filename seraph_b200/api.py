@@ -83,11 +83,14 @@ def load():
         "seraph_b200_last_status": (i, [vp]), "seraph_b200_set_gemm_mode": (i, [vp, i]), "seraph_b200_set_gemm_pair": (i, [vp, i]), "seraph_b200_set_gemm_tail_split": (i, [vp, i]), "seraph_b200_set_parts_cache": (i, [vp, i]), "seraph_b200_set_attn_fused": (i, [vp, i]), "seraph_b200_set_attn_flash": (i, [vp, i]), "seraph_b200_qk_norm": (None, [vp, vp, vp, i, i, i, i, f]), "seraph_b200_qk_norm_backward": (None, [vp, vp, vp, vp, vp, i, i, i, i, f]), "seraph_b200_set_eval_batch_tokens": (i, [vp, i]),
         "seraph_b200_set_lora_exact": (i, [vp, i]), "seraph_b200_set_grad_clip": (i, [vp, f]),
         "seraph_b200_launch_count": (C.c_ulonglong, [vp, i]),
+        "seraph_b200_selftest_bounded_wait": (i, [vp, C.c_longlong, vp]),
+        "seraph_b200_nan_flags": (i, [vp, vp, i]), "seraph_b200_profiler_totals": (i, [vp, vp]),
+        "seraph_b200_state_set_debug_nan": (None, [vp, i]), "seraph_b200_state_nan_detected": (i, [vp]),
         "seraph_b200_embedding_segments": (i, [vp, i, i, vp, vp, vp]),
         "seraph_b200_swiglu": (None, [vp, B, B, B, sz]), "seraph_b200_swiglu_backward": (None, [vp, B, B, B, B, B, sz]),
         "seraph_b200_timer_start": (None, [vp]), "seraph_b200_timer_stop": (f, [vp]),
         "seraph_b200_download_logits": (i, [vp, vp, i]), "seraph_b200_reset_model": (i, [vp]),
-        "seraph_b200_step_full_resident": (i, [vp, vp]), "seraph_b200_last_loss": (f, [vp]),
+        "seraph_b200_step_full_resident": (i, [vp, vp]), "seraph_b200_step_resident": (i, [vp, vp, i]), "seraph_b200_last_loss": (f, [vp]),
         "seraph_b200_timing_enable": (i, [vp, i]), "seraph_b200_timing_classes": (i, []),
         "seraph_b200_timing_class_name": (C.c_char_p, [i]), "seraph_b200_timing_read": (i, [vp, vp]),
         "seraph_b200_state_create_lean": (vp, [i] * 7 + [f, f, i]),

@@ -85,6 +85,7 @@ cuda_train_context_t* cuda_train_init(int device_id) {
     { const char* e = getenv("SERAPH_B200_GEMM_TAIL_SPLIT"); c->gemm_tail_split = (e && e[0] == '0') ? 0 : 1; }
     { const char* e = getenv("SERAPH_B200_PARTS_CACHE"); c->parts_cache = (e && e[0] == '0') ? 0 : 1; }
     c->dp_world = 1;
+    { const char* e = getenv("SERAPH_B200_DP_TIMEOUT_MS"); c->dp_timeout_ms = (e && atoi(e) > 0) ? atoi(e) : 120000; }
     cuda_train_context_t* p = &c->pub;
     p->device_id = device_id; p->stream = s; p->initialized = 1;
     p->gpu_sm_count = prop.multiProcessorCount;
@@ -186,7 +187,19 @@ void cuda_train_copy_buffer(cuda_train_context_t* ctx, cuda_buffer_t* src, cuda_
 // Per-class timer: one CUDA-event pair per launch, recorded on the context's
 // stream, summed per kernel class on read-out.
 // ---------------------------------------------------------------------------
+// Names under which the class timer's launches appear in a cuda_profiler_t report; the reference's analysis sorts ops into its
+// categories by substrings of these names (src/cuda_profiler.cu:159-178).
+static const char* sb_prof_class_name(int cls) {
+    static const char* names[SB_NCLS] = {"matmul", "matmul_operand_prep", "attention", "attention_bwd", "rmsnorm", "rmsnorm_bwd",
+                                         "swiglu", "rope", "cross_entropy", "embedding", "adamw", "copy", "other"};
+    return (cls >= 0 && cls < SB_NCLS) ? names[cls] : "other";
+}
 int sb_tick_begin(sb_ctx_t* c, int cls) {
+    // every launcher passes through here, the training step's own launches included: with a profiler attached and no op-level
+    // record open around this launch, the launch becomes a profiler op of its class
+    c->tick_prof = 0;
+    if (c->profiler && c->profiler->enabled && c->prof_depth == 0)
+        c->tick_prof = 1 + cuda_profiler_begin_op(c->profiler, sb_prof_class_name(cls), c->pub.stream);
     if (!c->timing_on) return -1;
     if (c->tick_n >= c->tick_cap) {
         int ncap = c->tick_cap ? c->tick_cap * 2 : 4096;
@@ -212,6 +225,12 @@ int sb_tick_begin(sb_ctx_t* c, int cls) {
     return i;
 }
 void sb_tick_end(sb_ctx_t* c, int slot, double flops, double bytes) {
+    if (c->tick_prof > 0 && c->profiler) {
+        const int op = c->tick_prof - 1;
+        cuda_profiler_end_op(c->profiler, op, c->pub.stream);
+        cuda_profiler_set_flops(c->profiler, op, (size_t)flops); cuda_profiler_set_bytes(c->profiler, op, (size_t)bytes);
+    }
+    c->tick_prof = 0;
     if (slot < 0) return;
     cudaEventRecord((cudaEvent_t)c->tick_ev[2 * slot + 1], (cudaStream_t)c->pub.stream);
     c->tick_flops[slot] = flops; c->tick_bytes[slot] = bytes;
@@ -323,6 +342,27 @@ int seraph_b200_set_grad_clip(cuda_train_context_t* ctx, float max_norm) {
     if (!c || max_norm < 0) return SB_ERR_ARG;
     c->grad_clip = max_norm;
     return SB_OK;
+}
+
+// the NaN/Inf flags of the last step that ran with state->debug_nan_check (ctx->debug_nan_flags), copied to the host;
+// returns the number of words written
+int seraph_b200_nan_flags(cuda_train_context_t* ctx, uint32_t* out, int max_words) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c || !out || max_words <= 0 || !c->pub.debug_nan_flags) return 0;
+    int n = (int)(c->pub.debug_nan_flags->size / 4);
+    if (n > max_words) n = max_words;
+    cudaStreamSynchronize((cudaStream_t)ctx->stream);
+    return cudaMemcpy(out, c->pub.debug_nan_flags->data, (size_t)n * 4, cudaMemcpyDeviceToHost) == cudaSuccess ? n : 0;
+}
+
+// category totals of an analysed cuda_profiler_t as floats: step, matmul, attention, attention_bwd, rmsnorm, rmsnorm_bwd,
+// cross_entropy, adamw, copy, other (milliseconds); returns the number of recorded ops
+int seraph_b200_profiler_totals(cuda_profiler_t* p, float* out10) {
+    if (!p || !out10) return 0;
+    out10[0] = p->total_step_ms; out10[1] = p->total_matmul_ms; out10[2] = p->total_attention_ms; out10[3] = p->total_attention_bwd_ms;
+    out10[4] = p->total_rmsnorm_ms; out10[5] = p->total_rmsnorm_bwd_ms; out10[6] = p->total_cross_entropy_ms; out10[7] = p->total_adamw_ms;
+    out10[8] = p->total_copy_ms; out10[9] = p->total_other_ms;
+    return p->num_ops;
 }
 
 unsigned long long seraph_b200_launch_count(cuda_train_context_t* ctx, int reset) {

@@ -64,9 +64,11 @@ int seraph_dp_get_unique_id(void* id_out_128) {
     return SB_OK;
 }
 
+void sb_dp_finalize(sb_ctx_t* c);
 int seraph_dp_init(cuda_train_context_t* ctx, int rank, int world, const void* nccl_unique_id) {
     sb_ctx_t* c = sb_priv(ctx);
     if (!c || world < 1 || rank < 0 || rank >= world) return SB_ERR_ARG;
+    if (c->nccl_comm || c->comm_stream) sb_dp_finalize(c);      /* a second init, or one after an aborted communicator */
     if (world == 1) { c->dp_world = 1; c->dp_rank = 0; return SB_OK; }
     if (!nccl_unique_id || load_nccl()) return SB_ERR_NCCL;
     if (cudaSetDevice(ctx->device_id) != cudaSuccess) return SB_ERR_CUDA;
@@ -80,13 +82,33 @@ int seraph_dp_init(cuda_train_context_t* ctx, int rank, int world, const void* n
     return SB_OK;
 }
 
+/* The communicator is gone (destroyed or aborted): single-GPU from here on.  The stream and the events stay until
+ * sb_dp_finalize, because work of the compute stream may still be ordered behind them. */
+static void dp_drop_comm(sb_ctx_t* c, int status) {
+    if (c->nccl_comm) N.CommAbort((ncclComm_t)c->nccl_comm);
+    c->nccl_comm = NULL; c->dp_world = 1; c->dp_rank = 0;
+    if (status) {
+        c->status = status;
+        fprintf(stderr, "seraph_b200: data parallelism is off for this context after the failure above; later steps run on this GPU alone\n");
+    }
+}
+
+#define DP_FINALIZE_TIMEOUT_MS 30000
 void sb_dp_finalize(sb_ctx_t* c) {
-    if (!c || !c->nccl_comm) return;
-    cudaStreamSynchronize((cudaStream_t)c->comm_stream);
-    N.CommDestroy((ncclComm_t)c->nccl_comm);
-    for (int i = 0; i < 64; i++) if (c->ev_bucket[i]) cudaEventDestroy((cudaEvent_t)c->ev_bucket[i]);
-    cudaStreamDestroy((cudaStream_t)c->comm_stream);
-    c->nccl_comm = NULL; c->comm_stream = NULL; c->dp_world = 1; c->dp_rank = 0;
+    if (!c) return;
+    if (c->nccl_comm) {
+        /* bounded: a peer that died leaves collectives of this rank unfinished for ever */
+        if (seraph_dp_wait(&c->pub, DP_FINALIZE_TIMEOUT_MS) == SB_OK && c->nccl_comm) {
+            N.CommDestroy((ncclComm_t)c->nccl_comm);
+            c->nccl_comm = NULL;
+        }
+    }
+    if (c->comm_stream) {
+        for (int i = 0; i < 64; i++) if (c->ev_bucket[i]) { cudaEventDestroy((cudaEvent_t)c->ev_bucket[i]); c->ev_bucket[i] = NULL; }
+        cudaStreamDestroy((cudaStream_t)c->comm_stream);
+        c->comm_stream = NULL;
+    }
+    c->nccl_comm = NULL; c->dp_world = 1; c->dp_rank = 0; c->n_buckets = 0;
 }
 void seraph_dp_finalize(cuda_train_context_t* ctx) { sb_dp_finalize(sb_priv(ctx)); }
 
@@ -111,8 +133,7 @@ int sb_dp_join(sb_ctx_t* c) {
     ncclResult_t async = ncclSuccess;
     if (N.CommGetAsyncError((ncclComm_t)c->nccl_comm, &async) != ncclSuccess || async != ncclSuccess) {
         fprintf(stderr, "seraph_b200: NCCL reported an asynchronous error; aborting the communicator\n");
-        N.CommAbort((ncclComm_t)c->nccl_comm);
-        c->nccl_comm = NULL; c->dp_world = 1; c->status = SB_ERR_NCCL;
+        dp_drop_comm(c, SB_ERR_NCCL);
         return 1;
     }
     return 0;
@@ -145,9 +166,9 @@ int seraph_dp_wait(cuda_train_context_t* ctx, int timeout_ms) {
         if (q != cudaErrorNotReady || async != ncclSuccess || ms > timeout_ms) {
             fprintf(stderr, "seraph_b200: data-parallel wait failed (%s); aborting the communicator\n",
                     ms > timeout_ms ? "time-out" : "error");
-            N.CommAbort((ncclComm_t)c->nccl_comm);
-            c->nccl_comm = NULL; c->dp_world = 1; c->status = ms > timeout_ms ? SB_ERR_TIMEOUT : SB_ERR_NCCL;
-            return c->status;
+            const int st = ms > timeout_ms ? SB_ERR_TIMEOUT : SB_ERR_NCCL;
+            dp_drop_comm(c, st);
+            return st;
         }
         struct timespec nap = {0, 200000}; nanosleep(&nap, NULL);
     }

@@ -289,3 +289,30 @@ extern "C" int sb_gemm_tc(sb_ctx_t* c, const float* A, const float* B, float* C,
     if (!ok) { sb_set_status(c, SB_ERR_CUDA); return 1; }
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Self-test of the bounded-wait rule every tensor-core kernel of this library follows: one warp waits, with a limit of
+// `limit_cycles` clock cycles, on an mbarrier phase that nothing completes; the wait gives up, the kernel records
+// SB_ERR_TIMEOUT in the context's device status word and returns normally (no trap, the context stays usable).
+__global__ void tc_bounded_wait_selftest_kernel(long long limit_cycles, int* status, long long* waited) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        const long long t0 = clock64();
+        const bool ok = mbar_wait_limit(&bar, 0, limit_cycles);
+        if (waited) *waited = clock64() - t0;
+        if (!ok) atomicExch(status, SB_ERR_TIMEOUT);
+    }
+}
+extern "C" int seraph_b200_selftest_bounded_wait(cuda_train_context_t* ctx, long long limit_cycles, long long* waited_cycles_out) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c || limit_cycles <= 0 || limit_cycles > 2000000000ll) return SB_ERR_ARG;      // at most about a second
+    long long* d_w = (long long*)sb_scratch(c, 64);
+    if (!d_w) return SB_ERR_OOM;
+    tc_bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)c->pub.stream>>>(limit_cycles, c->d_status, d_w);
+    c->launches++;
+    if (sb_check(c, cudaStreamSynchronize((cudaStream_t)c->pub.stream), "bounded-wait self-test")) return SB_ERR_CUDA;
+    if (waited_cycles_out && cudaMemcpy(waited_cycles_out, d_w, sizeof(long long), cudaMemcpyDeviceToHost) != cudaSuccess) return SB_ERR_CUDA;
+    return SB_OK;
+}

@@ -99,17 +99,18 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-// bounded wait; returns false when the deadline passed
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// bounded wait; returns false when `limit` clock cycles passed without the phase completing
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, long long limit) {
     uint32_t addr = smem_u32(bar), done = 0;
     long long t0 = clock64();
     for (;;) {
         asm volatile("{\n\t.reg .pred P;\n\tmbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\tselp.u32 %0, 1, 0, P;\n\t}"
                      : "=r"(done) : "r"(addr), "r"(parity) : "memory");
         if (done) return true;
-        if (clock64() - t0 > TC_SPIN_CYCLES) return false;
+        if (clock64() - t0 > limit) return false;
     }
 }
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) { return mbar_wait_limit(bar, parity, TC_SPIN_CYCLES); }
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
                  ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");

@@ -114,6 +114,9 @@ void seraph_b200_state_get_counters(train_state_t* st, int* optimizer_step, int*
 void seraph_b200_state_set_lr(train_state_t* st, float lr, int accum) { st->learning_rate = lr; st->gradient_accumulation_steps = accum; }
 void* seraph_b200_state_weights(train_state_t* st) { return st ? (void*)st->full_weights : NULL; }
 void seraph_b200_state_set_qk_norm(train_state_t* st, int on) { if (st && st->config) st->config->use_qk_norm = on ? 1 : 0; }
+/* train_state_t.debug_nan_check (the CLI's --debug-nan) and the flag the step sets when it trips */
+void seraph_b200_state_set_debug_nan(train_state_t* st, int on) { if (st) { st->debug_nan_check = on ? 1 : 0; st->nan_detected = 0; } }
+int seraph_b200_state_nan_detected(train_state_t* st) { return st ? st->nan_detected : 0; }
 
 /* ---- LoRA ---- */
 static void dims(const model_config_t* c, int a, int* in, int* out) {

@@ -319,7 +319,7 @@ void cuda_train_nan_check(cuda_train_context_t* ctx, cuda_buffer_t* input, size_
 
 void cuda_train_set_profiler(cuda_train_context_t* ctx, cuda_profiler_t* prof) {
     sb_ctx_t* c = sb_priv(ctx);
-    if (c) c->profiler = prof;
+    if (c) { c->profiler = prof; c->prof_depth = 0; c->tick_prof = 0; }
 }
 
 // ---------------------------------------------------------------------------

@@ -123,12 +123,16 @@ void cuda_profiler_print_top(cuda_profiler_t* p, int top_n) {
 }
 void cuda_profiler_set_log(cuda_profiler_t* p, void* file_ptr) { if (p) p->log_file = file_ptr; }
 
+// op-level record around one call of the per-op C ABI; the launches inside it are not recorded a second time
 int sb_prof_begin(sb_ctx_t* c, const char* name) {
     if (!c->profiler || !c->profiler->enabled) return -1;
-    return cuda_profiler_begin_op(c->profiler, name, c->pub.stream);
+    const int op = cuda_profiler_begin_op(c->profiler, name, c->pub.stream);
+    if (op >= 0) c->prof_depth++;
+    return op;
 }
 void sb_prof_end(sb_ctx_t* c, int op, size_t flops, size_t bytes) {
     if (op < 0 || !c->profiler) return;
+    if (c->prof_depth > 0) c->prof_depth--;
     cuda_profiler_end_op(c->profiler, op, c->pub.stream);
     c->profiler->ops[op].flops = flops; c->profiler->ops[op].bytes = bytes;
 }

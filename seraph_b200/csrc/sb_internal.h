@@ -80,6 +80,8 @@ typedef struct sb_ctx {
     int gemm_pair;                   /* 1: plain GEMMs run on CTA pairs (cta_group::2), 0: one CTA per tile */
     int lora_exact;                  /* 0: reference behaviour (adapter dX term left out), 1: full chain rule */
     float grad_clip;                 /* 0 = off (the reference has none) */
+    int nan_on; uint32_t nan_count;  /* a step with state->debug_nan_check is filling pub.debug_nan_flags (nan_count words) */
+    int prof_depth; int tick_prof;   /* an op-level profiler record is open; 1 + the profiler record opened by the running class timer */
     cuda_profiler_t* profiler;
     size_t launches;                 /* kernels launched since the last reset */
     int timing_on;                   /* per-class CUDA-event timing of every launch */
@@ -123,6 +125,7 @@ typedef struct sb_ctx {
 
     /* data parallel */
     void* nccl_comm; int dp_rank, dp_world;
+    int dp_timeout_ms;               /* host-side limit for a step's collectives (SERAPH_B200_DP_TIMEOUT_MS, default 120 s) */
     void* comm_stream; void* ev_bucket[64]; int n_buckets;
     void* side_stream[4]; void* side_ev[5]; int side_ready;   /* side streams of the attention path (sequences run side by side) */
     size_t bucket_begin[64], bucket_end[64];

@@ -206,6 +206,8 @@ static void down_tensor(sb_ctx_t* c, weight_tensor_t* t, size_t off, void* arg) 
 
 /* Allocate the arenas for this geometry and upload the host master copy once
  * (the reference uploads once and afterwards only downloads, src/train_cuda.c:286-291). */
+static void free_lora(sb_ctx_t* c);
+static void free_activations(sb_ctx_t* c);
 static int ensure_model(sb_ctx_t* c, const train_state_t* st, int frozen_base) {
     const model_config_t* cfg = st->config;
     int V = cfg->vocab_size, d = cfg->hidden_size, L = cfg->num_hidden_layers, F = cfg->intermediate_size;
@@ -215,6 +217,9 @@ static int ensure_model(sb_ctx_t* c, const train_state_t* st, int frozen_base) {
         c->frozen_base == frozen_base) return 0;
     if (!st->full_weights) { sb_set_status(c, SB_ERR_ARG); return 1; }
     cudaStreamSynchronize(S(c));
+    /* the activation slots, the registered operand parts and the adapter arenas were carved for the old geometry
+       (the reference reallocates on a geometry change too, src/train.c:2705) */
+    if (c->V != V || c->d != d || c->L != L || c->F != F || c->Hq != Hq || c->Hkv != Hkv || c->hd != hd) { free_activations(c); free_lora(c); }
     free_model(c);
     c->V = V; c->d = d; c->L = L; c->F = F; c->Hq = Hq; c->Hkv = Hkv; c->hd = hd; c->qd = Hq * hd; c->kvd = Hkv * hd;
     c->frozen_base = frozen_base;
@@ -420,10 +425,69 @@ static void lora_bwd(sb_ctx_t* c, int l, int a, const float* dY, const float* X,
     if (c->lora_exact && dX) sb_gemm(c, c->lora_tmp, r.A, dX, T, r.in, c->lora_rank, 0, 0, 1);
 }
 
+/* NaN/Inf flags of a training step with state->debug_nan_check set, indexed as the reference indexes them
+ * (src/train_cuda.c:626-645): [0..9] fixed buffers, [10 + l] hidden after layer l, [10 + L + 5 l + 0..3] grad_attn,
+ * grad_q, grad_k, grad_v of layer l, [10 + 6 L + l] grad_hidden after layer l's backward, [10 + 7 L] embedding weights. */
+static uint32_t nan_fwd_base(const sb_ctx_t* c) { (void)c; return 10u; }
+static uint32_t nan_bwd_base(const sb_ctx_t* c) { return 10u + (uint32_t)c->L; }
+static uint32_t nan_ghid_base(const sb_ctx_t* c) { return 10u + 6u * (uint32_t)c->L; }
+static uint32_t nan_weight_idx(const sb_ctx_t* c) { return 10u + 7u * (uint32_t)c->L; }
+static void nan_mark(sb_ctx_t* c, const float* p, size_t n, uint32_t idx) {
+    if (!c->nan_on || !c->pub.debug_nan_flags || idx >= c->nan_count) return;
+    sb_nan_check(c, p, n, (uint32_t*)c->pub.debug_nan_flags->data, idx);
+}
+static int nan_begin(sb_ctx_t* c, int on) {
+    c->nan_on = 0;
+    if (!on) return 0;
+    uint32_t count = nan_weight_idx(c) + 5u;
+    if (!c->pub.debug_nan_flags || c->pub.debug_nan_flags->size < (size_t)count * 4) {
+        cudaStreamSynchronize(S(c));
+        if (c->pub.debug_nan_flags) cuda_train_buffer_free(&c->pub, c->pub.debug_nan_flags);
+        c->pub.debug_nan_flags = cuda_train_buffer_create(&c->pub, (size_t)count * 4);
+        if (!c->pub.debug_nan_flags) return 1;
+    }
+    c->nan_count = count; c->nan_on = 1;
+    sb_memset(c, c->pub.debug_nan_flags->data, 0, (size_t)count * 4);
+    return 0;
+}
+/* Reads the flags back (synchronises).  Returns 1 and reports the buffers when any is set. */
+static int nan_tripped(sb_ctx_t* c, const train_state_t* st, int T) {
+    if (!c->nan_on) return 0;
+    uint32_t* h = (uint32_t*)calloc(c->nan_count, sizeof(uint32_t));
+    if (!h) return 0;
+    int any = 0;
+    if (cudaMemcpyAsync(h, c->pub.debug_nan_flags->data, (size_t)c->nan_count * 4, cudaMemcpyDeviceToHost, S(c)) == cudaSuccess &&
+        cudaStreamSynchronize(S(c)) == cudaSuccess)
+        for (uint32_t i = 0; i < c->nan_count; i++) if (h[i]) { any = 1; break; }
+    if (any) {
+        static const char* fixed[10] = {"grad_hidden (post final-norm backward)", "logits (LM head output)", "hidden_norm (LM head input)",
+            "grad_logits (cross-entropy grad)", "grad_hidden (after LM head backward)", "grad_tmp_hidden (final rmsnorm backward output)",
+            "final_input (pre final rmsnorm)", "hidden (post embedding)", "grad_hidden (pre embedding_backward)", "g_embed (post embedding_backward)"};
+        fprintf(stderr, "[NAN] detected at step=%d seq=%d (optimizer skipped)\n", st->current_step + 1, T);
+        fprintf(stderr, "  - lr(base)=%g opt_step=%d accum=%d/%d\n", (double)st->learning_rate, st->optimizer_step, st->accumulation_counter,
+                st->gradient_accumulation_steps);
+        for (int i = 0; i < 10; i++) if (h[i]) fprintf(stderr, "  - buffer: %s\n", fixed[i]);
+        if (h[nan_weight_idx(c)]) fprintf(stderr, "  - buffer: w_embed (weights already NaN/Inf at step start)\n");
+        for (int l = 0; l < c->L; l++) if (h[nan_fwd_base(c) + l]) { fprintf(stderr, "  - buffer: hidden (post layer) layer=%d\n", l); break; }
+        for (int l = 0; l < c->L; l++) {
+            const uint32_t* b = h + nan_bwd_base(c) + 5u * (uint32_t)l;
+            static const char* nm[4] = {"grad_attn (input to attn backward)", "grad_q (post rope_backward)", "grad_k (post attn backward)", "grad_v (post attn backward)"};
+            int hit = -1;
+            for (int k = 0; k < 4; k++) if (b[k]) { hit = k; break; }
+            if (hit >= 0) { fprintf(stderr, "  - buffer: %s layer=%d\n", nm[hit], l); break; }
+        }
+        for (int l = 0; l < c->L; l++) if (h[nan_ghid_base(c) + l]) { fprintf(stderr, "  - buffer: grad_hidden (after layer backward) layer=%d\n", l); break; }
+    }
+    free(h);
+    return any;
+}
+
 static void forward_pass(sb_ctx_t* c, int T, int max_seq, float theta, int use_lora) {
     const int d = c->d, F = c->F, qd = c->qd, kvd = c->kvd, L = c->L;
     const size_t Td = (size_t)T * d;
+    nan_mark(c, c->W, (size_t)c->V * d, nan_weight_idx(c));
     sb_embed_lookup(c, c->tokens, c->W, c->act[0].layer_in, T, d, c->V);
+    nan_mark(c, c->act[0].layer_in, Td, 7);
     for (int l = 0; l < L; l++) {
         const sb_layer_off_t* o = &c->off[l];
         sb_layer_act_t* a = &c->act[l];
@@ -457,10 +521,13 @@ static void forward_pass(sb_ctx_t* c, int T, int max_seq, float theta, int use_l
         sb_swiglu(c, a->gate, a->up, a->ffn_hidden, (size_t)T * F);
         sb_copy(c, next_in, a->post_attn_in, Td * sizeof(float));
         linear_fwd(c, use_lora, l, 6, a->ffn_hidden, c->W + o->down, next_in, T, F, d, 1);
+        nan_mark(c, next_in, Td, nan_fwd_base(c) + (uint32_t)l);
     }
     sb_amax_announce(c, c->hidden_norm, Td);
     sb_rmsnorm(c, c->final_in, c->W + (size_t)c->V * d, c->hidden_norm, T, d, RMS_EPS);
+    nan_mark(c, c->hidden_norm, Td, 2); nan_mark(c, c->final_in, Td, 6);
     sb_gemm(c, c->hidden_norm, c->W, c->logits, T, c->V, d, 0, 1, 0);       /* tied LM head */
+    nan_mark(c, c->logits, (size_t)T * c->V, 1);
 }
 
 /* `reduce`: hand every finished gradient range to the data-parallel all-reduce as soon as it is complete */
@@ -474,8 +541,10 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
     sb_gemm(c, c->dlogits, c->W, gx, T, d, V, 0, 0, 0);
     if (full) sb_gemm(c, c->dlogits, c->hidden_norm, Gd, V, d, T, 1, 0, 1);
     sb_gemm_keep_end(c);
+    nan_mark(c, c->dlogits, (size_t)T * V, 3); nan_mark(c, gx, (size_t)T * d, 4);
     sb_amax_announce(c, gh, (size_t)T * d);
     sb_rmsnorm_backward(c, c->final_in, c->W + (size_t)V * d, gx, NULL, gh, full ? Gd + (size_t)V * d : norm_sink, T, d, RMS_EPS);
+    nan_mark(c, gh, (size_t)T * d, 5); nan_mark(c, gh, (size_t)T * d, 0);
     for (int l = L - 1; l >= 0; l--) {
         const sb_layer_off_t* o = &c->off[l];
         sb_layer_act_t* a = &c->act[l];
@@ -504,6 +573,7 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
         sb_gemm(c, gh, c->W + o->o, c->g_attn, T, qd, d, 0, 0, 0);
         sb_gemm_keep_end(c);
         if (!full) lora_bwd(c, l, 3, gh, a->attn_out, c->g_attn, T);
+        nan_mark(c, c->g_attn, (size_t)T * qd, nan_bwd_base(c) + 5u * (uint32_t)l);
         sb_attention_backward(c, a->q, a->k, a->v, a->attn_out, a->lse, c->g_attn, c->g_q, c->g_k, c->g_v, 0,
                               c->seq_starts, c->seq_ids, B, T, c->Hq, c->Hkv, c->hd);
         if (c->qk_norm) {
@@ -513,6 +583,10 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
         }
         sb_amax_announce(c, c->g_q, (size_t)T * qd); sb_amax_announce(c, c->g_k, (size_t)T * kvd);
         sb_rope2(c, c->g_q, c->g_k, c->pos_ids, T, c->Hq, c->Hkv, c->hd, theta, max_seq, 1);
+        if (c->nan_on) {
+            const uint32_t nb = nan_bwd_base(c) + 5u * (uint32_t)l;
+            nan_mark(c, c->g_q, (size_t)T * qd, nb + 1); nan_mark(c, c->g_k, (size_t)T * kvd, nb + 2); nan_mark(c, c->g_v, (size_t)T * kvd, nb + 3);
+        }
         if (full) {
             sb_gemm_keep_begin(c);
             sb_gemm(c, c->g_q, a->x_norm_attn, Gd + o->q, qd, d, T, 1, 0, 1);
@@ -526,13 +600,16 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
         if (!full) { lora_bwd(c, l, 0, c->g_q, a->x_norm_attn, gx, T); lora_bwd(c, l, 1, c->g_k, a->x_norm_attn, gx, T); lora_bwd(c, l, 2, c->g_v, a->x_norm_attn, gx, T); }
         sb_amax_announce(c, gh, (size_t)T * d);
         sb_rmsnorm_backward(c, a->layer_in, c->W + o->in_norm, gx, gh, gh, full ? Gd + o->in_norm : norm_sink, T, d, RMS_EPS);
+        nan_mark(c, gh, (size_t)T * d, nan_ghid_base(c) + (uint32_t)l);
         if (reduce) {
             if (full) sb_dp_bucket_ready(c, Gd + o->q, o->post_norm + (size_t)d - o->q);
             else { size_t per = lora_layer_params(c); sb_dp_bucket_ready(c, c->LG + per * (size_t)l, per); }
         }
     }
     if (full) {
+        nan_mark(c, gh, (size_t)T * d, 8);
         sb_embedding_backward(c, c->tokens, gh, Gd, T, d, V);
+        nan_mark(c, Gd, (size_t)V * d, 9);
         if (reduce) sb_dp_bucket_ready(c, Gd, c->off[0].q);      /* embedding (LM head + scatter) and final norm */
     }
 }
@@ -605,6 +682,7 @@ static float step_body(train_state_t* st, int* tokens, int T, int* seq_starts, i
     }
     c->pub.batch_size = B;
 
+    if (nan_begin(c, train && st->debug_nan_check)) return -1.0f;
     if (train && st->accumulation_counter == 0) {
         if (full) sb_memset(c, c->G, 0, c->n_params * sizeof(float));
         else sb_memset(c, c->LG, 0, c->n_lora * sizeof(float));
@@ -618,6 +696,17 @@ static float step_body(train_state_t* st, int* tokens, int T, int* seq_starts, i
         int accum = st->gradient_accumulation_steps < 1 ? 1 : st->gradient_accumulation_steps;
         int last_micro = (st->accumulation_counter + 1 >= accum);
         backward_pass(c, T, B, max_seq, theta, full, last_micro && c->dp_world > 1);
+        if (c->nan_on) {
+            /* the reference reads its flags back before the optimizer and skips it when one is set, leaving the counters alone
+               (src/train_cuda.c:1086-1187).  Data parallel: the buckets are already in flight, so every rank first waits for them and
+               then looks at the whole reduced gradient, which is the same on all ranks, so that all of them skip or none does. */
+            if (last_micro && c->dp_world > 1) {
+                if (sb_dp_join(c)) return -1.0f;
+                nan_mark(c, full ? c->G : c->LG, full ? c->n_params : c->n_lora, 9);
+            }
+            if (nan_tripped(c, st, T)) { c->nan_on = 0; st->nan_detected = 1; return NAN; }
+            c->nan_on = 0;
+        }
         st->accumulation_counter++;
         if (st->accumulation_counter >= accum) {
             st->optimizer_step++;
@@ -637,6 +726,9 @@ static float step_body(train_state_t* st, int* tokens, int T, int* seq_starts, i
         }
     }
     if (resident) return sb_check(c, cudaGetLastError(), "training step (resident batch)") ? -1.0f : 0.0f;
+    /* data parallel: a peer that died leaves this rank's collectives unfinished for ever; wait for them with a limit on the host
+       (the communicator is aborted when it runs out) instead of inside the unbounded stream synchronisation below */
+    if (train && c->dp_world > 1 && seraph_dp_wait(ctx, c->dp_timeout_ms) != SB_OK) return -1.0f;
     float* h_loss = (float*)((char*)c->h_pinned + c->h_pinned_bytes - 64);
     cudaMemcpyAsync(h_loss, c->d_loss, sizeof(float), cudaMemcpyDeviceToHost, S(c));
     if (sb_check(c, cudaStreamSynchronize(S(c)), "training step")) return -1.0f;
@@ -803,6 +895,13 @@ int seraph_b200_step_full_resident(train_state_t* state, cuda_train_context_t* c
     float r = step_common(state, NULL, c->res_T, NULL, c->res_B, ctx, 1, 1, 1);
     return r < 0.f ? (c->status ? c->status : SB_ERR_ARG) : SB_OK;
 }
+/* the same for either kind of step: full != 0 the full-weight step, 0 the LoRA step of a state with adapters attached */
+int seraph_b200_step_resident(train_state_t* state, cuda_train_context_t* ctx, int full) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c || !state || c->res_T <= 0) return SB_ERR_ARG;
+    float r = step_common(state, NULL, c->res_T, NULL, c->res_B, ctx, full ? 1 : 0, 1, 1);
+    return r < 0.f ? (c->status ? c->status : SB_ERR_ARG) : SB_OK;
+}
 /* mean loss of the last step, read from the device (synchronises) */
 float seraph_b200_last_loss(cuda_train_context_t* ctx) {
     sb_ctx_t* c = sb_priv(ctx);
@@ -834,6 +933,7 @@ int seraph_b200_reset_model(cuda_train_context_t* ctx) {
     if (!c) return SB_ERR_ARG;
     cudaStreamSynchronize(S(c));
     free_lora(c);
+    free_activations(c);
     free_model(c);
     return SB_OK;
 }

@@ -1,0 +1,108 @@
+"""Child process of tests/test_gpu_dp.py: one data-parallel rank driving libseraph_b200 directly (no torch, so that the
+NCCL the library opens with dlopen is the one LD_LIBRARY_PATH offers).  Not collected by pytest.
+
+    python dp_worker.py real  <rank> <world> <dir> <accum>     two or more real ranks over NCCL, one GPU each
+    python dp_worker.py fake  <mode> <dir>                     one rank of a pretended world of 2 over a fake libnccl.so.2
+"""
+import os
+import sys
+import time
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+sys.path.insert(0, os.path.dirname(HERE))
+
+
+def exchange_id(lib, rank, d):
+    path = os.path.join(d, "nccl_id.bin")
+    uid = np.zeros(128, np.uint8)
+    if rank == 0:
+        assert lib.seraph_dp_get_unique_id(uid.ctypes.data) == 0
+        with open(path + ".tmp", "wb") as f:
+            f.write(uid.tobytes())
+        os.rename(path + ".tmp", path)
+    else:
+        t0 = time.time()
+        while not os.path.exists(path):
+            if time.time() - t0 > 120:
+                raise RuntimeError("rank 0 never wrote the communicator id")
+            time.sleep(0.05)
+        uid = np.frombuffer(open(path, "rb").read(), np.uint8).copy()
+    return uid
+
+
+def real(rank, world, d, accum):
+    from seraph_b200 import api
+    import oracle_lib as O
+    cfg, ss = O.TINY, np.array(O.TINY_SEQS, np.int32)
+    ctx = api.Context(rank)
+    uid = exchange_id(ctx.lib, rank, d)
+    assert ctx.lib.seraph_dp_init(ctx.h, rank, world, uid.ctypes.data) == 0
+    assert ctx.lib.seraph_dp_world(ctx.h) == world
+    p = cfg.init_params(7, norm_jitter=0.1)                         # same weights on every rank
+    st = api.TrainState(cfg, p, accum=accum)
+    losses = []
+    for micro in range(accum):
+        tok = np.random.default_rng(100 + 10 * rank + micro).integers(0, cfg.V, int(ss[-1])).astype(np.int32)
+        losses.append(api.step_full_batch(ctx, st, tok, ss))
+    ctx.check()
+    assert ctx.lib.seraph_dp_wait(ctx.h, 20000) == 0
+    ctx.lib.cuda_download_gpu_gradients(ctx.h, st.h)
+    ctx.lib.cuda_download_full_weights(ctx.h, st.h)
+    np.savez(os.path.join(d, f"rank{rank}.npz"), w=st.get(0), g=st.get(1), m=st.get(2), v=st.get(3), loss=np.array(losses),
+             counters=np.array(st.counters()))
+    st.close()
+    ctx.close()
+
+
+def fake(mode, d):
+    """world of 2 with a libnccl.so.2 that only pretends: its all-reduce parks a host callback on the stream that sleeps
+    FAKE_NCCL_SLEEP_MS, its asynchronous-error query reports FAKE_NCCL_ASYNC_ERROR.  Nothing on the GPU waits or faults."""
+    from seraph_b200 import api
+    import oracle_lib as O
+    cfg, ss = O.TINY, np.array(O.TINY_SEQS, np.int32)
+    ctx = api.Context(0)
+    uid = np.zeros(128, np.uint8)
+    assert ctx.lib.seraph_dp_get_unique_id(uid.ctypes.data) == 0
+    assert bytes(uid[:4]) == b"FAKE", "the fake NCCL was not the one loaded"
+    assert ctx.lib.seraph_dp_init(ctx.h, 0, 2, uid.ctypes.data) == 0
+    st = api.TrainState(cfg, cfg.init_params(7))
+    tok = np.random.default_rng(1).integers(0, cfg.V, int(ss[-1])).astype(np.int32)
+    out = {}
+    if mode == "timeout":
+        # the pretended all-reduce outlasts SERAPH_B200_DP_TIMEOUT_MS: the step gives up on the host, aborts the communicator
+        # and returns -1 instead of hanging in its stream synchronisation
+        t0 = time.time()
+        loss = api.step_full_batch(ctx, st, tok, ss)
+        out["step_rc"], out["step_s"] = float(loss), time.time() - t0
+        out["world_after"] = int(ctx.lib.seraph_dp_world(ctx.h))
+        out["status"] = int(ctx.status())
+        ctx.sync()                                                  # the parked callbacks end by themselves; the context stays usable
+        loss2 = api.step_full_batch(ctx, st, tok, ss)               # single-GPU from here on
+        out["loss_after_finite"] = bool(np.isfinite(loss2) and loss2 > 0)
+    elif mode == "async_error":
+        loss = api.step_full_batch(ctx, st, tok, ss)
+        out["step_rc"] = float(loss)
+        out["world_after"] = int(ctx.lib.seraph_dp_world(ctx.h))
+        out["status"] = int(ctx.status())
+    elif mode == "ok":
+        loss = api.step_full_batch(ctx, st, tok, ss)
+        out["loss_finite"] = bool(np.isfinite(loss))
+        out["wait_rc"] = int(ctx.lib.seraph_dp_wait(ctx.h, 5000))
+        out["world_after"] = int(ctx.lib.seraph_dp_world(ctx.h))
+        ctx.lib.seraph_dp_finalize(ctx.h)
+        out["world_final"] = int(ctx.lib.seraph_dp_world(ctx.h))
+    st.close()
+    ctx.close()
+    import json
+    with open(os.path.join(d, "fake_result.json"), "w") as f:
+        json.dump(out, f)
+
+
+if __name__ == "__main__":
+    if sys.argv[1] == "real":
+        real(int(sys.argv[2]), int(sys.argv[3]), sys.argv[4], int(sys.argv[5]))
+    else:
+        fake(sys.argv[2], sys.argv[3])

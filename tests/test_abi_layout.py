@@ -10,7 +10,8 @@ import tempfile
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF = os.environ.get("SERAPH_REFERENCE", "/root/reference")
+# the reference checkout: SERAPH_REFERENCE, or a directory `reference` beside this repository
+REF = os.environ.get("SERAPH_REFERENCE") or os.path.abspath(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "reference"))
 
 FIELDS = {
     "cuda_buffer_t": ["data", "size"],

@@ -237,7 +237,7 @@ def reference_cuda_legs(device):
         rc = fn(device, Q, K, V, dO, np.arange(0, T + 1, S, dtype=np.int32), B, T, H, H, D, S, 2, o, lse, dq, dk, dv, ms)
         if rc == 0:
             out["c2_attn_fwd_ms"], out["c2_attn_bwd_ms"] = float(ms[0]), float(ms[1])
-            out["c2_attn_bwd_tflops"] = attention_flops(B, S, H, D)[1] / (ms[1] * 1e-3) * 1e-12
+            out["c2_attn_bwd_tflops"] = float(attention_flops(B, S, H, D)[1] / (float(ms[1]) * 1e-3) * 1e-12)
         else:
             out["c2_unavailable"] = f"reference attention call returned {rc}"
     except Exception as e:      # noqa: BLE001
@@ -361,7 +361,7 @@ def run_attention(args, w):
                                       f"issued = three FP16 passes per product x {args.attn_products} products per block"}}
     if not args.no_cpu_baseline:
         line["reference_cuda"] = reference_cuda_legs(0)
-    os.write(real_stdout, (json.dumps(line) + "\n").encode())
+    os.write(real_stdout, (json.dumps(line, default=float) + "\n").encode())
     ctx.close()
 
 
@@ -537,7 +537,7 @@ def run_ours(args):
             line["cpu_baseline"] = cpu_reference_sample(mc, S)
             if ref_cuda is not None:
                 line["reference_cuda"] = ref_cuda
-        os.write(real_stdout, (json.dumps(line) + "\n").encode())
+        os.write(real_stdout, (json.dumps(line, default=float) + "\n").encode())
     st.close()
     ctx.close()
     if world > 1:

@@ -199,6 +199,14 @@ int seraph_b200_load_safetensors(cuda_train_context_t* ctx, train_state_t* state
  * safetensors file as above plus "<path>.state" (current_epoch, current_step, current_loss, optimizer_step).
  * SB_ERR_ARG for a LoRA state (those go through cuda_download_lora_weights and the reference's lora_save). */
 int seraph_b200_save_checkpoint(cuda_train_context_t* ctx, train_state_t* state, const char* path);
+/* LoRA adapter files.  version 2 is the reference's format, byte for byte (lora_save, src/lora.c:441-494): the Q and V
+ * adapters only, which is all that format holds.  version 3 is an extension that keeps every adapter the model trains
+ * (k, o, gate, up, down too, which the reference trains and then drops on save) and, with with_moments != 0, the Adam
+ * moments and the optimizer step, so that a LoRA run can resume.  Saving first downloads the resident adapters
+ * (cuda_download_lora_weights).  seraph_b200_lora_load reads either version into the adapters `state` already holds (same
+ * rank and shapes, as lora_load of src/lora.c:496-560 would create them) and makes the next LoRA step upload them. */
+int seraph_b200_lora_save(cuda_train_context_t* ctx, train_state_t* state, const char* path, int version, int with_moments);
+int seraph_b200_lora_load(cuda_train_context_t* ctx, train_state_t* state, const char* path);
 /* cuda_evaluate (include/train_cuda.h:60-64 of the reference, src/train_cuda.c:2812-2846) runs one forward pass per
  * validation sample there; here it packs samples into passes of up to `tokens` tokens (default 8192, at least
  * max_seq_len, at most 256 samples; SERAPH_B200_EVAL_BATCH_TOKENS sets the default) and takes every sample's mean loss

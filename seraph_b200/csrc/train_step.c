@@ -282,6 +282,13 @@ static void free_lora(sb_ctx_t* c) {
     c->n_lora = 0; c->lora_rank = 0; c->lora_mask = 0;
 }
 
+/* the host adapters changed (a file was loaded into them): the next LoRA step uploads them again */
+void sb_lora_mark_stale(sb_ctx_t* c) {
+    if (!c || !c->LW) return;
+    cudaStreamSynchronize(S(c));
+    free_lora(c);
+}
+
 static int ensure_lora(sb_ctx_t* c, const lora_model_t* m) {
     int mask = 0;
     for (int a = 0; a < 7; a++) { lora_adapter_t** ls = lora_list(m, a); if (ls && ls[0]) mask |= 1 << a; }

@@ -328,6 +328,10 @@ void seraph_b200_state_set_qk_norm(train_state_t* st, int on);
 /* state->debug_nan_check (tools/seraph_train_cuda.c --debug-nan) and state->nan_detected */
 void seraph_b200_state_set_debug_nan(train_state_t* st, int on);
 int seraph_b200_state_nan_detected(train_state_t* st);
+/* Turns the state into what the reference's train_init builds for LoRA training (src/train.c:7900-7909): full_weights = NULL
+ * and state->model = the safetensors file at `path`, memory-mapped; the frozen base is then read from its BF16 tensors by
+ * their Hugging Face names, as ensure_cuda_lora_base_weights does (src/train_cuda.c:1376-1460).  Returns 0 on success. */
+int seraph_b200_state_attach_model_file(train_state_t* st, const char* path);
 size_t seraph_b200_state_lora_count(train_state_t* st, int rank, int mask);
 int seraph_b200_state_attach_lora(train_state_t* st, int rank, float alpha, int mask, const float* flat);
 void seraph_b200_state_lora_get(train_state_t* st, int which, float* flat);

@@ -145,6 +145,37 @@ typedef struct {
     char model_dir[512];
 } model_config_t;
 
+/* ---- the model the frozen LoRA base is read from: include/safetensors.h:25-45, include/transformer.h:15-43 -------- */
+typedef struct {
+    char* name;
+    int dtype;                           /* dtype_t: 1 F32, 2 F16, 3 BF16 */
+    int64_t* shape;
+    int n_dims;
+    int64_t offset_start, offset_end;    /* bytes from the start of the data section */
+    size_t num_elements;
+} tensor_metadata_t;
+
+typedef struct {
+    int fd;
+    uint8_t* data;                       /* the whole file, memory-mapped */
+    size_t file_size, data_offset;       /* data_offset = 8 + header length */
+    tensor_metadata_t* tensors;
+    int num_tensors;
+} safetensors_t;
+
+typedef struct { char name[256]; char orig_name[256]; int file_idx; } tensor_location_t;
+
+typedef struct {
+    safetensors_t* st[8];
+    int num_files;
+    tensor_location_t* tensor_map;
+    int num_tensors;
+    model_config_t* config;
+    void* kv_cache;
+    lora_model_t* lora;
+    void* act_cache;
+} seraph_model_t;
+
 typedef struct {
     void *model;                         /* seraph_model_t* */
     model_config_t* config;

@@ -83,6 +83,7 @@ def load():
         "seraph_b200_last_status": (i, [vp]), "seraph_b200_set_gemm_mode": (i, [vp, i]), "seraph_b200_set_gemm_pair": (i, [vp, i]), "seraph_b200_set_gemm_tail_split": (i, [vp, i]), "seraph_b200_set_parts_cache": (i, [vp, i]), "seraph_b200_set_attn_fused": (i, [vp, i]), "seraph_b200_set_attn_flash": (i, [vp, i]), "seraph_b200_qk_norm": (None, [vp, vp, vp, i, i, i, i, f]), "seraph_b200_qk_norm_backward": (None, [vp, vp, vp, vp, vp, i, i, i, i, f]), "seraph_b200_set_eval_batch_tokens": (i, [vp, i]),
         "seraph_b200_set_lora_exact": (i, [vp, i]), "seraph_b200_set_grad_clip": (i, [vp, f]),
         "seraph_b200_launch_count": (C.c_ulonglong, [vp, i]),
+        "seraph_b200_state_attach_model_file": (i, [vp, C.c_char_p]),
         "seraph_b200_lora_save": (i, [vp, vp, C.c_char_p, i, i]), "seraph_b200_lora_load": (i, [vp, vp, C.c_char_p]),
         "seraph_b200_selftest_bounded_wait": (i, [vp, C.c_longlong, vp]),
         "seraph_b200_nan_flags": (i, [vp, vp, i]), "seraph_b200_profiler_totals": (i, [vp, vp]),

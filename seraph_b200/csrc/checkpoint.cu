@@ -205,3 +205,34 @@ extern "C" int seraph_b200_load_safetensors(cuda_train_context_t* ctx, train_sta
     return rc;
 }
 
+
+// BF16 words in host memory (pageable: a memory-mapped safetensors file) widened into FP32 device memory: chunks go through
+// two pinned buffers, 2 bytes per element over the bus, the 16-bit shift of bf16_to_f32 (src/train_cuda.c:19-23) on the GPU.
+extern "C" int sb_upload_bf16(sb_ctx_t* c, const uint16_t* src, float* dst, size_t n) {
+    size_t chunk = CK_CHUNK_DEFAULT;
+    { const char* e = getenv("SERAPH_B200_CKPT_CHUNK"); if (e && atol(e) >= 1024) chunk = ((size_t)atol(e) + 3) & ~(size_t)3; }
+    if (chunk > n) chunk = (n + 3) & ~(size_t)3;
+    uint16_t* dbuf[2] = {NULL, NULL}; uint16_t* hbuf[2] = {NULL, NULL};
+    cudaEvent_t ev[2] = {NULL, NULL};
+    cudaStream_t st = (cudaStream_t)c->pub.stream;
+    int rc = SB_OK;
+    for (int i = 0; i < 2 && rc == SB_OK; i++)
+        if (cudaMalloc((void**)&dbuf[i], chunk * 2) != cudaSuccess || cudaMallocHost((void**)&hbuf[i], chunk * 2) != cudaSuccess ||
+            cudaEventCreateWithFlags(&ev[i], cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); rc = SB_ERR_OOM; }
+    const int blocks = (c->pub.gpu_sm_count > 0 ? c->pub.gpu_sm_count : 148) * 8;
+    int k = 0;
+    for (size_t o = 0; o < n && rc == SB_OK; o += chunk, k++) {
+        const size_t m = n - o < chunk ? n - o : chunk;
+        const int b = k & 1;
+        if (k >= 2 && cudaEventSynchronize(ev[b]) != cudaSuccess) { rc = SB_ERR_CUDA; break; }
+        memcpy(hbuf[b], src + o, m * 2);
+        cudaMemcpyAsync(dbuf[b], hbuf[b], m * 2, cudaMemcpyHostToDevice, st);
+        cudaEventRecord(ev[b], st);
+        unpack_bf16_kernel<<<blocks, 256, 0, st>>>(dbuf[b], dst + o, m);
+        c->launches++;
+    }
+    cudaStreamSynchronize(st);
+    if (sb_check(c, cudaGetLastError(), "BF16 weight upload")) rc = SB_ERR_CUDA;
+    for (int i = 0; i < 2; i++) { if (dbuf[i]) cudaFree(dbuf[i]); if (hbuf[i]) cudaFreeHost(hbuf[i]); if (ev[i]) cudaEventDestroy(ev[i]); }
+    return rc;
+}

@@ -10,8 +10,13 @@
  * selected by the mask (bit 0 q, 1 k, 2 v, 3 o, 4 gate, 5 up, 6 down): A [r,in]
  * then B [out,r].
  */
+#include <fcntl.h>
+#include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
 #include "sb_internal.h"
 
 typedef struct {
@@ -20,6 +25,8 @@ typedef struct {
     trainable_weights_t w;
     lora_model_t lora;
     int lora_mask;
+    seraph_model_t model;      /* a memory-mapped safetensors file as the frozen LoRA base (seraph_b200_state_attach_model_file) */
+    safetensors_t file;
 } harness_t;
 
 static int g_lean = 0;     /* weights only: no host copies of gradients and Adam moments */
@@ -80,9 +87,100 @@ train_state_t* seraph_b200_state_create_lean(int V, int d, int L, int Hq, int Hk
 
 static void f_free(weight_tensor_t* t, void* a) { (void)a; wt_free(t); }
 static void lora_free_all(harness_t* h);
+static void model_file_close(harness_t* h) {
+    if (h->file.tensors) { for (int i = 0; i < h->file.num_tensors; i++) { free(h->file.tensors[i].name); free(h->file.tensors[i].shape); } free(h->file.tensors); }
+    if (h->file.data) munmap(h->file.data, h->file.file_size);
+    if (h->file.fd > 0) close(h->file.fd);
+    free(h->model.tensor_map);
+    memset(&h->file, 0, sizeof h->file); memset(&h->model, 0, sizeof h->model);
+    h->st.model = NULL;
+}
+
+/* A state shaped like the one the reference's train_init builds for LoRA training (src/train.c:7900-7909): no FP32 host
+ * copies of the base (full_weights = NULL), state->model = the safetensors file at `path`, memory-mapped, its tensors
+ * found by their Hugging Face names.  The library then reads the frozen base as raw BF16 from that mapping.  The header
+ * is scanned for every tensor's name, shape and data_offsets; returns 0, or 1 when the file cannot be mapped or parsed. */
+static const char* skip_string(const char* p, const char* end) {      /* p at the opening quote; returns past the closing one */
+    for (p++; p < end && *p != '"'; p++) if (*p == '\\' && p + 1 < end) p++;
+    return p < end ? p + 1 : end;
+}
+static const char* find_key(const char* p, const char* end, const char* key) {   /* inside one object: value position of "key": */
+    size_t n = strlen(key);
+    while (p < end) {
+        if (*p == '"') {
+            const char* q = skip_string(p, end);
+            if ((size_t)(q - p - 2) == n && !memcmp(p + 1, key, n)) { while (q < end && (*q == ':' || *q == ' ')) q++; return q; }
+            p = q;
+        } else p++;
+    }
+    return NULL;
+}
+int seraph_b200_state_attach_model_file(train_state_t* st, const char* path) {
+    harness_t* h = (harness_t*)st;
+    if (!h || !path) return 1;
+    model_file_close(h);
+    int fd = open(path, O_RDONLY);
+    if (fd < 0) return 1;
+    struct stat sb;
+    if (fstat(fd, &sb) || sb.st_size < 16) { close(fd); return 1; }
+    uint8_t* data = (uint8_t*)mmap(NULL, (size_t)sb.st_size, PROT_READ, MAP_PRIVATE, fd, 0);
+    if (data == MAP_FAILED) { close(fd); return 1; }
+    uint64_t hlen; memcpy(&hlen, data, 8);
+    if (hlen + 8 > (uint64_t)sb.st_size) { munmap(data, (size_t)sb.st_size); close(fd); return 1; }
+    h->file.fd = fd; h->file.data = data; h->file.file_size = (size_t)sb.st_size; h->file.data_offset = 8 + (size_t)hlen;
+    const char* p = (const char*)data + 8; const char* end = p + hlen;
+    int cap = 64, n = 0;
+    tensor_metadata_t* tm = (tensor_metadata_t*)calloc((size_t)cap, sizeof *tm);
+    while (p < end && *p != '{') p++;
+    p++;
+    while (tm && p < end) {
+        while (p < end && *p != '"' && *p != '}') p++;
+        if (p >= end || *p == '}') break;
+        const char* q = skip_string(p, end);
+        size_t kl = (size_t)(q - p - 2);
+        const char* key = p + 1;
+        p = q;
+        while (p < end && *p != '{') p++;                     /* the value object: find its end with brace matching */
+        const char* ob = p; int depth = 0;
+        for (; p < end; p++) { if (*p == '"') { p = skip_string(p, end) - 1; continue; } if (*p == '{') depth++; else if (*p == '}' && --depth == 0) { p++; break; } }
+        const char* oe = p;
+        if (kl == 12 && !memcmp(key, "__metadata__", 12)) continue;
+        const char* v = find_key(ob, oe, "data_offsets");
+        if (!v) continue;
+        long long a = 0, b = 0;
+        if (sscanf(v, "[%lld,%lld]", &a, &b) != 2 && sscanf(v, "[%lld, %lld]", &a, &b) != 2) continue;
+        if (n == cap) { cap *= 2; tensor_metadata_t* t2 = (tensor_metadata_t*)realloc(tm, (size_t)cap * sizeof *tm); if (!t2) break; tm = t2; memset(tm + n, 0, (size_t)(cap - n) * sizeof *tm); }
+        tensor_metadata_t* t = &tm[n++];
+        t->name = (char*)malloc(kl + 1); memcpy(t->name, key, kl); t->name[kl] = 0;
+        t->offset_start = a; t->offset_end = b;
+        const char* d = find_key(ob, oe, "dtype");
+        t->dtype = (d && !strncmp(d, "\"BF16\"", 6)) ? 3 : (d && !strncmp(d, "\"F16\"", 5)) ? 2 : (d && !strncmp(d, "\"F32\"", 5)) ? 1 : 0;
+        t->num_elements = (size_t)(b - a) / (t->dtype == 1 ? 4 : 2);
+        const char* sh = find_key(ob, oe, "shape");
+        if (sh && *sh == '[') {
+            int64_t dims[8]; int nd = 0; const char* r = sh + 1;
+            while (r < oe && *r != ']' && nd < 8) { dims[nd++] = strtoll(r, (char**)&r, 10); while (r < oe && (*r == ',' || *r == ' ')) r++; }
+            t->n_dims = nd; t->shape = (int64_t*)malloc(sizeof(int64_t) * (size_t)(nd ? nd : 1)); memcpy(t->shape, dims, sizeof(int64_t) * (size_t)nd);
+        }
+    }
+    if (!tm || n == 0) { free(tm); model_file_close(h); return 1; }
+    h->file.tensors = tm; h->file.num_tensors = n;
+    h->model.st[0] = &h->file; h->model.num_files = 1; h->model.config = &h->cfg; h->model.num_tensors = n;
+    h->model.tensor_map = (tensor_location_t*)calloc((size_t)n, sizeof(tensor_location_t));
+    if (!h->model.tensor_map) { model_file_close(h); return 1; }
+    for (int i = 0; i < n; i++) {
+        strncpy(h->model.tensor_map[i].name, tm[i].name, 255); strncpy(h->model.tensor_map[i].orig_name, tm[i].name, 255);
+        h->model.tensor_map[i].file_idx = 0;
+    }
+    h->st.model = &h->model;
+    h->st.full_weights = NULL; h->st.use_full_training = 0;          /* the host FP32 copies stay allocated inside the harness, unused */
+    return 0;
+}
+
 void seraph_b200_state_free(train_state_t* st) {
     harness_t* h = (harness_t*)st;
     if (!h) return;
+    model_file_close(h);
     lora_free_all(h);
     visit(h, f_free, NULL);
     free(h->w.layers);

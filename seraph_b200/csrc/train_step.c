@@ -204,6 +204,47 @@ static void down_tensor(sb_ctx_t* c, weight_tensor_t* t, size_t off, void* arg) 
     }
 }
 
+/* The frozen base of a LoRA state the reference's train_init built: no FP32 host copies (full_weights is NULL in LoRA mode,
+ * src/train.c:7900-7909), the weights are the BF16 tensors of the memory-mapped model, found by name as
+ * ensure_cuda_lora_base_weights does (src/train_cuda.c:1376-1460) and read as raw BF16 whatever the file's dtype says. */
+int sb_upload_bf16(sb_ctx_t* c, const uint16_t* src, float* dst, size_t n);
+static const uint16_t* model_tensor(const seraph_model_t* m, const char* name, size_t want) {
+    for (int i = 0; i < m->num_tensors; i++) {
+        if (strcmp(m->tensor_map[i].name, name)) continue;
+        const int fi = m->tensor_map[i].file_idx;
+        if (fi < 0 || fi >= 8 || !m->st[fi]) return NULL;
+        const safetensors_t* f = m->st[fi];
+        for (int t = 0; t < f->num_tensors; t++)
+            if (f->tensors[t].name && !strcmp(f->tensors[t].name, m->tensor_map[i].orig_name)) {
+                if (f->tensors[t].num_elements != want) return NULL;
+                return (const uint16_t*)(f->data + f->data_offset + f->tensors[t].offset_start);
+            }
+        return NULL;
+    }
+    return NULL;
+}
+static int upload_base_from_model(sb_ctx_t* c, const seraph_model_t* m) {
+    static const char* per_layer[9] = {"self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj", "mlp.gate_proj",
+                                       "mlp.up_proj", "mlp.down_proj", "input_layernorm", "post_attention_layernorm"};
+    char name[320];
+    const size_t nE = (size_t)c->V * c->d;
+    const uint16_t* p = model_tensor(m, "model.embed_tokens.weight", nE);
+    if (!p || sb_upload_bf16(c, p, c->W, nE)) { fprintf(stderr, "seraph_b200: model.embed_tokens.weight missing from the model or of another size\n"); return 1; }
+    p = model_tensor(m, "model.norm.weight", (size_t)c->d);
+    if (!p || sb_upload_bf16(c, p, c->W + nE, (size_t)c->d)) { fprintf(stderr, "seraph_b200: model.norm.weight missing from the model or of another size\n"); return 1; }
+    for (int l = 0; l < c->L; l++) {
+        const sb_layer_off_t* o = &c->off[l];
+        const size_t offs[9] = {o->q, o->k, o->v, o->o, o->gate, o->up, o->down, o->in_norm, o->post_norm};
+        for (int t = 0; t < 9; t++) {
+            snprintf(name, sizeof name, "model.layers.%d.%s.weight", l, per_layer[t]);
+            const size_t n = tensor_len(c, offs[t]);
+            p = model_tensor(m, name, n);
+            if (!p || sb_upload_bf16(c, p, c->W + offs[t], n)) { fprintf(stderr, "seraph_b200: %s missing from the model or of another size\n", name); return 1; }
+        }
+    }
+    return 0;
+}
+
 /* Allocate the arenas for this geometry and upload the host master copy once
  * (the reference uploads once and afterwards only downloads, src/train_cuda.c:286-291). */
 static void free_lora(sb_ctx_t* c);
@@ -215,7 +256,7 @@ static int ensure_model(sb_ctx_t* c, const train_state_t* st, int frozen_base) {
     if (V <= 0 || d <= 0 || L <= 0 || F <= 0 || Hq <= 0 || Hkv <= 0 || hd <= 0 || Hq % Hkv) { sb_set_status(c, SB_ERR_ARG); return 1; }
     if (c->W && c->V == V && c->d == d && c->L == L && c->F == F && c->Hq == Hq && c->Hkv == Hkv && c->hd == hd &&
         c->frozen_base == frozen_base) return 0;
-    if (!st->full_weights) { sb_set_status(c, SB_ERR_ARG); return 1; }
+    if (!st->full_weights && !(frozen_base && st->model)) { sb_set_status(c, SB_ERR_ARG); return 1; }
     cudaStreamSynchronize(S(c));
     /* the activation slots, the registered operand parts and the adapter arenas were carved for the old geometry
        (the reference reallocates on a geometry change too, src/train.c:2705) */
@@ -244,7 +285,8 @@ static int ensure_model(sb_ctx_t* c, const train_state_t* st, int frozen_base) {
         sb_parts_register(c, 0, c->W + o->gate, (size_t)F * d); sb_parts_register(c, 0, c->W + o->up, (size_t)F * d);
         sb_parts_register(c, 0, c->W + o->down, (size_t)F * d);
     }
-    for_each_tensor(c, st->full_weights, up_tensor, NULL);
+    if (st->full_weights) for_each_tensor(c, st->full_weights, up_tensor, NULL);
+    else if (upload_base_from_model(c, (const seraph_model_t*)st->model)) { sb_set_status(c, SB_ERR_ARG); return 1; }
     publish_views(c);
     return sb_check(c, cudaStreamSynchronize(S(c)), "weight upload");
 }

@@ -42,6 +42,10 @@ FIELDS = {
                       "num_samples", "current_epoch", "current_step", "current_loss", "nan_detected",
                       "optimizer_step", "accumulation_counter", "gradient_accumulation_steps", "learning_rate",
                       "debug", "debug_nan_check", "metrics_count", "vap_total_tracks"],
+    "tensor_metadata_t": ["name", "dtype", "shape", "n_dims", "offset_start", "offset_end", "num_elements"],
+    "safetensors_t": ["fd", "data", "file_size", "data_offset", "tensors", "num_tensors"],
+    "tensor_location_t": ["name", "orig_name", "file_idx"],
+    "seraph_model_t": ["st", "num_files", "tensor_map", "num_tensors", "config", "kv_cache", "lora", "act_cache"],
     "profiler_op_t": ["name", "event_start", "event_end", "elapsed_ms", "grid_x", "block_z", "shared_mem", "flops", "bytes"],
     "struct cuda_profiler_t": ["enabled", "num_ops", "ops", "total_step_ms", "total_other_ms", "log_file"],
 }

@@ -353,3 +353,47 @@ def test_bounded_wait_runs_out_and_the_context_survives(ctx):
     ctx.check()
     assert abs(loss - ref["loss"]) < 1e-5 * abs(ref["loss"])
     st.close()
+
+
+def test_lora_state_without_host_weights_reads_the_bf16_model(ctx, tmp_path):
+    """The state the reference's train_init builds for LoRA training has no FP32 host copies (full_weights is NULL,
+    src/train.c:7900-7909): the frozen base comes from the BF16 tensors of the memory-mapped model, by name
+    (src/train_cuda.c:1376-1460).  Such a state steps and evaluates, its adapter gradients are bit-identical to those of a
+    state that carries the same BF16-rounded weights as FP32 host arrays, and they match the oracle."""
+    from seraph_b200 import api
+    cfg, ss = O.ModelCfg(V=1024, d=512, L=2, Hq=4, Hkv=2, hd=128, F=1024, theta=1e4), [0, 300, 512, 645]
+    rank, alpha, mask = 8, 16.0, 0b0001111
+    p = cfg.init_params(81, norm_jitter=0.1)
+    p_bf16 = (p.view(np.uint32) & np.uint32(0xFFFF0000)).view(np.float32)        # what the file will hold (truncation, src/train.c:255-260)
+    tens, n = cfg.lora_tensors(rank, mask)
+    lo = (0.02 * np.random.default_rng(82).standard_normal(n)).astype(np.float32)
+    tok = tokens_for(cfg, ss[-1], 83)
+    path = str(tmp_path / "base.safetensors")
+    ctx.lib.seraph_b200_reset_model(ctx.h)
+    st = api.TrainState(cfg, p)
+    api.step_full_batch(ctx, st, tok, ss)                                          # makes the model resident; lr is tiny, the weights move
+    st.set(0, p)
+    ctx.lib.seraph_b200_reset_model(ctx.h)
+    st2 = api.TrainState(cfg, p, lr=0.0)
+    api.step_full_batch(ctx, st2, tok, ss)                                         # lr 0 at step 1 of the warm-up: weights stay p
+    assert ctx.lib.seraph_b200_save_safetensors(ctx.h, st2.h, path.encode()) == 0
+    st.close(); st2.close()
+    grads = []
+    for from_file in (False, True):
+        ctx.lib.seraph_b200_reset_model(ctx.h)
+        s = api.TrainState(cfg, p_bf16)
+        s.attach_lora(rank, alpha, mask, lo)
+        if from_file:
+            assert ctx.lib.seraph_b200_state_attach_model_file(s.h, path.encode()) == 0
+        loss = api.step_lora_batch(ctx, s, tok, ss)
+        ctx.check()
+        assert loss > 0
+        ev = ctx.lib.cuda_eval_forward(s.h, tok.ctypes.data, 300, ctx.h)
+        assert ev > 0
+        ctx.lib.cuda_download_lora_weights(ctx.h, s.lora_ptr())
+        grads.append((loss, s.lora_get(1)))
+        s.close()
+    assert grads[0][0] == grads[1][0] and np.array_equal(grads[0][1], grads[1][1])
+    ref = O.train_step(cfg, p_bf16, tok, ss, lora=lo, rank=rank, alpha=alpha, mask=mask)
+    assert abs(grads[1][0] - ref["loss"]) < 1e-5 * abs(ref["loss"])
+    worst_tensor(tens, grads[1][1], ref["grads"])

@@ -199,6 +199,17 @@ int seraph_b200_load_safetensors(cuda_train_context_t* ctx, train_state_t* state
  * safetensors file as above plus "<path>.state" (current_epoch, current_step, current_loss, optimizer_step).
  * SB_ERR_ARG for a LoRA state (those go through cuda_download_lora_weights and the reference's lora_save). */
 int seraph_b200_save_checkpoint(cuda_train_context_t* ctx, train_state_t* state, const char* path);
+/* Model options beyond the reference's training step (its trainable_weights_t has no tensors for them, include/train.h:75-90),
+ * so that Qwen3- and Mistral-shaped models run as their configurations state them:
+ *   per_head_qk_norm  q and k pass through a learned RMSNorm over each head before RoPE (scales q_norm [hd], k_norm [hd] per layer);
+ *   untied_lm_head    logits come from a separate lm_head [V,d] instead of the embedding matrix.
+ * `flat` holds the parameters (per layer q_norm then k_norm; then lm_head), n their count; both options off takes NULL, 0.
+ * The call drops the resident model; the next step uploads everything again.  Full-weight steps train the extra parameters
+ * with the same AdamW (and reduce their gradients across data-parallel ranks); LoRA steps keep them frozen.  They are not part
+ * of the reference's checkpoint formats: read them with seraph_b200_get_model_extras (which: 0 parameters, 1 gradients,
+ * 2 Adam m, 3 Adam v).  Distinct from config->use_qk_norm, the reference's unweighted whole-row form. */
+int seraph_b200_set_model_extras(cuda_train_context_t* ctx, int per_head_qk_norm, int untied_lm_head, const float* flat, size_t n);
+int seraph_b200_get_model_extras(cuda_train_context_t* ctx, int which, float* out, size_t n);
 /* LoRA adapter files.  version 2 is the reference's format, byte for byte (lora_save, src/lora.c:441-494): the Q and V
  * adapters only, which is all that format holds.  version 3 is an extension that keeps every adapter the model trains
  * (k, o, gate, up, down too, which the reference trains and then drops on save) and, with with_moments != 0, the Adam

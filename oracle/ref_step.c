@@ -43,7 +43,15 @@ void ref_embedding_backward(const uint32_t*, const float*, float*, int, int);
 void ref_lora_backward(const float*, const float*, const float*, const float*, float*, float*, float*, int, int, int, int, float);
 void ref_lora_forward_add(const float*, float*, const float*, const float*, float*, int, int, int, int, float);
 
-typedef struct { int V, d, L, Hq, Hkv, hd, F; float eps, theta; int qk_norm; } ref_cfg_t;
+/* head_norm: learned RMSNorm over each head of q and k before RoPE (weights q_norm [hd], k_norm [hd] per layer);
+ * untied: a separate lm_head [V,d] instead of the embedding matrix.  Neither exists in the reference's training step
+ * (trainable_weights_t has no such tensors, include/train.h:75-90): they are options of the new library, and their
+ * parameters travel in a second flat array ("extras": per layer q_norm, k_norm; then lm_head). */
+typedef struct { int V, d, L, Hq, Hkv, hd, F; float eps, theta; int qk_norm, head_norm, untied; } ref_cfg_t;
+
+size_t ref_extras_count(const ref_cfg_t* c) {
+    return (c->head_norm ? (size_t)c->L * 2 * c->hd : 0) + (c->untied ? (size_t)c->V * c->d : 0);
+}
 
 typedef struct { size_t q, k, v, o, gate, up, down, in_norm, post_norm; } layer_off_t;
 
@@ -113,7 +121,7 @@ static float* fbuf(size_t n) { return (float*)calloc(n ? n : 1, sizeof(float)); 
 float ref_train_step(const ref_cfg_t* c, const float* P, float* G,
                      const float* lora, float* lora_grads, int rank, float alpha, int mask, int lora_exact,
                      const int* tokens, int T, const int* seq_starts, int B,
-                     float* logits_out, float* dhidden0_out) {
+                     float* logits_out, float* dhidden0_out, const float* X, float* GX) {
     const int d = c->d, F = c->F, V = c->V, L = c->L, Hq = c->Hq, Hkv = c->Hkv, hd = c->hd;
     const int qd = Hq * hd, kvd = Hkv * hd;
     const float eps = c->eps, theta = c->theta > 0 ? c->theta : 10000.0f;
@@ -145,6 +153,9 @@ float ref_train_step(const ref_cfg_t* c, const float* P, float* G,
           **c_pa = malloc(sizeof(float*) * L), **c_xf = malloc(sizeof(float*) * L), **c_g = malloc(sizeof(float*) * L),
           **c_u = malloc(sizeof(float*) * L), **c_s = malloc(sizeof(float*) * L), **c_fh = malloc(sizeof(float*) * L);
     float **c_qr = calloc((size_t)L, sizeof(float*)), **c_kr = calloc((size_t)L, sizeof(float*));      /* row statistics of qk_norm */
+    float **c_qp = calloc((size_t)L, sizeof(float*)), **c_kp = calloc((size_t)L, sizeof(float*));      /* q, k before the per-head norm */
+    const float* Wlm = (c->untied && X) ? X + (c->head_norm ? (size_t)L * 2 * hd : 0) : NULL;
+    float* GWlm = (c->untied && GX) ? GX + (c->head_norm ? (size_t)L * 2 * hd : 0) : NULL;
     float* hidden = fbuf(Td); float* tmp = fbuf(Td); float* ltmp = fbuf((size_t)T * (rank > 0 ? rank : 1));
 
 #define LA(l, a) (lora + lora_off(c, rank, mask, l, a))
@@ -165,6 +176,12 @@ float ref_train_step(const ref_cfg_t* c, const float* P, float* G,
         if (HAS(1)) ref_lora_forward_add(c_xa[l], c_k[l], LA(l, 1), LB(l, 1, d), ltmp, T, d, kvd, rank, ls);
         ref_matmul(c_xa[l], P + o->v, c_v[l], T, kvd, d, 0, 1, 0);
         if (HAS(2)) ref_lora_forward_add(c_xa[l], c_v[l], LA(l, 2), LB(l, 2, d), ltmp, T, d, kvd, rank, ls);
+        if (c->head_norm && X) {    /* every head of q and k normalised with a learned scale, before RoPE */
+            c_qp[l] = fbuf(Tq); memcpy(c_qp[l], c_q[l], Tq * 4);
+            c_kp[l] = fbuf(Tkv); memcpy(c_kp[l], c_k[l], Tkv * 4);
+            ref_rmsnorm(c_qp[l], X + (size_t)l * 2 * hd, c_q[l], T * Hq, hd, eps);
+            ref_rmsnorm(c_kp[l], X + (size_t)l * 2 * hd + hd, c_k[l], T * Hkv, hd, eps);
+        }
         ref_rope(c_q[l], c_q[l], ss, T, B, Hq, hd, theta, 0);
         ref_rope(c_k[l], c_k[l], ss, T, B, Hkv, hd, theta, 0);
         if (c->qk_norm) {       /* shaders/qk_norm.comp after RoPE (src/train.c:4688-4689) */
@@ -193,7 +210,7 @@ float ref_train_step(const ref_cfg_t* c, const float* P, float* G,
     float* final_in = fbuf(Td); memcpy(final_in, hidden, Td * 4);
     float* hn = fbuf(Td); ref_rmsnorm(hidden, wfin, hn, T, d, eps);
     float* logits = fbuf((size_t)T * V);
-    ref_matmul(hn, E, logits, T, V, d, 0, 1, 0);   /* tied LM head, src/train_cuda.c:2156 */
+    ref_matmul(hn, Wlm ? Wlm : E, logits, T, V, d, 0, 1, 0);   /* tied LM head, src/train_cuda.c:2156 (or the separate lm_head) */
     if (logits_out) memcpy(logits_out, logits, (size_t)T * V * 4);
 
     float* dlog = fbuf((size_t)T * V); float* loss_rows = fbuf(T);
@@ -206,8 +223,8 @@ float ref_train_step(const ref_cfg_t* c, const float* P, float* G,
     float* scratch_norm = fbuf(d);
     int full = (lora == NULL);
 
-    ref_matmul(dlog, E, gh, T, d, V, 0, 0, 0);
-    if (full) ref_matmul(dlog, hn, G, V, d, T, 1, 0, 1);
+    ref_matmul(dlog, Wlm ? Wlm : E, gh, T, d, V, 0, 0, 0);
+    if (full) ref_matmul(dlog, hn, (Wlm && GWlm) ? GWlm : G, V, d, T, 1, 0, 1);
     ref_rmsnorm_backward(final_in, wfin, gh, gt, full ? G + (size_t)V * d : scratch_norm, T, d, eps);
     memcpy(gh, gt, Td * 4);
 
@@ -248,6 +265,13 @@ float ref_train_step(const ref_cfg_t* c, const float* P, float* G,
         }
         ref_rope(gq, gq, ss, T, B, Hq, hd, theta, 1);
         ref_rope(gk, gk, ss, T, B, Hkv, hd, theta, 1);
+        if (c->head_norm && X) {
+            float* t1 = fbuf(Tq); float* t2 = fbuf(Tkv); float* sink = fbuf((size_t)hd);
+            ref_rmsnorm_backward(c_qp[l], X + (size_t)l * 2 * hd, gq, t1, (full && GX) ? GX + (size_t)l * 2 * hd : sink, T * Hq, hd, eps);
+            ref_rmsnorm_backward(c_kp[l], X + (size_t)l * 2 * hd + hd, gk, t2, (full && GX) ? GX + (size_t)l * 2 * hd + hd : sink, T * Hkv, hd, eps);
+            memcpy(gq, t1, Tq * 4); memcpy(gk, t2, Tkv * 4);
+            free(t1); free(t2); free(sink);
+        }
         if (full) {
             ref_matmul(gq, c_xa[l], G + o->q, qd, d, T, 1, 0, 1);
             ref_matmul(gk, c_xa[l], G + o->k, kvd, d, T, 1, 0, 1);
@@ -270,9 +294,9 @@ float ref_train_step(const ref_cfg_t* c, const float* P, float* G,
     for (int l = 0; l < L; l++) {
         free(c_in[l]); free(c_xa[l]); free(c_q[l]); free(c_k[l]); free(c_v[l]); free(c_att[l]);
         free(c_pa[l]); free(c_xf[l]); free(c_g[l]); free(c_u[l]); free(c_s[l]); free(c_fh[l]);
-        free(c_qr[l]); free(c_kr[l]);
+        free(c_qr[l]); free(c_kr[l]); free(c_qp[l]); free(c_kp[l]);
     }
-    free(c_qr); free(c_kr);
+    free(c_qr); free(c_kr); free(c_qp); free(c_kp);
     free(c_in); free(c_xa); free(c_q); free(c_k); free(c_v); free(c_att); free(c_pa); free(c_xf);
     free(c_g); free(c_u); free(c_s); free(c_fh);
     free(hidden); free(tmp); free(ltmp); free(final_in); free(hn); free(logits); free(dlog); free(loss_rows);

@@ -84,6 +84,7 @@ def load():
         "seraph_b200_set_lora_exact": (i, [vp, i]), "seraph_b200_set_grad_clip": (i, [vp, f]),
         "seraph_b200_launch_count": (C.c_ulonglong, [vp, i]),
         "seraph_b200_state_attach_model_file": (i, [vp, C.c_char_p]),
+        "seraph_b200_set_model_extras": (i, [vp, i, i, vp, sz]), "seraph_b200_get_model_extras": (i, [vp, i, vp, sz]),
         "seraph_b200_lora_save": (i, [vp, vp, C.c_char_p, i, i]), "seraph_b200_lora_load": (i, [vp, vp, C.c_char_p]),
         "seraph_b200_selftest_bounded_wait": (i, [vp, C.c_longlong, vp]),
         "seraph_b200_nan_flags": (i, [vp, vp, i]), "seraph_b200_profiler_totals": (i, [vp, vp]),

@@ -10,7 +10,8 @@ import numpy as np
 
 class RefCfg(C.Structure):
     _fields_ = [("V", C.c_int), ("d", C.c_int), ("L", C.c_int), ("Hq", C.c_int), ("Hkv", C.c_int),
-                ("hd", C.c_int), ("F", C.c_int), ("eps", C.c_float), ("theta", C.c_float), ("qk_norm", C.c_int)]
+                ("hd", C.c_int), ("F", C.c_int), ("eps", C.c_float), ("theta", C.c_float), ("qk_norm", C.c_int),
+                ("head_norm", C.c_int), ("untied", C.c_int)]
 
 
 @dataclass
@@ -25,6 +26,8 @@ class ModelCfg:
     theta: float = 10000.0
     eps: float = 1e-5
     qk_norm: int = 0          # whole-row normalisation of q and k after RoPE (config->use_qk_norm)
+    head_norm: int = 0        # learned RMSNorm over each head of q and k before RoPE (an option of this library, not of the reference)
+    untied: int = 0           # separate lm_head [V, d] instead of the embedding matrix (likewise)
 
     @property
     def qd(self):
@@ -35,7 +38,29 @@ class ModelCfg:
         return self.Hkv * self.hd
 
     def c(self):
-        return RefCfg(self.V, self.d, self.L, self.Hq, self.Hkv, self.hd, self.F, self.eps, self.theta, self.qk_norm)
+        return RefCfg(self.V, self.d, self.L, self.Hq, self.Hkv, self.hd, self.F, self.eps, self.theta, self.qk_norm,
+                      self.head_norm, self.untied)
+
+    def extras_tensors(self):
+        """(name, shape, offset) of the parameters that are not in the reference's trainable_weights_t, in their flat order:
+        per layer q_norm [hd], k_norm [hd] (head_norm), then lm_head [V, d] (untied)."""
+        out, off = [], 0
+        if self.head_norm:
+            for l in range(self.L):
+                for nm in ("q_norm", "k_norm"):
+                    out.append((f"l{l}.{nm}", (self.hd,), off)); off += self.hd
+        if self.untied:
+            out.append(("lm_head", (self.V, self.d), off)); off += self.V * self.d
+        return out, off
+
+    def init_extras(self, seed, std=0.02, norm_jitter=0.1):
+        tens, n = self.extras_tensors()
+        rng = np.random.default_rng(seed)
+        x = np.empty(n, np.float32)
+        for name, shp, off in tens:
+            k = int(np.prod(shp))
+            x[off:off + k] = (1.0 + norm_jitter * rng.standard_normal(k)) if name.endswith("norm") else std * rng.standard_normal(k)
+        return x
 
     def layer_shapes(self):
         d, F, qd, kvd = self.d, self.F, self.qd, self.kvd

@@ -48,6 +48,7 @@ typedef struct { size_t q, k, v, o, gate, up, down, in_norm, post_norm; } sb_lay
 typedef struct {
     float *layer_in, *x_norm_attn, *q, *k, *v, *attn_out, *lse, *post_attn_in, *x_norm_ffn, *gate, *up, *ffn_hidden;
     float *q_rms, *k_rms;            /* per-token sqrt(mean(x^2)) of q and k before their whole-row normalisation (use_qk_norm) */
+    float *q_pre, *k_pre;            /* q and k before the learned per-head RMSNorm (head_norm), kept for its backward */
 } sb_layer_act_t;
 
 typedef struct { const float* ptr; size_t n, cur, off; unsigned gen; int kind; float* amax_ptr; } sb_parts_entry_t;   /* n: registered floats, cur: floats of the parts held */
@@ -95,6 +96,13 @@ typedef struct sb_ctx {
     float *W, *G, *M, *Vv;           /* parameter, gradient, Adam m, Adam v arenas (flat order) */
     int qk_norm;                     /* config->use_qk_norm of the step in flight */
     int frozen_base;                 /* 1: LoRA mode, G/M/Vv not allocated */
+    /* model options the reference's trainable_weights_t has no tensors for (seraph_b200_set_model_extras): a learned RMSNorm over
+       each head of q and k before RoPE (per layer q_norm [hd], k_norm [hd]) and a separate lm_head [V,d].  Flat order: the norms of
+       layer 0, 1, ..., then lm_head.  h_extras is the host master copy (uploaded when the model becomes resident). */
+    int head_norm, untied;
+    float* h_extras; size_t n_extras_host;
+    float *XW, *XG, *XM, *XV; size_t n_extras;
+    float *g_q2, *g_k2;              /* gradients of q, k before the per-head norm */
 
     /* LoRA adapters: one arena per kind, same flat order as the oracle */
     int lora_rank, lora_mask; float lora_alpha;

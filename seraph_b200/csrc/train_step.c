@@ -98,6 +98,11 @@ static void free_model(sb_ctx_t* c) {
     if (c->M) cudaFree(c->M);
     if (c->Vv) cudaFree(c->Vv);
     c->W = c->G = c->M = c->Vv = NULL;
+    if (c->XW) cudaFree(c->XW);
+    if (c->XG) cudaFree(c->XG);
+    if (c->XM) cudaFree(c->XM);
+    if (c->XV) cudaFree(c->XV);
+    c->XW = c->XG = c->XM = c->XV = NULL; c->n_extras = 0;
     free(c->off); c->off = NULL;
 #define FREE1(f) do { free(p->f); p->f = NULL; } while (0)
 #define FREEL(f) do { free_view_array(p->f, L); p->f = NULL; } while (0)
@@ -291,6 +296,64 @@ static int ensure_model(sb_ctx_t* c, const train_state_t* st, int frozen_base) {
     return sb_check(c, cudaStreamSynchronize(S(c)), "weight upload");
 }
 
+/* Parameters of the model options (per-head q/k norm scales, separate lm_head): resident beside the arenas, uploaded from the
+ * host copy seraph_b200_set_model_extras left; gradients and Adam moments only in full-weight mode. */
+static size_t extras_lm_off(const sb_ctx_t* c) { return c->head_norm ? (size_t)c->L * 2 * c->hd : 0; }
+static int ensure_extras(sb_ctx_t* c, int full) {
+    const size_t n = extras_lm_off(c) + (c->untied ? (size_t)c->V * c->d : 0);
+    if (n == 0) return 0;
+    if (!c->XW) {
+        if (!c->h_extras || c->n_extras_host != n) {
+            fprintf(stderr, "seraph_b200: the model options need %zu extra parameters, seraph_b200_set_model_extras gave %zu\n", n, c->n_extras_host);
+            sb_set_status(c, SB_ERR_ARG); return 1;
+        }
+        if (sb_check(c, cudaMalloc((void**)&c->XW, n * 4), "extra parameters")) { c->status = SB_ERR_OOM; return 1; }
+        c->n_extras = n;
+        cudaMemcpyAsync(c->XW, c->h_extras, n * 4, cudaMemcpyHostToDevice, S(c));
+        if (c->untied) sb_parts_register(c, 0, c->XW + extras_lm_off(c), (size_t)c->V * c->d);
+        if (sb_check(c, cudaStreamSynchronize(S(c)), "extra parameter upload")) return 1;
+    }
+    if (full && !c->XG) {
+        if (sb_check(c, cudaMalloc((void**)&c->XG, n * 4), "extra gradients") || sb_check(c, cudaMalloc((void**)&c->XM, n * 4), "extra Adam m") ||
+            sb_check(c, cudaMalloc((void**)&c->XV, n * 4), "extra Adam v")) { c->status = SB_ERR_OOM; return 1; }
+        cudaMemsetAsync(c->XG, 0, n * 4, S(c)); cudaMemsetAsync(c->XM, 0, n * 4, S(c)); cudaMemsetAsync(c->XV, 0, n * 4, S(c));
+    }
+    return 0;
+}
+
+/* Model options beyond the reference's training step (its trainable_weights_t has no tensors for them, include/train.h:75-90):
+ * per_head_qk_norm: q and k pass through a learned RMSNorm over each head before RoPE (scales q_norm [hd], k_norm [hd] per layer);
+ * untied_lm_head: logits come from a separate lm_head [V,d] instead of the embedding matrix.  `flat` holds the parameters
+ * (per layer q_norm then k_norm; then lm_head), n their count; both options off takes flat = NULL.  Takes effect at the next
+ * step, which uploads them; in full-weight mode they are trained by the same AdamW, in LoRA mode they are frozen. */
+int seraph_b200_set_model_extras(cuda_train_context_t* ctx, int per_head_qk_norm, int untied_lm_head, const float* flat, size_t n) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c || ((per_head_qk_norm || untied_lm_head) && (!flat || !n))) return SB_ERR_ARG;
+    cudaStreamSynchronize(S(c));
+    if (c->XW) { sb_parts_unregister(c, 0); }          /* weight parts are registered again with the model */
+    free_activations(c); free_lora(c); free_model(c);
+    free(c->h_extras); c->h_extras = NULL; c->n_extras_host = 0;
+    c->head_norm = per_head_qk_norm ? 1 : 0; c->untied = untied_lm_head ? 1 : 0;
+    if (c->head_norm || c->untied) {
+        c->h_extras = (float*)malloc(n * 4);
+        if (!c->h_extras) { c->head_norm = c->untied = 0; return SB_ERR_OOM; }
+        memcpy(c->h_extras, flat, n * 4); c->n_extras_host = n;
+    }
+    return SB_OK;
+}
+/* which: 0 parameters, 1 gradients, 2 Adam m, 3 Adam v of the extra parameters, copied to out[n]; reading the parameters also
+ * refreshes the host copy, so that a later seraph_b200_reset_model continues from the trained values. */
+int seraph_b200_get_model_extras(cuda_train_context_t* ctx, int which, float* out, size_t n) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c || !out || which < 0 || which > 3) return SB_ERR_ARG;
+    const float* src = which == 0 ? c->XW : which == 1 ? c->XG : which == 2 ? c->XM : c->XV;
+    if (!src || n != c->n_extras) return SB_ERR_ARG;
+    cudaMemcpyAsync(out, src, n * 4, cudaMemcpyDeviceToHost, S(c));
+    if (sb_check(c, cudaStreamSynchronize(S(c)), "extra parameter download")) return SB_ERR_CUDA;
+    if (which == 0 && c->h_extras && c->n_extras_host == n) memcpy(c->h_extras, out, n * 4);
+    return SB_OK;
+}
+
 /* ------------------------------------------------------------------------ */
 /* LoRA adapters                                                             */
 /* ------------------------------------------------------------------------ */
@@ -397,8 +460,9 @@ static int ensure_activations(sb_ctx_t* c, int T, int need_logits_grad) {
     size_t Td = r4((size_t)T * c->d), TF = r4((size_t)T * c->F), Tq = r4((size_t)T * c->qd), Tkv = r4((size_t)T * c->kvd);
     size_t TH = r4((size_t)T * c->Hq), TV = r4((size_t)T * c->V);
     size_t per_layer = 4 * Td + 2 * Tq + 2 * Tkv + TH + 3 * TF + 2 * r4((size_t)T);    /* layer_in x_norm_attn post_attn_in x_norm_ffn | q attn_out | k v | lse | gate up ffn_hidden */
+    if (c->head_norm) per_layer += Tq + Tkv;                                          /* q_pre k_pre */
     size_t shared = 3 * Td /* hidden_norm final_in (+1 spare) */ + 2 * TV + r4((size_t)T)
-                  + 3 * Td /* g_hidden g_tmp g_xnorm */ + 2 * Tq + 2 * Tkv + 3 * TF;
+                  + 3 * Td /* g_hidden g_tmp g_xnorm */ + 2 * Tq + 2 * Tkv + 3 * TF + (c->head_norm ? Tq + Tkv : 0);
     (void)need_logits_grad;
     size_t total = per_layer * (size_t)c->L + shared;
     if (sb_check(c, cudaMalloc((void**)&c->act_arena, total * sizeof(float)), "activation arena")) { c->status = SB_ERR_OOM; return 1; }
@@ -412,12 +476,14 @@ static int ensure_activations(sb_ctx_t* c, int T, int need_logits_grad) {
         TAKE(a->layer_in, Td); TAKE(a->x_norm_attn, Td); TAKE(a->post_attn_in, Td); TAKE(a->x_norm_ffn, Td);
         TAKE(a->q, Tq); TAKE(a->attn_out, Tq); TAKE(a->k, Tkv); TAKE(a->v, Tkv); TAKE(a->lse, TH); TAKE(a->q_rms, r4((size_t)T)); TAKE(a->k_rms, r4((size_t)T));
         TAKE(a->gate, TF); TAKE(a->up, TF); TAKE(a->ffn_hidden, TF);
+        if (c->head_norm) { TAKE(a->q_pre, Tq); TAKE(a->k_pre, Tkv); }
     }
     TAKE(c->hidden_norm, Td); TAKE(c->final_in, Td); TAKE(c->hidden, Td);
     TAKE(c->logits, TV); TAKE(c->dlogits, TV); TAKE(c->loss_rows, r4((size_t)T));
     TAKE(c->g_hidden, Td); TAKE(c->g_tmp, Td); TAKE(c->g_xnorm, Td);
     TAKE(c->g_q, Tq); TAKE(c->g_attn, Tq); TAKE(c->g_k, Tkv); TAKE(c->g_v, Tkv);
     TAKE(c->g_ffn, TF); TAKE(c->g_gate, TF); TAKE(c->g_up, TF);
+    if (c->head_norm) { TAKE(c->g_q2, Tq); TAKE(c->g_k2, Tkv); }
 #undef TAKE
     /* operands of more than one product per step, written once by the forward pass */
     for (int l = 0; l < c->L; l++) {
@@ -545,10 +611,15 @@ static void forward_pass(sb_ctx_t* c, int T, int max_seq, float theta, int use_l
         sb_rmsnorm(c, a->layer_in, c->W + o->in_norm, a->x_norm_attn, T, d, RMS_EPS);
         /* runs of products that share an operand keep its prepared parts (not with adapters: their scratch is rewritten in between) */
         if (!use_lora) sb_gemm_keep_begin(c);
-        linear_fwd(c, use_lora, l, 0, a->x_norm_attn, c->W + o->q, a->q, T, d, qd, 0);
-        linear_fwd(c, use_lora, l, 1, a->x_norm_attn, c->W + o->k, a->k, T, d, kvd, 0);
+        linear_fwd(c, use_lora, l, 0, a->x_norm_attn, c->W + o->q, c->head_norm ? a->q_pre : a->q, T, d, qd, 0);
+        linear_fwd(c, use_lora, l, 1, a->x_norm_attn, c->W + o->k, c->head_norm ? a->k_pre : a->k, T, d, kvd, 0);
         linear_fwd(c, use_lora, l, 2, a->x_norm_attn, c->W + o->v, a->v, T, d, kvd, 0);
         sb_gemm_keep_end(c);
+        if (c->head_norm) {       /* learned RMSNorm over each head (rows of head_dim), before RoPE */
+            const float* wn = c->XW + (size_t)l * 2 * c->hd;
+            sb_rmsnorm(c, a->q_pre, wn, a->q, T * c->Hq, c->hd, RMS_EPS);
+            sb_rmsnorm(c, a->k_pre, wn + c->hd, a->k, T * c->Hkv, c->hd, RMS_EPS);
+        }
         if (!c->qk_norm) { sb_amax_announce(c, a->q, (size_t)T * qd); sb_amax_announce(c, a->k, (size_t)T * kvd); }
         sb_rope2(c, a->q, a->k, c->pos_ids, T, c->Hq, c->Hkv, c->hd, theta, max_seq, 0);
         if (c->qk_norm) {
@@ -575,7 +646,7 @@ static void forward_pass(sb_ctx_t* c, int T, int max_seq, float theta, int use_l
     sb_amax_announce(c, c->hidden_norm, Td);
     sb_rmsnorm(c, c->final_in, c->W + (size_t)c->V * d, c->hidden_norm, T, d, RMS_EPS);
     nan_mark(c, c->hidden_norm, Td, 2); nan_mark(c, c->final_in, Td, 6);
-    sb_gemm(c, c->hidden_norm, c->W, c->logits, T, c->V, d, 0, 1, 0);       /* tied LM head */
+    sb_gemm(c, c->hidden_norm, c->untied ? c->XW + extras_lm_off(c) : c->W, c->logits, T, c->V, d, 0, 1, 0);       /* tied LM head, or the separate one */
     nan_mark(c, c->logits, (size_t)T * c->V, 1);
 }
 
@@ -587,8 +658,8 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
     float* norm_sink = c->g_tmp;                 /* LoRA mode: norm-scale gradients are discarded */
     if (!full) sb_memset(c, norm_sink, 0, (size_t)d * sizeof(float));
     if (full) sb_gemm_keep_begin(c);
-    sb_gemm(c, c->dlogits, c->W, gx, T, d, V, 0, 0, 0);
-    if (full) sb_gemm(c, c->dlogits, c->hidden_norm, Gd, V, d, T, 1, 0, 1);
+    sb_gemm(c, c->dlogits, c->untied ? c->XW + extras_lm_off(c) : c->W, gx, T, d, V, 0, 0, 0);
+    if (full) sb_gemm(c, c->dlogits, c->hidden_norm, c->untied ? c->XG + extras_lm_off(c) : Gd, V, d, T, 1, 0, 1);
     sb_gemm_keep_end(c);
     nan_mark(c, c->dlogits, (size_t)T * V, 3); nan_mark(c, gx, (size_t)T * d, 4);
     sb_amax_announce(c, gh, (size_t)T * d);
@@ -636,17 +707,25 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
             const uint32_t nb = nan_bwd_base(c) + 5u * (uint32_t)l;
             nan_mark(c, c->g_q, (size_t)T * qd, nb + 1); nan_mark(c, c->g_k, (size_t)T * kvd, nb + 2); nan_mark(c, c->g_v, (size_t)T * kvd, nb + 3);
         }
+        float* gq = c->g_q; float* gk = c->g_k;
+        if (c->head_norm) {
+            const size_t xo = (size_t)l * 2 * c->hd;
+            sb_amax_announce(c, c->g_q2, (size_t)T * qd); sb_amax_announce(c, c->g_k2, (size_t)T * kvd);
+            sb_rmsnorm_backward(c, a->q_pre, c->XW + xo, c->g_q, NULL, c->g_q2, full ? c->XG + xo : norm_sink, T * c->Hq, c->hd, RMS_EPS);
+            sb_rmsnorm_backward(c, a->k_pre, c->XW + xo + c->hd, c->g_k, NULL, c->g_k2, full ? c->XG + xo + c->hd : norm_sink, T * c->Hkv, c->hd, RMS_EPS);
+            gq = c->g_q2; gk = c->g_k2;
+        }
         if (full) {
             sb_gemm_keep_begin(c);
-            sb_gemm(c, c->g_q, a->x_norm_attn, Gd + o->q, qd, d, T, 1, 0, 1);
-            sb_gemm(c, c->g_k, a->x_norm_attn, Gd + o->k, kvd, d, T, 1, 0, 1);
+            sb_gemm(c, gq, a->x_norm_attn, Gd + o->q, qd, d, T, 1, 0, 1);
+            sb_gemm(c, gk, a->x_norm_attn, Gd + o->k, kvd, d, T, 1, 0, 1);
             sb_gemm(c, c->g_v, a->x_norm_attn, Gd + o->v, kvd, d, T, 1, 0, 1);
         }
-        sb_gemm(c, c->g_q, c->W + o->q, gx, T, d, qd, 0, 0, 0);
-        sb_gemm(c, c->g_k, c->W + o->k, gx, T, d, kvd, 0, 0, 1);
+        sb_gemm(c, gq, c->W + o->q, gx, T, d, qd, 0, 0, 0);
+        sb_gemm(c, gk, c->W + o->k, gx, T, d, kvd, 0, 0, 1);
         sb_gemm(c, c->g_v, c->W + o->v, gx, T, d, kvd, 0, 0, 1);
         sb_gemm_keep_end(c);
-        if (!full) { lora_bwd(c, l, 0, c->g_q, a->x_norm_attn, gx, T); lora_bwd(c, l, 1, c->g_k, a->x_norm_attn, gx, T); lora_bwd(c, l, 2, c->g_v, a->x_norm_attn, gx, T); }
+        if (!full) { lora_bwd(c, l, 0, gq, a->x_norm_attn, gx, T); lora_bwd(c, l, 1, gk, a->x_norm_attn, gx, T); lora_bwd(c, l, 2, c->g_v, a->x_norm_attn, gx, T); }
         sb_amax_announce(c, gh, (size_t)T * d);
         sb_rmsnorm_backward(c, a->layer_in, c->W + o->in_norm, gx, gh, gh, full ? Gd + o->in_norm : norm_sink, T, d, RMS_EPS);
         nan_mark(c, gh, (size_t)T * d, nan_ghid_base(c) + (uint32_t)l);
@@ -660,6 +739,7 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
         sb_embedding_backward(c, c->tokens, gh, Gd, T, d, V);
         nan_mark(c, Gd, (size_t)V * d, 9);
         if (reduce) sb_dp_bucket_ready(c, Gd, c->off[0].q);      /* embedding (LM head + scatter) and final norm */
+        if (reduce && c->XG) sb_dp_bucket_ready(c, c->XG, c->n_extras);
     }
 }
 
@@ -711,6 +791,7 @@ static float step_body(train_state_t* st, int* tokens, int T, int* seq_starts, i
     c->qk_norm = st->config->use_qk_norm ? 1 : 0;
     if (ensure_model(c, st, full ? 0 : (use_lora ? 1 : c->frozen_base))) return -1.0f;
     if (use_lora && ensure_lora(c, st->lora)) return -1.0f;
+    if (ensure_extras(c, full && train)) return -1.0f;
     if (ensure_activations(c, T, train)) return -1.0f;
     if (use_lora && c->lora_tmp_cap < (size_t)T * c->lora_rank) {
         cudaStreamSynchronize(S(c));
@@ -735,6 +816,7 @@ static float step_body(train_state_t* st, int* tokens, int T, int* seq_starts, i
     if (train && st->accumulation_counter == 0) {
         if (full) sb_memset(c, c->G, 0, c->n_params * sizeof(float));
         else sb_memset(c, c->LG, 0, c->n_lora * sizeof(float));
+        if (full && c->XG) sb_memset(c, c->XG, 0, c->n_extras * sizeof(float));
     }
     forward_pass(c, T, max_seq, theta, use_lora);
     if (train) sb_amax_announce(c, c->dlogits, (size_t)T * c->V);
@@ -769,8 +851,13 @@ static float step_body(train_state_t* st, int* tokens, int T, int* seq_starts, i
                 gscale = 1.0f / (float)c->dp_world;
             }
             const float* sumsq = NULL;
-            if (c->grad_clip > 0.f) { sb_sumsq(c, g, n, c->d_gnorm); sumsq = c->d_gnorm; }
+            const int extras = full && c->XG != NULL;
+            if (c->grad_clip > 0.f) {
+                sb_sumsq(c, g, n, c->d_gnorm); sumsq = c->d_gnorm;
+                if (extras) { sb_sumsq(c, c->XG, c->n_extras, c->d_gnorm + 1); sb_add(c, c->d_gnorm, c->d_gnorm + 1, c->d_gnorm, 1); }   /* one norm over all trained parameters */
+            }
             sb_adamw(c, w, g, m, v, n, lr, 0.9f, 0.999f, 0.01f, 1e-8f, st->optimizer_step, gscale, sumsq, c->grad_clip);
+            if (extras) sb_adamw(c, c->XW, c->XG, c->XM, c->XV, c->n_extras, lr, 0.9f, 0.999f, 0.01f, 1e-8f, st->optimizer_step, gscale, sumsq, c->grad_clip);
             st->accumulation_counter = 0;
         }
     }
@@ -1013,6 +1100,7 @@ void cuda_train_free(cuda_train_context_t* ctx) {
     if (c->d_loss) cudaFree(c->d_loss);
     if (c->h_pinned) cudaFreeHost(c->h_pinned);
     free(c->h_seq);
+    free(c->h_extras);
     if (c->pub.debug_nan_flags) cuda_train_buffer_free(ctx, c->pub.debug_nan_flags);
     cudaStreamDestroy(S(c));
     c->magic = 0;

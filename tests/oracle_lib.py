@@ -70,7 +70,7 @@ def lib():
         "ref_lora_param_count": (sz, [C.POINTER(RefCfg), C.c_int, C.c_int]),
         "ref_train_step": (C.c_float, [C.POINTER(RefCfg), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                        C.c_int, C.c_float, C.c_int, C.c_int,
-                                       i32p, C.c_int, i32p, C.c_int, C.c_void_p, C.c_void_p]),
+                                       i32p, C.c_int, i32p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
         "ref_effective_lr": (C.c_float, [C.c_float, C.c_int, C.c_int]),
     }
     for name, (res, args) in sig.items():
@@ -85,7 +85,7 @@ def _ptr(a):
 
 
 def train_step(cfg, params, tokens, seq_starts, lora=None, rank=0, alpha=0.0, mask=0, lora_exact=0,
-               grads=None, want_logits=False, want_dh0=False):
+               grads=None, want_logits=False, want_dh0=False, extras=None):
     """One oracle step.  Returns dict(loss, grads, logits?, dh0?).  grads is
     accumulated into when given (full-weight: parameter grads; LoRA: adapter grads)."""
     L = lib()
@@ -101,9 +101,10 @@ def train_step(cfg, params, tokens, seq_starts, lora=None, rank=0, alpha=0.0, ma
         pg, lg = None, g
     logits = np.empty((T, cfg.V), np.float32) if want_logits else None
     dh0 = np.empty((T, cfg.d), np.float32) if want_dh0 else None
+    xg = np.zeros_like(extras) if (extras is not None and lora is None) else None
     loss = L.ref_train_step(C.byref(c), _ptr(params), _ptr(pg), _ptr(lora), _ptr(lg), rank, alpha, mask, lora_exact,
-                            tokens, T, ss, B, _ptr(logits), _ptr(dh0))
-    return {"loss": float(loss), "grads": g, "logits": logits, "dh0": dh0}
+                            tokens, T, ss, B, _ptr(logits), _ptr(dh0), _ptr(extras), _ptr(xg))
+    return {"loss": float(loss), "grads": g, "logits": logits, "dh0": dh0, "extras_grads": xg}
 
 
 def ref_lib(kind):

@@ -370,14 +370,10 @@ def test_lora_state_without_host_weights_reads_the_bf16_model(ctx, tmp_path):
     tok = tokens_for(cfg, ss[-1], 83)
     path = str(tmp_path / "base.safetensors")
     ctx.lib.seraph_b200_reset_model(ctx.h)
-    st = api.TrainState(cfg, p)
-    api.step_full_batch(ctx, st, tok, ss)                                          # makes the model resident; lr is tiny, the weights move
-    st.set(0, p)
-    ctx.lib.seraph_b200_reset_model(ctx.h)
-    st2 = api.TrainState(cfg, p, lr=0.0)
-    api.step_full_batch(ctx, st2, tok, ss)                                         # lr 0 at step 1 of the warm-up: weights stay p
-    assert ctx.lib.seraph_b200_save_safetensors(ctx.h, st2.h, path.encode()) == 0
-    st.close(); st2.close()
+    st = api.TrainState(cfg, p, lr=0.0)
+    api.step_full_batch(ctx, st, tok, ss)                                          # makes the model resident; learning rate 0: the weights stay p
+    assert ctx.lib.seraph_b200_save_safetensors(ctx.h, st.h, path.encode()) == 0
+    st.close()
     grads = []
     for from_file in (False, True):
         ctx.lib.seraph_b200_reset_model(ctx.h)
@@ -397,3 +393,49 @@ def test_lora_state_without_host_weights_reads_the_bf16_model(ctx, tmp_path):
     ref = O.train_step(cfg, p_bf16, tok, ss, lora=lo, rank=rank, alpha=alpha, mask=mask)
     assert abs(grads[1][0] - ref["loss"]) < 1e-5 * abs(ref["loss"])
     worst_tensor(tens, grads[1][1], ref["grads"])
+
+
+@pytest.mark.parametrize("head_norm,untied", [(1, 0), (0, 1), (1, 1)])
+def test_per_head_qk_norm_and_untied_lm_head(ctx, head_norm, untied):
+    """The model options that let Qwen3- and Mistral-shaped configurations run as written (not part of the reference's
+    training step, so pinned against the oracle's restatement, itself held against float64 autograd in tests/test_oracle.py):
+    a learned RMSNorm over each head of q and k before RoPE, and a separate lm_head.  Full-weight step: every weight gradient,
+    the gradients of the extra parameters and their AdamW update; tiny shape and a 128-wide-head shape."""
+    import dataclasses
+    from seraph_b200 import api
+    for base, ss, seed in ((O.TINY, O.TINY_SEQS, 91), (O.ModelCfg(V=1024, d=512, L=2, Hq=4, Hkv=2, hd=128, F=1024, theta=1e4), [0, 300, 512, 645], 92)):
+        cfg = dataclasses.replace(base, head_norm=head_norm, untied=untied)
+        p = cfg.init_params(seed, norm_jitter=0.1)
+        x = cfg.init_extras(seed + 1)
+        tok = tokens_for(cfg, ss[-1], seed + 2)
+        ref = O.train_step(cfg, p, tok, ss, extras=x)
+        assert ctx.lib.seraph_b200_set_model_extras(ctx.h, head_norm, untied, x.ctypes.data, x.size) == 0
+        st = api.TrainState(cfg, p)
+        loss = api.step_full_batch(ctx, st, tok, ss)
+        ctx.check()
+        assert abs(loss - ref["loss"]) < 1e-5 * abs(ref["loss"]), (loss, ref["loss"])
+        ctx.lib.cuda_download_gpu_gradients(ctx.h, st.h)
+        worst_tensor(cfg.tensors(), st.get(1), ref["grads"])
+        xg, xw = np.empty_like(x), np.empty_like(x)
+        assert ctx.lib.seraph_b200_get_model_extras(ctx.h, 1, xg.ctypes.data, xg.size) == 0
+        assert ctx.lib.seraph_b200_get_model_extras(ctx.h, 0, xw.ctypes.data, xw.size) == 0
+        print("extra parameters, worst gradient:", worst_tensor(cfg.extras_tensors()[0], xg, ref["extras_grads"]))
+        w, m, v = x.copy(), np.zeros_like(x), np.zeros_like(x)
+        O.lib().ref_adamw(w, ref["extras_grads"], m, v, x.size, O.lib().ref_effective_lr(3.14e-4, 1, 1), 0.9, 0.999, 0.01, 1e-8, 1)
+        assert rel_l2(xw, w) < 1e-6 and not np.array_equal(xw, x)
+        st.close()
+        # LoRA on top: the extra parameters are frozen, adapters see them in the forward and backward pass
+        rank, alpha, mask = 4, 8.0, 0x7F
+        tens, n = cfg.lora_tensors(rank, mask)
+        lo = (0.05 * np.random.default_rng(seed + 3).standard_normal(n)).astype(np.float32)
+        refl = O.train_step(cfg, p, tok, ss, lora=lo, rank=rank, alpha=alpha, mask=mask, extras=x)
+        assert ctx.lib.seraph_b200_set_model_extras(ctx.h, head_norm, untied, x.ctypes.data, x.size) == 0
+        st = api.TrainState(cfg, p)
+        st.attach_lora(rank, alpha, mask, lo)
+        loss = api.step_lora_batch(ctx, st, tok, ss)
+        ctx.check()
+        assert abs(loss - refl["loss"]) < 1e-5 * abs(refl["loss"])
+        ctx.lib.cuda_download_lora_weights(ctx.h, st.lora_ptr())
+        worst_tensor(tens, st.lora_get(1), refl["grads"])
+        st.close()
+    assert ctx.lib.seraph_b200_set_model_extras(ctx.h, 0, 0, None, 0) == 0

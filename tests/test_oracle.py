@@ -214,3 +214,29 @@ def test_qk_norm_forward_follows_shader_and_backward_is_its_derivative(eps):
     O.lib().ref_qk_norm(y2, None, T, H, hd, 0, eps)
     O.lib().ref_qk_norm_backward(y2, rms, dy, dx, T, H, hd, 0, eps)
     assert np.array_equal(y2, x) and np.array_equal(dx, dy)
+
+
+@pytest.mark.parametrize("head_norm,untied", [(1, 0), (0, 1), (1, 1)])
+def test_extras_per_head_norm_and_untied_head_match_autograd_float64(head_norm, untied):
+    """The two model options the reference's training step lacks (a learned RMSNorm over each head of q and k before RoPE;
+    a separate lm_head): the oracle's gradients of every weight and of the extra parameters against float64 autograd."""
+    import dataclasses
+    cfg = dataclasses.replace(TINY, head_norm=head_norm, untied=untied)
+    p = cfg.init_params(31, norm_jitter=0.1)
+    x = cfg.init_extras(32)
+    tok = np.random.default_rng(33).integers(0, cfg.V, TINY_SEQS[-1]).astype(np.int32)
+    ref = O.train_step(cfg, p, tok, TINY_SEQS, extras=x)
+    P = TM.unflatten(cfg, p)
+    X = TM.unflatten_extras(cfg, x)
+    loss, _ = TM.forward_loss(cfg, P, tok, TINY_SEQS, X=X)
+    loss.backward()
+    g = TM.flatten_grads(cfg, P)
+    assert abs(ref["loss"] - float(loss)) < 1e-6 * float(loss)
+    for name, shp, off in cfg.tensors():
+        n = int(np.prod(shp))
+        assert rel_l2(ref["grads"][off:off + n], g[off:off + n]) < 2e-6, name
+    for name, shp, off in cfg.extras_tensors()[0]:
+        n = int(np.prod(shp))
+        assert rel_l2(ref["extras_grads"][off:off + n], X[name].grad.numpy().ravel()) < 2e-6, name
+    base = O.train_step(TINY, p, tok, TINY_SEQS)
+    assert abs(base["loss"] - ref["loss"]) > 1e-5          # the options do change the model

@@ -43,7 +43,15 @@ def rmsnorm(x, w, eps):
     return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w
 
 
-def forward_loss(cfg, P, tokens, seq_starts, lora=None, rank=0, alpha=0.0):
+def unflatten_extras(cfg, flat, device="cpu", dtype=torch.float64, requires_grad=True):
+    out = {}
+    for name, shp, off in cfg.extras_tensors()[0]:
+        n = int(np.prod(shp))
+        out[name] = torch.tensor(flat[off:off + n].reshape(shp), dtype=dtype, device=device).requires_grad_(requires_grad)
+    return out
+
+
+def forward_loss(cfg, P, tokens, seq_starts, lora=None, rank=0, alpha=0.0, X=None):
     dev = P["embed"].device
     T, B = len(tokens), len(seq_starts) - 1
     tok = torch.tensor(np.maximum(np.asarray(tokens), 0), dtype=torch.long, device=dev)
@@ -69,8 +77,12 @@ def forward_loss(cfg, P, tokens, seq_starts, lora=None, rank=0, alpha=0.0):
     g = cfg.Hq // cfg.Hkv
     for l in range(cfg.L):
         x = rmsnorm(h, P[f"l{l}.in_norm"], cfg.eps)
-        q = rope(lin(x, f"l{l}.q"), pos, cfg.Hq, cfg.hd, cfg.theta)
-        k = rope(lin(x, f"l{l}.k"), pos, cfg.Hkv, cfg.hd, cfg.theta)
+        q, k = lin(x, f"l{l}.q"), lin(x, f"l{l}.k")
+        if getattr(cfg, "head_norm", 0) and X is not None:      # learned RMSNorm over each head, before RoPE
+            q = rmsnorm(q.view(T, cfg.Hq, cfg.hd), X[f"l{l}.q_norm"], cfg.eps).reshape(T, cfg.qd)
+            k = rmsnorm(k.view(T, cfg.Hkv, cfg.hd), X[f"l{l}.k_norm"], cfg.eps).reshape(T, cfg.kvd)
+        q = rope(q, pos, cfg.Hq, cfg.hd, cfg.theta)
+        k = rope(k, pos, cfg.Hkv, cfg.hd, cfg.theta)
         if getattr(cfg, "qk_norm", 0):           # whole-row normalisation after RoPE (shaders/qk_norm.comp)
             q = q.reshape(T, -1); k = k.reshape(T, -1)
             q = q / torch.clamp(torch.sqrt((q * q).mean(dim=1, keepdim=True)), min=cfg.eps)
@@ -86,7 +98,8 @@ def forward_loss(cfg, P, tokens, seq_starts, lora=None, rank=0, alpha=0.0):
         x = rmsnorm(h, P[f"l{l}.post_norm"], cfg.eps)
         ff = torch.nn.functional.silu(lin(x, f"l{l}.gate")) * lin(x, f"l{l}.up")
         h = h + lin(ff, f"l{l}.down")
-    logits = rmsnorm(h, P["final_norm"], cfg.eps) @ P["embed"].T
+    head = X["lm_head"] if (getattr(cfg, "untied", 0) and X is not None) else P["embed"]
+    logits = rmsnorm(h, P["final_norm"], cfg.eps) @ head.T
     tgt = torch.zeros(T, dtype=torch.long, device=dev)
     tgt[:-1] = tok[1:]
     lp = torch.log_softmax(logits, -1)

@@ -29,10 +29,10 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-QWEN = dict(V=151936, d=2048, L=28, Hq=16, Hkv=8, hd=128, F=6144, theta=1e6)
+QWEN = dict(V=151936, d=2048, L=28, Hq=16, Hkv=8, hd=128, F=6144, theta=1e6, head_norm=1)    # per-head q/k RMSNorm, tied embeddings
 SMALL = dict(V=8192, d=512, L=8, Hq=8, Hkv=8, hd=64, F=1408, theta=10000.0)
-SLICE = dict(V=16384, d=2048, L=2, Hq=16, Hkv=8, hd=128, F=6144, theta=1e6)     # two Qwen3-1.7B-shaped layers: small enough to profile
-MISTRAL4 = dict(V=32000, d=4096, L=4, Hq=32, Hkv=8, hd=128, F=14336, theta=1e6)  # four of the 32 Mistral-7B-shaped layers
+SLICE = dict(V=16384, d=2048, L=2, Hq=16, Hkv=8, hd=128, F=6144, theta=1e6, head_norm=1)     # two Qwen3-1.7B-shaped layers: small enough to profile
+MISTRAL4 = dict(V=32000, d=4096, L=4, Hq=32, Hkv=8, hd=128, F=14336, theta=1e6, untied=1)  # four of the 32 Mistral-7B-shaped layers, separate lm_head
 WORKLOADS = {
     "qwen3-1.7b-shaped full-weight FP32, 4x2048 tokens per rank": dict(kind="full", model=QWEN, B=4, S=2048),
     "profiling slice: 2 qwen3-1.7b-shaped layers, vocab 16384, 2x2048 tokens": dict(kind="full", model=SLICE, B=2, S=2048),
@@ -43,7 +43,7 @@ WORKLOADS = {
         dict(kind="attn", B=8, H=16, S=2048, D=128),
     "qwen3-1.7b-shaped LoRA rank 16 alpha 32 on q,k,v,o, frozen FP32 base, 4x2048 tokens":
         dict(kind="lora", model=QWEN, B=4, S=2048, rank=16, alpha=32.0, mask=0b0001111),
-    "mistral-7b-shaped LoRA rank 64 on all seven projections, 4 of the 32 layers, tied head, 2x4096 tokens per rank":
+    "mistral-7b-shaped LoRA rank 64 on all seven projections, 4 of the 32 layers, untied head, 2x4096 tokens per rank":
         dict(kind="lora", model=MISTRAL4, B=2, S=4096, rank=64, alpha=128.0, mask=0x7F),
 }
 METRIC = "train tokens/sec (fwd+bwd+AdamW)"
@@ -407,6 +407,10 @@ def run_ours(args):
         uid = t.cpu().numpy()
         assert ctx.lib.seraph_dp_init(ctx.h, rank, world, uid.ctypes.data) == 0, "seraph_dp_init failed"
         dpc = dp_check(ctx, dist, torch, rank, world, local)
+    if cfg.head_norm or cfg.untied:
+        x = cfg.init_extras(4321, norm_jitter=0.0)
+        assert ctx.lib.seraph_b200_set_model_extras(ctx.h, cfg.head_norm, cfg.untied, x.ctypes.data, x.size) == 0
+        del x
     # same weights on every rank (seed), different tokens per rank
     params = seeded_params(cfg)
     st = api.TrainState(cfg, params, lr=3.14e-4, accum=1, lean=True)
@@ -508,9 +512,9 @@ def run_ours(args):
             "config": {"workload": args.workload, "tokens_per_rank": T, "global_tokens": T * world,
                        "parallelism": f"dp{world}", "gemm_mode": ["fp32x3_tcgen05", "tf32_tcgen05", "bf16_tcgen05", "fp32_cuda_cores", "fp32_f16x3_tcgen05"][args.gemm_mode],
                        "l2": "working set per step (weights 6.9 GB + activations) far exceeds the 126 MB L2; no flush needed",
-                       "qk_norm": "whole-row (the reference's shader form)" if mc.get("qk_norm") else
-                                  "off: the reference's training step has no per-head q/k RMSNorm (its qk_norm is a whole-row form for video mode)",
-                       "lm_head": "tied to the embedding, as the reference always trains it",
+                       "qk_norm": ("whole-row, unweighted, after RoPE (the reference's shader form)" if mc.get("qk_norm") else
+                                   "learned per-head RMSNorm of q and k before RoPE, trained" if mc.get("head_norm") else "off"),
+                       "lm_head": "separate lm_head [V, d]" if mc.get("untied") else "tied to the embedding",
                        "optimizer": "AdamW lr 3.14e-4 (reference warm-up), betas 0.9/0.999, wd 0.01, no clip (the reference has none)"},
             "loss": loss_res, "loss_first": loss0,
             "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,

@@ -314,6 +314,18 @@ int seraph_dp_init(cuda_train_context_t* ctx, int rank, int world, const void* n
 void seraph_dp_finalize(cuda_train_context_t* ctx);
 int seraph_dp_wait(cuda_train_context_t* ctx, int timeout_ms);
 int seraph_dp_world(cuda_train_context_t* ctx);
+/* For a command-line trainer run as one process per GPU (the reference's tools/seraph_train_cuda.c runs a single process):
+ * env: rank and world from SERAPH_DP_RANK / SERAPH_DP_WORLD, else RANK / WORLD_SIZE (0, 1 when unset); returns 0 or 1 (inconsistent).
+ * init_from_env: seraph_dp_init for that rank, the communicator id carried from rank 0 through the file SERAPH_DP_ID_FILE
+ *   (default /tmp/seraph_dp_id.<MASTER_PORT>); the other ranks wait up to two minutes for it.
+ * shard_samples: this rank's contiguous share (num_samples / world samples) of what train_load_data left in the state
+ *   (src/train.c:812), moved to the front of sample_offsets, num_train_tokens set to the share's end; returns the first
+ *   sample's original index or -1.
+ * all_min: the smallest value any rank passed; with 1 = "I have a batch" a trainer stops all ranks together. */
+int seraph_dp_env(int* rank, int* world);
+int seraph_dp_init_from_env(cuda_train_context_t* ctx);
+int seraph_dp_shard_samples(int* sample_offsets, int* num_samples, int* num_train_tokens, int rank, int world);
+int seraph_dp_all_min(cuda_train_context_t* ctx, int value);
 
 /* A train_state_t built in memory from flat float arrays, for callers that hold
  * the weights already (the reference only builds one from a model directory,

@@ -100,6 +100,8 @@ def load():
         "seraph_b200_rmsnorm_backward_static": (i, [vp, vp, vp, vp, vp, i, i, f, vp]),
         "seraph_dp_get_unique_id": (i, [vp]), "seraph_dp_init": (i, [vp, i, i, vp]), "seraph_dp_finalize": (None, [vp]),
         "seraph_dp_wait": (i, [vp, i]), "seraph_dp_world": (i, [vp]),
+        "seraph_dp_env": (i, [vp, vp]), "seraph_dp_init_from_env": (i, [vp]), "seraph_dp_shard_samples": (i, [vp, vp, vp, i, i]),
+        "seraph_dp_all_min": (i, [vp, i]),
         "seraph_b200_state_create": (vp, [i] * 7 + [f, f, i]), "seraph_b200_state_free": (None, [vp]),
         "seraph_b200_state_param_count": (sz, [vp]), "seraph_b200_state_set": (None, [vp, i, vp]),
         "seraph_b200_state_get": (None, [vp, i, vp]), "seraph_b200_state_set_counters": (None, [vp, i, i]),

@@ -174,4 +174,23 @@ int seraph_dp_wait(cuda_train_context_t* ctx, int timeout_ms) {
     }
 }
 
+/* The smallest `value` any rank passed (every rank must call it at the same point).  A trainer whose ranks may run out of
+ * batches at different times calls it once per step with 1 = "I have a batch" and stops when it returns 0, so that no rank
+ * enters a step whose collectives the others never join.  A world of one returns `value`; -1 on a communication failure. */
+int seraph_dp_all_min(cuda_train_context_t* ctx, int value) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c) return -1;
+    if (c->dp_world <= 1 || !c->nccl_comm) return value;
+    int* d = (int*)sb_scratch(c, 64);
+    if (!d) return -1;
+    cudaStream_t cs = (cudaStream_t)c->comm_stream;
+    cudaStreamSynchronize((cudaStream_t)c->pub.stream);            /* the scratch word may still be in use by the step */
+    if (cudaMemcpyAsync(d, &value, sizeof value, cudaMemcpyHostToDevice, cs) != cudaSuccess) return -1;
+    if (nccl_fail(c, N.AllReduce(d, d, 1, ncclInt32, ncclMin, (ncclComm_t)c->nccl_comm, cs), "ncclAllReduce(min)")) return -1;
+    if (seraph_dp_wait(ctx, c->dp_timeout_ms) != SB_OK) return -1;
+    int out = value;
+    if (cudaMemcpy(&out, d, sizeof out, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    return out;
+}
+
 int seraph_dp_world(cuda_train_context_t* ctx) { sb_ctx_t* c = sb_priv(ctx); return c ? c->dp_world : 0; }

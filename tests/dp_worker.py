@@ -15,32 +15,15 @@ sys.path.insert(0, HERE)
 sys.path.insert(0, os.path.dirname(HERE))
 
 
-def exchange_id(lib, rank, d):
-    path = os.path.join(d, "nccl_id.bin")
-    uid = np.zeros(128, np.uint8)
-    if rank == 0:
-        assert lib.seraph_dp_get_unique_id(uid.ctypes.data) == 0
-        with open(path + ".tmp", "wb") as f:
-            f.write(uid.tobytes())
-        os.rename(path + ".tmp", path)
-    else:
-        t0 = time.time()
-        while not os.path.exists(path):
-            if time.time() - t0 > 120:
-                raise RuntimeError("rank 0 never wrote the communicator id")
-            time.sleep(0.05)
-        uid = np.frombuffer(open(path, "rb").read(), np.uint8).copy()
-    return uid
-
-
 def real(rank, world, d, accum):
     from seraph_b200 import api
     import oracle_lib as O
     cfg, ss = O.TINY, np.array(O.TINY_SEQS, np.int32)
     ctx = api.Context(rank)
-    uid = exchange_id(ctx.lib, rank, d)
-    assert ctx.lib.seraph_dp_init(ctx.h, rank, world, uid.ctypes.data) == 0
+    # rank, world and the id file come from the environment the parent set (RANK, WORLD_SIZE, SERAPH_DP_ID_FILE)
+    assert ctx.lib.seraph_dp_init_from_env(ctx.h) == 0
     assert ctx.lib.seraph_dp_world(ctx.h) == world
+    assert ctx.lib.seraph_dp_all_min(ctx.h, 5 + rank) == 5 and ctx.lib.seraph_dp_all_min(ctx.h, 1 if rank else 0) == 0
     p = cfg.init_params(7, norm_jitter=0.1)                         # same weights on every rank
     st = api.TrainState(cfg, p, accum=accum)
     losses = []

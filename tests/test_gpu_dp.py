@@ -86,8 +86,9 @@ def test_two_ranks_over_nccl_stay_identical_and_match_the_oracle(tmp_path, accum
     if gpu_count() < 2:
         pytest.skip("needs two GPUs")
     world = 2
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    procs = [subprocess.Popen([sys.executable, WORKER, "real", str(r), str(world), str(tmp_path), str(accum)], env=env) for r in range(world)]
+    procs = [subprocess.Popen([sys.executable, WORKER, "real", str(r), str(world), str(tmp_path), str(accum)],
+                              env=dict(os.environ, NCCL_NVLS_ENABLE="0", RANK=str(r), WORLD_SIZE=str(world),
+                                       SERAPH_DP_ID_FILE=str(tmp_path / "nccl_id.bin"))) for r in range(world)]
     for p in procs:
         assert p.wait(timeout=600) == 0
     out = [np.load(tmp_path / f"rank{r}.npz") for r in range(world)]

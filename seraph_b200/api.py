@@ -218,7 +218,7 @@ class Context:
         assert self.lib.seraph_b200_set_gemm_mode(self.h, mode) == 0
 
     def set_attn_flash(self, on):
-        assert self.lib.seraph_b200_set_attn_flash(self.h, 1 if on else 0) == 0
+        assert self.lib.seraph_b200_set_attn_flash(self.h, int(on)) == 0
 
     def set_attn_fused(self, on):
         assert self.lib.seraph_b200_set_attn_fused(self.h, 1 if on else 0) == 0

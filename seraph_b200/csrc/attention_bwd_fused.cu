@@ -1,0 +1,378 @@
+// attention_bwd_fused.cu - causal attention backward with dK and dV kept on chip (head size 128, FP16 hi/lo parts,
+// FP32-level accuracy).  Replaces batch_attention_backward_packed_kernel / flash_attention_bwd_packed_kernel of the
+// reference (src/cuda_train_context.cu:1013, :2012), which add into dK and dV with float atomics from every query tile.
+//
+// One CTA owns 128 consecutive keys of one (sequence, K/V head): the FP16 parts of those rows of K and V stay in shared
+// memory (2 x 64 KB) for the CTA's whole life.  It walks over the query heads of the K/V head's group and, for each, over
+// the sequence's queries from the diagonal to the end in blocks of 32 (Q and dO parts, 32 KB per block, three stages):
+//
+//   S^T  = K Q_j^T,  dP^T = V dO_j^T     tcgen05.mma kind::f16, M 128 (keys) x N 32 (queries) x K 128, three passes each
+//                                        (k1 q1 + k2 q1 + k1 q2), accumulators in tensor memory, two buffers
+//   P^T  = exp(S^T/sqrt(hd) - lse),  dS^T = P^T o (dP^T - D)/sqrt(hd)      by the elementwise warps, one key row per
+//                                        thread; both go BACK INTO TENSOR MEMORY as FP16 hi/lo parts, over the very
+//                                        columns S^T and dP^T came from (tcgen05.st), to be the A operand of
+//   dV  += P^T dO_j,  dK += dS^T Q_j     M 128 (keys) x N 128 (head dim) x K 32 (queries), A from tensor memory, B = the
+//                                        same Q / dO tiles read in place MN-major; accumulators of 128 columns each in
+//                                        tensor memory, summed over the query blocks and heads
+//
+// The tensor core adds into its accumulator with truncation, so a chain of accumulation is cut after AB_DRAIN query
+// blocks: four drain warps read dK and dV out of tensor memory and add them into the output with red.global.add.f32
+// (round to nearest, performed in L2).  A dK/dV element is only ever touched by the one CTA that owns its key, its
+// additions are issued by one thread in program order, and the output is zeroed (or holds the caller's values) before
+// the launch: the result does not depend on scheduling and is the same bits on every run.
+// dS^T also leaves the chip, as FP16 parts laid out [head slot][key][query]: dQ = dS K is one more product on the
+// GEMM kernel (M = queries, K = keys up to the diagonal, A read MN-major).  P never reaches memory, dS is written once
+// and read once: 8 bytes per score element instead of the 20 of the score-materialising path.
+//
+// Warps (16): 0 TMA producer, 1 MMA issuer (owns the tensor-memory allocation), 4-7 elementwise for even steps, 8-11 for
+// odd steps, 12-15 drain.  Every mbarrier wait is bounded; a wait that runs out sets the status word and the CTA drains
+// and frees its tensor memory.
+#include "attention_fused.cuh"
+
+#define AB_BK 128                 // keys per CTA
+#define AB_BQ 32                  // queries per step
+#define AB_STAGES 3
+#define AB_THREADS 512
+#define AB_DRAIN 4                // steps per accumulation chain in tensor memory (4 x 12 instructions)
+#define AB_KV_BYTES 65536         // the parts of 128 rows of K (or V): 2 parts x 2 halves of the head dimension x 128 x 128 B
+#define AB_OFF_V AB_KV_BYTES
+#define AB_OFF_ST (2 * AB_KV_BYTES)
+#define AB_STAGE_BYTES 32768      // Q parts 16 KB, dO parts 16 KB
+#define AB_OFF_BAR (AB_OFF_ST + AB_STAGES * AB_STAGE_BYTES)
+#define AB_SMEM (AB_OFF_BAR + 1024 + 1024)
+#define AB_REGS_LIGHT 72
+#define AB_REGS_EW 168
+// tensor-memory columns: dK 0..127, dV 128..255, then per buffer e: S^T at 256 + 64 e (32 columns, one per query), dP^T 32 further.
+// The FP16 parts of P^T and dS^T replace them in place: for each k-step of 16 queries, 8 columns of hi parts then 8 of lo parts.
+#define AB_COL_DK 0
+#define AB_COL_DV 128
+#define AB_COL_S(e) (256 + 64 * (e))
+#define AB_COL_DP(e) (256 + 64 * (e) + 32)
+
+// A from tensor memory (M 128 lanes, 16 halfs of k = 8 columns), B from shared memory
+__device__ __forceinline__ void ab_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void ab_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+}
+#define AB_REGS16(r) "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), \
+                     "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+__device__ __forceinline__ void ab_ld_wait2(uint32_t (&a)[16], uint32_t (&b)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : AB_REGS16(a), AB_REGS16(b) :: "memory");
+}
+__device__ __forceinline__ void ab_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+}
+__device__ __forceinline__ void ab_red4(float* p, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__global__ void __launch_bounds__(AB_THREADS, 1)
+at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant__ CUtensorMap mQ2,
+                  const __grid_constant__ CUtensorMap mD1, const __grid_constant__ CUtensorMap mD2,
+                  const __grid_constant__ CUtensorMap mK1, const __grid_constant__ CUtensorMap mK2,
+                  const __grid_constant__ CUtensorMap mV1, const __grid_constant__ CUtensorMap mV2,
+                  const float* __restrict__ lse, const float* __restrict__ D,
+                  __half* __restrict__ dS1, __half* __restrict__ dS2, float* __restrict__ dK, float* __restrict__ dV,
+                  const float* __restrict__ amax_q, const float* __restrict__ amax_k, const float* __restrict__ amax_v,
+                  const float* __restrict__ amax_do, const float* __restrict__ ds_bound,
+                  const __grid_constant__ AfSeqs seqs, int Sp, int Hq, int g, int nkb, float scale, int* status) {
+    // which (key block, sequence, K/V head): key blocks from the start of the sequences first, they have the most queries
+    const int Hkv = Hq / g;
+    const int per_kb = seqs.n * Hkv;
+    const int kb = (int)blockIdx.x / per_kb;
+    const int rem = (int)blockIdx.x % per_kb;
+    const int b = rem / Hkv, kvh = rem % Hkv;
+    const int t0 = seqs.start[b], S = seqs.start[b + 1] - t0;
+    const int k0 = kb * AB_BK;
+    if (kb >= nkb || k0 >= S) return;
+    if (*(volatile int*)status != 0) return;
+    const int nq = (S + AB_BQ - 1) / AB_BQ, j0 = k0 / AB_BQ, per_head = nq - j0;
+    const int nsteps = g * per_head;
+    const int nchains = (nsteps + AB_DRAIN - 1) / AB_DRAIN;
+    const int kvd = Hkv * AF_HD;
+
+    extern __shared__ uint8_t af_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)af_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + AB_OFF_BAR);
+    uint64_t* kv_full = bars;            // 1
+    uint64_t* full = bars + 1;           // 3
+    uint64_t* empty = bars + 4;          // 3
+    uint64_t* sdp_full = bars + 7;       // 2
+    uint64_t* p_full = bars + 9;         // 2
+    uint64_t* acc_ready = bars + 11;     // 1
+    uint64_t* acc_free = bars + 12;      // 1
+    uint32_t* tmem_slot = (uint32_t*)(bars + 16);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        mbar_init(kv_full, 1); mbar_init(acc_ready, 1); mbar_init(acc_free, 4);
+        for (int i = 0; i < AB_STAGES; i++) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < 2; i++) { mbar_init(&sdp_full[i], 1); mbar_init(&p_full[i], 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    bool ok = true;
+
+    if (warp < 4 || warp >= 12) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(AB_REGS_LIGHT));
+        if (warp == 0) {
+            // ---------------- TMA producer ----------------
+            if (elect_one()) {
+                mbar_expect_tx(kv_full, 2 * AB_KV_BYTES);
+                for (int p = 0; p < 2; p++) {
+                    af_tma_2d(smem + p * 16384, &mK1, kv_full, kvh * AF_HD + p * 64, t0 + k0);
+                    af_tma_2d(smem + 32768 + p * 16384, &mK2, kv_full, kvh * AF_HD + p * 64, t0 + k0);
+                    af_tma_2d(smem + AB_OFF_V + p * 16384, &mV1, kv_full, kvh * AF_HD + p * 64, t0 + k0);
+                    af_tma_2d(smem + AB_OFF_V + 32768 + p * 16384, &mV2, kv_full, kvh * AF_HD + p * 64, t0 + k0);
+                }
+                for (int t = 0; t < nsteps && ok; t++) {
+                    const int s = t % AB_STAGES, u = t / AB_STAGES;
+                    const int h = kvh * g + t / per_head, j = j0 + t % per_head;
+                    ok = mbar_wait(&empty[s], (u & 1) ^ 1);
+                    if (!ok) break;
+                    uint8_t* st = smem + AB_OFF_ST + s * AB_STAGE_BYTES;
+                    mbar_expect_tx(&full[s], AB_STAGE_BYTES);
+                    for (int p = 0; p < 2; p++) {
+                        af_tma_2d(st + p * 4096, &mQ1, &full[s], h * AF_HD + p * 64, t0 + j * AB_BQ);
+                        af_tma_2d(st + 8192 + p * 4096, &mQ2, &full[s], h * AF_HD + p * 64, t0 + j * AB_BQ);
+                        af_tma_2d(st + 16384 + p * 4096, &mD1, &full[s], h * AF_HD + p * 64, t0 + j * AB_BQ);
+                        af_tma_2d(st + 24576 + p * 4096, &mD2, &full[s], h * AF_HD + p * 64, t0 + j * AB_BQ);
+                    }
+                }
+                if (!ok) atomicExch(status, SB_ERR_TIMEOUT);
+            }
+        } else if (warp == 1) {
+            // ---------------- MMA issuer ----------------
+            if (elect_one()) {
+                const uint32_t idesc_s = (1u << 4) | ((uint32_t)(AB_BQ >> 3) << 17) | ((uint32_t)(AB_BK >> 4) << 24);
+                const uint32_t idesc_o = (1u << 4) | (1u << 16) | ((uint32_t)(AF_HD >> 3) << 17) | ((uint32_t)(AB_BK >> 4) << 24);
+                const uint32_t sk = smem_u32(smem), sv = smem_u32(smem + AB_OFF_V);
+                ok = mbar_wait(kv_full, 0);
+                for (int t = 0; t <= nsteps && ok; t++) {
+                    if (t < nsteps) {
+                        // S^T and dP^T of step t into buffer t & 1 (its parts of step t - 2 were consumed by instructions issued before these)
+                        const int s = t % AB_STAGES, e = t & 1;
+                        ok = mbar_wait(&full[s], (t / AB_STAGES) & 1);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t st = smem_u32(smem + AB_OFF_ST + s * AB_STAGE_BYTES);
+#pragma unroll
+                        for (int prod = 0; prod < 2; prod++) {
+                            const uint32_t sa = prod ? sv : sk, sb = st + (prod ? 16384 : 0);
+                            const uint32_t d = tmem_base + (uint32_t)(prod ? AB_COL_DP(e) : AB_COL_S(e));
+#pragma unroll
+                            for (int p = 0; p < 2; p++) {
+                                const uint64_t a1 = make_kmajor_desc<128>(sa + p * 16384), a2 = make_kmajor_desc<128>(sa + 32768 + p * 16384);
+                                const uint64_t b1 = make_kmajor_desc<128>(sb + p * 4096), b2 = make_kmajor_desc<128>(sb + 8192 + p * 4096);
+#pragma unroll
+                                for (int kk = 0; kk < 4; kk++) {
+                                    const uint64_t adv = (uint64_t)(kk * 2);
+                                    af_mma_f16(d, a1 + adv, b1 + adv, idesc_s, (p | kk) ? 1u : 0u);
+                                    af_mma_f16(d, a2 + adv, b1 + adv, idesc_s, 1);
+                                    af_mma_f16(d, a1 + adv, b2 + adv, idesc_s, 1);
+                                }
+                            }
+                        }
+                        tc_commit(&sdp_full[e]);
+                    }
+                    if (t >= 1) {
+                        // dV += P^T dO and dK += dS^T Q of step t - 1
+                        const int u = t - 1, e = u & 1, s = u % AB_STAGES;
+                        ok = mbar_wait(&p_full[e], (u >> 1) & 1);
+                        if (!ok) break;
+                        const bool first = (u % AB_DRAIN) == 0;
+                        if (first && u > 0) {                        // the drain warps have read the previous chain out
+                            ok = mbar_wait(acc_free, (u / AB_DRAIN - 1) & 1);
+                            if (!ok) break;
+                        }
+                        tc_fence_after();
+                        const uint32_t st = smem_u32(smem + AB_OFF_ST + s * AB_STAGE_BYTES);
+#pragma unroll
+                        for (int prod = 0; prod < 2; prod++) {
+                            const uint32_t ta = tmem_base + (uint32_t)(prod ? AB_COL_DP(e) : AB_COL_S(e));      // per k-step of 16 queries: hi part 8 columns, lo part the next 8
+                            const uint32_t sb = st + (prod ? 0 : 16384);                                       // dK takes Q, dV takes dO
+                            const uint64_t b1 = make_mn16_desc<AB_BQ>(sb), b2 = make_mn16_desc<AB_BQ>(sb + 8192);
+                            const uint32_t d = tmem_base + (uint32_t)(prod ? AB_COL_DK : AB_COL_DV);
+#pragma unroll
+                            for (int kk = 0; kk < 2; kk++) {
+                                const uint64_t advb = (uint64_t)(kk * 128);
+                                ab_mma_ts(d, ta + kk * 16, b1 + advb, idesc_o, (first && kk == 0) ? 0u : 1u);
+                                ab_mma_ts(d, ta + kk * 16 + 8, b1 + advb, idesc_o, 1);
+                                ab_mma_ts(d, ta + kk * 16, b2 + advb, idesc_o, 1);
+                            }
+                        }
+                        tc_commit(&empty[s]);
+                        if (((u + 1) % AB_DRAIN) == 0 || u == nsteps - 1) tc_commit(acc_ready);
+                    }
+                }
+                if (!ok) atomicExch(status, SB_ERR_TIMEOUT);
+            }
+        } else if (warp >= 12) {
+            // ---------------- drain: dK and dV chains out of tensor memory, added into the output ----------------
+            const int q = warp & 3, r = q * 32 + lane, kg = k0 + r;
+            const bool live = kg < S;
+            // dV accumulates (P 2^14) (dO 2^s_do), dK accumulates (dS 2^s_ds) (Q 2^s_q)
+            const float fv = tc_pow2(-14) * tc_pow2(-tc_f16_shift(__ldg(amax_do)));
+            const float fk = tc_pow2(-tc_f16_shift(__ldg(ds_bound))) * tc_pow2(-tc_f16_shift(__ldg(amax_q)));
+            float* rowk = dK + (size_t)(t0 + (live ? kg : 0)) * kvd + (size_t)kvh * AF_HD;
+            float* rowv = dV + (size_t)(t0 + (live ? kg : 0)) * kvd + (size_t)kvh * AF_HD;
+            for (int c = 0; c < nchains && ok; c++) {
+                ok = mbar_wait(acc_ready, c & 1);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t ta = tmem_base + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+                for (int piece = 0; piece < 8; piece++) {          // 4 x 32 columns of dK, then of dV
+                    uint32_t v[32];
+                    af_ld32_issue(ta + (uint32_t)(piece * 32), v);
+                    af_ld_wait(v);
+                    if (piece == 7) {                               // everything is in registers: the next chain may overwrite the accumulators
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) af_arrive(acc_free);
+                    }
+                    if (live) {
+                        const float f = piece < 4 ? fk : fv;
+                        float* dst = (piece < 4 ? rowk : rowv) + (piece & 3) * 32;
+#pragma unroll
+                        for (int i = 0; i < 8; i++)
+                            ab_red4(dst + 4 * i, __uint_as_float(v[4 * i]) * f, __uint_as_float(v[4 * i + 1]) * f,
+                                    __uint_as_float(v[4 * i + 2]) * f, __uint_as_float(v[4 * i + 3]) * f);
+                    }
+                }
+            }
+            if (!ok && lane == 0) atomicExch(status, SB_ERR_TIMEOUT);
+        }
+    } else {
+        // ---------------- elementwise: one key row per thread; warps 4-7 take the even steps, 8-11 the odd ones ----------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(AB_REGS_EW));
+        const int e = (warp - 4) >> 2, q = warp & 3, r = q * 32 + lane, kg = k0 + r;
+        const float cs = tc_pow2(-tc_f16_shift(__ldg(amax_q))) * tc_pow2(-tc_f16_shift(__ldg(amax_k))) * (scale * 1.4426950408889634f);
+        const float cp = tc_pow2(-tc_f16_shift(__ldg(amax_do))) * tc_pow2(-tc_f16_shift(__ldg(amax_v)));
+        const float dsc = tc_pow2(tc_f16_shift(__ldg(ds_bound))) * scale * (1.0f / 16384.f);      // p holds P * 2^14
+        const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+        // Columns before this key block that the dQ product reads together with it (its query tiles are 256 wide): zeros
+        if (e == 0 && (k0 & 255) != 0) {
+            for (int hi = 0; hi < g; hi++) {
+                const int h = kvh * g + hi;
+                const size_t hb = (size_t)(b * g + hi) * Hkv + kvh;
+                uint4* z1 = (uint4*)(dS1 + (hb * Sp + (size_t)kg) * Sp + (k0 - 128));
+                uint4* z2 = (uint4*)(dS2 + (hb * Sp + (size_t)kg) * Sp + (k0 - 128));
+#pragma unroll
+                for (int i = 0; i < 16; i++) { z1[i] = make_uint4(0, 0, 0, 0); z2[i] = make_uint4(0, 0, 0, 0); }
+                (void)h;
+            }
+        }
+        for (int t = e; t < nsteps && ok; t += 2) {
+            const int hi = t / per_head, j = j0 + t % per_head;
+            const int h = kvh * g + hi, q0 = j * AB_BQ;
+            // this lane's query of the block: log-sum-exp (in powers of two) and D; handed round the warp by shuffles
+            const int ql = q0 + lane;
+            const float myL2 = ql < S ? __ldg(&lse[(size_t)(t0 + ql) * Hq + h]) * 1.4426950408889634f : 0.f;
+            const float myD = ql < S ? __ldg(&D[(size_t)(t0 + ql) * Hq + h]) : 0.f;
+            ok = mbar_wait(&sdp_full[e], (t >> 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            const size_t hb = (size_t)(b * g + hi) * Hkv + kvh;
+            __half* o1 = dS1 + (hb * Sp + (size_t)kg) * Sp + q0;
+            __half* o2 = dS2 + (hb * Sp + (size_t)kg) * Sp + q0;
+#pragma unroll
+            for (int half = 0; half < 2; half++) {                      // 16 queries at a time: one k-step of the dV and dK products
+                uint32_t sr[16], dr[16];
+                ab_ld16(tmem_base + lane_addr + (uint32_t)(AB_COL_S(e) + half * 16), sr);
+                ab_ld16(tmem_base + lane_addr + (uint32_t)(AB_COL_DP(e) + half * 16), dr);
+                ab_ld_wait2(sr, dr);
+                uint32_t p1[8], p2[8], d1[8], d2[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    float pv[2], dv[2];
+#pragma unroll
+                    for (int w = 0; w < 2; w++) {
+                        const int c = half * 16 + 2 * i + w;
+                        const float L2 = __shfl_sync(0xffffffffu, myL2, c), Dq = __shfl_sync(0xffffffffu, myD, c);
+                        const int qi = q0 + c;
+                        const bool valid = kg <= qi && qi < S && kg < S;
+                        const float y = fmaf(__uint_as_float(sr[2 * i + w]), cs, 14.f - L2);
+                        pv[w] = valid ? af_ex2(y) : 0.f;                                             // P * 2^14
+                        dv[w] = pv[w] * (__uint_as_float(dr[2 * i + w]) * cp - Dq) * dsc;
+                    }
+                    af_split2(pv[0], pv[1], p1[i], p2[i]);
+                    af_split2(dv[0], dv[1], d1[i], d2[i]);
+                }
+                // The parts of these 16 queries go back over the 16 columns their scores came from (all of them are in registers by
+                // now): hi part in the first 8 columns, lo part in the next 8, which is where the MMA issuer looks for k-step `half`.
+                ab_st8(tmem_base + lane_addr + (uint32_t)(AB_COL_S(e) + half * 16), p1);
+                ab_st8(tmem_base + lane_addr + (uint32_t)(AB_COL_S(e) + half * 16 + 8), p2);
+                ab_st8(tmem_base + lane_addr + (uint32_t)(AB_COL_DP(e) + half * 16), d1);
+                ab_st8(tmem_base + lane_addr + (uint32_t)(AB_COL_DP(e) + half * 16 + 8), d2);
+                // dS^T parts of this key row to memory: 16 queries = 32 bytes per part
+                *(uint4*)(o1 + half * 16) = make_uint4(d1[0], d1[1], d1[2], d1[3]); *(uint4*)(o1 + half * 16 + 8) = make_uint4(d1[4], d1[5], d1[6], d1[7]);
+                *(uint4*)(o2 + half * 16) = make_uint4(d2[0], d2[1], d2[2], d2[3]); *(uint4*)(o2 + half * 16 + 8) = make_uint4(d2[4], d2[5], d2[6], d2[7]);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) af_arrive(&p_full[e]);
+        }
+        if (!ok && lane == 0) atomicExch(status, SB_ERR_TIMEOUT);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
+    }
+}
+
+// q, do, k, v: the FP16 parts of Q, dO [T, Hq*128] and K, V [T, Hkv*128]; amax_*: the device words their scales derive from;
+// ds_bound: the device word that bounds |dS|.  dS1/dS2: the parts of dS^T, laid out [sequence][group member][K-V head][Sp][Sp]
+// (key rows, query columns).  dK and dV are added into (the caller zeroes them when they do not accumulate).
+// Returns 0 when the kernel was launched, 1 when this path does not take the call.
+extern "C" int sb_attention_fused_dkv(sb_ctx_t* c, const void* q1, const void* q2, const void* do1, const void* do2,
+                                      const void* k1, const void* k2, const void* v1, const void* v2,
+                                      const float* amax_q, const float* amax_k, const float* amax_v, const float* amax_do, const float* ds_bound,
+                                      const float* lse, const float* D, void* dS1, void* dS2, float* dK, float* dV,
+                                      int Sp, int T, int Hq, int Hkv, int hd) {
+    if (hd != AF_HD || (Sp % 256) || Hkv <= 0 || Hq % Hkv || !tc_load_encode()) return 1;
+    if (c->h_seq_n <= 0 || c->h_seq_n > AF_MAXSEQ) return 1;
+    if (!tc_aligned16(dK) || !tc_aligned16(dV)) return 1;
+    static bool attr_done = false;
+    if (!attr_done) {
+        if (cudaFuncSetAttribute(at_dkv_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AB_SMEM) != cudaSuccess) { cudaGetLastError(); return 1; }
+        attr_done = true;
+    }
+    AfSeqs seqs;
+    seqs.n = c->h_seq_n;
+    int Smax = 0;
+    for (int b = 0; b <= c->h_seq_n; b++) seqs.start[b] = c->h_seq[b];
+    for (int b = 0; b < c->h_seq_n; b++) Smax = max(Smax, c->h_seq[b + 1] - c->h_seq[b]);
+    if (Smax <= 0 || Smax > Sp) return 1;
+    const int qd = Hq * hd, kvd = Hkv * hd, nkb = (Smax + AB_BK - 1) / AB_BK;
+    CUtensorMap mQ1, mQ2, mD1, mD2, mK1, mK2, mV1, mV2;
+    if (!af_make_map(&mQ1, q1, T, qd, AB_BQ) || !af_make_map(&mQ2, q2, T, qd, AB_BQ) ||
+        !af_make_map(&mD1, do1, T, qd, AB_BQ) || !af_make_map(&mD2, do2, T, qd, AB_BQ) ||
+        !af_make_map(&mK1, k1, T, kvd, AB_BK) || !af_make_map(&mK2, k2, T, kvd, AB_BK) ||
+        !af_make_map(&mV1, v1, T, kvd, AB_BK) || !af_make_map(&mV2, v2, T, kvd, AB_BK)) return 1;
+    const long blocks = (long)nkb * seqs.n * Hkv;
+    if (blocks > 0x7fffffffL) return 1;
+    at_dkv_bwd_kernel<<<(unsigned)blocks, AB_THREADS, AB_SMEM, (cudaStream_t)c->pub.stream>>>(
+        mQ1, mQ2, mD1, mD2, mK1, mK2, mV1, mV2, lse, D, (__half*)dS1, (__half*)dS2, dK, dV,
+        amax_q, amax_k, amax_v, amax_do, ds_bound, seqs, Sp, Hq, Hq / Hkv, nkb, 1.0f / sqrtf((float)hd), c->d_status);
+    c->launches++;
+    return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}

@@ -440,7 +440,14 @@ extern "C" int sb_attention_tc_backward(sb_ctx_t* c, const float* Q, const float
     { const char* e = getenv("SERAPH_B200_ATTN_ALL_SCORES_MB"); if (e && e[0]) all_limit = (size_t)atol(e) << 20; }
     const bool all_scores = f16 && c->attn_flash && !c->attn_fused && hd == 128 && c->h_seq_n <= 240 && n_all * 8 <= all_limit;
     const size_t group_bytes = AT_SIDE * per_stream * sizeof(float);
-    float* bb = (float*)sb_gemm_stage(c, 3, all_scores ? (n_all * 8 > group_bytes ? n_all * 8 : group_bytes) : group_bytes);
+    // 128-wide heads, default mode: dK and dV accumulate on chip in one launch over all sequences and K/V heads that leaves only
+    // the FP16 parts of dS^T (4 bytes per score, [sequence][group member][K-V head][key][query]); dQ is then one product per
+    // sequence and group member.  seraph_b200_set_attn_flash(ctx, 2) or SERAPH_B200_ATTN_FLASH=2 selects the older
+    // score-materialising path instead.
+    const bool dkv_fused = f16 && c->attn_flash == 1 && !c->attn_fused && hd == 128 && c->h_seq_n <= 240 && !all_scores;
+    size_t need = all_scores ? (n_all * 8 > group_bytes ? n_all * 8 : group_bytes) : group_bytes;
+    if (dkv_fused && n_all * 4 > need) need = n_all * 4;
+    float* bb = (float*)sb_gemm_stage(c, 3, need);
     if (!st0 || !bb) return 1;
     float* D = st0;
     float* consts = st0 + d_floats;                                  // [0] 1.0, [1] dS bound, [2] max |dO row|, [3] max |V row|, [8..11] amax of Q, K, V, dO
@@ -477,6 +484,35 @@ extern "C" int sb_attention_tc_backward(sb_ctx_t* c, const float* Q, const float
         __half* a = (__half*)bb;
         have_all = sb_attention_fused_scores(c, pq.h1, pq.h2, pdo.h1, pdo.h2, pk.h1, pk.h2, pv.h1, pv.h2, pq.amax, pk.amax, pv.amax, pdo.amax,
                                              consts + 1, lse, D, a, a + n_all, a + 2 * n_all, a + 3 * n_all, 0, 0, Sp, T, Hq, Hkv, hd, 0, 0, 0) == 0;
+    }
+    if (dkv_fused) {
+        __half* a = (__half*)bb;
+        if (!accumulate_kv) {
+            cudaMemsetAsync(dK, 0, n_kv * sizeof(float), s0);
+            cudaMemsetAsync(dV, 0, n_kv * sizeof(float), s0);
+        }
+        if (sb_attention_fused_dkv(c, pq.h1, pq.h2, pdo.h1, pdo.h2, pk.h1, pk.h2, pv.h1, pv.h2, pq.amax, pk.amax, pv.amax, pdo.amax,
+                                   consts + 1, lse, D, a, a + n_all, dK, dV, Sp, T, Hq, Hkv, hd) == 0) {
+            const int ns2 = at_fork(c, c->h_seq_n);
+            const long sb = (long)Sp * Sp;
+            for (int b = 0; b < c->h_seq_n && ok; b++) {
+                const int t0 = c->h_seq[b], S = c->h_seq[b + 1] - t0;
+                if (S <= 0) continue;
+                flops += 5.0 * Hq * (double)S * S * hd;
+                if (ns2 > 1) c->pub.stream = c->side_stream[b % ns2];
+                for (int r = 0; r < g && ok; r++) {
+                    __half* d1 = a + ((size_t)(b * g + r) * Hkv) * (size_t)sb;
+                    const AtParts pds = {d1, d1 + n_all, consts + 1};
+                    ok = ok && at_gemm(c, op_scratch(bb, pds, S, Sp, Hkv, 1), op_tokens_mn(K, pk, t0, kvd, Hkv, hd, 0, 1),
+                                       dQ + (size_t)t0 * qd + (size_t)r * hd, qd, (long)g * hd, S, hd, S, 0, Hkv, TC_CAUSAL_K_UPTO_M,
+                                       nullptr, pds.amax, pk.amax);                                                           // dQ = dS K
+                }
+            }
+            at_join(c, ns2, main_stream);
+            sb_tick_end(c, tk, flops, 0.0);
+            if (!ok) { sb_set_status(c, SB_ERR_CUDA); return 1; }
+            return 0;
+        }
     }
     const int Gl = have_all ? Hkv : G;                               // K-V heads per launch of the long products
     const int ns = at_fork(c, c->h_seq_n);

@@ -75,7 +75,8 @@ typedef struct sb_ctx {
     struct { const float* ptr; size_t n; } hint_pending[4]; int hint_npending;
     unsigned parts_gen; int parts_open; int parts_cache;   /* parts_cache 0: off (switch, or the arena did not fit) */
     int eval_batch_tokens;           /* cuda_evaluate packs samples up to this many tokens per forward pass; 0: one sample per pass */
-    int attn_flash;                  /* 1: attention forward of 128-wide heads runs as one kernel (no score scratch) */
+    int attn_flash;                  /* 128-wide heads: 0 a launch per product over a score scratch; 1 (default) forward in one kernel, backward with
+                                        dK/dV kept on chip; 2 forward in one kernel, backward scores in one kernel and three long products */
     int attn_fused;                  /* 1: P and dS of the attention backward come out of the score products' epilogues */
     int gemm_tail_split;             /* 1: tiles of the last partial wave are cut into k pieces */
     int gemm_pair;                   /* 1: plain GEMMs run on CTA pairs (cta_group::2), 0: one CTA per tile */
@@ -228,6 +229,10 @@ int  sb_attention_fused_scores(sb_ctx_t*, const void* q1, const void* q2, const 
                                const void* v1, const void* v2, const float* amax_q, const float* amax_k, const float* amax_v, const float* amax_do,
                                const float* ds_bound, const float* lse, const float* D, void* P1, void* P2, void* dS1, void* dS2,
                                int t0, int S, int Sp, int T, int Hq, int Hkv, int hd, int head0, int head_step, int nb);
+int  sb_attention_fused_dkv(sb_ctx_t*, const void* q1, const void* q2, const void* do1, const void* do2, const void* k1, const void* k2,
+                            const void* v1, const void* v2, const float* amax_q, const float* amax_k, const float* amax_v, const float* amax_do,
+                            const float* ds_bound, const float* lse, const float* D, void* dS1, void* dS2, float* dK, float* dV,
+                            int Sp, int T, int Hq, int Hkv, int hd);
 int  sb_attention_tc_forward(sb_ctx_t*, const float* Q, const float* K, const float* V, float* O, float* lse, int T, int Hq, int Hkv, int hd);
 int  sb_attention_tc_backward(sb_ctx_t*, const float* Q, const float* K, const float* V, const float* O, const float* lse, const float* dO,
                               float* dQ, float* dK, float* dV, int accumulate_kv, int T, int Hq, int Hkv, int hd);

@@ -222,6 +222,8 @@ static const uint16_t* model_tensor(const seraph_model_t* m, const char* name, s
         for (int t = 0; t < f->num_tensors; t++)
             if (f->tensors[t].name && !strcmp(f->tensors[t].name, m->tensor_map[i].orig_name)) {
                 if (f->tensors[t].num_elements != want) return NULL;
+                /* the offsets come from the file's header: stay inside the mapping whatever it claims */
+                if (f->tensors[t].offset_start < 0 || f->data_offset + (size_t)f->tensors[t].offset_start + want * 2 > f->file_size) return NULL;
                 return (const uint16_t*)(f->data + f->data_offset + f->tensors[t].offset_start);
             }
         return NULL;

@@ -355,6 +355,33 @@ def test_bounded_wait_runs_out_and_the_context_survives(ctx):
     st.close()
 
 
+def write_hf_safetensors(path, cfg, p):
+    """A BF16 safetensors file with Hugging Face tensor names and true shapes, as a model directory holds it (the reference's
+    own checkpoint writer states hidden x hidden for the K and V projections of grouped-query models, src/train.c:472-473, so
+    its header cannot be used to locate tensors)."""
+    import json
+    names = {"embed": "model.embed_tokens.weight", "final_norm": "model.norm.weight", "q": "self_attn.q_proj", "k": "self_attn.k_proj",
+             "v": "self_attn.v_proj", "o": "self_attn.o_proj", "gate": "mlp.gate_proj", "up": "mlp.up_proj", "down": "mlp.down_proj",
+             "in_norm": "input_layernorm", "post_norm": "post_attention_layernorm"}
+    header, blobs, off = {"__metadata__": {"format": "pt"}}, [], 0
+    for name, shp, o in cfg.tensors():
+        n = int(np.prod(shp))
+        if name.startswith("l") and "." in name:
+            l, short = name[1:].split(".", 1)
+            full = f"model.layers.{l}.{names[short]}.weight"
+        else:
+            full = names[name]
+        raw = (p[o:o + n].view(np.uint32) >> 16).astype(np.uint16).tobytes()
+        header[full] = {"dtype": "BF16", "shape": list(shp), "data_offsets": [off, off + len(raw)]}
+        blobs.append(raw); off += len(raw)
+    h = json.dumps(header, separators=(",", ":")).encode()
+    h += b" " * ((8 - len(h) % 8) % 8)
+    with open(path, "wb") as f:
+        f.write(len(h).to_bytes(8, "little")); f.write(h)
+        for bl in blobs:
+            f.write(bl)
+
+
 def test_lora_state_without_host_weights_reads_the_bf16_model(ctx, tmp_path):
     """The state the reference's train_init builds for LoRA training has no FP32 host copies (full_weights is NULL,
     src/train.c:7900-7909): the frozen base comes from the BF16 tensors of the memory-mapped model, by name
@@ -369,11 +396,7 @@ def test_lora_state_without_host_weights_reads_the_bf16_model(ctx, tmp_path):
     lo = (0.02 * np.random.default_rng(82).standard_normal(n)).astype(np.float32)
     tok = tokens_for(cfg, ss[-1], 83)
     path = str(tmp_path / "base.safetensors")
-    ctx.lib.seraph_b200_reset_model(ctx.h)
-    st = api.TrainState(cfg, p, lr=0.0)
-    api.step_full_batch(ctx, st, tok, ss)                                          # makes the model resident; learning rate 0: the weights stay p
-    assert ctx.lib.seraph_b200_save_safetensors(ctx.h, st.h, path.encode()) == 0
-    st.close()
+    write_hf_safetensors(path, cfg, p)
     grads = []
     for from_file in (False, True):
         ctx.lib.seraph_b200_reset_model(ctx.h)

@@ -192,14 +192,16 @@ def test_attention_forward_backward(ctx, ss, Hq, Hkv, hd, fused):
     ctx.release(bq, bk, bv, bdo, bs, bout, blse, bdq, bdk, bdv, bdk2, bdv2)
 
 
-@pytest.mark.parametrize("flash", [1, 2, 0])
+@pytest.mark.parametrize("flash", [1, 2, 3, 0])
 @pytest.mark.parametrize("ss,Hq,Hkv", [([0, 257], 4, 1), ([0, 1024], 4, 1), ([0, 100, 420, 1000], 4, 2), ([0, 1, 130, 131, 450], 2, 2),
-                                       ([0, 2048, 2100], 6, 3)])
+                                       ([0, 2048, 2100], 6, 3), ([0, 33, 700], 2, 2)])
 def test_attention_head128_one_kernel_paths(ctx, ss, Hq, Hkv, flash):
-    """Head size 128, default GEMM mode.  flash = 1: the forward is one kernel (scores in tensor memory, online softmax)
-    and the backward's S, dP, P, dS come from one kernel launch per sequence and head group that writes only the FP16
-    parts of P and dS (flash = 2: one such launch for the whole call, an option that is measured slower at full size);
-    flash = 0: a launch per product over a score scratch.  Both against the oracle, and bit-reproducible."""
+    """Head size 128, default GEMM mode.  flash = 1 (the default): the forward is one kernel (scores in tensor memory, online
+    softmax); the backward keeps dK and dV on chip in one launch over all sequences and K/V heads (P^T and dS^T go back into
+    tensor memory as the A operand of the dV and dK products) and leaves only the parts of dS^T for the dQ product.
+    flash = 2: the older backward, S, dP, P, dS from one kernel launch per sequence and head group that writes the FP16 parts
+    of P and dS for three long products (flash = 3: one such launch for the whole call); flash = 0: a launch per product over
+    a score scratch.  All against the oracle, and bit-reproducible."""
     hd = 128
     ss = np.array(ss, np.uint32)
     T, B = int(ss[-1]), len(ss) - 1
@@ -211,8 +213,8 @@ def test_attention_head128_one_kernel_paths(ctx, ss, Hq, Hkv, flash):
     dQ_ref, dK_ref, dV_ref = np.empty_like(Q), np.zeros_like(K), np.zeros_like(V)
     O.lib().ref_attention_backward(Q, K, V, dO, dQ_ref, dK_ref, dV_ref, ss, T, B, Hq, Hkv, hd)
     bq, bk, bv, bdo, bs = ctx.upload(Q), ctx.upload(K), ctx.upload(V), ctx.upload(dO), ctx.upload(ss)
-    ctx.set_attn_flash(1 if flash else 0)
-    if flash == 2:                                    # backward scores: one launch per call instead of one per sequence and head group
+    ctx.set_attn_flash({1: 1, 2: 2, 3: 2, 0: 0}[flash])
+    if flash == 3:                                    # backward scores: one launch per call instead of one per sequence and head group
         os.environ["SERAPH_B200_ATTN_ALL_SCORES_MB"] = "4096"
     runs = []
     for rep in range(2):

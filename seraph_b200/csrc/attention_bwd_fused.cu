@@ -24,8 +24,8 @@
 // GEMM kernel (M = queries, K = keys up to the diagonal, A read MN-major).  P never reaches memory, dS is written once
 // and read once: 8 bytes per score element instead of the 20 of the score-materialising path.
 //
-// Warps (16): 0 TMA producer, 1 MMA issuer (owns the tensor-memory allocation), 4-7 elementwise for even steps, 8-11 for
-// odd steps, 12-15 drain.  Every mbarrier wait is bounded; a wait that runs out sets the status word and the CTA drains
+// Warps (16): 0 TMA producer, 1 MMA issuer (owns the tensor-memory allocation), 4-11 elementwise (a lane quarter and half of
+// a step's queries each), 12-15 drain.  Every mbarrier wait is bounded; a wait that runs out sets the status word and the CTA drains
 // and frees its tensor memory.
 #include "attention_fused.cuh"
 
@@ -40,8 +40,9 @@
 #define AB_STAGE_BYTES 32768      // Q parts 16 KB, dO parts 16 KB
 #define AB_OFF_BAR (AB_OFF_ST + AB_STAGES * AB_STAGE_BYTES)
 #define AB_SMEM (AB_OFF_BAR + 1024 + 1024)
-#define AB_REGS_LIGHT 72
-#define AB_REGS_EW 168
+#define AB_REGS_LIGHT 72          // producer / MMA issuer warpgroup
+#define AB_REGS_EW 120             // the two elementwise warpgroups
+#define AB_REGS_DRAIN 200          // the drain warpgroup holds 128 accumulator values at a time   (128*72 + 256*120 + 128*200 = 65536)
 // tensor-memory columns: dK 0..127, dV 128..255, then per buffer e: S^T at 256 + 64 e (32 columns, one per query), dP^T 32 further.
 // The FP16 parts of P^T and dS^T replace them in place: for each k-step of 16 queries, 8 columns of hi parts then 8 of lo parts.
 #define AB_COL_DK 0
@@ -115,7 +116,7 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
     if (threadIdx.x == 0) {
         mbar_init(kv_full, 1); mbar_init(acc_ready, 1); mbar_init(acc_free, 4);
         for (int i = 0; i < AB_STAGES; i++) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-        for (int i = 0; i < 2; i++) { mbar_init(&sdp_full[i], 1); mbar_init(&p_full[i], 4); }
+        for (int i = 0; i < 2; i++) { mbar_init(&sdp_full[i], 1); mbar_init(&p_full[i], 8); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -128,7 +129,7 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
 
-    if (warp < 4 || warp >= 12) {
+    if (warp < 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(AB_REGS_LIGHT));
         if (warp == 0) {
             // ---------------- TMA producer ----------------
@@ -222,8 +223,11 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
                 }
                 if (!ok) atomicExch(status, SB_ERR_TIMEOUT);
             }
-        } else if (warp >= 12) {
-            // ---------------- drain: dK and dV chains out of tensor memory, added into the output ----------------
+        }
+    } else if (warp >= 12) {
+        // ---------------- drain: dK and dV chains out of tensor memory, added into the output ----------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(AB_REGS_DRAIN));
+        {
             const int q = warp & 3, r = q * 32 + lane, kg = k0 + r;
             const bool live = kg < S;
             // dV accumulates (P 2^14) (dO 2^s_do), dK accumulates (dS 2^s_ds) (Q 2^s_q)
@@ -231,103 +235,103 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
             const float fk = tc_pow2(-tc_f16_shift(__ldg(ds_bound))) * tc_pow2(-tc_f16_shift(__ldg(amax_q)));
             float* rowk = dK + (size_t)(t0 + (live ? kg : 0)) * kvd + (size_t)kvh * AF_HD;
             float* rowv = dV + (size_t)(t0 + (live ? kg : 0)) * kvd + (size_t)kvh * AF_HD;
+            const uint32_t ta = tmem_base + ((uint32_t)(q * 32) << 16);
             for (int c = 0; c < nchains && ok; c++) {
                 ok = mbar_wait(acc_ready, c & 1);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t ta = tmem_base + ((uint32_t)(q * 32) << 16);
-#pragma unroll 1
-                for (int piece = 0; piece < 8; piece++) {          // 4 x 32 columns of dK, then of dV
-                    uint32_t v[32];
-                    af_ld32_issue(ta + (uint32_t)(piece * 32), v);
-                    af_ld_wait(v);
-                    if (piece == 7) {                               // everything is in registers: the next chain may overwrite the accumulators
+#pragma unroll
+                for (int which = 0; which < 2; which++) {          // dK (columns 0..127), then dV (128..255): four loads in flight, one wait
+                    uint32_t v0[32], v1[32], v2[32], v3[32];
+                    af_ld32_issue(ta + (uint32_t)(which * 128), v0);
+                    af_ld32_issue(ta + (uint32_t)(which * 128 + 32), v1);
+                    af_ld32_issue(ta + (uint32_t)(which * 128 + 64), v2);
+                    af_ld32_issue(ta + (uint32_t)(which * 128 + 96), v3);
+                    af_ld_wait(v0); af_ld_dep(v1); af_ld_dep(v2); af_ld_dep(v3);
+                    if (which == 1) {                               // everything is in registers: the next chain may overwrite the accumulators
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) af_arrive(acc_free);
                     }
                     if (live) {
-                        const float f = piece < 4 ? fk : fv;
-                        float* dst = (piece < 4 ? rowk : rowv) + (piece & 3) * 32;
+                        const float f = which ? fv : fk;
+                        float* dst = which ? rowv : rowk;
 #pragma unroll
-                        for (int i = 0; i < 8; i++)
-                            ab_red4(dst + 4 * i, __uint_as_float(v[4 * i]) * f, __uint_as_float(v[4 * i + 1]) * f,
-                                    __uint_as_float(v[4 * i + 2]) * f, __uint_as_float(v[4 * i + 3]) * f);
+                        for (int i = 0; i < 8; i++) {
+                            ab_red4(dst + 4 * i, __uint_as_float(v0[4 * i]) * f, __uint_as_float(v0[4 * i + 1]) * f, __uint_as_float(v0[4 * i + 2]) * f, __uint_as_float(v0[4 * i + 3]) * f);
+                            ab_red4(dst + 32 + 4 * i, __uint_as_float(v1[4 * i]) * f, __uint_as_float(v1[4 * i + 1]) * f, __uint_as_float(v1[4 * i + 2]) * f, __uint_as_float(v1[4 * i + 3]) * f);
+                            ab_red4(dst + 64 + 4 * i, __uint_as_float(v2[4 * i]) * f, __uint_as_float(v2[4 * i + 1]) * f, __uint_as_float(v2[4 * i + 2]) * f, __uint_as_float(v2[4 * i + 3]) * f);
+                            ab_red4(dst + 96 + 4 * i, __uint_as_float(v3[4 * i]) * f, __uint_as_float(v3[4 * i + 1]) * f, __uint_as_float(v3[4 * i + 2]) * f, __uint_as_float(v3[4 * i + 3]) * f);
+                        }
                     }
                 }
             }
             if (!ok && lane == 0) atomicExch(status, SB_ERR_TIMEOUT);
         }
     } else {
-        // ---------------- elementwise: one key row per thread; warps 4-7 take the even steps, 8-11 the odd ones ----------------
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(AB_REGS_EW));
-        const int e = (warp - 4) >> 2, q = warp & 3, r = q * 32 + lane, kg = k0 + r;
+        // ---------------- elementwise: one key row and 16 of the step's 32 queries per thread (warps 4-7: queries 0..15, 8-11: 16..31) ----------------
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(AB_REGS_EW));
+        const int ch = (warp - 4) >> 2, q = warp & 3, r = q * 32 + lane, kg = k0 + r;
         const float cs = tc_pow2(-tc_f16_shift(__ldg(amax_q))) * tc_pow2(-tc_f16_shift(__ldg(amax_k))) * (scale * 1.4426950408889634f);
         const float cp = tc_pow2(-tc_f16_shift(__ldg(amax_do))) * tc_pow2(-tc_f16_shift(__ldg(amax_v)));
         const float dsc = tc_pow2(tc_f16_shift(__ldg(ds_bound))) * scale * (1.0f / 16384.f);      // p holds P * 2^14
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
         // Columns before this key block that the dQ product reads together with it (its query tiles are 256 wide): zeros
-        if (e == 0 && (k0 & 255) != 0) {
+        if ((k0 & 255) != 0) {
             for (int hi = 0; hi < g; hi++) {
-                const int h = kvh * g + hi;
                 const size_t hb = (size_t)(b * g + hi) * Hkv + kvh;
-                uint4* z1 = (uint4*)(dS1 + (hb * Sp + (size_t)kg) * Sp + (k0 - 128));
-                uint4* z2 = (uint4*)(dS2 + (hb * Sp + (size_t)kg) * Sp + (k0 - 128));
+                uint4* z = (uint4*)((ch ? dS2 : dS1) + (hb * Sp + (size_t)kg) * Sp + (k0 - 128));
 #pragma unroll
-                for (int i = 0; i < 16; i++) { z1[i] = make_uint4(0, 0, 0, 0); z2[i] = make_uint4(0, 0, 0, 0); }
-                (void)h;
+                for (int i = 0; i < 16; i++) z[i] = make_uint4(0, 0, 0, 0);
             }
         }
-        for (int t = e; t < nsteps && ok; t += 2) {
-            const int hi = t / per_head, j = j0 + t % per_head;
+        for (int t = 0; t < nsteps && ok; t++) {
+            const int e = t & 1, hi = t / per_head, j = j0 + t % per_head;
             const int h = kvh * g + hi, q0 = j * AB_BQ;
-            // this lane's query of the block: log-sum-exp (in powers of two) and D; handed round the warp by shuffles
-            const int ql = q0 + lane;
+            // this lane's query of the step (lanes 0..15 of the warp matter): log-sum-exp in powers of two, and D; handed round by shuffles
+            const int ql = q0 + ch * 16 + (lane & 15);
             const float myL2 = ql < S ? __ldg(&lse[(size_t)(t0 + ql) * Hq + h]) * 1.4426950408889634f : 0.f;
             const float myD = ql < S ? __ldg(&D[(size_t)(t0 + ql) * Hq + h]) : 0.f;
             ok = mbar_wait(&sdp_full[e], (t >> 1) & 1);
             if (!ok) break;
             tc_fence_after();
             const size_t hb = (size_t)(b * g + hi) * Hkv + kvh;
-            __half* o1 = dS1 + (hb * Sp + (size_t)kg) * Sp + q0;
-            __half* o2 = dS2 + (hb * Sp + (size_t)kg) * Sp + q0;
+            __half* o1 = dS1 + (hb * Sp + (size_t)kg) * Sp + q0 + ch * 16;
+            __half* o2 = dS2 + (hb * Sp + (size_t)kg) * Sp + q0 + ch * 16;
+            uint32_t sr[16], dr[16];
+            ab_ld16(tmem_base + lane_addr + (uint32_t)(AB_COL_S(e) + ch * 16), sr);
+            ab_ld16(tmem_base + lane_addr + (uint32_t)(AB_COL_DP(e) + ch * 16), dr);
+            ab_ld_wait2(sr, dr);
+            uint32_t p1[8], p2[8], d1[8], d2[8];
 #pragma unroll
-            for (int half = 0; half < 2; half++) {                      // 16 queries at a time: one k-step of the dV and dK products
-                uint32_t sr[16], dr[16];
-                ab_ld16(tmem_base + lane_addr + (uint32_t)(AB_COL_S(e) + half * 16), sr);
-                ab_ld16(tmem_base + lane_addr + (uint32_t)(AB_COL_DP(e) + half * 16), dr);
-                ab_ld_wait2(sr, dr);
-                uint32_t p1[8], p2[8], d1[8], d2[8];
+            for (int i = 0; i < 8; i++) {
+                float pv[2], dv[2];
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    float pv[2], dv[2];
-#pragma unroll
-                    for (int w = 0; w < 2; w++) {
-                        const int c = half * 16 + 2 * i + w;
-                        const float L2 = __shfl_sync(0xffffffffu, myL2, c), Dq = __shfl_sync(0xffffffffu, myD, c);
-                        const int qi = q0 + c;
-                        const bool valid = kg <= qi && qi < S && kg < S;
-                        const float y = fmaf(__uint_as_float(sr[2 * i + w]), cs, 14.f - L2);
-                        pv[w] = valid ? af_ex2(y) : 0.f;                                             // P * 2^14
-                        dv[w] = pv[w] * (__uint_as_float(dr[2 * i + w]) * cp - Dq) * dsc;
-                    }
-                    af_split2(pv[0], pv[1], p1[i], p2[i]);
-                    af_split2(dv[0], dv[1], d1[i], d2[i]);
+                for (int w = 0; w < 2; w++) {
+                    const int c = 2 * i + w;
+                    const float L2 = __shfl_sync(0xffffffffu, myL2, c), Dq = __shfl_sync(0xffffffffu, myD, c);
+                    const int qi = q0 + ch * 16 + c;
+                    const bool valid = kg <= qi && qi < S && kg < S;
+                    const float y = fmaf(__uint_as_float(sr[c]), cs, 14.f - L2);
+                    pv[w] = valid ? af_ex2(y) : 0.f;                                             // P * 2^14
+                    dv[w] = pv[w] * (__uint_as_float(dr[c]) * cp - Dq) * dsc;
                 }
-                // The parts of these 16 queries go back over the 16 columns their scores came from (all of them are in registers by
-                // now): hi part in the first 8 columns, lo part in the next 8, which is where the MMA issuer looks for k-step `half`.
-                ab_st8(tmem_base + lane_addr + (uint32_t)(AB_COL_S(e) + half * 16), p1);
-                ab_st8(tmem_base + lane_addr + (uint32_t)(AB_COL_S(e) + half * 16 + 8), p2);
-                ab_st8(tmem_base + lane_addr + (uint32_t)(AB_COL_DP(e) + half * 16), d1);
-                ab_st8(tmem_base + lane_addr + (uint32_t)(AB_COL_DP(e) + half * 16 + 8), d2);
-                // dS^T parts of this key row to memory: 16 queries = 32 bytes per part
-                *(uint4*)(o1 + half * 16) = make_uint4(d1[0], d1[1], d1[2], d1[3]); *(uint4*)(o1 + half * 16 + 8) = make_uint4(d1[4], d1[5], d1[6], d1[7]);
-                *(uint4*)(o2 + half * 16) = make_uint4(d2[0], d2[1], d2[2], d2[3]); *(uint4*)(o2 + half * 16 + 8) = make_uint4(d2[4], d2[5], d2[6], d2[7]);
+                af_split2(pv[0], pv[1], p1[i], p2[i]);
+                af_split2(dv[0], dv[1], d1[i], d2[i]);
             }
+            // The parts of these 16 queries go back over the 16 columns their scores came from (all of them are in registers by now):
+            // hi part in the first 8 columns, lo part in the next 8, which is where the MMA issuer looks for k-step `ch`.
+            ab_st8(tmem_base + lane_addr + (uint32_t)(AB_COL_S(e) + ch * 16), p1);
+            ab_st8(tmem_base + lane_addr + (uint32_t)(AB_COL_S(e) + ch * 16 + 8), p2);
+            ab_st8(tmem_base + lane_addr + (uint32_t)(AB_COL_DP(e) + ch * 16), d1);
+            ab_st8(tmem_base + lane_addr + (uint32_t)(AB_COL_DP(e) + ch * 16 + 8), d2);
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             tc_fence_before();
             __syncwarp();
             if (lane == 0) af_arrive(&p_full[e]);
+            // dS^T parts of this key row to memory: 16 queries = 32 bytes per part
+            *(uint4*)(o1) = make_uint4(d1[0], d1[1], d1[2], d1[3]); *(uint4*)(o1 + 8) = make_uint4(d1[4], d1[5], d1[6], d1[7]);
+            *(uint4*)(o2) = make_uint4(d2[0], d2[1], d2[2], d2[3]); *(uint4*)(o2 + 8) = make_uint4(d2[4], d2[5], d2[6], d2[7]);
         }
         if (!ok && lane == 0) atomicExch(status, SB_ERR_TIMEOUT);
     }

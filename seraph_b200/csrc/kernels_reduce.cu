@@ -275,6 +275,54 @@ __global__ void __launch_bounds__(RB_THREADS, 2) rmsnorm_bwd_rows_kernel(const f
     sb_block_amax(am, amax_dx);
 }
 
+// RMSNorm backward for rows of exactly 128 columns (the learned per-head norm of q and k: rows = tokens x heads): one warp per
+// row, a float4 per lane, four rows in flight per warp; no CTA-wide reduction per row.  A lane's dscale partial stays in a
+// float4 over all rows its warp visits; the warps of a CTA add theirs in warp order into one partial row per CTA.
+__global__ void __launch_bounds__(RB_THREADS, 4) rmsnorm_bwd_w128_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                                         const float* __restrict__ dy, const float* resid, float* dx,
+                                                                         float* __restrict__ partial, int rows, float eps, unsigned* amax_dx) {
+    __shared__ float4 s_acc[RB_THREADS / 32][32];
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, nw = (gridDim.x * RB_THREADS) >> 5;
+    const float4 sc = ((const float4*)w)[lane];
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float am = 0.f;
+    for (int r0 = (blockIdx.x * (RB_THREADS / 32) + wib) * 4; r0 < rows; r0 += nw * 4) {
+        float4 v[4], g[4], q[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const bool in = r0 + i < rows;
+            const size_t o = (size_t)(r0 + i) * 32 + lane;
+            v[i] = in ? ((const float4*)x)[o] : make_float4(0.f, 0.f, 0.f, 0.f);
+            g[i] = in ? ((const float4*)dy)[o] : make_float4(0.f, 0.f, 0.f, 0.f);
+            q[i] = (in && resid) ? ((const float4*)resid)[o] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if (r0 + i >= rows) break;
+            float ss = v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+            float cp = g[i].x * sc.x * v[i].x + g[i].y * sc.y * v[i].y + g[i].z * sc.z * v[i].z + g[i].w * sc.w * v[i].w;
+            ss = warp_sum(ss); cp = warp_sum(cp);
+            const float inv = 1.0f / sqrtf(ss / 128.f + eps);
+            const float k = inv * inv * inv / 128.f * cp;
+            acc.x += g[i].x * v[i].x * inv; acc.y += g[i].y * v[i].y * inv; acc.z += g[i].z * v[i].z * inv; acc.w += g[i].w * v[i].w * inv;
+            float4 o;
+            o.x = g[i].x * sc.x * inv - v[i].x * k + q[i].x; o.y = g[i].y * sc.y * inv - v[i].y * k + q[i].y;
+            o.z = g[i].z * sc.z * inv - v[i].z * k + q[i].z; o.w = g[i].w * sc.w * inv - v[i].w * k + q[i].w;
+            ((float4*)dx)[(size_t)(r0 + i) * 32 + lane] = o;
+            am = sb_amax4(am, o);
+        }
+    }
+    s_acc[wib][lane] = acc;
+    __syncthreads();
+    if (wib == 0) {
+        float4 t = s_acc[0][lane];
+#pragma unroll
+        for (int k = 1; k < RB_THREADS / 32; k++) { const float4 u = s_acc[k][lane]; t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w; }
+        ((float4*)(partial + (size_t)blockIdx.x * 128))[lane] = t;
+    }
+    sb_block_amax(am, amax_dx);
+}
+
 // dscale[c] += sum over partial rows of partial[b][c], in a fixed order: 32 columns per CTA, the rows dealt to
 // 32 row groups (group g takes rows g, g+32, ...; ten independent loads are in flight per thread), the 32 group
 // sums then added in group order.
@@ -665,6 +713,20 @@ void sb_rmsnorm_backward(sb_ctx_t* c, const float* x, const float* w, const floa
     if (rows <= 0 || cols <= 0) return;
     if (cols > RB_THREADS * 4 * RN_MAX_SWEEP || (cols % 4 != 0 && cols > RB_THREADS * RN_MAX_SWEEP * 4)) { sb_set_status(c, SB_ERR_SIZE); return; }
     int vec = (cols % 4 == 0) && aligned16(x) && aligned16(w) && aligned16(dy) && aligned16(dx_out) && (!resid || aligned16(resid));
+    if (vec && cols == 128 && rows >= 1024) {
+        // many short rows (the per-head norm): a warp per row
+        int wgrid = (rows + 31) / 32; if (wgrid > 4 * sm_count(c)) wgrid = 4 * sm_count(c);
+        float* partial = (float*)sb_scratch(c, (size_t)wgrid * cols * sizeof(float));
+        if (!partial) return;
+        cudaStream_t st = (cudaStream_t)c->pub.stream;
+        int tk = sb_tick_begin(c, SB_CLS_NORM_BWD);
+        unsigned* am = sb_amax_take(c, dx_out, (size_t)rows * cols);
+        rmsnorm_bwd_w128_kernel<<<wgrid, RB_THREADS, 0, st>>>(x, w, dy, resid, dx_out, partial, rows, eps, am);
+        colsum_partials_kernel<<<(cols + 31) / 32, 32 * CS_GROUPS, 0, st>>>(partial, dscale, wgrid, cols);
+        sb_tick_end(c, tk, 0.0, (resid ? 16.0 : 12.0) * rows * cols);
+        c->launches += 2;
+        return;
+    }
     if (vec && cols <= 2048 && rows >= 64) {
         // row groups with the next group's loads in flight, two CTAs per SM; one dscale partial per CTA, summed in CTA order
         int wgrid = (rows + RNB_ROWS - 1) / RNB_ROWS; if (wgrid > 2 * sm_count(c)) wgrid = 2 * sm_count(c);

@@ -109,6 +109,12 @@ typedef struct sb_ctx {
     int lora_rank, lora_mask; float lora_alpha;
     size_t n_lora;
     float *LW, *LG, *LM, *LV;
+    /* The rank-r products are far too thin for the tensor-core kernel's 256-wide tiles (and ran 40 times slower on the CUDA-core
+       GEMM), so the step works on copies of A and B whose rank is padded with zero rows / columns to lora_R, a multiple of 256:
+       LWp [per adapter: A (R, in) then B (out, R)] is refreshed from LW before a step when the adapters changed, the gradient
+       products accumulate into LGp and the live part is copied to LG layer by layer.  Padding changes no value: the extra rows of
+       A and columns of B are zero, so the extra columns of X A^T are zero and the extra gradient rows / columns are never read. */
+    int lora_R; size_t n_lora_pad; float *LWp, *LGp; int lora_pad_stale;
     float* lora_tmp; size_t lora_tmp_cap;
 
     /* activations */

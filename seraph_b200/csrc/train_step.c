@@ -76,6 +76,18 @@ static size_t lora_off(const sb_ctx_t* c, int l, int a) {
     return n;
 }
 
+/* the same for the rank-padded working copies */
+static size_t lora_layer_params_pad(const sb_ctx_t* c) {
+    size_t n = 0;
+    for (int a = 0; a < 7; a++) if (c->lora_mask & (1 << a)) { int in, out; lora_dims(c, a, &in, &out); n += (size_t)c->lora_R * in + (size_t)out * c->lora_R; }
+    return n;
+}
+static size_t lora_off_pad(const sb_ctx_t* c, int l, int a) {
+    size_t n = lora_layer_params_pad(c) * (size_t)l;
+    for (int b = 0; b < a; b++) if (c->lora_mask & (1 << b)) { int in, out; lora_dims(c, b, &in, &out); n += (size_t)c->lora_R * in + (size_t)out * c->lora_R; }
+    return n;
+}
+
 static cudaStream_t S(sb_ctx_t* c) { return (cudaStream_t)c->pub.stream; }
 
 static cuda_buffer_t* view(float* p, size_t floats) {
@@ -373,7 +385,9 @@ static void free_lora(sb_ctx_t* c) {
     if (c->LM) cudaFree(c->LM);
     if (c->LV) cudaFree(c->LV);
     if (c->lora_tmp) cudaFree(c->lora_tmp);
-    c->LW = c->LG = c->LM = c->LV = c->lora_tmp = NULL; c->lora_tmp_cap = 0;
+    if (c->LWp) cudaFree(c->LWp);
+    if (c->LGp) cudaFree(c->LGp);
+    c->LW = c->LG = c->LM = c->LV = c->lora_tmp = c->LWp = c->LGp = NULL; c->lora_tmp_cap = 0; c->n_lora_pad = 0; c->lora_R = 0;
     cuda_lora_gpu_state_t* s = (cuda_lora_gpu_state_t*)c->pub.lora_gpu;
     if (s) {
         for (int a = 0; a < 7; a++) {
@@ -404,7 +418,13 @@ static int ensure_lora(sb_ctx_t* c, const lora_model_t* m) {
     cudaStreamSynchronize(S(c));
     free_lora(c);
     c->lora_rank = m->rank; c->lora_mask = mask; c->lora_alpha = m->alpha;
+    c->lora_R = (m->rank + 255) / 256 * 256;
     c->n_lora = lora_layer_params(c) * (size_t)c->L;
+    c->n_lora_pad = lora_layer_params_pad(c) * (size_t)c->L;
+    if (sb_check(c, cudaMalloc((void**)&c->LWp, c->n_lora_pad * sizeof(float)), "lora padded weights") ||
+        sb_check(c, cudaMalloc((void**)&c->LGp, c->n_lora_pad * sizeof(float)), "lora padded grads")) { c->status = SB_ERR_OOM; return 1; }
+    cudaMemsetAsync(c->LWp, 0, c->n_lora_pad * sizeof(float), S(c)); cudaMemsetAsync(c->LGp, 0, c->n_lora_pad * sizeof(float), S(c));
+    c->lora_pad_stale = 1;
     size_t bytes = c->n_lora * sizeof(float);
     if (sb_check(c, cudaMalloc((void**)&c->LW, bytes), "lora weights") || sb_check(c, cudaMalloc((void**)&c->LG, bytes), "lora grads") ||
         sb_check(c, cudaMalloc((void**)&c->LM, bytes), "lora m") || sb_check(c, cudaMalloc((void**)&c->LV, bytes), "lora v")) {
@@ -514,12 +534,40 @@ static int ensure_pinned(sb_ctx_t* c, size_t bytes) {
 /* the step                                                                  */
 /* ------------------------------------------------------------------------ */
 typedef struct { const float *A, *B; float *gA, *gB; int in, out; } lora_ref_t;
+/* the rank-padded working copies of adapter a of layer l */
 static int lora_get(sb_ctx_t* c, int l, int a, lora_ref_t* r) {
     if (!c->LW || !(c->lora_mask & (1 << a))) return 0;
     lora_dims(c, a, &r->in, &r->out);
-    size_t o = lora_off(c, l, a), nA = (size_t)c->lora_rank * r->in;
-    r->A = c->LW + o; r->B = c->LW + o + nA; r->gA = c->LG + o; r->gB = c->LG + o + nA;
+    size_t o = lora_off_pad(c, l, a), nA = (size_t)c->lora_R * r->in;
+    r->A = c->LWp + o; r->B = c->LWp + o + nA; r->gA = c->LGp + o; r->gB = c->LGp + o + nA;
     return 1;
+}
+/* LWp <- LW (all layers) when the adapters changed: A's r rows are the head of the padded block, B's r columns a strided copy */
+static void lora_refresh_padded(sb_ctx_t* c) {
+    if (!c->lora_pad_stale || !c->LWp) return;
+    const int r = c->lora_rank, R = c->lora_R;
+    for (int l = 0; l < c->L; l++)
+        for (int a = 0; a < 7; a++) {
+            if (!(c->lora_mask & (1 << a))) continue;
+            int in, out; lora_dims(c, a, &in, &out);
+            const size_t o = lora_off(c, l, a), op = lora_off_pad(c, l, a);
+            cudaMemcpyAsync(c->LWp + op, c->LW + o, (size_t)r * in * 4, cudaMemcpyDeviceToDevice, S(c));
+            cudaMemcpy2DAsync(c->LWp + op + (size_t)R * in, (size_t)R * 4, c->LW + o + (size_t)r * in, (size_t)r * 4, (size_t)r * 4, (size_t)out,
+                              cudaMemcpyDeviceToDevice, S(c));
+        }
+    c->lora_pad_stale = 0;
+}
+/* LG <- live part of LGp for layer l (the running total of this accumulation cycle) */
+static void lora_compact_grads(sb_ctx_t* c, int l) {
+    const int r = c->lora_rank, R = c->lora_R;
+    for (int a = 0; a < 7; a++) {
+        if (!(c->lora_mask & (1 << a))) continue;
+        int in, out; lora_dims(c, a, &in, &out);
+        const size_t o = lora_off(c, l, a), op = lora_off_pad(c, l, a);
+        cudaMemcpyAsync(c->LG + o, c->LGp + op, (size_t)r * in * 4, cudaMemcpyDeviceToDevice, S(c));
+        cudaMemcpy2DAsync(c->LG + o + (size_t)r * in, (size_t)r * 4, c->LGp + op + (size_t)R * in, (size_t)R * 4, (size_t)r * 4, (size_t)out,
+                          cudaMemcpyDeviceToDevice, S(c));
+    }
 }
 
 /* Y[T,out] (+)= X[T,in] W[out,in]^T, plus the adapter's (s X A^T) B^T when one is active */
@@ -528,9 +576,9 @@ static void linear_fwd(sb_ctx_t* c, int use_lora, int l, int a, const float* X, 
     lora_ref_t r;
     if (use_lora && lora_get(c, l, a, &r)) {
         float s = c->lora_alpha / (float)c->lora_rank;
-        sb_gemm(c, X, r.A, c->lora_tmp, T, c->lora_rank, in, 0, 1, 0);
-        sb_scale(c, c->lora_tmp, (size_t)T * c->lora_rank, s);
-        sb_gemm(c, c->lora_tmp, r.B, Y, T, out, c->lora_rank, 0, 1, 1);
+        sb_gemm(c, X, r.A, c->lora_tmp, T, c->lora_R, in, 0, 1, 0);
+        sb_scale(c, c->lora_tmp, (size_t)T * c->lora_R, s);
+        sb_gemm(c, c->lora_tmp, r.B, Y, T, out, c->lora_R, 0, 1, 1);
     }
 }
 /* adapter gradients for one projection; in exact mode also dX += (s dY B) A */
@@ -538,8 +586,8 @@ static void lora_bwd(sb_ctx_t* c, int l, int a, const float* dY, const float* X,
     lora_ref_t r;
     if (!lora_get(c, l, a, &r)) return;
     float s = c->lora_alpha / (float)c->lora_rank;
-    sb_lora_backward(c, dY, X, r.A, r.B, r.gA, r.gB, c->lora_tmp, T, r.in, r.out, c->lora_rank, s);
-    if (c->lora_exact && dX) sb_gemm(c, c->lora_tmp, r.A, dX, T, r.in, c->lora_rank, 0, 0, 1);
+    sb_lora_backward(c, dY, X, r.A, r.B, r.gA, r.gB, c->lora_tmp, T, r.in, r.out, c->lora_R, s);
+    if (c->lora_exact && dX) sb_gemm(c, c->lora_tmp, r.A, dX, T, r.in, c->lora_R, 0, 0, 1);
 }
 
 /* NaN/Inf flags of a training step with state->debug_nan_check set, indexed as the reference indexes them
@@ -731,6 +779,7 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
         sb_amax_announce(c, gh, (size_t)T * d);
         sb_rmsnorm_backward(c, a->layer_in, c->W + o->in_norm, gx, gh, gh, full ? Gd + o->in_norm : norm_sink, T, d, RMS_EPS);
         nan_mark(c, gh, (size_t)T * d, nan_ghid_base(c) + (uint32_t)l);
+        if (!full && c->LW) lora_compact_grads(c, l);
         if (reduce) {
             if (full) sb_dp_bucket_ready(c, Gd + o->q, o->post_norm + (size_t)d - o->q);
             else { size_t per = lora_layer_params(c); sb_dp_bucket_ready(c, c->LG + per * (size_t)l, per); }
@@ -795,13 +844,14 @@ static float step_body(train_state_t* st, int* tokens, int T, int* seq_starts, i
     if (use_lora && ensure_lora(c, st->lora)) return -1.0f;
     if (ensure_extras(c, full && train)) return -1.0f;
     if (ensure_activations(c, T, train)) return -1.0f;
-    if (use_lora && c->lora_tmp_cap < (size_t)T * c->lora_rank) {
+    if (use_lora && c->lora_tmp_cap < (size_t)T * c->lora_R) {
         cudaStreamSynchronize(S(c));
         if (c->lora_tmp) cudaFree(c->lora_tmp);
         c->lora_tmp = NULL;
-        if (sb_check(c, cudaMalloc((void**)&c->lora_tmp, (size_t)T * c->lora_rank * sizeof(float)), "lora tmp")) return -1.0f;
-        c->lora_tmp_cap = (size_t)T * c->lora_rank;
+        if (sb_check(c, cudaMalloc((void**)&c->lora_tmp, (size_t)T * c->lora_R * sizeof(float)), "lora tmp")) return -1.0f;
+        c->lora_tmp_cap = (size_t)T * c->lora_R;
     }
+    if (use_lora) lora_refresh_padded(c);
     float theta = st->config->rope_theta > 0 ? st->config->rope_theta : 10000.0f;
     int max_seq = 0;
     if (resident) {
@@ -817,7 +867,7 @@ static float step_body(train_state_t* st, int* tokens, int T, int* seq_starts, i
     if (nan_begin(c, train && st->debug_nan_check)) return -1.0f;
     if (train && st->accumulation_counter == 0) {
         if (full) sb_memset(c, c->G, 0, c->n_params * sizeof(float));
-        else sb_memset(c, c->LG, 0, c->n_lora * sizeof(float));
+        else { sb_memset(c, c->LG, 0, c->n_lora * sizeof(float)); sb_memset(c, c->LGp, 0, c->n_lora_pad * sizeof(float)); }
         if (full && c->XG) sb_memset(c, c->XG, 0, c->n_extras * sizeof(float));
     }
     forward_pass(c, T, max_seq, theta, use_lora);
@@ -860,6 +910,7 @@ static float step_body(train_state_t* st, int* tokens, int T, int* seq_starts, i
             }
             sb_adamw(c, w, g, m, v, n, lr, 0.9f, 0.999f, 0.01f, 1e-8f, st->optimizer_step, gscale, sumsq, c->grad_clip);
             if (extras) sb_adamw(c, c->XW, c->XG, c->XM, c->XV, c->n_extras, lr, 0.9f, 0.999f, 0.01f, 1e-8f, st->optimizer_step, gscale, sumsq, c->grad_clip);
+            if (!full) c->lora_pad_stale = 1;          /* the adapters moved: the padded copies follow before the next step */
             st->accumulation_counter = 0;
         }
     }
@@ -1022,6 +1073,7 @@ void cuda_train_zero_lora_grads(cuda_train_context_t* ctx) {
     sb_ctx_t* c = sb_priv(ctx);
     if (!c || !c->LG) return;
     sb_memset(c, c->LG, 0, c->n_lora * sizeof(float));
+    if (c->LGp) sb_memset(c, c->LGp, 0, c->n_lora_pad * sizeof(float));
 }
 
 /* Extension: repeat the full-weight step on the batch the previous step call left on the device.

@@ -66,7 +66,7 @@ def test_matmul_simt_mode_matches(ctx):
     ctx.release(a, b, c)
 
 
-@pytest.mark.parametrize("rows,cols", [(1, 32), (24, 64), (300, 512), (77, 2048), (5, 100)])
+@pytest.mark.parametrize("rows,cols", [(1, 32), (24, 64), (300, 512), (77, 2048), (5, 100), (4096, 128), (1501, 128)])
 def test_rmsnorm_forward_backward(ctx, rows, cols):
     r = rng(rows + cols)
     x, w, dy = f32(r.standard_normal((rows, cols))), f32(1 + 0.1 * r.standard_normal(cols)), f32(r.standard_normal((rows, cols)))

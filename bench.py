@@ -299,6 +299,8 @@ def run_attention(args, w):
     T = B * S
     ctx = api.Context(0)
     ctx.set_gemm_mode(args.gemm_mode)
+    if args.attn_flash is not None:
+        ctx.set_attn_flash(args.attn_flash)
     r = np.random.default_rng(2048)
     Q, K, V, dO = (np.ascontiguousarray(r.standard_normal((T, H * D)), np.float32) for _ in range(4))
     ss = np.arange(0, T + 1, S, dtype=np.uint32)
@@ -397,6 +399,8 @@ def run_ours(args):
         ref_cuda = reference_cuda_legs(local)        # before this library's arenas take the memory
     ctx = api.Context(local)
     ctx.set_gemm_mode(args.gemm_mode)
+    if args.attn_flash is not None:
+        ctx.set_attn_flash(args.attn_flash)
     dpc = None
     if world > 1:
         uid = np.zeros(128, np.uint8)
@@ -592,6 +596,7 @@ def main():
                          "use_qk_norm, 4 = attention-backward microbenchmark, 5 = LoRA rank 16 on the benchmark model, 6 = Mistral-7B-shaped LoRA slice)")
     ap.add_argument("--gemm-mode", type=int, default=4, help="4 FP32-accurate tensor cores, FP16 parts where possible (default), 0 FP32-accurate with TF32 parts, 1 TF32, 2 BF16, 3 CUDA cores")
     ap.add_argument("--attn-products", type=int, default=5, help="matrix products per key/query block the attention backward issues (for the issued-FLOPs figure)")
+    ap.add_argument("--attn-flash", type=int, default=None, help="attention path for 128-wide heads: 1 backward with dK/dV kept on chip, 2 score kernel + three products, 0 a launch per product (default: the library's)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU and reference-CUDA baseline legs")
     ap.add_argument("--short-warmup", action="store_true", help="honour --warmup below 3 (profiler captures only; not a valid bench number)")
     args = ap.parse_args()

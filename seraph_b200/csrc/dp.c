@@ -29,6 +29,7 @@ static struct {
     void* lib;
     ncclResult_t (*GetUniqueId)(ncclUniqueId*);
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int);
+    ncclResult_t (*CommInitRankConfig)(ncclComm_t*, int, ncclUniqueId, int, ncclConfig_t*);      /* optional */
     ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t);
     ncclResult_t (*CommDestroy)(ncclComm_t);
     ncclResult_t (*CommAbort)(ncclComm_t);
@@ -44,6 +45,7 @@ static int load_nccl(void) {
 #define SYM(f) do { *(void**)(&N.f) = dlsym(h, "nccl" #f); if (!N.f) { fprintf(stderr, "seraph_b200: NCCL lacks nccl" #f "\n"); dlclose(h); return 1; } } while (0)
     SYM(GetUniqueId); SYM(CommInitRank); SYM(AllReduce); SYM(CommDestroy); SYM(CommAbort); SYM(CommGetAsyncError); SYM(GetErrorString);
 #undef SYM
+    *(void**)(&N.CommInitRankConfig) = dlsym(h, "ncclCommInitRankConfig");
     N.lib = h;
     return 0;
 }
@@ -74,7 +76,19 @@ int seraph_dp_init(cuda_train_context_t* ctx, int rank, int world, const void* n
     if (cudaSetDevice(ctx->device_id) != cudaSuccess) return SB_ERR_CUDA;
     ncclUniqueId id; memcpy(&id, nccl_unique_id, sizeof id);
     ncclComm_t comm;
-    if (nccl_fail(c, N.CommInitRank(&comm, world, id, rank), "ncclCommInitRank")) return SB_ERR_NCCL;
+    /* The all-reduce kernels run beside the backward pass, whose GEMM launches are persistent grids of one CTA pair per SM pair:
+       every SM a collective takes makes a straggler pair.  The gradients of a whole step need well under a tenth of NVLink's
+       bandwidth to finish inside the backward pass, so the communicator is held to a few CTAs (SERAPH_B200_NCCL_MAX_CTAS,
+       default 8; 0 leaves NCCL's own choice). */
+    int max_ctas = 8;
+    { const char* e = getenv("SERAPH_B200_NCCL_MAX_CTAS"); if (e && e[0]) max_ctas = atoi(e); }
+    ncclResult_t ir;
+    if (N.CommInitRankConfig && max_ctas > 0) {
+        ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
+        cfg.minCTAs = 1; cfg.maxCTAs = max_ctas;
+        ir = N.CommInitRankConfig(&comm, world, id, rank, &cfg);
+    } else ir = N.CommInitRank(&comm, world, id, rank);
+    if (nccl_fail(c, ir, "ncclCommInitRank")) return SB_ERR_NCCL;
     cudaStream_t cs;
     if (cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking) != cudaSuccess) { N.CommAbort(comm); return SB_ERR_CUDA; }
     c->nccl_comm = comm; c->comm_stream = cs; c->dp_rank = rank; c->dp_world = world;
@@ -116,11 +130,20 @@ void seraph_dp_finalize(cuda_train_context_t* ctx) { sb_dp_finalize(sb_priv(ctx)
  * compute stream records an event, the communication stream waits for it. */
 int sb_dp_bucket_ready(sb_ctx_t* c, float* p, size_t n) {
     if (c->dp_world <= 1 || !n) return 0;
-    cudaEvent_t e = (cudaEvent_t)c->ev_bucket[c->n_buckets & 63];
+    cudaEvent_t e = (cudaEvent_t)c->ev_bucket[c->n_buckets % 62];      /* 62 and 63 are the join events */
     c->n_buckets++;
     if (sb_check(c, cudaEventRecord(e, (cudaStream_t)c->pub.stream), "bucket event")) return 1;
     if (sb_check(c, cudaStreamWaitEvent((cudaStream_t)c->comm_stream, e, 0), "bucket wait")) return 1;
     return nccl_fail(c, N.AllReduce(p, p, n, ncclFloat32, ncclSum, (ncclComm_t)c->nccl_comm, (cudaStream_t)c->comm_stream), "ncclAllReduce");
+}
+
+/* compute stream waits until the buckets handed over so far are reduced; unlike sb_dp_join, more may follow (the step uses it to
+ * start AdamW on the layers while the last bucket, embedding and final norm, is still being reduced) */
+int sb_dp_join_partial(sb_ctx_t* c) {
+    if (c->dp_world <= 1) return 0;
+    cudaEvent_t e = (cudaEvent_t)c->ev_bucket[62];
+    if (sb_check(c, cudaEventRecord(e, (cudaStream_t)c->comm_stream), "partial join event")) return 1;
+    return sb_check(c, cudaStreamWaitEvent((cudaStream_t)c->pub.stream, e, 0), "partial join wait");
 }
 
 /* compute stream waits until every bucket handed over so far is reduced */

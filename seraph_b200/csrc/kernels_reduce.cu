@@ -6,6 +6,7 @@
 // cross_entropy_grad[_packed] :1566/:1657, reduce_sum :2209 (atomicAdd),
 // embedding_backward :2175 (atomicAdd, blockDim = hidden_size), adamw :2187.
 #include <cuda_runtime.h>
+#include <cuda_fp16.h>
 #include <math.h>
 #include <stdio.h>
 #include <stdint.h>
@@ -480,16 +481,23 @@ __global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(const float* 
                                                                    float* __restrict__ grad, float* __restrict__ loss_rows,
                                                                    const uint32_t* __restrict__ pos_ids, const uint32_t* __restrict__ seq_ids,
                                                                    const uint32_t* __restrict__ seq_starts,
-                                                                   int T, int V, float inv_valid, int vec, int* status, unsigned* amax_grad) {
+                                                                   int T, int V, float inv_valid, int vec, int* status, unsigned* amax_grad,
+                                                                   __half* __restrict__ g1, __half* __restrict__ g2, float part_scale, float* part_amax) {
+    // g1 != NULL (vec only): the gradient leaves as the two FP16 parts the LM-head backward products read, h1 = fp16(g * part_scale),
+    // h2 = fp16(g * part_scale - h1), laid out like grad; nothing is written to grad.  |g| <= inv_valid everywhere (softmax minus
+    // one-hot, over the number of predictions), so the parts' scale is known before a single logit is read: *part_amax = inv_valid.
     __shared__ float redm[32], reds[32];
     float am = 0.f;
     int r = blockIdx.x;
     if (r >= T) return;
+    if (g1 && r == 0 && threadIdx.x == 0) *part_amax = inv_valid;
     const float* lr = logits + (size_t)r * V; float* gr = grad + (size_t)r * V;
+    uint2* p1 = g1 ? (uint2*)(g1 + (size_t)r * V) : NULL; uint2* p2 = g1 ? (uint2*)(g2 + (size_t)r * V) : NULL;
     uint32_t s = seq_ids[r];
     int seq_len = (int)(seq_starts[s + 1] - seq_starts[s]);
     if ((int)pos_ids[r] >= seq_len - 1) {
-        if (vec) for (int i = threadIdx.x; i < V / 4; i += blockDim.x) ((float4*)gr)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (g1) for (int i = threadIdx.x; i < V / 4; i += blockDim.x) { p1[i] = make_uint2(0u, 0u); p2[i] = make_uint2(0u, 0u); }
+        else if (vec) for (int i = threadIdx.x; i < V / 4; i += blockDim.x) ((float4*)gr)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         else     for (int i = threadIdx.x; i < V; i += blockDim.x) gr[i] = 0.f;
         if (threadIdx.x == 0) loss_rows[r] = 0.f;
         return;
@@ -523,8 +531,16 @@ __global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(const float* 
         uint32_t b = (uint32_t)i * 4;
         if (tg - b < 4u) { if (tg == b) g.x -= 1.f; else if (tg == b + 1) g.y -= 1.f; else if (tg == b + 2) g.z -= 1.f; else g.w -= 1.f; }
         g.x *= inv_valid; g.y *= inv_valid; g.z *= inv_valid; g.w *= inv_valid;
-        ((float4*)gr)[i] = g;
-        am = sb_amax4(am, g);
+        if (g1) {
+            const float q0 = g.x * part_scale, q1 = g.y * part_scale, q2 = g.z * part_scale, q3 = g.w * part_scale;
+            const __half2 ha = __floats2half2_rn(q0, q1), hb = __floats2half2_rn(q2, q3);
+            const float2 fa = __half22float2(ha), fb = __half22float2(hb);
+            const __half2 la = __floats2half2_rn(q0 - fa.x, q1 - fa.y), lb = __floats2half2_rn(q2 - fb.x, q3 - fb.y);
+            p1[i] = make_uint2(*(const uint32_t*)&ha, *(const uint32_t*)&hb); p2[i] = make_uint2(*(const uint32_t*)&la, *(const uint32_t*)&lb);
+        } else {
+            ((float4*)gr)[i] = g;
+            am = sb_amax4(am, g);
+        }
     } else for (int i = threadIdx.x; i < V; i += blockDim.x) {
         float g = expf(lr[i] - m) * inv;
         if ((uint32_t)i == tg) g -= 1.f;
@@ -801,9 +817,33 @@ void sb_cross_entropy(sb_ctx_t* c, const float* logits, const uint32_t* targets,
     int vec = (V % 4 == 0) && aligned16(logits) && aligned16(grad);
     int tk = sb_tick_begin(c, SB_CLS_CE);
     cross_entropy_kernel<<<T, CE_THREADS, 0, (cudaStream_t)c->pub.stream>>>(logits, targets, grad, loss_rows, pos_ids, seq_ids,
-                                                                          seq_starts, T, V, 1.0f / (float)num_valid, vec, c->d_status, sb_amax_take(c, grad, (size_t)T * V));
+                                                                          seq_starts, T, V, 1.0f / (float)num_valid, vec, c->d_status, sb_amax_take(c, grad, (size_t)T * V),
+                                                                          NULL, NULL, 0.f, NULL);
     sb_tick_end(c, tk, 0.0, 12.0 * T * V);
     c->launches++;
+}
+
+// The same, with the gradient written only as the FP16 parts of the registered tensor `grad` (its FP32 array is not touched): the
+// two LM-head backward products then find their operand prepared and no pass splits 4 T V bytes of gradient again.
+// Returns 1 when done, 0 when the parts of `grad` are not available (not registered, cache off, no memory): use sb_cross_entropy.
+static __device__ __host__ inline int ce_shift(float amax) {
+    int e; frexpf(amax, &e);                       // amax = f * 2^e, f in [0.5, 1): exponent of the leading bit is e - 1
+    return 14 - (e - 1);
+}
+int sb_cross_entropy_parts(sb_ctx_t* c, const float* logits, const uint32_t* targets, float* grad, float* loss_rows,
+                           const uint32_t* pos_ids, const uint32_t* seq_ids, const uint32_t* seq_starts, int T, int V, int num_valid) {
+    if (T <= 0 || V <= 0 || (V % 4) || !aligned16(logits) || num_valid <= 0) return 0;
+    void* h; float* amax; int fresh;
+    if (!sb_parts_find(c, grad, (size_t)T * V, &h, &amax, &fresh)) return 0;
+    const float inv_valid = 1.0f / (float)num_valid;
+    int sh = ce_shift(inv_valid); sh = sh < -100 ? -100 : (sh > 100 ? 100 : sh);      // the rule the products apply to *amax
+    const float sc = ldexpf(1.0f, sh);
+    int tk = sb_tick_begin(c, SB_CLS_CE);
+    cross_entropy_kernel<<<T, CE_THREADS, 0, (cudaStream_t)c->pub.stream>>>(logits, targets, grad, loss_rows, pos_ids, seq_ids, seq_starts, T, V,
+                                                                          inv_valid, 1, c->d_status, NULL, (__half*)h, (__half*)h + (size_t)T * V, sc, amax);
+    sb_tick_end(c, tk, 0.0, 12.0 * T * V);
+    c->launches++;
+    return 1;
 }
 
 static void sum_impl(sb_ctx_t* c, const float* in, float* out, size_t n, bool square) {

@@ -210,6 +210,8 @@ void sb_attention_backward(sb_ctx_t*, const float* Q, const float* K, const floa
 void sb_cross_entropy(sb_ctx_t*, const float* logits, const uint32_t* targets, float* grad, float* loss_rows,
                       const uint32_t* pos_ids, const uint32_t* seq_ids, const uint32_t* seq_starts,
                       int T, int V, int num_valid);
+int  sb_cross_entropy_parts(sb_ctx_t*, const float* logits, const uint32_t* targets, float* grad, float* loss_rows,
+                            const uint32_t* pos_ids, const uint32_t* seq_ids, const uint32_t* seq_starts, int T, int V, int num_valid);
 void sb_reduce_sum(sb_ctx_t*, const float* in, float* out, size_t n);          /* deterministic; out[0] = sum */
 void sb_embedding_backward(sb_ctx_t*, const uint32_t* tok, const float* g, float* dE, int T, int d, int V);
 void sb_adamw(sb_ctx_t*, float* w, const float* g, float* m, float* v, size_t n, float lr, float b1, float b2,

@@ -31,6 +31,7 @@
 int sb_ensure_tokens(sb_ctx_t* c, int T, int B);
 int sb_dp_bucket_ready(sb_ctx_t* c, float* p, size_t n);      /* dp.c: no-ops when not data parallel */
 int sb_dp_join(sb_ctx_t* c);
+int sb_dp_join_partial(sb_ctx_t* c);
 
 #define RMS_EPS 1e-5f   /* hard-coded in every training path of the reference (src/train_cuda.c:1984) */
 
@@ -516,6 +517,7 @@ static int ensure_activations(sb_ctx_t* c, int T, int need_logits_grad) {
         sb_parts_register(c, 1, a->v, (size_t)T * c->kvd);
     }
     sb_parts_register(c, 1, c->hidden_norm, (size_t)T * c->d);
+    sb_parts_register(c, 1, c->dlogits, (size_t)T * c->V);
     return 0;
 }
 
@@ -700,8 +702,11 @@ static void forward_pass(sb_ctx_t* c, int T, int max_seq, float theta, int use_l
     nan_mark(c, c->logits, (size_t)T * c->V, 1);
 }
 
+/* AdamW of the layer ranges, run from inside the backward pass of a data-parallel step (see there) */
+typedef struct { int on, done, step; float lr, gscale; } early_adamw_t;
+
 /* `reduce`: hand every finished gradient range to the data-parallel all-reduce as soon as it is complete */
-static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, int full, int reduce) {
+static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, int full, int reduce, early_adamw_t* early) {
     const int d = c->d, F = c->F, qd = c->qd, kvd = c->kvd, L = c->L, V = c->V;
     float* gh = c->g_hidden; float* gx = c->g_xnorm;
     float* Gd = full ? c->G : NULL;
@@ -783,6 +788,17 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
         if (reduce) {
             if (full) sb_dp_bucket_ready(c, Gd + o->q, o->post_norm + (size_t)d - o->q);
             else { size_t per = lora_layer_params(c); sb_dp_bucket_ready(c, c->LG + per * (size_t)l, per); }
+        }
+    }
+    if (full && reduce && early && early->on) {
+        /* every layer's gradients are with the all-reduce: AdamW of the layer ranges runs as soon as they are back, while the
+           embedding scatter below and the reduction of the last bucket (1.2 GB at the benchmark size) are still to come.  The
+           update is elementwise, so doing it in two launches changes no value. */
+        const size_t o0 = c->off[0].q;
+        if (sb_dp_join_partial(c) == 0) {
+            sb_adamw(c, c->W + o0, c->G + o0, c->M + o0, c->Vv + o0, c->n_params - o0, early->lr, 0.9f, 0.999f, 0.01f, 1e-8f, early->step,
+                     early->gscale, NULL, 0.f);
+            early->done = 1;
         }
     }
     if (full) {
@@ -871,14 +887,28 @@ static float step_body(train_state_t* st, int* tokens, int T, int* seq_starts, i
         if (full && c->XG) sb_memset(c, c->XG, 0, c->n_extras * sizeof(float));
     }
     forward_pass(c, T, max_seq, theta, use_lora);
-    if (train) sb_amax_announce(c, c->dlogits, (size_t)T * c->V);
-    sb_cross_entropy(c, c->logits, c->targets, c->dlogits, c->loss_rows, c->pos_ids, c->seq_ids, c->seq_starts, T, c->V, num_valid);
+    /* training: the gradient of the logits leaves the loss kernel as the FP16 parts the two LM-head backward products read (its
+       FP32 form is never written); evaluation, the NaN guard (which inspects the FP32 array) and contexts without the parts arena
+       take the plain kernel */
+    if (!(train && !c->nan_on && sb_cross_entropy_parts(c, c->logits, c->targets, c->dlogits, c->loss_rows, c->pos_ids, c->seq_ids, c->seq_starts,
+                                                          T, c->V, num_valid))) {
+        if (train) sb_amax_announce(c, c->dlogits, (size_t)T * c->V);
+        sb_cross_entropy(c, c->logits, c->targets, c->dlogits, c->loss_rows, c->pos_ids, c->seq_ids, c->seq_starts, T, c->V, num_valid);
+    }
     sb_reduce_sum(c, c->loss_rows, c->d_loss, (size_t)T);
 
     if (train) {
         int accum = st->gradient_accumulation_steps < 1 ? 1 : st->gradient_accumulation_steps;
         int last_micro = (st->accumulation_counter + 1 >= accum);
-        backward_pass(c, T, B, max_seq, theta, full, last_micro && c->dp_world > 1);
+        /* data parallel, last micro-batch, no clipping (its norm needs every gradient first): the optimizer's parameters are known
+           now, so the layer ranges can be updated while the last bucket is still being reduced */
+        early_adamw_t early = {0, 0, 0, 0.f, 0.f};
+        if (full && last_micro && c->dp_world > 1 && c->grad_clip <= 0.f && !c->nan_on) {
+            early.on = 1; early.step = st->optimizer_step + 1; early.gscale = 1.0f / (float)c->dp_world;
+            train_state_t tmp = *st; tmp.optimizer_step = early.step;
+            early.lr = lr_for_step(&tmp, accum);
+        }
+        backward_pass(c, T, B, max_seq, theta, full, last_micro && c->dp_world > 1, &early);
         if (c->nan_on) {
             /* the reference reads its flags back before the optimizer and skips it when one is set, leaving the counters alone
                (src/train_cuda.c:1086-1187).  Data parallel: the buckets are already in flight, so every rank first waits for them and
@@ -908,6 +938,7 @@ static float step_body(train_state_t* st, int* tokens, int T, int* seq_starts, i
                 sb_sumsq(c, g, n, c->d_gnorm); sumsq = c->d_gnorm;
                 if (extras) { sb_sumsq(c, c->XG, c->n_extras, c->d_gnorm + 1); sb_add(c, c->d_gnorm, c->d_gnorm + 1, c->d_gnorm, 1); }   /* one norm over all trained parameters */
             }
+            if (early.done) n = c->off[0].q;           /* the layer ranges were updated inside the backward pass: embedding and final norm remain */
             sb_adamw(c, w, g, m, v, n, lr, 0.9f, 0.999f, 0.01f, 1e-8f, st->optimizer_step, gscale, sumsq, c->grad_clip);
             if (extras) sb_adamw(c, c->XW, c->XG, c->XM, c->XV, c->n_extras, lr, 0.9f, 0.999f, 0.01f, 1e-8f, st->optimizer_step, gscale, sumsq, c->grad_clip);
             if (!full) c->lora_pad_stale = 1;          /* the adapters moved: the padded copies follow before the next step */

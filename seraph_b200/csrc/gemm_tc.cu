@@ -213,6 +213,21 @@ extern "C" void sb_gemm_keep_end(sb_ctx_t* c) {
     for (int i = 0; i < 8; i++) c->f16_slot[i].valid = 0;
 }
 
+// 1 when sb_gemm(A, B, ..., M, N, K, tA, tB) in the context's present mode reads its operands as prepared FP16 parts (so that a
+// producer may hand over the parts of a registered operand instead of its FP32 array); the same conditions as in sb_gemm_tc below
+static bool tc_f16_direct(const sb_ctx_t* c, int mode, int M, int N, int K, bool a_kmajor, bool b_kmajor) {
+    return c->gemm_pair && M > 128 && N > 128 && (a_kmajor ? (K & 3) == 0 : (M & 3) == 0) && (b_kmajor ? (K & 3) == 0 : (N & 3) == 0) &&
+           mode == SB_GEMM_FP16X3 && (a_kmajor ? (K & 7) == 0 : (M & 7) == 0) && (b_kmajor ? (K & 7) == 0 : (N & 7) == 0);
+}
+extern "C" int sb_gemm_reads_f16_parts(sb_ctx_t* c, int M, int N, int K, int tA, int tB) {
+    const int mode = c->pub.use_bf16 ? SB_GEMM_BF16 : c->gemm_mode;
+    if (K <= 0 || M < 32 || N < 32 || (double)M * N * K < (double)(1 << 21)) return 0;
+    if (tA && tB) { tA = 0; tB = 0; }
+    const bool a_kmajor = !tA, b_kmajor = tB != 0;
+    if ((a_kmajor || b_kmajor) && (K & 3)) return 0;
+    return tc_f16_direct(c, mode, M, N, K, a_kmajor, b_kmajor) ? 1 : 0;
+}
+
 extern "C" int sb_gemm_tc(sb_ctx_t* c, const float* A, const float* B, float* C, int M, int N, int K, int tA, int tB, int acc, int mode) {
     if (K <= 0 || M < 32 || N < 32) return 1;
     if ((double)M * N * K < (double)(1 << 21)) return 1;                 // too small to pay for the pipeline
@@ -233,7 +248,7 @@ extern "C" int sb_gemm_tc(sb_ctx_t* c, const float* A, const float* B, float* C,
         p.B.hi = B; p.B.lo = nullptr; p.B.rows = N; p.B.mn = b_kmajor ? 0 : 1; p.B.pitch = b_kmajor ? K : N;
         p.A.c2_dim = p.B.c2_dim = 1; p.A.c2_stride = p.B.c2_stride = 0; p.A.c2_base = p.B.c2_base = 0; p.A.c2_step = p.B.c2_step = 0;
         p.A.h1 = p.A.h2 = p.B.h1 = p.B.h2 = nullptr;
-        if (mode == SB_GEMM_FP16X3 && N > 128 && (a_kmajor ? (K & 7) == 0 : (M & 7) == 0) && (b_kmajor ? (K & 7) == 0 : (N & 7) == 0)) {
+        if (tc_f16_direct(c, mode, M, N, K, a_kmajor, b_kmajor)) {
             // FP16 split: each operand's largest magnitude, then its two FP16 parts (skipped for an operand whose parts are kept)
             const size_t na = (size_t)M * K, nb = (size_t)N * K;
             bool fa = false, fb = false;

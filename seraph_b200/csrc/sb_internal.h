@@ -220,6 +220,7 @@ void sb_sumsq(sb_ctx_t*, const float* g, size_t n, float* d_out);               
 void sb_nan_check(sb_ctx_t*, const float* x, size_t n, uint32_t* flags, uint32_t idx);
 /* C[M,N] (+)= op(A) op(B); same semantics as the reference's matmul_dispatch */
 void sb_gemm(sb_ctx_t*, const float* A, const float* B, float* C, int M, int N, int K, int tA, int tB, int acc);
+int  sb_gemm_reads_f16_parts(sb_ctx_t*, int M, int N, int K, int tA, int tB);      /* 1: that product takes prepared FP16 parts of its operands */
 void sb_gemm_simt(sb_ctx_t*, const float* A, const float* B, float* C, int M, int N, int K, int tA, int tB, int acc);
 /* returns 0 if the tensor-core path took the call, nonzero if the shape is not eligible */
 int  sb_gemm_tc(sb_ctx_t*, const float* A, const float* B, float* C, int M, int N, int K, int tA, int tB, int acc, int mode);

@@ -890,7 +890,8 @@ static float step_body(train_state_t* st, int* tokens, int T, int* seq_starts, i
     /* training: the gradient of the logits leaves the loss kernel as the FP16 parts the two LM-head backward products read (its
        FP32 form is never written); evaluation, the NaN guard (which inspects the FP32 array) and contexts without the parts arena
        take the plain kernel */
-    if (!(train && !c->nan_on && sb_cross_entropy_parts(c, c->logits, c->targets, c->dlogits, c->loss_rows, c->pos_ids, c->seq_ids, c->seq_starts,
+    const int ce_parts = train && !c->nan_on && sb_gemm_reads_f16_parts(c, T, c->d, c->V, 0, 0) && (!full || sb_gemm_reads_f16_parts(c, c->V, c->d, T, 1, 0));
+    if (!(ce_parts && sb_cross_entropy_parts(c, c->logits, c->targets, c->dlogits, c->loss_rows, c->pos_ids, c->seq_ids, c->seq_starts,
                                                           T, c->V, num_valid))) {
         if (train) sb_amax_announce(c, c->dlogits, (size_t)T * c->V);
         sb_cross_entropy(c, c->logits, c->targets, c->dlogits, c->loss_rows, c->pos_ids, c->seq_ids, c->seq_starts, T, c->V, num_valid);

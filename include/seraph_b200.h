@@ -223,9 +223,13 @@ int seraph_b200_lora_load(cuda_train_context_t* ctx, train_state_t* state, const
  * max_seq_len, at most 256 samples; SERAPH_B200_EVAL_BATCH_TOKENS sets the default) and takes every sample's mean loss
  * from the per-token losses of the pass.  0 = one pass per sample. */
 int seraph_b200_set_eval_batch_tokens(cuda_train_context_t* ctx, int tokens);
-/* Attention forward of 128-wide heads in the default GEMM mode: 1 = one kernel per call that keeps the scores in
- * tensor memory and the probabilities in shared memory (online softmax, no score-sized scratch); 0 = score product,
- * row softmax and value product as separate launches over a score scratch.  SERAPH_B200_ATTN_FLASH sets the default. */
+/* Attention of 128-wide heads in the default GEMM mode.  0 = score product, row softmax and value product as separate
+ * launches over a score scratch.  Otherwise the forward is one kernel per call that keeps the scores in tensor memory and the
+ * probabilities in shared memory (online softmax, no score-sized scratch), and the backward is
+ *   3  one kernel that keeps dK and dV on chip (P^T and dS^T return to tensor memory as operands) plus one product for dQ,
+ *   2  the scores in one kernel per sequence and head group, written as FP16 parts for three long products,
+ *   1  (default) 3 where it measured faster (no head grouping, or sequences from 3072 tokens), else 2.
+ * SERAPH_B200_ATTN_FLASH sets the default. */
 int seraph_b200_set_attn_flash(cuda_train_context_t* ctx, int on);
 /* Attention backward on the tensor cores: 0 (default) P and dS are made by a
  * streaming kernel from the stored scores; 1: by the epilogues of the two score

@@ -80,7 +80,7 @@ cuda_train_context_t* cuda_train_init(int device_id) {
     c->gemm_mode = SB_GEMM_FP16X3;
     { const char* e = getenv("SERAPH_B200_GEMM_PAIR"); c->gemm_pair = (e && e[0] == '0') ? 0 : 1; }
     { const char* e = getenv("SERAPH_B200_EVAL_BATCH_TOKENS"); c->eval_batch_tokens = (e && e[0]) ? atoi(e) : 8192; if (c->eval_batch_tokens < 0) c->eval_batch_tokens = 0; }
-    { const char* e = getenv("SERAPH_B200_ATTN_FLASH"); c->attn_flash = (e && e[0] == '0') ? 0 : (e && e[0] == '2') ? 2 : 1; }
+    { const char* e = getenv("SERAPH_B200_ATTN_FLASH"); c->attn_flash = (e && e[0] >= '0' && e[0] <= '3') ? e[0] - '0' : 1; }
     { const char* e = getenv("SERAPH_B200_ATTN_FUSED"); c->attn_fused = (e && e[0] == '1') ? 1 : 0; }
     { const char* e = getenv("SERAPH_B200_GEMM_TAIL_SPLIT"); c->gemm_tail_split = (e && e[0] == '0') ? 0 : 1; }
     { const char* e = getenv("SERAPH_B200_PARTS_CACHE"); c->parts_cache = (e && e[0] == '0') ? 0 : 1; }
@@ -305,7 +305,7 @@ int seraph_b200_set_eval_batch_tokens(cuda_train_context_t* ctx, int tokens) {
 int seraph_b200_set_attn_flash(cuda_train_context_t* ctx, int on) {
     sb_ctx_t* c = sb_priv(ctx);
     if (!c) return SB_ERR_ARG;
-    c->attn_flash = on == 2 ? 2 : (on ? 1 : 0);
+    c->attn_flash = (on >= 0 && on <= 3) ? on : 1;
     return SB_OK;
 }
 

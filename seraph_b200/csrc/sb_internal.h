@@ -75,8 +75,9 @@ typedef struct sb_ctx {
     struct { const float* ptr; size_t n; } hint_pending[4]; int hint_npending;
     unsigned parts_gen; int parts_open; int parts_cache;   /* parts_cache 0: off (switch, or the arena did not fit) */
     int eval_batch_tokens;           /* cuda_evaluate packs samples up to this many tokens per forward pass; 0: one sample per pass */
-    int attn_flash;                  /* 128-wide heads: 0 a launch per product over a score scratch; 1 (default) forward in one kernel, backward with
-                                        dK/dV kept on chip; 2 forward in one kernel, backward scores in one kernel and three long products */
+    int attn_flash;                  /* 128-wide heads: 0 a launch per product over a score scratch; otherwise the forward is one kernel and the backward
+                                        is 2: scores in one kernel and three long products, 3: dK/dV kept on chip, 1 (default): whichever of the two
+                                        measured faster for the shape */
     int attn_fused;                  /* 1: P and dS of the attention backward come out of the score products' epilogues */
     int gemm_tail_split;             /* 1: tiles of the last partial wave are cut into k pieces */
     int gemm_pair;                   /* 1: plain GEMMs run on CTA pairs (cta_group::2), 0: one CTA per tile */

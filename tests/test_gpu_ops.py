@@ -192,11 +192,11 @@ def test_attention_forward_backward(ctx, ss, Hq, Hkv, hd, fused):
     ctx.release(bq, bk, bv, bdo, bs, bout, blse, bdq, bdk, bdv, bdk2, bdv2)
 
 
-@pytest.mark.parametrize("flash", [1, 2, 3, 0])
+@pytest.mark.parametrize("flash", [1, 2, 3, 0, 4])
 @pytest.mark.parametrize("ss,Hq,Hkv", [([0, 257], 4, 1), ([0, 1024], 4, 1), ([0, 100, 420, 1000], 4, 2), ([0, 1, 130, 131, 450], 2, 2),
                                        ([0, 2048, 2100], 6, 3), ([0, 33, 700], 2, 2)])
 def test_attention_head128_one_kernel_paths(ctx, ss, Hq, Hkv, flash):
-    """Head size 128, default GEMM mode.  flash = 1 (the default): the forward is one kernel (scores in tensor memory, online
+    """Head size 128, default GEMM mode.  flash = 1: the forward is one kernel (scores in tensor memory, online
     softmax); the backward keeps dK and dV on chip in one launch over all sequences and K/V heads (P^T and dS^T go back into
     tensor memory as the A operand of the dV and dK products) and leaves only the parts of dS^T for the dQ product.
     flash = 2: the older backward, S, dP, P, dS from one kernel launch per sequence and head group that writes the FP16 parts
@@ -213,7 +213,7 @@ def test_attention_head128_one_kernel_paths(ctx, ss, Hq, Hkv, flash):
     dQ_ref, dK_ref, dV_ref = np.empty_like(Q), np.zeros_like(K), np.zeros_like(V)
     O.lib().ref_attention_backward(Q, K, V, dO, dQ_ref, dK_ref, dV_ref, ss, T, B, Hq, Hkv, hd)
     bq, bk, bv, bdo, bs = ctx.upload(Q), ctx.upload(K), ctx.upload(V), ctx.upload(dO), ctx.upload(ss)
-    ctx.set_attn_flash({1: 1, 2: 2, 3: 2, 0: 0}[flash])
+    ctx.set_attn_flash({1: 3, 2: 2, 3: 2, 0: 0, 4: 1}[flash])      # 4: the library's own choice between 1's and 2's backward
     if flash == 3:                                    # backward scores: one launch per call instead of one per sequence and head group
         os.environ["SERAPH_B200_ATTN_ALL_SCORES_MB"] = "4096"
     runs = []

@@ -84,12 +84,17 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
                   __half* __restrict__ dS1, __half* __restrict__ dS2, float* __restrict__ dK, float* __restrict__ dV,
                   const float* __restrict__ amax_q, const float* __restrict__ amax_k, const float* __restrict__ amax_v,
                   const float* __restrict__ amax_do, const float* __restrict__ ds_bound,
-                  const __grid_constant__ AfSeqs seqs, int Sp, int Hq, int g, int nkb, float scale, int* status) {
-    // which (key block, sequence, K/V head): key blocks from the start of the sequences first, they have the most queries
+                  const __grid_constant__ AfSeqs seqs, int Sp, int Hq, int g, int nkb, int chunk, float scale, int* status) {
+    // which (key block, sequence, K/V head).  The (sequence, head) pairs are taken `chunk` at a time, so that the Q and dO parts
+    // the CTAs in flight read again and again (once per key block) stay in L2; inside a chunk the key blocks from the start of
+    // the sequences come first, they have the most queries.
     const int Hkv = Hq / g;
-    const int per_kb = seqs.n * Hkv;
-    const int kb = (int)blockIdx.x / per_kb;
-    const int rem = (int)blockIdx.x % per_kb;
+    const int pairs = seqs.n * Hkv;
+    const int ci = (int)blockIdx.x / (chunk * nkb);
+    const int in_chunk = min(chunk, pairs - ci * chunk);
+    const int cr = (int)blockIdx.x - ci * chunk * nkb;
+    const int kb = cr / in_chunk;
+    const int rem = ci * chunk + cr % in_chunk;
     const int b = rem / Hkv, kvh = rem % Hkv;
     const int t0 = seqs.start[b], S = seqs.start[b + 1] - t0;
     const int k0 = kb * AB_BK;
@@ -381,10 +386,14 @@ extern "C" int sb_attention_fused_dkv(sb_ctx_t* c, const void* q1, const void* q
         !af_make_map(&mK1, k1, T, kvd, AB_BK) || !af_make_map(&mK2, k2, T, kvd, AB_BK) ||
         !af_make_map(&mV1, v1, T, kvd, AB_BK) || !af_make_map(&mV2, v2, T, kvd, AB_BK)) return 1;
     const long blocks = (long)nkb * seqs.n * Hkv;
+    // pairs per chunk: their Q and dO parts (8 bytes per element) within about a third of the L2
+    const size_t pair_bytes = (size_t)(Hq / Hkv) * Smax * hd * 8;
+    int chunk = (int)((size_t)(40u << 20) / pair_bytes);
+    chunk = max(1, min(chunk, seqs.n * Hkv));
     if (blocks > 0x7fffffffL) return 1;
     at_dkv_bwd_kernel<<<(unsigned)blocks, AB_THREADS, AB_SMEM, (cudaStream_t)c->pub.stream>>>(
         mQ1, mQ2, mD1, mD2, mK1, mK2, mV1, mV2, lse, D, (__half*)dS1, (__half*)dS2, dK, dV,
-        amax_q, amax_k, amax_v, amax_do, ds_bound, seqs, Sp, Hq, Hq / Hkv, nkb, 1.0f / sqrtf((float)hd), c->d_status);
+        amax_q, amax_k, amax_v, amax_do, ds_bound, seqs, Sp, Hq, Hq / Hkv, nkb, chunk, 1.0f / sqrtf((float)hd), c->d_status);
     c->launches++;
     return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }

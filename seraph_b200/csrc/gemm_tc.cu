@@ -41,16 +41,16 @@ static bool prep_operand(sb_ctx_t* c, const float* src, int rows, int K, bool km
     return true;
 }
 
-// Slot holding (or about to hold) the FP16 parts of operand x[n].  Inside a keep region the six kept slots are searched
+// Slot holding (or about to hold) the FP16 parts of operand x[n].  Inside a keep region the kept slots are searched
 // first and the least recently used one is taken on a miss; outside, the call's own slot `own` is used.  *fresh: the
 // parts must be made.  Returns the slot index, -1 on allocation failure.
 static int f16_slot(sb_ctx_t* c, const float* x, size_t n, int own, bool* fresh) {
-    if (!c->d_amax && sb_check(c, cudaMalloc(&c->d_amax, 8 * sizeof(float)), "amax alloc")) return -1;
+    if (!c->d_amax && sb_check(c, cudaMalloc(&c->d_amax, SB_F16_SLOTS * sizeof(float)), "amax alloc")) return -1;
     int s = own;
     *fresh = true;
     if (c->f16_keep) {
         int lru = 0;
-        for (int i = 0; i < 6; i++) {
+        for (int i = 0; i < SB_F16_KEPT; i++) {
             if (c->f16_slot[i].valid && c->f16_slot[i].ptr == x && c->f16_slot[i].n == n) { c->f16_slot[i].stamp = ++c->f16_clock; *fresh = false; return i; }
             if (!c->f16_slot[i].valid) { lru = i; break; }
             if (c->f16_slot[i].stamp < c->f16_slot[lru].stamp) lru = i;
@@ -208,9 +208,13 @@ extern "C" int sb_parts_find(sb_ctx_t* c, const float* x, size_t n, void** hout,
 }
 
 extern "C" void sb_gemm_keep_begin(sb_ctx_t* c) { c->f16_keep = 1; }
+// the array at `p` is about to be rewritten inside a keep region: parts kept for it are stale
+extern "C" void sb_gemm_keep_forget(sb_ctx_t* c, const float* p) {
+    for (int i = 0; i < SB_F16_SLOTS; i++) if (c->f16_slot[i].valid && c->f16_slot[i].ptr == p) c->f16_slot[i].valid = 0;
+}
 extern "C" void sb_gemm_keep_end(sb_ctx_t* c) {
     c->f16_keep = 0;
-    for (int i = 0; i < 8; i++) c->f16_slot[i].valid = 0;
+    for (int i = 0; i < SB_F16_SLOTS; i++) c->f16_slot[i].valid = 0;
 }
 
 // 1 when sb_gemm(A, B, ..., M, N, K, tA, tB) in the context's present mode reads its operands as prepared FP16 parts (so that a
@@ -255,9 +259,9 @@ extern "C" int sb_gemm_tc(sb_ctx_t* c, const float* A, const float* B, float* C,
             __half *ha, *hb; float *ma, *mb;
             void* hv; int fr; int sa = -1, sb = -1;
             if (sb_parts_find(c, A, na, &hv, &ma, &fr)) { ha = (__half*)hv; fa = fr != 0; }
-            else { sa = f16_slot(c, A, na, 6, &fa); if (sa < 0) return 1; ha = (__half*)c->f16_slot[sa].h; if (fa) c->f16_slot[sa].amax = c->d_amax + sa; ma = c->f16_slot[sa].amax; }
+            else { sa = f16_slot(c, A, na, SB_F16_KEPT, &fa); if (sa < 0) return 1; ha = (__half*)c->f16_slot[sa].h; if (fa) c->f16_slot[sa].amax = c->d_amax + sa; ma = c->f16_slot[sa].amax; }
             if (sb_parts_find(c, B, nb, &hv, &mb, &fr)) { hb = (__half*)hv; fb = fr != 0; }
-            else { sb = f16_slot(c, B, nb, 7, &fb); if (sb < 0) return 1; hb = (__half*)c->f16_slot[sb].h; if (fb) c->f16_slot[sb].amax = c->d_amax + sb; mb = c->f16_slot[sb].amax; }
+            else { sb = f16_slot(c, B, nb, SB_F16_KEPT + 1, &fb); if (sb < 0) return 1; hb = (__half*)c->f16_slot[sb].h; if (fb) c->f16_slot[sb].amax = c->d_amax + sb; mb = c->f16_slot[sb].amax; }
             if (fa || fb) {
                 cudaStream_t st = (cudaStream_t)c->pub.stream;
                 int tp = sb_tick_begin(c, SB_CLS_GEMM_PREP);

@@ -166,6 +166,30 @@ __global__ void __launch_bounds__(RB_THREADS) rmsnorm_warp_kernel(const float* _
     sb_block_amax(am, amax_out);
 }
 
+// Rows of exactly 128 columns (the learned per-head norm: rows = tokens x heads): one float4 per lane, four rows of a warp in
+// flight together, so that a warp has 2 KB of loads outstanding instead of 512 bytes.
+__global__ void __launch_bounds__(RB_THREADS) rmsnorm_w128_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ y,
+                                                                  int rows, float eps, unsigned* amax_out) {
+    const int lane = threadIdx.x & 31, warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+    const float4 s = ((const float4*)w)[lane];
+    float am = 0.f;
+    for (int r0 = warp * 4; r0 < rows; r0 += nwarps * 4) {
+        float4 v[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) v[i] = r0 + i < rows ? ((const float4*)x)[(size_t)(r0 + i) * 32 + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if (r0 + i >= rows) break;
+            const float ss = warp_sum(v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w);
+            const float inv = 1.0f / sqrtf(ss / 128.f + eps);
+            const float4 o = make_float4(v[i].x * inv * s.x, v[i].y * inv * s.y, v[i].z * inv * s.z, v[i].w * inv * s.w);
+            ((float4*)y)[(size_t)(r0 + i) * 32 + lane] = o;
+            am = sb_amax4(am, o);
+        }
+    }
+    sb_block_amax(am, amax_out);
+}
+
 // RMSNorm backward for a 256-thread CTA that visits row groups of RNB_ROWS rows.  Thread t owns the float4 column
 // chunks t, t+256, ... (NC of them) of every row the CTA visits, so its dscale partial stays in NC float4
 // registers.  The loads of the next group (x, dy, residual) are issued before the current group is reduced,
@@ -700,6 +724,10 @@ void sb_rmsnorm(sb_ctx_t* c, const float* x, const float* w, float* y, int rows,
         { int cap = sm_count(c) * 2, k = (wgrid + cap - 1) / cap; wgrid = (wgrid + k - 1) / k; }
         cudaStream_t st = (cudaStream_t)c->pub.stream;
         unsigned* am = sb_amax_take(c, y, (size_t)rows * cols);
+        if (cols == 128 && rows >= 1024) {
+            int g4 = (rows + 31) / 32; if (g4 > sm_count(c) * 4) g4 = sm_count(c) * 4;      // 8 warps x 4 rows per CTA and pass
+            rmsnorm_w128_kernel<<<g4, RB_THREADS, 0, st>>>(x, w, y, rows, eps, am);
+        } else
         if (cols <= 512)       rmsnorm_warp_kernel<4><<<wgrid, RB_THREADS, 0, st>>>(x, w, y, rows, cols, eps, am);
         else if (cols <= 1024) rmsnorm_warp_kernel<8><<<wgrid, RB_THREADS, 0, st>>>(x, w, y, rows, cols, eps, am);
         else if (cols <= 2048) rmsnorm_warp_kernel<16><<<wgrid, RB_THREADS, 0, st>>>(x, w, y, rows, cols, eps, am);

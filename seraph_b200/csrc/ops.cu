@@ -329,9 +329,11 @@ void cuda_train_set_profiler(cuda_train_context_t* ctx, cuda_profiler_t* prof) {
 // ---------------------------------------------------------------------------
 void sb_lora_backward(sb_ctx_t* c, const float* dY, const float* X, const float* A, const float* B, float* gA, float* gB,
                       float* tmp, int T, int in, int out, int r, float s) {
+    sb_gemm_keep_forget(c, tmp);                       /* tmp is written twice below: parts a caller's keep region holds for it go stale */
     sb_gemm(c, X, A, tmp, T, r, in, 0, 1, 0);
     sb_scale(c, tmp, (size_t)T * r, s);
     sb_gemm(c, dY, tmp, gB, out, r, T, 1, 0, 1);
+    sb_gemm_keep_forget(c, tmp);
     sb_gemm(c, dY, B, tmp, T, r, out, 0, 0, 0);
     sb_scale(c, tmp, (size_t)T * r, s);
     sb_gemm(c, tmp, X, gA, r, in, T, 1, 0, 1);

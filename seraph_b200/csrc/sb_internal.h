@@ -16,6 +16,8 @@ extern "C" {
 #endif
 
 #define SB_MAGIC 0x53423230u   /* "SB20" */
+#define SB_F16_KEPT 10          /* operand-part slots kept across the products of a keep region */
+#define SB_F16_SLOTS 12         /* plus one per operand for products outside a region */
 
 /* status codes (seraph_b200_last_status) */
 enum {
@@ -60,8 +62,8 @@ typedef struct sb_ctx {
     int* d_status;                   /* device status word (bounds checks, bounded waits) */
     int gemm_mode;                   /* SB_GEMM_* (use_bf16 in pub overrides to BF16) */
     float* d_amax;                   /* FP16 split: max |x| of the operand held by each part slot */
-    struct { void* h; size_t cap; const float* ptr; size_t n; unsigned stamp; int valid; float* amax; } f16_slot[8];   /* FP16 parts of GEMM operands: 0-5 kept across
-                                        calls inside a keep region (train_step.c marks runs of GEMMs that share operands), 6-7 for one call */
+    struct { void* h; size_t cap; const float* ptr; size_t n; unsigned stamp; int valid; float* amax; } f16_slot[SB_F16_SLOTS];   /* FP16 parts of GEMM operands: 0-9 kept across
+                                        calls inside a keep region (train_step.c marks runs of GEMMs that share operands), 10-11 for one call */
     int f16_keep; unsigned f16_clock;
     /* FP16 parts of registered tensors (weights, saved activations), valid from their first use inside a training or
        evaluation step until that step returns: made once, then shared by every product of the step that reads the tensor */
@@ -185,6 +187,7 @@ void sb_seq_index(sb_ctx_t*, const uint32_t* seq_starts, int B, int T, uint32_t*
 int sb_ensure_full_model(sb_ctx_t*, const train_state_t* st);
 void sb_gemm_keep_begin(sb_ctx_t*);
 void sb_gemm_keep_end(sb_ctx_t*);
+void sb_gemm_keep_forget(sb_ctx_t*, const float* p);      /* p is about to be rewritten inside the region */
 /* step-scoped FP16 parts of registered tensors: kind 0 = weights, 1 = saved activations */
 void sb_parts_register(sb_ctx_t*, int kind, const float* p, size_t n);
 void sb_parts_unregister(sb_ctx_t*, int kind);

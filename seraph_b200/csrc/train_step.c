@@ -578,6 +578,7 @@ static void linear_fwd(sb_ctx_t* c, int use_lora, int l, int a, const float* X, 
     lora_ref_t r;
     if (use_lora && lora_get(c, l, a, &r)) {
         float s = c->lora_alpha / (float)c->lora_rank;
+        sb_gemm_keep_forget(c, c->lora_tmp);
         sb_gemm(c, X, r.A, c->lora_tmp, T, c->lora_R, in, 0, 1, 0);
         sb_scale(c, c->lora_tmp, (size_t)T * c->lora_R, s);
         sb_gemm(c, c->lora_tmp, r.B, Y, T, out, c->lora_R, 0, 1, 1);
@@ -661,8 +662,8 @@ static void forward_pass(sb_ctx_t* c, int T, int max_seq, float theta, int use_l
         float* next_in = (l + 1 < L) ? c->act[l + 1].layer_in : c->final_in;
         sb_amax_announce(c, a->x_norm_attn, Td);           /* producers of GEMM operands leave max |x| behind for the operand split */
         sb_rmsnorm(c, a->layer_in, c->W + o->in_norm, a->x_norm_attn, T, d, RMS_EPS);
-        /* runs of products that share an operand keep its prepared parts (not with adapters: their scratch is rewritten in between) */
-        if (!use_lora) sb_gemm_keep_begin(c);
+        /* runs of products that share an operand keep its prepared parts (the adapters' scratch, rewritten in between, is dropped from the kept set at every write) */
+        sb_gemm_keep_begin(c);
         linear_fwd(c, use_lora, l, 0, a->x_norm_attn, c->W + o->q, c->head_norm ? a->q_pre : a->q, T, d, qd, 0);
         linear_fwd(c, use_lora, l, 1, a->x_norm_attn, c->W + o->k, c->head_norm ? a->k_pre : a->k, T, d, kvd, 0);
         linear_fwd(c, use_lora, l, 2, a->x_norm_attn, c->W + o->v, a->v, T, d, kvd, 0);
@@ -685,7 +686,7 @@ static void forward_pass(sb_ctx_t* c, int T, int max_seq, float theta, int use_l
         linear_fwd(c, use_lora, l, 3, a->attn_out, c->W + o->o, a->post_attn_in, T, qd, d, 1);
         sb_amax_announce(c, a->x_norm_ffn, Td);
         sb_rmsnorm(c, a->post_attn_in, c->W + o->post_norm, a->x_norm_ffn, T, d, RMS_EPS);
-        if (!use_lora) sb_gemm_keep_begin(c);
+        sb_gemm_keep_begin(c);
         linear_fwd(c, use_lora, l, 4, a->x_norm_ffn, c->W + o->gate, a->gate, T, d, F, 0);
         linear_fwd(c, use_lora, l, 5, a->x_norm_ffn, c->W + o->up, a->up, T, d, F, 0);
         sb_gemm_keep_end(c);
@@ -712,7 +713,7 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
     float* Gd = full ? c->G : NULL;
     float* norm_sink = c->g_tmp;                 /* LoRA mode: norm-scale gradients are discarded */
     if (!full) sb_memset(c, norm_sink, 0, (size_t)d * sizeof(float));
-    if (full) sb_gemm_keep_begin(c);
+    sb_gemm_keep_begin(c);
     sb_gemm(c, c->dlogits, c->untied ? c->XW + extras_lm_off(c) : c->W, gx, T, d, V, 0, 0, 0);
     if (full) sb_gemm(c, c->dlogits, c->hidden_norm, c->untied ? c->XG + extras_lm_off(c) : Gd, V, d, T, 1, 0, 1);
     sb_gemm_keep_end(c);
@@ -724,30 +725,30 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
         const sb_layer_off_t* o = &c->off[l];
         sb_layer_act_t* a = &c->act[l];
         /* FFN */
-        if (full) sb_gemm_keep_begin(c);
+        sb_gemm_keep_begin(c);                       /* gh (and, with adapters, what they read) is split once for the whole group */
         if (full) sb_gemm(c, gh, a->ffn_hidden, Gd + o->down, d, F, T, 1, 0, 1);
         sb_gemm(c, gh, c->W + o->down, c->g_ffn, T, F, d, 0, 0, 0);
-        sb_gemm_keep_end(c);
         if (!full) lora_bwd(c, l, 6, gh, a->ffn_hidden, c->g_ffn, T);
+        sb_gemm_keep_end(c);
         sb_amax_announce(c, c->g_gate, (size_t)T * F); sb_amax_announce(c, c->g_up, (size_t)T * F);
         sb_swiglu_backward(c, a->gate, a->up, c->g_ffn, c->g_gate, c->g_up, (size_t)T * F);
+        sb_gemm_keep_begin(c);
         if (full) {
-            sb_gemm_keep_begin(c);
             sb_gemm(c, c->g_gate, a->x_norm_ffn, Gd + o->gate, F, d, T, 1, 0, 1);
             sb_gemm(c, c->g_up, a->x_norm_ffn, Gd + o->up, F, d, T, 1, 0, 1);
         }
         sb_gemm(c, c->g_gate, c->W + o->gate, gx, T, d, F, 0, 0, 0);
         sb_gemm(c, c->g_up, c->W + o->up, gx, T, d, F, 0, 0, 1);
-        sb_gemm_keep_end(c);
         if (!full) { lora_bwd(c, l, 4, c->g_gate, a->x_norm_ffn, gx, T); lora_bwd(c, l, 5, c->g_up, a->x_norm_ffn, gx, T); }
+        sb_gemm_keep_end(c);
         sb_amax_announce(c, gh, (size_t)T * d);
         sb_rmsnorm_backward(c, a->post_attn_in, c->W + o->post_norm, gx, gh, gh, full ? Gd + o->post_norm : norm_sink, T, d, RMS_EPS);
         /* attention */
-        if (full) sb_gemm_keep_begin(c);
+        sb_gemm_keep_begin(c);
         if (full) sb_gemm(c, gh, a->attn_out, Gd + o->o, d, qd, T, 1, 0, 1);
         sb_gemm(c, gh, c->W + o->o, c->g_attn, T, qd, d, 0, 0, 0);
-        sb_gemm_keep_end(c);
         if (!full) lora_bwd(c, l, 3, gh, a->attn_out, c->g_attn, T);
+        sb_gemm_keep_end(c);
         nan_mark(c, c->g_attn, (size_t)T * qd, nan_bwd_base(c) + 5u * (uint32_t)l);
         sb_attention_backward(c, a->q, a->k, a->v, a->attn_out, a->lse, c->g_attn, c->g_q, c->g_k, c->g_v, 0,
                               c->seq_starts, c->seq_ids, B, T, c->Hq, c->Hkv, c->hd);
@@ -770,8 +771,8 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
             sb_rmsnorm_backward(c, a->k_pre, c->XW + xo + c->hd, c->g_k, NULL, c->g_k2, full ? c->XG + xo + c->hd : norm_sink, T * c->Hkv, c->hd, RMS_EPS);
             gq = c->g_q2; gk = c->g_k2;
         }
+        sb_gemm_keep_begin(c);
         if (full) {
-            sb_gemm_keep_begin(c);
             sb_gemm(c, gq, a->x_norm_attn, Gd + o->q, qd, d, T, 1, 0, 1);
             sb_gemm(c, gk, a->x_norm_attn, Gd + o->k, kvd, d, T, 1, 0, 1);
             sb_gemm(c, c->g_v, a->x_norm_attn, Gd + o->v, kvd, d, T, 1, 0, 1);
@@ -779,8 +780,8 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
         sb_gemm(c, gq, c->W + o->q, gx, T, d, qd, 0, 0, 0);
         sb_gemm(c, gk, c->W + o->k, gx, T, d, kvd, 0, 0, 1);
         sb_gemm(c, c->g_v, c->W + o->v, gx, T, d, kvd, 0, 0, 1);
-        sb_gemm_keep_end(c);
         if (!full) { lora_bwd(c, l, 0, gq, a->x_norm_attn, gx, T); lora_bwd(c, l, 1, gk, a->x_norm_attn, gx, T); lora_bwd(c, l, 2, c->g_v, a->x_norm_attn, gx, T); }
+        sb_gemm_keep_end(c);
         sb_amax_announce(c, gh, (size_t)T * d);
         sb_rmsnorm_backward(c, a->layer_in, c->W + o->in_norm, gx, gh, gh, full ? Gd + o->in_norm : norm_sink, T, d, RMS_EPS);
         nan_mark(c, gh, (size_t)T * d, nan_ghid_base(c) + (uint32_t)l);
@@ -1181,7 +1182,7 @@ void cuda_train_free(cuda_train_context_t* ctx) {
     if (c->rope_tab) cudaFree(c->rope_tab);
     sb_parts_free(c);
     if (c->d_amax) cudaFree(c->d_amax);
-    for (int i = 0; i < 8; i++) if (c->f16_slot[i].h) cudaFree(c->f16_slot[i].h);
+    for (int i = 0; i < SB_F16_SLOTS; i++) if (c->f16_slot[i].h) cudaFree(c->f16_slot[i].h);
     if (c->d_status) cudaFree(c->d_status);
     if (c->d_loss) cudaFree(c->d_loss);
     if (c->h_pinned) cudaFreeHost(c->h_pinned);

@@ -2,9 +2,11 @@
 // FP32-level accuracy).  Replaces batch_attention_backward_packed_kernel / flash_attention_bwd_packed_kernel of the
 // reference (src/cuda_train_context.cu:1013, :2012), which add into dK and dV with float atomics from every query tile.
 //
-// One CTA owns 128 consecutive keys of one (sequence, K/V head): the FP16 parts of those rows of K and V stay in shared
-// memory (2 x 64 KB) for the CTA's whole life.  It walks over the query heads of the K/V head's group and, for each, over
-// the sequence's queries from the diagonal to the end in blocks of 32 (Q and dO parts, 32 KB per block, three stages):
+// One CTA owns 128 consecutive keys of one (sequence, K/V head) for its whole life: the FP16 parts of those rows of V
+// stay in shared memory (64 KB), those of K in tensor memory (128 columns), where they are the A operand of the S^T
+// product: an MMA of 32 queries then reads 1 KB instead of 5 KB from shared memory, which is what its time went by.
+// The CTA walks over the query heads of the K/V head's group and, for each, over the sequence's queries from the
+// diagonal to the end in blocks of 32 (Q and dO parts, 32 KB per block, five stages):
 //
 //   S^T  = K Q_j^T,  dP^T = V dO_j^T     tcgen05.mma kind::f16, M 128 (keys) x N 32 (queries) x K 128, three passes each
 //                                        (k1 q1 + k2 q1 + k1 q2), accumulators in tensor memory, two buffers
@@ -31,24 +33,26 @@
 
 #define AB_BK 128                 // keys per CTA
 #define AB_BQ 32                  // queries per step
-#define AB_STAGES 3
+#define AB_STAGES 5
 #define AB_THREADS 512
 #define AB_DRAIN 8                // steps per accumulation chain in tensor memory (8 x 12 instructions: 3e-6 of one-sided truncation)
-#define AB_KV_BYTES 65536         // the parts of 128 rows of K (or V): 2 parts x 2 halves of the head dimension x 128 x 128 B
-#define AB_OFF_V AB_KV_BYTES
-#define AB_OFF_ST (2 * AB_KV_BYTES)
+#define AB_KV_BYTES 65536         // the parts of 128 rows of V: 2 parts x 2 halves of the head dimension x 128 x 128 B
+#define AB_OFF_V 0
+#define AB_OFF_ST AB_KV_BYTES
 #define AB_STAGE_BYTES 32768      // Q parts 16 KB, dO parts 16 KB
 #define AB_OFF_BAR (AB_OFF_ST + AB_STAGES * AB_STAGE_BYTES)
 #define AB_SMEM (AB_OFF_BAR + 1024 + 1024)
 #define AB_REGS_LIGHT 72          // producer / MMA issuer warpgroup
 #define AB_REGS_EW 120             // the two elementwise warpgroups
 #define AB_REGS_DRAIN 200          // the drain warpgroup holds 128 accumulator values at a time   (128*72 + 256*120 + 128*200 = 65536)
-// tensor-memory columns: dK 0..127, dV 128..255, then per buffer e: S^T at 256 + 64 e (32 columns, one per query), dP^T 32 further.
-// The FP16 parts of P^T and dS^T replace them in place: for each k-step of 16 queries, 8 columns of hi parts then 8 of lo parts.
+// tensor-memory columns: dK 0..127, dV 128..255, the parts of K 256..383 (for each k-step of 16 head-dimension elements, 8 columns
+// of hi parts then 8 of lo parts, two halfs per column), then per buffer e: S^T at 384 + 64 e (32 columns, one per query), dP^T 32
+// further.  The FP16 parts of P^T and dS^T replace them in place: for each k-step of 16 queries, 8 columns of hi parts then 8 of lo parts.
 #define AB_COL_DK 0
 #define AB_COL_DV 128
-#define AB_COL_S(e) (256 + 64 * (e))
-#define AB_COL_DP(e) (256 + 64 * (e) + 32)
+#define AB_COL_K 256
+#define AB_COL_S(e) (384 + 64 * (e))
+#define AB_COL_DP(e) (384 + 64 * (e) + 32)
 
 // A from tensor memory (M 128 lanes, 16 halfs of k = 8 columns), B from shared memory
 __device__ __forceinline__ void ab_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
@@ -78,8 +82,8 @@ __device__ __forceinline__ void ab_red4(float* p, float a, float b, float c, flo
 __global__ void __launch_bounds__(AB_THREADS, 1)
 at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant__ CUtensorMap mQ2,
                   const __grid_constant__ CUtensorMap mD1, const __grid_constant__ CUtensorMap mD2,
-                  const __grid_constant__ CUtensorMap mK1, const __grid_constant__ CUtensorMap mK2,
                   const __grid_constant__ CUtensorMap mV1, const __grid_constant__ CUtensorMap mV2,
+                  const __half* __restrict__ k1, const __half* __restrict__ k2,
                   const float* __restrict__ lse, const float* __restrict__ D,
                   __half* __restrict__ dS1, __half* __restrict__ dS2, float* __restrict__ dK, float* __restrict__ dV,
                   const float* __restrict__ amax_q, const float* __restrict__ amax_k, const float* __restrict__ amax_v,
@@ -108,18 +112,19 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
     extern __shared__ uint8_t af_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)af_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + AB_OFF_BAR);
-    uint64_t* kv_full = bars;            // 1
-    uint64_t* full = bars + 1;           // 3
-    uint64_t* empty = bars + 4;          // 3
-    uint64_t* sdp_full = bars + 7;       // 2
-    uint64_t* p_full = bars + 9;         // 2
-    uint64_t* acc_ready = bars + 11;     // 1
-    uint64_t* acc_free = bars + 12;      // 1
-    uint32_t* tmem_slot = (uint32_t*)(bars + 16);
+    uint64_t* kv_full = bars;                          // 1: V in shared memory
+    uint64_t* full = bars + 1;                         // AB_STAGES
+    uint64_t* empty = full + AB_STAGES;                // AB_STAGES
+    uint64_t* sdp_full = empty + AB_STAGES;            // 2
+    uint64_t* p_full = sdp_full + 2;                   // 2
+    uint64_t* acc_ready = p_full + 2;                  // 1
+    uint64_t* acc_free = acc_ready + 1;                // 1
+    uint64_t* k_ready = acc_free + 1;                  // 1: K in tensor memory
+    uint32_t* tmem_slot = (uint32_t*)(k_ready + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        mbar_init(kv_full, 1); mbar_init(acc_ready, 1); mbar_init(acc_free, 4);
+        mbar_init(kv_full, 1); mbar_init(acc_ready, 1); mbar_init(acc_free, 4); mbar_init(k_ready, 8);
         for (int i = 0; i < AB_STAGES; i++) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
         for (int i = 0; i < 2; i++) { mbar_init(&sdp_full[i], 1); mbar_init(&p_full[i], 8); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -139,10 +144,8 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
         if (warp == 0) {
             // ---------------- TMA producer ----------------
             if (elect_one()) {
-                mbar_expect_tx(kv_full, 2 * AB_KV_BYTES);
+                mbar_expect_tx(kv_full, AB_KV_BYTES);
                 for (int p = 0; p < 2; p++) {
-                    af_tma_2d(smem + p * 16384, &mK1, kv_full, kvh * AF_HD + p * 64, t0 + k0);
-                    af_tma_2d(smem + 32768 + p * 16384, &mK2, kv_full, kvh * AF_HD + p * 64, t0 + k0);
                     af_tma_2d(smem + AB_OFF_V + p * 16384, &mV1, kv_full, kvh * AF_HD + p * 64, t0 + k0);
                     af_tma_2d(smem + AB_OFF_V + 32768 + p * 16384, &mV2, kv_full, kvh * AF_HD + p * 64, t0 + k0);
                 }
@@ -167,8 +170,8 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
             if (elect_one()) {
                 const uint32_t idesc_s = (1u << 4) | ((uint32_t)(AB_BQ >> 3) << 17) | ((uint32_t)(AB_BK >> 4) << 24);
                 const uint32_t idesc_o = (1u << 4) | (1u << 16) | ((uint32_t)(AF_HD >> 3) << 17) | ((uint32_t)(AB_BK >> 4) << 24);
-                const uint32_t sk = smem_u32(smem), sv = smem_u32(smem + AB_OFF_V);
-                ok = mbar_wait(kv_full, 0);
+                const uint32_t sv = smem_u32(smem + AB_OFF_V), tk = tmem_base + AB_COL_K;
+                ok = mbar_wait(kv_full, 0) && mbar_wait(k_ready, 0);
                 for (int t = 0; t <= nsteps && ok; t++) {
                     if (t < nsteps) {
                         // S^T and dP^T of step t into buffer t & 1 (its parts of step t - 2 were consumed by instructions issued before these)
@@ -177,13 +180,27 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
                         if (!ok) break;
                         tc_fence_after();
                         const uint32_t st = smem_u32(smem + AB_OFF_ST + s * AB_STAGE_BYTES);
-#pragma unroll
-                        for (int prod = 0; prod < 2; prod++) {
-                            const uint32_t sa = prod ? sv : sk, sb = st + (prod ? 16384 : 0);
-                            const uint32_t d = tmem_base + (uint32_t)(prod ? AB_COL_DP(e) : AB_COL_S(e));
+                        {                                          // S^T: K parts from tensor memory
+                            const uint32_t d = tmem_base + (uint32_t)AB_COL_S(e);
 #pragma unroll
                             for (int p = 0; p < 2; p++) {
-                                const uint64_t a1 = make_kmajor_desc<128>(sa + p * 16384), a2 = make_kmajor_desc<128>(sa + 32768 + p * 16384);
+                                const uint64_t b1 = make_kmajor_desc<128>(st + p * 4096), b2 = make_kmajor_desc<128>(st + 8192 + p * 4096);
+#pragma unroll
+                                for (int kk = 0; kk < 4; kk++) {
+                                    const uint64_t adv = (uint64_t)(kk * 2);
+                                    const uint32_t ta = tk + (uint32_t)((p * 4 + kk) * 16);
+                                    ab_mma_ts(d, ta, b1 + adv, idesc_s, (p | kk) ? 1u : 0u);
+                                    ab_mma_ts(d, ta + 8, b1 + adv, idesc_s, 1);
+                                    ab_mma_ts(d, ta, b2 + adv, idesc_s, 1);
+                                }
+                            }
+                        }
+                        {                                          // dP^T: V parts from shared memory
+                            const uint32_t sb = st + 16384;
+                            const uint32_t d = tmem_base + (uint32_t)AB_COL_DP(e);
+#pragma unroll
+                            for (int p = 0; p < 2; p++) {
+                                const uint64_t a1 = make_kmajor_desc<128>(sv + p * 16384), a2 = make_kmajor_desc<128>(sv + 32768 + p * 16384);
                                 const uint64_t b1 = make_kmajor_desc<128>(sb + p * 4096), b2 = make_kmajor_desc<128>(sb + 8192 + p * 4096);
 #pragma unroll
                                 for (int kk = 0; kk < 4; kk++) {
@@ -281,6 +298,25 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
         const float cp = tc_pow2(-tc_f16_shift(__ldg(amax_do))) * tc_pow2(-tc_f16_shift(__ldg(amax_v)));
         const float dsc = tc_pow2(tc_f16_shift(__ldg(ds_bound))) * scale * (1.0f / 16384.f);      // p holds P * 2^14
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+        // This key row's parts of K into tensor memory: head-dimension k-steps ch*4 .. ch*4+3, 32 bytes of each part per k-step,
+        // two consecutive halfs per column as they lie in memory (rows past the sequence's end: zeros, their scores are masked anyway)
+        {
+            const uint4* g1 = (const uint4*)(k1 + (size_t)(t0 + kg) * kvd + (size_t)kvh * AF_HD) + ch * 8;
+            const uint4* g2 = (const uint4*)(k2 + (size_t)(t0 + kg) * kvd + (size_t)kvh * AF_HD) + ch * 8;
+#pragma unroll
+            for (int kk = 0; kk < 4; kk++) {
+                uint4 a = make_uint4(0, 0, 0, 0), bq = a, c2 = a, d2 = a;
+                if (kg < S) { a = __ldg(g1 + 2 * kk); bq = __ldg(g1 + 2 * kk + 1); c2 = __ldg(g2 + 2 * kk); d2 = __ldg(g2 + 2 * kk + 1); }
+                const uint32_t h8[8] = {a.x, a.y, a.z, a.w, bq.x, bq.y, bq.z, bq.w};
+                const uint32_t l8[8] = {c2.x, c2.y, c2.z, c2.w, d2.x, d2.y, d2.z, d2.w};
+                ab_st8(tmem_base + lane_addr + (uint32_t)(AB_COL_K + (ch * 4 + kk) * 16), h8);
+                ab_st8(tmem_base + lane_addr + (uint32_t)(AB_COL_K + (ch * 4 + kk) * 16 + 8), l8);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) af_arrive(k_ready);
+        }
         // Columns before this key block that the dQ product reads together with it (its query tiles are 256 wide): zeros
         if ((k0 & 255) != 0) {
             for (int hi = 0; hi < g; hi++) {
@@ -380,10 +416,10 @@ extern "C" int sb_attention_fused_dkv(sb_ctx_t* c, const void* q1, const void* q
     for (int b = 0; b < c->h_seq_n; b++) Smax = max(Smax, c->h_seq[b + 1] - c->h_seq[b]);
     if (Smax <= 0 || Smax > Sp) return 1;
     const int qd = Hq * hd, kvd = Hkv * hd, nkb = (Smax + AB_BK - 1) / AB_BK;
-    CUtensorMap mQ1, mQ2, mD1, mD2, mK1, mK2, mV1, mV2;
+    CUtensorMap mQ1, mQ2, mD1, mD2, mV1, mV2;
     if (!af_make_map(&mQ1, q1, T, qd, AB_BQ) || !af_make_map(&mQ2, q2, T, qd, AB_BQ) ||
         !af_make_map(&mD1, do1, T, qd, AB_BQ) || !af_make_map(&mD2, do2, T, qd, AB_BQ) ||
-        !af_make_map(&mK1, k1, T, kvd, AB_BK) || !af_make_map(&mK2, k2, T, kvd, AB_BK) ||
+        !tc_aligned16(k1) || !tc_aligned16(k2) ||
         !af_make_map(&mV1, v1, T, kvd, AB_BK) || !af_make_map(&mV2, v2, T, kvd, AB_BK)) return 1;
     const long blocks = (long)nkb * seqs.n * Hkv;
     // pairs per chunk: their Q and dO parts (8 bytes per element) within about a third of the L2
@@ -392,7 +428,7 @@ extern "C" int sb_attention_fused_dkv(sb_ctx_t* c, const void* q1, const void* q
     chunk = max(1, min(chunk, seqs.n * Hkv));
     if (blocks > 0x7fffffffL) return 1;
     at_dkv_bwd_kernel<<<(unsigned)blocks, AB_THREADS, AB_SMEM, (cudaStream_t)c->pub.stream>>>(
-        mQ1, mQ2, mD1, mD2, mK1, mK2, mV1, mV2, lse, D, (__half*)dS1, (__half*)dS2, dK, dV,
+        mQ1, mQ2, mD1, mD2, mV1, mV2, (const __half*)k1, (const __half*)k2, lse, D, (__half*)dS1, (__half*)dS2, dK, dV,
         amax_q, amax_k, amax_v, amax_do, ds_bound, seqs, Sp, Hq, Hq / Hkv, nkb, chunk, 1.0f / sqrtf((float)hd), c->d_status);
     c->launches++;
     return cudaGetLastError() == cudaSuccess ? 0 : 1;

@@ -220,7 +220,7 @@ extern "C" void sb_gemm_keep_end(sb_ctx_t* c) {
 // 1 when sb_gemm(A, B, ..., M, N, K, tA, tB) in the context's present mode reads its operands as prepared FP16 parts (so that a
 // producer may hand over the parts of a registered operand instead of its FP32 array); the same conditions as in sb_gemm_tc below
 static bool tc_f16_direct(const sb_ctx_t* c, int mode, int M, int N, int K, bool a_kmajor, bool b_kmajor) {
-    return c->gemm_pair && M > 128 && N > 128 && (a_kmajor ? (K & 3) == 0 : (M & 3) == 0) && (b_kmajor ? (K & 3) == 0 : (N & 3) == 0) &&
+    return c->gemm_pair && M >= 128 && N >= 128 && (a_kmajor ? (K & 3) == 0 : (M & 3) == 0) && (b_kmajor ? (K & 3) == 0 : (N & 3) == 0) &&
            mode == SB_GEMM_FP16X3 && (a_kmajor ? (K & 7) == 0 : (M & 7) == 0) && (b_kmajor ? (K & 7) == 0 : (N & 7) == 0);
 }
 extern "C" int sb_gemm_reads_f16_parts(sb_ctx_t* c, int M, int N, int K, int tA, int tB) {
@@ -247,7 +247,7 @@ extern "C" int sb_gemm_tc(sb_ctx_t* c, const float* A, const float* B, float* C,
     p.amax_a = p.amax_b = nullptr;
     p.C = C; p.ldc = N; p.c_batch_stride = 0; p.M = M; p.N = N; p.K = K; p.acc = acc; p.nbatch = 1; p.causal = TC_CAUSAL_NONE;
     // direct path: the pair kernel on the caller's arrays (rows of either layout must be 16-byte multiples)
-    if (c->gemm_pair && M > 128 && N > 128 && (a_kmajor ? (K & 3) == 0 : (M & 3) == 0) && (b_kmajor ? (K & 3) == 0 : (N & 3) == 0)) {
+    if (c->gemm_pair && M >= 128 && N >= 128 && (a_kmajor ? (K & 3) == 0 : (M & 3) == 0) && (b_kmajor ? (K & 3) == 0 : (N & 3) == 0)) {
         p.A.hi = A; p.A.lo = nullptr; p.A.rows = M; p.A.mn = a_kmajor ? 0 : 1; p.A.pitch = a_kmajor ? K : M;
         p.B.hi = B; p.B.lo = nullptr; p.B.rows = N; p.B.mn = b_kmajor ? 0 : 1; p.B.pitch = b_kmajor ? K : N;
         p.A.c2_dim = p.B.c2_dim = 1; p.A.c2_stride = p.B.c2_stride = 0; p.A.c2_base = p.B.c2_base = 0; p.A.c2_step = p.B.c2_step = 0;

@@ -112,8 +112,9 @@ typedef struct sb_ctx {
     int lora_rank, lora_mask; float lora_alpha;
     size_t n_lora;
     float *LW, *LG, *LM, *LV;
-    /* The rank-r products are far too thin for the tensor-core kernel's 256-wide tiles (and ran 40 times slower on the CUDA-core
-       GEMM), so the step works on copies of A and B whose rank is padded with zero rows / columns to lora_R, a multiple of 256:
+    /* The rank-r products are far too thin for the tensor-core kernel's tiles (and ran 40 times slower on the CUDA-core GEMM),
+       so the step works on copies of A and B whose rank is padded with zero rows / columns to lora_R, a multiple of 128 (the
+       narrow tile of the CTA-pair kernel):
        LWp [per adapter: A (R, in) then B (out, R)] is refreshed from LW before a step when the adapters changed, the gradient
        products accumulate into LGp and the live part is copied to LG layer by layer.  Padding changes no value: the extra rows of
        A and columns of B are zero, so the extra columns of X A^T are zero and the extra gradient rows / columns are never read. */

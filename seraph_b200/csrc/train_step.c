@@ -419,7 +419,7 @@ static int ensure_lora(sb_ctx_t* c, const lora_model_t* m) {
     cudaStreamSynchronize(S(c));
     free_lora(c);
     c->lora_rank = m->rank; c->lora_mask = mask; c->lora_alpha = m->alpha;
-    c->lora_R = (m->rank + 255) / 256 * 256;
+    c->lora_R = (m->rank + 127) / 128 * 128;
     c->n_lora = lora_layer_params(c) * (size_t)c->L;
     c->n_lora_pad = lora_layer_params_pad(c) * (size_t)c->L;
     if (sb_check(c, cudaMalloc((void**)&c->LWp, c->n_lora_pad * sizeof(float)), "lora padded weights") ||

@@ -226,9 +226,9 @@ int seraph_b200_set_eval_batch_tokens(cuda_train_context_t* ctx, int tokens);
 /* Attention of 128-wide heads in the default GEMM mode.  0 = score product, row softmax and value product as separate
  * launches over a score scratch.  Otherwise the forward is one kernel per call that keeps the scores in tensor memory and the
  * probabilities in shared memory (online softmax, no score-sized scratch), and the backward is
- *   3  one kernel that keeps dK and dV on chip (P^T and dS^T return to tensor memory as operands) plus one product for dQ,
- *   2  the scores in one kernel per sequence and head group, written as FP16 parts for three long products,
- *   1  (default) 3 where it measured faster (no head grouping, or sequences from 3072 tokens), else 2.
+ *   1  (default) and 3  one kernel that keeps dK and dV on chip (P^T and dS^T return to tensor memory as operands) plus one
+ *      product for dQ,
+ *   2  the scores in one kernel per sequence and head group, written as FP16 parts for three long products.
  * SERAPH_B200_ATTN_FLASH sets the default. */
 int seraph_b200_set_attn_flash(cuda_train_context_t* ctx, int on);
 /* Attention backward on the tensor cores: 0 (default) P and dS are made by a

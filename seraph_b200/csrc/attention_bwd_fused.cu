@@ -6,7 +6,7 @@
 // stay in shared memory (64 KB), those of K in tensor memory (128 columns), where they are the A operand of the S^T
 // product: an MMA of 32 queries then reads 1 KB instead of 5 KB from shared memory, which is what its time went by.
 // The CTA walks over the query heads of the K/V head's group and, for each, over the sequence's queries from the
-// diagonal to the end in blocks of 32 (Q and dO parts, 32 KB per block, five stages):
+// diagonal to the end in blocks of 32 (Q and dO parts, 32 KB per block, three stages):
 //
 //   S^T  = K Q_j^T,  dP^T = V dO_j^T     tcgen05.mma kind::f16, M 128 (keys) x N 32 (queries) x K 128, three passes each
 //                                        (k1 q1 + k2 q1 + k1 q2), accumulators in tensor memory, two buffers
@@ -18,13 +18,23 @@
 //                                        tensor memory, summed over the query blocks and heads
 //
 // The tensor core adds into its accumulator with truncation, so a chain of accumulation is cut after AB_DRAIN query
-// blocks: four drain warps read dK and dV out of tensor memory and add them into the output with red.global.add.f32
-// (round to nearest, performed in L2).  A dK/dV element is only ever touched by the one CTA that owns its key, its
-// additions are issued by one thread in program order, and the output is zeroed (or holds the caller's values) before
-// the launch: the result does not depend on scheduling and is the same bits on every run.
+// blocks: four drain warps read dK and dV out of tensor memory and add them into the output (round to nearest,
+// performed in L2).  A dK/dV element is only ever touched by the one CTA that owns its key, one chain's additions have
+// been performed before the next chain's are issued, and the output is zeroed (or holds the caller's values) before the
+// launch: the result does not depend on scheduling and is the same bits on every run.
 // dS^T also leaves the chip, as FP16 parts laid out [head slot][key][query]: dQ = dS K is one more product on the
 // GEMM kernel (M = queries, K = keys up to the diagonal, A read MN-major).  P never reaches memory, dS is written once
 // and read once: 8 bytes per score element instead of the 20 of the score-materialising path.
+//
+// Everything that leaves the CTA goes through shared memory and the TMA unit.  With one key row per thread (the layout
+// tensor memory gives), a warp's direct stores and reductions touch 32 different rows per instruction, 32 memory
+// transactions each; cycle counters in the warps showed the load/store unit busy two thirds of a step with them and the
+// elementwise warps, which bound the step, waiting on it.  So each elementwise warp stages its 32 rows x 16 queries of dS^T
+// parts in shared memory and stores them as two tiles, each drain warp stages 32 rows x 32 columns of a chain at a time
+// (128-byte swizzle, conflict-free for row-per-lane writes) and adds it with a TMA reduction, and the log-sum-exp and the row
+// dot products D are read from copies transposed to [sequence][head][query] (at_lse_d_rows_kernel), 16 consecutive queries as
+// four 16-byte loads from one address for the whole warp.  A key block that reaches past its sequence's end keeps the
+// per-thread reductions, so that no CTA ever adds (even a zero) into a row of the next sequence.
 //
 // Warps (16): 0 TMA producer, 1 MMA issuer (owns the tensor-memory allocation), 4-11 elementwise (a lane quarter and half of
 // a step's queries each), 12-15 drain.  Every mbarrier wait is bounded; a wait that runs out sets the status word and the CTA drains
@@ -33,14 +43,16 @@
 
 #define AB_BK 128                 // keys per CTA
 #define AB_BQ 32                  // queries per step
-#define AB_STAGES 5
+#define AB_STAGES 3
 #define AB_THREADS 512
 #define AB_DRAIN 8                // steps per accumulation chain in tensor memory (8 x 12 instructions: 3e-6 of one-sided truncation)
 #define AB_KV_BYTES 65536         // the parts of 128 rows of V: 2 parts x 2 halves of the head dimension x 128 x 128 B
 #define AB_OFF_V 0
 #define AB_OFF_ST AB_KV_BYTES
 #define AB_STAGE_BYTES 32768      // Q parts 16 KB, dO parts 16 KB
-#define AB_OFF_BAR (AB_OFF_ST + AB_STAGES * AB_STAGE_BYTES)
+#define AB_OFF_EWS (AB_OFF_ST + AB_STAGES * AB_STAGE_BYTES)      // per elementwise warp 2 buffers x (hi tile 1 KB + lo tile 1 KB): 32 rows x 32 bytes each
+#define AB_OFF_DRS (AB_OFF_EWS + 8 * 4096)                       // per drain warp 2 buffers x 4 KB: 32 rows x 32 floats, 128-byte swizzle
+#define AB_OFF_BAR (AB_OFF_DRS + 4 * 8192)
 #define AB_SMEM (AB_OFF_BAR + 1024 + 1024)
 #define AB_REGS_LIGHT 72          // producer / MMA issuer warpgroup
 #define AB_REGS_EW 120             // the two elementwise warpgroups
@@ -78,26 +90,60 @@ __device__ __forceinline__ void ab_st8(uint32_t taddr, const uint32_t (&r)[8]) {
 __device__ __forceinline__ void ab_red4(float* p, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
+__device__ __forceinline__ void ab_sts4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// tile in shared memory -> global memory through a tensor map, as a store or as an FP32 addition; completion by bulk group
+__device__ __forceinline__ void ab_tma_store(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(c0), "r"(c1), "r"(src) : "memory");
+}
+__device__ __forceinline__ void ab_tma_add(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(c0), "r"(c1), "r"(src) : "memory");
+}
+#define AB_BULK_COMMIT() asm volatile("cp.async.bulk.commit_group;" ::: "memory")
+#define AB_BULK_WAIT_READ(n) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(n) : "memory")
+#define AB_BULK_WAIT(n) asm volatile("cp.async.bulk.wait_group %0;" ::"n"(n) : "memory")
+#define AB_FENCE_ASYNC() asm volatile("fence.proxy.async.shared::cta;" ::: "memory")
+
+// lse and D, [token][head], as [sequence][head][Sp queries] (zeros past the sequence's end); lse comes out times log2(e)
+__global__ void at_lse_d_rows_kernel(const float* __restrict__ lse, const float* __restrict__ D, float* __restrict__ LT, float* __restrict__ DT,
+                                     const __grid_constant__ AfSeqs seqs, int Hq, int Sp) {
+    const size_t n = (size_t)seqs.n * Hq * Sp;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const int q = (int)(i % Sp), h = (int)((i / Sp) % Hq), b = (int)(i / ((size_t)Sp * Hq));
+        const int t0 = seqs.start[b], S = seqs.start[b + 1] - t0;
+        float l = 0.f, d = 0.f;
+        if (q < S) { l = __ldg(&lse[(size_t)(t0 + q) * Hq + h]) * 1.4426950408889634f; d = __ldg(&D[(size_t)(t0 + q) * Hq + h]); }
+        LT[i] = l; DT[i] = d;
+    }
+}
 
 __global__ void __launch_bounds__(AB_THREADS, 1)
 at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant__ CUtensorMap mQ2,
                   const __grid_constant__ CUtensorMap mD1, const __grid_constant__ CUtensorMap mD2,
                   const __grid_constant__ CUtensorMap mV1, const __grid_constant__ CUtensorMap mV2,
+                  const __grid_constant__ CUtensorMap mS1, const __grid_constant__ CUtensorMap mS2,
+                  const __grid_constant__ CUtensorMap mdK, const __grid_constant__ CUtensorMap mdV,
                   const __half* __restrict__ k1, const __half* __restrict__ k2,
-                  const float* __restrict__ lse, const float* __restrict__ D,
+                  const float* __restrict__ LT, const float* __restrict__ DT,
                   __half* __restrict__ dS1, __half* __restrict__ dS2, float* __restrict__ dK, float* __restrict__ dV,
                   const float* __restrict__ amax_q, const float* __restrict__ amax_k, const float* __restrict__ amax_v,
                   const float* __restrict__ amax_do, const float* __restrict__ ds_bound,
                   const __grid_constant__ AfSeqs seqs, int Sp, int Hq, int g, int nkb, int chunk, float scale, int* status) {
-    // which (key block, sequence, K/V head).  The (sequence, head) pairs are taken `chunk` at a time, so that the Q and dO parts
-    // the CTAs in flight read again and again (once per key block) stay in L2; inside a chunk the key blocks from the start of
-    // the sequences come first, they have the most queries.
+    // which (key block, sequence, K/V head).  Key blocks from the start of the sequences have the most queries, so the launch runs
+    // in up to four phases over ranges of key blocks, the longest first, and ends on CTAs of a few steps that fill the last wave.
+    // Inside a phase the (sequence, head) pairs are taken `chunk` at a time, so that the Q and dO parts the CTAs in flight read
+    // again and again (once per key block) stay in L2.
     const int Hkv = Hq / g;
     const int pairs = seqs.n * Hkv;
-    const int ci = (int)blockIdx.x / (chunk * nkb);
+    const int nph = min(4, nkb);
+    int bid = (int)blockIdx.x, ph = 0;
+    while (ph + 1 < nph && bid >= pairs * ((ph + 1) * nkb / nph - ph * nkb / nph)) { bid -= pairs * ((ph + 1) * nkb / nph - ph * nkb / nph); ph++; }
+    const int kb_lo = ph * nkb / nph, nk = (ph + 1) * nkb / nph - kb_lo;
+    const int ci = bid / (chunk * nk);
     const int in_chunk = min(chunk, pairs - ci * chunk);
-    const int cr = (int)blockIdx.x - ci * chunk * nkb;
-    const int kb = cr / in_chunk;
+    const int cr = bid - ci * chunk * nk;
+    const int kb = kb_lo + cr / in_chunk;
     const int rem = ci * chunk + cr % in_chunk;
     const int b = rem / Hkv, kvh = rem % Hkv;
     const int t0 = seqs.start[b], S = seqs.start[b + 1] - t0;
@@ -258,10 +304,18 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
             float* rowk = dK + (size_t)(t0 + (live ? kg : 0)) * kvd + (size_t)kvh * AF_HD;
             float* rowv = dV + (size_t)(t0 + (live ? kg : 0)) * kvd + (size_t)kvh * AF_HD;
             const uint32_t ta = tmem_base + ((uint32_t)(q * 32) << 16);
+            const bool whole = k0 + AB_BK <= S;                // all 128 keys belong to this sequence: tiles through the TMA unit
+            const uint32_t stg = smem_u32(smem + AB_OFF_DRS + q * 8192);
+            const int row0 = t0 + k0 + q * 32, col0 = kvh * AF_HD;
+            int pieces = 0;                                     // tiles this warp has handed to the TMA unit
             for (int c = 0; c < nchains && ok; c++) {
                 ok = mbar_wait(acc_ready, c & 1);
                 if (!ok) break;
                 tc_fence_after();
+                if (whole && c > 0) {                           // the previous chain's additions have been performed: one order per element
+                    if (lane == 0) AB_BULK_WAIT(0);
+                    __syncwarp();
+                }
 #pragma unroll
                 for (int which = 0; which < 2; which++) {          // dK (columns 0..127), then dV (128..255): four loads in flight, one wait
                     uint32_t v0[32], v1[32], v2[32], v3[32];
@@ -275,8 +329,25 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
                         __syncwarp();
                         if (lane == 0) af_arrive(acc_free);
                     }
-                    if (live) {
-                        const float f = which ? fv : fk;
+                    const float f = which ? fv : fk;
+                    if (whole) {
+#define AB_STAGE_PIECE(v, pc)                                                                                                              \
+                        {                                                                                                                  \
+                            const uint32_t buf = stg + (uint32_t)((pieces & 1) * 4096);                                                    \
+                            if (pieces >= 2) { if (lane == 0) AB_BULK_WAIT_READ(1); __syncwarp(); }     /* the tile staged here two pieces ago has been read */ \
+                            _Pragma("unroll")                                                                                              \
+                            for (int i = 0; i < 8; i++)                                                                                    \
+                                ab_sts4(buf + (uint32_t)(lane * 128 + ((i ^ (lane & 7)) << 4)),                                            \
+                                        __float_as_uint(__uint_as_float(v[4 * i]) * f), __float_as_uint(__uint_as_float(v[4 * i + 1]) * f), \
+                                        __float_as_uint(__uint_as_float(v[4 * i + 2]) * f), __float_as_uint(__uint_as_float(v[4 * i + 3]) * f)); \
+                            AB_FENCE_ASYNC();                                                                                              \
+                            __syncwarp();                                                                                                  \
+                            if (lane == 0) { ab_tma_add(which ? &mdV : &mdK, buf, col0 + (pc) * 32, row0); AB_BULK_COMMIT(); }             \
+                            pieces++;                                                                                                      \
+                        }
+                        AB_STAGE_PIECE(v0, 0) AB_STAGE_PIECE(v1, 1) AB_STAGE_PIECE(v2, 2) AB_STAGE_PIECE(v3, 3)
+#undef AB_STAGE_PIECE
+                    } else if (live) {
                         float* dst = which ? rowv : rowk;
 #pragma unroll
                         for (int i = 0; i < 8; i++) {
@@ -288,6 +359,7 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
                     }
                 }
             }
+            if (lane == 0) AB_BULK_WAIT_READ(0);               // the staging buffers are read out before the CTA gives its shared memory back
             if (!ok && lane == 0) atomicExch(status, SB_ERR_TIMEOUT);
         }
     } else {
@@ -326,30 +398,27 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
                 for (int i = 0; i < 16; i++) z[i] = make_uint4(0, 0, 0, 0);
             }
         }
-        // this lane's query of a step (lanes 0..15 of the warp matter): log-sum-exp and D, loaded one step ahead, handed round by shuffles
-        float nxL = 0.f, nxD = 0.f;
-        {
-            const int ql = j0 * AB_BQ + ch * 16 + (lane & 15);
-            if (ql < S) { nxL = __ldg(&lse[(size_t)(t0 + ql) * Hq + kvh * g]); nxD = __ldg(&D[(size_t)(t0 + ql) * Hq + kvh * g]); }
-        }
+        const uint32_t ews = smem_u32(smem + AB_OFF_EWS + (warp - 4) * 4096);
+        const int srow0 = k0 + q * 32;                          // first key row of this warp's tiles of dS^T
+        int hi = 0, j = j0;                                     // query head within the group, query block
         for (int t = 0; t < nsteps && ok; t++) {
-            const int e = t & 1, hi = t / per_head, j = j0 + t % per_head;
+            const int e = t & 1;
             const int q0 = j * AB_BQ;
-            const float myL2 = nxL * 1.4426950408889634f, myD = nxD;
-            if (t + 1 < nsteps) {
-                const int h1 = kvh * g + (t + 1) / per_head, ql = (j0 + (t + 1) % per_head) * AB_BQ + ch * 16 + (lane & 15);
-                nxL = 0.f; nxD = 0.f;
-                if (ql < S) { nxL = __ldg(&lse[(size_t)(t0 + ql) * Hq + h1]); nxD = __ldg(&D[(size_t)(t0 + ql) * Hq + h1]); }
-            }
             ok = mbar_wait(&sdp_full[e], (t >> 1) & 1);
             if (!ok) break;
             tc_fence_after();
             const size_t hb = (size_t)(b * g + hi) * Hkv + kvh;
-            __half* o1 = dS1 + (hb * Sp + (size_t)kg) * Sp + q0 + ch * 16;
-            __half* o2 = dS2 + (hb * Sp + (size_t)kg) * Sp + q0 + ch * 16;
             uint32_t sr[16], dr[16];
             ab_ld16(tmem_base + lane_addr + (uint32_t)(AB_COL_S(e) + ch * 16), sr);
             ab_ld16(tmem_base + lane_addr + (uint32_t)(AB_COL_DP(e) + ch * 16), dr);
+            // log-sum-exp (times log2 e) and D of this warp's 16 queries: the same addresses for every lane
+            float4 L4[4], D4[4];
+            {
+                const size_t o = ((size_t)(b * Hq + kvh * g + hi)) * Sp + q0 + ch * 16;
+                const float4* lp = (const float4*)(LT + o); const float4* dp = (const float4*)(DT + o);
+#pragma unroll
+                for (int i = 0; i < 4; i++) { L4[i] = __ldg(lp + i); D4[i] = __ldg(dp + i); }
+            }
             ab_ld_wait2(sr, dr);
             uint32_t p1[8], p2[8], d1[8], d2[8];
 #pragma unroll
@@ -358,7 +427,9 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
 #pragma unroll
                 for (int w = 0; w < 2; w++) {
                     const int c = 2 * i + w;
-                    const float L2 = __shfl_sync(0xffffffffu, myL2, c), Dq = __shfl_sync(0xffffffffu, myD, c);
+                    const float4 l4 = L4[c >> 2], dq4 = D4[c >> 2];
+                    const float L2 = (c & 3) == 0 ? l4.x : (c & 3) == 1 ? l4.y : (c & 3) == 2 ? l4.z : l4.w;
+                    const float Dq = (c & 3) == 0 ? dq4.x : (c & 3) == 1 ? dq4.y : (c & 3) == 2 ? dq4.z : dq4.w;
                     const int qi = q0 + ch * 16 + c;
                     const bool valid = kg <= qi && qi < S && kg < S;
                     const float y = fmaf(__uint_as_float(sr[c]), cs, 14.f - L2);
@@ -378,10 +449,23 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
             tc_fence_before();
             __syncwarp();
             if (lane == 0) af_arrive(&p_full[e]);
-            // dS^T parts of this key row to memory: 16 queries = 32 bytes per part
-            *(uint4*)(o1) = make_uint4(d1[0], d1[1], d1[2], d1[3]); *(uint4*)(o1 + 8) = make_uint4(d1[4], d1[5], d1[6], d1[7]);
-            *(uint4*)(o2) = make_uint4(d2[0], d2[1], d2[2], d2[3]); *(uint4*)(o2 + 8) = make_uint4(d2[4], d2[5], d2[6], d2[7]);
+            // dS^T parts of this key row, 16 queries = 32 bytes per part, into this warp's two tiles; one lane hands them to the TMA unit
+            {
+                const uint32_t buf = ews + (uint32_t)(e * 2048);
+                if (t >= 2) { if (lane == 0) AB_BULK_WAIT_READ(1); __syncwarp(); }          // the tiles staged here two steps ago have been read
+                ab_sts4(buf + lane * 32, d1[0], d1[1], d1[2], d1[3]); ab_sts4(buf + lane * 32 + 16, d1[4], d1[5], d1[6], d1[7]);
+                ab_sts4(buf + 1024 + lane * 32, d2[0], d2[1], d2[2], d2[3]); ab_sts4(buf + 1024 + lane * 32 + 16, d2[4], d2[5], d2[6], d2[7]);
+                AB_FENCE_ASYNC();
+                __syncwarp();
+                if (lane == 0) {
+                    const int y = (int)(hb * Sp) + srow0, x = q0 + ch * 16;
+                    ab_tma_store(&mS1, buf, x, y); ab_tma_store(&mS2, buf + 1024, x, y);
+                    AB_BULK_COMMIT();
+                }
+            }
+            if (++j == nq) { j = j0; hi++; }
         }
+        if (lane == 0) AB_BULK_WAIT_READ(0);                   // the staging tiles are read out before the CTA gives its shared memory back
         if (!ok && lane == 0) atomicExch(status, SB_ERR_TIMEOUT);
     }
     tc_fence_before();
@@ -399,7 +483,7 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
 extern "C" int sb_attention_fused_dkv(sb_ctx_t* c, const void* q1, const void* q2, const void* do1, const void* do2,
                                       const void* k1, const void* k2, const void* v1, const void* v2,
                                       const float* amax_q, const float* amax_k, const float* amax_v, const float* amax_do, const float* ds_bound,
-                                      const float* lse, const float* D, void* dS1, void* dS2, float* dK, float* dV,
+                                      const float* lse, const float* D, void* dS1, void* dS2, float* LT, float* DT, float* dK, float* dV,
                                       int Sp, int T, int Hq, int Hkv, int hd) {
     if (hd != AF_HD || (Sp % 256) || Hkv <= 0 || Hq % Hkv || !tc_load_encode()) return 1;
     if (c->h_seq_n <= 0 || c->h_seq_n > AF_MAXSEQ) return 1;
@@ -416,19 +500,42 @@ extern "C" int sb_attention_fused_dkv(sb_ctx_t* c, const void* q1, const void* q
     for (int b = 0; b < c->h_seq_n; b++) Smax = max(Smax, c->h_seq[b + 1] - c->h_seq[b]);
     if (Smax <= 0 || Smax > Sp) return 1;
     const int qd = Hq * hd, kvd = Hkv * hd, nkb = (Smax + AB_BK - 1) / AB_BK;
-    CUtensorMap mQ1, mQ2, mD1, mD2, mV1, mV2;
+    CUtensorMap mQ1, mQ2, mD1, mD2, mV1, mV2, mS1, mS2, mdK, mdV;
     if (!af_make_map(&mQ1, q1, T, qd, AB_BQ) || !af_make_map(&mQ2, q2, T, qd, AB_BQ) ||
         !af_make_map(&mD1, do1, T, qd, AB_BQ) || !af_make_map(&mD2, do2, T, qd, AB_BQ) ||
         !tc_aligned16(k1) || !tc_aligned16(k2) ||
         !af_make_map(&mV1, v1, T, kvd, AB_BK) || !af_make_map(&mV2, v2, T, kvd, AB_BK)) return 1;
+    {
+        // dS^T parts: [head slots x Sp keys][Sp queries] halfs, tiles of 16 queries x 32 keys, plain rows of 32 bytes in shared memory;
+        // dK, dV: [T][kvd] floats, tiles of 32 columns x 32 keys, 128-byte swizzle
+        const cuuint64_t slots = (cuuint64_t)seqs.n * Hq;
+        cuuint64_t sd[2] = {(cuuint64_t)Sp, slots * (cuuint64_t)Sp}, ss[1] = {(cuuint64_t)Sp * 2};
+        cuuint32_t sbx[2] = {16u, 32u}, est[2] = {1, 1};
+        cuuint64_t gd[2] = {(cuuint64_t)kvd, (cuuint64_t)T}, gs[1] = {(cuuint64_t)kvd * 4};
+        cuuint32_t gbx[2] = {32u, 32u};
+        if (slots * (cuuint64_t)Sp > 0x7fffffffull || !tc_aligned16(dS1) || !tc_aligned16(dS2) ||
+            g_tc_encode(&mS1, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, dS1, sd, ss, sbx, est, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS ||
+            g_tc_encode(&mS2, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, dS2, sd, ss, sbx, est, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS ||
+            g_tc_encode(&mdK, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, dK, gd, gs, gbx, est, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS ||
+            g_tc_encode(&mdV, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, dV, gd, gs, gbx, est, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return 1;
+    }
     const long blocks = (long)nkb * seqs.n * Hkv;
     // pairs per chunk: their Q and dO parts (8 bytes per element) within about a third of the L2
     const size_t pair_bytes = (size_t)(Hq / Hkv) * Smax * hd * 8;
     int chunk = (int)((size_t)(40u << 20) / pair_bytes);
     chunk = max(1, min(chunk, seqs.n * Hkv));
     if (blocks > 0x7fffffffL) return 1;
+    {
+        const size_t n = (size_t)seqs.n * Hq * Sp;
+        at_lse_d_rows_kernel<<<(unsigned)((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184), 256, 0, (cudaStream_t)c->pub.stream>>>(lse, D, LT, DT, seqs, Hq, Sp);
+        c->launches++;
+    }
     at_dkv_bwd_kernel<<<(unsigned)blocks, AB_THREADS, AB_SMEM, (cudaStream_t)c->pub.stream>>>(
-        mQ1, mQ2, mD1, mD2, mV1, mV2, (const __half*)k1, (const __half*)k2, lse, D, (__half*)dS1, (__half*)dS2, dK, dV,
+        mQ1, mQ2, mD1, mD2, mV1, mV2, mS1, mS2, mdK, mdV, (const __half*)k1, (const __half*)k2, LT, DT, (__half*)dS1, (__half*)dS2, dK, dV,
         amax_q, amax_k, amax_v, amax_do, ds_bound, seqs, Sp, Hq, Hq / Hkv, nkb, chunk, 1.0f / sqrtf((float)hd), c->d_status);
     c->launches++;
     return cudaGetLastError() == cudaSuccess ? 0 : 1;

@@ -444,12 +444,13 @@ extern "C" int sb_attention_tc_backward(sb_ctx_t* c, const float* Q, const float
     // the FP16 parts of dS^T (4 bytes per score, [sequence][group member][K-V head][key][query]); dQ is then one product per
     // sequence and group member.  seraph_b200_set_attn_flash(ctx, 2) or SERAPH_B200_ATTN_FLASH=2 selects the older
     // score-materialising path, 3 this one, for every shape.
-    // attn_flash 3: always; 1 (default): where it measured faster than the score-materialising path - without head grouping, or
-    // with sequences of 3072 tokens and more (at 2048 tokens with two query heads per K/V head the older path is 8 % ahead)
-    const bool dkv_fused = f16 && (c->attn_flash == 3 || (c->attn_flash == 1 && (g == 1 || Smax >= 3072))) && !c->attn_fused && hd == 128 &&
+    // attn_flash 1 (default) and 3 take this path (it measured faster at every shape tried: 16 % at 2048 tokens with two query heads
+    // per K/V head, 30 % without head grouping)
+    const bool dkv_fused = f16 && (c->attn_flash == 3 || c->attn_flash == 1) && !c->attn_fused && hd == 128 &&
                            c->h_seq_n <= 240 && !all_scores;
     size_t need = all_scores ? (n_all * 8 > group_bytes ? n_all * 8 : group_bytes) : group_bytes;
-    if (dkv_fused && n_all * 4 > need) need = n_all * 4;
+    const size_t n_rows = (size_t)c->h_seq_n * Hq * Sp;             // log-sum-exp and D by [sequence][head][query] for the on-chip kernel
+    if (dkv_fused && n_all * 4 + 2 * n_rows * sizeof(float) > need) need = n_all * 4 + 2 * n_rows * sizeof(float);
     float* bb = (float*)sb_gemm_stage(c, 3, need);
     if (!st0 || !bb) return 1;
     float* D = st0;
@@ -495,7 +496,7 @@ extern "C" int sb_attention_tc_backward(sb_ctx_t* c, const float* Q, const float
             cudaMemsetAsync(dV, 0, n_kv * sizeof(float), s0);
         }
         if (sb_attention_fused_dkv(c, pq.h1, pq.h2, pdo.h1, pdo.h2, pk.h1, pk.h2, pv.h1, pv.h2, pq.amax, pk.amax, pv.amax, pdo.amax,
-                                   consts + 1, lse, D, a, a + n_all, dK, dV, Sp, T, Hq, Hkv, hd) == 0) {
+                                   consts + 1, lse, D, a, a + n_all, (float*)(a + 2 * n_all), (float*)(a + 2 * n_all) + n_rows, dK, dV, Sp, T, Hq, Hkv, hd) == 0) {
             const int ns2 = at_fork(c, c->h_seq_n);
             const long sb = (long)Sp * Sp;
             for (int b = 0; b < c->h_seq_n && ok; b++) {

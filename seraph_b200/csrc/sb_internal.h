@@ -245,8 +245,8 @@ int  sb_attention_fused_scores(sb_ctx_t*, const void* q1, const void* q2, const 
                                int t0, int S, int Sp, int T, int Hq, int Hkv, int hd, int head0, int head_step, int nb);
 int  sb_attention_fused_dkv(sb_ctx_t*, const void* q1, const void* q2, const void* do1, const void* do2, const void* k1, const void* k2,
                             const void* v1, const void* v2, const float* amax_q, const float* amax_k, const float* amax_v, const float* amax_do,
-                            const float* ds_bound, const float* lse, const float* D, void* dS1, void* dS2, float* dK, float* dV,
-                            int Sp, int T, int Hq, int Hkv, int hd);
+                            const float* ds_bound, const float* lse, const float* D, void* dS1, void* dS2, float* lse_rows, float* d_rows, float* dK, float* dV,
+                            int Sp, int T, int Hq, int Hkv, int hd);     /* lse_rows, d_rows: scratch of sequences x Hq x Sp floats each */
 int  sb_attention_tc_forward(sb_ctx_t*, const float* Q, const float* K, const float* V, float* O, float* lse, int T, int Hq, int Hkv, int hd);
 int  sb_attention_tc_backward(sb_ctx_t*, const float* Q, const float* K, const float* V, const float* O, const float* lse, const float* dO,
                               float* dQ, float* dK, float* dV, int accumulate_kv, int T, int Hq, int Hkv, int hd);

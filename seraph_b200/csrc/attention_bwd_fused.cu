@@ -29,8 +29,9 @@
 // Everything that leaves the CTA goes through shared memory and the TMA unit.  With one key row per thread (the layout
 // tensor memory gives), a warp's direct stores and reductions touch 32 different rows per instruction, 32 memory
 // transactions each; cycle counters in the warps showed the load/store unit busy two thirds of a step with them and the
-// elementwise warps, which bound the step, waiting on it.  So each elementwise warp stages its 32 rows x 16 queries of dS^T
-// parts in shared memory and stores them as two tiles, each drain warp stages 32 rows x 32 columns of a chain at a time
+// elementwise warps, which bound the step, waiting on it.  So the elementwise warps stage a step's dS^T parts in shared memory
+// and one thread stores them as two tiles of 128 keys x 32 queries (a store per warp cost the issuing lane 500 cycles a step: the
+// TMA unit takes few, large requests), each drain warp stages 32 rows x 32 columns of a chain at a time
 // (128-byte swizzle, conflict-free for row-per-lane writes) and adds it with a TMA reduction, and the log-sum-exp and the row
 // dot products D are read from copies transposed to [sequence][head][query] (at_lse_d_rows_kernel), 16 consecutive queries as
 // four 16-byte loads from one address for the whole warp.  A key block that reaches past its sequence's end keeps the
@@ -39,6 +40,7 @@
 // Warps (16): 0 TMA producer, 1 MMA issuer (owns the tensor-memory allocation), 4-11 elementwise (a lane quarter and half of
 // a step's queries each), 12-15 drain.  Every mbarrier wait is bounded; a wait that runs out sets the status word and the CTA drains
 // and frees its tensor memory.
+#include <type_traits>
 #include "attention_fused.cuh"
 
 #define AB_BK 128                 // keys per CTA
@@ -50,8 +52,9 @@
 #define AB_OFF_V 0
 #define AB_OFF_ST AB_KV_BYTES
 #define AB_STAGE_BYTES 32768      // Q parts 16 KB, dO parts 16 KB
-#define AB_OFF_EWS (AB_OFF_ST + AB_STAGES * AB_STAGE_BYTES)      // per elementwise warp 2 buffers x (hi tile 1 KB + lo tile 1 KB): 32 rows x 32 bytes each
-#define AB_OFF_DRS (AB_OFF_EWS + 8 * 4096)                       // per drain warp 2 buffers x 4 KB: 32 rows x 32 floats, 128-byte swizzle
+#define AB_OFF_EWS (AB_OFF_ST + AB_STAGES * AB_STAGE_BYTES)      // dS^T staging: 2 buffers x (hi tile 8 KB, lo tile 8 KB); a tile is 128 keys x 32 queries (64-byte rows)
+#define AB_OFF_DRS (AB_OFF_EWS + 2 * 16384)                      // per drain warp 2 buffers x 4 KB: 32 rows x 32 floats, 128-byte swizzle
+                                                                 // (before the first step these 64 KB receive the parts of K on their way to tensor memory)
 #define AB_OFF_BAR (AB_OFF_DRS + 4 * 8192)
 #define AB_SMEM (AB_OFF_BAR + 1024 + 1024)
 #define AB_REGS_LIGHT 72          // producer / MMA issuer warpgroup
@@ -105,15 +108,17 @@ __device__ __forceinline__ void ab_tma_add(const CUtensorMap* map, uint32_t src,
 #define AB_BULK_WAIT(n) asm volatile("cp.async.bulk.wait_group %0;" ::"n"(n) : "memory")
 #define AB_FENCE_ASYNC() asm volatile("fence.proxy.async.shared::cta;" ::: "memory")
 
-// lse and D, [token][head], as [sequence][head][Sp queries] (zeros past the sequence's end); lse comes out times log2(e)
+// lse and D, [token][head], as [sequence][head][Sp queries] (zeros past the sequence's end), in the form the elementwise warps use:
+// 14 - lse log2(e) (the probabilities are formed times 2^14) and D times the factor that takes P 2^14 (dP - D) to the scaled dS
 __global__ void at_lse_d_rows_kernel(const float* __restrict__ lse, const float* __restrict__ D, float* __restrict__ LT, float* __restrict__ DT,
-                                     const __grid_constant__ AfSeqs seqs, int Hq, int Sp) {
+                                     const __grid_constant__ AfSeqs seqs, int Hq, int Sp, const float* __restrict__ ds_bound, float scale) {
     const size_t n = (size_t)seqs.n * Hq * Sp;
+    const float dsc = tc_pow2(tc_f16_shift(__ldg(ds_bound))) * scale * (1.0f / 16384.f);
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const int q = (int)(i % Sp), h = (int)((i / Sp) % Hq), b = (int)(i / ((size_t)Sp * Hq));
         const int t0 = seqs.start[b], S = seqs.start[b + 1] - t0;
         float l = 0.f, d = 0.f;
-        if (q < S) { l = __ldg(&lse[(size_t)(t0 + q) * Hq + h]) * 1.4426950408889634f; d = __ldg(&D[(size_t)(t0 + q) * Hq + h]); }
+        if (q < S) { l = 14.f - __ldg(&lse[(size_t)(t0 + q) * Hq + h]) * 1.4426950408889634f; d = __ldg(&D[(size_t)(t0 + q) * Hq + h]) * dsc; }
         LT[i] = l; DT[i] = d;
     }
 }
@@ -121,10 +126,10 @@ __global__ void at_lse_d_rows_kernel(const float* __restrict__ lse, const float*
 __global__ void __launch_bounds__(AB_THREADS, 1)
 at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant__ CUtensorMap mQ2,
                   const __grid_constant__ CUtensorMap mD1, const __grid_constant__ CUtensorMap mD2,
+                  const __grid_constant__ CUtensorMap mK1, const __grid_constant__ CUtensorMap mK2,
                   const __grid_constant__ CUtensorMap mV1, const __grid_constant__ CUtensorMap mV2,
                   const __grid_constant__ CUtensorMap mS1, const __grid_constant__ CUtensorMap mS2,
                   const __grid_constant__ CUtensorMap mdK, const __grid_constant__ CUtensorMap mdV,
-                  const __half* __restrict__ k1, const __half* __restrict__ k2,
                   const float* __restrict__ LT, const float* __restrict__ DT,
                   __half* __restrict__ dS1, __half* __restrict__ dS2, float* __restrict__ dK, float* __restrict__ dV,
                   const float* __restrict__ amax_q, const float* __restrict__ amax_k, const float* __restrict__ amax_v,
@@ -166,11 +171,13 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
     uint64_t* acc_ready = p_full + 2;                  // 1
     uint64_t* acc_free = acc_ready + 1;                // 1
     uint64_t* k_ready = acc_free + 1;                  // 1: K in tensor memory
-    uint32_t* tmem_slot = (uint32_t*)(k_ready + 1);
+    uint64_t* k_full = k_ready + 1;                    // 1: K in shared memory, on its way there
+    uint64_t* ew_sync = k_full + 1;                    // 1: the elementwise warps have staged their rows of a step's dS^T tiles
+    uint32_t* tmem_slot = (uint32_t*)(ew_sync + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        mbar_init(kv_full, 1); mbar_init(acc_ready, 1); mbar_init(acc_free, 4); mbar_init(k_ready, 8);
+        mbar_init(kv_full, 1); mbar_init(acc_ready, 1); mbar_init(acc_free, 4); mbar_init(k_ready, 8); mbar_init(k_full, 1); mbar_init(ew_sync, 8);
         for (int i = 0; i < AB_STAGES; i++) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
         for (int i = 0; i < 2; i++) { mbar_init(&sdp_full[i], 1); mbar_init(&p_full[i], 8); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -190,6 +197,11 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
         if (warp == 0) {
             // ---------------- TMA producer ----------------
             if (elect_one()) {
+                mbar_expect_tx(k_full, AB_KV_BYTES);
+                for (int p = 0; p < 2; p++) {
+                    af_tma_2d(smem + AB_OFF_EWS + p * 16384, &mK1, k_full, kvh * AF_HD + p * 64, t0 + k0);
+                    af_tma_2d(smem + AB_OFF_EWS + 32768 + p * 16384, &mK2, k_full, kvh * AF_HD + p * 64, t0 + k0);
+                }
                 mbar_expect_tx(kv_full, AB_KV_BYTES);
                 for (int p = 0; p < 2; p++) {
                     af_tma_2d(smem + AB_OFF_V + p * 16384, &mV1, kv_full, kvh * AF_HD + p * 64, t0 + k0);
@@ -305,6 +317,7 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
             float* rowv = dV + (size_t)(t0 + (live ? kg : 0)) * kvd + (size_t)kvh * AF_HD;
             const uint32_t ta = tmem_base + ((uint32_t)(q * 32) << 16);
             const bool whole = k0 + AB_BK <= S;                // all 128 keys belong to this sequence: tiles through the TMA unit
+            ok = mbar_wait(k_ready, 0);                         // the staging area held the parts of K until now
             const uint32_t stg = smem_u32(smem + AB_OFF_DRS + q * 8192);
             const int row0 = t0 + k0 + q * 32, col0 = kvh * AF_HD;
             int pieces = 0;                                     // tiles this warp has handed to the TMA unit
@@ -368,19 +381,21 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
         const int ch = (warp - 4) >> 2, q = warp & 3, r = q * 32 + lane, kg = k0 + r;
         const float cs = tc_pow2(-tc_f16_shift(__ldg(amax_q))) * tc_pow2(-tc_f16_shift(__ldg(amax_k))) * (scale * 1.4426950408889634f);
         const float cp = tc_pow2(-tc_f16_shift(__ldg(amax_do))) * tc_pow2(-tc_f16_shift(__ldg(amax_v)));
-        const float dsc = tc_pow2(tc_f16_shift(__ldg(ds_bound))) * scale * (1.0f / 16384.f);      // p holds P * 2^14
+        const float cpd = cp * (tc_pow2(tc_f16_shift(__ldg(ds_bound))) * scale * (1.0f / 16384.f));      // p holds P * 2^14
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-        // This key row's parts of K into tensor memory: head-dimension k-steps ch*4 .. ch*4+3, 32 bytes of each part per k-step,
-        // two consecutive halfs per column as they lie in memory (rows past the sequence's end: zeros, their scores are masked anyway)
+        // This key row's parts of K from shared memory (four 128-byte-swizzled tiles: hi and lo part of each half of the head
+        // dimension) into tensor memory: head-dimension k-steps ch*4 .. ch*4+3 are half `ch`, two consecutive halfs per column
+        ok = mbar_wait(k_full, 0);
         {
-            const uint4* g1 = (const uint4*)(k1 + (size_t)(t0 + kg) * kvd + (size_t)kvh * AF_HD) + ch * 8;
-            const uint4* g2 = (const uint4*)(k2 + (size_t)(t0 + kg) * kvd + (size_t)kvh * AF_HD) + ch * 8;
+            const uint32_t kt = smem_u32(smem + AB_OFF_EWS + ch * 16384) + (uint32_t)(r * 128);
 #pragma unroll
             for (int kk = 0; kk < 4; kk++) {
-                uint4 a = make_uint4(0, 0, 0, 0), bq = a, c2 = a, d2 = a;
-                if (kg < S) { a = __ldg(g1 + 2 * kk); bq = __ldg(g1 + 2 * kk + 1); c2 = __ldg(g2 + 2 * kk); d2 = __ldg(g2 + 2 * kk + 1); }
-                const uint32_t h8[8] = {a.x, a.y, a.z, a.w, bq.x, bq.y, bq.z, bq.w};
-                const uint32_t l8[8] = {c2.x, c2.y, c2.z, c2.w, d2.x, d2.y, d2.z, d2.w};
+                uint32_t h8[8], l8[8];
+                const uint32_t c0 = (uint32_t)(((2 * kk) ^ (r & 7)) << 4), c1 = (uint32_t)(((2 * kk + 1) ^ (r & 7)) << 4);
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(h8[0]), "=r"(h8[1]), "=r"(h8[2]), "=r"(h8[3]) : "r"(kt + c0) : "memory");
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(h8[4]), "=r"(h8[5]), "=r"(h8[6]), "=r"(h8[7]) : "r"(kt + c1) : "memory");
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(l8[0]), "=r"(l8[1]), "=r"(l8[2]), "=r"(l8[3]) : "r"(kt + 32768 + c0) : "memory");
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(l8[4]), "=r"(l8[5]), "=r"(l8[6]), "=r"(l8[7]) : "r"(kt + 32768 + c1) : "memory");
                 ab_st8(tmem_base + lane_addr + (uint32_t)(AB_COL_K + (ch * 4 + kk) * 16), h8);
                 ab_st8(tmem_base + lane_addr + (uint32_t)(AB_COL_K + (ch * 4 + kk) * 16 + 8), l8);
             }
@@ -389,17 +404,33 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
             __syncwarp();
             if (lane == 0) af_arrive(k_ready);
         }
-        // Columns before this key block that the dQ product reads together with it (its query tiles are 256 wide): zeros
-        if ((k0 & 255) != 0) {
-            for (int hi = 0; hi < g; hi++) {
-                const size_t hb = (size_t)(b * g + hi) * Hkv + kvh;
-                uint4* z = (uint4*)((ch ? dS2 : dS1) + (hb * Sp + (size_t)kg) * Sp + (k0 - 128));
-#pragma unroll
-                for (int i = 0; i < 16; i++) z[i] = make_uint4(0, 0, 0, 0);
+        ok = ok && mbar_wait(k_ready, 0);                       // every warp has its rows of K out of the staging area
+        const uint32_t ews = smem_u32(smem + AB_OFF_EWS);
+        const bool issuer = warp == 4 && lane == 0;            // hands the staged tiles to the TMA unit
+        // Columns before this key block that the dQ product reads together with it (its query tiles are 256 wide): zeros, stored
+        // from a tile of zeros that sits where the second step will stage its hi parts
+        // ew_sync counts one phase per hand-over: a warp arrives when its rows are staged; the issuing thread waits for all eight, and
+        // before it arrives it makes sure that everything it handed over earlier has been read.  So a completed phase n tells every
+        // warp that the tiles handed over in phases < n are read out: a buffer is written again one phase after the next.
+        int sync_n = 0;
+        if ((k0 & 255) != 0 && ok) {
+            ab_sts4(ews + 16384 + (uint32_t)((warp - 4) * 1024 + lane * 32), 0, 0, 0, 0);
+            ab_sts4(ews + 16384 + (uint32_t)((warp - 4) * 1024 + lane * 32 + 16), 0, 0, 0, 0);
+            AB_FENCE_ASYNC();
+            __syncwarp();
+            if (lane == 0) af_arrive(ew_sync);
+            if (warp == 4) {
+                ok = mbar_wait(ew_sync, 0);
+                if (issuer && ok) {
+                    for (int hi = 0; hi < g; hi++) {
+                        const int y = (int)(((size_t)(b * g + hi) * Hkv + kvh) * Sp) + k0;
+                        for (int i = 0; i < 4; i++) { ab_tma_store(&mS1, ews + 16384, k0 - 128 + i * 32, y); ab_tma_store(&mS2, ews + 16384, k0 - 128 + i * 32, y); }
+                    }
+                    AB_BULK_COMMIT();
+                }
             }
+            sync_n = 1;
         }
-        const uint32_t ews = smem_u32(smem + AB_OFF_EWS + (warp - 4) * 4096);
-        const int srow0 = k0 + q * 32;                          // first key row of this warp's tiles of dS^T
         int hi = 0, j = j0;                                     // query head within the group, query block
         for (int t = 0; t < nsteps && ok; t++) {
             const int e = t & 1;
@@ -421,24 +452,29 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
             }
             ab_ld_wait2(sr, dr);
             uint32_t p1[8], p2[8], d1[8], d2[8];
+            // away from the diagonal and from the sequence's end no element of the step is masked
+            const bool nomask = q0 >= k0 + AB_BK && q0 + AB_BQ <= S && k0 + AB_BK <= S;
+            auto columns = [&](auto masked) {
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                float pv[2], dv[2];
+                for (int i = 0; i < 8; i++) {
+                    float pv[2], dv[2];
 #pragma unroll
-                for (int w = 0; w < 2; w++) {
-                    const int c = 2 * i + w;
-                    const float4 l4 = L4[c >> 2], dq4 = D4[c >> 2];
-                    const float L2 = (c & 3) == 0 ? l4.x : (c & 3) == 1 ? l4.y : (c & 3) == 2 ? l4.z : l4.w;
-                    const float Dq = (c & 3) == 0 ? dq4.x : (c & 3) == 1 ? dq4.y : (c & 3) == 2 ? dq4.z : dq4.w;
-                    const int qi = q0 + ch * 16 + c;
-                    const bool valid = kg <= qi && qi < S && kg < S;
-                    const float y = fmaf(__uint_as_float(sr[c]), cs, 14.f - L2);
-                    pv[w] = valid ? af_ex2(y) : 0.f;                                             // P * 2^14
-                    dv[w] = pv[w] * (__uint_as_float(dr[c]) * cp - Dq) * dsc;
+                    for (int w = 0; w < 2; w++) {
+                        const int c = 2 * i + w;
+                        const float4 l4 = L4[c >> 2], dq4 = D4[c >> 2];
+                        const float Lq = (c & 3) == 0 ? l4.x : (c & 3) == 1 ? l4.y : (c & 3) == 2 ? l4.z : l4.w;      // 14 - lse log2 e
+                        const float Dq = (c & 3) == 0 ? dq4.x : (c & 3) == 1 ? dq4.y : (c & 3) == 2 ? dq4.z : dq4.w;  // D dsc
+                        const int qi = q0 + ch * 16 + c;
+                        const bool valid = !decltype(masked)::value || (kg <= qi && qi < S && kg < S);
+                        const float y = fmaf(__uint_as_float(sr[c]), cs, Lq);
+                        pv[w] = valid ? af_ex2(y) : 0.f;                                             // P * 2^14
+                        dv[w] = pv[w] * fmaf(__uint_as_float(dr[c]), cpd, -Dq);
+                    }
+                    af_split2(pv[0], pv[1], p1[i], p2[i]);
+                    af_split2(dv[0], dv[1], d1[i], d2[i]);
                 }
-                af_split2(pv[0], pv[1], p1[i], p2[i]);
-                af_split2(dv[0], dv[1], d1[i], d2[i]);
-            }
+            };
+            if (nomask) columns(std::false_type{}); else columns(std::true_type{});
             // The parts of these 16 queries go back over the 16 columns their scores came from (all of them are in registers by now):
             // hi part in the first 8 columns, lo part in the next 8, which is where the MMA issuer looks for k-step `ch`.
             ab_st8(tmem_base + lane_addr + (uint32_t)(AB_COL_S(e) + ch * 16), p1);
@@ -449,23 +485,36 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
             tc_fence_before();
             __syncwarp();
             if (lane == 0) af_arrive(&p_full[e]);
-            // dS^T parts of this key row, 16 queries = 32 bytes per part, into this warp's two tiles; one lane hands them to the TMA unit
+            // dS^T parts of this key row, 16 queries = 32 bytes per part, into the step's two tiles (64-byte rows).  The issuing thread
+            // first makes sure that everything it handed over earlier has been read (the other buffer is written in the next step),
+            // then all eight warps meet and it hands this step's tiles to the TMA unit.
             {
-                const uint32_t buf = ews + (uint32_t)(e * 2048);
-                if (t >= 2) { if (lane == 0) AB_BULK_WAIT_READ(1); __syncwarp(); }          // the tiles staged here two steps ago have been read
-                ab_sts4(buf + lane * 32, d1[0], d1[1], d1[2], d1[3]); ab_sts4(buf + lane * 32 + 16, d1[4], d1[5], d1[6], d1[7]);
-                ab_sts4(buf + 1024 + lane * 32, d2[0], d2[1], d2[2], d2[3]); ab_sts4(buf + 1024 + lane * 32 + 16, d2[4], d2[5], d2[6], d2[7]);
+                const uint32_t buf = ews + (uint32_t)(e * 16384);
+                const uint32_t row = buf + (uint32_t)(r * 64 + ch * 32);
+                if (warp != 4 && sync_n > 0) {                  // (the issuer's warp waited for this phase when it handed the tiles over)
+                    ok = mbar_wait(ew_sync, (sync_n - 1) & 1);
+                    if (!ok) break;
+                }
+                ab_sts4(row, d1[0], d1[1], d1[2], d1[3]); ab_sts4(row + 16, d1[4], d1[5], d1[6], d1[7]);
+                ab_sts4(row + 8192, d2[0], d2[1], d2[2], d2[3]); ab_sts4(row + 8192 + 16, d2[4], d2[5], d2[6], d2[7]);
                 AB_FENCE_ASYNC();
                 __syncwarp();
-                if (lane == 0) {
-                    const int y = (int)(hb * Sp) + srow0, x = q0 + ch * 16;
-                    ab_tma_store(&mS1, buf, x, y); ab_tma_store(&mS2, buf + 1024, x, y);
-                    AB_BULK_COMMIT();
+                if (issuer) AB_BULK_WAIT_READ(0);
+                if (lane == 0) af_arrive(ew_sync);
+                if (warp == 4) {
+                    ok = mbar_wait(ew_sync, sync_n & 1);
+                    if (!ok) break;
+                    if (issuer) {
+                        const int y = (int)(hb * Sp) + k0;
+                        ab_tma_store(&mS1, buf, q0, y); ab_tma_store(&mS2, buf + 8192, q0, y);
+                        AB_BULK_COMMIT();
+                    }
                 }
+                sync_n++;
             }
             if (++j == nq) { j = j0; hi++; }
         }
-        if (lane == 0) AB_BULK_WAIT_READ(0);                   // the staging tiles are read out before the CTA gives its shared memory back
+        if (issuer) AB_BULK_WAIT_READ(0);                      // the staging tiles are read out before the CTA gives its shared memory back
         if (!ok && lane == 0) atomicExch(status, SB_ERR_TIMEOUT);
     }
     tc_fence_before();
@@ -500,17 +549,17 @@ extern "C" int sb_attention_fused_dkv(sb_ctx_t* c, const void* q1, const void* q
     for (int b = 0; b < c->h_seq_n; b++) Smax = max(Smax, c->h_seq[b + 1] - c->h_seq[b]);
     if (Smax <= 0 || Smax > Sp) return 1;
     const int qd = Hq * hd, kvd = Hkv * hd, nkb = (Smax + AB_BK - 1) / AB_BK;
-    CUtensorMap mQ1, mQ2, mD1, mD2, mV1, mV2, mS1, mS2, mdK, mdV;
+    CUtensorMap mQ1, mQ2, mD1, mD2, mK1, mK2, mV1, mV2, mS1, mS2, mdK, mdV;
     if (!af_make_map(&mQ1, q1, T, qd, AB_BQ) || !af_make_map(&mQ2, q2, T, qd, AB_BQ) ||
         !af_make_map(&mD1, do1, T, qd, AB_BQ) || !af_make_map(&mD2, do2, T, qd, AB_BQ) ||
-        !tc_aligned16(k1) || !tc_aligned16(k2) ||
+        !af_make_map(&mK1, k1, T, kvd, AB_BK) || !af_make_map(&mK2, k2, T, kvd, AB_BK) ||
         !af_make_map(&mV1, v1, T, kvd, AB_BK) || !af_make_map(&mV2, v2, T, kvd, AB_BK)) return 1;
     {
-        // dS^T parts: [head slots x Sp keys][Sp queries] halfs, tiles of 16 queries x 32 keys, plain rows of 32 bytes in shared memory;
+        // dS^T parts: [head slots x Sp keys][Sp queries] halfs, tiles of 32 queries x 128 keys, plain rows of 64 bytes in shared memory;
         // dK, dV: [T][kvd] floats, tiles of 32 columns x 32 keys, 128-byte swizzle
         const cuuint64_t slots = (cuuint64_t)seqs.n * Hq;
         cuuint64_t sd[2] = {(cuuint64_t)Sp, slots * (cuuint64_t)Sp}, ss[1] = {(cuuint64_t)Sp * 2};
-        cuuint32_t sbx[2] = {16u, 32u}, est[2] = {1, 1};
+        cuuint32_t sbx[2] = {32u, 128u}, est[2] = {1, 1};
         cuuint64_t gd[2] = {(cuuint64_t)kvd, (cuuint64_t)T}, gs[1] = {(cuuint64_t)kvd * 4};
         cuuint32_t gbx[2] = {32u, 32u};
         if (slots * (cuuint64_t)Sp > 0x7fffffffull || !tc_aligned16(dS1) || !tc_aligned16(dS2) ||
@@ -531,11 +580,11 @@ extern "C" int sb_attention_fused_dkv(sb_ctx_t* c, const void* q1, const void* q
     if (blocks > 0x7fffffffL) return 1;
     {
         const size_t n = (size_t)seqs.n * Hq * Sp;
-        at_lse_d_rows_kernel<<<(unsigned)((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184), 256, 0, (cudaStream_t)c->pub.stream>>>(lse, D, LT, DT, seqs, Hq, Sp);
+        at_lse_d_rows_kernel<<<(unsigned)((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184), 256, 0, (cudaStream_t)c->pub.stream>>>(lse, D, LT, DT, seqs, Hq, Sp, ds_bound, 1.0f / sqrtf((float)hd));
         c->launches++;
     }
     at_dkv_bwd_kernel<<<(unsigned)blocks, AB_THREADS, AB_SMEM, (cudaStream_t)c->pub.stream>>>(
-        mQ1, mQ2, mD1, mD2, mV1, mV2, mS1, mS2, mdK, mdV, (const __half*)k1, (const __half*)k2, LT, DT, (__half*)dS1, (__half*)dS2, dK, dV,
+        mQ1, mQ2, mD1, mD2, mK1, mK2, mV1, mV2, mS1, mS2, mdK, mdV, LT, DT, (__half*)dS1, (__half*)dS2, dK, dV,
         amax_q, amax_k, amax_v, amax_do, ds_bound, seqs, Sp, Hq, Hq / Hkv, nkb, chunk, 1.0f / sqrtf((float)hd), c->d_status);
     c->launches++;
     return cudaGetLastError() == cudaSuccess ? 0 : 1;

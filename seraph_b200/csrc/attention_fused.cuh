@@ -58,11 +58,17 @@ __device__ __forceinline__ void af_ld_dep(uint32_t (&r)[32]) { asm volatile("" :
 
 __device__ __forceinline__ float af_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 // two values as FP16 parts: hi = the packed roundings of (x0, x1), lo = the packed roundings of what the roundings left
+// (what is left, x - hi, is formed by the mixed-precision fma hi * -1 + x: exact, and no conversion of hi back to FP32, which
+// shares the slow conversion pipe with the two packed roundings)
 __device__ __forceinline__ void af_split2(float x0, float x1, uint32_t& hi, uint32_t& lo) {
-    const __half2 h = __floats2half2_rn(x0, x1);
-    const float2 b = __half22float2(h);
-    const __half2 l = __floats2half2_rn(x0 - b.x, x1 - b.y);
-    hi = *(const uint32_t*)&h; lo = *(const uint32_t*)&l;
+    asm("{\n\t.reg .b16 h0, h1, m1;\n\t.reg .f32 l0, l1;\n\t"
+        "cvt.rn.f16x2.f32 %0, %3, %2;\n\t"
+        "mov.b32 {h0, h1}, %0;\n\t"
+        "mov.b16 m1, 0xBC00;\n\t"
+        "fma.rn.f32.f16 l0, h0, m1, %2;\n\t"
+        "fma.rn.f32.f16 l1, h1, m1, %3;\n\t"
+        "cvt.rn.f16x2.f32 %1, l1, l0;\n\t}"
+        : "=&r"(hi), "=r"(lo) : "f"(x0), "f"(x1));
 }
 
 // 4 x 4 transpose of 16-byte chunks among the four lanes of a quad: afterwards w[t] of lane c is what w[c] of lane t was

@@ -30,6 +30,7 @@ static struct {
     ncclResult_t (*GetUniqueId)(ncclUniqueId*);
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int);
     ncclResult_t (*CommInitRankConfig)(ncclComm_t*, int, ncclUniqueId, int, ncclConfig_t*);      /* optional */
+    ncclResult_t (*CommSplit)(ncclComm_t, int, int, ncclComm_t*, ncclConfig_t*);                 /* optional */
     ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t);
     ncclResult_t (*CommDestroy)(ncclComm_t);
     ncclResult_t (*CommAbort)(ncclComm_t);
@@ -46,6 +47,7 @@ static int load_nccl(void) {
     SYM(GetUniqueId); SYM(CommInitRank); SYM(AllReduce); SYM(CommDestroy); SYM(CommAbort); SYM(CommGetAsyncError); SYM(GetErrorString);
 #undef SYM
     *(void**)(&N.CommInitRankConfig) = dlsym(h, "ncclCommInitRankConfig");
+    *(void**)(&N.CommSplit) = dlsym(h, "ncclCommSplit");
     N.lib = h;
     return 0;
 }
@@ -77,9 +79,10 @@ int seraph_dp_init(cuda_train_context_t* ctx, int rank, int world, const void* n
     ncclUniqueId id; memcpy(&id, nccl_unique_id, sizeof id);
     ncclComm_t comm;
     /* The all-reduce kernels run beside the backward pass, whose GEMM launches are persistent grids of one CTA pair per SM pair:
-       every SM a collective takes makes a straggler pair.  The gradients of a whole step need well under a tenth of NVLink's
-       bandwidth to finish inside the backward pass, so the communicator is held to a few CTAs (SERAPH_B200_NCCL_MAX_CTAS,
-       default 8; 0 leaves NCCL's own choice). */
+       every SM a collective takes makes a straggler pair that runs its share of the tiles after the others, which can double
+       a product's time.  The gradients of a whole step need well under a tenth of NVLink's bandwidth to finish inside the backward
+       pass, so the communicator is held to a few CTAs (SERAPH_B200_NCCL_MAX_CTAS, default 8; 0 leaves NCCL's own choice), and
+       while buckets are being reduced the GEMM grids are launched that many SMs smaller (gemm_reserve_sms). */
     int max_ctas = 8;
     { const char* e = getenv("SERAPH_B200_NCCL_MAX_CTAS"); if (e && e[0]) max_ctas = atoi(e); }
     ncclResult_t ir;
@@ -89,9 +92,20 @@ int seraph_dp_init(cuda_train_context_t* ctx, int rank, int world, const void* n
         ir = N.CommInitRankConfig(&comm, world, id, rank, &cfg);
     } else ir = N.CommInitRank(&comm, world, id, rank);
     if (nccl_fail(c, ir, "ncclCommInitRank")) return SB_ERR_NCCL;
+    /* The step's last bucket (embedding and final norm, a sixth of the gradients) is reduced after the backward pass, beside
+       AdamW on the layers and no GEMM: a second communicator over the same ranks, without the cap, takes it at full NVLink
+       bandwidth.  SERAPH_B200_NCCL_WIDE=0 switches it off. */
+    ncclComm_t wide = NULL;
+    { const char* e = getenv("SERAPH_B200_NCCL_WIDE");
+      if (N.CommSplit && N.CommInitRankConfig && max_ctas > 0 && !(e && e[0] == '0')) {
+          ncclConfig_t cfg2 = NCCL_CONFIG_INITIALIZER;
+          cfg2.minCTAs = 1; cfg2.maxCTAs = 64;
+          if (N.CommSplit(comm, 0, rank, &wide, &cfg2) != ncclSuccess) wide = NULL;
+      } }
     cudaStream_t cs;
-    if (cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking) != cudaSuccess) { N.CommAbort(comm); return SB_ERR_CUDA; }
-    c->nccl_comm = comm; c->comm_stream = cs; c->dp_rank = rank; c->dp_world = world;
+    if (cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking) != cudaSuccess) { if (wide) N.CommAbort(wide); N.CommAbort(comm); return SB_ERR_CUDA; }
+    c->nccl_comm = comm; c->nccl_comm_wide = wide; c->comm_stream = cs; c->dp_rank = rank; c->dp_world = world;
+    c->dp_ctas = (N.CommInitRankConfig && max_ctas > 0) ? max_ctas : 0; c->gemm_reserve_sms = 0;
     for (int i = 0; i < 64; i++) { cudaEvent_t e; cudaEventCreateWithFlags(&e, cudaEventDisableTiming); c->ev_bucket[i] = e; }
     return SB_OK;
 }
@@ -99,8 +113,9 @@ int seraph_dp_init(cuda_train_context_t* ctx, int rank, int world, const void* n
 /* The communicator is gone (destroyed or aborted): single-GPU from here on.  The stream and the events stay until
  * sb_dp_finalize, because work of the compute stream may still be ordered behind them. */
 static void dp_drop_comm(sb_ctx_t* c, int status) {
+    if (c->nccl_comm_wide) N.CommAbort((ncclComm_t)c->nccl_comm_wide);
     if (c->nccl_comm) N.CommAbort((ncclComm_t)c->nccl_comm);
-    c->nccl_comm = NULL; c->dp_world = 1; c->dp_rank = 0;
+    c->nccl_comm = NULL; c->nccl_comm_wide = NULL; c->dp_world = 1; c->dp_rank = 0; c->gemm_reserve_sms = 0;
     if (status) {
         c->status = status;
         fprintf(stderr, "seraph_b200: data parallelism is off for this context after the failure above; later steps run on this GPU alone\n");
@@ -113,8 +128,9 @@ void sb_dp_finalize(sb_ctx_t* c) {
     if (c->nccl_comm) {
         /* bounded: a peer that died leaves collectives of this rank unfinished for ever */
         if (seraph_dp_wait(&c->pub, DP_FINALIZE_TIMEOUT_MS) == SB_OK && c->nccl_comm) {
+            if (c->nccl_comm_wide) N.CommDestroy((ncclComm_t)c->nccl_comm_wide);
             N.CommDestroy((ncclComm_t)c->nccl_comm);
-            c->nccl_comm = NULL;
+            c->nccl_comm = NULL; c->nccl_comm_wide = NULL;
         }
     }
     if (c->comm_stream) {
@@ -122,28 +138,37 @@ void sb_dp_finalize(sb_ctx_t* c) {
         cudaStreamDestroy((cudaStream_t)c->comm_stream);
         c->comm_stream = NULL;
     }
-    c->nccl_comm = NULL; c->dp_world = 1; c->dp_rank = 0; c->n_buckets = 0;
+    c->nccl_comm = NULL; c->nccl_comm_wide = NULL; c->dp_world = 1; c->dp_rank = 0; c->n_buckets = 0; c->gemm_reserve_sms = 0;
 }
 void seraph_dp_finalize(cuda_train_context_t* ctx) { sb_dp_finalize(sb_priv(ctx)); }
 
 /* Hand a finished gradient range to the communication stream.  Ordering: the
  * compute stream records an event, the communication stream waits for it. */
-int sb_dp_bucket_ready(sb_ctx_t* c, float* p, size_t n) {
+static int dp_bucket(sb_ctx_t* c, float* p, size_t n, int wide);
+int sb_dp_bucket_ready(sb_ctx_t* c, float* p, size_t n) { return dp_bucket(c, p, n, 0); }
+/* a bucket handed over when no GEMM follows it in the step: on the communicator without the CTA cap when there is one */
+int sb_dp_bucket_ready_last(sb_ctx_t* c, float* p, size_t n) { return dp_bucket(c, p, n, 1); }
+static int dp_bucket(sb_ctx_t* c, float* p, size_t n, int wide) {
     if (c->dp_world <= 1 || !n) return 0;
     cudaEvent_t e = (cudaEvent_t)c->ev_bucket[c->n_buckets % 62];      /* 62 and 63 are the join events */
     c->n_buckets++;
+    c->gemm_reserve_sms = (c->dp_ctas + 1) & ~1;                        /* whole SM pairs; until the join */
     if (sb_check(c, cudaEventRecord(e, (cudaStream_t)c->pub.stream), "bucket event")) return 1;
     if (sb_check(c, cudaStreamWaitEvent((cudaStream_t)c->comm_stream, e, 0), "bucket wait")) return 1;
-    return nccl_fail(c, N.AllReduce(p, p, n, ncclFloat32, ncclSum, (ncclComm_t)c->nccl_comm, (cudaStream_t)c->comm_stream), "ncclAllReduce");
+    ncclComm_t comm = (ncclComm_t)((wide && c->nccl_comm_wide) ? c->nccl_comm_wide : c->nccl_comm);
+    return nccl_fail(c, N.AllReduce(p, p, n, ncclFloat32, ncclSum, comm, (cudaStream_t)c->comm_stream), "ncclAllReduce");
 }
 
-/* compute stream waits until the buckets handed over so far are reduced; unlike sb_dp_join, more may follow (the step uses it to
- * start AdamW on the layers while the last bucket, embedding and final norm, is still being reduced) */
-int sb_dp_join_partial(sb_ctx_t* c) {
-    if (c->dp_world <= 1) return 0;
-    cudaEvent_t e = (cudaEvent_t)c->ev_bucket[62];
-    if (sb_check(c, cudaEventRecord(e, (cudaStream_t)c->comm_stream), "partial join event")) return 1;
-    return sb_check(c, cudaStreamWaitEvent((cudaStream_t)c->pub.stream, e, 0), "partial join wait");
+/* A mark on the communication stream behind the buckets handed over so far, and the compute stream's wait for that mark.  Buckets
+ * handed over between the two calls are not waited for: the step marks, hands over its last bucket and then waits, so that AdamW
+ * on the layers runs while the last bucket is still being reduced. */
+int sb_dp_mark_partial(sb_ctx_t* c) {
+    if (c->dp_world <= 1) return 1;
+    return sb_check(c, cudaEventRecord((cudaEvent_t)c->ev_bucket[62], (cudaStream_t)c->comm_stream), "partial join event");
+}
+int sb_dp_wait_partial(sb_ctx_t* c) {
+    if (c->dp_world <= 1) return 1;
+    return sb_check(c, cudaStreamWaitEvent((cudaStream_t)c->pub.stream, (cudaEvent_t)c->ev_bucket[62], 0), "partial join wait");
 }
 
 /* compute stream waits until every bucket handed over so far is reduced */
@@ -152,7 +177,7 @@ int sb_dp_join(sb_ctx_t* c) {
     cudaEvent_t e = (cudaEvent_t)c->ev_bucket[63];
     if (sb_check(c, cudaEventRecord(e, (cudaStream_t)c->comm_stream), "join event")) return 1;
     if (sb_check(c, cudaStreamWaitEvent((cudaStream_t)c->pub.stream, e, 0), "join wait")) return 1;
-    c->n_buckets = 0;
+    c->n_buckets = 0; c->gemm_reserve_sms = 0;
     ncclResult_t async = ncclSuccess;
     if (N.CommGetAsyncError((ncclComm_t)c->nccl_comm, &async) != ncclSuccess || async != ncclSuccess) {
         fprintf(stderr, "seraph_b200: NCCL reported an asynchronous error; aborting the communicator\n");

@@ -1027,7 +1027,10 @@ static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
     // square tile grid with everything above the diagonal skipped: only the tiles on or below it are enumerated
     const int tri = (p.causal == TC_CAUSAL_SKIP_UPPER && BN == TC_BM * CTAS && tiles_m == tiles_n) ? 1 : 0;
     const int tiles = tri ? tiles_m * (tiles_m + 1) / 2 : tiles_m * tiles_n;
-    const int slots = (c->pub.gpu_sm_count > 0 ? c->pub.gpu_sm_count : 148) / CTAS;
+    // one CTA (pair) per SM (pair); while gradient buckets are being reduced beside the backward pass the grid leaves the
+    // collective's SMs free, or the CTAs that found no SM would run their share of the tiles after all the others
+    const int sms = (c->pub.gpu_sm_count > 0 ? c->pub.gpu_sm_count : 148);
+    const int slots = max(1, (sms - (c->gemm_reserve_sms < sms ? c->gemm_reserve_sms : 0)) / CTAS);
     // tail split: cut the tiles of the last, partly filled wave into k pieces that fill it
     int split_full = tiles, split_s = 1;
     float* partial = nullptr;

@@ -144,6 +144,9 @@ typedef struct sb_ctx {
 
     /* data parallel */
     void* nccl_comm; int dp_rank, dp_world;
+    void* nccl_comm_wide;            /* second communicator over the same ranks without the CTA cap, for the step's last bucket (NULL: none) */
+    int dp_ctas;                     /* CTA cap of the communicator (0: NCCL's own choice) */
+    int gemm_reserve_sms;            /* SMs the persistent GEMM grids leave free: set while gradient buckets are being reduced */
     int dp_timeout_ms;               /* host-side limit for a step's collectives (SERAPH_B200_DP_TIMEOUT_MS, default 120 s) */
     void* comm_stream; void* ev_bucket[64]; int n_buckets;
     void* side_stream[4]; void* side_ev[5]; int side_ready;   /* side streams of the attention path (sequences run side by side) */

@@ -30,8 +30,10 @@
 
 int sb_ensure_tokens(sb_ctx_t* c, int T, int B);
 int sb_dp_bucket_ready(sb_ctx_t* c, float* p, size_t n);      /* dp.c: no-ops when not data parallel */
+int sb_dp_bucket_ready_last(sb_ctx_t* c, float* p, size_t n);
 int sb_dp_join(sb_ctx_t* c);
-int sb_dp_join_partial(sb_ctx_t* c);
+int sb_dp_mark_partial(sb_ctx_t* c);
+int sb_dp_wait_partial(sb_ctx_t* c);
 
 #define RMS_EPS 1e-5f   /* hard-coded in every training path of the reference (src/train_cuda.c:1984) */
 
@@ -791,23 +793,24 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
             else { size_t per = lora_layer_params(c); sb_dp_bucket_ready(c, c->LG + per * (size_t)l, per); }
         }
     }
-    if (full && reduce && early && early->on) {
-        /* every layer's gradients are with the all-reduce: AdamW of the layer ranges runs as soon as they are back, while the
-           embedding scatter below and the reduction of the last bucket (1.2 GB at the benchmark size) are still to come.  The
-           update is elementwise, so doing it in two launches changes no value. */
-        const size_t o0 = c->off[0].q;
-        if (sb_dp_join_partial(c) == 0) {
-            sb_adamw(c, c->W + o0, c->G + o0, c->M + o0, c->Vv + o0, c->n_params - o0, early->lr, 0.9f, 0.999f, 0.01f, 1e-8f, early->step,
-                     early->gscale, NULL, 0.f);
-            early->done = 1;
-        }
-    }
     if (full) {
         nan_mark(c, gh, (size_t)T * d, 8);
         sb_embedding_backward(c, c->tokens, gh, Gd, T, d, V);
         nan_mark(c, Gd, (size_t)V * d, 9);
-        if (reduce) sb_dp_bucket_ready(c, Gd, c->off[0].q);      /* embedding (LM head + scatter) and final norm */
-        if (reduce && c->XG) sb_dp_bucket_ready(c, c->XG, c->n_extras);
+    }
+    /* Every layer's gradients are with the all-reduce.  The last bucket (embedding with the LM head's share, and the final norm:
+       1.2 GB at the benchmark size) is handed over now; AdamW of the layer ranges starts as soon as the layers' buckets are back
+       and runs beside its reduction.  The update is elementwise, so doing it in two launches changes no value. */
+    const int early_on = full && reduce && early && early->on && sb_dp_mark_partial(c) == 0;
+    if (full && reduce) {
+        sb_dp_bucket_ready_last(c, Gd, c->off[0].q);
+        if (c->XG) sb_dp_bucket_ready_last(c, c->XG, c->n_extras);
+    }
+    if (early_on && sb_dp_wait_partial(c) == 0) {
+        const size_t o0 = c->off[0].q;
+        sb_adamw(c, c->W + o0, c->G + o0, c->M + o0, c->Vv + o0, c->n_params - o0, early->lr, 0.9f, 0.999f, 0.01f, 1e-8f, early->step,
+                 early->gscale, NULL, 0.f);
+        early->done = 1;
     }
 }
 

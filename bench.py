@@ -358,9 +358,14 @@ def run_attention(args, w):
             "gpu_launches": int(launches), "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": "attention_bwd", "achieved": useful, "peak": peak, "unit": "TFLOP/s",
                          "frac": useful / peak, "issued_tflops": useful * 3 * args.attn_products / 5.0,
-                         "issued_frac": useful * 3 * args.attn_products / 5.0 / peak, "traffic": None,
-                         "peak_note": f"{pk_kind} bf16 sustained {peak} TFLOP/s (FP16 MMAs run at the BF16 rate); achieved = useful FLOPs; "
-                                      f"issued = three FP16 passes per product x {args.attn_products} products per block"}}
+                         "issued_frac": useful * 3 * args.attn_products / 5.0 / peak,
+                         # DRAM bytes of the at_dkv_bwd_kernel launch from one ncu capture at this shape (1.38 GB read, 1.56 GB written),
+                         # scaled by the score elements when another shape is benchmarked
+                         "traffic": 2.94e9 * (B * H * S * S) / (8.0 * 16 * 2048 * 2048),
+                         "peak_note": f"{pk_kind} bf16 sustained {peak} TFLOP/s (FP16 MMAs run at the BF16 rate); achieved = useful FLOPs of the "
+                                      f"whole call (operand preparation, the on-chip dK/dV kernel, the dQ product); issued = three FP16 passes "
+                                      f"per product x {args.attn_products} products per block; the dK/dV kernel alone issues 0.67 of the peak "
+                                      f"(ncu, tensor pipe 49 % active)"}}
     if not args.no_cpu_baseline:
         line["reference_cuda"] = reference_cuda_legs(0)
     os.write(real_stdout, (json.dumps(line, default=float) + "\n").encode())

@@ -156,6 +156,11 @@ extern "C" unsigned* sb_amax_take(sb_ctx_t* c, const float* out, size_t n) {
         }
     return NULL;
 }
+extern "C" void sb_amax_forget(sb_ctx_t* c, const float* x) {
+    if (!c->parts_open || !c->hint_n) return;
+    for (int i = c->hint_n - 1; i >= 0; i--)
+        if (c->hint_tab[i].ptr == x) { c->hint_tab[i].n = 0; return; }      // the latest writer decides: a length nobody asks for
+}
 extern "C" float* sb_amax_lookup(sb_ctx_t* c, const float* x, size_t n) {
     if (!c->parts_open) return NULL;
     for (int i = c->hint_n - 1; i >= 0; i--)
@@ -168,6 +173,14 @@ extern "C" void sb_parts_set_amax(sb_ctx_t* c, const float* x, float* word) {
     int idx;
     while ((idx = c->parts_hash[h]) >= 0 && c->parts_tab[idx].ptr != x) h = (h + 1) & (size_t)(c->parts_hash_cap - 1);
     if (idx >= 0) c->parts_tab[idx].amax_ptr = word;
+}
+// x is being rewritten as a plain FP32 array: parts held for it in this step are stale
+extern "C" void sb_parts_invalidate(sb_ctx_t* c, const float* x) {
+    if (!c->parts_cache || !c->parts_open || !c->parts_n) return;
+    size_t h = parts_hash_of(x, c->parts_hash_cap);
+    int idx;
+    while ((idx = c->parts_hash[h]) >= 0 && c->parts_tab[idx].ptr != x) h = (h + 1) & (size_t)(c->parts_hash_cap - 1);
+    if (idx >= 0) c->parts_tab[idx].cur = 0;
 }
 extern "C" void sb_parts_free(sb_ctx_t* c) {
     parts_drop_arena(c);
@@ -292,6 +305,7 @@ extern "C" int sb_gemm_tc(sb_ctx_t* c, const float* A, const float* B, float* C,
             p.A.h1 = ha; p.A.h2 = ha + na; p.B.h1 = hb; p.B.h2 = hb + nb;
         }
         int tg = sb_tick_begin(c, SB_CLS_GEMM);
+        if (!acc) p.out_amax = sb_amax_take(c, C, (size_t)M * N);      // an announced output: the epilogue leaves max |C| for the next operand split
         bool ok = tc_launch(c, p, x3 ? 3 : 1);
         sb_tick_end(c, tg, 2.0 * M * N * K, 4.0 * ((double)M * K + (double)N * K + (double)M * N * (acc ? 2 : 1)));
         if (!ok) { sb_set_status(c, SB_ERR_CUDA); return 1; }
@@ -303,6 +317,7 @@ extern "C" int sb_gemm_tc(sb_ctx_t* c, const float* A, const float* B, float* C,
     double prep_bytes = (double)M * K * (a_kmajor ? (x3 ? 8 : 0) : (x3 ? 12 : 8)) + (double)N * K * (b_kmajor ? (x3 ? 8 : 0) : (x3 ? 12 : 8));
     sb_tick_end(c, tp, 0.0, prep_bytes);
     int tg = sb_tick_begin(c, SB_CLS_GEMM);
+    if (!acc) p.out_amax = sb_amax_take(c, C, (size_t)M * N);
     bool ok = tc_launch(c, p, x3 ? 3 : 1);
     sb_tick_end(c, tg, 2.0 * M * N * K, 4.0 * ((double)M * K + (double)N * K + (double)M * N * (acc ? 2 : 1)));
     if (!ok) { sb_set_status(c, SB_ERR_CUDA); return 1; }

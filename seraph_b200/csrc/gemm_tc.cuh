@@ -84,6 +84,7 @@ struct TcProblem {
     int M, N, K, acc, nbatch, causal;
     TcEpi epi;
     const float* amax_a; const float* amax_b;      // FP16 split: device floats max |A|, max |B|; NULL = TF32 split
+    unsigned* out_amax = nullptr;                  // when set (plain stores only, no accumulation into C): max |C| is left there as float bits
 };
 
 // --------------------------------------------------------------------------- PTX helpers
@@ -144,13 +145,8 @@ __device__ __forceinline__ void tc_mma_f16_pair(uint32_t tmem_d, uint64_t adesc,
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 // FP16 split: power-of-two exponent s with amax * 2^s in [2^14, 2^15) (0 for an all-zero operand); 2^s as a float
-__device__ __forceinline__ int tc_f16_shift(float amax) {
-    const int e = (int)((__float_as_uint(amax) >> 23) & 255u) - 127;
-    if (amax == 0.f || e < -100) return 0;
-    const int sh = 14 - e;
-    return sh < -100 ? -100 : (sh > 100 ? 100 : sh);
-}
-__device__ __forceinline__ float tc_pow2(int sh) { return __uint_as_float((uint32_t)(127 + sh) << 23); }
+__device__ __forceinline__ int tc_f16_shift(float amax) { return sb_f16_shift(amax); }
+__device__ __forceinline__ float tc_pow2(int sh) { return sb_pow2(sh); }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
 }
@@ -348,7 +344,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
                float* __restrict__ Cbase, long ldc, long c_batch_stride, int M, int N, int K, int acc, int causal,
                int a_c2_base, int a_c2_step, int b_c2_base, int b_c2_step, int swap_mask,
                int split_full, int split_s, float* __restrict__ partial, const TcEpi epi,
-               int nbatch, int total_items, int snake, int tri, int store_warps, const float* __restrict__ amax_a, const float* __restrict__ amax_b, int* status) {
+               int nbatch, int total_items, int snake, int tri, int store_warps, const float* __restrict__ amax_a, const float* __restrict__ amax_b,
+               unsigned* __restrict__ out_amax, int* status) {
     constexpr int SWZ = BK * 4;
     constexpr int BROWS = BN / CTAS;                             // B rows this CTA loads
     constexpr int TILE_M = TC_BM * CTAS;
@@ -661,6 +658,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
 #pragma unroll
                 for (int j = 0; j < COLS_PER_WARP; j++) accr[j] = accr[j] * ua * ub;
             }
+            if (out_amax && !w.split) {
+                // largest magnitude of the tile for whoever splits C into FP16 parts next (rows and columns past the edge are zero)
+                float m = 0.f;
+#pragma unroll
+                for (int j = 0; j < COLS_PER_WARP; j++) m = fmaxf(m, fabsf(accr[j]));
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                if (lane == 0 && m > 0.f) atomicMax(out_amax, __float_as_uint(m));
+            }
             if (CONV && store_warps) {
                 // plain tile: write this warp's rows into its quarter's half of the staging buffer and hand it to the store warp
                 const int b = q & 1;
@@ -813,7 +819,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
 // (the loads of a thread are independent, and a grid of many small CTAs keeps the latency hidden).
 static __global__ void __launch_bounds__(256) tc_splitk_fixup_kernel(const float* __restrict__ partial, float* __restrict__ C, long ldc,
                                                                      int M, int N, int acc, int BN, int ctas, int split_full, int split_s,
-                                                                     int nblocks) {
+                                                                     int nblocks, unsigned* __restrict__ out_amax) {
     const int bn4 = BN >> 2;
     const long item = (long)blockIdx.x * blockDim.x + threadIdx.x;
     const int blk = (int)(item / (TC_BM * bn4)), i = (int)(item % (TC_BM * bn4));
@@ -845,6 +851,15 @@ static __global__ void __launch_bounds__(256) tc_splitk_fixup_kernel(const float
         for (int p = 0; p < 8; p++) if (p < split_s) { v.x += o[p].x; v.y += o[p].y; v.z += o[p].z; v.w += o[p].w; }
         if (whole) *(float4*)crow = v;
         else { crow[0] = v.x; if (n0 + col + 1 < N) crow[1] = v.y; if (n0 + col + 2 < N) crow[2] = v.z; if (n0 + col + 3 < N) crow[3] = v.w; }
+        if (out_amax) {
+            float m = fabsf(v.x);
+            if (whole) m = fmaxf(fmaxf(m, fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+            else { if (n0 + col + 1 < N) m = fmaxf(m, fabsf(v.y)); if (n0 + col + 2 < N) m = fmaxf(m, fabsf(v.z)); if (n0 + col + 3 < N) m = fmaxf(m, fabsf(v.w)); }
+            // one atomic per warp: among the lanes still here, non-negative floats order like their bits
+            const unsigned live = __activemask();
+            const unsigned wm = __reduce_max_sync(live, __float_as_uint(m));
+            if ((int)(threadIdx.x & 31) == __ffs(live) - 1 && wm != 0u) atomicMax(out_amax, wm);
+        }
     }
 }
 
@@ -1081,19 +1096,19 @@ static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
         cfg.attrs = at; cfg.numAttrs = 1;
         if (cudaLaunchKernelEx(&cfg, kern, mAh, mAl, mBh, mBl, p.C, p.ldc, p.c_batch_stride, p.M, p.N, p.K, p.acc, p.causal,
                                p.A.c2_base, p.A.c2_step, p.B.c2_base, p.B.c2_step, swap_mask, split_full, split_s, partial, p.epi,
-                               nbatch, total_items, snake, tri, store_warps, p.amax_a, p.amax_b, c->d_status) != cudaSuccess) return false;
+                               nbatch, total_items, snake, tri, store_warps, p.amax_a, p.amax_b, p.out_amax, c->d_status) != cudaSuccess) return false;
     } else {
         kern<<<grid, THREADS, smem, (cudaStream_t)c->pub.stream>>>(mAh, mAl, mBh, mBl, p.C, p.ldc, p.c_batch_stride, p.M, p.N, p.K, p.acc,
                                                                      p.causal, p.A.c2_base, p.A.c2_step, p.B.c2_base, p.B.c2_step,
                                                                      swap_mask, split_full, split_s, partial, p.epi,
-                                                                     nbatch, total_items, snake, tri, store_warps, p.amax_a, p.amax_b, c->d_status);
+                                                                     nbatch, total_items, snake, tri, store_warps, p.amax_a, p.amax_b, p.out_amax, c->d_status);
     }
     c->launches++;
     if (split_s > 1) {
         const int nblocks = (tiles - split_full) * CTAS;
         const long items = (long)nblocks * TC_BM * (BN / 4);
         tc_splitk_fixup_kernel<<<(unsigned)((items + 255) / 256), 256, 0, (cudaStream_t)c->pub.stream>>>(partial, p.C, p.ldc, p.M, p.N, p.acc, BN, CTAS,
-                                                                                                        split_full, split_s, nblocks);
+                                                                                                        split_full, split_s, nblocks, p.acc ? nullptr : p.out_amax);
         c->launches++;
     }
     return cudaGetLastError() == cudaSuccess;

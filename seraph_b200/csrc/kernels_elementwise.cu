@@ -114,6 +114,50 @@ __global__ void __launch_bounds__(EW_THREADS) swiglu_bwd_kernel(const float* __r
     sb_block_amax(amu, amax_dup);
 }
 
+// The two SwiGLU kernels with their outputs written only as FP16 operand parts (hi, lo) of the products that read them: the
+// scale comes from a bound formed on the device from the largest magnitudes the inputs' producers left behind,
+//   |silu(g) u| <= max|g| max|u|,   |dup| = |d silu(g)| <= max|d| max|g|,   |dgate| = |d u silu'(g)| <= 1.1 max|d| max|u|
+// (silu' lies in [-0.1, 1.1]).  12 instead of 24 bytes per element forward, 20 instead of 44 backward, counting the split pass
+// that no longer runs.
+__global__ void __launch_bounds__(EW_THREADS) swiglu_parts_kernel(const float4* __restrict__ gate, const float4* __restrict__ up,
+                                                                  uint2* __restrict__ h1, uint2* __restrict__ h2, size_t n4,
+                                                                  const float* __restrict__ amax_g, const float* __restrict__ amax_u,
+                                                                  float* __restrict__ bound_out) {
+    const float bound = fminf(__ldg(amax_g) * __ldg(amax_u), 3.0e38f);
+    const float sc = sb_pow2(sb_f16_shift(bound));
+    if (blockIdx.x == 0 && threadIdx.x == 0) *bound_out = bound;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        const float4 g = gate[i], u = up[i];
+        const float r0 = ew_apply<OP_SWIGLU>(g.x, u.x) * sc, r1 = ew_apply<OP_SWIGLU>(g.y, u.y) * sc;
+        const float r2 = ew_apply<OP_SWIGLU>(g.z, u.z) * sc, r3 = ew_apply<OP_SWIGLU>(g.w, u.w) * sc;
+        uint2 a, b;
+        sb_split2(r0, r1, a.x, b.x); sb_split2(r2, r3, a.y, b.y);
+        h1[i] = a; h2[i] = b;
+    }
+}
+__global__ void __launch_bounds__(EW_THREADS) swiglu_bwd_parts_kernel(const float4* __restrict__ gate, const float4* __restrict__ up,
+                                                                      const float4* __restrict__ dout,
+                                                                      uint2* __restrict__ dg1, uint2* __restrict__ dg2,
+                                                                      uint2* __restrict__ du1, uint2* __restrict__ du2, size_t n4,
+                                                                      const float* __restrict__ amax_g, const float* __restrict__ amax_u,
+                                                                      const float* __restrict__ amax_d,
+                                                                      float* __restrict__ bound_dg, float* __restrict__ bound_du) {
+    const float ad = __ldg(amax_d);
+    const float bg = fminf(1.1f * ad * __ldg(amax_u), 3.0e38f), bu = fminf(ad * __ldg(amax_g), 3.0e38f);
+    const float sg_ = sb_pow2(sb_f16_shift(bg)), su = sb_pow2(sb_f16_shift(bu));
+    if (blockIdx.x == 0 && threadIdx.x == 0) { *bound_dg = bg; *bound_du = bu; }
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        const float4 g = gate[i], u = up[i], d = dout[i];
+        float4 dg, du;
+        SWIGLU_BWD_ONE(g.x, u.x, d.x, dg.x, du.x) SWIGLU_BWD_ONE(g.y, u.y, d.y, dg.y, du.y)
+        SWIGLU_BWD_ONE(g.z, u.z, d.z, dg.z, du.z) SWIGLU_BWD_ONE(g.w, u.w, d.w, dg.w, du.w)
+        uint2 a, b, e, f;
+        sb_split2(dg.x * sg_, dg.y * sg_, a.x, b.x); sb_split2(dg.z * sg_, dg.w * sg_, a.y, b.y);
+        sb_split2(du.x * su, du.y * su, e.x, f.x); sb_split2(du.z * su, du.w * su, e.y, f.y);
+        dg1[i] = a; dg2[i] = b; du1[i] = e; du2[i] = f;
+    }
+}
+
 // out[t,:] = E[tok[t],:]; one CTA per few rows, float4 when d%4==0.  Token ids
 // beyond the table set the status word and read row 0 instead of faulting.
 __global__ void __launch_bounds__(EW_THREADS) embed_lookup_kernel(const uint32_t* __restrict__ tok, const float* __restrict__ E,
@@ -234,7 +278,7 @@ void sb_add(sb_ctx_t* c, const float* a, const float* b, float* o, size_t n) { e
 void sb_mul(sb_ctx_t* c, const float* a, const float* b, float* o, size_t n) { ew_launch<OP_MUL, true>(c, a, b, o, n); }
 void sb_silu(sb_ctx_t* c, const float* x, float* y, size_t n) { ew_launch<OP_SILU, false>(c, x, x, y, n); }
 void sb_silu_backward(sb_ctx_t* c, const float* x, const float* dy, float* dx, size_t n) { ew_launch<OP_SILU_BWD, true>(c, x, dy, dx, n); }
-void sb_swiglu(sb_ctx_t* c, const float* g, const float* u, float* o, size_t n) { ew_launch<OP_SWIGLU, true>(c, g, u, o, n); }
+void sb_swiglu(sb_ctx_t* c, const float* g, const float* u, float* o, size_t n) { sb_parts_invalidate(c, o); ew_launch<OP_SWIGLU, true>(c, g, u, o, n); }
 
 void sb_scale(sb_ctx_t* c, float* a, size_t n, float alpha) {
     if (!n) return;
@@ -251,11 +295,42 @@ void sb_mul_backward(sb_ctx_t* c, const float* A, const float* B, const float* d
 void sb_swiglu_backward(sb_ctx_t* c, const float* gate, const float* up, const float* dout, float* dgate, float* dup, size_t n) {
     if (!n) return;
     int vec = aligned16(gate) && aligned16(up) && aligned16(dout) && aligned16(dgate) && aligned16(dup);
+    sb_parts_invalidate(c, dgate); sb_parts_invalidate(c, dup);
     int tk = sb_tick_begin(c, SB_CLS_SWIGLU);
     swiglu_bwd_kernel<<<ew_grid(c, (n + 3) / 4), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(gate, up, dout, dgate, dup, n, vec,
                                                                                                   sb_amax_take(c, dgate, n), sb_amax_take(c, dup, n));
     sb_tick_end(c, tk, 0.0, 20.0 * (double)n);
     c->launches++;
+}
+
+int sb_swiglu_parts(sb_ctx_t* c, const float* gate, const float* up, float* out, size_t n) {
+    if (!n || (n & 7) || !aligned16(gate) || !aligned16(up)) return 0;
+    float* ag = sb_amax_lookup(c, gate, n); float* au = sb_amax_lookup(c, up, n);
+    if (!ag || !au) return 0;
+    void* h; float* bound; int fresh;
+    if (!sb_parts_find(c, out, n, &h, &bound, &fresh)) return 0;
+    sb_amax_forget(c, out);
+    int tk = sb_tick_begin(c, SB_CLS_SWIGLU);
+    swiglu_parts_kernel<<<ew_grid(c, n / 4), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>((const float4*)gate, (const float4*)up, (uint2*)h,
+                                                                                         (uint2*)((uint16_t*)h + n), n / 4, ag, au, bound);
+    sb_tick_end(c, tk, 0.0, 12.0 * (double)n);
+    c->launches++;
+    return 1;
+}
+int sb_swiglu_backward_parts(sb_ctx_t* c, const float* gate, const float* up, const float* dout, float* dgate, float* dup, size_t n) {
+    if (!n || (n & 7) || !aligned16(gate) || !aligned16(up) || !aligned16(dout)) return 0;
+    float* ag = sb_amax_lookup(c, gate, n); float* au = sb_amax_lookup(c, up, n); float* ad = sb_amax_lookup(c, dout, n);
+    if (!ag || !au || !ad) return 0;
+    void *hg, *hu; float *bg, *bu; int fresh;
+    if (!sb_parts_find(c, dgate, n, &hg, &bg, &fresh) || !sb_parts_find(c, dup, n, &hu, &bu, &fresh)) return 0;
+    sb_amax_forget(c, dgate); sb_amax_forget(c, dup);
+    int tk = sb_tick_begin(c, SB_CLS_SWIGLU);
+    swiglu_bwd_parts_kernel<<<ew_grid(c, n / 4), EW_THREADS, 0, (cudaStream_t)c->pub.stream>>>(
+        (const float4*)gate, (const float4*)up, (const float4*)dout, (uint2*)hg, (uint2*)((uint16_t*)hg + n), (uint2*)hu, (uint2*)((uint16_t*)hu + n),
+        n / 4, ag, au, ad, bg, bu);
+    sb_tick_end(c, tk, 0.0, 20.0 * (double)n);
+    c->launches++;
+    return 1;
 }
 
 void sb_embed_lookup(sb_ctx_t* c, const uint32_t* tok, const float* E, float* out, int T, int d, int V) {

@@ -410,6 +410,53 @@ __global__ void __launch_bounds__(RB_THREADS) softmax_kernel(const float* __rest
 // row because it overwrites x.  One warp per row, the row in registers (cols % 4 == 0, cols <= 128 * NV): 8 bytes
 // per element forward, 12 backward.  Other shapes: one CTA per row.
 // ---------------------------------------------------------------------------
+// The same rows with y written only as FP16 operand parts: every |y_i| = |x_i| rstd |w_i| is at most sqrt(cols) max|w| (x_i^2 cannot
+// exceed the row's sum of squares), so that bound sets the scale and no pass over y looks for its maximum or splits it again.
+template <int NV>
+__global__ void __launch_bounds__(RB_THREADS) rmsnorm_warp_parts_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                                        uint2* __restrict__ h1, uint2* __restrict__ h2, int rows, int cols, float eps,
+                                                                        float* __restrict__ bound_out) {
+    const int lane = threadIdx.x & 31, warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+    const int c4 = cols >> 2;
+    float4 s[NV];
+    float wm = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+        const int j = lane + 32 * i;
+        s[i] = j < c4 ? ((const float4*)w)[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+        wm = sb_amax4(wm, s[i]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
+    const float bound = fminf(sqrtf((float)cols) * wm * 1.0001f, 3.0e38f);
+    const float sc = sb_pow2(sb_f16_shift(bound));
+    if (warp == 0 && lane == 0) *bound_out = bound;
+    for (int r = warp; r < rows; r += nwarps) {
+        const float4* xr = (const float4*)(x + (size_t)r * cols);
+        float4 v[NV];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            int j = lane + 32 * i;
+            v[i] = j < c4 ? xr[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+            ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+        }
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / cols + eps);
+        uint2* o1 = h1 + (size_t)r * c4; uint2* o2 = h2 + (size_t)r * c4;
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            int j = lane + 32 * i;
+            if (j < c4) {
+                // the FP32 value first, exactly as the plain kernel forms it, then the scale (a power of two: exact)
+                const float y0 = v[i].x * inv * s[i].x, y1 = v[i].y * inv * s[i].y, y2 = v[i].z * inv * s[i].z, y3 = v[i].w * inv * s[i].w;
+                uint2 a, b;
+                sb_split2(y0 * sc, y1 * sc, a.x, b.x); sb_split2(y2 * sc, y3 * sc, a.y, b.y);
+                o1[j] = a; o2[j] = b;
+            }
+        }
+    }
+}
 template <int NV>
 __global__ void __launch_bounds__(RB_THREADS) qk_norm_warp_kernel(float* __restrict__ x, float* __restrict__ rms_out, int rows, int cols, float eps) {
     const int lane = threadIdx.x & 31, warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
@@ -715,6 +762,7 @@ extern "C" {
 
 void sb_rmsnorm(sb_ctx_t* c, const float* x, const float* w, float* y, int rows, int cols, float eps) {
     if (rows <= 0 || cols <= 0) return;
+    sb_parts_invalidate(c, y);
     int grid = rows < sm_count(c) * 8 ? rows : sm_count(c) * 8;
     int vec = (cols % 4 == 0) && aligned16(x) && aligned16(w) && aligned16(y);
     int tk = sb_tick_begin(c, SB_CLS_NORM_FWD);
@@ -736,6 +784,27 @@ void sb_rmsnorm(sb_ctx_t* c, const float* x, const float* w, float* y, int rows,
     rmsnorm_kernel<<<grid, RB_THREADS, 0, (cudaStream_t)c->pub.stream>>>(x, w, y, rows, cols, eps, vec);
     sb_tick_end(c, tk, 0.0, 8.0 * rows * cols);
     c->launches++;
+}
+
+// y only as the FP16 parts of the registered tensor `y`; 1 = done, 0 = not possible here (call sb_rmsnorm)
+int sb_rmsnorm_parts(sb_ctx_t* c, const float* x, const float* w, float* y, int rows, int cols, float eps) {
+    if (rows < 64 || cols <= 0 || (cols & 7) || cols > 4096 || !aligned16(x) || !aligned16(w)) return 0;
+    void* h; float* bound; int fresh;
+    const size_t n = (size_t)rows * cols;
+    if (!sb_parts_find(c, y, n, &h, &bound, &fresh)) return 0;
+    sb_amax_forget(c, y);
+    int wgrid = (rows + 7) / 8;
+    { int cap = sm_count(c) * 2, k = (wgrid + cap - 1) / cap; wgrid = (wgrid + k - 1) / k; }
+    cudaStream_t st = (cudaStream_t)c->pub.stream;
+    uint2* h1 = (uint2*)h; uint2* h2 = (uint2*)((uint16_t*)h + n);
+    int tk = sb_tick_begin(c, SB_CLS_NORM_FWD);
+    if (cols <= 512)       rmsnorm_warp_parts_kernel<4><<<wgrid, RB_THREADS, 0, st>>>(x, w, h1, h2, rows, cols, eps, bound);
+    else if (cols <= 1024) rmsnorm_warp_parts_kernel<8><<<wgrid, RB_THREADS, 0, st>>>(x, w, h1, h2, rows, cols, eps, bound);
+    else if (cols <= 2048) rmsnorm_warp_parts_kernel<16><<<wgrid, RB_THREADS, 0, st>>>(x, w, h1, h2, rows, cols, eps, bound);
+    else                   rmsnorm_warp_parts_kernel<32><<<wgrid, RB_THREADS, 0, st>>>(x, w, h1, h2, rows, cols, eps, bound);
+    sb_tick_end(c, tk, 0.0, 8.0 * rows * cols);
+    c->launches++;
+    return 1;
 }
 
 // number of CTAs the rmsnorm backward uses for `rows` rows (also the row count of its partial buffer)

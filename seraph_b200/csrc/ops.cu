@@ -88,6 +88,7 @@ static int index_single(sb_ctx_t* c, int T, int len) {
 void sb_gemm(sb_ctx_t* c, const float* A, const float* B, float* C, int M, int N, int K, int tA, int tB, int acc) {
     if (M <= 0 || N <= 0 || K < 0) return;
     int mode = c->pub.use_bf16 ? SB_GEMM_BF16 : c->gemm_mode;
+    sb_amax_forget(c, C);                 /* a maximum left for C by an earlier writer is void; the tensor-core launch leaves a new one when asked */
     if (mode != SB_GEMM_SIMT && sb_gemm_tc(c, A, B, C, M, N, K, tA, tB, acc, mode) == 0) return;
     int t = sb_tick_begin(c, SB_CLS_GEMM);
     sb_gemm_simt(c, A, B, C, M, N, K, tA, tB, acc);

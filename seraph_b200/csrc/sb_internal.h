@@ -185,6 +185,12 @@ void sb_silu_backward(sb_ctx_t*, const float* x, const float* dy, float* dx, siz
 void sb_mul_backward(sb_ctx_t*, const float* A, const float* B, const float* dC, float* dA, float* dB, size_t n);
 void sb_swiglu(sb_ctx_t*, const float* gate, const float* up, float* out, size_t n);
 void sb_swiglu_backward(sb_ctx_t*, const float* gate, const float* up, const float* dout, float* dgate, float* dup, size_t n);
+/* The same two, writing `out` (dgate, dup) only as the FP16 parts of registered tensors, scaled by bounds formed from the largest
+   magnitudes their producers left for the inputs; 1 = done, 0 = not possible here (no parts, no hints): call the plain one */
+int  sb_swiglu_parts(sb_ctx_t*, const float* gate, const float* up, float* out, size_t n);
+int  sb_rmsnorm_parts(sb_ctx_t*, const float* x, const float* w, float* y, int rows, int cols, float eps);      /* bound: sqrt(cols) max|w| */
+int  sb_swiglu_backward_parts(sb_ctx_t*, const float* gate, const float* up, const float* dout, float* dgate, float* dup, size_t n);
+void sb_amax_forget(sb_ctx_t*, const float* x);      /* x is written by something that leaves no maximum: earlier hints for it are void */
 void sb_seq_index(sb_ctx_t*, const uint32_t* seq_starts, int B, int T, uint32_t* pos_ids, uint32_t* seq_ids);
 /* Between begin and end the FP16 parts of GEMM operands are kept and reused by later calls on the same array; the caller
  * guarantees that no operand array is written inside the region. */
@@ -207,6 +213,7 @@ float* sb_amax_lookup(sb_ctx_t*, const float* x, size_t n);
 void sb_parts_set_amax(sb_ctx_t*, const float* x, float* word);
 /* 1: x[n] is registered and the step is open; *h = its two parts (h, h + n), *amax its scale word, *fresh = parts must be made now */
 int sb_parts_find(sb_ctx_t*, const float* x, size_t n, void** h, float** amax, int* fresh);
+void sb_parts_invalidate(sb_ctx_t*, const float* x);      /* x is rewritten as plain FP32: parts held for it are stale */
 void sb_rope2(sb_ctx_t*, float* q, float* k, const uint32_t* pos_ids, int T, int Hq, int Hkv, int hd, float theta, int max_pos, int backward);
 void sb_rope(sb_ctx_t*, const float* in, float* out, const uint32_t* pos_ids, int T, int H, int hd, float theta,
              int max_pos, int backward);
@@ -281,5 +288,27 @@ static __device__ __forceinline__ void sb_block_amax(float v, unsigned* out) {
 }
 static __device__ __forceinline__ float sb_amax4(float m, float4 v) {
     return fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+}
+/* FP16 operand parts: an operand whose largest magnitude (or a bound of it) is `amax` is scaled by 2^s with amax 2^s in
+   [2^14, 2^15) (s = 0 for an all-zero operand) and every scaled value x is stored as hi = fp16(x), lo = fp16(x - hi).  Both parts
+   are floating point, so a bound that is loose by 2^k only moves the few values below 2^-(18-k) of the largest into fp16's
+   subnormal range; the bound must be a true upper bound, or hi overflows. */
+static __device__ __forceinline__ int sb_f16_shift(float amax) {
+    const int e = (int)((__float_as_uint(amax) >> 23) & 255u) - 127;
+    if (amax == 0.f || e < -100) return 0;
+    const int sh = 14 - e;
+    return sh < -100 ? -100 : (sh > 100 ? 100 : sh);
+}
+static __device__ __forceinline__ float sb_pow2(int sh) { return __uint_as_float((unsigned)(127 + sh) << 23); }
+/* two scaled values as packed parts (x0 in the low half); x - hi by the mixed-precision fma hi * -1 + x, exact */
+static __device__ __forceinline__ void sb_split2(float x0, float x1, unsigned& hi, unsigned& lo) {
+    asm("{\n\t.reg .b16 h0, h1, m1;\n\t.reg .f32 l0, l1;\n\t"
+        "cvt.rn.f16x2.f32 %0, %3, %2;\n\t"
+        "mov.b32 {h0, h1}, %0;\n\t"
+        "mov.b16 m1, 0xBC00;\n\t"
+        "fma.rn.f32.f16 l0, h0, m1, %2;\n\t"
+        "fma.rn.f32.f16 l1, h1, m1, %3;\n\t"
+        "cvt.rn.f16x2.f32 %1, l1, l0;\n\t}"
+        : "=&r"(hi), "=r"(lo) : "f"(x0), "f"(x1));
 }
 #endif

@@ -520,6 +520,7 @@ static int ensure_activations(sb_ctx_t* c, int T, int need_logits_grad) {
     }
     sb_parts_register(c, 1, c->hidden_norm, (size_t)T * c->d);
     sb_parts_register(c, 1, c->dlogits, (size_t)T * c->V);
+    sb_parts_register(c, 1, c->g_gate, (size_t)T * c->F); sb_parts_register(c, 1, c->g_up, (size_t)T * c->F);      /* written as parts by the SwiGLU backward */
     return 0;
 }
 
@@ -655,6 +656,15 @@ static int nan_tripped(sb_ctx_t* c, const train_state_t* st, int T) {
 static void forward_pass(sb_ctx_t* c, int T, int max_seq, float theta, int use_lora) {
     const int d = c->d, F = c->F, qd = c->qd, kvd = c->kvd, L = c->L;
     const size_t Td = (size_t)T * d;
+    /* producers that may write an operand only as FP16 parts: every product that reads it must take parts */
+    const int ffn_lora = use_lora && (c->lora_mask & 0x70);
+    const int ffn_parts = !c->nan_on && !ffn_lora && sb_gemm_reads_f16_parts(c, T, d, F, 0, 1) && sb_gemm_reads_f16_parts(c, d, F, T, 1, 0);
+    /* the normalised rows are read by the projections and by their weight gradients only (adapters read them too: FP32 stays then) */
+    const int norm_ok = !c->nan_on && !use_lora;
+    const int xa_parts = norm_ok && sb_gemm_reads_f16_parts(c, T, qd, d, 0, 1) && sb_gemm_reads_f16_parts(c, T, kvd, d, 0, 1) &&
+                         sb_gemm_reads_f16_parts(c, qd, d, T, 1, 0) && sb_gemm_reads_f16_parts(c, kvd, d, T, 1, 0);
+    const int xf_parts = norm_ok && sb_gemm_reads_f16_parts(c, T, F, d, 0, 1) && sb_gemm_reads_f16_parts(c, F, d, T, 1, 0);
+    const int hn_parts = norm_ok && sb_gemm_reads_f16_parts(c, T, c->V, d, 0, 1) && sb_gemm_reads_f16_parts(c, c->V, d, T, 1, 0);
     nan_mark(c, c->W, (size_t)c->V * d, nan_weight_idx(c));
     sb_embed_lookup(c, c->tokens, c->W, c->act[0].layer_in, T, d, c->V);
     nan_mark(c, c->act[0].layer_in, Td, 7);
@@ -662,8 +672,10 @@ static void forward_pass(sb_ctx_t* c, int T, int max_seq, float theta, int use_l
         const sb_layer_off_t* o = &c->off[l];
         sb_layer_act_t* a = &c->act[l];
         float* next_in = (l + 1 < L) ? c->act[l + 1].layer_in : c->final_in;
-        sb_amax_announce(c, a->x_norm_attn, Td);           /* producers of GEMM operands leave max |x| behind for the operand split */
-        sb_rmsnorm(c, a->layer_in, c->W + o->in_norm, a->x_norm_attn, T, d, RMS_EPS);
+        if (!(xa_parts && sb_rmsnorm_parts(c, a->layer_in, c->W + o->in_norm, a->x_norm_attn, T, d, RMS_EPS))) {
+            sb_amax_announce(c, a->x_norm_attn, Td);       /* producers of GEMM operands leave max |x| behind for the operand split */
+            sb_rmsnorm(c, a->layer_in, c->W + o->in_norm, a->x_norm_attn, T, d, RMS_EPS);
+        }
         /* runs of products that share an operand keep its prepared parts (the adapters' scratch, rewritten in between, is dropped from the kept set at every write) */
         sb_gemm_keep_begin(c);
         linear_fwd(c, use_lora, l, 0, a->x_norm_attn, c->W + o->q, c->head_norm ? a->q_pre : a->q, T, d, qd, 0);
@@ -686,20 +698,30 @@ static void forward_pass(sb_ctx_t* c, int T, int max_seq, float theta, int use_l
         sb_attention(c, a->q, a->k, a->v, a->attn_out, a->lse, c->seq_starts, c->seq_ids, T, c->Hq, c->Hkv, c->hd);
         sb_copy(c, a->post_attn_in, a->layer_in, Td * sizeof(float));
         linear_fwd(c, use_lora, l, 3, a->attn_out, c->W + o->o, a->post_attn_in, T, qd, d, 1);
-        sb_amax_announce(c, a->x_norm_ffn, Td);
-        sb_rmsnorm(c, a->post_attn_in, c->W + o->post_norm, a->x_norm_ffn, T, d, RMS_EPS);
+        if (!(xf_parts && sb_rmsnorm_parts(c, a->post_attn_in, c->W + o->post_norm, a->x_norm_ffn, T, d, RMS_EPS))) {
+            sb_amax_announce(c, a->x_norm_ffn, Td);
+            sb_rmsnorm(c, a->post_attn_in, c->W + o->post_norm, a->x_norm_ffn, T, d, RMS_EPS);
+        }
         sb_gemm_keep_begin(c);
+        sb_amax_announce(c, a->gate, (size_t)T * F);        /* the products' epilogues leave max |gate|, max |up| for the bound below */
         linear_fwd(c, use_lora, l, 4, a->x_norm_ffn, c->W + o->gate, a->gate, T, d, F, 0);
+        sb_amax_announce(c, a->up, (size_t)T * F);
         linear_fwd(c, use_lora, l, 5, a->x_norm_ffn, c->W + o->up, a->up, T, d, F, 0);
         sb_gemm_keep_end(c);
-        sb_amax_announce(c, a->ffn_hidden, (size_t)T * F);
-        sb_swiglu(c, a->gate, a->up, a->ffn_hidden, (size_t)T * F);
+        /* silu(gate) * up is read only as an operand (down projection, its weight gradient): when those products take FP16 parts
+           the kernel writes the parts and no FP32 copy */
+        if (!(ffn_parts && sb_swiglu_parts(c, a->gate, a->up, a->ffn_hidden, (size_t)T * F))) {
+            sb_amax_announce(c, a->ffn_hidden, (size_t)T * F);
+            sb_swiglu(c, a->gate, a->up, a->ffn_hidden, (size_t)T * F);
+        }
         sb_copy(c, next_in, a->post_attn_in, Td * sizeof(float));
         linear_fwd(c, use_lora, l, 6, a->ffn_hidden, c->W + o->down, next_in, T, F, d, 1);
         nan_mark(c, next_in, Td, nan_fwd_base(c) + (uint32_t)l);
     }
-    sb_amax_announce(c, c->hidden_norm, Td);
-    sb_rmsnorm(c, c->final_in, c->W + (size_t)c->V * d, c->hidden_norm, T, d, RMS_EPS);
+    if (!(hn_parts && sb_rmsnorm_parts(c, c->final_in, c->W + (size_t)c->V * d, c->hidden_norm, T, d, RMS_EPS))) {
+        sb_amax_announce(c, c->hidden_norm, Td);
+        sb_rmsnorm(c, c->final_in, c->W + (size_t)c->V * d, c->hidden_norm, T, d, RMS_EPS);
+    }
     nan_mark(c, c->hidden_norm, Td, 2); nan_mark(c, c->final_in, Td, 6);
     sb_gemm(c, c->hidden_norm, c->untied ? c->XW + extras_lm_off(c) : c->W, c->logits, T, c->V, d, 0, 1, 0);       /* tied LM head, or the separate one */
     nan_mark(c, c->logits, (size_t)T * c->V, 1);
@@ -723,17 +745,22 @@ static void backward_pass(sb_ctx_t* c, int T, int B, int max_seq, float theta, i
     sb_amax_announce(c, gh, (size_t)T * d);
     sb_rmsnorm_backward(c, c->final_in, c->W + (size_t)V * d, gx, NULL, gh, full ? Gd + (size_t)V * d : norm_sink, T, d, RMS_EPS);
     nan_mark(c, gh, (size_t)T * d, 5); nan_mark(c, gh, (size_t)T * d, 0);
+    const int ffn_lora = !full && (c->lora_mask & 0x70);
+    const int ffn_parts_bwd = !c->nan_on && !ffn_lora && sb_gemm_reads_f16_parts(c, T, d, F, 0, 0) && (!full || sb_gemm_reads_f16_parts(c, F, d, T, 1, 0));
     for (int l = L - 1; l >= 0; l--) {
         const sb_layer_off_t* o = &c->off[l];
         sb_layer_act_t* a = &c->act[l];
         /* FFN */
         sb_gemm_keep_begin(c);                       /* gh (and, with adapters, what they read) is split once for the whole group */
         if (full) sb_gemm(c, gh, a->ffn_hidden, Gd + o->down, d, F, T, 1, 0, 1);
+        sb_amax_announce(c, c->g_ffn, (size_t)T * F);
         sb_gemm(c, gh, c->W + o->down, c->g_ffn, T, F, d, 0, 0, 0);
         if (!full) lora_bwd(c, l, 6, gh, a->ffn_hidden, c->g_ffn, T);
         sb_gemm_keep_end(c);
-        sb_amax_announce(c, c->g_gate, (size_t)T * F); sb_amax_announce(c, c->g_up, (size_t)T * F);
-        sb_swiglu_backward(c, a->gate, a->up, c->g_ffn, c->g_gate, c->g_up, (size_t)T * F);
+        if (!(ffn_parts_bwd && sb_swiglu_backward_parts(c, a->gate, a->up, c->g_ffn, c->g_gate, c->g_up, (size_t)T * F))) {
+            sb_amax_announce(c, c->g_gate, (size_t)T * F); sb_amax_announce(c, c->g_up, (size_t)T * F);
+            sb_swiglu_backward(c, a->gate, a->up, c->g_ffn, c->g_gate, c->g_up, (size_t)T * F);
+        }
         sb_gemm_keep_begin(c);
         if (full) {
             sb_gemm(c, c->g_gate, a->x_norm_ffn, Gd + o->gate, F, d, T, 1, 0, 1);

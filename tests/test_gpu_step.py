@@ -364,7 +364,7 @@ def test_c1_lora_step_on_tensor_cores_matches_oracle(ctx):
     tok = tokens_for(cfg, 1024, 33)
     ref = O.train_step(cfg, p, tok, ss, lora=lo, rank=rank, alpha=alpha, mask=mask, lora_exact=1)
     outs = []
-    for keep in (1, 0):
+    for keep in (1, 0, 1):
         ctx.set_parts_cache(keep)
         ctx.lib.seraph_b200_reset_model(ctx.h)
         st = api.TrainState(cfg, p)
@@ -387,16 +387,18 @@ def test_c1_lora_step_on_tensor_cores_matches_oracle(ctx):
 
 
 def test_operand_parts_kept_within_a_step_change_nothing(ctx):
-    """The FP16 parts of weights and saved activations are made once per call and shared by the call's products.  Three
-    optimizer steps (the weights move between them), then a step on fewer tokens and one on the full batch again: losses,
-    gradients and weights are bit-identical to the run in which every product prepares its own operands."""
+    """The FP16 parts of weights and saved activations are made once per call and shared by the call's products, and the SwiGLU
+    kernels write their outputs straight into that arena (scaled by a bound instead of the exact maximum, so those operands
+    round differently in their last bits).  Three optimizer steps (the weights move between them), then a step on fewer tokens
+    and one on the full batch again: losses, gradients and weights agree with the run in which every product prepares its own
+    operands to a few 1e-6 (both inside the parity bound), and the run with the arena repeats bit for bit."""
     from seraph_b200 import api
     cfg = C1
     p = cfg.init_params(77)
     ss = list(range(0, 2049, 256))
     tok = tokens_for(cfg, 2048, 5)
     runs = []
-    for keep in (1, 0):
+    for keep in (1, 0, 1):
         ctx.set_parts_cache(keep)
         ctx.lib.seraph_b200_reset_model(ctx.h)
         st = api.TrainState(cfg, p, lr=1e-2)
@@ -409,8 +411,12 @@ def test_operand_parts_kept_within_a_step_change_nothing(ctx):
         runs.append((losses, st.get(1), st.get(0)))
         st.close()
     ctx.set_parts_cache(1)
-    assert runs[0][0] == runs[1][0], (runs[0][0], runs[1][0])
-    assert np.array_equal(runs[0][1], runs[1][1]) and np.array_equal(runs[0][2], runs[1][2])
+    assert np.allclose(runs[0][0], runs[1][0], rtol=2e-6, atol=0), (runs[0][0], runs[1][0])
+    eg, ew = O.rel_l2(runs[0][1], runs[1][1]), O.rel_l2(runs[0][2], runs[1][2])
+    print(f"arena on vs off: gradients rel-L2 {eg:.2e}, weights {ew:.2e}")
+    # two roundings of the same sums: each is within 2.5e-6 of the oracle, so they may differ from each other by their root sum
+    assert eg < 6e-6 and ew < 2e-6, (eg, ew)
+    assert runs[0][0] == runs[2][0] and np.array_equal(runs[0][1], runs[2][1]) and np.array_equal(runs[0][2], runs[2][2])
     assert runs[0][0][0] != runs[0][0][2]          # the weights did move
 
 

@@ -262,6 +262,11 @@ unsigned long long seraph_b200_launch_count(cuda_train_context_t* ctx, int reset
  * occurring rows in ascending order, their token counts, and the token
  * positions sorted by (row, position).  Returns the number of rows or -1. */
 int seraph_b200_embedding_segments(cuda_train_context_t* ctx, int T, int V, int* rows_out, int* counts_out, int* sorted_pos_out);
+/* C = op(A) op(B) like cuda_train_matmul_transpose without accumulation, plus the largest |C| that the tensor-core kernel's
+ * epilogue leaves behind for the next operand split inside a training step (test surface).  1: *amax_out set; 0: the shape
+ * does not run on that kernel (C is computed all the same); -1: bad arguments. */
+int seraph_b200_matmul_amax(cuda_train_context_t* ctx, cuda_buffer_t* A, cuda_buffer_t* B, cuda_buffer_t* C, int M, int N, int K,
+                            int transpose_A, int transpose_B, float* amax_out);
 /* Fused SwiGLU: out = silu(gate)*up; backward gives dgate and dup from gate, up, dout. */
 void seraph_b200_swiglu(cuda_train_context_t* ctx, cuda_buffer_t* gate, cuda_buffer_t* up, cuda_buffer_t* out, size_t count);
 void seraph_b200_swiglu_backward(cuda_train_context_t* ctx, cuda_buffer_t* gate, cuda_buffer_t* up, cuda_buffer_t* grad_out,

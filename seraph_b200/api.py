@@ -90,6 +90,7 @@ def load():
         "seraph_b200_nan_flags": (i, [vp, vp, i]), "seraph_b200_profiler_totals": (i, [vp, vp]),
         "seraph_b200_state_set_debug_nan": (None, [vp, i]), "seraph_b200_state_nan_detected": (i, [vp]),
         "seraph_b200_embedding_segments": (i, [vp, i, i, vp, vp, vp]),
+        "seraph_b200_matmul_amax": (i, [vp, vp, vp, vp, i, i, i, i, i, vp]),
         "seraph_b200_swiglu": (None, [vp, B, B, B, sz]), "seraph_b200_swiglu_backward": (None, [vp, B, B, B, B, B, sz]),
         "seraph_b200_timer_start": (None, [vp]), "seraph_b200_timer_stop": (f, [vp]),
         "seraph_b200_download_logits": (i, [vp, vp, i]), "seraph_b200_reset_model": (i, [vp]),

@@ -323,6 +323,24 @@ void cuda_train_set_profiler(cuda_train_context_t* ctx, cuda_profiler_t* prof) {
     if (c) { c->profiler = prof; c->prof_depth = 0; c->tick_prof = 0; }
 }
 
+// Extension (test surface): C = op(A) op(B) as cuda_train_matmul_transpose does without accumulation, and the largest |C| the
+// tensor-core kernel's epilogue (and its split-K fix-up) left behind for the next operand split.  Returns 1 with *amax_out set
+// when the launch produced it, 0 when this shape does not run on that kernel (C is computed all the same), -1 on bad arguments.
+int seraph_b200_matmul_amax(cuda_train_context_t* ctx, cuda_buffer_t* A, cuda_buffer_t* B, cuda_buffer_t* C, int M, int N, int K,
+                            int transpose_A, int transpose_B, float* amax_out) {
+    sb_ctx_t* c = sb_priv(ctx);
+    if (!c || !A || !B || !C || !amax_out || M <= 0 || N <= 0 || K <= 0) return -1;
+    sb_parts_open(c);
+    sb_amax_announce(c, C->data, (size_t)M * N);
+    sb_gemm(c, A->data, B->data, C->data, M, N, K, transpose_A, transpose_B, 0);
+    float* w = sb_amax_lookup(c, C->data, (size_t)M * N);
+    int got = 0;
+    if (w && cudaMemcpyAsync(amax_out, w, sizeof(float), cudaMemcpyDeviceToHost, (cudaStream_t)c->pub.stream) == cudaSuccess &&
+        cudaStreamSynchronize((cudaStream_t)c->pub.stream) == cudaSuccess) got = 1;
+    sb_parts_close(c);
+    return got;
+}
+
 // ---------------------------------------------------------------------------
 // LoRA (src/cuda_train_context.cu:3240-3290)
 //   h = X A^T ; gB += dY^T (s h) ; gh = s (dY B) ; gA += gh^T X

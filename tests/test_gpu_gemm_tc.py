@@ -76,3 +76,29 @@ def test_tc_gemm_long_k_and_reproducible(ctx):
     ctx.check()
     assert rel_l2(o3, ref) < 2e-6
     ctx.release(a, b, c, c2)
+
+
+@pytest.mark.parametrize("mode", [4, 0])
+@pytest.mark.parametrize("tA,tB", [(0, 1), (0, 0), (1, 0)])
+@pytest.mark.parametrize("M,N,K", [(384, 512, 1024), (130, 257, 96), (1000, 1000, 40), (2048, 2048, 512), (256, 512, 16384),
+                                   (4096, 1024, 256), (300, 300, 64), (2049, 6144, 128)])
+def test_epilogue_leaves_the_largest_magnitude_of_the_output(ctx, M, N, K, tA, tB, mode):
+    """Inside a training step the product's epilogue (and the fix-up pass of tiles whose k range was cut into pieces) leaves
+    max |C| behind, and the kernels that write the next operand as FP16 parts scale by bounds formed from it: a value below the
+    true maximum would overflow FP16.  The maximum of floats is exact, so it must equal the maximum of the downloaded result,
+    with ragged edges, with whole and split tiles, in every layout."""
+    import ctypes
+    r = np.random.default_rng(11 * M + 5 * N + K + tA + 2 * tB)
+    A = r.standard_normal((K, M) if tA else (M, K)).astype(np.float32)
+    B = r.standard_normal((N, K) if tB else (K, N)).astype(np.float32)
+    A[r.integers(0, A.shape[0]), r.integers(0, A.shape[1])] = 37.0            # one outlier, so that the maximum sits in one tile
+    a, b, c = ctx.upload(A), ctx.upload(B), ctx.upload(np.full((M, N), 1e9, np.float32))
+    ctx.set_gemm_mode(mode)
+    am = ctypes.c_float(-1.0)
+    got = ctx.lib.seraph_b200_matmul_amax(ctx.h, a.b, b.b, c.b, M, N, K, tA, tB, ctypes.byref(am))
+    out = c.numpy(shape=(M, N))
+    ctx.set_gemm_mode(4)
+    ctx.check()
+    assert got == 1, "shape expected on the tensor-core kernel"
+    assert am.value == float(np.abs(out).max()), (am.value, float(np.abs(out).max()))
+    ctx.release(a, b, c)

@@ -660,11 +660,12 @@ static void forward_pass(sb_ctx_t* c, int T, int max_seq, float theta, int use_l
     const int ffn_lora = use_lora && (c->lora_mask & 0x70);
     const int ffn_parts = !c->nan_on && !ffn_lora && sb_gemm_reads_f16_parts(c, T, d, F, 0, 1) && sb_gemm_reads_f16_parts(c, d, F, T, 1, 0);
     /* the normalised rows are read by the projections and by their weight gradients only (adapters read them too: FP32 stays then) */
-    const int norm_ok = !c->nan_on && !use_lora;
-    const int xa_parts = norm_ok && sb_gemm_reads_f16_parts(c, T, qd, d, 0, 1) && sb_gemm_reads_f16_parts(c, T, kvd, d, 0, 1) &&
+    const int xa_parts = !c->nan_on && !(use_lora && (c->lora_mask & 0x07)) &&
+                         sb_gemm_reads_f16_parts(c, T, qd, d, 0, 1) && sb_gemm_reads_f16_parts(c, T, kvd, d, 0, 1) &&
                          sb_gemm_reads_f16_parts(c, qd, d, T, 1, 0) && sb_gemm_reads_f16_parts(c, kvd, d, T, 1, 0);
-    const int xf_parts = norm_ok && sb_gemm_reads_f16_parts(c, T, F, d, 0, 1) && sb_gemm_reads_f16_parts(c, F, d, T, 1, 0);
-    const int hn_parts = norm_ok && sb_gemm_reads_f16_parts(c, T, c->V, d, 0, 1) && sb_gemm_reads_f16_parts(c, c->V, d, T, 1, 0);
+    const int xf_parts = !c->nan_on && !(use_lora && (c->lora_mask & 0x30)) &&
+                         sb_gemm_reads_f16_parts(c, T, F, d, 0, 1) && sb_gemm_reads_f16_parts(c, F, d, T, 1, 0);
+    const int hn_parts = !c->nan_on && sb_gemm_reads_f16_parts(c, T, c->V, d, 0, 1) && sb_gemm_reads_f16_parts(c, c->V, d, T, 1, 0);
     nan_mark(c, c->W, (size_t)c->V * d, nan_weight_idx(c));
     sb_embed_lookup(c, c->tokens, c->W, c->act[0].layer_in, T, d, c->V);
     nan_mark(c, c->act[0].layer_in, Td, 7);

@@ -22,7 +22,7 @@
 // performed in L2).  A dK/dV element is only ever touched by the one CTA that owns its key, one chain's additions have
 // been performed before the next chain's are issued, and the output is zeroed (or holds the caller's values) before the
 // launch: the result does not depend on scheduling and is the same bits on every run.
-// dS^T also leaves the chip, as FP16 parts laid out [head slot][key][query]: dQ = dS K is one more product on the
+// dS^T also leaves the chip, as FP16 parts laid out [head slot = (sequence, K/V head, group member)][key][query]: dQ = dS K is one more product on the
 // GEMM kernel (M = queries, K = keys up to the diagonal, A read MN-major).  P never reaches memory, dS is written once
 // and read once: 8 bytes per score element instead of the 20 of the score-materialising path.
 //
@@ -423,7 +423,7 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
                 ok = mbar_wait(ew_sync, 0);
                 if (issuer && ok) {
                     for (int hi = 0; hi < g; hi++) {
-                        const int y = (int)(((size_t)(b * g + hi) * Hkv + kvh) * Sp) + k0;
+                        const int y = (int)(((size_t)(b * Hkv + kvh) * g + hi) * Sp) + k0;
                         for (int i = 0; i < 4; i++) { ab_tma_store(&mS1, ews + 16384, k0 - 128 + i * 32, y); ab_tma_store(&mS2, ews + 16384, k0 - 128 + i * 32, y); }
                     }
                     AB_BULK_COMMIT();
@@ -438,7 +438,7 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
             ok = mbar_wait(&sdp_full[e], (t >> 1) & 1);
             if (!ok) break;
             tc_fence_after();
-            const size_t hb = (size_t)(b * g + hi) * Hkv + kvh;
+            const size_t hb = (size_t)(b * Hkv + kvh) * g + hi;
             uint32_t sr[16], dr[16];
             ab_ld16(tmem_base + lane_addr + (uint32_t)(AB_COL_S(e) + ch * 16), sr);
             ab_ld16(tmem_base + lane_addr + (uint32_t)(AB_COL_DP(e) + ch * 16), dr);
@@ -526,7 +526,7 @@ at_dkv_bwd_kernel(const __grid_constant__ CUtensorMap mQ1, const __grid_constant
 }
 
 // q, do, k, v: the FP16 parts of Q, dO [T, Hq*128] and K, V [T, Hkv*128]; amax_*: the device words their scales derive from;
-// ds_bound: the device word that bounds |dS|.  dS1/dS2: the parts of dS^T, laid out [sequence][group member][K-V head][Sp][Sp]
+// ds_bound: the device word that bounds |dS|.  dS1/dS2: the parts of dS^T, laid out [sequence][K-V head][group member][Sp][Sp]
 // (key rows, query columns).  dK and dV are added into (the caller zeroes them when they do not accumulate).
 // Returns 0 when the kernel was launched, 1 when this path does not take the call.
 extern "C" int sb_attention_fused_dkv(sb_ctx_t* c, const void* q1, const void* q2, const void* do1, const void* do2,

@@ -441,8 +441,8 @@ extern "C" int sb_attention_tc_backward(sb_ctx_t* c, const float* Q, const float
     const bool all_scores = f16 && c->attn_flash && !c->attn_fused && hd == 128 && c->h_seq_n <= 240 && n_all * 8 <= all_limit;
     const size_t group_bytes = AT_SIDE * per_stream * sizeof(float);
     // 128-wide heads, default mode: dK and dV accumulate on chip in one launch over all sequences and K/V heads that leaves only
-    // the FP16 parts of dS^T (4 bytes per score, [sequence][group member][K-V head][key][query]); dQ is then one product per
-    // sequence and group member.  seraph_b200_set_attn_flash(ctx, 2) or SERAPH_B200_ATTN_FLASH=2 selects the older
+    // the FP16 parts of dS^T (4 bytes per score, [sequence][K-V head][group member][key][query]); dQ is then one product per
+    // sequence over all its query heads.  seraph_b200_set_attn_flash(ctx, 2) or SERAPH_B200_ATTN_FLASH=2 selects the older
     // score-materialising path, 3 this one, for every shape.
     // attn_flash 1 (default) and 3 take this path (it measured faster at every shape tried: 16 % at 2048 tokens with two query heads
     // per K/V head, 30 % without head grouping)
@@ -504,12 +504,14 @@ extern "C" int sb_attention_tc_backward(sb_ctx_t* c, const float* Q, const float
                 if (S <= 0) continue;
                 flops += 5.0 * Hq * (double)S * S * hd;
                 if (ns2 > 1) c->pub.stream = c->side_stream[b % ns2];
-                for (int r = 0; r < g && ok; r++) {
-                    __half* d1 = a + ((size_t)(b * g + r) * Hkv) * (size_t)sb;
+                {
+                    // all query heads of the sequence in one launch: head h reads slot b Hq + h of dS^T and K/V head h / g
+                    __half* d1 = a + ((size_t)b * Hq) * (size_t)sb;
                     const AtParts pds = {d1, d1 + n_all, consts + 1};
-                    ok = ok && at_gemm(c, op_scratch(bb, pds, S, Sp, Hkv, 1), op_tokens_mn(K, pk, t0, kvd, Hkv, hd, 0, 1),
-                                       dQ + (size_t)t0 * qd + (size_t)r * hd, qd, (long)g * hd, S, hd, S, 0, Hkv, TC_CAUSAL_K_UPTO_M,
-                                       nullptr, pds.amax, pk.amax);                                                           // dQ = dS K
+                    TcOperand kop = op_tokens_mn(K, pk, t0, kvd, Hkv, hd, 0, 1);
+                    kop.c2_div = g;
+                    ok = ok && at_gemm(c, op_scratch(bb, pds, S, Sp, Hq, 1), kop, dQ + (size_t)t0 * qd, qd, (long)hd, S, hd, S, 0, Hq,
+                                       TC_CAUSAL_K_UPTO_M, nullptr, pds.amax, pk.amax);                                       // dQ = dS K
                 }
             }
             at_join(c, ns2, main_stream);

@@ -67,7 +67,8 @@ struct TcOperand {
     int mn;                              // 1: the array is [K, rows], rows contiguous (CTA-pair kernel only)
     const void* h1; const void* h2;      // prepared FP16 parts (same layout as hi), or NULL
     int c2_dim; long c2_stride;          // third tensor-map dimension (floats); c2_dim = 1 for a plain matrix
-    int c2_base, c2_step;                // slot of batch b = c2_base + b*c2_step
+    int c2_base, c2_step;                // slot of batch b = c2_base + (b / c2_div)*c2_step
+    int c2_div = 1;                      // batch entries that share a slot (query heads of one K/V head)
 };
 // What the epilogue writes for an accumulator value x at (row, col) of batch b (attention's score-sized products):
 //   TC_EPI_EXP  col <= row ? exp(x*scale - vec[row*vec_row_stride + b*vec_batch_stride]) : 0      (P from S and the log-sum-exp)
@@ -342,7 +343,7 @@ __global__ void __launch_bounds__((CTAS == 2 && NTERMS == 3) ? TC_CONV_THREADS :
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
                const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
                float* __restrict__ Cbase, long ldc, long c_batch_stride, int M, int N, int K, int acc, int causal,
-               int a_c2_base, int a_c2_step, int b_c2_base, int b_c2_step, int swap_mask,
+               int a_c2_base, int a_c2_step, int b_c2_base, int b_c2_step, int b_c2_div, int swap_mask,
                int split_full, int split_s, float* __restrict__ partial, const TcEpi epi,
                int nbatch, int total_items, int snake, int tri, int store_warps, const float* __restrict__ amax_a, const float* __restrict__ amax_b,
                unsigned* __restrict__ out_amax, int* status) {
@@ -420,7 +421,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
                 const int item = tc_item(k, cid, G, snake);
                 TcWork w;
                 if (item >= total_items || !tc_work<BN, BKE, CTAS>(item, (int)rank, M, N, K, causal, nbatch, split_full, split_s, tri, w)) continue;
-                const int a_c2 = a_c2_base + w.batch * a_c2_step, b_c2 = b_c2_base + w.batch * b_c2_step;
+                const int a_c2 = a_c2_base + w.batch * a_c2_step, b_c2 = b_c2_base + (b_c2_div > 1 ? w.batch / b_c2_div : w.batch) * b_c2_step;
                 for (int it = 0; it < w.num_kb && ok; it++, git++) {
                     const int s = git % STAGES, kb = w.kb_begin + it;
                     ok = mbar_wait(&empty[s], ((git / STAGES) & 1) ^ 1);
@@ -1095,11 +1096,11 @@ static bool tc_launch_t(sb_ctx_t* c, const TcProblem& p) {
         at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
         cfg.attrs = at; cfg.numAttrs = 1;
         if (cudaLaunchKernelEx(&cfg, kern, mAh, mAl, mBh, mBl, p.C, p.ldc, p.c_batch_stride, p.M, p.N, p.K, p.acc, p.causal,
-                               p.A.c2_base, p.A.c2_step, p.B.c2_base, p.B.c2_step, swap_mask, split_full, split_s, partial, p.epi,
+                               p.A.c2_base, p.A.c2_step, p.B.c2_base, p.B.c2_step, p.B.c2_div, swap_mask, split_full, split_s, partial, p.epi,
                                nbatch, total_items, snake, tri, store_warps, p.amax_a, p.amax_b, p.out_amax, c->d_status) != cudaSuccess) return false;
     } else {
         kern<<<grid, THREADS, smem, (cudaStream_t)c->pub.stream>>>(mAh, mAl, mBh, mBl, p.C, p.ldc, p.c_batch_stride, p.M, p.N, p.K, p.acc,
-                                                                     p.causal, p.A.c2_base, p.A.c2_step, p.B.c2_base, p.B.c2_step,
+                                                                     p.causal, p.A.c2_base, p.A.c2_step, p.B.c2_base, p.B.c2_step, p.B.c2_div,
                                                                      swap_mask, split_full, split_s, partial, p.epi,
                                                                      nbatch, total_items, snake, tri, store_warps, p.amax_a, p.amax_b, p.out_amax, c->d_status);
     }

@@ -418,13 +418,11 @@ __global__ void __launch_bounds__(RB_THREADS) rmsnorm_warp_parts_kernel(const fl
                                                                         float* __restrict__ bound_out) {
     const int lane = threadIdx.x & 31, warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
     const int c4 = cols >> 2;
-    float4 s[NV];
-    float wm = 0.f;
+    float wm = 0.f;                       // (w is read again from cache in the output loop: keeping it would double the registers)
 #pragma unroll
     for (int i = 0; i < NV; i++) {
         const int j = lane + 32 * i;
-        s[i] = j < c4 ? ((const float4*)w)[j] : make_float4(0.f, 0.f, 0.f, 0.f);
-        wm = sb_amax4(wm, s[i]);
+        if (j < c4) wm = sb_amax4(wm, ((const float4*)w)[j]);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
@@ -449,7 +447,8 @@ __global__ void __launch_bounds__(RB_THREADS) rmsnorm_warp_parts_kernel(const fl
             int j = lane + 32 * i;
             if (j < c4) {
                 // the FP32 value first, exactly as the plain kernel forms it, then the scale (a power of two: exact)
-                const float y0 = v[i].x * inv * s[i].x, y1 = v[i].y * inv * s[i].y, y2 = v[i].z * inv * s[i].z, y3 = v[i].w * inv * s[i].w;
+                const float4 s = ((const float4*)w)[j];
+                const float y0 = v[i].x * inv * s.x, y1 = v[i].y * inv * s.y, y2 = v[i].z * inv * s.z, y3 = v[i].w * inv * s.w;
                 uint2 a, b;
                 sb_split2(y0 * sc, y1 * sc, a.x, b.x); sb_split2(y2 * sc, y3 * sc, a.y, b.y);
                 o1[j] = a; o2[j] = b;

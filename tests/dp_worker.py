@@ -2,6 +2,7 @@
 NCCL the library opens with dlopen is the one LD_LIBRARY_PATH offers).  Not collected by pytest.
 
     python dp_worker.py real  <rank> <world> <dir> <accum>     two or more real ranks over NCCL, one GPU each
+    python dp_worker.py lora  <rank> <world> <dir>             the same with a LoRA step (adapters on all seven projections)
     python dp_worker.py fake  <mode> <dir>                     one rank of a pretended world of 2 over a fake libnccl.so.2
 """
 import os
@@ -36,6 +37,32 @@ def real(rank, world, d, accum):
     ctx.lib.cuda_download_full_weights(ctx.h, st.h)
     np.savez(os.path.join(d, f"rank{rank}.npz"), w=st.get(0), g=st.get(1), m=st.get(2), v=st.get(3), loss=np.array(losses),
              counters=np.array(st.counters()))
+    st.close()
+    ctx.close()
+
+
+LORA = dict(rank=4, alpha=8.0, mask=0x7F, seed=9)
+
+
+def lora(rank, world, d):
+    """Every rank steps the same adapters on its own tokens; only the adapters' gradients are reduced."""
+    from seraph_b200 import api
+    import oracle_lib as O
+    cfg, ss = O.TINY, np.array(O.TINY_SEQS, np.int32)
+    ctx = api.Context(rank)
+    assert ctx.lib.seraph_dp_init_from_env(ctx.h) == 0 and ctx.lib.seraph_dp_world(ctx.h) == world
+    p = cfg.init_params(7, norm_jitter=0.1)
+    _, n = cfg.lora_tensors(LORA["rank"], LORA["mask"])
+    lo = (0.05 * np.random.default_rng(LORA["seed"]).standard_normal(n)).astype(np.float32)
+    st = api.TrainState(cfg, p)
+    st.attach_lora(LORA["rank"], LORA["alpha"], LORA["mask"], lo)
+    assert ctx.lib.seraph_b200_set_lora_exact(ctx.h, 1) == 0
+    tok = np.random.default_rng(200 + rank).integers(0, cfg.V, int(ss[-1])).astype(np.int32)
+    loss = api.step_lora_batch(ctx, st, tok, ss)
+    ctx.check()
+    assert ctx.lib.seraph_dp_wait(ctx.h, 20000) == 0
+    ctx.lib.cuda_download_lora_weights(ctx.h, st.lora_ptr())
+    np.savez(os.path.join(d, f"lora_rank{rank}.npz"), w=st.lora_get(0), g=st.lora_get(1), loss=np.array([loss]))
     st.close()
     ctx.close()
 
@@ -87,5 +114,7 @@ def fake(mode, d):
 if __name__ == "__main__":
     if sys.argv[1] == "real":
         real(int(sys.argv[2]), int(sys.argv[3]), sys.argv[4], int(sys.argv[5]))
+    elif sys.argv[1] == "lora":
+        lora(int(sys.argv[2]), int(sys.argv[3]), sys.argv[4])
     else:
         fake(sys.argv[2], sys.argv[3])

@@ -109,3 +109,34 @@ def test_two_ranks_over_nccl_stay_identical_and_match_the_oracle(tmp_path, accum
     w, m, v = p.copy(), np.zeros_like(p), np.zeros_like(p)
     O.lib().ref_adamw(w, (g_sum / world).astype(np.float32), m, v, p.size, lr, 0.9, 0.999, 0.01, 1e-8, 1)
     assert rel_l2(out[0]["w"], w) < 1e-6 and rel_l2(out[0]["m"], m) < 1e-5
+
+
+def test_two_ranks_lora_step_reduces_the_adapter_gradients(tmp_path):
+    """LoRA under data parallelism: each rank steps the same adapters (all seven projections, full chain rule) on its own
+    tokens; the adapters' gradients are summed over NCCL layer by layer, AdamW applies their mean.  Both ranks end with
+    bit-identical adapters, equal to the oracle's AdamW on the mean of the two oracle gradients."""
+    if gpu_count() < 2:
+        pytest.skip("needs two GPUs")
+    import dp_worker as W
+    world = 2
+    procs = [subprocess.Popen([sys.executable, WORKER, "lora", str(r), str(world), str(tmp_path)],
+                              env=dict(os.environ, NCCL_NVLS_ENABLE="0", RANK=str(r), WORLD_SIZE=str(world),
+                                       SERAPH_DP_ID_FILE=str(tmp_path / "nccl_id.bin"))) for r in range(world)]
+    for p in procs:
+        assert p.wait(timeout=600) == 0
+    out = [np.load(tmp_path / f"lora_rank{r}.npz") for r in range(world)]
+    assert np.array_equal(out[0]["w"], out[1]["w"]) and np.array_equal(out[0]["g"], out[1]["g"])
+    cfg, L = TINY, W.LORA
+    p = cfg.init_params(7, norm_jitter=0.1)
+    _, n = cfg.lora_tensors(L["rank"], L["mask"])
+    lo = (0.05 * np.random.default_rng(L["seed"]).standard_normal(n)).astype(np.float32)
+    g_sum = np.zeros(n, np.float32)
+    for r in range(world):
+        tok = np.random.default_rng(200 + r).integers(0, cfg.V, TINY_SEQS[-1]).astype(np.int32)
+        ref = O.train_step(cfg, p, tok, TINY_SEQS, lora=lo, rank=L["rank"], alpha=L["alpha"], mask=L["mask"], lora_exact=1)
+        g_sum += ref["grads"]
+        assert abs(out[r]["loss"][0] - ref["loss"]) < 1e-5 * abs(ref["loss"])
+    assert rel_l2(out[0]["g"], g_sum) < 1e-5
+    w, m, v = lo.copy(), np.zeros_like(lo), np.zeros_like(lo)
+    O.lib().ref_adamw(w, (g_sum / world).astype(np.float32), m, v, n, O.lib().ref_effective_lr(3.14e-4, 1, 1), 0.9, 0.999, 0.01, 1e-8, 1)
+    assert rel_l2(out[0]["w"], w) < 1e-6

@@ -152,7 +152,8 @@ static int dp_bucket(sb_ctx_t* c, float* p, size_t n, int wide) {
     if (c->dp_world <= 1 || !n) return 0;
     cudaEvent_t e = (cudaEvent_t)c->ev_bucket[c->n_buckets % 62];      /* 62 and 63 are the join events */
     c->n_buckets++;
-    c->gemm_reserve_sms = (c->dp_ctas + 1) & ~1;                        /* whole SM pairs; until the join */
+    /* whole SM pairs, until the join; not for buckets whose reduction is over in a fraction of one product's time (adapter gradients) */
+    if (n * sizeof(float) >= ((size_t)32 << 20)) c->gemm_reserve_sms = (c->dp_ctas + 1) & ~1;
     if (sb_check(c, cudaEventRecord(e, (cudaStream_t)c->pub.stream), "bucket event")) return 1;
     if (sb_check(c, cudaStreamWaitEvent((cudaStream_t)c->comm_stream, e, 0), "bucket wait")) return 1;
     ncclComm_t comm = (ncclComm_t)((wide && c->nccl_comm_wide) ? c->nccl_comm_wide : c->nccl_comm);

@@ -73,6 +73,10 @@ class ClockSampler:
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
+        # nvidia-smi numbers the GPUs of the machine; a CUDA_VISIBLE_DEVICES list of indices renumbers them for the process
+        vis = [v.strip() for v in os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",") if v.strip()]
+        if vis and all(v.isdigit() for v in vis) and 0 <= index < len(vis):
+            index = int(vis[index])
         self.rows, self.proc, self.index = [], None, index
 
     def start(self):
